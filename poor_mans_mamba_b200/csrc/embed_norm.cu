@@ -1,0 +1,111 @@
+// Embedding gather and the fused "residual add + RMSNorm" kernel.
+//
+// The residual stream is float in every mode.  Branch outputs (mixer / feed-forward
+// results in the storage type) are folded into it by the same kernel that produces
+// the next normalised activation, so the stream is read and written once per norm.
+//
+// Formulas: h[t] = mult * E[tok[t]]  (reference src/ops/gpu/embed.cu:5-16);
+// y = x * (1/sqrt(mean(x^2)+eps)) * w  (reference src/ops/gpu/rms_norm.cu:6-26).
+#include "common.cuh"
+
+namespace pmm {
+
+template <typename S>
+__global__ void embed_kernel(float* __restrict__ out, const S* __restrict__ table,
+                             const int* __restrict__ tokens, float mult, int D, int V) {
+  const int t = blockIdx.x;
+  int id = tokens[t];
+  const bool ok = id >= 0 && id < V;  // the host rejects such ids before launching
+  if (!ok) id = 0;
+  const S* row = table + static_cast<size_t>(id) * D;
+  float* o = out + static_cast<size_t>(t) * D;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = ok ? mult * ldf(row + i) : 0.f;
+}
+
+// One block per output row.  h' = (h + sa*a) + sb*b ; out = h' * rsqrt(mean(h'^2)+eps) * w.
+// rows == nullptr: row r of h is updated in place and out[r] written.
+// rows != nullptr: h is left untouched, out[r] is computed from row rows[r].
+template <typename S>
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const S* __restrict__ a, float sa,
+                                   const S* __restrict__ b, float sb, const float* __restrict__ w,
+                                   float eps, S* __restrict__ out, const int* __restrict__ rows,
+                                   int D) {
+  extern __shared__ float buf[];
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const size_t src = static_cast<size_t>(rows ? rows[r] : r) * D;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float v = h[src + i];
+    if (a) v = v + sa * ldf(a + src + i);
+    if (b) v = v + sb * ldf(b + src + i);
+    buf[i] = v;
+    ss += v * v;
+    if (!rows && (a || b)) h[src + i] = v;
+  }
+  if (!out) return;
+  const float total = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(total / static_cast<float>(D) + eps);
+  S* o = out + static_cast<size_t>(r) * D;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) stf(o + i, buf[i] * inv * w[i]);
+}
+
+__global__ void scale_f32_kernel(float* __restrict__ x, float s, size_t n) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) x[i] *= s;
+}
+
+template <typename S>
+__global__ void cast_scale_kernel(float* __restrict__ out, const S* __restrict__ in, float s, size_t n) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = s * ldf(in + i);
+}
+
+}  // namespace pmm
+
+PMM_EXPORT int pmm_embed(void* out, const void* table, const int* tokens, float mult, int T, int D,
+                         int V, int dtype, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  PMM_DISPATCH_DTYPE(dtype, S, pmm::embed_kernel<S><<<T, 256, 0, stream>>>(
+                                   static_cast<float*>(out), static_cast<const S*>(table), tokens,
+                                   mult, D, V));
+  return pmm::launch_status();
+}
+
+PMM_EXPORT int pmm_add_rmsnorm(void* h, const void* a, float sa, const void* b, float sb,
+                               const float* w, float eps, void* out, const int* rows, int R, int D,
+                               int dtype, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (out && !w) return PMM_ERR_BAD_ARGUMENT;
+  const size_t smem = static_cast<size_t>(D) * sizeof(float);
+  if (smem > 200 * 1024) return PMM_ERR_BAD_ARGUMENT;  // width beyond one block's shared memory
+  const int threads = D >= 1024 ? 256 : 128;
+  PMM_DISPATCH_DTYPE(dtype, S, {
+    auto kern = pmm::add_rmsnorm_kernel<S>;
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(smem));
+      if (e != cudaSuccess) return static_cast<int>(e);
+    }
+    kern<<<R, threads, smem, stream>>>(static_cast<float*>(h), static_cast<const S*>(a), sa,
+                                       static_cast<const S*>(b), sb, w, eps, static_cast<S*>(out),
+                                       rows, D);
+  });
+  return pmm::launch_status();
+}
+
+PMM_EXPORT int pmm_scale_f32(float* x, float s, long long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  pmm::scale_f32_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(
+      x, s, static_cast<size_t>(n));
+  return pmm::launch_status();
+}
+
+PMM_EXPORT int pmm_cast_scale(float* out, const void* in, float s, long long n, int dtype,
+                              cudaStream_t stream) {
+  if (n <= 0) return 0;
+  PMM_DISPATCH_DTYPE(dtype, S, pmm::cast_scale_kernel<S><<<static_cast<unsigned>((n + 255) / 256), 256,
+                                                          0, stream>>>(
+                                   out, static_cast<const S*>(in), s, static_cast<size_t>(n)));
+  return pmm::launch_status();
+}

@@ -1,0 +1,39 @@
+"""What a step hands to the parts: the flattened batch on the device and scratch memory."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+from .workspace import Workspace
+
+Tensor = torch.Tensor
+
+
+@dataclass
+class StepContext:
+    """One step's batch.  All index tensors are int32 on the device.
+
+    tokens[T], positions[T] (absolute position of each token in its request), seq_of[T]
+    (index of the token's sequence within the step), cu_seqlens[n_seq+1] (token offsets of
+    the sequences), slots[n_seq] (fixed-state slot of each sequence), logit_rows[n_rows]
+    (token rows whose logits are wanted).  ``decode_only``: every sequence brings exactly one
+    token.  ``kv_len_bound``: an upper bound of position+1 over the step (host value, for
+    launch decisions only).  ``new_lens`` / ``past_lens``: host copies per sequence.
+    """
+    n_tokens: int
+    n_seq: int
+    tokens: Tensor
+    positions: Tensor
+    seq_of: Tensor
+    cu_seqlens: Tensor
+    slots: Tensor
+    logit_rows: Tensor
+    n_rows: int
+    decode_only: bool
+    kv_len_bound: int
+    dtype: torch.dtype
+    workspace: Workspace
+    new_lens: List[int] = field(default_factory=list)
+    past_lens: List[int] = field(default_factory=list)

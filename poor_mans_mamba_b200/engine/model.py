@@ -1,0 +1,124 @@
+"""A model assembled from a ModelSpec: embedding, layers (arrangements of parts), the
+order in which the layers run, final norm and output head.
+
+The forward pass is the same for every architecture:
+  h = multiplier * E[tokens]                       (float32 residual stream)
+  for (layer, cache_of) in order: layers[layer](h, cache of cache_of)
+  logits = (norm(h)[wanted rows] @ W_head^T) * head_multiplier       (float32)
+(reference src/runtime/runner/falconh1_runner.cpp:129-228, which keeps the last row only).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..kernels import ops as K
+from ..parts.base import LayerCache, ModelSpec, ParamSpec, Part, StateSpec, build_part, _REGISTRIES
+from ..parts.block import ResidualStream
+from .context import StepContext
+
+Tensor = torch.Tensor
+
+
+class Model:
+    def __init__(self, spec: ModelSpec):
+        self.spec = spec
+        self.hidden_size = spec.hidden_size
+        self.vocab_size = spec.vocab_size
+        self.layers = []
+        for ls in spec.layers:
+            factory = _REGISTRIES["arrangement"].get(ls.arrangement)
+            if factory is None:
+                raise KeyError(f"unknown arrangement '{ls.arrangement}'")
+            self.layers.append(factory(ls, hidden_size=spec.hidden_size))
+        for call in spec.order:
+            if not (0 <= call.layer < len(self.layers) and 0 <= call.cache_of < len(self.layers)):
+                raise ValueError(f"execution order names a layer that does not exist: {call}")
+        self.final_norm = build_part("norm", spec.final_norm, width=spec.hidden_size)
+        self.embedding: Optional[Tensor] = None
+        self.head: Optional[Tensor] = None
+        self.dtype: Optional[torch.dtype] = None
+        self.device: Optional[torch.device] = None
+        self._branch_buffers = max(l.branch_buffers_needed() for l in self.layers) if self.layers else 1
+        self._logits: Optional[Tensor] = None
+        self._logits_lowp: Optional[Tensor] = None
+
+    # ------------------------------------------------------------------ tensors
+    def named_parts(self) -> List[Tuple[str, Part]]:
+        """(name prefix, part) for every part that owns tensors."""
+        out: List[Tuple[str, Part]] = []
+        for layer in self.layers:
+            for part in layer.parts():
+                out.append((f"{layer.prefix}{part.name}.", part))
+        out.append((f"{self.spec.final_norm.name}.", self.final_norm))
+        return out
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        specs: Dict[str, ParamSpec] = {
+            self.spec.embedding_name: ParamSpec(self.spec.embedding_name,
+                                                (self.vocab_size, self.hidden_size)),
+        }
+        if self.spec.head_name is not None:
+            specs[self.spec.head_name] = ParamSpec(self.spec.head_name, (self.vocab_size, self.hidden_size))
+        for prefix, part in self.named_parts():
+            for ps in part.param_specs():
+                specs[prefix + ps.name] = ps
+        return specs
+
+    def ignored_names(self) -> List[str]:
+        names: List[str] = []
+        for prefix, part in self.named_parts():
+            names += [prefix + n for n in getattr(part, "ignored_names", lambda: [])()]
+        return names
+
+    def bind(self, tensors: Dict[str, Tensor], dtype: torch.dtype, device: torch.device) -> None:
+        """``tensors``: full name -> tensor on ``device`` in the policy type of its spec."""
+        self.dtype, self.device = dtype, torch.device(device)
+        self.embedding = tensors[self.spec.embedding_name]
+        self.head = self.embedding if self.spec.head_name is None else tensors[self.spec.head_name]
+        for prefix, part in self.named_parts():
+            part.bind({ps.name: tensors[prefix + ps.name] for ps in part.param_specs()})
+        for layer in self.layers:
+            layer.finalize(dtype, self.device)
+        self.final_norm.finalize(dtype, self.device)
+
+    # ------------------------------------------------------------------ state
+    def state_specs(self) -> Dict[int, List[Tuple[str, StateSpec]]]:
+        """Layer index -> its (qualified name, spec) list, for layers that own a cache."""
+        owners = sorted({c.cache_of for c in self.spec.order})
+        return {i: self.layers[i].state_specs() for i in owners}
+
+    # ------------------------------------------------------------------ the step
+    def forward(self, ctx: StepContext, caches: Dict[int, LayerCache]) -> Tensor:
+        """Runs the step's tokens through the layers; returns logits [n_rows, V] float32 (a
+        buffer of the model, valid until the next call)."""
+        ws = ctx.workspace
+        T, D = ctx.n_tokens, self.hidden_size
+        h = ws.alloc((T, D), torch.float32)
+        K.embed(h, self.embedding, ctx.tokens, self.spec.embedding_multiplier)
+        stream = ResidualStream(h, ctx, self._branch_buffers)
+        for call in self.spec.order:
+            self.layers[call.layer].forward(stream, ctx, caches[call.cache_of])
+        if ctx.n_rows == 0:
+            stream.flush()
+            return torch.empty((0, self.vocab_size), dtype=torch.float32, device=h.device)
+        normed = stream.normed(self.final_norm, rows=ctx.logit_rows)
+        return self._head(normed, ctx.n_rows)
+
+    def _head(self, normed: Tensor, n_rows: int) -> Tensor:
+        V = self.vocab_size
+        if self._logits is None or self._logits.shape[0] < n_rows:
+            cap = max(n_rows, 16)
+            self._logits = torch.empty((cap, V), dtype=torch.float32, device=normed.device)
+            self._logits_lowp = (torch.empty((cap, V), dtype=normed.dtype, device=normed.device)
+                                 if normed.dtype != torch.float32 else None)
+        logits = self._logits[:n_rows]
+        mult = self.spec.head_multiplier
+        if normed.dtype == torch.float32:
+            K.linear(normed, self.head, logits)
+            if mult != 1.0:
+                K.scale_f32_(logits, mult)
+        else:
+            K.linear_f32_out(normed, self.head, logits, self._logits_lowp[:n_rows], mult)
+        return logits

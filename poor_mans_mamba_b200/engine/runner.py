@@ -1,0 +1,206 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A step takes any mix of prompt portions and single decoded tokens, cut anywhere.  It
+runs only the tokens it is given, as one flattened batch, on top of what earlier steps
+left in the cache (keys/values in pages, conv windows and SSM states in slots), and
+returns the logits at the wanted places as float32 [n_rows, vocab].  The reference has
+no counterpart: its runner takes one whole prompt or one token of one request at a time
+(include/runtime/runner/runner.h:13-23).
+
+Host work per step: page bookkeeping, packing all index arrays into one pinned int32
+buffer, one host-to-device copy.  Everything else is kernels on the current stream.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.pages import OutOfPages
+from .context import StepContext
+from .model import Model
+from .workspace import Workspace
+
+Tensor = torch.Tensor
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens and the places (indices into
+    ``tokens``) whose logits are wanted."""
+    req: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=list)
+
+
+class _Staging:
+    """A few pinned int32 host buffers used in rotation for the per-step index upload."""
+
+    def __init__(self, device: torch.device, n_buffers: int = 3):
+        self.device = device
+        self.pinned = device.type == "cuda"
+        self._host: List[Optional[Tensor]] = [None] * n_buffers
+        self._events: List[Optional[torch.cuda.Event]] = [None] * n_buffers
+        self._dev: Optional[Tensor] = None
+        self._i = 0
+
+    def upload(self, n: int, fill) -> Tensor:
+        """Calls fill(numpy int32 array of n) and returns the device copy."""
+        i = self._i
+        self._i = (i + 1) % len(self._host)
+        if self._host[i] is None or self._host[i].numel() < n:
+            cap = max(1024, 1 << (n - 1).bit_length())
+            self._host[i] = torch.empty(cap, dtype=torch.int32, pin_memory=self.pinned)
+        elif self._events[i] is not None:
+            self._events[i].synchronize()  # the copy that last read this buffer has finished
+        if self._dev is None or self._dev.numel() < n:
+            cap = max(1024, 1 << (n - 1).bit_length())
+            self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        host = self._host[i]
+        fill(host.numpy()[:n])
+        dev = self._dev[:n]
+        dev.copy_(host[:n], non_blocking=True)
+        if self.pinned:
+            ev = torch.cuda.Event()
+            ev.record()
+            self._events[i] = ev
+        return dev
+
+
+class ModelRunner:
+    """Owns the cache manager and the per-request lengths; ``step`` is the step function."""
+
+    def __init__(self, model: Model, cache: CacheManager):
+        self.model = model
+        self.cache = cache
+        self.device = cache.device
+        self.dtype = cache.dtype
+        self.workspace = Workspace(self.device)
+        self.lengths: Dict[Hashable, int] = {}
+        self._staging = _Staging(self.device)
+        self.steps_run = 0
+        self.tokens_run = 0
+
+    # ------------------------------------------------------------------ requests
+    def start(self, req: Hashable) -> None:
+        self.cache.admit(req)
+        self.lengths[req] = 0
+
+    def finish(self, req: Hashable) -> None:
+        self.cache.release(req)
+        del self.lengths[req]
+
+    def length(self, req: Hashable) -> int:
+        return self.lengths[req]
+
+    def can_run(self, entries: Sequence[StepEntry]) -> bool:
+        """Whether the cache has the pages (and slots) this batch needs."""
+        reserved: Dict[Tuple, int] = {k: 0 for k in self.cache.groups}
+        new_reqs = 0
+        for e in entries:
+            known = self.cache.has(e.req)
+            new_reqs += 0 if known else 1
+            new_len = self.lengths.get(e.req, 0) + len(e.tokens)
+            for k, g in self.cache.groups.items():
+                reserved[k] += g.pages_to_grow(e.req, new_len) if known else g.blocks_for(new_len)
+        return (new_reqs <= self.cache.free_slots
+                and all(reserved[k] <= g.pool.n_free for k, g in self.cache.groups.items()))
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence[StepEntry]) -> Tensor:
+        """Run one batch; returns logits [n_rows, vocab] float32 in the order of the entries
+        and of their ``want`` lists (a buffer that the next step overwrites).  Requests seen
+        for the first time are admitted.  Raises OutOfPages before touching anything if the
+        cache cannot hold the batch."""
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        seen = set()
+        vocab = self.model.vocab_size
+        for e in entries:
+            if e.req in seen:
+                raise ValueError(f"request {e.req!r} appears twice in one step")
+            seen.add(e.req)
+            if len(e.tokens) == 0:
+                raise ValueError(f"request {e.req!r} brings no tokens")
+            for t in e.tokens:
+                if not 0 <= int(t) < vocab:
+                    raise ValueError("token id out of range")
+            for w in e.want:
+                if not 0 <= int(w) < len(e.tokens):
+                    raise ValueError(f"request {e.req!r}: wanted place {w} is outside its tokens")
+        if not self.can_run(entries):
+            raise OutOfPages("the cache cannot hold this batch")
+
+        cache = self.cache
+        for e in entries:
+            if not cache.has(e.req):
+                self.start(e.req)
+            cache.grow(e.req, self.lengths[e.req] + len(e.tokens))
+
+        n_seq = len(entries)
+        new_lens = [len(e.tokens) for e in entries]
+        past = [self.lengths[e.req] for e in entries]
+        T = sum(new_lens)
+        n_rows = sum(len(e.want) for e in entries)
+        groups = list(cache.groups.values())
+        widths = [max(len(g.tables[e.req]) for e in entries) for g in groups]
+
+        # one packed int32 upload: tokens | positions | seq_of | cu | slots | rows | tables...
+        o_tok, o_pos, o_seq = 0, T, 2 * T
+        o_cu = 3 * T
+        o_slot = o_cu + n_seq + 1
+        o_rows = o_slot + n_seq
+        o_tab = o_rows + n_rows
+        tab_offsets = []
+        total = o_tab
+        for w in widths:
+            tab_offsets.append(total)
+            total += n_seq * w
+
+        def fill(buf: np.ndarray) -> None:
+            t0 = 0
+            r = 0
+            buf[o_cu] = 0
+            for s, e in enumerate(entries):
+                n = new_lens[s]
+                buf[o_tok + t0:o_tok + t0 + n] = np.asarray(e.tokens, dtype=np.int32)
+                buf[o_pos + t0:o_pos + t0 + n] = np.arange(past[s], past[s] + n, dtype=np.int32)
+                buf[o_seq + t0:o_seq + t0 + n] = s
+                buf[o_cu + s + 1] = t0 + n
+                buf[o_slot + s] = cache.slot(e.req)
+                for w in e.want:
+                    buf[o_rows + r] = t0 + int(w)
+                    r += 1
+                t0 += n
+            for g, w, off in zip(groups, widths, tab_offsets):
+                tab = buf[off:off + n_seq * w].reshape(n_seq, w)
+                tab[:] = g.num_pages  # the spare page: never owned, safe to touch
+                for s, e in enumerate(entries):
+                    row = g.tables[e.req]
+                    arr = np.asarray(row, dtype=np.int32)
+                    arr[arr < 0] = g.num_pages
+                    tab[s, :len(row)] = arr
+
+        dev = self._staging.upload(total, fill)
+        block_tables = {g.key: dev[off:off + n_seq * w].view(n_seq, w)
+                        for g, w, off in zip(groups, widths, tab_offsets)}
+        self.workspace.reset()
+        ctx = StepContext(
+            n_tokens=T, n_seq=n_seq,
+            tokens=dev[o_tok:o_tok + T], positions=dev[o_pos:o_pos + T], seq_of=dev[o_seq:o_seq + T],
+            cu_seqlens=dev[o_cu:o_cu + n_seq + 1], slots=dev[o_slot:o_slot + n_seq],
+            logit_rows=dev[o_rows:o_rows + n_rows], n_rows=n_rows,
+            decode_only=all(n == 1 for n in new_lens),
+            kv_len_bound=max(p + n for p, n in zip(past, new_lens)),
+            dtype=self.dtype, workspace=self.workspace, new_lens=new_lens, past_lens=past)
+        logits = self.model.forward(ctx, cache.layer_caches(block_tables))
+
+        for e, n in zip(entries, new_lens):
+            self.lengths[e.req] += n
+            cache.trim(e.req, self.lengths[e.req])
+        self.steps_run += 1
+        self.tokens_run += T
+        return logits

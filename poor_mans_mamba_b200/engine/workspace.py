@@ -1,0 +1,72 @@
+"""Per-step scratch memory: a bump arena over device buffers that are kept between steps.
+
+Parts take temporaries with ``alloc`` and give them back in stack order with
+``mark``/``release``; ``reset`` starts a new step.  The arena grows only when a step needs
+more than any step before it (it then adds a chunk, and merges the chunks at the next
+``reset``), so steady-state steps allocate nothing.
+"""
+from __future__ import annotations
+
+from typing import List, Tuple
+
+import torch
+
+_ALIGN = 256
+
+
+class Workspace:
+    def __init__(self, device: torch.device, initial_bytes: int = 0):
+        self.device = torch.device(device)
+        self._chunks: List[torch.Tensor] = []
+        self._chunk = 0
+        self._offset = 0
+        self._frozen = False
+        self.high_water = 0
+        if initial_bytes > 0:
+            self._chunks.append(torch.empty(int(initial_bytes), dtype=torch.uint8, device=self.device))
+
+    def freeze(self, frozen: bool = True) -> None:
+        """While frozen the arena refuses to grow (addresses captured in a CUDA graph stay valid)."""
+        self._frozen = frozen
+
+    def capacity(self) -> int:
+        return sum(c.numel() for c in self._chunks)
+
+    def reset(self) -> None:
+        if len(self._chunks) > 1 and not self._frozen:
+            total = self.capacity()
+            self._chunks = []
+            self._chunks.append(torch.empty(total, dtype=torch.uint8, device=self.device))
+        self._chunk = 0
+        self._offset = 0
+
+    def mark(self) -> Tuple[int, int]:
+        return (self._chunk, self._offset)
+
+    def release(self, mark: Tuple[int, int]) -> None:
+        self._chunk, self._offset = mark
+
+    def _used(self) -> int:
+        return sum(c.numel() for c in self._chunks[:self._chunk]) + self._offset
+
+    def alloc(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        numel = 1
+        for s in shape:
+            numel *= int(s)
+        nbytes = numel * torch.empty((), dtype=dtype).element_size()
+        size = (max(nbytes, 1) + _ALIGN - 1) // _ALIGN * _ALIGN
+        while True:
+            if self._chunk < len(self._chunks):
+                chunk = self._chunks[self._chunk]
+                if self._offset + size <= chunk.numel():
+                    view = chunk[self._offset:self._offset + nbytes].view(dtype).view(tuple(int(s) for s in shape))
+                    self._offset += size
+                    self.high_water = max(self.high_water, self._used())
+                    return view
+                self._chunk += 1
+                self._offset = 0
+                continue
+            if self._frozen:
+                raise RuntimeError("workspace is frozen and too small for this step")
+            grow = max(size, self.capacity(), 1 << 20)
+            self._chunks.append(torch.empty(grow, dtype=torch.uint8, device=self.device))

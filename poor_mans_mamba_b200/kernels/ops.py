@@ -1,0 +1,461 @@
+"""Python face of the CUDA kernels: argument checks, then one C call per op on the
+current CUDA stream.  Nothing here computes on the host and nothing falls back: a tensor
+that is not on a CUDA device, a size a kernel cannot take, or a missing library raises.
+
+Matrix products go to the library (cuBLAS through ``torch.mm``), as the reference sends
+its linear layers to ``cublasSgemm`` (src/ops/gpu/linear.cu:3-21); in float32 the
+reduced-precision matrix mode is switched off for the call.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import build as _build
+
+Tensor = torch.Tensor
+
+PMM_ERR_BAD_ARGUMENT = 1001
+
+
+class KernelError(RuntimeError):
+    """A kernel launch was refused or failed."""
+
+
+_SIGNATURES = {
+    "pmm_embed": [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p],
+    "pmm_add_rmsnorm": [c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p, c_float, c_void_p,
+                        c_void_p, c_int, c_int, c_int, c_void_p],
+    "pmm_scale_f32": [c_void_p, c_float, c_longlong, c_void_p],
+    "pmm_cast_scale": [c_void_p, c_void_p, c_float, c_longlong, c_int, c_void_p],
+    "pmm_conv1d_fwd": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                       c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "pmm_conv1d_window_update": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "pmm_conv1d_decode": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                          c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "pmm_ssm_scan_seq": [c_void_p, c_int, c_void_p, c_longlong, c_float, c_void_p, c_void_p,
+                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                         c_int, c_int, c_void_p],
+    "pmm_gated_norm": [c_void_p, c_void_p, c_longlong, c_float, c_void_p, c_void_p, c_float, c_int,
+                       c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "pmm_qkv_rope_store": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_float,
+                           c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                           c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                           c_void_p],
+    "pmm_kv_store": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                     c_int, c_int, c_void_p],
+    "pmm_paged_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                            c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
+                            c_int, c_int, c_int, c_void_p],
+    "pmm_silu_mul": [c_void_p, c_longlong, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
+    "pmm_add_row_bias": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "pmm_sample_rows": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                        c_void_p],
+}
+
+_FUNCS = {}
+launch_count = 0  # kernels of this library launched since import (library GEMMs not counted)
+
+
+def _fn(name: str):
+    f = _FUNCS.get(name)
+    if f is None:
+        lib = _build.load()
+        try:
+            f = getattr(lib, name)
+        except AttributeError as exc:
+            raise KernelError(f"kernel library has no symbol {name}; rebuild it") from exc
+        f.argtypes = _SIGNATURES[name]
+        f.restype = c_int
+        _FUNCS[name] = f
+    return f
+
+
+def _call(name: str, *args) -> None:
+    global launch_count
+    rc = _fn(name)(*args)
+    launch_count += 1
+    if rc != 0:
+        if rc == PMM_ERR_BAD_ARGUMENT:
+            raise KernelError(f"{name}: sizes or arguments outside what the kernel supports")
+        raise KernelError(f"{name}: CUDA error {rc} at launch")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dt(t: Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"storage type must be float32 or bfloat16, got {t.dtype}")
+
+
+def _ptr(t: Optional[Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _cuda(*tensors: Optional[Tensor]) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernels run on CUDA tensors only (no CPU path exists)")
+
+
+def _rows_view(t: Tensor, what: str) -> int:
+    """Row stride (elements) of a 2-D view whose rows are contiguous."""
+    _need(t.dim() == 2 and t.stride(1) == 1, f"{what}: need a 2-D view with unit column stride")
+    return t.stride(0)
+
+
+def _f32vec(t: Optional[Tensor], n: int, what: str) -> None:
+    if t is not None:
+        _need(t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n,
+              f"{what}: need a contiguous float32 vector of {n}")
+
+
+def _i32(t: Tensor, what: str) -> None:
+    _need(t.dtype == torch.int32 and t.is_contiguous(), f"{what}: need contiguous int32")
+
+
+# ----------------------------------------------------------------------------- library GEMM
+def linear(x: Tensor, weight: Tensor, out: Tensor) -> Tensor:
+    """out[T, N] = x[T, K] @ weight[N, K]^T through the GEMM library."""
+    _cuda(x, weight, out)
+    _need(x.dtype == weight.dtype, f"linear: activation {x.dtype} vs weight {weight.dtype}")
+    if x.dtype == torch.float32:
+        prev = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = False
+        try:
+            torch.mm(x, weight.t(), out=out)
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = prev
+    else:
+        torch.mm(x, weight.t(), out=out)
+    return out
+
+
+_MM_F32_OUT: Optional[bool] = None
+
+
+def linear_f32_out(x: Tensor, weight: Tensor, out: Tensor, scratch_low: Optional[Tensor], scale: float) -> None:
+    """out (float32) = scale * (x @ weight^T) for bfloat16 operands.  The library is asked for
+    a float32 result directly; a library build without that option gets a bfloat16 product
+    that is widened (and scaled) by cast_scale."""
+    global _MM_F32_OUT
+    _cuda(x, weight, out)
+    if _MM_F32_OUT is None:
+        try:
+            torch.mm(x[:1], weight[:8].t(), out_dtype=torch.float32)
+            _MM_F32_OUT = True
+        except (TypeError, RuntimeError):
+            _MM_F32_OUT = False
+    if _MM_F32_OUT:
+        torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+        if scale != 1.0:
+            scale_f32_(out, scale)
+    else:
+        _need(scratch_low is not None, "linear_f32_out: needs a low-precision scratch buffer")
+        torch.mm(x, weight.t(), out=scratch_low)
+        cast_scale(out, scratch_low, scale)
+
+
+# ----------------------------------------------------------------------------- own kernels
+def embed(out: Tensor, table: Tensor, tokens: Tensor, mult: float) -> None:
+    _cuda(out, table, tokens)
+    T, D = out.shape
+    _need(out.dtype == torch.float32 and out.is_contiguous(), "embed: out must be contiguous float32")
+    _need(table.dim() == 2 and table.shape[1] == D and table.is_contiguous(), "embed: table must be [V, D]")
+    _i32(tokens, "embed: tokens")
+    _need(tokens.numel() == T, "embed: one token per output row")
+    _call("pmm_embed", out.data_ptr(), table.data_ptr(), tokens.data_ptr(), float(mult), T, D,
+          table.shape[0], _dt(table), _stream())
+
+
+def add_rmsnorm(h: Tensor, branches: Sequence[Tuple[Tensor, float]], weight: Optional[Tensor],
+                eps: float, out: Optional[Tensor], rows: Optional[Tensor] = None) -> None:
+    """h <- (h + s0*b0) + s1*b1 (rows is None), then out = rmsnorm(h) * weight.
+    With ``rows`` (int32 row indices) h is left as it is and out[r] comes from row rows[r]."""
+    _cuda(h, weight, out, rows)
+    _need(h.dtype == torch.float32 and h.dim() == 2 and h.is_contiguous(),
+          "add_rmsnorm: the residual stream must be contiguous float32 [T, D]")
+    T, D = h.shape
+    _need(len(branches) <= 2, "add_rmsnorm: at most two branches")
+    _need(D * 4 <= 200 * 1024, f"add_rmsnorm: width {D} exceeds one block's shared memory")
+    ptrs: List[Optional[int]] = [None, None]
+    scales = [0.0, 0.0]
+    dtype = None
+    for i, (b, s) in enumerate(branches):
+        _cuda(b)
+        _need(b.shape == h.shape and b.is_contiguous(), "add_rmsnorm: branch must be contiguous [T, D]")
+        ptrs[i], scales[i] = b.data_ptr(), float(s)
+        dtype = _dt(b) if dtype is None else dtype
+        _need(_dt(b) == dtype, "add_rmsnorm: branches of different storage types")
+    R = T
+    if rows is not None:
+        _i32(rows, "add_rmsnorm: rows")
+        R = rows.numel()
+    if out is not None:
+        _need(weight is not None, "add_rmsnorm: a norm needs its weight")
+        _f32vec(weight, D, "add_rmsnorm: weight")
+        _need(out.shape == (R, D) and out.is_contiguous(), "add_rmsnorm: out must be contiguous [rows, D]")
+        _need(dtype is None or _dt(out) == dtype, "add_rmsnorm: out and branches differ in storage type")
+        dtype = _dt(out)
+    if dtype is None:
+        return  # nothing to add and nothing to write
+    _call("pmm_add_rmsnorm", h.data_ptr(), ptrs[0], scales[0], ptrs[1], scales[1], _ptr(weight),
+          float(eps), _ptr(out), _ptr(rows), R, D, dtype, _stream())
+
+
+def scale_f32_(x: Tensor, s: float) -> None:
+    _cuda(x)
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "scale_f32_: contiguous float32 only")
+    _call("pmm_scale_f32", x.data_ptr(), float(s), x.numel(), _stream())
+
+
+def cast_scale(out: Tensor, src: Tensor, s: float) -> None:
+    _cuda(out, src)
+    _need(out.dtype == torch.float32 and out.is_contiguous() and src.is_contiguous()
+          and out.numel() == src.numel(), "cast_scale: contiguous tensors of equal size, float32 out")
+    _call("pmm_cast_scale", out.data_ptr(), src.data_ptr(), float(s), src.numel(), _dt(src), _stream())
+
+
+def _conv_common(x: Tensor, pre_scale: Tensor, pre_bias: Optional[Tensor], window: Tensor, K: int):
+    C = x.shape[1]
+    _f32vec(pre_scale, C, "conv1d: pre_scale")
+    _f32vec(pre_bias, C, "conv1d: pre_bias")
+    _need(window.dtype == torch.float32 and window.is_contiguous() and window.dim() == 3
+          and tuple(window.shape[1:]) == (K - 1, C), "conv1d: window must be float32 [slots, K-1, C]")
+    return C
+
+
+def conv1d_fwd(x: Tensor, pre_scale: Tensor, pre_bias: Optional[Tensor], weight: Tensor,
+               bias: Optional[Tensor], window: Tensor, seq_of: Tensor, cu: Tensor, slots: Tensor,
+               out: Tensor) -> None:
+    """Causal depthwise conv + SiLU over all tokens of the step; reads the windows."""
+    _cuda(x, pre_scale, pre_bias, weight, bias, window, seq_of, cu, slots, out)
+    ld = _rows_view(x, "conv1d: x")
+    T = x.shape[0]
+    _need(weight.dtype == torch.float32 and weight.dim() == 2 and weight.is_contiguous()
+          and weight.shape[0] == x.shape[1], "conv1d: weight must be contiguous float32 [C, K]")
+    K = weight.shape[1]
+    C = _conv_common(x, pre_scale, pre_bias, window, K)
+    _f32vec(bias, C, "conv1d: bias")
+    _need(out.shape == (T, C) and out.is_contiguous() and out.dtype == x.dtype, "conv1d: out must be [T, C]")
+    _call("pmm_conv1d_fwd", x.data_ptr(), ld, pre_scale.data_ptr(), _ptr(pre_bias), weight.data_ptr(),
+          _ptr(bias), window.data_ptr(), seq_of.data_ptr(), cu.data_ptr(), slots.data_ptr(),
+          out.data_ptr(), T, C, K, _dt(x), _stream())
+
+
+def conv1d_window_update(x: Tensor, pre_scale: Tensor, pre_bias: Optional[Tensor], window: Tensor,
+                         cu: Tensor, slots: Tensor, n_seq: int, K: int) -> None:
+    """Leaves the last K-1 conv inputs of every sequence in its window."""
+    _cuda(x, pre_scale, pre_bias, window, cu, slots)
+    ld = _rows_view(x, "conv1d: x")
+    C = _conv_common(x, pre_scale, pre_bias, window, K)
+    _call("pmm_conv1d_window_update", x.data_ptr(), ld, pre_scale.data_ptr(), _ptr(pre_bias),
+          window.data_ptr(), cu.data_ptr(), slots.data_ptr(), n_seq, C, K, _dt(x), _stream())
+
+
+def conv1d_decode(x: Tensor, pre_scale: Tensor, pre_bias: Optional[Tensor], weight: Tensor,
+                  bias: Optional[Tensor], window: Tensor, slots: Tensor, out: Tensor) -> None:
+    """Conv + SiLU + window shift for a step in which every sequence brings one token."""
+    _cuda(x, pre_scale, pre_bias, weight, bias, window, slots, out)
+    ld = _rows_view(x, "conv1d: x")
+    n_seq = x.shape[0]
+    K = weight.shape[1]
+    C = _conv_common(x, pre_scale, pre_bias, window, K)
+    _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.shape[0] == C,
+          "conv1d: weight must be contiguous float32 [C, K]")
+    _f32vec(bias, C, "conv1d: bias")
+    _need(out.shape == (n_seq, C) and out.is_contiguous() and out.dtype == x.dtype, "conv1d: out must be [T, C]")
+    _call("pmm_conv1d_decode", x.data_ptr(), ld, pre_scale.data_ptr(), _ptr(pre_bias),
+          weight.data_ptr(), _ptr(bias), window.data_ptr(), slots.data_ptr(), out.data_ptr(), n_seq, C,
+          K, _dt(x), _stream())
+
+
+def ssm_scan_seq(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Tensor, a_log: Tensor,
+                 d_skip: Tensor, state: Tensor, cu: Tensor, slots: Tensor, n_seq: int, out: Tensor,
+                 n_groups: int) -> None:
+    """Token-serial Mamba2 recurrence from the saved state; state[slots, H, P, N] is updated."""
+    _cuda(xbc, dt_raw, dt_shift, a_log, d_skip, state, cu, slots, out)
+    _need(state.dtype == torch.float32 and state.dim() == 4 and state.is_contiguous(),
+          "ssm_scan: state must be contiguous float32 [slots, H, P, N]")
+    _, H, P, N = state.shape
+    _need(N <= 256, f"ssm_scan: d_state {N} above 256 is not supported")
+    ld_x = _rows_view(xbc, "ssm_scan: xbc")
+    _need(xbc.shape[1] == H * P + 2 * n_groups * N, "ssm_scan: xbc must hold [x | B | C]")
+    ld_dt = _rows_view(dt_raw, "ssm_scan: dt")
+    _need(dt_raw.shape[1] == H and dt_raw.dtype == xbc.dtype, "ssm_scan: dt must be [T, H]")
+    for v, nm in ((dt_shift, "dt_shift"), (a_log, "A_log"), (d_skip, "D")):
+        _f32vec(v, H, f"ssm_scan: {nm}")
+    _need(out.shape == (xbc.shape[0], H * P) and out.is_contiguous() and out.dtype == xbc.dtype,
+          "ssm_scan: out must be [T, H*P]")
+    _call("pmm_ssm_scan_seq", xbc.data_ptr(), ld_x, dt_raw.data_ptr(), ld_dt, float(dt_scale),
+          dt_shift.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), cu.data_ptr(),
+          slots.data_ptr(), out.data_ptr(), n_seq, H, P, N, n_groups, _dt(xbc), _stream())
+
+
+def gated_norm(y: Tensor, z_raw: Tensor, z_scale: float, z_bias: Optional[Tensor],
+               weight: Optional[Tensor], eps: float, n_groups: int, norm_before_gate: bool,
+               out: Tensor) -> None:
+    """out = y*silu(z), optionally RMS-normalised per group of channels (before or after the gate)."""
+    _cuda(y, z_raw, z_bias, weight, out)
+    T, I = y.shape
+    _need(y.is_contiguous() and out.is_contiguous() and out.shape == y.shape and out.dtype == y.dtype,
+          "gated_norm: y and out must be contiguous [T, I] of one type")
+    ld_z = _rows_view(z_raw, "gated_norm: z")
+    _need(z_raw.shape == y.shape and z_raw.dtype == y.dtype, "gated_norm: z must match y")
+    _f32vec(z_bias, I, "gated_norm: z_bias")
+    _f32vec(weight, I, "gated_norm: weight")
+    groups = n_groups if weight is not None else 1
+    _need(I % groups == 0, "gated_norm: width must be a multiple of the group count")
+    _call("pmm_gated_norm", y.data_ptr(), z_raw.data_ptr(), ld_z, float(z_scale), _ptr(z_bias),
+          _ptr(weight), float(eps), int(bool(norm_before_gate)), out.data_ptr(), T, I, groups, _dt(y),
+          _stream())
+
+
+def check_head_dim(head_dim: int) -> None:
+    _need(head_dim % 16 == 0 and 16 <= head_dim <= 256,
+          f"attention kernels take head sizes 16..256 in steps of 16, got {head_dim}")
+
+
+def qkv_rope_store(q: Tensor, k: Tensor, v: Tensor, q_scale: float, k_scale: float, v_scale: float,
+                   inv_freq: Optional[Tensor], positions: Tensor, seq_of: Tensor,
+                   block_table: Optional[Tensor], pool: Optional[Tensor], q_out: Tensor,
+                   k_out: Optional[Tensor], v_out: Optional[Tensor], n_q_heads: int, n_kv_heads: int,
+                   head_dim: int) -> None:
+    """Scales q/k/v, rotates q and k (when inv_freq is given) and stores k/v into the pages of
+    ``pool`` [pages, 2, page_size, Hkv*Dh] through ``block_table`` [n_seq, max_blocks], or into
+    k_out/v_out when no pool is given."""
+    _cuda(q, k, v, inv_freq, positions, seq_of, block_table, pool, q_out, k_out, v_out)
+    check_head_dim(head_dim)
+    T = q.shape[0]
+    ldq, ldk, ldv = _rows_view(q, "qkv: q"), _rows_view(k, "qkv: k"), _rows_view(v, "qkv: v")
+    kv_dim = n_kv_heads * head_dim
+    _need(q.shape[1] == n_q_heads * head_dim and k.shape[1] == kv_dim and v.shape[1] == kv_dim,
+          "qkv: slice widths do not match the head counts")
+    _need(q.dtype == k.dtype == v.dtype == q_out.dtype, "qkv: one storage type expected")
+    _need(q_out.is_contiguous() and q_out.shape == (T, n_q_heads * head_dim), "qkv: q_out must be [T, Hq*Dh]")
+    _f32vec(inv_freq, head_dim // 2, "qkv: inv_freq")
+    _i32(positions, "qkv: positions")
+    _i32(seq_of, "qkv: seq_of")
+    page_size, max_blocks = 0, 0
+    if pool is not None:
+        _need(block_table is not None, "qkv: a pool needs a block table")
+        _i32(block_table, "qkv: block_table")
+        _need(pool.dim() == 4 and pool.shape[1] == 2 and pool.shape[3] == kv_dim and pool.is_contiguous()
+              and pool.dtype == q.dtype, "qkv: pool must be contiguous [pages, 2, page_size, Hkv*Dh]")
+        page_size, max_blocks = pool.shape[2], block_table.shape[1]
+    else:
+        _need(k_out is not None and v_out is not None and k_out.is_contiguous() and v_out.is_contiguous()
+              and k_out.shape == (T, kv_dim) and v_out.shape == (T, kv_dim), "qkv: k_out/v_out must be [T, Hkv*Dh]")
+    _call("pmm_qkv_rope_store", q.data_ptr(), ldq, k.data_ptr(), ldk, v.data_ptr(), ldv, float(q_scale),
+          float(k_scale), float(v_scale), _ptr(inv_freq), positions.data_ptr(), seq_of.data_ptr(),
+          _ptr(block_table), max_blocks, _ptr(pool), page_size, q_out.data_ptr(), _ptr(k_out),
+          _ptr(v_out), T, n_q_heads, n_kv_heads, head_dim, _dt(q), _stream())
+
+
+def kv_store(k: Tensor, v: Tensor, positions: Tensor, seq_of: Tensor, block_table: Tensor,
+             pool: Tensor) -> None:
+    """Copies contiguous k/v rows [T, Hkv*Dh] into the pages of ``pool``."""
+    _cuda(k, v, positions, seq_of, block_table, pool)
+    T, kv_dim = k.shape
+    _need(k.is_contiguous() and v.is_contiguous() and v.shape == k.shape and k.dtype == v.dtype == pool.dtype,
+          "kv_store: k and v must be contiguous [T, Hkv*Dh] of the pool's type")
+    _need(pool.dim() == 4 and pool.shape[1] == 2 and pool.shape[3] == kv_dim and pool.is_contiguous(),
+          "kv_store: pool must be contiguous [pages, 2, page_size, Hkv*Dh]")
+    _i32(block_table, "kv_store: block_table")
+    _call("pmm_kv_store", k.data_ptr(), v.data_ptr(), positions.data_ptr(), seq_of.data_ptr(),
+          block_table.data_ptr(), block_table.shape[1], pool.data_ptr(), pool.shape[2], T, kv_dim,
+          _dt(k), _stream())
+
+
+def attention_scratch_floats(T: int, n_q_heads: int, head_dim: int, n_splits: int) -> int:
+    return T * n_q_heads * n_splits * (head_dim + 2) if n_splits > 1 else 0
+
+
+def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Tensor, seq_of: Tensor,
+                    out: Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int, softmax_scale: float,
+                    window: int = 0, n_splits: int = 1, split_len: int = 0,
+                    scratch: Optional[Tensor] = None) -> None:
+    """Causal attention of every token over keys lo..pos of its request in the paged cache."""
+    _cuda(q, pool, block_table, positions, seq_of, out, scratch)
+    check_head_dim(head_dim)
+    T = q.shape[0]
+    _need(q.is_contiguous() and out.is_contiguous() and q.shape == (T, n_q_heads * head_dim)
+          and out.shape == q.shape and q.dtype == out.dtype == pool.dtype,
+          "attention: q and out must be contiguous [T, Hq*Dh] of the pool's type")
+    _need(n_q_heads % n_kv_heads == 0, "attention: query heads must be a multiple of key/value heads")
+    _need(pool.dim() == 4 and pool.shape[1] == 2 and pool.shape[3] == n_kv_heads * head_dim
+          and pool.is_contiguous(), "attention: pool must be contiguous [pages, 2, page_size, Hkv*Dh]")
+    _i32(block_table, "attention: block_table")
+    _i32(positions, "attention: positions")
+    _i32(seq_of, "attention: seq_of")
+    part_o = part_ml = None
+    if n_splits > 1:
+        need = attention_scratch_floats(T, n_q_heads, head_dim, n_splits)
+        _need(scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous()
+              and scratch.numel() >= need, f"attention: split keys need {need} floats of scratch")
+        _need(split_len > 0 and split_len % 32 == 0, "attention: split_len must be a positive multiple of 32")
+        part_o = scratch.data_ptr()
+        part_ml = part_o + 4 * T * n_q_heads * n_splits * head_dim
+    _call("pmm_paged_attention", q.data_ptr(), pool.data_ptr(), block_table.data_ptr(),
+          block_table.shape[1], positions.data_ptr(), seq_of.data_ptr(), out.data_ptr(), part_o, part_ml,
+          float(softmax_scale), int(window), int(split_len), int(n_splits), pool.shape[2], T, n_q_heads,
+          n_kv_heads, head_dim, _dt(q), _stream())
+
+
+def silu_mul(gate_up: Tensor, gate_mult: float, out: Tensor) -> None:
+    """out[t, f] = silu(gate_up[t, f] * gate_mult) * gate_up[t, F + f]."""
+    _cuda(gate_up, out)
+    ld = _rows_view(gate_up, "silu_mul: gate_up")
+    T, F2 = gate_up.shape
+    _need(F2 % 2 == 0 and out.shape == (T, F2 // 2) and out.is_contiguous() and out.dtype == gate_up.dtype,
+          "silu_mul: out must be contiguous [T, F] for gate_up [T, 2F]")
+    _call("pmm_silu_mul", gate_up.data_ptr(), ld, float(gate_mult), out.data_ptr(), T, F2 // 2,
+          _dt(gate_up), _stream())
+
+
+def add_row_bias_(x: Tensor, bias: Tensor) -> None:
+    """x[t, :] += bias (float32 vector) for a contiguous [T, D] activation."""
+    _cuda(x, bias)
+    _need(x.dim() == 2 and x.is_contiguous(), "add_row_bias_: x must be contiguous [T, D]")
+    _f32vec(bias, x.shape[1], "add_row_bias_: bias")
+    _call("pmm_add_row_bias", x.data_ptr(), bias.data_ptr(), x.shape[0], x.shape[1], _dt(x), _stream())
+
+
+def sample_rows(logits: Tensor, temperature: Optional[Tensor], seeds: Optional[Tensor],
+                steps: Optional[Tensor], out: Tensor) -> None:
+    """out[r] = argmax (first index on ties) where temperature[r] <= 0, else a draw from
+    softmax(logits[r] / temperature[r]) keyed by (seeds[r], steps[r])."""
+    _cuda(logits, temperature, seeds, steps, out)
+    ld = _rows_view(logits, "sample: logits")
+    n, V = logits.shape
+    _need(logits.dtype == torch.float32, "sample: logits must be float32")
+    _i32(out, "sample: out")
+    _need(out.numel() == n, "sample: one output per row")
+    if temperature is not None:
+        _f32vec(temperature, n, "sample: temperature")
+        _need(seeds is not None and seeds.dtype == torch.int64 and seeds.numel() == n and seeds.is_contiguous(),
+              "sample: seeds must be int64 [rows]")
+        _need(steps is not None and steps.numel() == n, "sample: steps must be int32 [rows]")
+        _i32(steps, "sample: steps")
+    _call("pmm_sample_rows", logits.data_ptr(), ld, _ptr(temperature), _ptr(seeds), _ptr(steps),
+          out.data_ptr(), n, V, _stream())
+
+
+def ensure_built() -> str:
+    """Build (if needed) and load the library; returns its path."""
+    _build.load()
+    return _build.library_path()

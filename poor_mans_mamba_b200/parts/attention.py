@@ -1,0 +1,132 @@
+"""Grouped-query attention over the paged key/value cache.
+
+a_in = x * in_multiplier; Q, K, V projections (one stacked matrix); K * key_multiplier
+before the position encoding; keys and values are written to the request's pages; every
+token attends causally to keys lo..pos of its own request; o_proj; the out multiplier is
+``out_scale`` (reference src/ops/cpu_backend.cpp:48-202, src/runtime/runner/
+falconh1_runner.cpp:66-101).  Softmax scale is 1/sqrt(head_dim).  ``window`` > 0 limits
+every token to the last ``window`` keys (and lets the cache manager give older pages back).
+"""
+from __future__ import annotations
+
+import math
+from typing import Any, Dict, List, Optional
+
+import torch
+
+from ..kernels import ops as K
+from .base import Mixer, ParamSpec, PartSpec, StateSpec, build_part, register_mixer
+
+Tensor = torch.Tensor
+
+# Key splits are sized so that a step launches about this many attention blocks.
+_TARGET_BLOCKS = 592
+_MIN_SPLIT_LEN = 128
+
+
+class PagedAttention(Mixer):
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 position_encoding: Optional[Dict[str, Any]] = None, in_multiplier: float = 1.0,
+                 out_multiplier: float = 1.0, key_multiplier: float = 1.0, window: int = 0):
+        if num_heads % num_kv_heads:
+            raise ValueError("query heads must be a multiple of key/value heads")
+        K.check_head_dim(head_dim)
+        self.hidden_size = int(hidden_size)
+        self.num_heads, self.num_kv_heads, self.head_dim = int(num_heads), int(num_kv_heads), int(head_dim)
+        self.q_dim = self.num_heads * self.head_dim
+        self.kv_dim = self.num_kv_heads * self.head_dim
+        self.in_multiplier = float(in_multiplier)
+        self.key_multiplier = float(key_multiplier)
+        self.out_scale = float(out_multiplier)
+        self.window = int(window)
+        pe = position_encoding or {"kind": "none"}
+        pe_params = {k: v for k, v in pe.items() if k != "kind"}
+        self.position_encoding = build_part("position_encoding", PartSpec(pe["kind"], "", pe_params),
+                                            head_dim=self.head_dim)
+        self.w_in: Optional[Tensor] = None
+        self.w_out: Optional[Tensor] = None
+
+    # -- tensors and state
+    def param_specs(self) -> List[ParamSpec]:
+        d = self.hidden_size
+        return [ParamSpec("q_proj.weight", (self.q_dim, d)), ParamSpec("k_proj.weight", (self.kv_dim, d)),
+                ParamSpec("v_proj.weight", (self.kv_dim, d)), ParamSpec("o_proj.weight", (d, self.q_dim))]
+
+    def state_specs(self) -> List[StateSpec]:
+        return [StateSpec.paged("kv", planes=2, width=self.kv_dim, window=self.window)]
+
+    def bind(self, params: Dict[str, Tensor]) -> None:
+        self.w_in = torch.cat([params["q_proj.weight"], params["k_proj.weight"], params["v_proj.weight"]],
+                              dim=0).contiguous()
+        self.w_out = params["o_proj.weight"].contiguous()
+
+    def finalize(self, dtype: torch.dtype, device: torch.device) -> None:
+        self.position_encoding.finalize(dtype, device)
+
+    # -- shared input projection
+    def input_rows(self) -> int:
+        return self.q_dim + 2 * self.kv_dim
+
+    def input_weight(self) -> Tensor:
+        return self.w_in
+
+    def adopt_input_weight(self, view: Tensor) -> None:
+        self.w_in = view
+
+    # -- the step
+    def forward(self, x: Tensor, ctx, cache, out: Tensor) -> None:
+        proj = ctx.workspace.alloc((x.shape[0], self.input_rows()), x.dtype)
+        K.linear(x, self.w_in, proj)
+        self.forward_projected(proj, ctx, cache, out)
+
+    def forward_projected(self, proj: Tensor, ctx, cache, out: Tensor) -> None:
+        T = proj.shape[0]
+        ws = ctx.workspace
+        kv = cache.paged(f"{self.name}.kv")
+        q = proj[:, :self.q_dim]
+        k = proj[:, self.q_dim:self.q_dim + self.kv_dim]
+        v = proj[:, self.q_dim + self.kv_dim:]
+        q_rot = ws.alloc((T, self.q_dim), proj.dtype)
+        s_in = self.in_multiplier
+        pe = self.position_encoding
+        if hasattr(pe, "inv_freq"):  # rotary (or none): fused with the page write
+            K.qkv_rope_store(q, k, v, s_in, s_in * self.key_multiplier, s_in, pe.inv_freq, ctx.positions,
+                             ctx.seq_of, kv.block_table, kv.pool, q_rot, None, None, self.num_heads,
+                             self.num_kv_heads, self.head_dim)
+        else:  # a position encoding defined elsewhere: scale, let it act, then store
+            k_lin = ws.alloc((T, self.kv_dim), proj.dtype)
+            v_lin = ws.alloc((T, self.kv_dim), proj.dtype)
+            K.qkv_rope_store(q, k, v, s_in, s_in * self.key_multiplier, s_in, None, ctx.positions,
+                             ctx.seq_of, None, None, q_rot, k_lin, v_lin, self.num_heads,
+                             self.num_kv_heads, self.head_dim)
+            pe.apply(q_rot.view(T, self.num_heads, self.head_dim),
+                     k_lin.view(T, self.num_kv_heads, self.head_dim), ctx.positions)
+            K.kv_store(k_lin, v_lin, ctx.positions, ctx.seq_of, kv.block_table, kv.pool)
+
+        n_splits, split_len = self.plan_splits(T, ctx.kv_len_bound)
+        scratch = None
+        if n_splits > 1:
+            scratch = ws.alloc((K.attention_scratch_floats(T, self.num_heads, self.head_dim, n_splits),),
+                               torch.float32)
+        attn = ws.alloc((T, self.q_dim), proj.dtype)
+        K.paged_attention(q_rot, kv.pool, kv.block_table, ctx.positions, ctx.seq_of, attn, self.num_heads,
+                          self.num_kv_heads, self.head_dim, 1.0 / math.sqrt(float(self.head_dim)),
+                          window=self.window, n_splits=n_splits, split_len=split_len, scratch=scratch)
+        K.linear(attn, self.w_out, out)
+
+    def plan_splits(self, n_tokens: int, kv_len_bound: int):
+        """How many key ranges each (token, head) is cut into: enough blocks to fill the GPU
+        when few tokens are in flight, one when the tokens alone do."""
+        blocks = n_tokens * ((self.num_heads + 3) // 4)
+        reach = min(kv_len_bound, self.window) if self.window > 0 else kv_len_bound
+        if blocks >= _TARGET_BLOCKS or reach <= _MIN_SPLIT_LEN:
+            return 1, 0
+        want = min((_TARGET_BLOCKS + blocks - 1) // blocks, (reach + _MIN_SPLIT_LEN - 1) // _MIN_SPLIT_LEN)
+        if want <= 1:
+            return 1, 0
+        split_len = ((kv_len_bound + want - 1) // want + 31) // 32 * 32
+        n_splits = (kv_len_bound + split_len - 1) // split_len
+        return (n_splits, split_len) if n_splits > 1 else (1, 0)
+
+
+register_mixer("paged_attention", PagedAttention)

@@ -1,0 +1,133 @@
+"""Arrangements: how the parts of one layer are ordered around the residual stream.
+
+``ParallelPreNormBlock``: one norm feeds every mixer of the layer; their scaled outputs
+join the residual stream in order; then a second norm feeds the feed-forward
+(reference src/runtime/runner/falconh1_runner.cpp:20-127: h = (h + mamba) + attn;
+h += mlp(norm(h))).  With one mixer it is the usual pre-norm decoder layer; without a
+feed-forward it is a bare mixer layer.
+
+The residual stream is float32.  Branch outputs are not added by a kernel of their own:
+they stay *pending* on the stream and are folded in by the next norm, which reads and
+writes the stream once.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..kernels import ops as K
+from .base import (FeedForward, LayerCache, LayerSpec, Mixer, Norm, ParamSpec, Part, StateSpec,
+                   build_part, register_arrangement)
+from .norm import fold_branches
+
+Tensor = torch.Tensor
+
+
+class ResidualStream:
+    """The float32 hidden state [T, D] of a step plus the branches waiting to be added."""
+
+    def __init__(self, h: Tensor, ctx, n_branch_buffers: int):
+        self.h = h
+        self.ctx = ctx
+        self.pending: List[Tuple[Tensor, float]] = []
+        self._buffers = [ctx.workspace.alloc(tuple(h.shape), ctx.dtype) for _ in range(n_branch_buffers)]
+        self._taken = 0
+
+    def take_branch(self) -> Tensor:
+        """A [T, D] buffer in the storage type for a part to write its output into."""
+        if self._taken >= len(self._buffers):
+            raise RuntimeError("more branches in flight than the stream has buffers for")
+        buf = self._buffers[self._taken]
+        self._taken += 1
+        return buf
+
+    def add(self, branch: Tensor, scale: float) -> None:
+        self.pending.append((branch, float(scale)))
+
+    def normed(self, norm: Norm, rows: Optional[Tensor] = None) -> Tensor:
+        """Fold the pending branches into the stream and return norm(stream) (of the selected
+        rows only, if given: then the stream itself is left unchanged)."""
+        n_rows = self.h.shape[0] if rows is None else rows.numel()
+        out = self.ctx.workspace.alloc((n_rows, self.h.shape[1]), self.ctx.dtype)
+        norm.forward(self.h, self.pending, out, rows, self.ctx)
+        if rows is None:
+            self.pending = []
+            self._taken = 0
+        return out
+
+    def flush(self) -> Tensor:
+        fold_branches(self.h, self.pending)
+        self.pending = []
+        self._taken = 0
+        return self.h
+
+
+class ParallelPreNormBlock(Part):
+    def __init__(self, spec: LayerSpec, hidden_size: int):
+        self.prefix = spec.prefix
+        self.hidden_size = hidden_size
+        self.mixer_norm: Norm = build_part("norm", spec.mixer_norm, width=hidden_size)
+        self.mixers: List[Mixer] = [build_part("mixer", m, hidden_size=hidden_size) for m in spec.mixers]
+        self.ffn_norm: Optional[Norm] = None
+        self.ffn: Optional[FeedForward] = None
+        if spec.ffn is not None:
+            if spec.ffn_norm is None:
+                raise ValueError("a feed-forward needs its norm")
+            self.ffn_norm = build_part("norm", spec.ffn_norm, width=hidden_size)
+            self.ffn = build_part("feed_forward", spec.ffn, hidden_size=hidden_size)
+        self._fused_in: Optional[Tensor] = None
+        self._fused_cols: List[Tuple[int, int]] = []
+
+    def parts(self) -> List[Part]:
+        out: List[Part] = [self.mixer_norm, *self.mixers]
+        if self.ffn is not None:
+            out += [self.ffn_norm, self.ffn]
+        return out
+
+    def branch_buffers_needed(self) -> int:
+        return max(len(self.mixers), 1)
+
+    def state_specs(self) -> List[Tuple[str, StateSpec]]:
+        """(qualified name, spec) for every state of every mixer of this layer."""
+        return [(f"{m.name}.{s.name}", s) for m in self.mixers for s in m.state_specs()]
+
+    def finalize(self, dtype: torch.dtype, device: torch.device) -> None:
+        for p in self.parts():
+            p.finalize(dtype, device)
+        # One input projection for all mixers that expose theirs.
+        if len(self.mixers) > 1 and all(m.input_rows() > 0 for m in self.mixers):
+            fused = torch.cat([m.input_weight() for m in self.mixers], dim=0).contiguous()
+            start = 0
+            for m in self.mixers:
+                rows = m.input_rows()
+                m.adopt_input_weight(fused[start:start + rows])
+                self._fused_cols.append((start, start + rows))
+                start += rows
+            self._fused_in = fused
+
+    def forward(self, stream: ResidualStream, ctx, cache: LayerCache) -> None:
+        ws = ctx.workspace
+        mark = ws.mark()
+        n = stream.normed(self.mixer_norm)
+        if self._fused_in is not None:
+            proj = ws.alloc((n.shape[0], self._fused_in.shape[0]), n.dtype)
+            K.linear(n, self._fused_in, proj)
+            for m, (c0, c1) in zip(self.mixers, self._fused_cols):
+                out = stream.take_branch()
+                m.forward_projected(proj[:, c0:c1], ctx, cache, out)
+                stream.add(out, m.out_scale)
+        else:
+            for m in self.mixers:
+                out = stream.take_branch()
+                m.forward(n, ctx, cache, out)
+                stream.add(out, m.out_scale)
+        if self.ffn is not None:
+            f = stream.normed(self.ffn_norm)
+            out = stream.take_branch()
+            self.ffn.forward(f, ctx, out)
+            stream.add(out, self.ffn.out_scale)
+        ws.release(mark)
+
+
+register_arrangement("parallel_prenorm", ParallelPreNormBlock)

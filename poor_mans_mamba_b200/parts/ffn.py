@@ -1,0 +1,49 @@
+"""Dense SwiGLU feed-forward.
+
+g = (x Wg^T) * gate_multiplier; u = x Wu^T; out = (silu(g) * u) Wd^T; the down
+multiplier is the part's ``out_scale`` and is applied where the branch joins the
+residual stream (reference src/ops/cpu_backend.cpp:494-531).  Gate and up weights are
+stacked into one [2F, D] matrix at load so the two projections are one product.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..kernels import ops as K
+from .base import FeedForward, ParamSpec, register_feed_forward
+
+Tensor = torch.Tensor
+
+
+class SwiGLU(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int, gate_multiplier: float = 1.0,
+                 down_multiplier: float = 1.0):
+        self.hidden_size = int(hidden_size)
+        self.intermediate_size = int(intermediate_size)
+        self.gate_multiplier = float(gate_multiplier)
+        self.out_scale = float(down_multiplier)
+        self.gate_up: Optional[Tensor] = None
+        self.down: Optional[Tensor] = None
+
+    def param_specs(self) -> List[ParamSpec]:
+        f, d = self.intermediate_size, self.hidden_size
+        return [ParamSpec("gate_proj.weight", (f, d)), ParamSpec("up_proj.weight", (f, d)),
+                ParamSpec("down_proj.weight", (d, f))]
+
+    def bind(self, params: Dict[str, Tensor]) -> None:
+        self.gate_up = torch.cat([params["gate_proj.weight"], params["up_proj.weight"]], dim=0).contiguous()
+        self.down = params["down_proj.weight"].contiguous()
+
+    def forward(self, x: Tensor, ctx, out: Tensor) -> None:
+        T = x.shape[0]
+        f = self.intermediate_size
+        gu = ctx.workspace.alloc((T, 2 * f), x.dtype)
+        K.linear(x, self.gate_up, gu)
+        act = ctx.workspace.alloc((T, f), x.dtype)
+        K.silu_mul(gu, self.gate_multiplier, act)
+        K.linear(act, self.down, out)
+
+
+register_feed_forward("swiglu", SwiGLU)

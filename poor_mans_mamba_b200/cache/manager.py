@@ -99,6 +99,7 @@ class CacheManager:
                                     dtype=dtype, device=self.device)
         self._free_slots: List[int] = list(range(self.num_slots - 1, -1, -1))
         self._slot_of: Dict[Hashable, int] = {}
+        self.lengths: Dict[Hashable, int] = {}  # tokens whose state each live request holds
         self.layers = sorted(state_specs)
 
     # ------------------------------------------------------------------ requests
@@ -110,6 +111,7 @@ class CacheManager:
             raise OutOfPages("no free state slot")
         slot = self._free_slots.pop()
         self._slot_of[req] = slot
+        self.lengths[req] = 0
         for t in self._fixed.values():
             t[slot].zero_()
         for g in self.groups.values():
@@ -165,6 +167,14 @@ class CacheManager:
                 if page >= 0:
                     g.pool.free(page, req)
         self._free_slots.append(self._slot_of.pop(req))
+        del self.lengths[req]
+
+    def advance(self, req: Hashable, n_tokens: int) -> int:
+        """A step has written ``n_tokens`` more tokens of ``req``; pages that a window has
+        passed are given back.  Returns the new length."""
+        self.lengths[req] += int(n_tokens)
+        self.trim(req, self.lengths[req])
+        return self.lengths[req]
 
     # ------------------------------------------------------------------ queries
     @property

@@ -30,9 +30,10 @@ __global__ void qkv_rope_store_kernel(const S* __restrict__ q, long long ldq, co
   const float fpos = static_cast<float>(pos);
   const int half = Dh / 2;
   const int kv_dim = Hkv * Dh;
-  S* k_dst;
-  S* v_dst;
-  if (pool) {
+  S* k_dst = nullptr;
+  S* v_dst = nullptr;
+  if (Hkv == 0) {
+  } else if (pool) {
     const int page = block_table[static_cast<size_t>(seq_of[t]) * max_blocks + pos / page_size];
     const size_t base = (static_cast<size_t>(page) * 2 * page_size + pos % page_size) * kv_dim;
     k_dst = pool + base;
@@ -88,8 +89,11 @@ PMM_EXPORT int pmm_qkv_rope_store(const void* q, long long ldq, const void* k, l
                                   void* pool, int page_size, void* q_out, void* k_out, void* v_out,
                                   int T, int Hq, int Hkv, int Dh, int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (Dh <= 0 || Dh % 2 || Hq <= 0 || Hkv <= 0) return PMM_ERR_BAD_ARGUMENT;
-  if (!pool && (!k_out || !v_out)) return PMM_ERR_BAD_ARGUMENT;
+  if (Dh <= 0 || Dh % 2 || Hq <= 0 || Hkv < 0) return PMM_ERR_BAD_ARGUMENT;
+  // Hkv == 0: queries only (a layer that reads another layer's keys and values)
+  if (Hkv > 0 && !pool && (!k_out || !v_out)) return PMM_ERR_BAD_ARGUMENT;
+  if (Hkv > 0 && (!k || !v)) return PMM_ERR_BAD_ARGUMENT;
+  if (Hkv == 0) pool = nullptr;
   if (pool && (!block_table || page_size <= 0)) return PMM_ERR_BAD_ARGUMENT;
   PMM_DISPATCH_DTYPE(dtype, S, pmm::qkv_rope_store_kernel<S><<<T, 256, 0, stream>>>(
                                    static_cast<const S*>(q), ldq, static_cast<const S*>(k), ldk,

@@ -33,7 +33,7 @@ class Model:
                 raise KeyError(f"unknown arrangement '{ls.arrangement}'")
             self.layers.append(factory(ls, hidden_size=spec.hidden_size))
         for call in spec.order:
-            if not (0 <= call.layer < len(self.layers) and 0 <= call.cache_of < len(self.layers)):
+            if not 0 <= call.layer < len(self.layers):
                 raise ValueError(f"execution order names a layer that does not exist: {call}")
         self.final_norm = build_part("norm", spec.final_norm, width=spec.hidden_size)
         self.embedding: Optional[Tensor] = None
@@ -85,9 +85,20 @@ class Model:
 
     # ------------------------------------------------------------------ state
     def state_specs(self) -> Dict[int, List[Tuple[str, StateSpec]]]:
-        """Layer index -> its (qualified name, spec) list, for layers that own a cache."""
-        owners = sorted({c.cache_of for c in self.spec.order})
-        return {i: self.layers[i].state_specs() for i in owners}
+        """Cache id -> (qualified name, spec) of every state kept under it.  A cache id is what
+        the execution order's ``cache_of`` names: the states that the layers run with that id
+        declare, each name once (a layer that only reads another's state declares none)."""
+        out: Dict[int, List[Tuple[str, StateSpec]]] = {}
+        for call in self.spec.order:
+            have = out.setdefault(call.cache_of, [])
+            for name, spec in self.layers[call.layer].state_specs():
+                known = dict(have)
+                if name in known:
+                    if known[name] != spec:
+                        raise ValueError(f"cache {call.cache_of}: state '{name}' declared with two layouts")
+                    continue
+                have.append((name, spec))
+        return out
 
     # ------------------------------------------------------------------ the step
     def forward(self, ctx: StepContext, caches: Dict[int, LayerCache]) -> Tensor:

@@ -79,7 +79,6 @@ class ModelRunner:
         self.device = cache.device
         self.dtype = cache.dtype
         self.workspace = Workspace(self.device)
-        self.lengths: Dict[Hashable, int] = {}
         self._staging = _Staging(self.device)
         self.steps_run = 0
         self.tokens_run = 0
@@ -87,14 +86,12 @@ class ModelRunner:
     # ------------------------------------------------------------------ requests
     def start(self, req: Hashable) -> None:
         self.cache.admit(req)
-        self.lengths[req] = 0
 
     def finish(self, req: Hashable) -> None:
         self.cache.release(req)
-        del self.lengths[req]
 
     def length(self, req: Hashable) -> int:
-        return self.lengths[req]
+        return self.cache.lengths[req]
 
     def can_run(self, entries: Sequence[StepEntry]) -> bool:
         """Whether the cache has the pages (and slots) this batch needs."""
@@ -103,7 +100,7 @@ class ModelRunner:
         for e in entries:
             known = self.cache.has(e.req)
             new_reqs += 0 if known else 1
-            new_len = self.lengths.get(e.req, 0) + len(e.tokens)
+            new_len = self.cache.lengths.get(e.req, 0) + len(e.tokens)
             for k, g in self.cache.groups.items():
                 reserved[k] += g.pages_to_grow(e.req, new_len) if known else g.blocks_for(new_len)
         return (new_reqs <= self.cache.free_slots
@@ -138,11 +135,11 @@ class ModelRunner:
         for e in entries:
             if not cache.has(e.req):
                 self.start(e.req)
-            cache.grow(e.req, self.lengths[e.req] + len(e.tokens))
+            cache.grow(e.req, cache.lengths[e.req] + len(e.tokens))
 
         n_seq = len(entries)
         new_lens = [len(e.tokens) for e in entries]
-        past = [self.lengths[e.req] for e in entries]
+        past = [cache.lengths[e.req] for e in entries]
         T = sum(new_lens)
         n_rows = sum(len(e.want) for e in entries)
         groups = list(cache.groups.values())
@@ -199,8 +196,7 @@ class ModelRunner:
         logits = self.model.forward(ctx, cache.layer_caches(block_tables))
 
         for e, n in zip(entries, new_lens):
-            self.lengths[e.req] += n
-            cache.trim(e.req, self.lengths[e.req])
+            cache.advance(e.req, n)
         self.steps_run += 1
         self.tokens_run += T
         return logits

@@ -1,0 +1,109 @@
+"""The Python entry point: ``Engine`` = model + cache + step function + scheduler + sampler.
+
+    eng = Engine(model_dir, dtype="bfloat16", max_tokens=65536, max_seqs=64)
+    outs = eng.generate([[1, 5, 9], [7, 7]], max_new_tokens=16)          # token ids in and out
+
+or, in the manner of the reference's scheduler (submit / poll,
+include/runtime/cluster_scheduler.h:111-142): ``rid = eng.submit(ids, params)``,
+``eng.step()`` until ``eng.poll(rid).done``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import torch
+
+from .cache import CacheManager
+from .engine.load import load_model
+from .engine.runner import ModelRunner, StepEntry
+from .engine.scheduler import Request, SamplingParams, Scheduler, StepPlan
+from .kernels import ops as K
+from .sampling import Sampler
+
+
+@dataclass
+class Response:
+    """A snapshot of a request (reference include/runtime/session.h:9-37: tokens, done, status)."""
+    tokens: List[int]
+    done: bool
+    status: str
+    preemptions: int = 0
+
+
+class Engine:
+    def __init__(self, model_dir: str, dtype: str = "bfloat16", device: str = "cuda:0",
+                 max_tokens: int = 65536, max_seqs: int = 64, page_size: int = 64,
+                 max_batched_tokens: int = 2048):
+        """``max_tokens``: capacity of the key/value cache in tokens (whole pages);
+        ``max_seqs``: most requests alive at a time (= number of fixed-state slots);
+        ``max_batched_tokens``: token budget of one step."""
+        if not torch.cuda.is_available():
+            raise RuntimeError("poor_mans_mamba_b200 runs on a CUDA device only; there is no CPU path")
+        K.ensure_built()
+        self.model, self.config = load_model(model_dir, dtype, device)
+        self.device = self.model.device
+        self.cache = CacheManager(self.model.state_specs(), page_size=page_size,
+                                  num_pages=max(1, max_tokens // page_size), num_slots=max_seqs,
+                                  dtype=self.model.dtype, device=self.device)
+        self.runner = ModelRunner(self.model, self.cache)
+        self.scheduler = Scheduler(self.cache, max_batched_tokens=max_batched_tokens, max_seqs=max_seqs)
+        self.sampler = Sampler(self.device)
+        self._next_id = 0
+
+    # ------------------------------------------------------------------ submit / step / poll
+    def submit(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
+        params = params or SamplingParams(eos_id=self.model.spec.eos_token_id)
+        vocab = self.model.vocab_size
+        for t in prompt:
+            if not 0 <= int(t) < vocab:
+                raise ValueError("token id out of range")
+        rid = self._next_id
+        self._next_id += 1
+        self.scheduler.add(rid, [int(t) for t in prompt], params)
+        return rid
+
+    def step(self) -> StepPlan:
+        """Plan and run one step; returns the plan (empty when nothing could run)."""
+        plan = self.scheduler.plan()
+        if not plan.entries:
+            return plan
+        entries = []
+        temps, seeds, steps = [], [], []
+        for e in plan.entries:
+            r = e.req
+            n_prompt = len(r.prompt)
+            if e.start >= n_prompt:
+                toks = r.output[e.start - n_prompt:e.start - n_prompt + e.count]
+            else:
+                toks = r.tokens[e.start:e.start + e.count]
+            entries.append(StepEntry(r.id, toks, [e.count - 1] if e.samples else []))
+            if e.samples:
+                temps.append(r.params.temperature)
+                seeds.append(r.params.seed)
+                steps.append(len(r.output))
+        with torch.cuda.device(self.device):
+            logits = self.runner.step(entries)
+            sampled = self.sampler.sample(logits, temps, seeds, steps)
+        self.scheduler.complete(plan, sampled)
+        return plan
+
+    def poll(self, rid: Hashable) -> Response:
+        r = self.scheduler.requests[rid]
+        return Response(list(r.output), r.finished, r.status, r.preemptions)
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    # ------------------------------------------------------------------ one-call generation
+    def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 16, temperature: float = 0.0,
+                 seed: int = 0, eos_token_id: Optional[int] = None) -> List[List[int]]:
+        """Generated token ids for each prompt (the eos token, if hit, is the last one).
+        ``eos_token_id`` None: the model's own; -1: never stop early."""
+        eos = self.model.spec.eos_token_id if eos_token_id is None else eos_token_id
+        ids = [self.submit(p, SamplingParams(max_new_tokens=max_new_tokens, eos_id=eos,
+                                             temperature=temperature, seed=seed + i))
+               for i, p in enumerate(prompts)]
+        while self.scheduler.has_work():
+            self.step()
+        return [self.poll(i).tokens for i in ids]

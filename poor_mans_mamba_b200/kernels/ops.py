@@ -330,37 +330,43 @@ def check_head_dim(head_dim: int) -> None:
           f"attention kernels take head sizes 16..256 in steps of 16, got {head_dim}")
 
 
-def qkv_rope_store(q: Tensor, k: Tensor, v: Tensor, q_scale: float, k_scale: float, v_scale: float,
-                   inv_freq: Optional[Tensor], positions: Tensor, seq_of: Tensor,
+def qkv_rope_store(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], q_scale: float, k_scale: float,
+                   v_scale: float, inv_freq: Optional[Tensor], positions: Tensor, seq_of: Tensor,
                    block_table: Optional[Tensor], pool: Optional[Tensor], q_out: Tensor,
                    k_out: Optional[Tensor], v_out: Optional[Tensor], n_q_heads: int, n_kv_heads: int,
                    head_dim: int) -> None:
     """Scales q/k/v, rotates q and k (when inv_freq is given) and stores k/v into the pages of
     ``pool`` [pages, 2, page_size, Hkv*Dh] through ``block_table`` [n_seq, max_blocks], or into
-    k_out/v_out when no pool is given."""
+    k_out/v_out when no pool is given.  With k and v None (n_kv_heads 0) only q is prepared."""
     _cuda(q, k, v, inv_freq, positions, seq_of, block_table, pool, q_out, k_out, v_out)
     check_head_dim(head_dim)
     T = q.shape[0]
-    ldq, ldk, ldv = _rows_view(q, "qkv: q"), _rows_view(k, "qkv: k"), _rows_view(v, "qkv: v")
-    kv_dim = n_kv_heads * head_dim
-    _need(q.shape[1] == n_q_heads * head_dim and k.shape[1] == kv_dim and v.shape[1] == kv_dim,
-          "qkv: slice widths do not match the head counts")
-    _need(q.dtype == k.dtype == v.dtype == q_out.dtype, "qkv: one storage type expected")
+    ldq = _rows_view(q, "qkv: q")
+    _need(q.shape[1] == n_q_heads * head_dim and q.dtype == q_out.dtype, "qkv: q width or type")
     _need(q_out.is_contiguous() and q_out.shape == (T, n_q_heads * head_dim), "qkv: q_out must be [T, Hq*Dh]")
     _f32vec(inv_freq, head_dim // 2, "qkv: inv_freq")
     _i32(positions, "qkv: positions")
     _i32(seq_of, "qkv: seq_of")
-    page_size, max_blocks = 0, 0
-    if pool is not None:
-        _need(block_table is not None, "qkv: a pool needs a block table")
-        _i32(block_table, "qkv: block_table")
-        _need(pool.dim() == 4 and pool.shape[1] == 2 and pool.shape[3] == kv_dim and pool.is_contiguous()
-              and pool.dtype == q.dtype, "qkv: pool must be contiguous [pages, 2, page_size, Hkv*Dh]")
-        page_size, max_blocks = pool.shape[2], block_table.shape[1]
+    page_size, max_blocks, ldk, ldv = 0, 0, 0, 0
+    if k is None or v is None:
+        _need(k is None and v is None and n_kv_heads == 0, "qkv: queries only means no k, no v, no kv heads")
+        pool = block_table = k_out = v_out = None
     else:
-        _need(k_out is not None and v_out is not None and k_out.is_contiguous() and v_out.is_contiguous()
-              and k_out.shape == (T, kv_dim) and v_out.shape == (T, kv_dim), "qkv: k_out/v_out must be [T, Hkv*Dh]")
-    _call("pmm_qkv_rope_store", q.data_ptr(), ldq, k.data_ptr(), ldk, v.data_ptr(), ldv, float(q_scale),
+        ldk, ldv = _rows_view(k, "qkv: k"), _rows_view(v, "qkv: v")
+        kv_dim = n_kv_heads * head_dim
+        _need(k.shape[1] == kv_dim and v.shape[1] == kv_dim and q.dtype == k.dtype == v.dtype,
+              "qkv: slice widths do not match the head counts")
+        if pool is not None:
+            _need(block_table is not None, "qkv: a pool needs a block table")
+            _i32(block_table, "qkv: block_table")
+            _need(pool.dim() == 4 and pool.shape[1] == 2 and pool.shape[3] == kv_dim and pool.is_contiguous()
+                  and pool.dtype == q.dtype, "qkv: pool must be contiguous [pages, 2, page_size, Hkv*Dh]")
+            page_size, max_blocks = pool.shape[2], block_table.shape[1]
+        else:
+            _need(k_out is not None and v_out is not None and k_out.is_contiguous() and v_out.is_contiguous()
+                  and k_out.shape == (T, kv_dim) and v_out.shape == (T, kv_dim),
+                  "qkv: k_out/v_out must be [T, Hkv*Dh]")
+    _call("pmm_qkv_rope_store", q.data_ptr(), ldq, _ptr(k), ldk, _ptr(v), ldv, float(q_scale),
           float(k_scale), float(v_scale), _ptr(inv_freq), positions.data_ptr(), seq_of.data_ptr(),
           _ptr(block_table), max_blocks, _ptr(pool), page_size, q_out.data_ptr(), _ptr(k_out),
           _ptr(v_out), T, n_q_heads, n_kv_heads, head_dim, _dt(q), _stream())

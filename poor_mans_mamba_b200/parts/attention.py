@@ -27,7 +27,8 @@ _MIN_SPLIT_LEN = 128
 class PagedAttention(Mixer):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position_encoding: Optional[Dict[str, Any]] = None, in_multiplier: float = 1.0,
-                 out_multiplier: float = 1.0, key_multiplier: float = 1.0, window: int = 0):
+                 out_multiplier: float = 1.0, key_multiplier: float = 1.0, window: int = 0,
+                 shared_kv: bool = False):
         if num_heads % num_kv_heads:
             raise ValueError("query heads must be a multiple of key/value heads")
         K.check_head_dim(head_dim)
@@ -39,6 +40,9 @@ class PagedAttention(Mixer):
         self.key_multiplier = float(key_multiplier)
         self.out_scale = float(out_multiplier)
         self.window = int(window)
+        # shared_kv: this layer projects queries only and reads the keys and values that the
+        # layer owning its cache has written (the execution order pairs them up)
+        self.shared_kv = bool(shared_kv)
         pe = position_encoding or {"kind": "none"}
         pe_params = {k: v for k, v in pe.items() if k != "kind"}
         self.position_encoding = build_part("position_encoding", PartSpec(pe["kind"], "", pe_params),
@@ -49,15 +53,22 @@ class PagedAttention(Mixer):
     # -- tensors and state
     def param_specs(self) -> List[ParamSpec]:
         d = self.hidden_size
+        if self.shared_kv:
+            return [ParamSpec("q_proj.weight", (self.q_dim, d)), ParamSpec("o_proj.weight", (d, self.q_dim))]
         return [ParamSpec("q_proj.weight", (self.q_dim, d)), ParamSpec("k_proj.weight", (self.kv_dim, d)),
                 ParamSpec("v_proj.weight", (self.kv_dim, d)), ParamSpec("o_proj.weight", (d, self.q_dim))]
 
     def state_specs(self) -> List[StateSpec]:
+        if self.shared_kv:
+            return []
         return [StateSpec.paged("kv", planes=2, width=self.kv_dim, window=self.window)]
 
     def bind(self, params: Dict[str, Tensor]) -> None:
-        self.w_in = torch.cat([params["q_proj.weight"], params["k_proj.weight"], params["v_proj.weight"]],
-                              dim=0).contiguous()
+        if self.shared_kv:
+            self.w_in = params["q_proj.weight"].contiguous()
+        else:
+            self.w_in = torch.cat([params["q_proj.weight"], params["k_proj.weight"], params["v_proj.weight"]],
+                                  dim=0).contiguous()
         self.w_out = params["o_proj.weight"].contiguous()
 
     def finalize(self, dtype: torch.dtype, device: torch.device) -> None:
@@ -65,7 +76,7 @@ class PagedAttention(Mixer):
 
     # -- shared input projection
     def input_rows(self) -> int:
-        return self.q_dim + 2 * self.kv_dim
+        return self.q_dim if self.shared_kv else self.q_dim + 2 * self.kv_dim
 
     def input_weight(self) -> Tensor:
         return self.w_in
@@ -84,24 +95,32 @@ class PagedAttention(Mixer):
         ws = ctx.workspace
         kv = cache.paged(f"{self.name}.kv")
         q = proj[:, :self.q_dim]
-        k = proj[:, self.q_dim:self.q_dim + self.kv_dim]
-        v = proj[:, self.q_dim + self.kv_dim:]
         q_rot = ws.alloc((T, self.q_dim), proj.dtype)
         s_in = self.in_multiplier
         pe = self.position_encoding
-        if hasattr(pe, "inv_freq"):  # rotary (or none): fused with the page write
-            K.qkv_rope_store(q, k, v, s_in, s_in * self.key_multiplier, s_in, pe.inv_freq, ctx.positions,
-                             ctx.seq_of, kv.block_table, kv.pool, q_rot, None, None, self.num_heads,
-                             self.num_kv_heads, self.head_dim)
-        else:  # a position encoding defined elsewhere: scale, let it act, then store
-            k_lin = ws.alloc((T, self.kv_dim), proj.dtype)
-            v_lin = ws.alloc((T, self.kv_dim), proj.dtype)
-            K.qkv_rope_store(q, k, v, s_in, s_in * self.key_multiplier, s_in, None, ctx.positions,
-                             ctx.seq_of, None, None, q_rot, k_lin, v_lin, self.num_heads,
-                             self.num_kv_heads, self.head_dim)
-            pe.apply(q_rot.view(T, self.num_heads, self.head_dim),
-                     k_lin.view(T, self.num_kv_heads, self.head_dim), ctx.positions)
-            K.kv_store(k_lin, v_lin, ctx.positions, ctx.seq_of, kv.block_table, kv.pool)
+        fused = hasattr(pe, "inv_freq")  # rotary (or none): one kernel with the page write
+        inv_freq = pe.inv_freq if fused else None
+        if self.shared_kv:  # queries only; keys and values are the cache owner's
+            K.qkv_rope_store(q, None, None, s_in, 0.0, 0.0, inv_freq, ctx.positions, ctx.seq_of, None, None,
+                             q_rot, None, None, self.num_heads, 0, self.head_dim)
+            if not fused:
+                pe.apply(q_rot.view(T, self.num_heads, self.head_dim), None, ctx.positions)
+        else:
+            k = proj[:, self.q_dim:self.q_dim + self.kv_dim]
+            v = proj[:, self.q_dim + self.kv_dim:]
+            if fused:
+                K.qkv_rope_store(q, k, v, s_in, s_in * self.key_multiplier, s_in, inv_freq, ctx.positions,
+                                 ctx.seq_of, kv.block_table, kv.pool, q_rot, None, None, self.num_heads,
+                                 self.num_kv_heads, self.head_dim)
+            else:  # a position encoding defined elsewhere: scale, let it act, then store
+                k_lin = ws.alloc((T, self.kv_dim), proj.dtype)
+                v_lin = ws.alloc((T, self.kv_dim), proj.dtype)
+                K.qkv_rope_store(q, k, v, s_in, s_in * self.key_multiplier, s_in, None, ctx.positions,
+                                 ctx.seq_of, None, None, q_rot, k_lin, v_lin, self.num_heads,
+                                 self.num_kv_heads, self.head_dim)
+                pe.apply(q_rot.view(T, self.num_heads, self.head_dim),
+                         k_lin.view(T, self.num_kv_heads, self.head_dim), ctx.positions)
+                K.kv_store(k_lin, v_lin, ctx.positions, ctx.seq_of, kv.block_table, kv.pool)
 
         n_splits, split_len = self.plan_splits(T, ctx.kv_len_bound)
         scratch = None

@@ -1,0 +1,115 @@
+"""Generation through the Python entry point and the command line (GPU)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from model_dirs import make_model_dir
+from plain.falcon_h1_plain import forward_logits, greedy_generate
+from tiny_configs import token_sequences
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module", params=["A", "B"])
+def case(request, tmp_path_factory):
+    which = request.param
+    d, cfg, weights = make_model_dir(which, str(tmp_path_factory.mktemp(f"gen{which}")))
+    return which, d, cfg, weights
+
+
+def prompts_of(which):
+    from tiny_configs import TINY_WORKLOADS
+    _, lens, n_dec = TINY_WORKLOADS[which]
+    return [s[:n] for s, n in zip(token_sequences(which), lens)], n_dec
+
+
+def test_greedy_generation_matches_plain(case):
+    from poor_mans_mamba_b200.entry import Engine
+    which, d, cfg, weights = case
+    prompts, n_dec = prompts_of(which)
+    want = [greedy_generate(p, n_dec, weights, cfg) for p in prompts]
+    eng = Engine(d, dtype="float32", max_tokens=1024, max_seqs=4, page_size=16, max_batched_tokens=24)
+    got = eng.generate(prompts, max_new_tokens=n_dec, eos_token_id=-1)
+    assert got == want
+    assert eng.cache.free_slots == 4 and eng.cache.min_free_pages() == 64
+    # bfloat16: same tokens except where the two best logits are closer than its rounding
+    eng16 = Engine(d, dtype="bfloat16", max_tokens=1024, max_seqs=4, page_size=16, max_batched_tokens=24)
+    got16 = eng16.generate(prompts, max_new_tokens=n_dec, eos_token_id=-1)
+    for p, g16, w in zip(prompts, got16, want):
+        for j, (a, b) in enumerate(zip(g16, w)):
+            if a != b:
+                logits = forward_logits(p + w[:j], weights, cfg)[-1]
+                top = torch.topk(logits, 2).values
+                assert float(top[0] - top[1]) < 0.03 * float(logits.abs().max()), (which, j, a, b)
+                break
+
+
+def test_stop_token_and_poll(case):
+    from poor_mans_mamba_b200.engine.scheduler import SamplingParams
+    from poor_mans_mamba_b200.entry import Engine
+    which, d, cfg, weights = case
+    prompts, _ = prompts_of(which)
+    want = greedy_generate(prompts[1], 6, weights, cfg)
+    eng = Engine(d, dtype="float32", max_tokens=512, max_seqs=2, page_size=16)
+    rid = eng.submit(prompts[1], SamplingParams(max_new_tokens=20, eos_id=want[3]))
+    assert eng.poll(rid).done is False
+    while eng.has_work():
+        eng.step()
+    r = eng.poll(rid)
+    stop = want.index(want[3])
+    assert r.done and r.status == "done" and r.tokens == want[:stop + 1]  # the stop token is kept
+    with pytest.raises(ValueError, match="out of range"):
+        eng.submit([cfg["vocab_size"] + 1])
+
+
+def test_preemption_on_the_device_gives_the_same_tokens(case):
+    """A pool too small for all requests at once: some are preempted and recomputed."""
+    from poor_mans_mamba_b200.entry import Engine
+    which, d, cfg, weights = case
+    prompts, _ = prompts_of(which)
+    prompts = prompts[:3]
+    n_new = 40
+    calm = Engine(d, dtype="float32", max_tokens=4096, max_seqs=4, page_size=16).generate(
+        prompts, max_new_tokens=n_new, eos_token_id=-1)
+    tight = Engine(d, dtype="float32", max_tokens=16 * 8, max_seqs=4, page_size=16)
+    got = tight.generate(prompts, max_new_tokens=n_new, eos_token_id=-1)
+    assert tight.scheduler.counters["preemptions"] > 0
+    assert got == calm
+    tight.cache.check()
+
+
+def test_temperature_sampling_is_seeded_and_independent_of_batching(case):
+    from poor_mans_mamba_b200.entry import Engine
+    which, d, cfg, weights = case
+    prompts, _ = prompts_of(which)
+    eng = Engine(d, dtype="float32", max_tokens=1024, max_seqs=4, page_size=16)
+    a = eng.generate(prompts, max_new_tokens=10, temperature=1.5, seed=7, eos_token_id=-1)
+    b = eng.generate(prompts, max_new_tokens=10, temperature=1.5, seed=7, eos_token_id=-1)
+    c = eng.generate(prompts, max_new_tokens=10, temperature=1.5, seed=8, eos_token_id=-1)
+    alone = eng.generate(prompts[:1], max_new_tokens=10, temperature=1.5, seed=7, eos_token_id=-1)
+    greedy = eng.generate(prompts, max_new_tokens=10, temperature=0.0, eos_token_id=-1)
+    assert a == b and a != c and a != greedy and alone[0] == a[0]
+
+
+def test_command_line(case):
+    which, d, cfg, weights = case
+    want = greedy_generate([5, 9, 2], 5, weights, cfg)
+    proc = subprocess.run([sys.executable, "-m", "poor_mans_mamba_b200", d, "256", "GPU", "1", "2", "5",
+                           "--dtype", "float32", "--prompt-ids", "5,9,2"], cwd=ROOT, capture_output=True,
+                          text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [l for l in proc.stdout.splitlines() if l.startswith("req_id=")]
+    assert len(lines) == 2 and all(f"tokens={want}" in l for l in lines), proc.stdout
+    bad = subprocess.run([sys.executable, "-m", "poor_mans_mamba_b200", d, "256", "CPU"], cwd=ROOT,
+                         capture_output=True, text=True, timeout=120)
+    assert bad.returncode == 1 and "no CPU path" in bad.stderr
+
+
+def test_smoke_entry():
+    sys.path.insert(0, ROOT)
+    import __graft_entry__
+    __graft_entry__.smoke()

@@ -1,0 +1,371 @@
+"""Each CUDA kernel alone against the plain formulas, at sizes other than the models' (GPU)."""
+import math
+import random
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from plain import falcon_h1_plain as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def K():
+    from poor_mans_mamba_b200.kernels import ops
+    return ops
+
+
+def tol(dtype, scale=1.0):
+    return (2e-6 if dtype == torch.float32 else 1.2e-2) * scale
+
+
+def close(got, ref, dtype, scale=None, what=""):
+    got, ref = got.detach().double().cpu(), ref.detach().double().cpu()
+    scale = float(ref.abs().max()) if scale is None else scale
+    err = float((got - ref).abs().max())
+    assert err <= tol(dtype, max(scale, 1e-3)), f"{what}: err {err:.3e} scale {scale:.3e}"
+
+
+def q(t, dtype):
+    """Round a float64/32 tensor to the storage type (so kernel and reference see equal inputs)."""
+    return t.to(dtype)
+
+
+def i32(x):
+    return torch.tensor(x, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed(dtype):
+    g = torch.Generator().manual_seed(1)
+    table = q(torch.randn(101, 200, generator=g), dtype).to(DEV)
+    toks = [100, 0, 57, 57, 3]
+    out = torch.empty(5, 200, device=DEV)
+    K().embed(out, table, i32(toks), 2.5)
+    close(out, P.embedding(toks, table.double().cpu(), 2.5), torch.float32, what="embed")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("D", [200, 1536, 13000])
+def test_add_rmsnorm(dtype, D):
+    g = torch.Generator().manual_seed(D)
+    T = 7
+    h0 = torch.randn(T, D, generator=g)
+    a, b = q(torch.randn(T, D, generator=g), dtype), q(torch.randn(T, D, generator=g), dtype)
+    w = torch.randn(D, generator=g)
+    for branches in ([], [(a, 0.6)], [(a, 0.6), (b, -1.3)]):
+        h = h0.clone().to(DEV)
+        out = torch.empty(T, D, dtype=dtype, device=DEV)
+        K().add_rmsnorm(h, [(t.to(DEV), s) for t, s in branches], w.to(DEV), 1e-3, out)
+        hs = h0.double()
+        for t, s in branches:
+            hs = hs + s * t.double()
+        close(h, hs, torch.float32, what="stream")
+        close(out, P.rms_norm(hs, w.double(), 1e-3), dtype, what="norm")
+    # selected rows leave the stream untouched
+    h = h0.clone().to(DEV)
+    rows = i32([6, 0, 3])
+    out = torch.empty(3, D, dtype=dtype, device=DEV)
+    K().add_rmsnorm(h, [(a.to(DEV), 0.6)], w.to(DEV), 1e-3, out, rows)
+    assert torch.equal(h.cpu(), h0)
+    close(out, P.rms_norm((h0.double() + 0.6 * a.double())[[6, 0, 3]], w.double(), 1e-3), dtype, what="rows")
+
+
+def _batch(lens_steps):
+    """lens_steps: per sequence a list of portion sizes.  Yields per step the flattened layout."""
+    n_steps = max(len(p) for p in lens_steps)
+    done = [0] * len(lens_steps)
+    for s in range(n_steps):
+        seqs = [(i, done[i], p[s]) for i, p in enumerate(lens_steps) if s < len(p)]
+        yield seqs
+        for i, a, n in seqs:
+            done[i] += n
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("C,Kc,bias", [(200, 4, True), (33, 2, False), (130, 5, True)])
+def test_conv1d_varlen_with_window(dtype, C, Kc, bias):
+    g = torch.Generator().manual_seed(C)
+    portions = [[5, 1, 1, 7], [1, 2, 9], [3, 1, 1, 1, 1]]
+    lens = [sum(p) for p in portions]
+    ld = C + 24  # the input is a column slice of a wider buffer
+    xs = [q(torch.randn(n, C, generator=g), dtype) for n in lens]
+    w = torch.randn(C, Kc, generator=g)
+    cb = torch.randn(C, generator=g) if bias else None
+    ps, pb = torch.rand(C, generator=g) + 0.5, (torch.randn(C, generator=g) if bias else None)
+    refs = [P.causal_conv1d_silu(x.double() * ps.double() + (pb.double() if bias else 0), w.double(),
+                                 cb.double() if bias else None) for x in xs]
+    window = torch.zeros(4, Kc - 1, C, device=DEV)
+    slots = [2, 0, 3]
+    got = [torch.empty(n, C, dtype=dtype) for n in lens]
+    dev = lambda t: None if t is None else t.to(DEV)
+    for seqs in _batch(portions):
+        T = sum(n for _, _, n in seqs)
+        buf = torch.zeros(T, ld, dtype=dtype, device=DEV)
+        x = buf[:, 8:8 + C]
+        seq_of, cu, t0 = [], [0], 0
+        for j, (i, a, n) in enumerate(seqs):
+            x[t0:t0 + n] = xs[i][a:a + n].to(DEV)
+            seq_of += [j] * n
+            t0 += n
+            cu.append(t0)
+        out = torch.empty(T, C, dtype=dtype, device=DEV)
+        sl = i32([slots[i] for i, _, _ in seqs])
+        if all(n == 1 for _, _, n in seqs):
+            K().conv1d_decode(x, dev(ps), dev(pb), dev(w), dev(cb), window, sl, out)
+        else:
+            K().conv1d_fwd(x, dev(ps), dev(pb), dev(w), dev(cb), window, i32(seq_of), i32(cu), sl, out)
+            K().conv1d_window_update(x, dev(ps), dev(pb), window, i32(cu), sl, len(seqs), Kc)
+        t0 = 0
+        for i, a, n in seqs:
+            got[i][a:a + n] = out[t0:t0 + n].cpu()
+            t0 += n
+    for i in range(3):
+        close(got[i], refs[i], dtype, what=f"conv seq {i}")
+    assert float(window[1].abs().sum()) == 0.0  # a slot nobody used
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,Pd,N,G", [(6, 20, 24, 3), (4, 64, 128, 1), (2, 40, 256, 2), (3, 16, 8, 1)])
+def test_ssm_scan_continues_from_saved_state(dtype, H, Pd, N, G):
+    g = torch.Generator().manual_seed(H * N)
+    portions = [[6, 1, 1, 9], [1, 30]]
+    lens = [sum(p) for p in portions]
+    I, conv_dim = H * Pd, H * Pd + 2 * G * N
+    xbcs = [q(torch.randn(n, conv_dim, generator=g), dtype) for n in lens]
+    dts = [q(torch.randn(n, H, generator=g), dtype) for n in lens]
+    a_log, d_skip, shift = torch.rand(H, generator=g) * 2, torch.randn(H, generator=g), torch.randn(H, generator=g)
+    refs = [P.ssm_recurrence(x[:, :I].double().view(-1, H, Pd), x[:, I:I + G * N].double().view(-1, G, N),
+                             x[:, I + G * N:].double().view(-1, G, N), dt.double() * 0.7, a_log.double(),
+                             d_skip.double(), shift.double()).reshape(-1, I) for x, dt in zip(xbcs, dts)]
+    state = torch.zeros(3, H, Pd, N, device=DEV)
+    slots = [2, 0]
+    got = [torch.empty(n, I, dtype=dtype) for n in lens]
+    for seqs in _batch(portions):
+        T = sum(n for _, _, n in seqs)
+        xbc = torch.cat([xbcs[i][a:a + n] for i, a, n in seqs]).to(DEV)
+        dtbuf = torch.zeros(T, H + 5, dtype=dtype, device=DEV)
+        dtbuf[:, 5:] = torch.cat([dts[i][a:a + n] for i, a, n in seqs]).to(DEV)
+        cu = [0]
+        for _, _, n in seqs:
+            cu.append(cu[-1] + n)
+        out = torch.empty(T, I, dtype=dtype, device=DEV)
+        K().ssm_scan_seq(xbc, dtbuf[:, 5:], 0.7, shift.to(DEV), a_log.to(DEV), d_skip.to(DEV), state, i32(cu),
+                         i32([slots[i] for i, _, _ in seqs]), len(seqs), out, G)
+        t0 = 0
+        for i, a, n in seqs:
+            got[i][a:a + n] = out[t0:t0 + n].cpu()
+            t0 += n
+    for i in range(2):
+        close(got[i], refs[i], dtype, what=f"scan seq {i}")
+    assert float(state[1].abs().sum()) == 0.0 and float(state[2].abs().sum()) > 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("mode", ["gate", "gate_then_norm", "norm_then_gate"])
+def test_gated_norm(dtype, mode):
+    g = torch.Generator().manual_seed(7)
+    T, I, G = 5, 240, 3
+    y, z = q(torch.randn(T, I, generator=g), dtype), q(torch.randn(T, I + 16, generator=g), dtype)
+    zb, w = torch.randn(I, generator=g), torch.randn(I, generator=g)
+    zz = z[:, 16:].double() * 1.3 + zb.double()
+    ref = P.gate_and_norm(y.double(), zz, None if mode == "gate" else w.double(), 1e-4, G, mode == "norm_then_gate")
+    out = torch.empty(T, I, dtype=dtype, device=DEV)
+    K().gated_norm(y.to(DEV), z.to(DEV)[:, 16:], 1.3, zb.to(DEV), None if mode == "gate" else w.to(DEV), 1e-4, G,
+                   mode == "norm_then_gate", out)
+    close(out, ref, dtype, what=mode)
+
+
+def _attention_case(dtype, Hq, Hkv, Dh, page_size, lens_steps, window=0, planted=True, n_splits=1, theta=1e4, seed=0):
+    """Runs qkv_rope_store + paged_attention over a script of portions with scattered pages and
+    compares with the plain rope + causal attention on the whole sequences."""
+    g = torch.Generator().manual_seed(seed)
+    ops = K()
+    lens = [sum(p) for p in lens_steps]
+    qd, kvd = Hq * Dh, Hkv * Dh
+    qs = [torch.randn(n, qd, generator=g) for n in lens]
+    ks = [torch.randn(n, kvd, generator=g) for n in lens]
+    vs = [torch.randn(n, kvd, generator=g) for n in lens]
+    if planted:
+        # one far key must win: the last query of every sequence is parallel to key 1
+        # (rotation undone below by giving them the same position-independent direction is
+        # impossible, so the score is made large through the norm instead)
+        for x_q, x_k in zip(qs, ks):
+            if x_k.shape[0] > 2:
+                x_k[1] *= 4.0
+                x_q[-1] *= 3.0
+    qs, ks, vs = [q(t, dtype) for t in qs], [q(t, dtype) for t in ks], [q(t, dtype) for t in vs]
+    q_scale, k_scale, v_scale = 0.8, 0.56, 0.8
+    inv_freq = (1.0 / torch.pow(torch.tensor(theta, dtype=torch.float32),
+                                (2.0 * torch.arange(Dh // 2, dtype=torch.float32)) / float(Dh)))
+    refs = []
+    for x_q, x_k, x_v in zip(qs, ks, vs):
+        n = x_q.shape[0]
+        pos = torch.arange(n)
+        rq = P.rope_rotate_half(x_q.double().view(n, Hq, Dh) * q_scale, pos, Dh, theta)
+        rk = P.rope_rotate_half(x_k.double().view(n, Hkv, Dh) * k_scale, pos, Dh, theta)
+        rv = x_v.double().view(n, Hkv, Dh) * v_scale
+        if dtype == torch.bfloat16:  # the cache holds rounded keys and values
+            rq, rk, rv = rq.to(dtype).double(), rk.to(dtype).double(), rv.to(dtype).double()
+        if window:
+            out = torch.zeros(n, Hq, Dh, dtype=torch.float64)
+            for t in range(n):
+                lo = max(0, t - window + 1)
+                o = P.causal_attention(torch.cat([rq[lo:t + 1]]), rk[lo:t + 1], rv[lo:t + 1], Hq // Hkv)
+                out[t] = o[-1]
+            refs.append(out.reshape(n, qd))
+        else:
+            refs.append(P.causal_attention(rq, rk, rv, Hq // Hkv).reshape(n, qd))
+    n_pages = sum((n + page_size - 1) // page_size for n in lens) + 3
+    order = list(range(n_pages))
+    random.Random(seed).shuffle(order)
+    pool = torch.zeros(n_pages + 1, 2, page_size, kvd, dtype=dtype, device=DEV)
+    pool[n_pages].fill_(float("nan"))  # the spare page must never be read for a real key
+    tables = [[] for _ in lens]
+    got = [torch.empty(n, qd, dtype=dtype) for n in lens]
+    for seqs in _batch(lens_steps):
+        T = sum(n for _, _, n in seqs)
+        for i, a, n in seqs:
+            while len(tables[i]) * page_size < a + n:
+                tables[i].append(order.pop())
+        width = max(len(tables[i]) for i, _, _ in seqs) + 1
+        bt = torch.full((len(seqs), width), n_pages, dtype=torch.int32)
+        for j, (i, _, _) in enumerate(seqs):
+            bt[j, :len(tables[i])] = torch.tensor(tables[i], dtype=torch.int32)
+        buf = torch.zeros(T, qd + 2 * kvd + 8, dtype=dtype, device=DEV)
+        pos, seq_of, t0 = [], [], 0
+        for j, (i, a, n) in enumerate(seqs):
+            buf[t0:t0 + n, 8:8 + qd] = qs[i][a:a + n].to(DEV)
+            buf[t0:t0 + n, 8 + qd:8 + qd + kvd] = ks[i][a:a + n].to(DEV)
+            buf[t0:t0 + n, 8 + qd + kvd:] = vs[i][a:a + n].to(DEV)
+            pos += list(range(a, a + n))
+            seq_of += [j] * n
+            t0 += n
+        q_rot = torch.empty(T, qd, dtype=dtype, device=DEV)
+        out = torch.empty(T, qd, dtype=dtype, device=DEV)
+        ops.qkv_rope_store(buf[:, 8:8 + qd], buf[:, 8 + qd:8 + qd + kvd], buf[:, 8 + qd + kvd:], q_scale, k_scale,
+                           v_scale, inv_freq.to(DEV), i32(pos), i32(seq_of), bt.to(DEV), pool, q_rot, None, None,
+                           Hq, Hkv, Dh)
+        split_len, scratch = 0, None
+        if n_splits > 1:
+            split_len = ((max(pos) + 1 + n_splits - 1) // n_splits + 31) // 32 * 32
+            ns = (max(pos) + 1 + split_len - 1) // split_len
+            scratch = torch.full((ops.attention_scratch_floats(T, Hq, Dh, ns),), float("nan"), device=DEV)
+        else:
+            ns = 1
+        ops.paged_attention(q_rot, pool, bt.to(DEV), i32(pos), i32(seq_of), out, Hq, Hkv, Dh, 1.0 / math.sqrt(Dh),
+                            window=window, n_splits=ns, split_len=split_len, scratch=scratch)
+        t0 = 0
+        for i, a, n in seqs:
+            got[i][a:a + n] = out[t0:t0 + n].cpu()
+            t0 += n
+    for i in range(len(lens)):
+        close(got[i], refs[i], dtype, what=f"attention seq {i} (len {lens[i]})")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hkv,Dh,page", [(6, 3, 48, 16), (8, 2, 64, 64), (5, 1, 128, 32), (2, 2, 16, 16), (9, 3, 256, 16)])
+def test_paged_attention_prefill_and_decode(dtype, Hq, Hkv, Dh, page):
+    steps = [[page + 1, 1, 1, page - 2, 1], [3, 2 * page, 1, 1], [1, 1, 1, 1, 1]]
+    _attention_case(dtype, Hq, Hkv, Dh, page, steps, seed=Hq)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_split_keys(dtype):
+    steps = [[300, 1, 1], [17, 1, 1], [129, 1, 1]]
+    _attention_case(dtype, 8, 2, 64, 16, steps, n_splits=4, seed=5)
+    _attention_case(dtype, 3, 1, 80, 32, steps, n_splits=7, seed=6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_window(dtype):
+    steps = [[40, 1, 1, 30], [5, 1, 60]]
+    _attention_case(dtype, 4, 2, 32, 16, steps, window=24, seed=9)
+    _attention_case(dtype, 4, 2, 32, 16, steps, window=24, n_splits=3, seed=9)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul_bias_and_scale(dtype):
+    g = torch.Generator().manual_seed(3)
+    T, Fd = 4, 1100
+    gu = q(torch.randn(T, 2 * Fd, generator=g), dtype)
+    out = torch.empty(T, Fd, dtype=dtype, device=DEV)
+    K().silu_mul(gu.to(DEV), 1.5, out)
+    close(out, P.silu(gu[:, :Fd].double() * 1.5) * gu[:, Fd:].double(), dtype, what="silu_mul")
+    x, b = q(torch.randn(T, 77, generator=g), dtype), torch.randn(77, generator=g)
+    xd = x.to(DEV)
+    K().add_row_bias_(xd, b.to(DEV))
+    close(xd, x.double() + b.double(), dtype, what="row bias")
+    f = torch.randn(1000, generator=g)
+    fd = f.to(DEV)
+    K().scale_f32_(fd, 0.3)
+    close(fd, f.double() * 0.3, torch.float32)
+    o = torch.empty(T, 77, device=DEV)
+    K().cast_scale(o, x.to(DEV), 0.3)
+    close(o, x.double() * 0.3, torch.float32)
+
+
+def test_library_linear_in_true_float32():
+    g = torch.Generator().manual_seed(4)
+    x, w = torch.randn(33, 1000, generator=g), torch.randn(70, 1000, generator=g)
+    out = torch.empty(33, 70, device=DEV)
+    K().linear(x.to(DEV), w.to(DEV), out)
+    err = float((out.double().cpu() - x.double() @ w.double().t()).abs().max())
+    assert err < 2e-4, err  # a reduced-precision (tf32) product would be off by ~3e-2 here
+    lo = torch.empty(33, 70, device=DEV)
+    K().linear_f32_out(x.bfloat16().to(DEV), w.bfloat16().to(DEV), lo, torch.empty(33, 70, dtype=torch.bfloat16, device=DEV), 0.5)
+    ref = 0.5 * (x.bfloat16().double() @ w.bfloat16().double().t())
+    assert float((lo.double().cpu() - ref).abs().max()) < 0.3
+
+
+def test_sampling_greedy_ties_and_temperature():
+    ops = K()
+    V = 1000
+    logits = torch.zeros(4, V)
+    logits[0, 5] = logits[0, 900] = 3.0     # tie: the first index wins
+    logits[1, 999] = 1.0
+    logits[2] = -1.0                         # all equal: index 0
+    logits[3, 17] = float("inf")
+    out = torch.empty(4, dtype=torch.int32, device=DEV)
+    ops.sample_rows(logits.to(DEV), None, None, None, out)
+    assert out.tolist() == [5, 999, 0, 17]
+    # temperature: draws follow softmax(logits / T); same (seed, step) -> same draw
+    V, n = 8, 4000
+    base = torch.tensor([2.0, 1.0, 0.0, -1.0, 0.5, 1.5, -3.0, 0.0])
+    rows = base.repeat(n, 1).to(DEV)
+    temps = torch.full((n,), 0.7, device=DEV)
+    seeds = torch.full((n,), 1234, dtype=torch.int64, device=DEV)
+    steps = torch.arange(n, dtype=torch.int32, device=DEV)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops.sample_rows(rows, temps, seeds, steps, out)
+    freq = torch.bincount(out.cpu().long(), minlength=V).double() / n
+    want = torch.softmax(base.double() / 0.7, 0)
+    assert float((freq - want).abs().max()) < 0.03, (freq, want)
+    out2 = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops.sample_rows(rows, temps, seeds, steps, out2)
+    assert torch.equal(out, out2)
+    ops.sample_rows(rows, temps, seeds + 1, steps, out2)
+    assert not torch.equal(out, out2)
+    temps[:] = 0.0  # temperature 0 inside a sampled batch is greedy
+    ops.sample_rows(rows, temps, seeds, steps, out2)
+    assert set(out2.tolist()) == {0}
+
+
+def test_unsupported_sizes_are_refused():
+    from poor_mans_mamba_b200.kernels.ops import KernelError
+    from poor_mans_mamba_b200.parts.attention import PagedAttention
+    from poor_mans_mamba_b200.parts.mamba2 import Mamba2Mixer
+    with pytest.raises(KernelError, match="steps of 16"):
+        PagedAttention(64, 4, 2, 24)
+    with pytest.raises(KernelError, match="steps of 16"):
+        PagedAttention(64, 4, 2, 512)
+    with pytest.raises(ValueError, match="d_state"):
+        Mamba2Mixer(64, 4, 16, 512, 4, 1)
+    with pytest.raises(KernelError, match="CUDA tensors only"):
+        K().silu_mul(torch.zeros(2, 4), 1.0, torch.zeros(2, 2))
+    with pytest.raises(KernelError, match="float32 or bfloat16"):
+        K().silu_mul(torch.zeros(2, 4, dtype=torch.float16, device=DEV), 1.0,
+                     torch.zeros(2, 2, dtype=torch.float16, device=DEV))

@@ -105,34 +105,30 @@ def script_mixed(seqs, max_live: int = 4, seed: int = 0, budget_pages=None, page
     waiting = list(range(len(seqs)))
     live: List[int] = []
     script: List[Step] = []
-    held = {}
 
     def pages(n):
         return (n + page_size - 1) // page_size
 
+    if budget_pages is not None:
+        assert all(pages(len(s)) <= budget_pages for s in seqs), "a sequence alone exceeds the pool"
     while waiting or live:
-        while waiting and len(live) < max_live:
+        # a request starts only when the pool can hold all of it beside the live ones, so the
+        # script can always go on; the pool is still far smaller than all requests together
+        while waiting and len(live) < max_live and (
+                budget_pages is None
+                or sum(pages(len(seqs[i])) for i in live) + pages(len(seqs[waiting[0]])) <= budget_pages):
             live.append(waiting.pop(0))
         portions, ended = [], []
         for i in list(live):
-            if len(live) > 1 and rng.random() < 0.25:
+            if len(live) > 1 and len(portions) > 0 and rng.random() < 0.25:
                 continue  # sits this step out
             rem = len(seqs[i]) - pos[i]
             # prompts advance in portions, the last quarter of every sequence token by token
             n = 1 if rem <= max(len(seqs[i]) // 4, 1) else min(rem, rng.choice([2, 3, 6, 11, 19, 40]))
-            if budget_pages is not None:
-                others = sum(v for k, v in held.items() if k != i)
-                while n > 0 and others + pages(pos[i] + n) > budget_pages:
-                    n -= 1
-                if n == 0:
-                    continue
-            held[i] = pages(pos[i] + n)
             portions.append((i, pos[i], n))
             pos[i] += n
             if pos[i] == len(seqs[i]):
                 ended.append(i)
                 live.remove(i)
-                held.pop(i)
-        if portions:
-            script.append((portions, ended))
+        script.append((portions, ended))
     return script

@@ -1,0 +1,309 @@
+#!/usr/bin/env python3
+"""Serving benchmark in the manner of the reference's generate harness
+(benchmarks/generate_bench.cpp:205-386: prefill tok/s, decode tok/s, batch always 1 there).
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step of the whole batch.  Default: Falcon-H1-0.5B layer sizes with
+random weights (seed 2), bfloat16, batch 8, every request at a context that ends at 4,096
+tokens.  Prints ONE JSON line:
+  value    decoded tokens/s over K steps, timed on the device with CUDA events;
+  e2e      the same through the Python entry point (Engine.step: scheduler, host token ids
+           in from pinned memory, sampled ids back to the host every step);
+  prefill  one 2,048-token prompt in one step: tokens/s, ms, fraction of the bf16 peak;
+  roofline bytes the decode step must read (every weight once, the cache of the live
+           requests) / its time, against the HBM copy peak;
+  points   decode tokens/s at batch 1 and 64.
+Peaks come from MEASURED_PEAKS.json beside this file when present, else from the stated
+fallback.  Inputs of a decode step (1 GB of weights plus the caches) exceed the L2, so no
+L2 flush is needed between timed iterations.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import random
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+# BASELINE.json configs[2]: Falcon-H1-0.5B layer sizes
+CONFIG_05B = {
+    "model_type": "falcon_h1", "architectures": ["FalconH1ForCausalLM"],
+    "num_hidden_layers": 36, "hidden_size": 1024, "vocab_size": 32784, "intermediate_size": 2048,
+    "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 64, "rope_theta": 1e11,
+    "attention_bias": False, "attention_dropout": 0.0, "mlp_bias": False,
+    "mamba_d_ssm": 1536, "mamba_n_heads": 24, "mamba_d_head": 64, "mamba_d_state": 128,
+    "mamba_n_groups": 1, "mamba_d_conv": 4, "mamba_chunk_size": 128, "mamba_conv_bias": True,
+    "mamba_proj_bias": False, "mamba_rms_norm": False, "mamba_norm_before_gate": False,
+    "rms_norm_eps": 1e-5, "hidden_act": "silu", "tie_word_embeddings": False,
+    "embedding_multiplier": 1.0, "lm_head_multiplier": 1.0, "attention_in_multiplier": 1.0,
+    "attention_out_multiplier": 1.0, "key_multiplier": 1.0, "ssm_in_multiplier": 1.0,
+    "ssm_out_multiplier": 1.0, "ssm_multipliers": [1.0] * 5, "mlp_multipliers": [1.0, 1.0],
+    "bos_token_id": 1, "eos_token_id": 11, "pad_token_id": 0,
+}
+FULL_LAYERS = 36
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as fh:
+                data = json.load(fh)
+            out = {"hbm_gbs": float(data["hbm_gbs"]), "bf16_tflops": float(data["bf16_tflops"]),
+                   "source": "measured"}
+            if "bf16_tflops_sustained" in data:
+                out["bf16_tflops_sustained"] = float(data["bf16_tflops_sustained"])
+            return out
+        except (OSError, KeyError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+
+    def _run(self):
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True,
+                                     timeout=5).stdout.strip().splitlines()
+                if out:
+                    f = [x.strip() for x in out[0].split(",")]
+                    self.samples.append(float(f[0]))
+                    self.max_mhz = float(f[1])
+                    for n, v in zip(names, f[2:]):
+                        if v.lower().startswith("active"):
+                            self.reasons.add(n)
+            except (OSError, ValueError, subprocess.SubprocessError, IndexError):
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=10)
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def model_numbers(cfg):
+    """Bytes and flops of the configuration, from its sizes alone."""
+    D, L, V, F = cfg["hidden_size"], cfg["num_hidden_layers"], cfg["vocab_size"], cfg["intermediate_size"]
+    Hq, Hkv, Dh = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    I, H, P, N, G, Kc = (cfg["mamba_d_ssm"], cfg["mamba_n_heads"], cfg["mamba_d_head"], cfg["mamba_d_state"],
+                         cfg["mamba_n_groups"], cfg["mamba_d_conv"])
+    conv_dim = I + 2 * G * N
+    proj = I + conv_dim + H
+    layer_mat = D * (proj + (Hq + 2 * Hkv) * Dh) + I * D + Hq * Dh * D + 3 * D * F
+    layer_vec = 2 * D + conv_dim * Kc + conv_dim + 3 * H
+    return {
+        "layer_matrix_params": layer_mat, "layer_vector_params": layer_vec,
+        "weight_bytes_per_step": L * (2 * layer_mat + 4 * layer_vec) + 2 * V * D + 2 * D + 4 * D,
+        "kv_bytes_per_token": L * 2 * Hkv * Dh * 2,
+        "state_bytes_per_seq": L * (H * P * N * 4 + (Kc - 1) * conv_dim * 4),
+        "flops_per_token_matmul": 2 * L * layer_mat,
+        "attn_flops": lambda T: L * 4 * Hq * Dh * T * (T + 1) // 2,
+        "ssd_flops_per_token": L * 6 * H * P * N,
+        "head_flops_per_row": 2 * V * D,
+        "params": L * (layer_mat + layer_vec) + 2 * V * D + D,
+    }
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096, help="context length at which decoding ends")
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration has "
+                    "(same layer sizes) where memory or time needs it")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a CMake C++ project without setup.py/pyproject.toml: pip install "
+                          "--no-index of /root/reference fails ('not installable'), and its CMake build fetches "
+                          "Eigen, nlohmann_json, safetensors-cpp and tokenizers-cpp from the network"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine serves from one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+
+    from poor_mans_mamba_b200.engine.runner import StepEntry
+    from poor_mans_mamba_b200.engine.scheduler import SamplingParams
+    from poor_mans_mamba_b200.entry import Engine
+    from poor_mans_mamba_b200.kernels import ops as K
+    from poor_mans_mamba_b200.weights import write_random_model
+
+    peaks = load_peaks()
+    cfg = dict(CONFIG_05B)
+    cfg["num_hidden_layers"] = args.layers
+    nums = model_numbers(cfg)
+    K_steps, W = args.steps, args.warmup
+    ctx_len = args.context
+    rng = random.Random(2)
+    vocab = cfg["vocab_size"]
+
+    tmp = tempfile.mkdtemp(prefix="pmm_bench_")
+    t0 = time.time()
+    write_random_model(cfg, seed=2, out_dir=tmp)
+    print(f"[bench] wrote random model in {time.time() - t0:.1f}s", file=sys.stderr, flush=True)
+
+    def make_engine(batch):
+        return Engine(tmp, dtype=args.dtype, max_tokens=batch * (ctx_len + 64), max_seqs=batch, page_size=64,
+                      max_batched_tokens=8192, max_seq_len=ctx_len + 64)
+
+    def decode_device_timed(eng, batch, steps, warmup):
+        """tokens/s with CUDA events around `steps` decode steps of `batch` requests whose context
+        ends at ctx_len; host work (index packing, launches) runs concurrently and is not waited for."""
+        prompt_len = ctx_len - steps - warmup
+        runner = eng.runner
+        reqs = [("bench", i) for i in range(batch)]
+        for r in reqs:  # prefill, untimed, in portions of <= 8192 tokens per step
+            toks = [rng.randrange(vocab) for _ in range(prompt_len)]
+            runner.step([StepEntry(r, toks, [])])
+        feed = [[rng.randrange(vocab) for _ in range(batch)] for _ in range(steps + warmup)]
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches0 = None
+        for s in range(steps + warmup):
+            if s == warmup:
+                torch.cuda.synchronize()
+                launches0 = runner.mark_launches()
+                start.record()
+            # the first step feeds host ids, the others the ids the device just sampled
+            runner.decode_tokens(reqs, feed[s] if s == 0 else None)
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop)
+        launches = runner.kernels_launched_since(launches0)
+        for r in reqs:
+            runner.finish(r)
+        return batch * steps / (ms / 1e3), ms / steps, launches
+
+    result = {}
+    with torch.cuda.device(0):
+        eng = make_engine(args.batch)
+        with ClockSampler() as clocks:
+            tok_s, ms_step, launches = decode_device_timed(eng, args.batch, K_steps, W)
+        clock_summary = clocks.summary()
+
+        # end to end through the entry point: scheduler + pinned host ids in + sampled ids out
+        prompt_len = ctx_len - K_steps - W - 1
+        ids = [eng.submit([rng.randrange(vocab) for _ in range(prompt_len)],
+                          SamplingParams(max_new_tokens=K_steps + W + 1, eos_id=-1)) for _ in range(args.batch)]
+        while any(r.pending > 1 or r.status == "waiting" for r in eng.scheduler.requests.values() if not r.finished):
+            eng.step()
+        for _ in range(W):
+            eng.step()
+        torch.cuda.synchronize()
+        h2d0 = eng.runner.h2d_bytes
+        t1 = time.perf_counter()
+        for _ in range(K_steps - 1):
+            eng.step()
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t1
+        e2e_steps = K_steps - 1
+        h2d_per_step = (eng.runner.h2d_bytes - h2d0) // e2e_steps
+        while eng.has_work():
+            eng.step()
+        assert all(len(eng.poll(i).tokens) == K_steps + W + 1 for i in ids)
+        e2e = {"value": args.batch * e2e_steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d_per_step),
+               "d2h_bytes_per_step": 4 * args.batch}
+
+        read_bytes = nums["weight_bytes_per_step"] + args.batch * (
+            nums["kv_bytes_per_token"] * (ctx_len - K_steps // 2) + nums["state_bytes_per_seq"])
+        achieved = read_bytes / (ms_step / 1e3) / 1e9
+        roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": round(achieved / peaks["hbm_gbs"], 4), "peak_source": peaks["source"]}
+
+        prefill, points = None, {}
+        if not args.no_points:
+            T = 2048
+            toks = [rng.randrange(vocab) for _ in range(T)]
+            times = []
+            for it in range(W + 3):
+                s_ev, e_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                s_ev.record()
+                eng.runner.step([StepEntry(("pf", it), toks, [T - 1])])
+                e_ev.record()
+                torch.cuda.synchronize()
+                eng.runner.finish(("pf", it))
+                if it >= W:
+                    times.append(s_ev.elapsed_time(e_ev))
+            pf_ms = statistics.median(times)
+            flops = (T * (nums["flops_per_token_matmul"] + nums["ssd_flops_per_token"]) + nums["attn_flops"](T)
+                     + nums["head_flops_per_row"])
+            prefill = {"value": round(T / (pf_ms / 1e3), 1), "tokens": T, "ms": round(pf_ms, 3),
+                       "frac": round(flops / (pf_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4),
+                       "flops": flops, "peak_tflops": peaks["bf16_tflops"], "peak_source": peaks["source"]}
+            del eng
+            torch.cuda.empty_cache()
+            for b in (1, 64):
+                e = make_engine(b)
+                steps_b = min(K_steps, 32)
+                v, _, _ = decode_device_timed(e, b, steps_b, W)
+                points[f"decode_b{b}"] = round(v, 1)
+                del e
+                torch.cuda.empty_cache()
+
+    result = {
+        "metric": "decode tokens/s (Falcon-H1-0.5B layer sizes, random weights)", "value": round(tok_s, 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": K_steps, "warmup": W, "ms_per_step": round(ms_step, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
+        "data": "synthetic: uniform random token ids (seed 2), random-init weights (seed 2)",
+        "config": {"model": "falcon-h1-0.5b-sizes", "layers": args.layers, "layers_full": FULL_LAYERS,
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": vocab, "d_ssm": cfg["mamba_d_ssm"],
+                   "ssm_heads": cfg["mamba_n_heads"], "d_state": cfg["mamba_d_state"], "d_conv": cfg["mamba_d_conv"],
+                   "chunk": cfg["mamba_chunk_size"], "global_batch": args.batch, "seq_len": ctx_len,
+                   "parallelism": "single-gpu", "page_size": 64, "l2": "inputs exceed L2 (no flush)"},
+        "clocks": clock_summary, "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items()},
+        "gpu_launches": int(launches), "roofline": roofline, "impl": "ours",
+    }
+    if prefill is not None:
+        result["prefill"] = prefill
+    if points:
+        result["points"] = points
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -100,6 +100,8 @@ class CacheManager:
         self._free_slots: List[int] = list(range(self.num_slots - 1, -1, -1))
         self._slot_of: Dict[Hashable, int] = {}
         self.lengths: Dict[Hashable, int] = {}  # tokens whose state each live request holds
+        self.admissions: Dict[Hashable, int] = {}  # a number that changes every time a request is admitted
+        self._admission_counter = 0
         self.layers = sorted(state_specs)
 
     # ------------------------------------------------------------------ requests
@@ -112,6 +114,8 @@ class CacheManager:
         slot = self._free_slots.pop()
         self._slot_of[req] = slot
         self.lengths[req] = 0
+        self._admission_counter += 1
+        self.admissions[req] = self._admission_counter
         for t in self._fixed.values():
             t[slot].zero_()
         for g in self.groups.values():
@@ -168,6 +172,7 @@ class CacheManager:
                     g.pool.free(page, req)
         self._free_slots.append(self._slot_of.pop(req))
         del self.lengths[req]
+        del self.admissions[req]
 
     def advance(self, req: Hashable, n_tokens: int) -> int:
         """A step has written ``n_tokens`` more tokens of ``req``; pages that a window has

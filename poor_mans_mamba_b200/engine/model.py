@@ -41,8 +41,6 @@ class Model:
         self.dtype: Optional[torch.dtype] = None
         self.device: Optional[torch.device] = None
         self._branch_buffers = max(l.branch_buffers_needed() for l in self.layers) if self.layers else 1
-        self._logits: Optional[Tensor] = None
-        self._logits_lowp: Optional[Tensor] = None
 
     # ------------------------------------------------------------------ tensors
     def named_parts(self) -> List[Tuple[str, Part]]:
@@ -102,8 +100,8 @@ class Model:
 
     # ------------------------------------------------------------------ the step
     def forward(self, ctx: StepContext, caches: Dict[int, LayerCache]) -> Tensor:
-        """Runs the step's tokens through the layers; returns logits [n_rows, V] float32 (a
-        buffer of the model, valid until the next call)."""
+        """Runs the step's tokens through the layers; returns logits [n_rows, V] float32 (taken
+        from the step's workspace: valid until the workspace is reset by the next step)."""
         ws = ctx.workspace
         T, D = ctx.n_tokens, self.hidden_size
         h = ws.alloc((T, D), torch.float32)
@@ -115,21 +113,18 @@ class Model:
             stream.flush()
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=h.device)
         normed = stream.normed(self.final_norm, rows=ctx.logit_rows)
-        return self._head(normed, ctx.n_rows)
+        return self._head(normed, ctx)
 
-    def _head(self, normed: Tensor, n_rows: int) -> Tensor:
-        V = self.vocab_size
-        if self._logits is None or self._logits.shape[0] < n_rows:
-            cap = max(n_rows, 16)
-            self._logits = torch.empty((cap, V), dtype=torch.float32, device=normed.device)
-            self._logits_lowp = (torch.empty((cap, V), dtype=normed.dtype, device=normed.device)
-                                 if normed.dtype != torch.float32 else None)
-        logits = self._logits[:n_rows]
+    def _head(self, normed: Tensor, ctx: StepContext) -> Tensor:
+        n_rows, V = normed.shape[0], self.vocab_size
+        ws = ctx.workspace
+        logits = ws.alloc((n_rows, V), torch.float32)
         mult = self.spec.head_multiplier
         if normed.dtype == torch.float32:
             K.linear(normed, self.head, logits)
             if mult != 1.0:
                 K.scale_f32_(logits, mult)
         else:
-            K.linear_f32_out(normed, self.head, logits, self._logits_lowp[:n_rows], mult)
+            low = None if K.mm_has_f32_out() else ws.alloc((n_rows, V), normed.dtype)
+            K.linear_f32_out(normed, self.head, logits, low, mult)
         return logits

@@ -82,6 +82,15 @@ class ModelRunner:
         self._staging = _Staging(self.device)
         self.steps_run = 0
         self.tokens_run = 0
+        self.h2d_bytes = 0
+        self.graphs = None
+        self._sampler = None
+
+    def enable_graphs(self, max_seq_len: int, buckets=None) -> None:
+        """Serve decode-only steps from CUDA graphs (captured per batch-size bucket on first use).
+        ``max_seq_len`` bounds the context of any request that decodes this way."""
+        from .decode_graph import GraphDecoder
+        self.graphs = GraphDecoder(self, max_seq_len, buckets)
 
     # ------------------------------------------------------------------ requests
     def start(self, req: Hashable) -> None:
@@ -89,6 +98,43 @@ class ModelRunner:
 
     def finish(self, req: Hashable) -> None:
         self.cache.release(req)
+        if self.graphs is not None:
+            self.graphs.forget(req)
+
+    def decode_tokens(self, reqs: Sequence[Hashable], tokens: Optional[Sequence[int]],
+                      temperatures: Optional[Sequence[float]] = None, seeds: Optional[Sequence[int]] = None,
+                      steps: Optional[Sequence[int]] = None) -> Tensor:
+        """One decode step (one token per request) including sampling; returns the sampled ids
+        [n] int32 on the device.  ``tokens`` None feeds every request the id sampled for it by
+        the previous call (same requests, same order)."""
+        if self.graphs is not None and all(
+                self.cache.lengths[r] + 1 <= self.graphs.max_seq_len for r in reqs):
+            out = self.graphs.decode(reqs, tokens, temperatures, seeds, steps)
+            if out is not None:
+                self.h2d_bytes += self.graphs.h2d_bytes_last
+                self.steps_run += 1
+                self.tokens_run += len(reqs)
+                return out
+        if self._sampler is None:
+            from ..sampling import Sampler
+            self._sampler = Sampler(self.device)
+        if tokens is None:
+            tokens = self._last_sampled.tolist()
+        logits = self.step([StepEntry(r, [int(t)], [0]) for r, t in zip(reqs, tokens)])
+        self._last_sampled = self._sampler.sample_device(logits, temperatures, seeds, steps)
+        return self._last_sampled
+
+    def kernels_launched_since(self, launch_count_before: int) -> int:
+        """Own kernels launched since ``launch_count_before`` (a value of kernels.ops.launch_count),
+        graph replays counted by the kernels they hold."""
+        from ..kernels import ops as K
+        n = K.launch_count - launch_count_before
+        return n + (self.graphs.kernels_replayed - getattr(self, "_replayed_mark", 0) if self.graphs else 0)
+
+    def mark_launches(self) -> int:
+        from ..kernels import ops as K
+        self._replayed_mark = self.graphs.kernels_replayed if self.graphs else 0
+        return K.launch_count
 
     def length(self, req: Hashable) -> int:
         return self.cache.lengths[req]
@@ -182,6 +228,7 @@ class ModelRunner:
                     tab[s, :len(row)] = arr
 
         dev = self._staging.upload(total, fill)
+        self.h2d_bytes += 4 * total
         block_tables = {g.key: dev[off:off + n_seq * w].view(n_seq, w)
                         for g, w, off in zip(groups, widths, tab_offsets)}
         self.workspace.reset()

@@ -34,10 +34,12 @@ class Response:
 class Engine:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", device: str = "cuda:0",
                  max_tokens: int = 65536, max_seqs: int = 64, page_size: int = 64,
-                 max_batched_tokens: int = 2048):
+                 max_batched_tokens: int = 2048, max_seq_len: int = 8192, cuda_graphs: bool = True):
         """``max_tokens``: capacity of the key/value cache in tokens (whole pages);
         ``max_seqs``: most requests alive at a time (= number of fixed-state slots);
-        ``max_batched_tokens``: token budget of one step."""
+        ``max_batched_tokens``: token budget of one step; ``max_seq_len``: longest context
+        served by the CUDA-graph decode path (longer requests decode through plain launches);
+        ``cuda_graphs``: capture decode-only steps into CUDA graphs."""
         if not torch.cuda.is_available():
             raise RuntimeError("poor_mans_mamba_b200 runs on a CUDA device only; there is no CPU path")
         K.ensure_built()
@@ -47,6 +49,8 @@ class Engine:
                                   num_pages=max(1, max_tokens // page_size), num_slots=max_seqs,
                                   dtype=self.model.dtype, device=self.device)
         self.runner = ModelRunner(self.model, self.cache)
+        if cuda_graphs:
+            self.runner.enable_graphs(max_seq_len)
         self.scheduler = Scheduler(self.cache, max_batched_tokens=max_batched_tokens, max_seqs=max_seqs)
         self.sampler = Sampler(self.device)
         self._next_id = 0
@@ -83,8 +87,13 @@ class Engine:
                 seeds.append(r.params.seed)
                 steps.append(len(r.output))
         with torch.cuda.device(self.device):
-            logits = self.runner.step(entries)
-            sampled = self.sampler.sample(logits, temps, seeds, steps)
+            if all(e.count == 1 and e.samples for e in plan.entries):
+                ids = self.runner.decode_tokens([e.req.id for e in plan.entries],
+                                                [en.tokens[0] for en in entries], temps, seeds, steps)
+                sampled = self.sampler.to_host(ids)
+            else:
+                logits = self.runner.step(entries)
+                sampled = self.sampler.sample(logits, temps, seeds, steps)
         self.scheduler.complete(plan, sampled)
         return plan
 

@@ -148,19 +148,25 @@ def linear(x: Tensor, weight: Tensor, out: Tensor) -> Tensor:
 _MM_F32_OUT: Optional[bool] = None
 
 
+def mm_has_f32_out() -> bool:
+    """Whether the GEMM library gives a float32 result from bfloat16 operands directly."""
+    global _MM_F32_OUT
+    if _MM_F32_OUT is None:
+        try:
+            a = torch.zeros(8, 16, dtype=torch.bfloat16, device="cuda")
+            torch.mm(a, a.t(), out_dtype=torch.float32)
+            _MM_F32_OUT = True
+        except (TypeError, RuntimeError):
+            _MM_F32_OUT = False
+    return _MM_F32_OUT
+
+
 def linear_f32_out(x: Tensor, weight: Tensor, out: Tensor, scratch_low: Optional[Tensor], scale: float) -> None:
     """out (float32) = scale * (x @ weight^T) for bfloat16 operands.  The library is asked for
     a float32 result directly; a library build without that option gets a bfloat16 product
     that is widened (and scaled) by cast_scale."""
-    global _MM_F32_OUT
     _cuda(x, weight, out)
-    if _MM_F32_OUT is None:
-        try:
-            torch.mm(x[:1], weight[:8].t(), out_dtype=torch.float32)
-            _MM_F32_OUT = True
-        except (TypeError, RuntimeError):
-            _MM_F32_OUT = False
-    if _MM_F32_OUT:
+    if mm_has_f32_out():
         torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
         if scale != 1.0:
             scale_f32_(out, scale)

@@ -42,6 +42,13 @@ class Sampler:
             K.sample_rows(logits, temp, sd, st, out)
         return out
 
+    def to_host(self, ids: torch.Tensor) -> List[int]:
+        """Device token ids -> python ints through a pinned buffer (waits for the step)."""
+        n = ids.numel()
+        _, host = self._buffers(n)
+        host.copy_(ids, non_blocking=False)
+        return host.tolist()
+
     def sample(self, logits: torch.Tensor, temperatures: Optional[Sequence[float]] = None,
                seeds: Optional[Sequence[int]] = None, steps: Optional[Sequence[int]] = None) -> List[int]:
         n = logits.shape[0]

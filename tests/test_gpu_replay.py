@@ -130,3 +130,38 @@ def test_trace_run_program(case, dtype, tmp_path):
         got = torch.from_numpy(np.fromfile(path, dtype="<f4").reshape(len(rows), v).copy())
         ref = torch.stack([refs[i][p] for i, p in rows])
         H.check_rows(got, ref, dtype, f"trace_run {dtype} step {step}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_through_cuda_graphs(case, dtype):
+    """Decode-only steps served from captured graphs: batches of changing size (buckets with
+    padded rows), requests that end and slots and pages that are used again."""
+    from poor_mans_mamba_b200.engine import StepEntry
+    which, d, cfg, seqs, refs = case
+    runner = H.make_runner(d, dtype, page_size=16, num_pages=40, num_slots=4)
+    runner.enable_graphs(max_seq_len=256)
+    order = [3, 1, 5, 2, 4, 0]  # sequence indices, three live at a time
+    live, nxt, pos = [], 0, {}
+    while live or nxt < len(order):
+        while len(live) < 3 and nxt < len(order):
+            i = order[nxt]
+            nxt += 1
+            head = max(len(seqs[i]) // 3, 1)
+            lg = runner.step([StepEntry(("g", i), seqs[i][:head], list(range(head)))]).cpu()
+            H.check_rows(lg, refs[i][:head], dtype, f"graph case prompt of seq {i}")
+            pos[i] = head
+            live.append(i)
+        reqs = [("g", i) for i in live]
+        ids = runner.decode_tokens(reqs, [seqs[i][pos[i]] for i in live])
+        assert ids.shape == (len(live),)
+        logits = runner.graphs.last_logits(len(live)).cpu()
+        for row, i in enumerate(list(live)):
+            H.check_rows(logits[row:row + 1], refs[i][pos[i]:pos[i] + 1], dtype,
+                         f"graph decode seq {i} pos {pos[i]} batch {len(live)}")
+            assert int(ids[row]) == int(torch.argmax(logits[row]))
+            pos[i] += 1
+            if pos[i] == len(seqs[i]):
+                runner.finish(("g", i))
+                live.remove(i)
+        runner.cache.check()
+    assert runner.graphs.replays > 100 and set(runner.graphs.buckets) <= {1, 2, 4}

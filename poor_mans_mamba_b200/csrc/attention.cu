@@ -7,7 +7,7 @@
 // absolute position pos sees keys lo..pos of its own request through the block table;
 // lo = pos-window+1 for a sliding window, else 0.  With one split the result is written
 // normalised; with several, (max, sum, unnormalised output) go to scratch and
-// attention_combine merges them.  This kernel is the 32-bit path and the general
+// flash_combine (attention_mma.cu) merges them.  This kernel is the 32-bit path and the general
 // fallback of the bfloat16 path; the tensor-core kernels cover the long cases.
 //
 //   sc[s] = (q.K[s]) * scale;  p = exp(sc - max);  o = sum p V / sum p
@@ -131,30 +131,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   }
 }
 
-// One warp per (token, query head): merges the partial results of the key splits.
-template <typename S>
-__global__ void attention_combine_kernel(const float* __restrict__ part_o,
-                                         const float* __restrict__ part_ml, S* __restrict__ out,
-                                         int n_rows, int n_splits, int Dh) {
-  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (row >= n_rows) return;
-  const float* ml = part_ml + static_cast<size_t>(row) * n_splits * 2;
-  float mx = -CUDART_INF_F;
-  for (int z = 0; z < n_splits; ++z) mx = fmaxf(mx, ml[2 * z]);
-  float total = 0.f;
-  for (int z = 0; z < n_splits; ++z)
-    if (ml[2 * z + 1] > 0.f) total += ml[2 * z + 1] * expf(ml[2 * z] - mx);
-  const float inv = 1.f / total;
-  for (int d = lane; d < Dh; d += 32) {
-    float o = 0.f;
-    for (int z = 0; z < n_splits; ++z)
-      if (ml[2 * z + 1] > 0.f)
-        o += part_o[(static_cast<size_t>(row) * n_splits + z) * Dh + d] * expf(ml[2 * z] - mx);
-    stf(out + static_cast<size_t>(row) * Dh + d, o * inv);
-  }
-}
-
 }  // namespace pmm
 
 // part_o needs T*Hq*n_splits*Dh floats and part_ml T*Hq*n_splits*2 floats when n_splits > 1.
@@ -178,11 +154,6 @@ PMM_EXPORT int pmm_paged_attention(const void* q, const void* pool, const int* b
         static_cast<const S*>(q), static_cast<const S*>(pool), block_table, max_blocks, positions,
         seq_of, static_cast<S*>(out), part_o, part_ml, scale, window, split_len, n_splits,
         page_size, Hq, Hkv, Dh);
-    if (n_splits > 1) {
-      const int rows = T * Hq;
-      pmm::attention_combine_kernel<S><<<(rows + 3) / 4, 128, 0, stream>>>(
-          part_o, part_ml, static_cast<S*>(out), rows, n_splits, Dh);
-    }
   });
   return pmm::launch_status();
 }

@@ -1,0 +1,456 @@
+// Paged grouped-query flash attention on tensor cores (bfloat16 storage, float accumulate).
+//
+// One block = one tile of query rows of ONE sequence and ONE key/value head, and one key
+// split.  A "row" is a (token, query head of the group) pair, so the G = Hq/Hkv query
+// heads that share a key/value head share every K/V tile that is fetched.  K/V tiles of 64
+// keys are gathered row by row through the block table with cp.async (16 bytes a time,
+// zero-filled beyond the key range) into double-buffered shared memory; S = Q K^T and
+// O += P V run on mma.sync m16n8k16 with ldmatrix operands; softmax is the online form in
+// float (exp2 with the scale folded in).  Two shapes:
+//   * tile of 64 rows, warp w owns rows 16w..16w+15 and walks all keys   (prompt portions)
+//   * tile of 16 rows, the 4 warps split every 64-key tile by keys and are merged at the
+//     end through shared memory                                           (decode: G rows)
+// With several key splits the block writes (max, sum, unnormalised output) and
+// flash_combine merges them; with one split it writes the normalised output.
+//
+//   sc[s] = (q.K[s]) * scale;  p = exp(sc - max);  o = sum p V / sum p
+// (reference src/ops/gpu/attention.cu:44-105), keys lo..pos per token, lo from the window.
+#include "common.cuh"
+#include <math_constants.h>
+
+namespace pmm {
+
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool pred) {
+  const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+  const int sz = pred ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(sz));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3,
+                                            const void* smem) {
+  const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3,
+                                                  const void* smem) {
+  const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float* d, const unsigned* a, unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const unsigned*>(&v);
+}
+
+constexpr int kFlashKeys = 64;  // keys per tile
+
+template <int DH, bool SPLITW>
+__global__ void __launch_bounds__(128)
+    flash_paged_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pool,
+                       const int* __restrict__ block_table, int max_blocks,
+                       const int* __restrict__ positions, const int* __restrict__ cu,
+                       bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                       float scale_log2, int window, int split_len, int n_splits, int page_size,
+                       int n_seq, int Hq, int Hkv) {
+  constexpr int M = SPLITW ? 16 : 64;
+  constexpr int KT = kFlashKeys;
+  constexpr int STRIDE = DH + 8;
+  constexpr int WKEYS = SPLITW ? 16 : 64;
+  constexpr int NT_S = WKEYS / 8;
+  constexpr int KS_Q = DH / 16;
+  constexpr int NT_O = DH / 8;
+  constexpr int CHUNKS = DH / 8;  // 16-byte chunks per row
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
+  bf16* sK = sQ + M * STRIDE;
+  bf16* sV = sK + 2 * KT * STRIDE;
+  __shared__ int s_pos[64];
+  __shared__ float s_wm[4][16], s_wl[4][16], s_M[16], s_L[16];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int G = Hq / Hkv;
+  const int tpt = M / G;  // tokens per tile (host guarantees G <= M)
+  const int hk = blockIdx.y, z = blockIdx.z;
+  const int kv_dim = Hkv * DH;
+
+  // which sequence and which of its tokens this tile covers
+  int seq = 0, acc = 0;
+  for (; seq < n_seq; ++seq) {
+    const int n = cu[seq + 1] - cu[seq];
+    const int nt = (n + tpt - 1) / tpt;
+    if (static_cast<int>(blockIdx.x) < acc + nt) break;
+    acc += nt;
+  }
+  if (seq >= n_seq) return;
+  const int tok0 = cu[seq] + (static_cast<int>(blockIdx.x) - acc) * tpt;
+  const int n_tok = min(cu[seq + 1], tok0 + tpt) - tok0;
+  const int n_rows = n_tok * G;
+  const int* bt = block_table + static_cast<size_t>(seq) * max_blocks;
+
+  if (tid < 64) s_pos[tid] = (tid < n_rows) ? positions[tok0 + tid / G] : -1;
+  const int pos_min = positions[tok0], pos_max = positions[tok0 + n_tok - 1];
+  const int lo_all = window > 0 ? max(0, pos_min - window + 1) : 0;
+  const int k_begin = max(lo_all, z * split_len);
+  const int k_end = min(pos_max + 1, (z + 1) * split_len);
+
+  // Q rows -> shared memory (rows beyond the tile are zero)
+  for (int c = tid; c < M * CHUNKS; c += 128) {
+    const int r = c / CHUNKS, col = c % CHUNKS;
+    const bool ok = r < n_rows;
+    const size_t src = ok ? (static_cast<size_t>(tok0 + r / G) * Hq + hk * G + r % G) * DH + col * 8 : 0;
+    cp_async16(sQ + r * STRIDE + col * 8, q + src, ok);
+  }
+
+  auto load_tile = [&](int stage, int base) {
+    bf16* dK = sK + stage * KT * STRIDE;
+    bf16* dV = sV + stage * KT * STRIDE;
+    for (int c = tid; c < KT * CHUNKS; c += 128) {
+      const int r = c / CHUNKS, col = c % CHUNKS;
+      const int key = base + r;
+      const bool ok = key >= k_begin && key < k_end;
+      size_t src = 0;
+      if (ok) {
+        const int page = bt[key / page_size];
+        src = (static_cast<size_t>(page) * 2 * page_size + key % page_size) * kv_dim + hk * DH + col * 8;
+      }
+      cp_async16(dK + r * STRIDE + col * 8, pool + src, ok);
+      cp_async16(dV + r * STRIDE + col * 8, pool + src + static_cast<size_t>(page_size) * kv_dim, ok);
+    }
+  };
+
+  const int first_tile = (k_begin / KT) * KT;
+  const int n_tiles = k_end > k_begin ? (k_end - first_tile + KT - 1) / KT : 0;
+  if (n_tiles > 0) load_tile(0, first_tile);
+  cp_async_commit();
+
+  const int row_base = SPLITW ? 0 : warp * 16;
+  const int key_lo = SPLITW ? warp * 16 : 0;
+  const int r_lo = lane >> 2, r_hi = r_lo + 8;
+  float m_lo = -CUDART_INF_F, m_hi = -CUDART_INF_F, l_lo = 0.f, l_hi = 0.f;
+  float o[NT_O][4];
+#pragma unroll
+  for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  for (int it = 0; it < n_tiles; ++it) {
+    const int stage = it & 1;
+    const int base = first_tile + it * KT;
+    if (it + 1 < n_tiles) load_tile(stage ^ 1, base + KT);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+
+    const bf16* tK = sK + stage * KT * STRIDE;
+    const bf16* tV = sV + stage * KT * STRIDE;
+    const int pos_lo = s_pos[row_base + r_lo], pos_hi = s_pos[row_base + r_hi];
+
+    // S = Q K^T for this warp's rows and keys
+    float s[NT_S][4];
+#pragma unroll
+    for (int i = 0; i < NT_S; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KS_Q; ++ks) {
+      unsigned a[4];
+      ldmatrix_x4(a[0], a[1], a[2], a[3],
+                  sQ + (row_base + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int np = 0; np < NT_S / 2; ++np) {
+        unsigned b0, b1, b2, b3;
+        ldmatrix_x4(b0, b1, b2, b3,
+                    tK + (key_lo + np * 16 + (lane & 7) + (lane >> 4) * 8) * STRIDE + ks * 16 + ((lane >> 3) & 1) * 8);
+        mma_bf16(s[2 * np], a, b0, b1);
+        mma_bf16(s[2 * np + 1], a, b2, b3);
+      }
+    }
+
+    // mask, scale, online softmax
+    float mx_lo = -CUDART_INF_F, mx_hi = -CUDART_INF_F;
+#pragma unroll
+    for (int nt = 0; nt < NT_S; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = base + key_lo + nt * 8 + (lane & 3) * 2 + (e & 1);
+        const int pos = (e < 2) ? pos_lo : pos_hi;
+        const int lo = window > 0 ? max(pos - window + 1, k_begin) : k_begin;
+        const bool ok = pos >= 0 && key <= pos && key >= lo && key < k_end;
+        const float v = ok ? s[nt][e] * scale_log2 : -CUDART_INF_F;
+        s[nt][e] = v;
+        if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
+      }
+    }
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+    const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+    const float mu_lo = (mn_lo == -CUDART_INF_F) ? 0.f : mn_lo;
+    const float mu_hi = (mn_hi == -CUDART_INF_F) ? 0.f : mn_hi;
+    const float al_lo = exp2f(m_lo - mu_lo), al_hi = exp2f(m_hi - mu_hi);
+    m_lo = mn_lo;
+    m_hi = mn_hi;
+    float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < NT_S; ++nt) {
+      s[nt][0] = exp2f(s[nt][0] - mu_lo);
+      s[nt][1] = exp2f(s[nt][1] - mu_lo);
+      s[nt][2] = exp2f(s[nt][2] - mu_hi);
+      s[nt][3] = exp2f(s[nt][3] - mu_hi);
+      sum_lo += s[nt][0] + s[nt][1];
+      sum_hi += s[nt][2] + s[nt][3];
+    }
+    l_lo = l_lo * al_lo + sum_lo;
+    l_hi = l_hi * al_hi + sum_hi;
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) {
+      o[i][0] *= al_lo;
+      o[i][1] *= al_lo;
+      o[i][2] *= al_hi;
+      o[i][3] *= al_hi;
+    }
+
+    // O += P V
+#pragma unroll
+    for (int kk = 0; kk < WKEYS / 16; ++kk) {
+      unsigned a[4];
+      a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+      a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+      a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int np = 0; np < NT_O / 2; ++np) {
+        unsigned b0, b1, b2, b3;
+        ldmatrix_x4_trans(b0, b1, b2, b3,
+                          tV + (key_lo + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + np * 16 + (lane >> 4) * 8);
+        mma_bf16(o[2 * np], a, b0, b1);
+        mma_bf16(o[2 * np + 1], a, b2, b3);
+      }
+    }
+    __syncthreads();  // the other stage may be overwritten by the next iteration's loads
+  }
+  cp_async_wait<0>();
+
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  constexpr float kLn2 = 0.6931471805599453f;
+
+  if constexpr (!SPLITW) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = row_base + (half ? r_hi : r_lo);
+      if (r >= n_rows) continue;
+      const float m = half ? m_hi : m_lo, l = half ? l_hi : l_lo;
+      const int t = tok0 + r / G, hq = hk * G + r % G;
+      if (n_splits == 1) {
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        bf16* dst = out + (static_cast<size_t>(t) * Hq + hq) * DH;
+#pragma unroll
+        for (int nt = 0; nt < NT_O; ++nt) {
+          const int d = nt * 8 + (lane & 3) * 2;
+          *reinterpret_cast<__nv_bfloat162*>(dst + d) =
+              __floats2bfloat162_rn(o[nt][half * 2] * inv, o[nt][half * 2 + 1] * inv);
+        }
+      } else {
+        const size_t pi = (static_cast<size_t>(t) * Hq + hq) * n_splits + z;
+        float* dst = part_o + pi * DH;
+#pragma unroll
+        for (int nt = 0; nt < NT_O; ++nt) {
+          const int d = nt * 8 + (lane & 3) * 2;
+          dst[d] = o[nt][half * 2];
+          dst[d + 1] = o[nt][half * 2 + 1];
+        }
+        if ((lane & 3) == 0) {
+          part_ml[pi * 2] = m * kLn2;
+          part_ml[pi * 2 + 1] = l;
+        }
+      }
+    }
+  } else {
+    // merge the four warps (each saw a quarter of the keys) through shared memory
+    float* sO = reinterpret_cast<float*>(sK);  // [16][DH], K/V tiles are no longer needed
+    if ((lane & 3) == 0) {
+      s_wm[warp][r_lo] = m_lo;
+      s_wm[warp][r_hi] = m_hi;
+      s_wl[warp][r_lo] = l_lo;
+      s_wl[warp][r_hi] = l_hi;
+    }
+    for (int i = tid; i < 16 * DH; i += 128) sO[i] = 0.f;
+    __syncthreads();
+    if (tid < 16) {
+      float mm = -CUDART_INF_F;
+      for (int w = 0; w < 4; ++w) mm = fmaxf(mm, s_wm[w][tid]);
+      const float mu = (mm == -CUDART_INF_F) ? 0.f : mm;
+      float ll = 0.f;
+      for (int w = 0; w < 4; ++w) ll += s_wl[w][tid] * exp2f(s_wm[w][tid] - mu);
+      s_M[tid] = mm;
+      s_L[tid] = ll;
+    }
+    __syncthreads();
+    {
+      const float mu_lo = (s_M[r_lo] == -CUDART_INF_F) ? 0.f : s_M[r_lo];
+      const float mu_hi = (s_M[r_hi] == -CUDART_INF_F) ? 0.f : s_M[r_hi];
+      const float f_lo = exp2f(m_lo - mu_lo), f_hi = exp2f(m_hi - mu_hi);
+#pragma unroll
+      for (int nt = 0; nt < NT_O; ++nt) {
+        const int d = nt * 8 + (lane & 3) * 2;
+        atomicAdd(sO + r_lo * DH + d, o[nt][0] * f_lo);
+        atomicAdd(sO + r_lo * DH + d + 1, o[nt][1] * f_lo);
+        atomicAdd(sO + r_hi * DH + d, o[nt][2] * f_hi);
+        atomicAdd(sO + r_hi * DH + d + 1, o[nt][3] * f_hi);
+      }
+    }
+    __syncthreads();
+    for (int i = tid; i < n_rows * DH; i += 128) {
+      const int r = i / DH, d = i % DH;
+      const int t = tok0 + r / G, hq = hk * G + r % G;
+      if (n_splits == 1) {
+        const float l = s_L[r];
+        out[(static_cast<size_t>(t) * Hq + hq) * DH + d] = __float2bfloat16_rn(l > 0.f ? sO[i] / l : 0.f);
+      } else {
+        const size_t pi = (static_cast<size_t>(t) * Hq + hq) * n_splits + z;
+        part_o[pi * DH + d] = sO[i];
+        if (d == 0) {
+          part_ml[pi * 2] = s_M[r] * kLn2;
+          part_ml[pi * 2 + 1] = s_L[r];
+        }
+      }
+    }
+  }
+}
+
+// One block per (token, query head): merges the partial results of the key splits.
+// weights w_z = sum_z>0 ? exp(m_z - max m) : 0 are formed first, then every output element
+// is a dot product over the splits with independent loads.
+template <typename S>
+__global__ void __launch_bounds__(128)
+    flash_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                         S* __restrict__ out, int n_splits, int Dh) {
+  extern __shared__ float w[];  // n_splits weights
+  __shared__ float red[32];
+  const size_t row = blockIdx.x;
+  const float* ml = part_ml + row * n_splits * 2;
+  float mx = -CUDART_INF_F;
+  for (int z = threadIdx.x; z < n_splits; z += blockDim.x)
+    if (ml[2 * z + 1] > 0.f) mx = fmaxf(mx, ml[2 * z]);
+  mx = warp_max(mx);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  mx = red[0];
+  for (int i = 1; i < static_cast<int>(blockDim.x >> 5); ++i) mx = fmaxf(mx, red[i]);
+  float part = 0.f;
+  for (int z = threadIdx.x; z < n_splits; z += blockDim.x) {
+    const float l = ml[2 * z + 1];
+    const float wz = l > 0.f ? expf(ml[2 * z] - mx) : 0.f;
+    w[z] = wz;
+    part += wz * l;
+  }
+  const float total = block_sum(part, red);  // syncs: w[] is complete afterwards
+  const float inv = total > 0.f ? 1.f / total : 0.f;
+  const float* po = part_o + row * n_splits * Dh;
+  for (int d = threadIdx.x; d < Dh; d += blockDim.x) {
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    int z = 0;
+    for (; z + 4 <= n_splits; z += 4) {
+      a0 += w[z] * po[static_cast<size_t>(z) * Dh + d];
+      a1 += w[z + 1] * po[static_cast<size_t>(z + 1) * Dh + d];
+      a2 += w[z + 2] * po[static_cast<size_t>(z + 2) * Dh + d];
+      a3 += w[z + 3] * po[static_cast<size_t>(z + 3) * Dh + d];
+    }
+    for (; z < n_splits; ++z) a0 += w[z] * po[static_cast<size_t>(z) * Dh + d];
+    stf(out + row * Dh + d, ((a0 + a1) + (a2 + a3)) * inv);
+  }
+}
+
+template <int DH, bool SPLITW>
+int launch_flash(const void* q, const void* pool, const int* block_table, int max_blocks,
+                 const int* positions, const int* cu, void* out, float* part_o, float* part_ml,
+                 float scale, int window, int split_len, int n_splits, int page_size, int n_seq,
+                 int n_tiles, int Hq, int Hkv, cudaStream_t stream) {
+  constexpr int M = SPLITW ? 16 : 64;
+  const size_t smem = static_cast<size_t>(M + 4 * kFlashKeys) * (DH + 8) * sizeof(bf16);
+  auto kern = flash_paged_kernel<DH, SPLITW>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  dim3 grid(n_tiles, Hkv, n_splits);
+  kern<<<grid, 128, smem, stream>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(pool),
+                                    block_table, max_blocks, positions, cu, static_cast<bf16*>(out),
+                                    part_o, part_ml, scale * 1.4426950408889634f, window, split_len,
+                                    n_splits, page_size, n_seq, Hq, Hkv);
+  return launch_status();
+}
+
+}  // namespace pmm
+
+// Whether the tensor-core kernel takes this shape (bfloat16 only; the caller checks the type).
+PMM_EXPORT int pmm_flash_supported(int Hq, int Hkv, int Dh) {
+  if (Hkv <= 0 || Hq % Hkv) return 0;
+  const int G = Hq / Hkv;
+  return (Dh == 16 || Dh == 32 || Dh == 64 || Dh == 128) && G <= 64 ? 1 : 0;
+}
+
+// n_tiles: number of row tiles = sum over sequences of ceil(new tokens / (M / G)), with
+// M = 16 when rows16 != 0 (every sequence brings at most 16/G tokens) else 64.
+PMM_EXPORT int pmm_flash_paged_attention(const void* q, const void* pool, const int* block_table,
+                                         int max_blocks, const int* positions, const int* cu,
+                                         void* out, float* part_o, float* part_ml, float scale,
+                                         int window, int split_len, int n_splits, int page_size,
+                                         int n_seq, int n_tiles, int rows16, int Hq, int Hkv, int Dh,
+                                         cudaStream_t stream) {
+  if (n_seq <= 0 || n_tiles <= 0) return 0;
+  if (!pmm_flash_supported(Hq, Hkv, Dh) || page_size <= 0 || n_splits < 1 || n_splits > 65535 ||
+      Hkv > 65535)
+    return PMM_ERR_BAD_ARGUMENT;
+  if (rows16 && Hq / Hkv > 16) return PMM_ERR_BAD_ARGUMENT;
+  if (n_splits > 1 && (!part_o || !part_ml || split_len <= 0)) return PMM_ERR_BAD_ARGUMENT;
+  if (n_splits == 1) split_len = 0x40000000;
+  int rc;
+#define PMM_FLASH_CASE(DH)                                                                          \
+  rc = rows16 ? pmm::launch_flash<DH, true>(q, pool, block_table, max_blocks, positions, cu, out,   \
+                                            part_o, part_ml, scale, window, split_len, n_splits,    \
+                                            page_size, n_seq, n_tiles, Hq, Hkv, stream)             \
+              : pmm::launch_flash<DH, false>(q, pool, block_table, max_blocks, positions, cu, out,  \
+                                             part_o, part_ml, scale, window, split_len, n_splits,   \
+                                             page_size, n_seq, n_tiles, Hq, Hkv, stream)
+  switch (Dh) {
+    case 16: PMM_FLASH_CASE(16); break;
+    case 32: PMM_FLASH_CASE(32); break;
+    case 64: PMM_FLASH_CASE(64); break;
+    case 128: PMM_FLASH_CASE(128); break;
+    default: return PMM_ERR_BAD_ARGUMENT;
+  }
+#undef PMM_FLASH_CASE
+  return rc;
+}
+
+// Merge of key splits: part_o [rows, n_splits, Dh], part_ml [rows, n_splits, 2] -> out [rows, Dh].
+PMM_EXPORT int pmm_flash_combine(const float* part_o, const float* part_ml, void* out, int n_rows,
+                                 int n_splits, int Dh, int dtype, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (n_splits < 1 || Dh <= 0) return PMM_ERR_BAD_ARGUMENT;
+  const size_t smem = static_cast<size_t>(n_splits) * sizeof(float);
+  if (smem > 48 * 1024) return PMM_ERR_BAD_ARGUMENT;
+  PMM_DISPATCH_DTYPE(dtype, S, pmm::flash_combine_kernel<S><<<n_rows, 128, smem, stream>>>(
+                                   part_o, part_ml, static_cast<S*>(out), n_splits, Dh));
+  return pmm::launch_status();
+}

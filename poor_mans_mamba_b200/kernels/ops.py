@@ -51,6 +51,11 @@ _SIGNATURES = {
     "pmm_paged_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                             c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
                             c_int, c_int, c_int, c_void_p],
+    "pmm_flash_supported": [c_int, c_int, c_int],
+    "pmm_flash_paged_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
+                                  c_int, c_int, c_int, c_int, c_void_p],
+    "pmm_flash_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_silu_mul": [c_void_p, c_longlong, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
     "pmm_add_row_bias": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "pmm_sample_rows": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
@@ -397,12 +402,20 @@ def attention_scratch_floats(T: int, n_q_heads: int, head_dim: int, n_splits: in
     return T * n_q_heads * n_splits * (head_dim + 2) if n_splits > 1 else 0
 
 
+def flash_supported(n_q_heads: int, n_kv_heads: int, head_dim: int) -> bool:
+    """Whether the tensor-core attention kernel takes this shape (bfloat16 caches only)."""
+    return bool(_fn("pmm_flash_supported")(n_q_heads, n_kv_heads, head_dim))
+
+
 def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Tensor, seq_of: Tensor,
                     out: Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int, softmax_scale: float,
                     window: int = 0, n_splits: int = 1, split_len: int = 0,
-                    scratch: Optional[Tensor] = None) -> None:
-    """Causal attention of every token over keys lo..pos of its request in the paged cache."""
-    _cuda(q, pool, block_table, positions, seq_of, out, scratch)
+                    scratch: Optional[Tensor] = None, cu_seqlens: Optional[Tensor] = None,
+                    new_lens: Optional[Sequence[int]] = None, use_tensor_cores: bool = True) -> None:
+    """Causal attention of every token over keys lo..pos of its request in the paged cache.
+    With ``cu_seqlens`` and ``new_lens`` (tokens per sequence, host values) a bfloat16 cache of a
+    supported shape goes to the tensor-core kernel; everything else to the float kernel."""
+    _cuda(q, pool, block_table, positions, seq_of, out, scratch, cu_seqlens)
     check_head_dim(head_dim)
     T = q.shape[0]
     _need(q.is_contiguous() and out.is_contiguous() and q.shape == (T, n_q_heads * head_dim)
@@ -422,10 +435,26 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
         _need(split_len > 0 and split_len % 32 == 0, "attention: split_len must be a positive multiple of 32")
         part_o = scratch.data_ptr()
         part_ml = part_o + 4 * T * n_q_heads * n_splits * head_dim
-    _call("pmm_paged_attention", q.data_ptr(), pool.data_ptr(), block_table.data_ptr(),
-          block_table.shape[1], positions.data_ptr(), seq_of.data_ptr(), out.data_ptr(), part_o, part_ml,
-          float(softmax_scale), int(window), int(split_len), int(n_splits), pool.shape[2], T, n_q_heads,
-          n_kv_heads, head_dim, _dt(q), _stream())
+    flash = (use_tensor_cores and q.dtype == torch.bfloat16 and cu_seqlens is not None and new_lens is not None
+             and flash_supported(n_q_heads, n_kv_heads, head_dim))
+    if flash:
+        _i32(cu_seqlens, "attention: cu_seqlens")
+        group = n_q_heads // n_kv_heads
+        rows16 = group <= 16 and max(new_lens) * group <= 16
+        tokens_per_tile = (16 if rows16 else 64) // group
+        n_tiles = sum((n + tokens_per_tile - 1) // tokens_per_tile for n in new_lens)
+        _call("pmm_flash_paged_attention", q.data_ptr(), pool.data_ptr(), block_table.data_ptr(),
+              block_table.shape[1], positions.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(), part_o,
+              part_ml, float(softmax_scale), int(window), int(split_len), int(n_splits), pool.shape[2],
+              len(new_lens), n_tiles, int(rows16), n_q_heads, n_kv_heads, head_dim, _stream())
+    else:
+        _call("pmm_paged_attention", q.data_ptr(), pool.data_ptr(), block_table.data_ptr(),
+              block_table.shape[1], positions.data_ptr(), seq_of.data_ptr(), out.data_ptr(), part_o, part_ml,
+              float(softmax_scale), int(window), int(split_len), int(n_splits), pool.shape[2], T, n_q_heads,
+              n_kv_heads, head_dim, _dt(q), _stream())
+    if n_splits > 1:
+        _call("pmm_flash_combine", part_o, part_ml, out.data_ptr(), T * n_q_heads, int(n_splits), head_dim,
+              _dt(out), _stream())
 
 
 def silu_mul(gate_up: Tensor, gate_mult: float, out: Tensor) -> None:

@@ -21,7 +21,6 @@ Tensor = torch.Tensor
 
 # Key splits are sized so that a step launches about this many attention blocks.
 _TARGET_BLOCKS = 592
-_MIN_SPLIT_LEN = 128
 
 
 class PagedAttention(Mixer):
@@ -122,7 +121,7 @@ class PagedAttention(Mixer):
                          k_lin.view(T, self.num_kv_heads, self.head_dim), ctx.positions)
                 K.kv_store(k_lin, v_lin, ctx.positions, ctx.seq_of, kv.block_table, kv.pool)
 
-        n_splits, split_len = self.plan_splits(T, ctx.kv_len_bound)
+        n_splits, split_len = self.plan_splits(ctx.new_lens, ctx.kv_len_bound, proj.dtype)
         scratch = None
         if n_splits > 1:
             scratch = ws.alloc((K.attention_scratch_floats(T, self.num_heads, self.head_dim, n_splits),),
@@ -130,20 +129,29 @@ class PagedAttention(Mixer):
         attn = ws.alloc((T, self.q_dim), proj.dtype)
         K.paged_attention(q_rot, kv.pool, kv.block_table, ctx.positions, ctx.seq_of, attn, self.num_heads,
                           self.num_kv_heads, self.head_dim, 1.0 / math.sqrt(float(self.head_dim)),
-                          window=self.window, n_splits=n_splits, split_len=split_len, scratch=scratch)
+                          window=self.window, n_splits=n_splits, split_len=split_len, scratch=scratch,
+                          cu_seqlens=ctx.cu_seqlens, new_lens=ctx.new_lens)
         K.linear(attn, self.w_out, out)
 
-    def plan_splits(self, n_tokens: int, kv_len_bound: int):
-        """How many key ranges each (token, head) is cut into: enough blocks to fill the GPU
+    def plan_splits(self, new_lens, kv_len_bound: int, dtype: torch.dtype):
+        """How many key ranges every block's keys are cut into: enough blocks to fill the GPU
         when few tokens are in flight, one when the tokens alone do."""
-        blocks = n_tokens * ((self.num_heads + 3) // 4)
+        group = self.num_heads // self.num_kv_heads
+        if dtype == torch.bfloat16 and K.flash_supported(self.num_heads, self.num_kv_heads, self.head_dim):
+            rows = 16 if (group <= 16 and max(new_lens) * group <= 16) else 64
+            per_tile = rows // group
+            blocks = sum((n + per_tile - 1) // per_tile for n in new_lens) * self.num_kv_heads
+            min_len = 64
+        else:
+            blocks = sum(new_lens) * ((self.num_heads + 3) // 4)
+            min_len = 128
         reach = min(kv_len_bound, self.window) if self.window > 0 else kv_len_bound
-        if blocks >= _TARGET_BLOCKS or reach <= _MIN_SPLIT_LEN:
+        if blocks >= _TARGET_BLOCKS or reach <= min_len:
             return 1, 0
-        want = min((_TARGET_BLOCKS + blocks - 1) // blocks, (reach + _MIN_SPLIT_LEN - 1) // _MIN_SPLIT_LEN)
+        want = min((_TARGET_BLOCKS + blocks - 1) // blocks, (reach + min_len - 1) // min_len)
         if want <= 1:
             return 1, 0
-        split_len = ((kv_len_bound + want - 1) // want + 31) // 32 * 32
+        split_len = ((kv_len_bound + want - 1) // want + 63) // 64 * 64
         n_splits = (kv_len_bound + split_len - 1) // split_len
         return (n_splits, split_len) if n_splits > 1 else (1, 0)
 

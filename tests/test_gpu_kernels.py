@@ -179,7 +179,8 @@ def test_gated_norm(dtype, mode):
     close(out, ref, dtype, what=mode)
 
 
-def _attention_case(dtype, Hq, Hkv, Dh, page_size, lens_steps, window=0, planted=True, n_splits=1, theta=1e4, seed=0):
+def _attention_case(dtype, Hq, Hkv, Dh, page_size, lens_steps, window=0, planted=True, n_splits=1, theta=1e4, seed=0,
+                    tensor_cores=True):
     """Runs qkv_rope_store + paged_attention over a script of portions with scattered pages and
     compares with the plain rope + causal attention on the whole sequences."""
     g = torch.Generator().manual_seed(seed)
@@ -256,8 +257,12 @@ def _attention_case(dtype, Hq, Hkv, Dh, page_size, lens_steps, window=0, planted
             scratch = torch.full((ops.attention_scratch_floats(T, Hq, Dh, ns),), float("nan"), device=DEV)
         else:
             ns = 1
+        cu = [0]
+        for _, _, n in seqs:
+            cu.append(cu[-1] + n)
         ops.paged_attention(q_rot, pool, bt.to(DEV), i32(pos), i32(seq_of), out, Hq, Hkv, Dh, 1.0 / math.sqrt(Dh),
-                            window=window, n_splits=ns, split_len=split_len, scratch=scratch)
+                            window=window, n_splits=ns, split_len=split_len, scratch=scratch, cu_seqlens=i32(cu),
+                            new_lens=[n for _, _, n in seqs], use_tensor_cores=tensor_cores)
         t0 = 0
         for i, a, n in seqs:
             got[i][a:a + n] = out[t0:t0 + n].cpu()
@@ -267,24 +272,32 @@ def _attention_case(dtype, Hq, Hkv, Dh, page_size, lens_steps, window=0, planted
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("Hq,Hkv,Dh,page", [(6, 3, 48, 16), (8, 2, 64, 64), (5, 1, 128, 32), (2, 2, 16, 16), (9, 3, 256, 16)])
-def test_paged_attention_prefill_and_decode(dtype, Hq, Hkv, Dh, page):
-    steps = [[page + 1, 1, 1, page - 2, 1], [3, 2 * page, 1, 1], [1, 1, 1, 1, 1]]
-    _attention_case(dtype, Hq, Hkv, Dh, page, steps, seed=Hq)
+@pytest.mark.parametrize("tensor_cores", [True, False])
+@pytest.mark.parametrize("Hq,Hkv,Dh,page", [(6, 3, 48, 16), (8, 2, 64, 64), (5, 1, 128, 32), (2, 2, 16, 16), (9, 3, 256, 16),
+                                            (6, 2, 64, 16), (12, 2, 128, 64), (40, 2, 32, 32)])
+def test_paged_attention_prefill_and_decode(dtype, tensor_cores, Hq, Hkv, Dh, page):
+    """Head groups of 1..20 (also 3 and 6, which do not divide a row tile), head sizes on and off
+    the tensor-core kernel's list, portions around page edges, single tokens."""
+    steps = [[page + 1, 1, 1, page - 2, 1], [3, 2 * page, 1, 1], [1, 1, 1, 1, 1], [70, 1, 90]]
+    _attention_case(dtype, Hq, Hkv, Dh, page, steps, seed=Hq, tensor_cores=tensor_cores)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_paged_attention_split_keys(dtype):
+@pytest.mark.parametrize("tensor_cores", [True, False])
+def test_paged_attention_split_keys(dtype, tensor_cores):
     steps = [[300, 1, 1], [17, 1, 1], [129, 1, 1]]
-    _attention_case(dtype, 8, 2, 64, 16, steps, n_splits=4, seed=5)
-    _attention_case(dtype, 3, 1, 80, 32, steps, n_splits=7, seed=6)
+    _attention_case(dtype, 8, 2, 64, 16, steps, n_splits=4, seed=5, tensor_cores=tensor_cores)
+    _attention_case(dtype, 3, 1, 80, 32, steps, n_splits=7, seed=6, tensor_cores=tensor_cores)
+    _attention_case(dtype, 6, 2, 128, 64, steps, n_splits=5, seed=7, tensor_cores=tensor_cores)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_paged_attention_window(dtype):
+@pytest.mark.parametrize("tensor_cores", [True, False])
+def test_paged_attention_window(dtype, tensor_cores):
     steps = [[40, 1, 1, 30], [5, 1, 60]]
-    _attention_case(dtype, 4, 2, 32, 16, steps, window=24, seed=9)
-    _attention_case(dtype, 4, 2, 32, 16, steps, window=24, n_splits=3, seed=9)
+    _attention_case(dtype, 4, 2, 32, 16, steps, window=24, seed=9, tensor_cores=tensor_cores)
+    _attention_case(dtype, 4, 2, 32, 16, steps, window=24, n_splits=3, seed=9, tensor_cores=tensor_cores)
+    _attention_case(dtype, 8, 2, 64, 64, [[200, 1, 1, 1]], window=70, n_splits=2, seed=10, tensor_cores=tensor_cores)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

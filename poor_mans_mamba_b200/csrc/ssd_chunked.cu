@@ -1,0 +1,408 @@
+// Chunked Mamba2 SSD scan for prompt portions (bfloat16 activations, float state), on
+// tensor cores.  The recurrence
+//   s_t = s_{t-1} * exp(a_t) + delta_t * B_t x_t^T ,   y_t = C_t . s_t + D x_t ,  a_t = delta_t * A
+// is evaluated per chunk of 64 tokens of one sequence portion and one head.  With
+// cs_i = a_0 + ... + a_i inside the chunk and S the state at the chunk's start:
+//   y_i   = sum_{j<=i} (C_i.B_j) exp(cs_i-cs_j) delta_j x_j  +  exp(cs_i) (C_i . S)  +  D x_i
+//   S_end = exp(cs_last) S  +  sum_j exp(cs_last-cs_j) delta_j B_j x_j^T
+// Three launches, all parallel over chunks except the cheap middle one:
+//   1. ssd_chunk_state:  local term of S_end and exp(cs_last) per (chunk, head)   -> scratch
+//   2. ssd_state_pass:   walks a sequence's chunks: scratch[c] <- state at the start of
+//                        chunk c (the request's saved state for c = 0), final state -> slot
+//   3. ssd_chunk_output: y for every token from C, B, x and the chunk's start state
+// All differences of cs are <= 0, so no exponential overflows; delta, cs and every
+// accumulator are float; the start state is rounded to bfloat16 only as an MMA operand.
+// Chunks are aligned to the start of the portion in this step; a portion that is cut
+// elsewhere gives the same result up to rounding.  Rows beyond a short chunk are zero-filled
+// (delta = 0), so they change nothing.
+// (reference src/ops/gpu/mamba2_scan.cu:11-50 walks the tokens serially; the formulas above
+// are that recurrence unrolled over a chunk.)
+#include "common.cuh"
+
+namespace pmm {
+
+using bf16 = __nv_bfloat16;
+constexpr int kQ = 64;  // tokens per chunk
+
+__device__ __forceinline__ void ssd_cp_async16(void* smem, const void* gmem, bool pred) {
+  const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+  const int sz = pred ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(sz));
+}
+__device__ __forceinline__ void ssd_cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::);
+}
+__device__ __forceinline__ void ssd_ldm(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void ssd_ldm_t(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void ssd_mma(float* d, const unsigned* a, unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned ssd_pack(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const unsigned*>(&v);
+}
+__device__ __forceinline__ unsigned ssd_scale2(unsigned packed, float s0, float s1) {
+  const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&packed));
+  return ssd_pack(f.x * s0, f.y * s1);
+}
+
+// Which (sequence, first token, length) chunk `c` is; chunk ids run over the sequences in order.
+__device__ __forceinline__ bool ssd_locate(const int* __restrict__ cu, int n_seq, int c, int& seq,
+                                           int& t0, int& len, int& first_chunk) {
+  int acc = 0;
+  for (seq = 0; seq < n_seq; ++seq) {
+    const int n = cu[seq + 1] - cu[seq];
+    const int nc = (n + kQ - 1) / kQ;
+    if (c < acc + nc) {
+      t0 = cu[seq] + (c - acc) * kQ;
+      len = min(kQ, cu[seq + 1] - t0);
+      first_chunk = acc;
+      return true;
+    }
+    acc += nc;
+  }
+  return false;
+}
+
+// delta_j, cs_j (inclusive cumulative sum of delta_j * A) for the chunk's tokens; rows >= len: 0.
+// Called by all threads; the first warp does the scan.  Ends with a __syncthreads().
+__device__ __forceinline__ void ssd_delta_cumsum(const bf16* __restrict__ dt_raw, long long ld_dt,
+                                                 float dt_scale, float shift, float A, int t0, int len,
+                                                 int h, float* s_delta, float* s_cs) {
+  const int tid = threadIdx.x;
+  if (tid < 32) {
+    float d0 = 0.f, d1 = 0.f;
+    const int j0 = 2 * tid, j1 = 2 * tid + 1;
+    if (j0 < len) d0 = softplus_f(__bfloat162float(dt_raw[static_cast<long long>(t0 + j0) * ld_dt + h]) * dt_scale + shift);
+    if (j1 < len) d1 = softplus_f(__bfloat162float(dt_raw[static_cast<long long>(t0 + j1) * ld_dt + h]) * dt_scale + shift);
+    const float a0 = d0 * A, a1 = d1 * A;
+    const float pair = a0 + a1;
+    float incl = pair;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (tid >= o) incl += up;
+    }
+    const float excl = incl - pair;
+    s_delta[j0] = d0;
+    s_delta[j1] = d1;
+    s_cs[j0] = excl + a0;
+    s_cs[j1] = excl + pair;
+  }
+  __syncthreads();
+}
+
+// ----------------------------------------------------------------------------- phase 1
+template <int P, int N>
+__global__ void __launch_bounds__(128)
+    ssd_chunk_state_kernel(const bf16* __restrict__ xbc, int ld_xbc, const bf16* __restrict__ dt_raw,
+                           long long ld_dt, float dt_scale, const float* __restrict__ dt_shift,
+                           const float* __restrict__ a_log, const int* __restrict__ cu, int n_seq,
+                           float* __restrict__ chunk_state, float* __restrict__ chunk_decay, int H, int G) {
+  constexpr int SX = P + 8, SB = N + 8;
+  constexpr int NB = N < 64 ? N : 64;  // columns of the state per work unit
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* sX = reinterpret_cast<bf16*>(smem_raw);
+  bf16* sB = sX + kQ * SX;
+  __shared__ float s_delta[kQ], s_cs[kQ], s_w[kQ];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.x, h = blockIdx.y;
+  int seq, t0, len, first;
+  if (!ssd_locate(cu, n_seq, c, seq, t0, len, first)) return;
+  const int I = H * P, g = h / (H / G);
+
+  for (int i = tid; i < kQ * (P / 8); i += 128) {
+    const int r = i / (P / 8), col = i % (P / 8);
+    const bool ok = r < len;
+    ssd_cp_async16(sX + r * SX + col * 8, xbc + (ok ? static_cast<size_t>(t0 + r) * ld_xbc + h * P + col * 8 : 0), ok);
+  }
+  for (int i = tid; i < kQ * (N / 8); i += 128) {
+    const int r = i / (N / 8), col = i % (N / 8);
+    const bool ok = r < len;
+    ssd_cp_async16(sB + r * SB + col * 8, xbc + (ok ? static_cast<size_t>(t0 + r) * ld_xbc + I + g * N + col * 8 : 0), ok);
+  }
+  ssd_delta_cumsum(dt_raw, ld_dt, dt_scale, dt_shift[h], -expf(a_log[h]), t0, len, h, s_delta, s_cs);
+  if (tid < kQ) s_w[tid] = expf(s_cs[kQ - 1] - s_cs[tid]) * s_delta[tid];
+  if (tid == 0) chunk_decay[static_cast<size_t>(c) * H + h] = expf(s_cs[kQ - 1]);
+  ssd_cp_async_wait_all();
+  __syncthreads();
+
+  float* dst = chunk_state + (static_cast<size_t>(c) * H + h) * P * N;
+  constexpr int UNITS = (P / 16) * (N / NB);
+  for (int u = warp; u < UNITS; u += 4) {
+    const int mt = u / (N / NB), nb = u % (N / NB);
+    float acc[NB / 8][4];
+#pragma unroll
+    for (int i = 0; i < NB / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < kQ / 16; ++ks) {
+      unsigned a[4];
+      // A[m = p][k = token] from sX[token][p]: transposed 8x8 loads
+      ssd_ldm_t(a[0], a[1], a[2], a[3], sX + (ks * 16 + (lane >> 4) * 8 + (lane & 7)) * SX + mt * 16 + ((lane >> 3) & 1) * 8);
+      const int k0 = ks * 16 + (lane & 3) * 2;
+      const float w0 = s_w[k0], w1 = s_w[k0 + 1], w8 = s_w[k0 + 8], w9 = s_w[k0 + 9];
+      a[0] = ssd_scale2(a[0], w0, w1);
+      a[1] = ssd_scale2(a[1], w0, w1);
+      a[2] = ssd_scale2(a[2], w8, w9);
+      a[3] = ssd_scale2(a[3], w8, w9);
+#pragma unroll
+      for (int np = 0; np < NB / 16; ++np) {
+        unsigned b0, b1, b2, b3;
+        ssd_ldm_t(b0, b1, b2, b3, sB + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SB + nb * NB + np * 16 + (lane >> 4) * 8);
+        ssd_mma(acc[2 * np], a, b0, b1);
+        ssd_mma(acc[2 * np + 1], a, b2, b3);
+      }
+    }
+    const int p_lo = mt * 16 + (lane >> 2);
+#pragma unroll
+    for (int nt = 0; nt < NB / 8; ++nt) {
+      const int n = nb * NB + nt * 8 + (lane & 3) * 2;
+      *reinterpret_cast<float2*>(dst + static_cast<size_t>(p_lo) * N + n) = make_float2(acc[nt][0], acc[nt][1]);
+      *reinterpret_cast<float2*>(dst + static_cast<size_t>(p_lo + 8) * N + n) = make_float2(acc[nt][2], acc[nt][3]);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- phase 2
+__global__ void ssd_state_pass_kernel(float* __restrict__ chunk_state, const float* __restrict__ chunk_decay,
+                                      float* __restrict__ state, const int* __restrict__ cu,
+                                      const int* __restrict__ slots, int H, int PN) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  const int h = blockIdx.y, seq = blockIdx.z;
+  if (e >= PN) return;
+  int first = 0;
+  for (int s = 0; s < seq; ++s) first += (cu[s + 1] - cu[s] + kQ - 1) / kQ;
+  const int nc = (cu[seq + 1] - cu[seq] + kQ - 1) / kQ;
+  if (nc <= 0) return;
+  float* sp = state + (static_cast<size_t>(slots[seq]) * H + h) * PN + e;
+  float s = *sp;
+  for (int c = 0; c < nc; ++c) {
+    const size_t ch = static_cast<size_t>(first + c) * H + h;
+    float* lp = chunk_state + ch * PN + e;
+    const float local = *lp;
+    *lp = s;  // the state at the start of chunk c
+    s = s * chunk_decay[ch] + local;
+  }
+  *sp = s;
+}
+
+// ----------------------------------------------------------------------------- phase 3
+template <int P, int N>
+__global__ void __launch_bounds__(128)
+    ssd_chunk_output_kernel(const bf16* __restrict__ xbc, int ld_xbc, const bf16* __restrict__ dt_raw,
+                            long long ld_dt, float dt_scale, const float* __restrict__ dt_shift,
+                            const float* __restrict__ a_log, const float* __restrict__ d_skip,
+                            const int* __restrict__ cu, int n_seq, const float* __restrict__ chunk_state,
+                            bf16* __restrict__ y, int H, int G) {
+  constexpr int SX = P + 8, SN = N + 8;
+  constexpr int PB = P < 64 ? P : 64;  // output columns per pass
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* sC = reinterpret_cast<bf16*>(smem_raw);
+  bf16* sB = sC + kQ * SN;
+  bf16* sS = sB + kQ * SN;   // [P][SN] start state, bfloat16
+  bf16* sX = sS + P * SN;    // [kQ][SX]
+  __shared__ float s_delta[kQ], s_cs[kQ];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.x, h = blockIdx.y;
+  int seq, t0, len, first;
+  if (!ssd_locate(cu, n_seq, c, seq, t0, len, first)) return;
+  const int I = H * P, g = h / (H / G);
+
+  for (int i = tid; i < kQ * (N / 8); i += 128) {
+    const int r = i / (N / 8), col = i % (N / 8);
+    const bool ok = r < len;
+    const size_t row = ok ? static_cast<size_t>(t0 + r) * ld_xbc : 0;
+    ssd_cp_async16(sB + r * SN + col * 8, xbc + row + (ok ? I + g * N + col * 8 : 0), ok);
+    ssd_cp_async16(sC + r * SN + col * 8, xbc + row + (ok ? I + G * N + g * N + col * 8 : 0), ok);
+  }
+  for (int i = tid; i < kQ * (P / 8); i += 128) {
+    const int r = i / (P / 8), col = i % (P / 8);
+    const bool ok = r < len;
+    ssd_cp_async16(sX + r * SX + col * 8, xbc + (ok ? static_cast<size_t>(t0 + r) * ld_xbc + h * P + col * 8 : 0), ok);
+  }
+  {
+    const float* src = chunk_state + (static_cast<size_t>(c) * H + h) * P * N;
+    for (int i = tid; i < P * N / 2; i += 128) {
+      const int p = (2 * i) / N, n = (2 * i) % N;
+      const float2 v = *reinterpret_cast<const float2*>(src + 2 * i);
+      *reinterpret_cast<__nv_bfloat162*>(sS + p * SN + n) = __floats2bfloat162_rn(v.x, v.y);
+    }
+  }
+  ssd_delta_cumsum(dt_raw, ld_dt, dt_scale, dt_shift[h], -expf(a_log[h]), t0, len, h, s_delta, s_cs);
+  ssd_cp_async_wait_all();
+  __syncthreads();
+
+  const int i_lo = warp * 16 + (lane >> 2), i_hi = i_lo + 8;
+  const float cs_lo = s_cs[i_lo], cs_hi = s_cs[i_hi];
+
+  // G = C B^T for this warp's 16 rows and the tokens up to its diagonal block; then the decayed,
+  // masked, delta-weighted matrix M as bfloat16 A-fragments
+  unsigned mfrag[kQ / 16][4];
+  {
+    float gacc[kQ / 8][4];
+#pragma unroll
+    for (int i = 0; i < kQ / 8; ++i) gacc[i][0] = gacc[i][1] = gacc[i][2] = gacc[i][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < N / 16; ++ks) {
+      unsigned a[4];
+      ssd_ldm(a[0], a[1], a[2], a[3], sC + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SN + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int np = 0; np < kQ / 16; ++np) {
+        if (np <= warp) {
+          unsigned b0, b1, b2, b3;
+          ssd_ldm(b0, b1, b2, b3, sB + (np * 16 + (lane & 7) + (lane >> 4) * 8) * SN + ks * 16 + ((lane >> 3) & 1) * 8);
+          ssd_mma(gacc[2 * np], a, b0, b1);
+          ssd_mma(gacc[2 * np + 1], a, b2, b3);
+        }
+      }
+    }
+#pragma unroll
+    for (int kk = 0; kk < kQ / 16; ++kk) {
+      float m[2][4];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int nt = 2 * kk + half;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = nt * 8 + (lane & 3) * 2 + (e & 1);
+          const int i = (e < 2) ? i_lo : i_hi;
+          const float csi = (e < 2) ? cs_lo : cs_hi;
+          m[half][e] = (j <= i) ? gacc[nt][e] * expf(csi - s_cs[j]) * s_delta[j] : 0.f;
+        }
+      }
+      mfrag[kk][0] = ssd_pack(m[0][0], m[0][1]);
+      mfrag[kk][1] = ssd_pack(m[0][2], m[0][3]);
+      mfrag[kk][2] = ssd_pack(m[1][0], m[1][1]);
+      mfrag[kk][3] = ssd_pack(m[1][2], m[1][3]);
+    }
+  }
+
+  const float e_lo = expf(cs_lo), e_hi = expf(cs_hi);
+  const float Dh = d_skip[h];
+#pragma unroll 1
+  for (int pb = 0; pb < P / PB; ++pb) {
+    float y1[PB / 8][4], y2[PB / 8][4];
+#pragma unroll
+    for (int i = 0; i < PB / 8; ++i) {
+      y1[i][0] = y1[i][1] = y1[i][2] = y1[i][3] = 0.f;
+      y2[i][0] = y2[i][1] = y2[i][2] = y2[i][3] = 0.f;
+    }
+    // within the chunk: M (delta x)
+#pragma unroll
+    for (int kk = 0; kk < kQ / 16; ++kk) {
+      if (kk <= warp) {
+#pragma unroll
+        for (int np = 0; np < PB / 16; ++np) {
+          unsigned b0, b1, b2, b3;
+          ssd_ldm_t(b0, b1, b2, b3, sX + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SX + pb * PB + np * 16 + (lane >> 4) * 8);
+          ssd_mma(y1[2 * np], mfrag[kk], b0, b1);
+          ssd_mma(y1[2 * np + 1], mfrag[kk], b2, b3);
+        }
+      }
+    }
+    // from before the chunk: C S^T
+#pragma unroll
+    for (int ks = 0; ks < N / 16; ++ks) {
+      unsigned a[4];
+      ssd_ldm(a[0], a[1], a[2], a[3], sC + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SN + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int np = 0; np < PB / 16; ++np) {
+        unsigned b0, b1, b2, b3;
+        ssd_ldm(b0, b1, b2, b3, sS + (pb * PB + np * 16 + (lane & 7) + (lane >> 4) * 8) * SN + ks * 16 + ((lane >> 3) & 1) * 8);
+        ssd_mma(y2[2 * np], a, b0, b1);
+        ssd_mma(y2[2 * np + 1], a, b2, b3);
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < PB / 8; ++nt) {
+      const int p = pb * PB + nt * 8 + (lane & 3) * 2;
+      if (i_lo < len) {
+        const float2 xv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sX + i_lo * SX + p));
+        *reinterpret_cast<__nv_bfloat162*>(y + static_cast<size_t>(t0 + i_lo) * I + h * P + p) =
+            __floats2bfloat162_rn(y1[nt][0] + e_lo * y2[nt][0] + Dh * xv.x, y1[nt][1] + e_lo * y2[nt][1] + Dh * xv.y);
+      }
+      if (i_hi < len) {
+        const float2 xv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sX + i_hi * SX + p));
+        *reinterpret_cast<__nv_bfloat162*>(y + static_cast<size_t>(t0 + i_hi) * I + h * P + p) =
+            __floats2bfloat162_rn(y1[nt][2] + e_hi * y2[nt][2] + Dh * xv.x, y1[nt][3] + e_hi * y2[nt][3] + Dh * xv.y);
+      }
+    }
+  }
+}
+
+template <int P, int N>
+int launch_ssd(const void* xbc, int ld_xbc, const void* dt_raw, long long ld_dt, float dt_scale,
+               const float* dt_shift, const float* a_log, const float* d_skip, float* state,
+               const int* cu, const int* slots, void* y, float* chunk_state, float* chunk_decay,
+               int n_seq, int n_chunks, int H, int G, cudaStream_t stream) {
+  const size_t smem1 = static_cast<size_t>(kQ) * ((P + 8) + (N + 8)) * sizeof(bf16);
+  const size_t smem3 = (static_cast<size_t>(kQ) * (2 * (N + 8) + (P + 8)) + static_cast<size_t>(P) * (N + 8)) * sizeof(bf16);
+  auto k1 = ssd_chunk_state_kernel<P, N>;
+  auto k3 = ssd_chunk_output_kernel<P, N>;
+  if (smem1 > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem1));
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  if (smem3 > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem3));
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  dim3 grid(n_chunks, H);
+  k1<<<grid, 128, smem1, stream>>>(static_cast<const bf16*>(xbc), ld_xbc, static_cast<const bf16*>(dt_raw), ld_dt,
+                                   dt_scale, dt_shift, a_log, cu, n_seq, chunk_state, chunk_decay, H, G);
+  const int PN = P * N;
+  dim3 grid2((PN + 255) / 256, H, n_seq);
+  ssd_state_pass_kernel<<<grid2, 256, 0, stream>>>(chunk_state, chunk_decay, state, cu, slots, H, PN);
+  k3<<<grid, 128, smem3, stream>>>(static_cast<const bf16*>(xbc), ld_xbc, static_cast<const bf16*>(dt_raw), ld_dt,
+                                   dt_scale, dt_shift, a_log, d_skip, cu, n_seq, chunk_state,
+                                   static_cast<bf16*>(y), H, G);
+  return launch_status();
+}
+
+}  // namespace pmm
+
+// Head size / state size pairs the tensor-core scan is compiled for.
+PMM_EXPORT int pmm_ssd_supported(int P, int N) {
+  return ((P == 16 && N == 16) || (P == 32 && N == 32) || (P == 64 && N == 64) || (P == 64 && N == 128) ||
+          (P == 64 && N == 256) || (P == 128 && N == 128) || (P == 128 && N == 256)) ? 1 : 0;
+}
+
+// chunk_state: n_chunks*H*P*N floats, chunk_decay: n_chunks*H floats of scratch;
+// n_chunks = sum over sequences of ceil(new tokens / 64).  bfloat16 activations only.
+PMM_EXPORT int pmm_ssd_chunked(const void* xbc, int ld_xbc, const void* dt_raw, long long ld_dt,
+                               float dt_scale, const float* dt_shift, const float* a_log,
+                               const float* d_skip, float* state, const int* cu, const int* slots,
+                               void* y, float* chunk_state, float* chunk_decay, int n_seq, int n_chunks,
+                               int H, int P, int N, int G, cudaStream_t stream) {
+  if (n_seq <= 0 || n_chunks <= 0) return 0;
+  if (!pmm_ssd_supported(P, N) || H <= 0 || G <= 0 || H % G || H > 65535 || n_seq > 65535 ||
+      !chunk_state || !chunk_decay)
+    return PMM_ERR_BAD_ARGUMENT;
+#define PMM_SSD_CASE(PP, NN)                                                                             \
+  if (P == PP && N == NN)                                                                                \
+    return pmm::launch_ssd<PP, NN>(xbc, ld_xbc, dt_raw, ld_dt, dt_scale, dt_shift, a_log, d_skip, state, \
+                                   cu, slots, y, chunk_state, chunk_decay, n_seq, n_chunks, H, G, stream)
+  PMM_SSD_CASE(16, 16);
+  PMM_SSD_CASE(32, 32);
+  PMM_SSD_CASE(64, 64);
+  PMM_SSD_CASE(64, 128);
+  PMM_SSD_CASE(64, 256);
+  PMM_SSD_CASE(128, 128);
+  PMM_SSD_CASE(128, 256);
+#undef PMM_SSD_CASE
+  return PMM_ERR_BAD_ARGUMENT;
+}

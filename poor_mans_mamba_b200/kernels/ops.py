@@ -40,6 +40,10 @@ _SIGNATURES = {
     "pmm_ssm_scan_seq": [c_void_p, c_int, c_void_p, c_longlong, c_float, c_void_p, c_void_p,
                          c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                          c_int, c_int, c_void_p],
+    "pmm_ssd_supported": [c_int, c_int],
+    "pmm_ssd_chunked": [c_void_p, c_int, c_void_p, c_longlong, c_float, c_void_p, c_void_p, c_void_p,
+                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                        c_int, c_int, c_int, c_void_p],
     "pmm_gated_norm": [c_void_p, c_void_p, c_longlong, c_float, c_void_p, c_void_p, c_float, c_int,
                        c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_qkv_rope_store": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_float,
@@ -315,6 +319,55 @@ def ssm_scan_seq(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Tensor,
     _call("pmm_ssm_scan_seq", xbc.data_ptr(), ld_x, dt_raw.data_ptr(), ld_dt, float(dt_scale),
           dt_shift.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), cu.data_ptr(),
           slots.data_ptr(), out.data_ptr(), n_seq, H, P, N, n_groups, _dt(xbc), _stream())
+
+
+SSD_CHUNK = 64  # tokens per chunk of the tensor-core scan
+
+
+def ssd_supported(d_head: int, d_state: int) -> bool:
+    """Whether the chunked tensor-core scan is compiled for this head size / state size."""
+    return bool(_fn("pmm_ssd_supported")(d_head, d_state))
+
+
+def ssd_chunks(new_lens: Sequence[int]) -> int:
+    return sum((n + SSD_CHUNK - 1) // SSD_CHUNK for n in new_lens)
+
+
+def ssd_scratch_floats(new_lens: Sequence[int], n_heads: int, d_head: int, d_state: int) -> int:
+    return ssd_chunks(new_lens) * n_heads * (d_head * d_state + 1)
+
+
+def ssm_scan_chunked(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Tensor, a_log: Tensor,
+                     d_skip: Tensor, state: Tensor, cu: Tensor, slots: Tensor, new_lens: Sequence[int],
+                     out: Tensor, n_groups: int, scratch: Tensor) -> None:
+    """The Mamba2 recurrence over prompt portions in chunks of 64 tokens on tensor cores
+    (bfloat16 activations); same contract as ssm_scan_seq.  ``scratch``: float32, at least
+    ssd_scratch_floats(...) elements."""
+    _cuda(xbc, dt_raw, dt_shift, a_log, d_skip, state, cu, slots, out, scratch)
+    _need(state.dtype == torch.float32 and state.dim() == 4 and state.is_contiguous(),
+          "ssm_scan: state must be contiguous float32 [slots, H, P, N]")
+    _, H, P, N = state.shape
+    _need(xbc.dtype == torch.bfloat16 and ssd_supported(P, N),
+          f"ssm_scan_chunked: needs bfloat16 and a compiled (d_head, d_state) pair, got {xbc.dtype} ({P}, {N})")
+    ld_x = _rows_view(xbc, "ssm_scan: xbc")
+    _need(xbc.shape[1] == H * P + 2 * n_groups * N and ld_x % 8 == 0 and xbc.data_ptr() % 16 == 0,
+          "ssm_scan_chunked: xbc must hold [x | B | C] in rows that start on 16-byte boundaries")
+    ld_dt = _rows_view(dt_raw, "ssm_scan: dt")
+    _need(dt_raw.shape[1] == H and dt_raw.dtype == xbc.dtype, "ssm_scan: dt must be [T, H]")
+    for v, nm in ((dt_shift, "dt_shift"), (a_log, "A_log"), (d_skip, "D")):
+        _f32vec(v, H, f"ssm_scan: {nm}")
+    _need(out.shape == (xbc.shape[0], H * P) and out.is_contiguous() and out.dtype == xbc.dtype,
+          "ssm_scan: out must be [T, H*P]")
+    n_chunks = ssd_chunks(new_lens)
+    need = n_chunks * H * (P * N + 1)
+    _need(scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= need,
+          f"ssm_scan_chunked: needs {need} floats of scratch")
+    chunk_state = scratch.data_ptr()
+    chunk_decay = chunk_state + 4 * n_chunks * H * P * N
+    _call("pmm_ssd_chunked", xbc.data_ptr(), ld_x, dt_raw.data_ptr(), ld_dt, float(dt_scale),
+          dt_shift.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), cu.data_ptr(),
+          slots.data_ptr(), out.data_ptr(), chunk_state, chunk_decay, len(new_lens), n_chunks, H, P, N,
+          n_groups, _stream())
 
 
 def gated_norm(y: Tensor, z_raw: Tensor, z_scale: float, z_bias: Optional[Tensor],

@@ -24,6 +24,9 @@ from .base import Mixer, ParamSpec, StateSpec, register_mixer
 
 Tensor = torch.Tensor
 
+# Steps whose longest portion has at least this many tokens use the chunked scan.
+_CHUNKED_FROM = 8
+
 
 class Mamba2Mixer(Mixer):
     def __init__(self, hidden_size: int, n_heads: int, d_head: int, d_state: int, d_conv: int,
@@ -152,8 +155,16 @@ class Mamba2Mixer(Mixer):
                                    ctx.slots, ctx.n_seq, self.d_conv)
 
         y = ws.alloc((T, i_dim), proj.dtype)
-        K.ssm_scan_seq(xbc, dt, self.dt_scale, self.dt_shift, self.a_log, self.d_skip, state, ctx.cu_seqlens,
-                       ctx.slots, ctx.n_seq, y, self.n_groups)
+        if (not ctx.decode_only and proj.dtype == torch.bfloat16 and max(ctx.new_lens) >= _CHUNKED_FROM
+                and K.ssd_supported(self.d_head, self.d_state)):
+            # prompt portions: chunks of 64 tokens on tensor cores
+            scratch = ws.alloc((K.ssd_scratch_floats(ctx.new_lens, self.n_heads, self.d_head, self.d_state),),
+                               torch.float32)
+            K.ssm_scan_chunked(xbc, dt, self.dt_scale, self.dt_shift, self.a_log, self.d_skip, state,
+                               ctx.cu_seqlens, ctx.slots, ctx.new_lens, y, self.n_groups, scratch)
+        else:
+            K.ssm_scan_seq(xbc, dt, self.dt_scale, self.dt_shift, self.a_log, self.d_skip, state,
+                           ctx.cu_seqlens, ctx.slots, ctx.n_seq, y, self.n_groups)
         gated = ws.alloc((T, i_dim), proj.dtype)
         K.gated_norm(y, z, self.z_scale, self.z_bias, self.norm_w, self.norm_eps, self.n_groups,
                      self.norm_before_gate, gated)

@@ -164,6 +164,53 @@ def test_ssm_scan_continues_from_saved_state(dtype, H, Pd, N, G):
     assert float(state[1].abs().sum()) == 0.0 and float(state[2].abs().sum()) > 0
 
 
+@pytest.mark.parametrize("H,Pd,N,G", [(6, 16, 16, 3), (4, 32, 32, 2), (2, 64, 64, 1), (4, 64, 128, 1), (2, 64, 256, 2),
+                                      (2, 128, 128, 1), (2, 128, 256, 1)])
+def test_ssd_chunked_scan(H, Pd, N, G):
+    """The tensor-core scan over portions that start from a saved state, end inside a chunk, span
+    several chunks, and share a step with single tokens; state checked against the serial kernel."""
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(H * N + Pd)
+    portions = [[70, 1, 64, 9], [3, 130, 1], [64, 8, 128]]
+    lens = [sum(p) for p in portions]
+    I, conv_dim = H * Pd, H * Pd + 2 * G * N
+    xbcs = [q(torch.randn(n, conv_dim, generator=g), dtype) for n in lens]
+    dts = [q(torch.randn(n, H, generator=g), dtype) for n in lens]
+    a_log, d_skip, shift = torch.rand(H, generator=g) * 2, torch.randn(H, generator=g), torch.randn(H, generator=g) - 1.0
+    refs = [P.ssm_recurrence(x[:, :I].double().view(-1, H, Pd), x[:, I:I + G * N].double().view(-1, G, N),
+                             x[:, I + G * N:].double().view(-1, G, N), dt.double() * 0.7, a_log.double(),
+                             d_skip.double(), shift.double()).reshape(-1, I) for x, dt in zip(xbcs, dts)]
+    state = torch.zeros(4, H, Pd, N, device=DEV)
+    state_seq = torch.zeros(4, H, Pd, N, device=DEV)
+    slots = [2, 0, 3]
+    got = [torch.empty(n, I, dtype=dtype) for n in lens]
+    for seqs in _batch(portions):
+        T = sum(n for _, _, n in seqs)
+        xbc = torch.cat([xbcs[i][a:a + n] for i, a, n in seqs]).to(DEV)
+        dtbuf = torch.zeros(T, H + 8, dtype=dtype, device=DEV)
+        dtbuf[:, 8:] = torch.cat([dts[i][a:a + n] for i, a, n in seqs]).to(DEV)
+        cu = [0]
+        for _, _, n in seqs:
+            cu.append(cu[-1] + n)
+        new_lens = [n for _, _, n in seqs]
+        out = torch.empty(T, I, dtype=dtype, device=DEV)
+        out_seq = torch.empty(T, I, dtype=dtype, device=DEV)
+        sl = i32([slots[i] for i, _, _ in seqs])
+        scratch = torch.full((K().ssd_scratch_floats(new_lens, H, Pd, N),), float("nan"), device=DEV)
+        K().ssm_scan_chunked(xbc, dtbuf[:, 8:], 0.7, shift.to(DEV), a_log.to(DEV), d_skip.to(DEV), state, i32(cu), sl,
+                             new_lens, out, G, scratch)
+        K().ssm_scan_seq(xbc, dtbuf[:, 8:], 0.7, shift.to(DEV), a_log.to(DEV), d_skip.to(DEV), state_seq, i32(cu), sl,
+                         len(seqs), out_seq, G)
+        t0 = 0
+        for i, a, n in seqs:
+            got[i][a:a + n] = out[t0:t0 + n].cpu()
+            t0 += n
+    for i in range(3):
+        close(got[i], refs[i], dtype, what=f"chunked scan seq {i}")
+    close(state, state_seq, dtype, what="final states of the chunked and the serial scan")
+    assert float(state[1].abs().sum()) == 0.0
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("mode", ["gate", "gate_then_norm", "norm_then_gate"])
 def test_gated_norm(dtype, mode):

@@ -189,12 +189,26 @@ __global__ void ssd_state_pass_kernel(float* __restrict__ chunk_state, const flo
   if (nc <= 0) return;
   float* sp = state + (static_cast<size_t>(slots[seq]) * H + h) * PN + e;
   float s = *sp;
-  for (int c = 0; c < nc; ++c) {
-    const size_t ch = static_cast<size_t>(first + c) * H + h;
-    float* lp = chunk_state + ch * PN + e;
-    const float local = *lp;
-    *lp = s;  // the state at the start of chunk c
-    s = s * chunk_decay[ch] + local;
+  // The chain through s is short; the loads are what cost.  They are issued eight chunks
+  // ahead of the stores (each address is read before it is written, by this thread only).
+  constexpr int kAhead = 8;
+  for (int c0 = 0; c0 < nc; c0 += kAhead) {
+    float local[kAhead], decay[kAhead];
+#pragma unroll
+    for (int i = 0; i < kAhead; ++i) {
+      const int c = min(c0 + i, nc - 1);
+      const size_t ch = static_cast<size_t>(first + c) * H + h;
+      local[i] = __ldcs(chunk_state + ch * PN + e);
+      decay[i] = chunk_decay[ch];
+    }
+#pragma unroll
+    for (int i = 0; i < kAhead; ++i) {
+      if (c0 + i < nc) {
+        const size_t ch = static_cast<size_t>(first + c0 + i) * H + h;
+        chunk_state[ch * PN + e] = s;  // the state at the start of this chunk
+        s = s * decay[i] + local[i];
+      }
+    }
   }
   *sp = s;
 }

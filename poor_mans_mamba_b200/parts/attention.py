@@ -142,13 +142,16 @@ class PagedAttention(Mixer):
             per_tile = rows // group
             blocks = sum((n + per_tile - 1) // per_tile for n in new_lens) * self.num_kv_heads
             min_len = 64
+            # small decode blocks: several per SM; 64-row prompt tiles: one wave is enough
+            target = _TARGET_BLOCKS if rows == 16 else _TARGET_BLOCKS // 4
         else:
             blocks = sum(new_lens) * ((self.num_heads + 3) // 4)
             min_len = 128
+            target = _TARGET_BLOCKS
         reach = min(kv_len_bound, self.window) if self.window > 0 else kv_len_bound
-        if blocks >= _TARGET_BLOCKS or reach <= min_len:
+        if blocks >= target or reach <= min_len:
             return 1, 0
-        want = min((_TARGET_BLOCKS + blocks - 1) // blocks, (reach + min_len - 1) // min_len)
+        want = min((target + blocks - 1) // blocks, (reach + min_len - 1) // min_len)
         if want <= 1:
             return 1, 0
         split_len = ((kv_len_bound + want - 1) // want + 63) // 64 * 64

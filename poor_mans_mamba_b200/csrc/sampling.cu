@@ -39,12 +39,25 @@ __global__ void sample_rows_kernel(const float* __restrict__ logits, long long l
   const unsigned step = steps ? static_cast<unsigned>(steps[r]) : 0u;
   float bv = -CUDART_INF_F;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    float v = row[i];
-    if (!greedy) v = v * inv_t + gumbel_noise(seed, step, static_cast<unsigned>(i));
-    if (v > bv || (v == bv && i < bi) || bi == 0x7fffffff) {
-      bv = v;
-      bi = i;
+  // eight independent loads per thread and pass, so a row costs few memory round trips
+  constexpr int kU = 8;
+  for (int base = 0; base < V; base += kU * blockDim.x) {
+    float v[kU];
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int i = base + u * blockDim.x + threadIdx.x;
+      v[u] = i < V ? row[i] : -CUDART_INF_F;
+    }
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int i = base + u * blockDim.x + threadIdx.x;
+      if (i >= V) continue;
+      float x = v[u];
+      if (!greedy) x = x * inv_t + gumbel_noise(seed, step, static_cast<unsigned>(i));
+      if (x > bv || (x == bv && i < bi) || bi == 0x7fffffff) {
+        bv = x;
+        bi = i;
+      }
     }
   }
   // warp, then block reduction; smaller index wins equal values

@@ -1,0 +1,371 @@
+// Weight-streaming matrix product for decode steps: y[M, N] = x[M, K] W[N, K]^T with few
+// tokens (M <= 64) and bfloat16 weights.  Such a product is a read of W at memory speed;
+// what matters is a deep copy pipeline, enough blocks, and not touching the small
+// activations more than once.  So the kernel fuses what surrounds the product:
+//   prologue  x = rmsnorm(h) * w  from the float32 residual stream (every block redoes it:
+//             M rows from L2), or x read as bfloat16;
+//   epilogue  STORE     y -> bfloat16 [M, N]
+//             SWIGLU    W holds gate rows [0, F) and up rows [F, 2F):
+//                       act[m, f] = silu(gate * gate_mult) * up  -> bfloat16 [M, F]
+//             RESIDUAL  h[m, n] += scale * y  (float32 atomics; the K range may be split over
+//                       blocks, and up to two products with their own x, W, K and scale can
+//                       share one launch: the mixers' output projections).
+// Tensor-core form: the weights are the 16-row MMA operand (A), the tokens the 8-column one
+// (B), mma.sync m16n8k16 with float accumulation.  A block of 8 warps owns 32 weight rows;
+// W arrives in chunks of 256 columns through a 4-stage cp.async pipeline (16 KB a stage,
+// every thread copies the same four 16-byte pieces of each chunk, so the addresses are made
+// once); warps split a chunk 2 (rows) x 4 (columns) and the column quarters are added at the end.
+// (reference: linear layers are cublasSgemm calls, src/ops/gpu/linear.cu:3-21, the
+// multipliers, SiLU and adds separate launches, src/ops/cuda_backend.cu:311-338.)
+#include "common.cuh"
+
+namespace pmm {
+
+using bf16 = __nv_bfloat16;
+
+constexpr int kSgRows = 32;     // weight rows per block
+constexpr int kSgChunk = 256;   // columns per pipeline stage
+constexpr int kSgStages = 4;
+constexpr int kSgWStride = kSgChunk + 8;
+constexpr int kSgThreads = 256;
+constexpr int kSgPieces = kSgRows * (kSgChunk / 8) / kSgThreads;  // 16-byte pieces per thread and chunk
+
+enum { kSgStore = 0, kSgSwiglu = 1, kSgResidual = 2 };
+
+struct SkinnyProblem {
+  const bf16* x;       // [M, ldx] activations, or nullptr when the norm prologue is used
+  long long ldx;
+  const float* h_in;   // [M, K] residual stream for the norm prologue
+  const float* norm_w; // [K]
+  float eps;
+  const bf16* w;       // [N or 2F, K]
+  int K;
+  float scale;         // RESIDUAL: factor on y; SWIGLU: gate multiplier
+};
+
+struct SkinnyArgs {
+  SkinnyProblem p[2];
+  int n_problems;
+  int M, N;            // tokens, output columns (SWIGLU: F)
+  int k_slice;         // columns of K per block along gridDim.y (multiple of 256)
+  bf16* y;             // STORE / SWIGLU output
+  long long ldy;
+  float* h_out;        // RESIDUAL target [M, N]
+};
+
+__device__ __forceinline__ void sg_cp16(void* smem, const void* gmem, bool pred) {
+  const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+  const int sz = pred ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(sz));
+}
+__device__ __forceinline__ void sg_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void sg_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void sg_ldm(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void sg_mma(float* d, const unsigned* a, unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// MT: token tiles of 8 (2, 4 or 8 -> up to 16, 32, 64 tokens).
+template <int MT, int MODE>
+__global__ void __launch_bounds__(kSgThreads) skinny_gemm_kernel(const SkinnyArgs args) {
+  constexpr int MP = MT * 8;  // padded tokens
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const SkinnyProblem& pr = args.p[blockIdx.z];
+  const int K = pr.K;
+  const int k0 = blockIdx.y * args.k_slice;
+  if (k0 >= K) return;
+  const int k1 = min(K, k0 + args.k_slice);
+  const int kx = (k1 - k0 + kSgChunk - 1) / kSgChunk * kSgChunk;  // slice length, whole chunks
+  const int xs = kx + 8;                                          // row stride of x in shared memory
+  bf16* sW = reinterpret_cast<bf16*>(smem_raw);                   // [stages][32][264]
+  bf16* sX = sW + kSgStages * kSgRows * kSgWStride;               // [MP][xs]
+  float* sRed = reinterpret_cast<float*>(sX + MP * xs);           // [3][32][MP] column quarters, then up rows
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int M = args.M;
+  const int n0 = blockIdx.x * (MODE == kSgSwiglu ? 16 : kSgRows);  // first output column of the block
+  const int n_chunks = kx / kSgChunk;
+
+  // global row of W behind row r of the block's tile (SWIGLU: 16 gate rows, then their 16 up rows)
+  auto w_row = [&](int r) -> int {
+    if (MODE == kSgSwiglu) return r < 16 ? n0 + r : args.N + n0 + (r - 16);
+    return n0 + r;
+  };
+  const int w_rows_total = MODE == kSgSwiglu ? 2 * args.N : args.N;
+  auto w_row_ok = [&](int r) -> bool {
+    if (MODE == kSgSwiglu) return n0 + (r & 15) < args.N;
+    return n0 + r < args.N;
+  };
+  (void)w_rows_total;
+
+  // every thread copies the same pieces (row r, 16-byte column c8) of every chunk
+  const int c8 = tid & 31;
+  const bf16* src[kSgPieces];
+  bool row_ok[kSgPieces];
+#pragma unroll
+  for (int j = 0; j < kSgPieces; ++j) {
+    const int r = (tid >> 5) + j * (kSgThreads / 32);
+    row_ok[j] = w_row_ok(r);
+    src[j] = pr.w + (row_ok[j] ? static_cast<size_t>(w_row(r)) * K : 0) + k0 + c8 * 8;
+  }
+  auto load_chunk = [&](int stage, int chunk) {
+    bf16* dst = sW + stage * kSgRows * kSgWStride + (tid >> 5) * kSgWStride + c8 * 8;
+    const bool col_ok = k0 + chunk * kSgChunk + c8 * 8 < k1;
+#pragma unroll
+    for (int j = 0; j < kSgPieces; ++j) {
+      const bool ok = row_ok[j] && col_ok;
+      sg_cp16(dst + j * (kSgThreads / 32) * kSgWStride, ok ? src[j] + chunk * kSgChunk : pr.w, ok);
+    }
+  };
+
+  // group 0: the activations when they are read as bfloat16 (empty for the norm prologue)
+  if (pr.h_in == nullptr) {
+    for (int i = tid; i < MP * (kx / 8); i += kSgThreads) {
+      const int m = i / (kx / 8), k = k0 + (i % (kx / 8)) * 8;
+      const bool ok = m < M && k < k1;
+      sg_cp16(sX + m * xs + (k - k0), pr.x + (ok ? static_cast<size_t>(m) * pr.ldx + k : 0), ok);
+    }
+  }
+  sg_commit();
+  // groups 1..stages-1: the first weight chunks; they do not depend on the activations
+#pragma unroll
+  for (int s = 0; s < kSgStages - 1; ++s) {
+    if (s < n_chunks) load_chunk(s, s);
+    sg_commit();
+  }
+
+  // norm prologue: x = h * rsqrt(mean(h^2) + eps) * w for this K slice -> shared memory as
+  // bfloat16 (rows >= M and columns >= K zero), while the weight chunks are in flight
+  if (pr.h_in != nullptr) {
+    // One warp per token, two tokens at a time, 8 float4 per lane and token in flight: for
+    // widths up to 1024 a token's row is read once and stays in registers between the sum of
+    // squares and the scaling.
+    constexpr int kV = 8;                 // float4 per lane per pass
+    constexpr int kPass = kV * 32 * 4;    // 1024 columns per pass
+    for (int m0 = warp * 2; m0 < MP; m0 += 2 * (kSgThreads / 32)) {
+      float inv[2];
+      float4 keep[2][kV];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int m = m0 + j;
+        float ss = 0.f;
+        if (m < M) {
+          const float* row = pr.h_in + static_cast<size_t>(m) * K;
+          for (int kb = 0; kb < K; kb += kPass) {
+#pragma unroll
+            for (int i = 0; i < kV; ++i) {
+              const int k = kb + (i * 32 + lane) * 4;
+              keep[j][i] = (k < K) ? *reinterpret_cast<const float4*>(row + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int i = 0; i < kV; ++i)
+              ss += keep[j][i].x * keep[j][i].x + keep[j][i].y * keep[j][i].y + keep[j][i].z * keep[j][i].z +
+                    keep[j][i].w * keep[j][i].w;
+          }
+        }
+        ss = warp_sum(ss);
+        inv[j] = 1.0f / sqrtf(ss / static_cast<float>(K) + pr.eps);
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int m = m0 + j;
+        if (m >= MP) continue;
+        const float* row = pr.h_in + static_cast<size_t>(m < M ? m : 0) * K;
+        for (int kb = k0; kb < k0 + kx; kb += kPass) {
+#pragma unroll
+          for (int i = 0; i < kV; ++i) {
+            const int k = kb + (i * 32 + lane) * 4;
+            if (k >= k0 + kx) continue;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (m < M && k < k1) {
+              v = (K <= kPass && k0 == 0) ? keep[j][i] : *reinterpret_cast<const float4*>(row + k);
+              const float4 w4 = *reinterpret_cast<const float4*>(pr.norm_w + k);
+              v.x = v.x * inv[j] * w4.x;
+              v.y = v.y * inv[j] * w4.y;
+              v.z = v.z * inv[j] * w4.z;
+              v.w = v.w * inv[j] * w4.w;
+            }
+            bf16* dst = sX + m * xs + (k - k0);
+            *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(v.x, v.y);
+            *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(v.z, v.w);
+          }
+        }
+      }
+    }
+  }
+
+  const int ft = warp & 1, kh = warp >> 1;  // row half, column quarter of a chunk
+  float acc[MT][4];
+#pragma unroll
+  for (int i = 0; i < MT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+
+  for (int c = 0; c < n_chunks; ++c) {
+    // groups committed so far: 1 (x) + (stages-1) + c; x and chunk c are complete when at most
+    // stages-2 of the newest groups are still in flight
+    sg_wait<kSgStages - 2>();
+    __syncthreads();
+    if (c + kSgStages - 1 < n_chunks) load_chunk((c + kSgStages - 1) % kSgStages, c + kSgStages - 1);
+    sg_commit();
+    const bf16* tW = sW + (c % kSgStages) * kSgRows * kSgWStride;
+#pragma unroll
+    for (int ks = 0; ks < kSgChunk / 64; ++ks) {  // this warp's quarter of the chunk: 4 steps of 16
+      const int kcol = kh * (kSgChunk / 4) + ks * 16;
+      unsigned a[4];
+      sg_ldm(a[0], a[1], a[2], a[3], tW + (ft * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kSgWStride + kcol + (lane >> 4) * 8);
+      const int kx_col = c * kSgChunk + kcol;
+#pragma unroll
+      for (int np = 0; np < MT / 2; ++np) {
+        unsigned b0, b1, b2, b3;
+        sg_ldm(b0, b1, b2, b3, sX + (np * 16 + (lane & 7) + (lane >> 4) * 8) * xs + kx_col + ((lane >> 3) & 1) * 8);
+        sg_mma(acc[2 * np], a, b0, b1);
+        sg_mma(acc[2 * np + 1], a, b2, b3);
+      }
+    }
+  }
+  sg_wait<0>();
+  __syncthreads();
+
+  // add the four column quarters: warps 2..7 hand their sums to warps 0,1
+  const int g = lane >> 2, t2 = (lane & 3) * 2;
+  if (kh > 0) {
+    float* d = sRed + ((kh - 1) * 32 + ft * 16) * MP;
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt) {
+      d[g * MP + nt * 8 + t2] = acc[nt][0];
+      d[g * MP + nt * 8 + t2 + 1] = acc[nt][1];
+      d[(g + 8) * MP + nt * 8 + t2] = acc[nt][2];
+      d[(g + 8) * MP + nt * 8 + t2 + 1] = acc[nt][3];
+    }
+  }
+  __syncthreads();
+  if (kh == 0) {
+#pragma unroll
+    for (int q = 0; q < 3; ++q) {
+      const float* d = sRed + (q * 32 + ft * 16) * MP;
+#pragma unroll
+      for (int nt = 0; nt < MT; ++nt) {
+        acc[nt][0] += d[g * MP + nt * 8 + t2];
+        acc[nt][1] += d[g * MP + nt * 8 + t2 + 1];
+        acc[nt][2] += d[(g + 8) * MP + nt * 8 + t2];
+        acc[nt][3] += d[(g + 8) * MP + nt * 8 + t2 + 1];
+      }
+    }
+  }
+
+  if (MODE == kSgSwiglu) {
+    __syncthreads();
+    if (kh == 0 && ft == 1) {  // up rows -> shared memory
+#pragma unroll
+      for (int nt = 0; nt < MT; ++nt) {
+        sRed[g * MP + nt * 8 + t2] = acc[nt][0];
+        sRed[g * MP + nt * 8 + t2 + 1] = acc[nt][1];
+        sRed[(g + 8) * MP + nt * 8 + t2] = acc[nt][2];
+        sRed[(g + 8) * MP + nt * 8 + t2 + 1] = acc[nt][3];
+      }
+    }
+    __syncthreads();
+    if (kh == 0 && ft == 0) {
+#pragma unroll
+      for (int nt = 0; nt < MT; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int f = n0 + g + (e >> 1) * 8, m = nt * 8 + t2 + (e & 1);
+          if (f < args.N && m < M) {
+            const float up = sRed[(g + (e >> 1) * 8) * MP + m];
+            args.y[static_cast<size_t>(m) * args.ldy + f] = __float2bfloat16_rn(silu_f(acc[nt][e] * pr.scale) * up);
+          }
+        }
+      }
+    }
+    return;
+  }
+
+  if (kh == 0) {
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int n = n0 + ft * 16 + g + (e >> 1) * 8, m = nt * 8 + t2 + (e & 1);
+        if (n < args.N && m < M) {
+          if (MODE == kSgStore) {
+            args.y[static_cast<size_t>(m) * args.ldy + n] = __float2bfloat16_rn(acc[nt][e]);
+          } else {
+            atomicAdd(args.h_out + static_cast<size_t>(m) * args.N + n, pr.scale * acc[nt][e]);
+          }
+        }
+      }
+    }
+  }
+}
+
+template <int MT, int MODE>
+int launch_skinny(const SkinnyArgs& a, int k_max, cudaStream_t stream) {
+  constexpr int MP = MT * 8;
+  const int kx = (min(a.k_slice, k_max) + kSgChunk - 1) / kSgChunk * kSgChunk;
+  const size_t smem = static_cast<size_t>(kSgStages) * kSgRows * kSgWStride * sizeof(bf16) +
+                      static_cast<size_t>(MP) * (kx + 8) * sizeof(bf16) + 3 * 32 * MP * sizeof(float);
+  if (smem > 220 * 1024) return PMM_ERR_BAD_ARGUMENT;
+  auto kern = skinny_gemm_kernel<MT, MODE>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const int cols_per_block = MODE == kSgSwiglu ? 16 : kSgRows;
+  dim3 grid((a.N + cols_per_block - 1) / cols_per_block, (k_max + a.k_slice - 1) / a.k_slice, a.n_problems);
+  kern<<<grid, kSgThreads, smem, stream>>>(a);
+  return launch_status();
+}
+
+template <int MODE>
+int dispatch_skinny(const SkinnyArgs& a, int k_max, cudaStream_t stream) {
+  if (a.M <= 16) return launch_skinny<2, MODE>(a, k_max, stream);
+  if (a.M <= 32) return launch_skinny<4, MODE>(a, k_max, stream);
+  if (a.M <= 64) return launch_skinny<8, MODE>(a, k_max, stream);
+  return PMM_ERR_BAD_ARGUMENT;
+}
+
+}  // namespace pmm
+
+// mode 0 STORE (y bfloat16 [M, ldy]), 1 SWIGLU (w = [gate; up] rows, N = F, scale0 = gate multiplier),
+// 2 RESIDUAL (h_out[M, N] += scale * y, k_split blocks along K, one or two products).
+// x0/x1: bfloat16 activations, or nullptr with h_in/norm_w/eps for the RMSNorm prologue (K0 == width of h_in).
+PMM_EXPORT int pmm_skinny_gemm(int mode, int M, int N, const void* x0, long long ldx0, const float* h_in,
+                               const float* norm_w, float eps, const void* w0, int K0, float scale0,
+                               const void* x1, long long ldx1, const void* w1, int K1, float scale1,
+                               void* y, long long ldy, float* h_out, int k_split, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 64 || K0 <= 0 || K0 % 8 || (w1 && (K1 <= 0 || K1 % 8)) || k_split < 1) return PMM_ERR_BAD_ARGUMENT;
+  if ((x0 == nullptr) == (h_in == nullptr)) return PMM_ERR_BAD_ARGUMENT;
+  if (mode != pmm::kSgResidual && (k_split != 1 || w1 != nullptr || !y)) return PMM_ERR_BAD_ARGUMENT;
+  if (mode == pmm::kSgResidual && !h_out) return PMM_ERR_BAD_ARGUMENT;
+  pmm::SkinnyArgs a{};
+  a.p[0] = {static_cast<const pmm::bf16*>(x0), ldx0, h_in, norm_w, eps, static_cast<const pmm::bf16*>(w0), K0, scale0};
+  a.n_problems = 1;
+  int k_max = K0;
+  if (w1) {
+    if (!x1) return PMM_ERR_BAD_ARGUMENT;
+    a.p[1] = {static_cast<const pmm::bf16*>(x1), ldx1, nullptr, nullptr, 0.f, static_cast<const pmm::bf16*>(w1), K1, scale1};
+    a.n_problems = 2;
+    k_max = K0 > K1 ? K0 : K1;
+  }
+  a.M = M;
+  a.N = N;
+  const int chunks = (k_max + pmm::kSgChunk - 1) / pmm::kSgChunk;
+  a.k_slice = ((chunks + k_split - 1) / k_split) * pmm::kSgChunk;
+  a.y = static_cast<pmm::bf16*>(y);
+  a.ldy = ldy;
+  a.h_out = h_out;
+  switch (mode) {
+    case pmm::kSgStore: return pmm::dispatch_skinny<pmm::kSgStore>(a, k_max, stream);
+    case pmm::kSgSwiglu: return pmm::dispatch_skinny<pmm::kSgSwiglu>(a, k_max, stream);
+    case pmm::kSgResidual: return pmm::dispatch_skinny<pmm::kSgResidual>(a, k_max, stream);
+    default: return PMM_ERR_BAD_ARGUMENT;
+  }
+}

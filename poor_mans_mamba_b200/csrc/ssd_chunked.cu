@@ -220,7 +220,8 @@ __global__ void __launch_bounds__(128)
                             long long ld_dt, float dt_scale, const float* __restrict__ dt_shift,
                             const float* __restrict__ a_log, const float* __restrict__ d_skip,
                             const int* __restrict__ cu, int n_seq, const float* __restrict__ chunk_state,
-                            bf16* __restrict__ y, int H, int G) {
+                            bf16* __restrict__ y, int H, int G, const bf16* __restrict__ z_raw, long long ld_z,
+                            float z_scale, const float* __restrict__ z_bias) {
   constexpr int SX = P + 8, SN = N + 8;
   constexpr int PB = P < 64 ? P : 64;  // output columns per pass
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -344,15 +345,22 @@ __global__ void __launch_bounds__(128)
 #pragma unroll
     for (int nt = 0; nt < PB / 8; ++nt) {
       const int p = pb * PB + nt * 8 + (lane & 3) * 2;
-      if (i_lo < len) {
-        const float2 xv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sX + i_lo * SX + p));
-        *reinterpret_cast<__nv_bfloat162*>(y + static_cast<size_t>(t0 + i_lo) * I + h * P + p) =
-            __floats2bfloat162_rn(y1[nt][0] + e_lo * y2[nt][0] + Dh * xv.x, y1[nt][1] + e_lo * y2[nt][1] + Dh * xv.y);
-      }
-      if (i_hi < len) {
-        const float2 xv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sX + i_hi * SX + p));
-        *reinterpret_cast<__nv_bfloat162*>(y + static_cast<size_t>(t0 + i_hi) * I + h * P + p) =
-            __floats2bfloat162_rn(y1[nt][2] + e_hi * y2[nt][2] + Dh * xv.x, y1[nt][3] + e_hi * y2[nt][3] + Dh * xv.y);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int i = half ? i_hi : i_lo;
+        if (i >= len) continue;
+        const float e = half ? e_hi : e_lo;
+        const float2 xv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sX + i * SX + p));
+        float v0 = y1[nt][2 * half] + e * y2[nt][2 * half] + Dh * xv.x;
+        float v1 = y1[nt][2 * half + 1] + e * y2[nt][2 * half + 1] + Dh * xv.y;
+        if (z_raw) {  // gate fused: y * silu(z), z = z_raw * z_scale + z_bias
+          const int c = h * P + p;
+          const float2 zv = __bfloat1622float2(
+              *reinterpret_cast<const __nv_bfloat162*>(z_raw + static_cast<long long>(t0 + i) * ld_z + c));
+          v0 *= silu_f(zv.x * z_scale + (z_bias ? z_bias[c] : 0.f));
+          v1 *= silu_f(zv.y * z_scale + (z_bias ? z_bias[c + 1] : 0.f));
+        }
+        *reinterpret_cast<__nv_bfloat162*>(y + static_cast<size_t>(t0 + i) * I + h * P + p) = __floats2bfloat162_rn(v0, v1);
       }
     }
   }
@@ -362,7 +370,8 @@ template <int P, int N>
 int launch_ssd(const void* xbc, int ld_xbc, const void* dt_raw, long long ld_dt, float dt_scale,
                const float* dt_shift, const float* a_log, const float* d_skip, float* state,
                const int* cu, const int* slots, void* y, float* chunk_state, float* chunk_decay,
-               int n_seq, int n_chunks, int H, int G, cudaStream_t stream) {
+               int n_seq, int n_chunks, int H, int G, const void* z_raw, long long ld_z, float z_scale,
+               const float* z_bias, cudaStream_t stream) {
   const size_t smem1 = static_cast<size_t>(kQ) * ((P + 8) + (N + 8)) * sizeof(bf16);
   const size_t smem3 = (static_cast<size_t>(kQ) * (2 * (N + 8) + (P + 8)) + static_cast<size_t>(P) * (N + 8)) * sizeof(bf16);
   auto k1 = ssd_chunk_state_kernel<P, N>;
@@ -383,7 +392,7 @@ int launch_ssd(const void* xbc, int ld_xbc, const void* dt_raw, long long ld_dt,
   ssd_state_pass_kernel<<<grid2, 256, 0, stream>>>(chunk_state, chunk_decay, state, cu, slots, H, PN);
   k3<<<grid, 128, smem3, stream>>>(static_cast<const bf16*>(xbc), ld_xbc, static_cast<const bf16*>(dt_raw), ld_dt,
                                    dt_scale, dt_shift, a_log, d_skip, cu, n_seq, chunk_state,
-                                   static_cast<bf16*>(y), H, G);
+                                   static_cast<bf16*>(y), H, G, static_cast<const bf16*>(z_raw), ld_z, z_scale, z_bias);
   return launch_status();
 }
 
@@ -401,7 +410,8 @@ PMM_EXPORT int pmm_ssd_chunked(const void* xbc, int ld_xbc, const void* dt_raw, 
                                float dt_scale, const float* dt_shift, const float* a_log,
                                const float* d_skip, float* state, const int* cu, const int* slots,
                                void* y, float* chunk_state, float* chunk_decay, int n_seq, int n_chunks,
-                               int H, int P, int N, int G, cudaStream_t stream) {
+                               int H, int P, int N, int G, const void* z_raw, long long ld_z, float z_scale,
+                               const float* z_bias, cudaStream_t stream) {
   if (n_seq <= 0 || n_chunks <= 0) return 0;
   if (!pmm_ssd_supported(P, N) || H <= 0 || G <= 0 || H % G || H > 65535 || n_seq > 65535 ||
       !chunk_state || !chunk_decay)
@@ -409,7 +419,8 @@ PMM_EXPORT int pmm_ssd_chunked(const void* xbc, int ld_xbc, const void* dt_raw, 
 #define PMM_SSD_CASE(PP, NN)                                                                             \
   if (P == PP && N == NN)                                                                                \
     return pmm::launch_ssd<PP, NN>(xbc, ld_xbc, dt_raw, ld_dt, dt_scale, dt_shift, a_log, d_skip, state, \
-                                   cu, slots, y, chunk_state, chunk_decay, n_seq, n_chunks, H, G, stream)
+                                   cu, slots, y, chunk_state, chunk_decay, n_seq, n_chunks, H, G, z_raw,   \
+                                   ld_z, z_scale, z_bias, stream)
   PMM_SSD_CASE(16, 16);
   PMM_SSD_CASE(32, 32);
   PMM_SSD_CASE(64, 64);

@@ -26,7 +26,8 @@ __global__ void __launch_bounds__(kScanRows* kScanTpr)
                         const float* __restrict__ a_log, const float* __restrict__ d_skip,
                         float* __restrict__ state, const int* __restrict__ cu,
                         const int* __restrict__ slots, S* __restrict__ y, int H, int P, int N,
-                        int G) {
+                        int G, const S* __restrict__ z_raw, long long ld_z, float z_scale,
+                        const float* __restrict__ z_bias) {
   const int lane_n = threadIdx.x % kScanTpr;
   const int p = blockIdx.x * kScanRows + threadIdx.x / kScanTpr;
   const int h = blockIdx.y;
@@ -68,7 +69,15 @@ __global__ void __launch_bounds__(kScanRows* kScanTpr)
     }
 #pragma unroll
     for (int o = kScanTpr / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (row_ok && lane_n == 0) stf(y + static_cast<size_t>(t) * I + h * P + p, acc + Dh * xv);
+    if (row_ok && lane_n == 0) {
+      float yv = acc + Dh * xv;
+      if (z_raw) {  // gate fused: y * silu(z), z = z_raw * z_scale + z_bias
+        const int c = h * P + p;
+        const float zv = ldf(z_raw + static_cast<long long>(t) * ld_z + c) * z_scale + (z_bias ? z_bias[c] : 0.f);
+        yv *= silu_f(zv);
+      }
+      stf(y + static_cast<size_t>(t) * I + h * P + p, yv);
+    }
   }
 
   if (row_ok) {
@@ -128,14 +137,15 @@ template <typename S>
 int launch_scan(const void* xbc, int ld_xbc, const void* dt_raw, long long ld_dt, float dt_scale,
                 const float* dt_shift, const float* a_log, const float* d_skip, float* state,
                 const int* cu, const int* slots, void* y, int n_seq, int H, int P, int N, int G,
-                cudaStream_t stream) {
+                const void* z_raw, long long ld_z, float z_scale, const float* z_bias, cudaStream_t stream) {
   dim3 grid((P + kScanRows - 1) / kScanRows, H, n_seq);
   dim3 block(kScanRows * kScanTpr);
   const int npt = (N + kScanTpr - 1) / kScanTpr;
 #define PMM_SCAN_CASE(NPT)                                                                         \
   ssm_scan_seq_kernel<S, NPT><<<grid, block, 0, stream>>>(                                         \
       static_cast<const S*>(xbc), ld_xbc, static_cast<const S*>(dt_raw), ld_dt, dt_scale, dt_shift, \
-      a_log, d_skip, state, cu, slots, static_cast<S*>(y), H, P, N, G)
+      a_log, d_skip, state, cu, slots, static_cast<S*>(y), H, P, N, G, static_cast<const S*>(z_raw),  \
+      ld_z, z_scale, z_bias)
   if (npt <= 1) PMM_SCAN_CASE(1);
   else if (npt <= 2) PMM_SCAN_CASE(2);
   else if (npt <= 4) PMM_SCAN_CASE(4);
@@ -152,14 +162,16 @@ int launch_scan(const void* xbc, int ld_xbc, const void* dt_raw, long long ld_dt
 PMM_EXPORT int pmm_ssm_scan_seq(const void* xbc, int ld_xbc, const void* dt_raw, long long ld_dt,
                                 float dt_scale, const float* dt_shift, const float* a_log,
                                 const float* d_skip, float* state, const int* cu, const int* slots,
-                                void* y, int n_seq, int H, int P, int N, int G, int dtype,
+                                void* y, int n_seq, int H, int P, int N, int G, const void* z_raw,
+                                long long ld_z, float z_scale, const float* z_bias, int dtype,
                                 cudaStream_t stream) {
   if (n_seq <= 0) return 0;
   if (H <= 0 || P <= 0 || N <= 0 || G <= 0 || H % G || H > 65535 || n_seq > 65535)
     return PMM_ERR_BAD_ARGUMENT;
   PMM_DISPATCH_DTYPE(dtype, S, return pmm::launch_scan<S>(xbc, ld_xbc, dt_raw, ld_dt, dt_scale,
                                                           dt_shift, a_log, d_skip, state, cu, slots,
-                                                          y, n_seq, H, P, N, G, stream));
+                                                          y, n_seq, H, P, N, G, z_raw, ld_z, z_scale,
+                                                          z_bias, stream));
   return 0;
 }
 

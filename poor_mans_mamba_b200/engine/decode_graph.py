@@ -116,6 +116,12 @@ class GraphDecoder:
                 return self.buckets[size]
         return None
 
+    def capture_all(self) -> None:
+        """Capture every bucket now, so that no step pays for a capture while serving."""
+        for size in self.bucket_sizes:
+            if size not in self.buckets:
+                self.buckets[size] = self._capture(size)
+
     def _capture(self, b: int) -> _Bucket:
         bk = _Bucket(b, self.widths, self.device)
         host = bk.host[0].numpy()

@@ -34,12 +34,14 @@ class Response:
 class Engine:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", device: str = "cuda:0",
                  max_tokens: int = 65536, max_seqs: int = 64, page_size: int = 64,
-                 max_batched_tokens: int = 2048, max_seq_len: int = 8192, cuda_graphs: bool = True):
+                 max_batched_tokens: int = 2048, max_seq_len: int = 8192, cuda_graphs: bool = True,
+                 warm_graphs: bool = False):
         """``max_tokens``: capacity of the key/value cache in tokens (whole pages);
         ``max_seqs``: most requests alive at a time (= number of fixed-state slots);
         ``max_batched_tokens``: token budget of one step; ``max_seq_len``: longest context
         served by the CUDA-graph decode path (longer requests decode through plain launches);
-        ``cuda_graphs``: capture decode-only steps into CUDA graphs."""
+        ``cuda_graphs``: capture decode-only steps into CUDA graphs (``warm_graphs``: all
+        batch-size buckets at once here, else each at its first use)."""
         if not torch.cuda.is_available():
             raise RuntimeError("poor_mans_mamba_b200 runs on a CUDA device only; there is no CPU path")
         K.ensure_built()
@@ -51,6 +53,9 @@ class Engine:
         self.runner = ModelRunner(self.model, self.cache)
         if cuda_graphs:
             self.runner.enable_graphs(max_seq_len)
+            if warm_graphs:
+                with torch.cuda.device(self.device):
+                    self.runner.graphs.capture_all()
         self.scheduler = Scheduler(self.cache, max_batched_tokens=max_batched_tokens, max_seqs=max_seqs)
         self.sampler = Sampler(self.device)
         self._next_id = 0

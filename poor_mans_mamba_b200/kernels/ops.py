@@ -39,11 +39,11 @@ _SIGNATURES = {
                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_ssm_scan_seq": [c_void_p, c_int, c_void_p, c_longlong, c_float, c_void_p, c_void_p,
                          c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                         c_int, c_int, c_void_p],
+                         c_int, c_void_p, c_longlong, c_float, c_void_p, c_int, c_void_p],
     "pmm_ssd_supported": [c_int, c_int],
     "pmm_ssd_chunked": [c_void_p, c_int, c_void_p, c_longlong, c_float, c_void_p, c_void_p, c_void_p,
                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                        c_int, c_int, c_int, c_void_p],
+                        c_int, c_int, c_int, c_void_p, c_longlong, c_float, c_void_p, c_void_p],
     "pmm_gated_norm": [c_void_p, c_void_p, c_longlong, c_float, c_void_p, c_void_p, c_float, c_int,
                        c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_qkv_rope_store": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_float,
@@ -60,6 +60,9 @@ _SIGNATURES = {
                                   c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
                                   c_int, c_int, c_int, c_int, c_void_p],
     "pmm_flash_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "pmm_skinny_gemm": [c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_int,
+                        c_float, c_void_p, c_longlong, c_void_p, c_int, c_float, c_void_p, c_longlong, c_void_p,
+                        c_int, c_void_p],
     "pmm_silu_mul": [c_void_p, c_longlong, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
     "pmm_add_row_bias": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "pmm_sample_rows": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
@@ -299,10 +302,23 @@ def conv1d_decode(x: Tensor, pre_scale: Tensor, pre_bias: Optional[Tensor], weig
           K, _dt(x), _stream())
 
 
+def _gate_args(gate, out: Tensor, what: str):
+    """(z pointer, row stride, scale, bias pointer) of an optional fused gate (z view, scale, bias)."""
+    if gate is None:
+        return None, 0, 0.0, None
+    z, z_scale, z_bias = gate
+    _cuda(z, z_bias)
+    ld_z = _rows_view(z, f"{what}: z")
+    _need(z.shape == out.shape and z.dtype == out.dtype, f"{what}: z must match the output")
+    _f32vec(z_bias, out.shape[1], f"{what}: z_bias")
+    return z.data_ptr(), ld_z, float(z_scale), _ptr(z_bias)
+
+
 def ssm_scan_seq(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Tensor, a_log: Tensor,
                  d_skip: Tensor, state: Tensor, cu: Tensor, slots: Tensor, n_seq: int, out: Tensor,
-                 n_groups: int) -> None:
-    """Token-serial Mamba2 recurrence from the saved state; state[slots, H, P, N] is updated."""
+                 n_groups: int, gate=None) -> None:
+    """Token-serial Mamba2 recurrence from the saved state; state[slots, H, P, N] is updated.
+    ``gate`` = (z view [T, I], z_scale, z_bias or None): the output is y * silu(z*z_scale + z_bias)."""
     _cuda(xbc, dt_raw, dt_shift, a_log, d_skip, state, cu, slots, out)
     _need(state.dtype == torch.float32 and state.dim() == 4 and state.is_contiguous(),
           "ssm_scan: state must be contiguous float32 [slots, H, P, N]")
@@ -316,9 +332,10 @@ def ssm_scan_seq(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Tensor,
         _f32vec(v, H, f"ssm_scan: {nm}")
     _need(out.shape == (xbc.shape[0], H * P) and out.is_contiguous() and out.dtype == xbc.dtype,
           "ssm_scan: out must be [T, H*P]")
+    zp, ld_z, zs, zb = _gate_args(gate, out, "ssm_scan")
     _call("pmm_ssm_scan_seq", xbc.data_ptr(), ld_x, dt_raw.data_ptr(), ld_dt, float(dt_scale),
           dt_shift.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), cu.data_ptr(),
-          slots.data_ptr(), out.data_ptr(), n_seq, H, P, N, n_groups, _dt(xbc), _stream())
+          slots.data_ptr(), out.data_ptr(), n_seq, H, P, N, n_groups, zp, ld_z, zs, zb, _dt(xbc), _stream())
 
 
 SSD_CHUNK = 64  # tokens per chunk of the tensor-core scan
@@ -339,7 +356,7 @@ def ssd_scratch_floats(new_lens: Sequence[int], n_heads: int, d_head: int, d_sta
 
 def ssm_scan_chunked(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Tensor, a_log: Tensor,
                      d_skip: Tensor, state: Tensor, cu: Tensor, slots: Tensor, new_lens: Sequence[int],
-                     out: Tensor, n_groups: int, scratch: Tensor) -> None:
+                     out: Tensor, n_groups: int, scratch: Tensor, gate=None) -> None:
     """The Mamba2 recurrence over prompt portions in chunks of 64 tokens on tensor cores
     (bfloat16 activations); same contract as ssm_scan_seq.  ``scratch``: float32, at least
     ssd_scratch_floats(...) elements."""
@@ -364,10 +381,12 @@ def ssm_scan_chunked(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Ten
           f"ssm_scan_chunked: needs {need} floats of scratch")
     chunk_state = scratch.data_ptr()
     chunk_decay = chunk_state + 4 * n_chunks * H * P * N
+    zp, ld_z, zs, zb = _gate_args(gate, out, "ssm_scan_chunked")
+    _need(zp is None or (ld_z % 2 == 0 and zp % 4 == 0), "ssm_scan_chunked: z rows must be 4-byte aligned")
     _call("pmm_ssd_chunked", xbc.data_ptr(), ld_x, dt_raw.data_ptr(), ld_dt, float(dt_scale),
           dt_shift.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), cu.data_ptr(),
           slots.data_ptr(), out.data_ptr(), chunk_state, chunk_decay, len(new_lens), n_chunks, H, P, N,
-          n_groups, _stream())
+          n_groups, zp, ld_z, zs, zb, _stream())
 
 
 def gated_norm(y: Tensor, z_raw: Tensor, z_scale: float, z_bias: Optional[Tensor],
@@ -508,6 +527,82 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
     if n_splits > 1:
         _call("pmm_flash_combine", part_o, part_ml, out.data_ptr(), T * n_q_heads, int(n_splits), head_dim,
               _dt(out), _stream())
+
+
+SKINNY_MAX_TOKENS = 16  # beyond this the activations no longer fit beside a deep weight pipeline
+
+
+def _skinny_check(M: int, w: Tensor, K: int, what: str) -> None:
+    _need(M <= 64, f"{what}: at most 64 tokens")
+    _need(w.dtype == torch.bfloat16 and w.dim() == 2 and w.is_contiguous() and w.shape[1] == K and K % 8 == 0,
+          f"{what}: weights must be contiguous bfloat16 [rows, K] with K a multiple of 8")
+
+
+def skinny_fits(M: int, K: int) -> bool:
+    """Whether M tokens x K columns of activations fit in shared memory beside the weight pipeline
+    (the products that cannot split K keep the whole row block resident)."""
+    mp = 16 if M <= 16 else 32 if M <= 32 else 64
+    kx = (K + 255) // 256 * 256
+    return M <= 64 and 4 * 32 * 264 * 2 + mp * (kx + 8) * 2 + 3 * 32 * mp * 4 <= 220 * 1024
+
+
+def skinny_linear_norm(h: Tensor, norm_weight: Tensor, eps: float, weight: Tensor, out: Tensor) -> None:
+    """out[M, N] = (rmsnorm(h) * norm_weight) @ weight^T for M <= 64 rows of the float32 stream."""
+    _cuda(h, norm_weight, weight, out)
+    M, K = h.shape
+    _need(h.dtype == torch.float32 and h.is_contiguous(), "skinny_linear_norm: h must be contiguous float32")
+    _skinny_check(M, weight, K, "skinny_linear_norm")
+    _need(skinny_fits(M, K), f"skinny_linear_norm: {M} tokens x {K} columns do not fit in shared memory")
+    _f32vec(norm_weight, K, "skinny_linear_norm: norm weight")
+    N = weight.shape[0]
+    _need(out.dtype == torch.bfloat16 and out.shape == (M, N) and out.stride(1) == 1, "skinny_linear_norm: out [M, N] bfloat16")
+    _call("pmm_skinny_gemm", 0, M, N, None, 0, h.data_ptr(), norm_weight.data_ptr(), float(eps), weight.data_ptr(), K,
+          1.0, None, 0, None, 0, 0.0, out.data_ptr(), out.stride(0), None, 1, _stream())
+
+
+def skinny_swiglu_norm(h: Tensor, norm_weight: Tensor, eps: float, gate_up: Tensor, gate_mult: float,
+                       out: Tensor) -> None:
+    """out[M, F] = silu(gate * gate_mult) * up with [gate | up] = (rmsnorm(h) * norm_weight) @ gate_up^T."""
+    _cuda(h, norm_weight, gate_up, out)
+    M, K = h.shape
+    _need(h.dtype == torch.float32 and h.is_contiguous(), "skinny_swiglu_norm: h must be contiguous float32")
+    _skinny_check(M, gate_up, K, "skinny_swiglu_norm")
+    _need(skinny_fits(M, K), f"skinny_swiglu_norm: {M} tokens x {K} columns do not fit in shared memory")
+    _f32vec(norm_weight, K, "skinny_swiglu_norm: norm weight")
+    F = gate_up.shape[0] // 2
+    _need(gate_up.shape[0] == 2 * F and out.dtype == torch.bfloat16 and out.shape == (M, F) and out.is_contiguous(),
+          "skinny_swiglu_norm: out [M, F] bfloat16 for gate_up [2F, K]")
+    _call("pmm_skinny_gemm", 1, M, F, None, 0, h.data_ptr(), norm_weight.data_ptr(), float(eps), gate_up.data_ptr(), K,
+          float(gate_mult), None, 0, None, 0, 0.0, out.data_ptr(), out.stride(0), None, 1, _stream())
+
+
+def skinny_residual(h: Tensor, products: Sequence[Tuple[Tensor, Tensor, float]]) -> None:
+    """h[M, N] += sum_i scale_i * (x_i @ w_i^T) for one or two (x, w, scale); float32 atomics, the K
+    ranges are split over blocks."""
+    _need(1 <= len(products) <= 2, "skinny_residual: one or two products")
+    M, N = h.shape
+    _cuda(h)
+    _need(h.dtype == torch.float32 and h.is_contiguous(), "skinny_residual: h must be contiguous float32")
+    args = []
+    k_max = 0
+    for x, w, sc in products:
+        _cuda(x, w)
+        K = x.shape[1]
+        _need(x.dtype == torch.bfloat16 and x.shape[0] == M and x.stride(1) == 1 and x.stride(0) % 8 == 0
+              and x.data_ptr() % 16 == 0, "skinny_residual: x must be bfloat16 [M, K] with 16-byte aligned rows")
+        _skinny_check(M, w, K, "skinny_residual")
+        _need(w.shape[0] == N, "skinny_residual: weight rows must equal the stream width")
+        args.append((x.data_ptr(), x.stride(0), w.data_ptr(), K, float(sc)))
+        k_max = max(k_max, K)
+    chunks = (k_max + 255) // 256
+    col_blocks = (N + 31) // 32 * len(products)
+    k_split = max(1, min(chunks, (296 + col_blocks - 1) // col_blocks))
+    while k_split < chunks and not skinny_fits(M, (chunks + k_split - 1) // k_split * 256):
+        k_split += 1
+    a0 = args[0]
+    a1 = args[1] if len(args) > 1 else (None, 0, None, 0, 0.0)
+    _call("pmm_skinny_gemm", 2, M, N, a0[0], a0[1], None, None, 0.0, a0[2], a0[3], a0[4], a1[0], a1[1], a1[2], a1[3],
+          a1[4], None, 0, h.data_ptr(), k_split, _stream())
 
 
 def silu_mul(gate_up: Tensor, gate_mult: float, out: Tensor) -> None:

@@ -90,6 +90,12 @@ class PagedAttention(Mixer):
         self.forward_projected(proj, ctx, cache, out)
 
     def forward_projected(self, proj: Tensor, ctx, cache, out: Tensor) -> None:
+        K.linear(self.pre_output(proj, ctx, cache), self.w_out, out)
+
+    def output_weight(self) -> Tensor:
+        return self.w_out
+
+    def pre_output(self, proj: Tensor, ctx, cache) -> Tensor:
         T = proj.shape[0]
         ws = ctx.workspace
         kv = cache.paged(f"{self.name}.kv")
@@ -131,7 +137,7 @@ class PagedAttention(Mixer):
                           self.num_kv_heads, self.head_dim, 1.0 / math.sqrt(float(self.head_dim)),
                           window=self.window, n_splits=n_splits, split_len=split_len, scratch=scratch,
                           cu_seqlens=ctx.cu_seqlens, new_lens=ctx.new_lens)
-        K.linear(attn, self.w_out, out)
+        return attn
 
     def plan_splits(self, new_lens, kv_len_bound: int, dtype: torch.dtype):
         """How many key ranges every block's keys are cut into: enough blocks to fill the GPU
@@ -141,9 +147,9 @@ class PagedAttention(Mixer):
             rows = 16 if (group <= 16 and max(new_lens) * group <= 16) else 64
             per_tile = rows // group
             blocks = sum((n + per_tile - 1) // per_tile for n in new_lens) * self.num_kv_heads
-            min_len = 64
-            # small decode blocks: several per SM; 64-row prompt tiles: one wave is enough
-            target = _TARGET_BLOCKS if rows == 16 else _TARGET_BLOCKS // 4
+            min_len = 256 if rows == 16 else 64
+            # small decode blocks: two per SM; 64-row prompt tiles: one wave is enough
+            target = _TARGET_BLOCKS // 2 if rows == 16 else _TARGET_BLOCKS // 4
         else:
             blocks = sum(new_lens) * ((self.num_heads + 3) // 4)
             min_len = 128

@@ -153,6 +153,19 @@ class Mixer(Part):
     def forward_projected(self, proj: Tensor, ctx, cache: LayerCache, out: Tensor) -> None:
         raise NotImplementedError
 
+    # A mixer whose last operation is a plain projection back to the stream may also expose
+    # that: ``pre_output`` returns the activation [T, inner] that ``output_weight`` [D, inner]
+    # is applied to (``output_bias`` [D] or None), so that an arrangement can run the output
+    # projections of its mixers as one product that accumulates into the residual stream.
+    def pre_output(self, proj: Tensor, ctx, cache: LayerCache) -> Tensor:
+        raise NotImplementedError
+
+    def output_weight(self) -> Optional[Tensor]:
+        return None
+
+    def output_bias(self) -> Optional[Tensor]:
+        return None
+
 
 class FeedForward(Part):
     """forward(x, ctx, out): x [T, D] normalised activations, out [T, D]."""

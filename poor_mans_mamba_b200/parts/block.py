@@ -106,7 +106,47 @@ class ParallelPreNormBlock(Part):
                 start += rows
             self._fused_in = fused
 
+    def _few_tokens_path(self, ctx) -> bool:
+        """Steps of few tokens in bfloat16 are reads of the weights: they take the fused
+        weight-streaming products (norm in the prologue, SwiGLU or the residual add in the
+        epilogue) instead of library products with separate element-wise launches."""
+        from .ffn import SwiGLU
+        from .norm import RMSNorm
+        if (ctx.dtype != torch.bfloat16 or ctx.n_tokens > K.SKINNY_MAX_TOKENS or self.hidden_size % 8
+                or not K.skinny_fits(ctx.n_tokens, self.hidden_size)):
+            return False
+        if self._fused_in is None or not isinstance(self.mixer_norm, RMSNorm):
+            return False
+        if any(m.output_weight() is None or m.output_bias() is not None for m in self.mixers):
+            return False
+        if len(self.mixers) > 2:
+            return False
+        if self.ffn is not None and not (isinstance(self.ffn, SwiGLU) and isinstance(self.ffn_norm, RMSNorm)):
+            return False
+        return True
+
+    def _forward_few_tokens(self, stream: ResidualStream, ctx, cache: LayerCache) -> None:
+        ws = ctx.workspace
+        mark = ws.mark()
+        h = stream.flush()
+        T = h.shape[0]
+        proj = ws.alloc((T, self._fused_in.shape[0]), ctx.dtype)
+        K.skinny_linear_norm(h, self.mixer_norm.weight, self.mixer_norm.eps, self._fused_in, proj)
+        products = []
+        for m, (c0, c1) in zip(self.mixers, self._fused_cols):
+            products.append((m.pre_output(proj[:, c0:c1], ctx, cache), m.output_weight(), m.out_scale))
+        K.skinny_residual(h, products)  # h = (h + s0 * y0 W0^T) + s1 * y1 W1^T, in one launch
+        if self.ffn is not None:
+            act = ws.alloc((T, self.ffn.intermediate_size), ctx.dtype)
+            K.skinny_swiglu_norm(h, self.ffn_norm.weight, self.ffn_norm.eps, self.ffn.gate_up,
+                                 self.ffn.gate_multiplier, act)
+            K.skinny_residual(h, [(act, self.ffn.down, self.ffn.out_scale)])
+        ws.release(mark)
+
     def forward(self, stream: ResidualStream, ctx, cache: LayerCache) -> None:
+        if self._few_tokens_path(ctx):
+            self._forward_few_tokens(stream, ctx, cache)
+            return
         ws = ctx.workspace
         mark = ws.mark()
         n = stream.normed(self.mixer_norm)

@@ -135,6 +135,17 @@ class Mamba2Mixer(Mixer):
         self.forward_projected(proj, ctx, cache, out)
 
     def forward_projected(self, proj: Tensor, ctx, cache, out: Tensor) -> None:
+        K.linear(self.pre_output(proj, ctx, cache), self.w_out, out)
+        if self.out_b is not None:
+            K.add_row_bias_(out, self.out_b)
+
+    def output_weight(self) -> Tensor:
+        return self.w_out
+
+    def output_bias(self) -> Optional[Tensor]:
+        return self.out_b
+
+    def pre_output(self, proj: Tensor, ctx, cache) -> Tensor:
         T = proj.shape[0]
         ws = ctx.workspace
         i_dim = self.d_ssm
@@ -155,22 +166,24 @@ class Mamba2Mixer(Mixer):
                                    ctx.slots, ctx.n_seq, self.d_conv)
 
         y = ws.alloc((T, i_dim), proj.dtype)
+        # without a norm the gate y * silu(z) is the scan kernels' epilogue
+        gate = (z, self.z_scale, self.z_bias) if self.norm_w is None else None
         if (not ctx.decode_only and proj.dtype == torch.bfloat16 and max(ctx.new_lens) >= _CHUNKED_FROM
                 and K.ssd_supported(self.d_head, self.d_state)):
             # prompt portions: chunks of 64 tokens on tensor cores
             scratch = ws.alloc((K.ssd_scratch_floats(ctx.new_lens, self.n_heads, self.d_head, self.d_state),),
                                torch.float32)
             K.ssm_scan_chunked(xbc, dt, self.dt_scale, self.dt_shift, self.a_log, self.d_skip, state,
-                               ctx.cu_seqlens, ctx.slots, ctx.new_lens, y, self.n_groups, scratch)
+                               ctx.cu_seqlens, ctx.slots, ctx.new_lens, y, self.n_groups, scratch, gate=gate)
         else:
             K.ssm_scan_seq(xbc, dt, self.dt_scale, self.dt_shift, self.a_log, self.d_skip, state,
-                           ctx.cu_seqlens, ctx.slots, ctx.n_seq, y, self.n_groups)
+                           ctx.cu_seqlens, ctx.slots, ctx.n_seq, y, self.n_groups, gate=gate)
+        if gate is not None:
+            return y
         gated = ws.alloc((T, i_dim), proj.dtype)
         K.gated_norm(y, z, self.z_scale, self.z_bias, self.norm_w, self.norm_eps, self.n_groups,
                      self.norm_before_gate, gated)
-        K.linear(gated, self.w_out, out)
-        if self.out_b is not None:
-            K.add_row_bias_(out, self.out_b)
+        return gated
 
 
 register_mixer("mamba2", Mamba2Mixer)

@@ -429,3 +429,47 @@ def test_unsupported_sizes_are_refused():
     with pytest.raises(KernelError, match="float32 or bfloat16"):
         K().silu_mul(torch.zeros(2, 4, dtype=torch.float16, device=DEV), 1.0,
                      torch.zeros(2, 2, dtype=torch.float16, device=DEV))
+
+
+@pytest.mark.parametrize("M", [1, 7, 16, 17, 40, 64])
+@pytest.mark.parametrize("N,Kd", [(50, 96), (1024, 1000), (4120, 1024), (200, 2048)])
+def test_skinny_gemm_modes(M, N, Kd):
+    """The weight-streaming product for few tokens: norm prologue + store, norm + SwiGLU, and
+    residual accumulation of one and two products, at widths on and off the chunk size."""
+    g = torch.Generator().manual_seed(M * 131 + N + Kd)
+    ops = K()
+    bf = torch.bfloat16
+    h = torch.randn(M, Kd, generator=g)
+    nw = torch.rand(Kd, generator=g) + 0.5
+    w = (torch.randn(N, Kd, generator=g) * 0.05).to(bf)
+    x64 = P.rms_norm(h.double(), nw.double(), 1e-5).to(bf).double()  # the kernel rounds the normed row
+    # STORE with the norm prologue, into a column slice of a wider buffer
+    buf = torch.zeros(M, N + 16, dtype=bf, device=DEV)
+    if not ops.skinny_fits(M, Kd):
+        with pytest.raises(ops.KernelError, match="do not fit"):
+            ops.skinny_linear_norm(h.to(DEV), nw.to(DEV), 1e-5, w.to(DEV), buf[:, 8:8 + N])
+    else:
+        ops.skinny_linear_norm(h.to(DEV), nw.to(DEV), 1e-5, w.to(DEV), buf[:, 8:8 + N])
+        close(buf[:, 8:8 + N], x64 @ w.double().t(), bf, what="skinny store")
+        assert float(buf[:, :8].abs().sum()) == 0 and float(buf[:, 8 + N:].abs().sum()) == 0
+    # SWIGLU
+    if N % 2 == 0 and ops.skinny_fits(M, Kd):
+        F = N // 2
+        act = torch.empty(M, F, dtype=bf, device=DEV)
+        ops.skinny_swiglu_norm(h.to(DEV), nw.to(DEV), 1e-5, w.to(DEV), 1.5, act)
+        gu = x64 @ w.double().t()
+        close(act, P.silu(gu[:, :F] * 1.5) * gu[:, F:], bf, what="skinny swiglu")
+    # RESIDUAL: one product, then two with different inner sizes and scales
+    K2 = 64
+    xa = (torch.randn(M, Kd, generator=g)).to(bf)
+    xb = (torch.randn(M, K2, generator=g)).to(bf)
+    wa = (torch.randn(N, Kd, generator=g) * 0.05).to(bf)
+    wb = (torch.randn(N, K2, generator=g) * 0.05).to(bf)
+    hres = torch.randn(M, N, generator=g)
+    hd = hres.clone().to(DEV)
+    ops.skinny_residual(hd, [(xa.to(DEV), wa.to(DEV), 0.6)])
+    ref1 = hres.double() + 0.6 * (xa.double() @ wa.double().t())
+    close(hd, ref1, torch.float32, scale=30.0, what="skinny residual one product")
+    ops.skinny_residual(hd, [(xa.to(DEV), wa.to(DEV), -0.3), (xb.to(DEV), wb.to(DEV), 1.1)])
+    ref2 = ref1 - 0.3 * (xa.double() @ wa.double().t()) + 1.1 * (xb.double() @ wb.double().t())
+    close(hd, ref2, torch.float32, scale=30.0, what="skinny residual two products")

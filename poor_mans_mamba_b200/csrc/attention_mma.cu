@@ -8,8 +8,8 @@
 // O += P V run on mma.sync m16n8k16 with ldmatrix operands; softmax is the online form in
 // float (exp2 with the scale folded in).  Two shapes:
 //   * tile of 64 rows, warp w owns rows 16w..16w+15 and walks all keys   (prompt portions)
-//   * tile of 16 rows, the 4 warps split every 64-key tile by keys and are merged at the
-//     end through shared memory                                           (decode: G rows)
+//   * tile of 16 rows, tiles are fetched four at a time, each warp takes one whole tile and
+//     the warps are merged at the end through shared memory              (decode: G rows)
 // With several key splits the block writes (max, sum, unnormalised output) and
 // flash_combine merges them; with one split it writes the normalised output.
 //
@@ -68,20 +68,23 @@ __global__ void __launch_bounds__(128)
                        const int* __restrict__ positions, const int* __restrict__ cu,
                        bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                        float scale_log2, int window, int split_len, int n_splits, int page_size,
-                       int n_seq, int Hq, int Hkv) {
+                       int n_seq, int Hq, int Hkv, int* __restrict__ split_counter) {
   constexpr int M = SPLITW ? 16 : 64;
   constexpr int KT = kFlashKeys;
   constexpr int STRIDE = DH + 8;
-  constexpr int WKEYS = SPLITW ? 16 : 64;
+  constexpr int WKEYS = 64;  // keys a warp handles per tile: all of them
   constexpr int NT_S = WKEYS / 8;
   constexpr int KS_Q = DH / 16;
   constexpr int NT_O = DH / 8;
   constexpr int CHUNKS = DH / 8;  // 16-byte chunks per row
+  // Decode blocks walk few tiles and pay memory latency for each one they wait for: they keep
+  // four tiles in flight.  Prompt tiles have work to hide it behind and keep shared memory small.
+  constexpr int NSTAGE = SPLITW ? 4 : 2;
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
   bf16* sK = sQ + M * STRIDE;
-  bf16* sV = sK + 2 * KT * STRIDE;
+  bf16* sV = sK + NSTAGE * KT * STRIDE;
   __shared__ int s_pos[64];
   __shared__ float s_wm[4][16], s_wl[4][16], s_M[16], s_L[16];
 
@@ -119,44 +122,54 @@ __global__ void __launch_bounds__(128)
     cp_async16(sQ + r * STRIDE + col * 8, q + src, ok);
   }
 
+  // A tile of 64 keys lies inside one page when the page size is a multiple of 64: then one
+  // table look-up serves the whole tile and every thread's pieces sit at fixed offsets from it.
+  const bool tile_in_page = (page_size % KT) == 0;
+  constexpr int PIECES = KT * CHUNKS / 128;  // (row, 16-byte column) pieces per thread and tile
   auto load_tile = [&](int stage, int base) {
     bf16* dK = sK + stage * KT * STRIDE;
     bf16* dV = sV + stage * KT * STRIDE;
-    for (int c = tid; c < KT * CHUNKS; c += 128) {
-      const int r = c / CHUNKS, col = c % CHUNKS;
-      const int key = base + r;
-      const bool ok = key >= k_begin && key < k_end;
-      size_t src = 0;
-      if (ok) {
-        const int page = bt[key / page_size];
-        src = (static_cast<size_t>(page) * 2 * page_size + key % page_size) * kv_dim + hk * DH + col * 8;
+    const size_t v_off = static_cast<size_t>(page_size) * kv_dim;
+    if (tile_in_page) {
+      const int page = bt[base / page_size];
+      const bf16* src0 = pool + (static_cast<size_t>(page) * 2 * page_size + base % page_size) * kv_dim + hk * DH;
+#pragma unroll
+      for (int j = 0; j < PIECES; ++j) {
+        const int c = tid + j * 128;
+        const int r = c / CHUNKS, col = c % CHUNKS;
+        const int key = base + r;
+        const bool ok = key >= k_begin && key < k_end;
+        const bf16* src = ok ? src0 + static_cast<size_t>(r) * kv_dim + col * 8 : pool;
+        cp_async16(dK + r * STRIDE + col * 8, src, ok);
+        cp_async16(dV + r * STRIDE + col * 8, ok ? src + v_off : pool, ok);
       }
-      cp_async16(dK + r * STRIDE + col * 8, pool + src, ok);
-      cp_async16(dV + r * STRIDE + col * 8, pool + src + static_cast<size_t>(page_size) * kv_dim, ok);
+    } else {
+      for (int c = tid; c < KT * CHUNKS; c += 128) {
+        const int r = c / CHUNKS, col = c % CHUNKS;
+        const int key = base + r;
+        const bool ok = key >= k_begin && key < k_end;
+        size_t src = 0;
+        if (ok) {
+          const int page = bt[key / page_size];
+          src = (static_cast<size_t>(page) * 2 * page_size + key % page_size) * kv_dim + hk * DH + col * 8;
+        }
+        cp_async16(dK + r * STRIDE + col * 8, pool + src, ok);
+        cp_async16(dV + r * STRIDE + col * 8, pool + (ok ? src + v_off : 0), ok);
+      }
     }
   };
 
   const int first_tile = (k_begin / KT) * KT;
   const int n_tiles = k_end > k_begin ? (k_end - first_tile + KT - 1) / KT : 0;
-  if (n_tiles > 0) load_tile(0, first_tile);
-  cp_async_commit();
-
   const int row_base = SPLITW ? 0 : warp * 16;
-  const int key_lo = SPLITW ? warp * 16 : 0;
   const int r_lo = lane >> 2, r_hi = r_lo + 8;
   float m_lo = -CUDART_INF_F, m_hi = -CUDART_INF_F, l_lo = 0.f, l_hi = 0.f;
   float o[NT_O][4];
 #pragma unroll
   for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
-  for (int it = 0; it < n_tiles; ++it) {
-    const int stage = it & 1;
-    const int base = first_tile + it * KT;
-    if (it + 1 < n_tiles) load_tile(stage ^ 1, base + KT);
-    cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
-
+  // one tile of 64 keys against this warp's 16 rows
+  auto process_tile = [&](int stage, int base) {
     const bf16* tK = sK + stage * KT * STRIDE;
     const bf16* tV = sV + stage * KT * STRIDE;
     const int pos_lo = s_pos[row_base + r_lo], pos_hi = s_pos[row_base + r_hi];
@@ -174,25 +187,41 @@ __global__ void __launch_bounds__(128)
       for (int np = 0; np < NT_S / 2; ++np) {
         unsigned b0, b1, b2, b3;
         ldmatrix_x4(b0, b1, b2, b3,
-                    tK + (key_lo + np * 16 + (lane & 7) + (lane >> 4) * 8) * STRIDE + ks * 16 + ((lane >> 3) & 1) * 8);
+                    tK + (np * 16 + (lane & 7) + (lane >> 4) * 8) * STRIDE + ks * 16 + ((lane >> 3) & 1) * 8);
         mma_bf16(s[2 * np], a, b0, b1);
         mma_bf16(s[2 * np + 1], a, b2, b3);
       }
     }
 
-    // mask, scale, online softmax
+    // mask, scale, online softmax.  A tile that every row of the block may read in full
+    // (inside the split, before the first row's position, inside the last row's window) needs
+    // no mask.
     float mx_lo = -CUDART_INF_F, mx_hi = -CUDART_INF_F;
+    const bool full = base >= k_begin && base + KT <= k_end && base + KT - 1 <= pos_min &&
+                      (window <= 0 || base >= pos_max - window + 1);  // rows beyond the tile are never written out
+    if (full) {
 #pragma unroll
-    for (int nt = 0; nt < NT_S; ++nt) {
+      for (int nt = 0; nt < NT_S; ++nt) {
+        s[nt][0] *= scale_log2;
+        s[nt][1] *= scale_log2;
+        s[nt][2] *= scale_log2;
+        s[nt][3] *= scale_log2;
+        mx_lo = fmaxf(mx_lo, fmaxf(s[nt][0], s[nt][1]));
+        mx_hi = fmaxf(mx_hi, fmaxf(s[nt][2], s[nt][3]));
+      }
+    } else {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = base + key_lo + nt * 8 + (lane & 3) * 2 + (e & 1);
-        const int pos = (e < 2) ? pos_lo : pos_hi;
-        const int lo = window > 0 ? max(pos - window + 1, k_begin) : k_begin;
-        const bool ok = pos >= 0 && key <= pos && key >= lo && key < k_end;
-        const float v = ok ? s[nt][e] * scale_log2 : -CUDART_INF_F;
-        s[nt][e] = v;
-        if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
+      for (int nt = 0; nt < NT_S; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = base + nt * 8 + (lane & 3) * 2 + (e & 1);
+          const int pos = (e < 2) ? pos_lo : pos_hi;
+          const int lo = window > 0 ? max(pos - window + 1, k_begin) : k_begin;
+          const bool ok = pos >= 0 && key <= pos && key >= lo && key < k_end;
+          const float v = ok ? s[nt][e] * scale_log2 : -CUDART_INF_F;
+          s[nt][e] = v;
+          if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
+        }
       }
     }
     mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
@@ -237,14 +266,44 @@ __global__ void __launch_bounds__(128)
       for (int np = 0; np < NT_O / 2; ++np) {
         unsigned b0, b1, b2, b3;
         ldmatrix_x4_trans(b0, b1, b2, b3,
-                          tV + (key_lo + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + np * 16 + (lane >> 4) * 8);
+                          tV + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + np * 16 + (lane >> 4) * 8);
         mma_bf16(o[2 * np], a, b0, b1);
         mma_bf16(o[2 * np + 1], a, b2, b3);
       }
     }
-    __syncthreads();  // the other stage may be overwritten by the next iteration's loads
+  };
+
+  if constexpr (SPLITW) {
+    // decode: rounds of four tiles, requested together (one memory latency a round), one per warp
+    for (int round0 = 0; round0 < n_tiles; round0 += NSTAGE) {
+#pragma unroll
+      for (int st = 0; st < NSTAGE; ++st)
+        if (round0 + st < n_tiles) load_tile(st, first_tile + (round0 + st) * KT);
+      cp_async_commit();  // the first group also carries the Q rows
+      cp_async_wait<0>();
+      __syncthreads();
+      if (round0 + warp < n_tiles) process_tile(warp, first_tile + (round0 + warp) * KT);
+      __syncthreads();  // the tiles are overwritten by the next round
+    }
+  } else {
+#pragma unroll
+    for (int st = 0; st < NSTAGE - 1; ++st) {
+      if (st < n_tiles) load_tile(st, first_tile + st * KT);
+      cp_async_commit();  // the first group also carries the Q rows
+    }
+    for (int it = 0; it < n_tiles; ++it) {
+      const int base = first_tile + it * KT;
+      // groups so far: (NSTAGE-1) + it; tile `it` has landed when at most NSTAGE-2 newer ones are pending
+      cp_async_wait<NSTAGE - 2>();
+      __syncthreads();  // tile `it` is visible to all; everyone is done with tile it-1, whose stage is refilled now
+      if (it + NSTAGE - 1 < n_tiles) load_tile((it + NSTAGE - 1) % NSTAGE, base + (NSTAGE - 1) * KT);
+      cp_async_commit();
+      process_tile(it % NSTAGE, base);
+    }
   }
+  cp_async_commit();
   cp_async_wait<0>();
+  __syncthreads();
 
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
@@ -284,15 +343,15 @@ __global__ void __launch_bounds__(128)
       }
     }
   } else {
-    // merge the four warps (each saw a quarter of the keys) through shared memory
-    float* sO = reinterpret_cast<float*>(sK);  // [16][DH], K/V tiles are no longer needed
+    // merge the four warps (each saw a quarter of the tiles) through shared memory
+    constexpr int SO = DH + 4;                 // padded row: rows g and g+1 fall into different banks
+    float* sO = reinterpret_cast<float*>(sK);  // [4 warps][16][SO], K/V tiles are no longer needed
     if ((lane & 3) == 0) {
       s_wm[warp][r_lo] = m_lo;
       s_wm[warp][r_hi] = m_hi;
       s_wl[warp][r_lo] = l_lo;
       s_wl[warp][r_hi] = l_hi;
     }
-    for (int i = tid; i < 16 * DH; i += 128) sO[i] = 0.f;
     __syncthreads();
     if (tid < 16) {
       float mm = -CUDART_INF_F;
@@ -308,30 +367,76 @@ __global__ void __launch_bounds__(128)
       const float mu_lo = (s_M[r_lo] == -CUDART_INF_F) ? 0.f : s_M[r_lo];
       const float mu_hi = (s_M[r_hi] == -CUDART_INF_F) ? 0.f : s_M[r_hi];
       const float f_lo = exp2f(m_lo - mu_lo), f_hi = exp2f(m_hi - mu_hi);
+      float* mine = sO + warp * 16 * SO;
 #pragma unroll
       for (int nt = 0; nt < NT_O; ++nt) {
         const int d = nt * 8 + (lane & 3) * 2;
-        atomicAdd(sO + r_lo * DH + d, o[nt][0] * f_lo);
-        atomicAdd(sO + r_lo * DH + d + 1, o[nt][1] * f_lo);
-        atomicAdd(sO + r_hi * DH + d, o[nt][2] * f_hi);
-        atomicAdd(sO + r_hi * DH + d + 1, o[nt][3] * f_hi);
+        *reinterpret_cast<float2*>(mine + r_lo * SO + d) = make_float2(o[nt][0] * f_lo, o[nt][1] * f_lo);
+        *reinterpret_cast<float2*>(mine + r_hi * SO + d) = make_float2(o[nt][2] * f_hi, o[nt][3] * f_hi);
       }
     }
     __syncthreads();
     for (int i = tid; i < n_rows * DH; i += 128) {
       const int r = i / DH, d = i % DH;
       const int t = tok0 + r / G, hq = hk * G + r % G;
+      const float sum = (sO[r * SO + d] + sO[(16 + r) * SO + d]) + (sO[(32 + r) * SO + d] + sO[(48 + r) * SO + d]);
       if (n_splits == 1) {
         const float l = s_L[r];
-        out[(static_cast<size_t>(t) * Hq + hq) * DH + d] = __float2bfloat16_rn(l > 0.f ? sO[i] / l : 0.f);
+        out[(static_cast<size_t>(t) * Hq + hq) * DH + d] = __float2bfloat16_rn(l > 0.f ? sum / l : 0.f);
       } else {
         const size_t pi = (static_cast<size_t>(t) * Hq + hq) * n_splits + z;
-        part_o[pi * DH + d] = sO[i];
+        part_o[pi * DH + d] = sum;
         if (d == 0) {
           part_ml[pi * 2] = s_M[r] * kLn2;
           part_ml[pi * 2 + 1] = s_L[r];
         }
       }
+    }
+  }
+
+  // With a counter the block that finishes a tile's last key split merges all of them, so no
+  // second launch is needed.  The counter returns to zero for the next use.
+  if (n_splits > 1 && split_counter != nullptr) {
+    __shared__ int s_last;
+    __shared__ float s_w[4][64];
+    __threadfence();
+    __syncthreads();
+    int* counter = split_counter + static_cast<size_t>(blockIdx.x) * gridDim.y + hk;
+    if (tid == 0) s_last = (atomicAdd(counter, 1) == n_splits - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (tid == 0) *counter = 0;
+    for (int r = warp; r < n_rows; r += 4) {
+      const int t = tok0 + r / G, hq = hk * G + r % G;
+      const size_t row = static_cast<size_t>(t) * Hq + hq;
+      const float* ml = part_ml + row * n_splits * 2;
+      float mx = -CUDART_INF_F;
+      for (int zz = lane; zz < n_splits; zz += 32)
+        if (__ldcg(ml + 2 * zz + 1) > 0.f) mx = fmaxf(mx, __ldcg(ml + 2 * zz));
+      mx = warp_max(mx);
+      float tot = 0.f;
+      for (int zz = lane; zz < n_splits; zz += 32) {
+        const float l = __ldcg(ml + 2 * zz + 1);
+        const float wz = l > 0.f ? expf(__ldcg(ml + 2 * zz) - mx) : 0.f;
+        s_w[warp][zz] = wz;
+        tot += wz * l;
+      }
+      tot = warp_sum(tot);
+      __syncwarp();
+      const float inv = tot > 0.f ? 1.f / tot : 0.f;
+      const float* po = part_o + row * n_splits * DH;
+      for (int d = lane; d < DH; d += 32) {
+        float a0 = 0.f, a1 = 0.f;
+        int zz = 0;
+        for (; zz + 2 <= n_splits; zz += 2) {
+          a0 += s_w[warp][zz] * __ldcg(po + static_cast<size_t>(zz) * DH + d);
+          a1 += s_w[warp][zz + 1] * __ldcg(po + static_cast<size_t>(zz + 1) * DH + d);
+        }
+        if (zz < n_splits) a0 += s_w[warp][zz] * __ldcg(po + static_cast<size_t>(zz) * DH + d);
+        out[row * DH + d] = __float2bfloat16_rn((a0 + a1) * inv);
+      }
+      __syncwarp();
     }
   }
 }
@@ -383,9 +488,10 @@ template <int DH, bool SPLITW>
 int launch_flash(const void* q, const void* pool, const int* block_table, int max_blocks,
                  const int* positions, const int* cu, void* out, float* part_o, float* part_ml,
                  float scale, int window, int split_len, int n_splits, int page_size, int n_seq,
-                 int n_tiles, int Hq, int Hkv, cudaStream_t stream) {
+                 int n_tiles, int Hq, int Hkv, int* split_counter, cudaStream_t stream) {
   constexpr int M = SPLITW ? 16 : 64;
-  const size_t smem = static_cast<size_t>(M + 4 * kFlashKeys) * (DH + 8) * sizeof(bf16);
+  constexpr int NSTAGE = SPLITW ? 4 : 2;
+  const size_t smem = static_cast<size_t>(M + 2 * NSTAGE * kFlashKeys) * (DH + 8) * sizeof(bf16);
   auto kern = flash_paged_kernel<DH, SPLITW>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -396,7 +502,7 @@ int launch_flash(const void* q, const void* pool, const int* block_table, int ma
   kern<<<grid, 128, smem, stream>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(pool),
                                     block_table, max_blocks, positions, cu, static_cast<bf16*>(out),
                                     part_o, part_ml, scale * 1.4426950408889634f, window, split_len,
-                                    n_splits, page_size, n_seq, Hq, Hkv);
+                                    n_splits, page_size, n_seq, Hq, Hkv, split_counter);
   return launch_status();
 }
 
@@ -411,27 +517,32 @@ PMM_EXPORT int pmm_flash_supported(int Hq, int Hkv, int Dh) {
 
 // n_tiles: number of row tiles = sum over sequences of ceil(new tokens / (M / G)), with
 // M = 16 when rows16 != 0 (every sequence brings at most 16/G tokens) else 64.
+// split_counter: nullptr (the caller merges key splits with pmm_flash_combine), or
+// n_tiles*Hkv ints that are zero between calls: then the last block of every tile merges
+// its splits (at most 64 of them) and writes `out` itself.
 PMM_EXPORT int pmm_flash_paged_attention(const void* q, const void* pool, const int* block_table,
                                          int max_blocks, const int* positions, const int* cu,
                                          void* out, float* part_o, float* part_ml, float scale,
                                          int window, int split_len, int n_splits, int page_size,
                                          int n_seq, int n_tiles, int rows16, int Hq, int Hkv, int Dh,
-                                         cudaStream_t stream) {
+                                         int* split_counter, cudaStream_t stream) {
   if (n_seq <= 0 || n_tiles <= 0) return 0;
   if (!pmm_flash_supported(Hq, Hkv, Dh) || page_size <= 0 || n_splits < 1 || n_splits > 65535 ||
       Hkv > 65535)
     return PMM_ERR_BAD_ARGUMENT;
   if (rows16 && Hq / Hkv > 16) return PMM_ERR_BAD_ARGUMENT;
   if (n_splits > 1 && (!part_o || !part_ml || split_len <= 0)) return PMM_ERR_BAD_ARGUMENT;
+  if (split_counter && n_splits > 64) return PMM_ERR_BAD_ARGUMENT;
   if (n_splits == 1) split_len = 0x40000000;
   int rc;
 #define PMM_FLASH_CASE(DH)                                                                          \
   rc = rows16 ? pmm::launch_flash<DH, true>(q, pool, block_table, max_blocks, positions, cu, out,   \
                                             part_o, part_ml, scale, window, split_len, n_splits,    \
-                                            page_size, n_seq, n_tiles, Hq, Hkv, stream)             \
+                                            page_size, n_seq, n_tiles, Hq, Hkv, split_counter,      \
+                                            stream)                                                 \
               : pmm::launch_flash<DH, false>(q, pool, block_table, max_blocks, positions, cu, out,  \
                                              part_o, part_ml, scale, window, split_len, n_splits,   \
-                                             page_size, n_seq, n_tiles, Hq, Hkv, stream)
+                                             page_size, n_seq, n_tiles, Hq, Hkv, split_counter, stream)
   switch (Dh) {
     case 16: PMM_FLASH_CASE(16); break;
     case 32: PMM_FLASH_CASE(32); break;

@@ -12,7 +12,7 @@
 //                       share one launch: the mixers' output projections).
 // Tensor-core form: the weights are the 16-row MMA operand (A), the tokens the 8-column one
 // (B), mma.sync m16n8k16 with float accumulation.  A block of 8 warps owns 32 weight rows;
-// W arrives in chunks of 256 columns through a 4-stage cp.async pipeline (16 KB a stage,
+// W arrives in chunks of 256 columns through a 5-stage cp.async pipeline (16 KB a stage,
 // every thread copies the same four 16-byte pieces of each chunk, so the addresses are made
 // once); warps split a chunk 2 (rows) x 4 (columns) and the column quarters are added at the end.
 // (reference: linear layers are cublasSgemm calls, src/ops/gpu/linear.cu:3-21, the
@@ -25,7 +25,7 @@ using bf16 = __nv_bfloat16;
 
 constexpr int kSgRows = 32;     // weight rows per block
 constexpr int kSgChunk = 256;   // columns per pipeline stage
-constexpr int kSgStages = 4;
+constexpr int kSgStages = 5;    // K = 1024 is four chunks: all of a block's weights are requested at once
 constexpr int kSgWStride = kSgChunk + 8;
 constexpr int kSgThreads = 256;
 constexpr int kSgPieces = kSgRows * (kSgChunk / 8) / kSgThreads;  // 16-byte pieces per thread and chunk
@@ -89,6 +89,7 @@ __global__ void __launch_bounds__(kSgThreads) skinny_gemm_kernel(const SkinnyArg
   bf16* sW = reinterpret_cast<bf16*>(smem_raw);                   // [stages][32][264]
   bf16* sX = sW + kSgStages * kSgRows * kSgWStride;               // [MP][xs]
   float* sRed = reinterpret_cast<float*>(sX + MP * xs);           // [3][32][MP] column quarters, then up rows
+  float* sNw = sRed + 3 * 32 * MP;                                // [kx] norm weights of the slice (norm prologue)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int M = args.M;
@@ -127,12 +128,17 @@ __global__ void __launch_bounds__(kSgThreads) skinny_gemm_kernel(const SkinnyArg
     }
   };
 
-  // group 0: the activations when they are read as bfloat16 (empty for the norm prologue)
+  // group 0: the activations when they are read as bfloat16, else the norm weights
   if (pr.h_in == nullptr) {
     for (int i = tid; i < MP * (kx / 8); i += kSgThreads) {
       const int m = i / (kx / 8), k = k0 + (i % (kx / 8)) * 8;
       const bool ok = m < M && k < k1;
       sg_cp16(sX + m * xs + (k - k0), pr.x + (ok ? static_cast<size_t>(m) * pr.ldx + k : 0), ok);
+    }
+  } else {
+    for (int i = tid; i < kx / 4; i += kSgThreads) {
+      const int k = k0 + i * 4;
+      sg_cp16(sNw + i * 4, pr.norm_w + (k < k1 ? k : 0), k < k1);
     }
   }
   sg_commit();
@@ -175,6 +181,8 @@ __global__ void __launch_bounds__(kSgThreads) skinny_gemm_kernel(const SkinnyArg
         ss = warp_sum(ss);
         inv[j] = 1.0f / sqrtf(ss / static_cast<float>(K) + pr.eps);
       }
+      sg_wait<kSgStages - 1>();  // group 0 (this thread's share of the norm weights) has landed
+      __syncthreads();           // ... and everyone else's; every warp walks this loop equally often
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int m = m0 + j;
@@ -188,7 +196,7 @@ __global__ void __launch_bounds__(kSgThreads) skinny_gemm_kernel(const SkinnyArg
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (m < M && k < k1) {
               v = (K <= kPass && k0 == 0) ? keep[j][i] : *reinterpret_cast<const float4*>(row + k);
-              const float4 w4 = *reinterpret_cast<const float4*>(pr.norm_w + k);
+              const float4 w4 = *reinterpret_cast<const float4*>(sNw + (k - k0));
               v.x = v.x * inv[j] * w4.x;
               v.y = v.y * inv[j] * w4.y;
               v.z = v.z * inv[j] * w4.z;
@@ -312,7 +320,8 @@ int launch_skinny(const SkinnyArgs& a, int k_max, cudaStream_t stream) {
   constexpr int MP = MT * 8;
   const int kx = (min(a.k_slice, k_max) + kSgChunk - 1) / kSgChunk * kSgChunk;
   const size_t smem = static_cast<size_t>(kSgStages) * kSgRows * kSgWStride * sizeof(bf16) +
-                      static_cast<size_t>(MP) * (kx + 8) * sizeof(bf16) + 3 * 32 * MP * sizeof(float);
+                      static_cast<size_t>(MP) * (kx + 8) * sizeof(bf16) + 3 * 32 * MP * sizeof(float) +
+                      static_cast<size_t>(kx) * sizeof(float);
   if (smem > 220 * 1024) return PMM_ERR_BAD_ARGUMENT;
   auto kern = skinny_gemm_kernel<MT, MODE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));

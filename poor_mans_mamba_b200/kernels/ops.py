@@ -58,7 +58,7 @@ _SIGNATURES = {
     "pmm_flash_supported": [c_int, c_int, c_int],
     "pmm_flash_paged_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
-                                  c_int, c_int, c_int, c_int, c_void_p],
+                                  c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "pmm_flash_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_skinny_gemm": [c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_int,
                         c_float, c_void_p, c_longlong, c_void_p, c_int, c_float, c_void_p, c_longlong, c_void_p,
@@ -483,10 +483,13 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
                     out: Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int, softmax_scale: float,
                     window: int = 0, n_splits: int = 1, split_len: int = 0,
                     scratch: Optional[Tensor] = None, cu_seqlens: Optional[Tensor] = None,
-                    new_lens: Optional[Sequence[int]] = None, use_tensor_cores: bool = True) -> None:
+                    new_lens: Optional[Sequence[int]] = None, use_tensor_cores: bool = True,
+                    split_counter: Optional[Tensor] = None) -> None:
     """Causal attention of every token over keys lo..pos of its request in the paged cache.
     With ``cu_seqlens`` and ``new_lens`` (tokens per sequence, host values) a bfloat16 cache of a
-    supported shape goes to the tensor-core kernel; everything else to the float kernel."""
+    supported shape goes to the tensor-core kernel; everything else to the float kernel.
+    ``split_counter`` (int32, zero between calls, at least tiles x kv heads entries) lets the
+    tensor-core kernel merge its key splits itself instead of in a second launch."""
     _cuda(q, pool, block_table, positions, seq_of, out, scratch, cu_seqlens)
     check_head_dim(head_dim)
     T = q.shape[0]
@@ -515,10 +518,17 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
         rows16 = group <= 16 and max(new_lens) * group <= 16
         tokens_per_tile = (16 if rows16 else 64) // group
         n_tiles = sum((n + tokens_per_tile - 1) // tokens_per_tile for n in new_lens)
+        counter = None
+        if (split_counter is not None and 1 < n_splits <= 64 and split_counter.numel() >= n_tiles * n_kv_heads):
+            _cuda(split_counter)
+            _i32(split_counter, "attention: split_counter")
+            counter = split_counter.data_ptr()
         _call("pmm_flash_paged_attention", q.data_ptr(), pool.data_ptr(), block_table.data_ptr(),
               block_table.shape[1], positions.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(), part_o,
               part_ml, float(softmax_scale), int(window), int(split_len), int(n_splits), pool.shape[2],
-              len(new_lens), n_tiles, int(rows16), n_q_heads, n_kv_heads, head_dim, _stream())
+              len(new_lens), n_tiles, int(rows16), n_q_heads, n_kv_heads, head_dim, counter, _stream())
+        if counter is not None:
+            return
     else:
         _call("pmm_paged_attention", q.data_ptr(), pool.data_ptr(), block_table.data_ptr(),
               block_table.shape[1], positions.data_ptr(), seq_of.data_ptr(), out.data_ptr(), part_o, part_ml,
@@ -543,7 +553,7 @@ def skinny_fits(M: int, K: int) -> bool:
     (the products that cannot split K keep the whole row block resident)."""
     mp = 16 if M <= 16 else 32 if M <= 32 else 64
     kx = (K + 255) // 256 * 256
-    return M <= 64 and 4 * 32 * 264 * 2 + mp * (kx + 8) * 2 + 3 * 32 * mp * 4 <= 220 * 1024
+    return M <= 64 and 5 * 32 * 264 * 2 + mp * (kx + 8) * 2 + 3 * 32 * mp * 4 + kx * 4 <= 220 * 1024
 
 
 def skinny_linear_norm(h: Tensor, norm_weight: Tensor, eps: float, weight: Tensor, out: Tensor) -> None:

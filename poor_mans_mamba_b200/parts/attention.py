@@ -72,6 +72,8 @@ class PagedAttention(Mixer):
 
     def finalize(self, dtype: torch.dtype, device: torch.device) -> None:
         self.position_encoding.finalize(dtype, device)
+        # tickets of the key splits (zero between steps): the last block of a tile merges them
+        self._split_counter = torch.zeros(4096, dtype=torch.int32, device=device) if device.type == "cuda" else None
 
     # -- shared input projection
     def input_rows(self) -> int:
@@ -136,7 +138,8 @@ class PagedAttention(Mixer):
         K.paged_attention(q_rot, kv.pool, kv.block_table, ctx.positions, ctx.seq_of, attn, self.num_heads,
                           self.num_kv_heads, self.head_dim, 1.0 / math.sqrt(float(self.head_dim)),
                           window=self.window, n_splits=n_splits, split_len=split_len, scratch=scratch,
-                          cu_seqlens=ctx.cu_seqlens, new_lens=ctx.new_lens)
+                          cu_seqlens=ctx.cu_seqlens, new_lens=ctx.new_lens,
+                          split_counter=getattr(self, "_split_counter", None))
         return attn
 
     def plan_splits(self, new_lens, kv_len_bound: int, dtype: torch.dtype):
@@ -148,8 +151,8 @@ class PagedAttention(Mixer):
             per_tile = rows // group
             blocks = sum((n + per_tile - 1) // per_tile for n in new_lens) * self.num_kv_heads
             min_len = 256 if rows == 16 else 64
-            # small decode blocks: two per SM; 64-row prompt tiles: one wave is enough
-            target = _TARGET_BLOCKS // 2 if rows == 16 else _TARGET_BLOCKS // 4
+            # about two blocks per SM: few warps per block, and causal tiles differ in length
+            target = _TARGET_BLOCKS // 2
         else:
             blocks = sum(new_lens) * ((self.num_heads + 3) // 4)
             min_len = 128

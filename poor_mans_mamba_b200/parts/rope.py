@@ -37,6 +37,9 @@ class NoPositionEncoding(PositionEncoding):
     """Queries and keys are used as projected."""
     inv_freq = None
 
+    def __init__(self, head_dim: int = 0):
+        self.head_dim = int(head_dim)
+
 
 register_position_encoding("rotary", RotaryEncoding)
 register_position_encoding("none", NoPositionEncoding)

@@ -112,3 +112,18 @@ def test_model_spec_is_data_taken_from_the_config():
     assert layer.mixers[1].params["position_encoding"] == {"kind": "rotary", "theta": 1e11}
     assert layer.mixer_norm.params["eps"] == 1e-6
     assert model_spec(FalconH1Config.from_dict(tiny_config("A"))).head_name is None
+
+
+def test_parts_are_built_from_specs_by_name():
+    from poor_mans_mamba_b200.parts import PartSpec, build_part, registered
+    assert {"mamba2", "paged_attention"} <= set(registered("mixer"))
+    assert {"rotary", "none"} <= set(registered("position_encoding"))
+    plain = build_part("mixer", PartSpec("paged_attention", "attn", {"num_heads": 4, "num_kv_heads": 2, "head_dim": 32}),
+                       hidden_size=64)
+    assert plain.position_encoding.inv_freq is None and plain.input_rows() == (4 + 2 * 2) * 32
+    assert [s.name for s in plain.state_specs()] == ["kv"] and plain.state_specs()[0].width == 64
+    shared = build_part("mixer", PartSpec("paged_attention", "attn", {"num_heads": 4, "num_kv_heads": 2, "head_dim": 32,
+                                                                      "shared_kv": True}), hidden_size=64)
+    assert shared.state_specs() == [] and [p.name for p in shared.param_specs()] == ["q_proj.weight", "o_proj.weight"]
+    with pytest.raises(KeyError, match="unknown mixer"):
+        build_part("mixer", PartSpec("nope", "x", {}), hidden_size=8)

@@ -227,7 +227,7 @@ def test_gated_norm(dtype, mode):
 
 
 def _attention_case(dtype, Hq, Hkv, Dh, page_size, lens_steps, window=0, planted=True, n_splits=1, theta=1e4, seed=0,
-                    tensor_cores=True):
+                    tensor_cores=True, fused_merge=False):
     """Runs qkv_rope_store + paged_attention over a script of portions with scattered pages and
     compares with the plain rope + causal attention on the whole sequences."""
     g = torch.Generator().manual_seed(seed)
@@ -274,6 +274,7 @@ def _attention_case(dtype, Hq, Hkv, Dh, page_size, lens_steps, window=0, planted
     pool[n_pages].fill_(float("nan"))  # the spare page must never be read for a real key
     tables = [[] for _ in lens]
     got = [torch.empty(n, qd, dtype=dtype) for n in lens]
+    counter = torch.zeros(1024, dtype=torch.int32, device=DEV)
     for seqs in _batch(lens_steps):
         T = sum(n for _, _, n in seqs)
         for i, a, n in seqs:
@@ -309,7 +310,8 @@ def _attention_case(dtype, Hq, Hkv, Dh, page_size, lens_steps, window=0, planted
             cu.append(cu[-1] + n)
         ops.paged_attention(q_rot, pool, bt.to(DEV), i32(pos), i32(seq_of), out, Hq, Hkv, Dh, 1.0 / math.sqrt(Dh),
                             window=window, n_splits=ns, split_len=split_len, scratch=scratch, cu_seqlens=i32(cu),
-                            new_lens=[n for _, _, n in seqs], use_tensor_cores=tensor_cores)
+                            new_lens=[n for _, _, n in seqs], use_tensor_cores=tensor_cores,
+                            split_counter=counter if fused_merge else None)
         t0 = 0
         for i, a, n in seqs:
             got[i][a:a + n] = out[t0:t0 + n].cpu()
@@ -336,6 +338,10 @@ def test_paged_attention_split_keys(dtype, tensor_cores):
     _attention_case(dtype, 8, 2, 64, 16, steps, n_splits=4, seed=5, tensor_cores=tensor_cores)
     _attention_case(dtype, 3, 1, 80, 32, steps, n_splits=7, seed=6, tensor_cores=tensor_cores)
     _attention_case(dtype, 6, 2, 128, 64, steps, n_splits=5, seed=7, tensor_cores=tensor_cores)
+    if tensor_cores:  # the last block of every tile merges the splits (counter returns to zero each step)
+        _attention_case(dtype, 8, 2, 64, 64, steps, n_splits=4, seed=5, fused_merge=True)
+        _attention_case(dtype, 6, 2, 128, 16, steps, n_splits=9, seed=8, fused_merge=True)
+        _attention_case(dtype, 4, 2, 32, 16, [[40, 1, 1, 30], [5, 1, 60]], window=24, n_splits=3, seed=9, fused_merge=True)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -63,6 +63,9 @@ _SIGNATURES = {
     "pmm_skinny_gemm": [c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_int,
                         c_float, c_void_p, c_longlong, c_void_p, c_int, c_float, c_void_p, c_longlong, c_void_p,
                         c_int, c_void_p],
+    "pmm_tc_gemm_supported": [c_int, c_int, c_int, c_longlong, c_longlong],
+    "pmm_tc_gemm": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_float,
+                    c_void_p, c_void_p],
     "pmm_silu_mul": [c_void_p, c_longlong, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
     "pmm_add_row_bias": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "pmm_sample_rows": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
@@ -613,6 +616,58 @@ def skinny_residual(h: Tensor, products: Sequence[Tuple[Tensor, Tensor, float]])
     a1 = args[1] if len(args) > 1 else (None, 0, None, 0, 0.0)
     _call("pmm_skinny_gemm", 2, M, N, a0[0], a0[1], None, None, 0.0, a0[2], a0[3], a0[4], a1[0], a1[1], a1[2], a1[3],
           a1[4], None, 0, h.data_ptr(), k_split, _stream())
+
+
+_TC_STATUS = {}
+
+
+def _tc_status(device: torch.device) -> Tensor:
+    t = _TC_STATUS.get(device)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _TC_STATUS[device] = t
+    return t
+
+
+def tc_gemm_status(device) -> int:
+    """0 unless a bounded wait inside a tensor-core product gave up (1 producer, 2 MMA issuer,
+    3 epilogue).  Reading it waits for the device."""
+    return int(_tc_status(torch.device(device)).item())
+
+
+def tc_gemm_supported(x: Tensor, weight: Tensor, n_out: int, swiglu: bool) -> bool:
+    """Whether the tcgen05 product takes these operands (bfloat16, K a multiple of 64, output
+    columns a multiple of 64 for SwiGLU or 128 otherwise, 16-byte aligned rows)."""
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or not x.is_cuda:
+        return False
+    if x.dim() != 2 or x.stride(1) != 1 or not weight.is_contiguous() or x.data_ptr() % 16 or weight.data_ptr() % 16:
+        return False
+    return bool(_fn("pmm_tc_gemm_supported")(1 if swiglu else 0, x.shape[1], n_out, x.stride(0), n_out))
+
+
+def tc_gemm_swiglu(x: Tensor, gate_up: Tensor, gate_mult: float, out: Tensor) -> None:
+    """out[T, F] = silu((x Wg^T) * gate_mult) * (x Wu^T), gate_up = [Wg; Wu]: one tcgen05 kernel
+    (TMA operands, accumulator in tensor memory, activation in the epilogue)."""
+    _cuda(x, gate_up, out)
+    T, K = x.shape
+    F = gate_up.shape[0] // 2
+    _need(gate_up.shape == (2 * F, K) and out.shape == (T, F) and out.is_contiguous() and out.dtype == torch.bfloat16,
+          "tc_gemm_swiglu: out must be contiguous bfloat16 [T, F] for gate_up [2F, K]")
+    _need(tc_gemm_supported(x, gate_up, F, True), "tc_gemm_swiglu: sizes or alignment outside what the kernel takes")
+    _call("pmm_tc_gemm", 1, x.data_ptr(), x.stride(0), gate_up.data_ptr(), out.data_ptr(), out.stride(0), T, K, F,
+          float(gate_mult), _tc_status(x.device).data_ptr(), _stream())
+
+
+def tc_gemm(x: Tensor, weight: Tensor, out: Tensor) -> None:
+    """out[T, N] = x @ weight^T on tcgen05 (bfloat16 in and out, float accumulation)."""
+    _cuda(x, weight, out)
+    T, K = x.shape
+    N = weight.shape[0]
+    _need(weight.shape == (N, K) and out.shape == (T, N) and out.stride(1) == 1 and out.dtype == torch.bfloat16
+          and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0, "tc_gemm: out must be bfloat16 [T, N], rows 16-byte aligned")
+    _need(tc_gemm_supported(x, weight, N, False), "tc_gemm: sizes or alignment outside what the kernel takes")
+    _call("pmm_tc_gemm", 0, x.data_ptr(), x.stride(0), weight.data_ptr(), out.data_ptr(), out.stride(0), T, K, N,
+          1.0, _tc_status(x.device).data_ptr(), _stream())
 
 
 def silu_mul(gate_up: Tensor, gate_mult: float, out: Tensor) -> None:

@@ -7,6 +7,7 @@ stacked into one [2F, D] matrix at load so the two projections are one product.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -15,6 +16,14 @@ from ..kernels import ops as K
 from .base import FeedForward, ParamSpec, register_feed_forward
 
 Tensor = torch.Tensor
+
+# The fused tcgen05 kernel (gate/up projection with the activation in its epilogue) is correct
+# and tested but, with 128 x 128 tiles fed by one block, bound by the L2-to-SM operand rate
+# (about 360-690 TFLOP/s measured against the library's 960-1460 on the same shapes), so the
+# library product plus the activation kernel stays the default until the two-block 256 x 256
+# form exists.  PMM_TCGEN05_FFN=1 switches it on for portions of at least this many tokens.
+_TC_FROM_TOKENS = 128
+_TC_ENABLED = os.environ.get("PMM_TCGEN05_FFN", "0") == "1"
 
 
 class SwiGLU(FeedForward):
@@ -39,10 +48,15 @@ class SwiGLU(FeedForward):
     def forward(self, x: Tensor, ctx, out: Tensor) -> None:
         T = x.shape[0]
         f = self.intermediate_size
-        gu = ctx.workspace.alloc((T, 2 * f), x.dtype)
-        K.linear(x, self.gate_up, gu)
         act = ctx.workspace.alloc((T, f), x.dtype)
-        K.silu_mul(gu, self.gate_multiplier, act)
+        if _TC_ENABLED and T >= _TC_FROM_TOKENS and K.tc_gemm_supported(x, self.gate_up, f, True):
+            # prompt portions in bfloat16: gate and up projection with the activation in the
+            # epilogue of one tcgen05 kernel; the [T, 2F] intermediate is never written
+            K.tc_gemm_swiglu(x, self.gate_up, self.gate_multiplier, act)
+        else:
+            gu = ctx.workspace.alloc((T, 2 * f), x.dtype)
+            K.linear(x, self.gate_up, gu)
+            K.silu_mul(gu, self.gate_multiplier, act)
         K.linear(act, self.down, out)
 
 

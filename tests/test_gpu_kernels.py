@@ -479,3 +479,28 @@ def test_skinny_gemm_modes(M, N, Kd):
     ops.skinny_residual(hd, [(xa.to(DEV), wa.to(DEV), -0.3), (xb.to(DEV), wb.to(DEV), 1.1)])
     ref2 = ref1 - 0.3 * (xa.double() @ wa.double().t()) + 1.1 * (xb.double() @ wb.double().t())
     close(hd, ref2, torch.float32, scale=30.0, what="skinny residual two products")
+
+
+@pytest.mark.parametrize("T,Kd,F", [(200, 128, 192), (128, 64, 64), (2048, 1024, 2048), (333, 1024, 448)])
+def test_tcgen05_gemm_swiglu_and_plain(T, Kd, F):
+    """The tcgen05 / TMA / tensor-memory product: SwiGLU epilogue and plain store, token counts
+    that are no multiple of the 128-row tile, several K stages (more than the pipeline is deep)."""
+    g = torch.Generator().manual_seed(T + Kd + F)
+    ops = K()
+    bf = torch.bfloat16
+    x = (torch.randn(T, Kd, generator=g)).to(bf)
+    w = (torch.randn(2 * F, Kd, generator=g) * 0.05).to(bf)
+    assert ops.tc_gemm_supported(x.to(DEV), w.to(DEV), F, True)
+    act = torch.full((T, F), float("nan"), dtype=bf, device=DEV)
+    ops.tc_gemm_swiglu(x.to(DEV), w.to(DEV), 1.5, act)
+    torch.cuda.synchronize()
+    assert ops.tc_gemm_status(DEV) == 0
+    gu = x.double() @ w.double().t()
+    close(act, P.silu(gu[:, :F] * 1.5) * gu[:, F:], bf, what="tcgen05 swiglu")
+    if (2 * F) % 128 == 0:
+        y = torch.full((T, 2 * F), float("nan"), dtype=bf, device=DEV)
+        ops.tc_gemm(x.to(DEV), w.to(DEV), y)
+        torch.cuda.synchronize()
+        assert ops.tc_gemm_status(DEV) == 0
+        close(y, gu, bf, what="tcgen05 plain")
+    assert not ops.tc_gemm_supported(x.to(DEV)[:, :Kd - 8], w.to(DEV), F, True)  # K no multiple of 64

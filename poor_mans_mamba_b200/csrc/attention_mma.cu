@@ -88,6 +88,8 @@ __global__ void __launch_bounds__(128)
   __shared__ int s_pos[64];
   __shared__ float s_wm[4][16], s_wl[4][16], s_M[16], s_L[16];
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = Hq / Hkv;
   const int tpt = M / G;  // tokens per tile (host guarantees G <= M)
@@ -450,6 +452,8 @@ __global__ void __launch_bounds__(128)
                          S* __restrict__ out, int n_splits, int Dh) {
   extern __shared__ float w[];  // n_splits weights
   __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t row = blockIdx.x;
   const float* ml = part_ml + row * n_splits * 2;
   float mx = -CUDART_INF_F;
@@ -499,10 +503,9 @@ int launch_flash(const void* q, const void* pool, const int* block_table, int ma
     if (e != cudaSuccess) return static_cast<int>(e);
   }
   dim3 grid(n_tiles, Hkv, n_splits);
-  kern<<<grid, 128, smem, stream>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(pool),
-                                    block_table, max_blocks, positions, cu, static_cast<bf16*>(out),
-                                    part_o, part_ml, scale * 1.4426950408889634f, window, split_len,
-                                    n_splits, page_size, n_seq, Hq, Hkv, split_counter);
+  launch_pdl(kern, grid, dim3(128), smem, stream, static_cast<const bf16*>(q), static_cast<const bf16*>(pool),
+             block_table, max_blocks, positions, cu, static_cast<bf16*>(out), part_o, part_ml,
+             scale * 1.4426950408889634f, window, split_len, n_splits, page_size, n_seq, Hq, Hkv, split_counter);
   return launch_status();
 }
 
@@ -561,7 +564,7 @@ PMM_EXPORT int pmm_flash_combine(const float* part_o, const float* part_ml, void
   if (n_splits < 1 || Dh <= 0) return PMM_ERR_BAD_ARGUMENT;
   const size_t smem = static_cast<size_t>(n_splits) * sizeof(float);
   if (smem > 48 * 1024) return PMM_ERR_BAD_ARGUMENT;
-  PMM_DISPATCH_DTYPE(dtype, S, pmm::flash_combine_kernel<S><<<n_rows, 128, smem, stream>>>(
-                                   part_o, part_ml, static_cast<S*>(out), n_splits, Dh));
+  PMM_DISPATCH_DTYPE(dtype, S, pmm::launch_pdl(pmm::flash_combine_kernel<S>, dim3(n_rows), dim3(128), smem, stream,
+                                               part_o, part_ml, static_cast<S*>(out), n_splits, Dh));
   return pmm::launch_status();
 }

@@ -55,6 +55,30 @@ __device__ __forceinline__ float softplus_f(float v) {
 
 inline int launch_status() { return static_cast<int>(cudaGetLastError()); }
 
+// Programmatic dependent launch.  A kernel started with launch_pdl may begin while the kernel
+// before it on the stream is still running; pdl_wait() inside it returns once that kernel has
+// finished and its writes are visible, so everything a kernel does before pdl_wait() must not
+// touch memory that other kernels write (reading constant weights is fine).
+// pdl_launch_dependents() lets the next kernel of the stream start its own preamble early.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);  // errors surface in launch_status()
+}
+
 }  // namespace pmm
 
 // Calls FN<float>(...) or FN<__nv_bfloat16>(...) by dtype code.

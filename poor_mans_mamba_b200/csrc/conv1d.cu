@@ -87,6 +87,8 @@ __global__ void conv1d_decode_kernel(const S* __restrict__ x, long long ldx,
                                      const float* __restrict__ bias, float* __restrict__ window,
                                      const int* __restrict__ slots, S* __restrict__ y, int n_seq,
                                      int C, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   const int s = blockIdx.y;
   if (c >= C || s >= n_seq) return;
@@ -142,8 +144,8 @@ PMM_EXPORT int pmm_conv1d_decode(const void* x, long long ldx, const float* pre_
   if (n_seq <= 0) return 0;
   if (K < 2 || C <= 0 || n_seq > 65535) return PMM_ERR_BAD_ARGUMENT;
   dim3 grid((C + 127) / 128, n_seq);
-  PMM_DISPATCH_DTYPE(dtype, S, pmm::conv1d_decode_kernel<S><<<grid, 128, 0, stream>>>(
-                                   static_cast<const S*>(x), ldx, pre_scale, pre_bias, w, bias,
-                                   window, slots, static_cast<S*>(y), n_seq, C, K));
+  PMM_DISPATCH_DTYPE(dtype, S, pmm::launch_pdl(pmm::conv1d_decode_kernel<S>, grid, dim3(128), 0, stream,
+                                               static_cast<const S*>(x), ldx, pre_scale, pre_bias, w, bias,
+                                               window, slots, static_cast<S*>(y), n_seq, C, K));
   return pmm::launch_status();
 }

@@ -13,6 +13,8 @@ namespace pmm {
 template <typename S>
 __global__ void embed_kernel(float* __restrict__ out, const S* __restrict__ table,
                              const int* __restrict__ tokens, float mult, int D, int V) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   int id = tokens[t];
   const bool ok = id >= 0 && id < V;  // the host rejects such ids before launching
@@ -32,6 +34,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const S* __restrict__ 
                                    int D) {
   extern __shared__ float buf[];
   __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const size_t src = static_cast<size_t>(rows ? rows[r] : r) * D;
   float ss = 0.f;
@@ -66,9 +70,9 @@ __global__ void cast_scale_kernel(float* __restrict__ out, const S* __restrict__
 PMM_EXPORT int pmm_embed(void* out, const void* table, const int* tokens, float mult, int T, int D,
                          int V, int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
-  PMM_DISPATCH_DTYPE(dtype, S, pmm::embed_kernel<S><<<T, 256, 0, stream>>>(
-                                   static_cast<float*>(out), static_cast<const S*>(table), tokens,
-                                   mult, D, V));
+  PMM_DISPATCH_DTYPE(dtype, S, pmm::launch_pdl(pmm::embed_kernel<S>, dim3(T), dim3(256), 0, stream,
+                                               static_cast<float*>(out), static_cast<const S*>(table), tokens,
+                                               mult, D, V));
   return pmm::launch_status();
 }
 
@@ -87,9 +91,8 @@ PMM_EXPORT int pmm_add_rmsnorm(void* h, const void* a, float sa, const void* b, 
                                            static_cast<int>(smem));
       if (e != cudaSuccess) return static_cast<int>(e);
     }
-    kern<<<R, threads, smem, stream>>>(static_cast<float*>(h), static_cast<const S*>(a), sa,
-                                       static_cast<const S*>(b), sb, w, eps, static_cast<S*>(out),
-                                       rows, D);
+    pmm::launch_pdl(kern, dim3(R), dim3(threads), smem, stream, static_cast<float*>(h), static_cast<const S*>(a), sa,
+                    static_cast<const S*>(b), sb, w, eps, static_cast<S*>(out), rows, D);
   });
   return pmm::launch_status();
 }

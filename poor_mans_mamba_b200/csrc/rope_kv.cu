@@ -25,6 +25,8 @@ __global__ void qkv_rope_store_kernel(const S* __restrict__ q, long long ldq, co
                                       S* __restrict__ pool, int page_size, S* __restrict__ q_out,
                                       S* __restrict__ k_out, S* __restrict__ v_out, int Hq, int Hkv,
                                       int Dh) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const float fpos = static_cast<float>(pos);
@@ -95,12 +97,12 @@ PMM_EXPORT int pmm_qkv_rope_store(const void* q, long long ldq, const void* k, l
   if (Hkv > 0 && (!k || !v)) return PMM_ERR_BAD_ARGUMENT;
   if (Hkv == 0) pool = nullptr;
   if (pool && (!block_table || page_size <= 0)) return PMM_ERR_BAD_ARGUMENT;
-  PMM_DISPATCH_DTYPE(dtype, S, pmm::qkv_rope_store_kernel<S><<<T, 256, 0, stream>>>(
-                                   static_cast<const S*>(q), ldq, static_cast<const S*>(k), ldk,
-                                   static_cast<const S*>(v), ldv, q_scale, k_scale, v_scale,
-                                   inv_freq, positions, seq_of, block_table, max_blocks,
-                                   static_cast<S*>(pool), page_size, static_cast<S*>(q_out),
-                                   static_cast<S*>(k_out), static_cast<S*>(v_out), Hq, Hkv, Dh));
+  PMM_DISPATCH_DTYPE(dtype, S, pmm::launch_pdl(pmm::qkv_rope_store_kernel<S>, dim3(T), dim3(256), 0, stream,
+                                               static_cast<const S*>(q), ldq, static_cast<const S*>(k), ldk,
+                                               static_cast<const S*>(v), ldv, q_scale, k_scale, v_scale,
+                                               inv_freq, positions, seq_of, block_table, max_blocks,
+                                               static_cast<S*>(pool), page_size, static_cast<S*>(q_out),
+                                               static_cast<S*>(k_out), static_cast<S*>(v_out), Hq, Hkv, Dh));
   return pmm::launch_status();
 }
 

@@ -30,6 +30,8 @@ __global__ void sample_rows_kernel(const float* __restrict__ logits, long long l
                                    const int* __restrict__ steps, int* __restrict__ out, int V) {
   __shared__ float best_v[32];
   __shared__ int best_i[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* row = logits + static_cast<long long>(r) * ld;
   const float temp = temperature ? temperature[r] : 0.f;
@@ -98,6 +100,7 @@ PMM_EXPORT int pmm_sample_rows(const float* logits, long long ld, const float* t
                                cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (V <= 0) return PMM_ERR_BAD_ARGUMENT;
-  pmm::sample_rows_kernel<<<n_rows, 1024, 0, stream>>>(logits, ld, temperature, seeds, steps, out, V);
+  pmm::launch_pdl(pmm::sample_rows_kernel, dim3(n_rows), dim3(1024), 0, stream, logits, ld, temperature, seeds, steps,
+                  out, V);
   return pmm::launch_status();
 }

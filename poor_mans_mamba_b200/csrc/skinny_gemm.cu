@@ -91,6 +91,7 @@ __global__ void __launch_bounds__(kSgThreads) skinny_gemm_kernel(const SkinnyArg
   float* sRed = reinterpret_cast<float*>(sX + MP * xs);           // [3][32][MP] column quarters, then up rows
   float* sNw = sRed + 3 * 32 * MP;                                // [kx] norm weights of the slice (norm prologue)
 
+  pdl_launch_dependents();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int M = args.M;
   const int n0 = blockIdx.x * (MODE == kSgSwiglu ? 16 : kSgRows);  // first output column of the block
@@ -128,7 +129,16 @@ __global__ void __launch_bounds__(kSgThreads) skinny_gemm_kernel(const SkinnyArg
     }
   };
 
-  // group 0: the activations when they are read as bfloat16, else the norm weights
+  // groups 0..stages-2: the first weight chunks.  They depend on nothing an earlier kernel
+  // writes, so they are requested before this kernel waits for its predecessor.
+#pragma unroll
+  for (int s = 0; s < kSgStages - 1; ++s) {
+    if (s < n_chunks) load_chunk(s, s);
+    sg_commit();
+  }
+
+  pdl_wait();
+  // next group: the activations when they are read as bfloat16, else the norm weights
   if (pr.h_in == nullptr) {
     for (int i = tid; i < MP * (kx / 8); i += kSgThreads) {
       const int m = i / (kx / 8), k = k0 + (i % (kx / 8)) * 8;
@@ -142,13 +152,6 @@ __global__ void __launch_bounds__(kSgThreads) skinny_gemm_kernel(const SkinnyArg
     }
   }
   sg_commit();
-  // groups 1..stages-1: the first weight chunks; they do not depend on the activations
-#pragma unroll
-  for (int s = 0; s < kSgStages - 1; ++s) {
-    if (s < n_chunks) load_chunk(s, s);
-    sg_commit();
-  }
-
   // norm prologue: x = h * rsqrt(mean(h^2) + eps) * w for this K slice -> shared memory as
   // bfloat16 (rows >= M and columns >= K zero), while the weight chunks are in flight
   if (pr.h_in != nullptr) {
@@ -181,7 +184,7 @@ __global__ void __launch_bounds__(kSgThreads) skinny_gemm_kernel(const SkinnyArg
         ss = warp_sum(ss);
         inv[j] = 1.0f / sqrtf(ss / static_cast<float>(K) + pr.eps);
       }
-      sg_wait<kSgStages - 1>();  // group 0 (this thread's share of the norm weights) has landed
+      sg_wait<0>();  // the norm weights (and, incidentally, the first weight chunks) have landed
       __syncthreads();           // ... and everyone else's; every warp walks this loop equally often
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
@@ -217,9 +220,10 @@ __global__ void __launch_bounds__(kSgThreads) skinny_gemm_kernel(const SkinnyArg
   for (int i = 0; i < MT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
   for (int c = 0; c < n_chunks; ++c) {
-    // groups committed so far: 1 (x) + (stages-1) + c; x and chunk c are complete when at most
-    // stages-2 of the newest groups are still in flight
-    sg_wait<kSgStages - 2>();
+    // groups committed so far: (stages-1) chunks, then x, then one per iteration; chunk c and x are
+    // complete when at most stages-2 of the newest groups are still in flight (for c = 0 the x
+    // group is the newest, so everything must have landed)
+    if (c == 0) sg_wait<0>(); else sg_wait<kSgStages - 2>();
     __syncthreads();
     if (c + kSgStages - 1 < n_chunks) load_chunk((c + kSgStages - 1) % kSgStages, c + kSgStages - 1);
     sg_commit();
@@ -328,7 +332,7 @@ int launch_skinny(const SkinnyArgs& a, int k_max, cudaStream_t stream) {
   if (e != cudaSuccess) return static_cast<int>(e);
   const int cols_per_block = MODE == kSgSwiglu ? 16 : kSgRows;
   dim3 grid((a.N + cols_per_block - 1) / cols_per_block, (k_max + a.k_slice - 1) / a.k_slice, a.n_problems);
-  kern<<<grid, kSgThreads, smem, stream>>>(a);
+  launch_pdl(kern, grid, dim3(kSgThreads), smem, stream, a);
   return launch_status();
 }
 

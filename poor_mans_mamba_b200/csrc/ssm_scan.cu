@@ -28,6 +28,8 @@ __global__ void __launch_bounds__(kScanRows* kScanTpr)
                         const int* __restrict__ slots, S* __restrict__ y, int H, int P, int N,
                         int G, const S* __restrict__ z_raw, long long ld_z, float z_scale,
                         const float* __restrict__ z_bias) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane_n = threadIdx.x % kScanTpr;
   const int p = blockIdx.x * kScanRows + threadIdx.x / kScanTpr;
   const int h = blockIdx.y;
@@ -100,6 +102,8 @@ __global__ void gated_norm_kernel(const S* __restrict__ y, const S* __restrict__
                                   S* __restrict__ out, int I, int group_width) {
   extern __shared__ float buf[];
   __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int c0 = blockIdx.y * group_width;
   float ss = 0.f;
@@ -142,10 +146,9 @@ int launch_scan(const void* xbc, int ld_xbc, const void* dt_raw, long long ld_dt
   dim3 block(kScanRows * kScanTpr);
   const int npt = (N + kScanTpr - 1) / kScanTpr;
 #define PMM_SCAN_CASE(NPT)                                                                         \
-  ssm_scan_seq_kernel<S, NPT><<<grid, block, 0, stream>>>(                                         \
-      static_cast<const S*>(xbc), ld_xbc, static_cast<const S*>(dt_raw), ld_dt, dt_scale, dt_shift, \
-      a_log, d_skip, state, cu, slots, static_cast<S*>(y), H, P, N, G, static_cast<const S*>(z_raw),  \
-      ld_z, z_scale, z_bias)
+  launch_pdl(ssm_scan_seq_kernel<S, NPT>, grid, block, 0, stream, static_cast<const S*>(xbc), ld_xbc,  \
+             static_cast<const S*>(dt_raw), ld_dt, dt_scale, dt_shift, a_log, d_skip, state, cu, slots, \
+             static_cast<S*>(y), H, P, N, G, static_cast<const S*>(z_raw), ld_z, z_scale, z_bias)
   if (npt <= 1) PMM_SCAN_CASE(1);
   else if (npt <= 2) PMM_SCAN_CASE(2);
   else if (npt <= 4) PMM_SCAN_CASE(4);
@@ -192,9 +195,8 @@ PMM_EXPORT int pmm_gated_norm(const void* y, const void* z_raw, long long ld_z, 
                                            static_cast<int>(smem));
       if (e != cudaSuccess) return static_cast<int>(e);
     }
-    kern<<<grid, 256, smem, stream>>>(static_cast<const S*>(y), static_cast<const S*>(z_raw), ld_z,
-                                      z_scale, z_bias, w, eps, norm_before_gate,
-                                      static_cast<S*>(out), I, gw);
+    pmm::launch_pdl(kern, grid, dim3(256), smem, stream, static_cast<const S*>(y), static_cast<const S*>(z_raw), ld_z,
+                    z_scale, z_bias, w, eps, norm_before_gate, static_cast<S*>(out), I, gw);
   });
   return pmm::launch_status();
 }

@@ -125,6 +125,16 @@ class ParallelPreNormBlock(Part):
             return False
         return True
 
+    _SIDE_STREAMS: Dict[torch.device, "torch.cuda.Stream"] = {}
+
+    @classmethod
+    def _side_stream(cls, device: torch.device) -> "torch.cuda.Stream":
+        st = cls._SIDE_STREAMS.get(device)
+        if st is None:
+            st = torch.cuda.Stream(device=device)
+            cls._SIDE_STREAMS[device] = st
+        return st
+
     def _forward_few_tokens(self, stream: ResidualStream, ctx, cache: LayerCache) -> None:
         ws = ctx.workspace
         mark = ws.mark()
@@ -132,9 +142,21 @@ class ParallelPreNormBlock(Part):
         T = h.shape[0]
         proj = ws.alloc((T, self._fused_in.shape[0]), ctx.dtype)
         K.skinny_linear_norm(h, self.mixer_norm.weight, self.mixer_norm.eps, self._fused_in, proj)
-        products = []
-        for m, (c0, c1) in zip(self.mixers, self._fused_cols):
-            products.append((m.pre_output(proj[:, c0:c1], ctx, cache), m.output_weight(), m.out_scale))
+        # The mixers only share their input: the first runs on a side stream beside the others
+        # (in a captured step the two become parallel branches of the graph).
+        products = [None] * len(self.mixers)
+        side = self._side_stream(h.device) if len(self.mixers) > 1 else None
+        main = torch.cuda.current_stream(h.device)
+        if side is not None:
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                m, (c0, c1) = self.mixers[0], self._fused_cols[0]
+                products[0] = (m.pre_output(proj[:, c0:c1], ctx, cache), m.output_weight(), m.out_scale)
+        for i, (m, (c0, c1)) in enumerate(zip(self.mixers, self._fused_cols)):
+            if products[i] is None:
+                products[i] = (m.pre_output(proj[:, c0:c1], ctx, cache), m.output_weight(), m.out_scale)
+        if side is not None:
+            main.wait_stream(side)
         K.skinny_residual(h, products)  # h = (h + s0 * y0 W0^T) + s1 * y1 W1^T, in one launch
         if self.ffn is not None:
             act = ws.alloc((T, self.ffn.intermediate_size), ctx.dtype)

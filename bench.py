@@ -149,6 +149,10 @@ def main() -> int:
                     "(same layer sizes) where memory or time needs it")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--profile-steps", action="store_true",
+                    help="small workload for a profiler instead of the benchmark: after an untimed set-up, one "
+                         "2,048-token prefill step and two decode steps of the batch, issued kernel by kernel "
+                         "(no CUDA graphs) between cudaProfilerStart and cudaProfilerStop; use with --layers 2")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -184,6 +188,27 @@ def main() -> int:
     t0 = time.time()
     write_random_model(cfg, seed=2, out_dir=tmp)
     print(f"[bench] wrote random model in {time.time() - t0:.1f}s", file=sys.stderr, flush=True)
+
+    if args.profile_steps:
+        with torch.cuda.device(0):
+            eng = Engine(tmp, dtype=args.dtype, max_tokens=args.batch * (ctx_len + 64) + 4096, max_seqs=args.batch + 1,
+                         page_size=64, max_batched_tokens=8192, max_seq_len=ctx_len + 64, cuda_graphs=False)
+            run = eng.runner
+            reqs = list(range(args.batch))
+            for r in reqs:
+                run.step([StepEntry(r, [rng.randrange(vocab) for _ in range(ctx_len - 8)], [])])
+            run.decode_tokens(reqs, [1] * args.batch)
+            run.step([StepEntry("warm", [rng.randrange(vocab) for _ in range(2048)], [2047])])
+            run.finish("warm")
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+            run.step([StepEntry("prefill", [rng.randrange(vocab) for _ in range(2048)], [2047])])
+            run.decode_tokens(reqs, [2] * args.batch)
+            run.decode_tokens(reqs, [3] * args.batch)
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+        print(json.dumps({"profile_steps": "done", "layers": args.layers, "batch": args.batch, "context": ctx_len}))
+        return 0
 
     def make_engine(batch):
         return Engine(tmp, dtype=args.dtype, max_tokens=batch * (ctx_len + 64), max_seqs=batch, page_size=64,

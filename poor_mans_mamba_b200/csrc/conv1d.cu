@@ -79,6 +79,87 @@ __global__ void conv1d_window_update_kernel(const S* __restrict__ x, long long l
   }
 }
 
+// Vector form for bfloat16 with 16-byte aligned rows: a thread owns 8 neighbouring channels
+// and walks a strip of tokens with the K-1 previous inputs in registers, so every input is
+// read once (plus K-1 rows at the start of a strip).  At the first token of a sequence the
+// history comes from the request's window.
+constexpr int kConvStrip = 16;
+
+template <int K>
+__global__ void __launch_bounds__(128)
+    conv1d_fwd_vec_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const float* __restrict__ pre_scale,
+                          const float* __restrict__ pre_bias, const float* __restrict__ w,
+                          const float* __restrict__ bias, const float* __restrict__ window,
+                          const int* __restrict__ seq_of, const int* __restrict__ cu,
+                          const int* __restrict__ slots, __nv_bfloat16* __restrict__ y, int T, int C) {
+  constexpr int L = K - 1;
+  const int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  const int t_begin = blockIdx.x * kConvStrip;
+  if (c0 >= C || t_begin >= T) return;
+  const int t_end = min(T, t_begin + kConvStrip);
+  float ps[8], pb[8], cb[8], wk[8][K];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    ps[i] = pre_scale[c0 + i];
+    pb[i] = pre_bias ? pre_bias[c0 + i] : 0.f;
+    cb[i] = bias ? bias[c0 + i] : 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) wk[i][k] = w[static_cast<size_t>(c0 + i) * K + k];
+  }
+  auto load_row = [&](int t, float* v) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(x + static_cast<long long>(t) * ldx + c0);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h2[i]);
+      v[2 * i] = f.x * ps[2 * i] + pb[2 * i];
+      v[2 * i + 1] = f.y * ps[2 * i + 1] + pb[2 * i + 1];
+    }
+  };
+  float hist[L][8];  // hist[i] = input of local index j - L + i
+  int cur_seq = -1;
+  for (int t = t_begin; t < t_end; ++t) {
+    const int s = seq_of[t];
+    const int j = t - cu[s];
+    if (s != cur_seq || t == t_begin) {  // (re)build the history at a strip or sequence start
+      cur_seq = s;
+      const float* win = window + static_cast<size_t>(slots[s]) * L * C;
+#pragma unroll
+      for (int i = 0; i < L; ++i) {
+        const int q = j - L + i;
+        if (q >= 0) {
+          load_row(t - L + i, hist[i]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) hist[i][e] = win[static_cast<size_t>(L + q) * C + c0 + e];
+        }
+      }
+    }
+    float v[8];
+    load_row(t, v);
+    uint4 outv;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&outv);
+    float a[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float acc = cb[e];
+#pragma unroll
+      for (int k = 0; k < L; ++k) acc += wk[e][k] * hist[k][e];
+      acc += wk[e][L] * v[e];
+      a[e] = silu_f(acc);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(a[2 * e], a[2 * e + 1]);
+    *reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * C + c0) = outv;
+#pragma unroll
+    for (int i = 0; i + 1 < L; ++i)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) hist[i][e] = hist[i + 1][e];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) hist[L - 1][e] = v[e];
+  }
+}
+
 // One token per sequence: token index == sequence index.
 template <typename S>
 __global__ void conv1d_decode_kernel(const S* __restrict__ x, long long ldx,
@@ -117,6 +198,16 @@ PMM_EXPORT int pmm_conv1d_fwd(const void* x, long long ldx, const float* pre_sca
                               cudaStream_t stream) {
   if (T <= 0) return 0;
   if (K < 2 || C <= 0 || (C + 127) / 128 > 65535) return PMM_ERR_BAD_ARGUMENT;
+  if (dtype == PMM_DTYPE_BF16 && K >= 2 && K <= 4 && C % 8 == 0 && ldx % 8 == 0 &&
+      reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0) {
+    dim3 vgrid((T + pmm::kConvStrip - 1) / pmm::kConvStrip, (C / 8 + 127) / 128);
+    const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
+    __nv_bfloat16* yb = static_cast<__nv_bfloat16*>(y);
+    if (K == 2) pmm::conv1d_fwd_vec_kernel<2><<<vgrid, 128, 0, stream>>>(xb, ldx, pre_scale, pre_bias, w, bias, window, seq_of, cu, slots, yb, T, C);
+    if (K == 3) pmm::conv1d_fwd_vec_kernel<3><<<vgrid, 128, 0, stream>>>(xb, ldx, pre_scale, pre_bias, w, bias, window, seq_of, cu, slots, yb, T, C);
+    if (K == 4) pmm::conv1d_fwd_vec_kernel<4><<<vgrid, 128, 0, stream>>>(xb, ldx, pre_scale, pre_bias, w, bias, window, seq_of, cu, slots, yb, T, C);
+    return pmm::launch_status();
+  }
   dim3 grid(T, (C + 127) / 128);
   PMM_DISPATCH_DTYPE(dtype, S, pmm::conv1d_fwd_kernel<S><<<grid, 128, 0, stream>>>(
                                    static_cast<const S*>(x), ldx, pre_scale, pre_bias, w, bias,

@@ -54,6 +54,59 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const S* __restrict__ 
   for (int i = threadIdx.x; i < D; i += blockDim.x) stf(o + i, buf[i] * inv * w[i]);
 }
 
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
+  uint2 raw;
+  *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+  *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// The same for widths that are a multiple of 4: four elements per thread and access.
+template <typename S>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const S* __restrict__ a, float sa,
+                                       const S* __restrict__ b, float sb, const float* __restrict__ w,
+                                       float eps, S* __restrict__ out, const int* __restrict__ rows,
+                                       int D) {
+  extern __shared__ float buf[];
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const size_t src = static_cast<size_t>(rows ? rows[r] : r) * D;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 4; i < D; i += blockDim.x * 4) {
+    float4 v = ld4(h + src + i);
+    if (a) {
+      const float4 x = ld4(a + src + i);
+      v.x += sa * x.x; v.y += sa * x.y; v.z += sa * x.z; v.w += sa * x.w;
+    }
+    if (b) {
+      const float4 x = ld4(b + src + i);
+      v.x += sb * x.x; v.y += sb * x.y; v.z += sb * x.z; v.w += sb * x.w;
+    }
+    *reinterpret_cast<float4*>(buf + i) = v;
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    if (!rows && (a || b)) st4(h + src + i, v);
+  }
+  if (!out) return;
+  const float total = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(total / static_cast<float>(D) + eps);
+  S* o = out + static_cast<size_t>(r) * D;
+  for (int i = threadIdx.x * 4; i < D; i += blockDim.x * 4) {
+    const float4 v = *reinterpret_cast<const float4*>(buf + i);
+    const float4 g = ld4(w + i);
+    st4(o + i, make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w));
+  }
+}
+
 __global__ void scale_f32_kernel(float* __restrict__ x, float s, size_t n) {
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < n) x[i] *= s;
@@ -84,8 +137,11 @@ PMM_EXPORT int pmm_add_rmsnorm(void* h, const void* a, float sa, const void* b, 
   const size_t smem = static_cast<size_t>(D) * sizeof(float);
   if (smem > 200 * 1024) return PMM_ERR_BAD_ARGUMENT;  // width beyond one block's shared memory
   const int threads = D >= 1024 ? 256 : 128;
+  const bool vec = D % 4 == 0 && reinterpret_cast<uintptr_t>(h) % 16 == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(b) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(w) % 16 == 0;
   PMM_DISPATCH_DTYPE(dtype, S, {
-    auto kern = pmm::add_rmsnorm_kernel<S>;
+    auto kern = vec ? pmm::add_rmsnorm_vec_kernel<S> : pmm::add_rmsnorm_kernel<S>;
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(smem));

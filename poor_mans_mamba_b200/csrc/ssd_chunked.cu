@@ -180,33 +180,38 @@ __global__ void __launch_bounds__(128)
 __global__ void ssd_state_pass_kernel(float* __restrict__ chunk_state, const float* __restrict__ chunk_decay,
                                       float* __restrict__ state, const int* __restrict__ cu,
                                       const int* __restrict__ slots, int H, int PN) {
-  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  // four state elements per thread (P*N is a multiple of 4 for every compiled pair)
+  const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
   const int h = blockIdx.y, seq = blockIdx.z;
   if (e >= PN) return;
   int first = 0;
   for (int s = 0; s < seq; ++s) first += (cu[s + 1] - cu[s] + kQ - 1) / kQ;
   const int nc = (cu[seq + 1] - cu[seq] + kQ - 1) / kQ;
   if (nc <= 0) return;
-  float* sp = state + (static_cast<size_t>(slots[seq]) * H + h) * PN + e;
-  float s = *sp;
+  float4* sp = reinterpret_cast<float4*>(state + (static_cast<size_t>(slots[seq]) * H + h) * PN + e);
+  float4 s = *sp;
   // The chain through s is short; the loads are what cost.  They are issued eight chunks
   // ahead of the stores (each address is read before it is written, by this thread only).
   constexpr int kAhead = 8;
   for (int c0 = 0; c0 < nc; c0 += kAhead) {
-    float local[kAhead], decay[kAhead];
+    float4 local[kAhead];
+    float decay[kAhead];
 #pragma unroll
     for (int i = 0; i < kAhead; ++i) {
       const int c = min(c0 + i, nc - 1);
       const size_t ch = static_cast<size_t>(first + c) * H + h;
-      local[i] = __ldcs(chunk_state + ch * PN + e);
+      local[i] = __ldcs(reinterpret_cast<const float4*>(chunk_state + ch * PN + e));
       decay[i] = chunk_decay[ch];
     }
 #pragma unroll
     for (int i = 0; i < kAhead; ++i) {
       if (c0 + i < nc) {
         const size_t ch = static_cast<size_t>(first + c0 + i) * H + h;
-        chunk_state[ch * PN + e] = s;  // the state at the start of this chunk
-        s = s * decay[i] + local[i];
+        *reinterpret_cast<float4*>(chunk_state + ch * PN + e) = s;  // the state at the start of this chunk
+        s.x = s.x * decay[i] + local[i].x;
+        s.y = s.y * decay[i] + local[i].y;
+        s.z = s.z * decay[i] + local[i].z;
+        s.w = s.w * decay[i] + local[i].w;
       }
     }
   }
@@ -251,10 +256,24 @@ __global__ void __launch_bounds__(128)
   }
   {
     const float* src = chunk_state + (static_cast<size_t>(c) * H + h) * P * N;
-    for (int i = tid; i < P * N / 2; i += 128) {
-      const int p = (2 * i) / N, n = (2 * i) % N;
-      const float2 v = *reinterpret_cast<const float2*>(src + 2 * i);
-      *reinterpret_cast<__nv_bfloat162*>(sS + p * SN + n) = __floats2bfloat162_rn(v.x, v.y);
+    constexpr int kQuads = P * N / 4;  // float4 pieces, a multiple of 4 * 128 for every compiled pair but (16,16)
+    for (int i0 = tid; i0 < kQuads; i0 += 4 * 128) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * 128;
+        v[u] = i < kQuads ? __ldcs(reinterpret_cast<const float4*>(src) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * 128;
+        if (i < kQuads) {
+          const int p = (4 * i) / N, n = (4 * i) % N;
+          __nv_bfloat162* d = reinterpret_cast<__nv_bfloat162*>(sS + p * SN + n);
+          d[0] = __floats2bfloat162_rn(v[u].x, v[u].y);
+          d[1] = __floats2bfloat162_rn(v[u].z, v[u].w);
+        }
+      }
     }
   }
   ssd_delta_cumsum(dt_raw, ld_dt, dt_scale, dt_shift[h], -expf(a_log[h]), t0, len, h, s_delta, s_cs);
@@ -388,7 +407,7 @@ int launch_ssd(const void* xbc, int ld_xbc, const void* dt_raw, long long ld_dt,
   k1<<<grid, 128, smem1, stream>>>(static_cast<const bf16*>(xbc), ld_xbc, static_cast<const bf16*>(dt_raw), ld_dt,
                                    dt_scale, dt_shift, a_log, cu, n_seq, chunk_state, chunk_decay, H, G);
   const int PN = P * N;
-  dim3 grid2((PN + 255) / 256, H, n_seq);
+  dim3 grid2((PN / 4 + 255) / 256, H, n_seq);
   ssd_state_pass_kernel<<<grid2, 256, 0, stream>>>(chunk_state, chunk_decay, state, cu, slots, H, PN);
   k3<<<grid, 128, smem3, stream>>>(static_cast<const bf16*>(xbc), ld_xbc, static_cast<const bf16*>(dt_raw), ld_dt,
                                    dt_scale, dt_shift, a_log, d_skip, cu, n_seq, chunk_state,

@@ -12,6 +12,7 @@ buffer, one host-to-device copy.  Everything else is kernels on the current stre
 """
 from __future__ import annotations
 
+import collections
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
@@ -36,6 +37,12 @@ class StepEntry:
     want: Sequence[int] = field(default_factory=list)
 
 
+# Steps of at least this many tokens are candidates for the step-graph cache (smaller mixed
+# steps change shape too often to be worth recording); the cache keeps this many shapes.
+_STEP_GRAPH_MIN_TOKENS = 256
+_STEP_GRAPH_CAPACITY = 6
+
+
 class _Staging:
     """A few pinned int32 host buffers used in rotation for the per-step index upload."""
 
@@ -47,8 +54,8 @@ class _Staging:
         self._dev: Optional[Tensor] = None
         self._i = 0
 
-    def upload(self, n: int, fill) -> Tensor:
-        """Calls fill(numpy int32 array of n) and returns the device copy."""
+    def upload(self, n: int, fill, dev: Optional[Tensor] = None) -> Tensor:
+        """Calls fill(numpy int32 array of n) and returns the device copy (in ``dev`` if given)."""
         i = self._i
         self._i = (i + 1) % len(self._host)
         if self._host[i] is None or self._host[i].numel() < n:
@@ -56,12 +63,15 @@ class _Staging:
             self._host[i] = torch.empty(cap, dtype=torch.int32, pin_memory=self.pinned)
         elif self._events[i] is not None:
             self._events[i].synchronize()  # the copy that last read this buffer has finished
-        if self._dev is None or self._dev.numel() < n:
-            cap = max(1024, 1 << (n - 1).bit_length())
-            self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        if dev is None:
+            if self._dev is None or self._dev.numel() < n:
+                cap = max(1024, 1 << (n - 1).bit_length())
+                self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+            dev = self._dev[:n]
+        else:
+            dev = dev[:n]
         host = self._host[i]
         fill(host.numpy()[:n])
-        dev = self._dev[:n]
         dev.copy_(host[:n], non_blocking=True)
         if self.pinned:
             ev = torch.cuda.Event()
@@ -85,6 +95,7 @@ class ModelRunner:
         self.h2d_bytes = 0
         self.graphs = None
         self._sampler = None
+        self._step_graphs: "collections.OrderedDict" = collections.OrderedDict()
 
     def enable_graphs(self, max_seq_len: int, buckets=None) -> None:
         """Serve decode-only steps from CUDA graphs (captured per batch-size bucket on first use).
@@ -123,6 +134,21 @@ class ModelRunner:
         logits = self.step([StepEntry(r, [int(t)], [0]) for r, t in zip(reqs, tokens)])
         self._last_sampled = self._sampler.sample_device(logits, temperatures, seeds, steps)
         return self._last_sampled
+
+    def _capture_step(self, entry: dict, total: int, fill, context) -> None:
+        """Record the forward pass of one step shape into a CUDA graph over buffers of its own."""
+        from ..kernels import ops as K
+        meta = torch.zeros(total, dtype=torch.int32, device=self.device)
+        self._staging.upload(total, fill, dev=meta)
+        workspace = Workspace(self.device, initial_bytes=self.workspace.high_water + (8 << 20))
+        workspace.freeze()
+        ctx, tables = context(meta, workspace)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        before = K.launch_count
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(ctx, self.cache.layer_caches(tables))
+        entry.update(graph=graph, meta=meta, workspace=workspace, logits=logits, kernels=K.launch_count - before)
 
     def kernels_launched_since(self, launch_count_before: int) -> int:
         """Own kernels launched since ``launch_count_before`` (a value of kernels.ops.launch_count),
@@ -168,9 +194,9 @@ class ModelRunner:
             seen.add(e.req)
             if len(e.tokens) == 0:
                 raise ValueError(f"request {e.req!r} brings no tokens")
-            for t in e.tokens:
-                if not 0 <= int(t) < vocab:
-                    raise ValueError("token id out of range")
+            toks = np.asarray(e.tokens)
+            if toks.dtype.kind not in "iu" or int(toks.min()) < 0 or int(toks.max()) >= vocab:
+                raise ValueError("token id out of range")
             for w in e.want:
                 if not 0 <= int(w) < len(e.tokens):
                     raise ValueError(f"request {e.req!r}: wanted place {w} is outside its tokens")
@@ -189,7 +215,18 @@ class ModelRunner:
         T = sum(new_lens)
         n_rows = sum(len(e.want) for e in entries)
         groups = list(cache.groups.values())
-        widths = [max(len(g.tables[e.req]) for e in entries) for g in groups]
+        kv_len = max(p + n for p, n in zip(past, new_lens))
+        # Steps of a shape that has been seen before are replayed from a CUDA graph (the host
+        # issues hundreds of launches per step otherwise).  Such steps use block tables of a
+        # fixed width and a key-length bound rounded up to a power of two, so that the launch
+        # shapes depend on the key only.
+        graph_key = None
+        if self.graphs is not None and kv_len <= self.graphs.max_seq_len and T >= _STEP_GRAPH_MIN_TOKENS:
+            kv_len = min(self.graphs.max_seq_len, 1 << (kv_len - 1).bit_length())
+            graph_key = (tuple(new_lens), n_rows, kv_len)
+            widths = [g.blocks_for(self.graphs.max_seq_len) for g in groups]
+        else:
+            widths = [max(len(g.tables[e.req]) for e in entries) for g in groups]
 
         # one packed int32 upload: tokens | positions | seq_of | cu | slots | rows | tables...
         o_tok, o_pos, o_seq = 0, T, 2 * T
@@ -227,20 +264,34 @@ class ModelRunner:
                     arr[arr < 0] = g.num_pages
                     tab[s, :len(row)] = arr
 
-        dev = self._staging.upload(total, fill)
+        def context(dev: Tensor, workspace: Workspace):
+            tables = {g.key: dev[off:off + n_seq * w].view(n_seq, w) for g, w, off in zip(groups, widths, tab_offsets)}
+            return StepContext(
+                n_tokens=T, n_seq=n_seq,
+                tokens=dev[o_tok:o_tok + T], positions=dev[o_pos:o_pos + T], seq_of=dev[o_seq:o_seq + T],
+                cu_seqlens=dev[o_cu:o_cu + n_seq + 1], slots=dev[o_slot:o_slot + n_seq],
+                logit_rows=dev[o_rows:o_rows + n_rows], n_rows=n_rows,
+                decode_only=all(n == 1 for n in new_lens), kv_len_bound=kv_len,
+                dtype=self.dtype, workspace=workspace, new_lens=new_lens, past_lens=past), tables
+
+        entry = self._step_graphs.get(graph_key) if graph_key is not None else None
+        if entry is not None and entry.get("graph") is None and entry["seen"] >= 1:
+            self._capture_step(entry, total, fill, context)  # second time this shape comes: capture it
+        if entry is not None and entry.get("graph") is not None:
+            self._step_graphs.move_to_end(graph_key)
+            self._staging.upload(total, fill, dev=entry["meta"])
+            entry["graph"].replay()
+            logits = entry["logits"]
+        else:
+            if graph_key is not None:
+                self._step_graphs[graph_key] = {"seen": 1}
+                while len(self._step_graphs) > _STEP_GRAPH_CAPACITY:
+                    self._step_graphs.popitem(last=False)
+            dev = self._staging.upload(total, fill)
+            self.workspace.reset()
+            ctx, block_tables = context(dev, self.workspace)
+            logits = self.model.forward(ctx, cache.layer_caches(block_tables))
         self.h2d_bytes += 4 * total
-        block_tables = {g.key: dev[off:off + n_seq * w].view(n_seq, w)
-                        for g, w, off in zip(groups, widths, tab_offsets)}
-        self.workspace.reset()
-        ctx = StepContext(
-            n_tokens=T, n_seq=n_seq,
-            tokens=dev[o_tok:o_tok + T], positions=dev[o_pos:o_pos + T], seq_of=dev[o_seq:o_seq + T],
-            cu_seqlens=dev[o_cu:o_cu + n_seq + 1], slots=dev[o_slot:o_slot + n_seq],
-            logit_rows=dev[o_rows:o_rows + n_rows], n_rows=n_rows,
-            decode_only=all(n == 1 for n in new_lens),
-            kv_len_bound=max(p + n for p, n in zip(past, new_lens)),
-            dtype=self.dtype, workspace=self.workspace, new_lens=new_lens, past_lens=past)
-        logits = self.model.forward(ctx, cache.layer_caches(block_tables))
 
         for e, n in zip(entries, new_lens):
             cache.advance(e.req, n)

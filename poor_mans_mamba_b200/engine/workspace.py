@@ -12,6 +12,8 @@ from typing import List, Tuple
 import torch
 
 _ALIGN = 256
+_ITEMSIZE = {torch.float32: 4, torch.bfloat16: 2, torch.float16: 2, torch.int32: 4, torch.int64: 8, torch.uint8: 1,
+             torch.float64: 8, torch.int8: 1, torch.int16: 2, torch.bool: 1}
 
 
 class Workspace:
@@ -21,6 +23,7 @@ class Workspace:
         self._chunk = 0
         self._offset = 0
         self._frozen = False
+        self._views = {}  # (chunk index, offset, shape, dtype) -> tensor: the same requests recur layer after layer
         self.high_water = 0
         if initial_bytes > 0:
             self._chunks.append(torch.empty(int(initial_bytes), dtype=torch.uint8, device=self.device))
@@ -36,6 +39,7 @@ class Workspace:
         if len(self._chunks) > 1 and not self._frozen:
             total = self.capacity()
             self._chunks = []
+            self._views = {}
             self._chunks.append(torch.empty(total, dtype=torch.uint8, device=self.device))
         self._chunk = 0
         self._offset = 0
@@ -50,18 +54,26 @@ class Workspace:
         return sum(c.numel() for c in self._chunks[:self._chunk]) + self._offset
 
     def alloc(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        shape = tuple(shape)
         numel = 1
         for s in shape:
-            numel *= int(s)
-        nbytes = numel * torch.empty((), dtype=dtype).element_size()
+            numel *= s
+        nbytes = numel * _ITEMSIZE[dtype]
         size = (max(nbytes, 1) + _ALIGN - 1) // _ALIGN * _ALIGN
         while True:
             if self._chunk < len(self._chunks):
                 chunk = self._chunks[self._chunk]
-                if self._offset + size <= chunk.numel():
-                    view = chunk[self._offset:self._offset + nbytes].view(dtype).view(tuple(int(s) for s in shape))
-                    self._offset += size
-                    self.high_water = max(self.high_water, self._used())
+                off = self._offset
+                if off + size <= chunk.numel():
+                    key = (self._chunk, off, shape, dtype)
+                    view = self._views.get(key)
+                    if view is None:
+                        view = chunk[off:off + nbytes].view(dtype).view(shape)
+                        self._views[key] = view
+                    self._offset = off + size
+                    used = self._used()
+                    if used > self.high_water:
+                        self.high_water = used
                     return view
                 self._chunk += 1
                 self._offset = 0

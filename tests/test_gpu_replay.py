@@ -165,3 +165,34 @@ def test_decode_through_cuda_graphs(case, dtype):
                 live.remove(i)
         runner.cache.check()
     assert runner.graphs.replays > 100 and set(runner.graphs.buckets) <= {1, 2, 4}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_repeated_step_shapes_replay_from_graphs(case, dtype):
+    """A step shape that comes again is recorded into a CUDA graph and replayed from then on:
+    same logits as the plain implementation for different requests, contents, slots and pages."""
+    from poor_mans_mamba_b200.engine import StepEntry
+    which, d, cfg, seqs, refs = case
+    rng = random.Random(7)
+    v = cfg["vocab_size"]
+    from model_dirs import make_model_dir  # weights of the case again, for fresh references
+    import tempfile
+    _, _, weights = make_model_dir(which, tempfile.mkdtemp())
+    runner = H.make_runner(d, dtype, page_size=16, num_pages=64, num_slots=3)
+    runner.enable_graphs(max_seq_len=512)
+    for rep in range(4):
+        a = [rng.randrange(v) for _ in range(300)]
+        b = [rng.randrange(v) for _ in range(40)]
+        ref_a, ref_b = H.reference_logits([a, b], weights, cfg)
+        # a filler request of changing length takes other pages and another slot first
+        runner.step([StepEntry(("f", rep), [1] * (1 + 17 * rep), [])])
+        # step 1: 280 tokens of a + 20 of b (same shape every repetition); step 2: the rest
+        lg1 = runner.step([StepEntry(("a", rep), a[:280], [0, 279]), StepEntry(("b", rep), b[:20], [19])]).cpu()
+        H.check_rows(lg1, torch.stack([ref_a[0], ref_a[279], ref_b[19]]), dtype, f"repetition {rep} first step")
+        lg2 = runner.step([StepEntry(("a", rep), a[280:], [19]), StepEntry(("b", rep), b[20:], [19])]).cpu()
+        H.check_rows(lg2, torch.stack([ref_a[299], ref_b[39]]), dtype, f"repetition {rep} second step")
+        for name in ("b", "f", "a"):
+            runner.finish((name, rep))
+        runner.cache.check()
+    recorded = [k for k, e in runner._step_graphs.items() if e.get("graph") is not None]
+    assert any(k[0] == (280, 20) for k in recorded)

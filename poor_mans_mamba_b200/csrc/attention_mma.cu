@@ -3,10 +3,11 @@
 // One block = one tile of query rows of ONE sequence and ONE key/value head, and one key
 // split.  A "row" is a (token, query head of the group) pair, so the G = Hq/Hkv query
 // heads that share a key/value head share every K/V tile that is fetched.  K/V tiles of 64
-// keys are gathered row by row through the block table with cp.async (16 bytes a time,
-// zero-filled beyond the key range) into double-buffered shared memory; S = Q K^T and
-// O += P V run on mma.sync m16n8k16 with ldmatrix operands; softmax is the online form in
-// float (exp2 with the scale folded in).  Two shapes:
+// keys are gathered row by row through the block table (its entries for the block's key range
+// are read into shared memory first) with cp.async (16 bytes a time, zero-filled beyond the
+// key range) into a ring of shared-memory stages; S = Q K^T and O += P V run on mma.sync
+// m16n8k16 with ldmatrix operands, the Q fragments staying in registers; softmax is the online
+// form in float (ex2 with the scale folded into the exponent).  Two shapes:
 //   * tile of 64 rows, warp w owns rows 16w..16w+15 and walks all keys   (prompt portions)
 //   * tile of 16 rows, tiles are fetched four at a time, each warp takes one whole tile and
 //     the warps are merged at the end through shared memory              (decode: G rows)
@@ -26,6 +27,16 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool pr
   const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
   const int sz = pred ? 16 : 0;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(sz));
+}
+__device__ __forceinline__ void cp_async16_all(void* smem, const void* gmem) {
+  const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+// 2^x, -inf -> 0; relative error about 2^-22, far below the bfloat16 probabilities it feeds
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
@@ -61,7 +72,14 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 
 constexpr int kFlashKeys = 64;  // keys per tile
 
-template <int DH, bool SPLITW>
+// Decode blocks walk few tiles and pay memory latency for each one they wait for: they keep
+// four tiles in flight.  Prompt tiles have work to hide it behind: two tiles ahead, one where
+// the rows are long and shared memory would limit the blocks per SM.
+__host__ __device__ constexpr int flash_stages(int dh, bool splitw) { return splitw ? 4 : (dh > 64 ? 2 : 3); }
+
+// MT = row tiles of 16 per warp: 1 (64 rows a block) or 2 (128 rows a block, every K/V fragment
+// read from shared memory feeds two row tiles).  Decode blocks (SPLITW) have one 16-row tile.
+template <int DH, bool SPLITW, int MT>
 __global__ void __launch_bounds__(128)
     flash_paged_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pool,
                        const int* __restrict__ block_table, int max_blocks,
@@ -69,24 +87,24 @@ __global__ void __launch_bounds__(128)
                        bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                        float scale_log2, int window, int split_len, int n_splits, int page_size,
                        int n_seq, int Hq, int Hkv, int* __restrict__ split_counter) {
-  constexpr int M = SPLITW ? 16 : 64;
+  static_assert(!SPLITW || MT == 1, "decode tiles have 16 rows");
+  constexpr int M = SPLITW ? 16 : 64 * MT;
   constexpr int KT = kFlashKeys;
   constexpr int STRIDE = DH + 8;
-  constexpr int WKEYS = 64;  // keys a warp handles per tile: all of them
-  constexpr int NT_S = WKEYS / 8;
+  constexpr int NT_S = KT / 8;
   constexpr int KS_Q = DH / 16;
   constexpr int NT_O = DH / 8;
   constexpr int CHUNKS = DH / 8;  // 16-byte chunks per row
-  // Decode blocks walk few tiles and pay memory latency for each one they wait for: they keep
-  // four tiles in flight.  Prompt tiles have work to hide it behind and keep shared memory small.
-  constexpr int NSTAGE = SPLITW ? 4 : 2;
+  constexpr int NSTAGE = flash_stages(DH, SPLITW);
+  constexpr int BT_CAP = 512;  // block-table entries of this block's key range kept in shared memory
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
   bf16* sK = sQ + M * STRIDE;
   bf16* sV = sK + NSTAGE * KT * STRIDE;
-  __shared__ int s_pos[64];
-  __shared__ float s_wm[4][16], s_wl[4][16], s_M[16], s_L[16];
+  __shared__ int s_pos[128];
+  __shared__ int s_bt[BT_CAP];
+  __shared__ float s_wm[4][16], s_wl[4][16], s_M[128], s_L[128];
 
   pdl_launch_dependents();
   pdl_wait();
@@ -96,181 +114,242 @@ __global__ void __launch_bounds__(128)
   const int hk = blockIdx.y, z = blockIdx.z;
   const int kv_dim = Hkv * DH;
 
-  // which sequence and which of its tokens this tile covers
+  // which sequence and which of its tokens this tile covers.  Blocks start in index order and
+  // a sequence's last tiles walk the most keys, so the tiles are handed out from the back.
+  const int tile_id = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
   int seq = 0, acc = 0;
   for (; seq < n_seq; ++seq) {
     const int n = cu[seq + 1] - cu[seq];
     const int nt = (n + tpt - 1) / tpt;
-    if (static_cast<int>(blockIdx.x) < acc + nt) break;
+    if (tile_id < acc + nt) break;
     acc += nt;
   }
   if (seq >= n_seq) return;
-  const int tok0 = cu[seq] + (static_cast<int>(blockIdx.x) - acc) * tpt;
+  const int tok0 = cu[seq] + (tile_id - acc) * tpt;
   const int n_tok = min(cu[seq + 1], tok0 + tpt) - tok0;
   const int n_rows = n_tok * G;
   const int* bt = block_table + static_cast<size_t>(seq) * max_blocks;
 
-  if (tid < 64) s_pos[tid] = (tid < n_rows) ? positions[tok0 + tid / G] : -1;
+  if (tid < M) s_pos[tid] = (tid < n_rows) ? positions[tok0 + tid / G] : -1;
   const int pos_min = positions[tok0], pos_max = positions[tok0 + n_tok - 1];
   const int lo_all = window > 0 ? max(0, pos_min - window + 1) : 0;
   const int k_begin = max(lo_all, z * split_len);
   const int k_end = min(pos_max + 1, (z + 1) * split_len);
 
+  const int first_tile = (k_begin / KT) * KT;
+  const int n_tiles = k_end > k_begin ? (k_end - first_tile + KT - 1) / KT : 0;
+
+  // The block-table entries of this block's key range go to shared memory once, so that no tile
+  // waits for a table entry from L2 before its copies can be issued.
+  const int bt_lo = first_tile / page_size;
+  const int n_bt = n_tiles > 0 ? (k_end - 1) / page_size - bt_lo + 1 : 0;
+  const bool bt_shared = n_bt <= BT_CAP;
+  if (bt_shared)
+    for (int i = tid; i < n_bt; i += 128) s_bt[i] = bt[bt_lo + i];
+  __syncthreads();
+  auto page_of = [&](int idx) { return bt_shared ? s_bt[idx - bt_lo] : bt[idx]; };
+
   // Q rows -> shared memory (rows beyond the tile are zero)
-  for (int c = tid; c < M * CHUNKS; c += 128) {
-    const int r = c / CHUNKS, col = c % CHUNKS;
-    const bool ok = r < n_rows;
-    const size_t src = ok ? (static_cast<size_t>(tok0 + r / G) * Hq + hk * G + r % G) * DH + col * 8 : 0;
-    cp_async16(sQ + r * STRIDE + col * 8, q + src, ok);
+  if (n_tiles > 0) {
+    for (int c = tid; c < M * CHUNKS; c += 128) {
+      const int r = c / CHUNKS, col = c % CHUNKS;
+      const bool ok = r < n_rows;
+      const size_t src = ok ? (static_cast<size_t>(tok0 + r / G) * Hq + hk * G + r % G) * DH + col * 8 : 0;
+      cp_async16(sQ + r * STRIDE + col * 8, q + src, ok);
+    }
   }
 
   // A tile of 64 keys lies inside one page when the page size is a multiple of 64: then one
   // table look-up serves the whole tile and every thread's pieces sit at fixed offsets from it.
   const bool tile_in_page = (page_size % KT) == 0;
-  constexpr int PIECES = KT * CHUNKS / 128;  // (row, 16-byte column) pieces per thread and tile
+  constexpr int RSTEP = 128 / CHUNKS;  // rows of a tile that one pass of the block covers
+  constexpr int PIECES = KT / RSTEP;   // passes (row, 16-byte column) per thread and tile
+  const int ld_r0 = tid / CHUNKS, ld_col = (tid % CHUNKS) * 8;
+  const int ld_soff = ld_r0 * STRIDE + ld_col;
+  const size_t v_off = static_cast<size_t>(page_size) * kv_dim;
   auto load_tile = [&](int stage, int base) {
-    bf16* dK = sK + stage * KT * STRIDE;
-    bf16* dV = sV + stage * KT * STRIDE;
-    const size_t v_off = static_cast<size_t>(page_size) * kv_dim;
+    bf16* dK = sK + stage * KT * STRIDE + ld_soff;
+    bf16* dV = sV + stage * KT * STRIDE + ld_soff;
     if (tile_in_page) {
-      const int page = bt[base / page_size];
-      const bf16* src0 = pool + (static_cast<size_t>(page) * 2 * page_size + base % page_size) * kv_dim + hk * DH;
+      const int page = page_of(base / page_size);
+      const bf16* src = pool + (static_cast<size_t>(page) * 2 * page_size + base % page_size + ld_r0) * kv_dim +
+                        hk * DH + ld_col;
+      if (base >= k_begin && base + KT <= k_end) {  // every key of the tile is wanted
 #pragma unroll
-      for (int j = 0; j < PIECES; ++j) {
-        const int c = tid + j * 128;
-        const int r = c / CHUNKS, col = c % CHUNKS;
-        const int key = base + r;
-        const bool ok = key >= k_begin && key < k_end;
-        const bf16* src = ok ? src0 + static_cast<size_t>(r) * kv_dim + col * 8 : pool;
-        cp_async16(dK + r * STRIDE + col * 8, src, ok);
-        cp_async16(dV + r * STRIDE + col * 8, ok ? src + v_off : pool, ok);
+        for (int j = 0; j < PIECES; ++j) {
+          cp_async16_all(dK + j * RSTEP * STRIDE, src + static_cast<size_t>(j * RSTEP) * kv_dim);
+          cp_async16_all(dV + j * RSTEP * STRIDE, src + static_cast<size_t>(j * RSTEP) * kv_dim + v_off);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < PIECES; ++j) {
+          const int key = base + ld_r0 + j * RSTEP;
+          const bool ok = key >= k_begin && key < k_end;
+          const bf16* sj = ok ? src + static_cast<size_t>(j * RSTEP) * kv_dim : pool;
+          cp_async16(dK + j * RSTEP * STRIDE, sj, ok);
+          cp_async16(dV + j * RSTEP * STRIDE, ok ? sj + v_off : pool, ok);
+        }
       }
     } else {
-      for (int c = tid; c < KT * CHUNKS; c += 128) {
-        const int r = c / CHUNKS, col = c % CHUNKS;
-        const int key = base + r;
+#pragma unroll
+      for (int j = 0; j < PIECES; ++j) {
+        const int key = base + ld_r0 + j * RSTEP;
         const bool ok = key >= k_begin && key < k_end;
         size_t src = 0;
         if (ok) {
-          const int page = bt[key / page_size];
-          src = (static_cast<size_t>(page) * 2 * page_size + key % page_size) * kv_dim + hk * DH + col * 8;
+          const int page = page_of(key / page_size);
+          src = (static_cast<size_t>(page) * 2 * page_size + key % page_size) * kv_dim + hk * DH + ld_col;
         }
-        cp_async16(dK + r * STRIDE + col * 8, pool + src, ok);
-        cp_async16(dV + r * STRIDE + col * 8, pool + (ok ? src + v_off : 0), ok);
+        cp_async16(dK + j * RSTEP * STRIDE, pool + src, ok);
+        cp_async16(dV + j * RSTEP * STRIDE, pool + (ok ? src + v_off : 0), ok);
       }
     }
   };
 
-  const int first_tile = (k_begin / KT) * KT;
-  const int n_tiles = k_end > k_begin ? (k_end - first_tile + KT - 1) / KT : 0;
-  const int row_base = SPLITW ? 0 : warp * 16;
+  // Warp w owns rows row_base .. row_base + 16*MT - 1; in fragment layout a thread holds, of
+  // each 16-row tile, row (lane/4) ["lo"] and row (lane/4 + 8) ["hi"].
+  const int row_base = SPLITW ? 0 : warp * 16 * MT;
   const int r_lo = lane >> 2, r_hi = r_lo + 8;
-  float m_lo = -CUDART_INF_F, m_hi = -CUDART_INF_F, l_lo = 0.f, l_hi = 0.f;
-  float o[NT_O][4];
+  // running maxima are kept in the exponent's unit (score * scale * log2 e)
+  float m_lo[MT], m_hi[MT], l_lo[MT], l_hi[MT];
+  float o[MT][NT_O][4];
+  unsigned qf[MT][KS_Q][4];  // the warp's query rows as mma A fragments, read from shared memory once
 #pragma unroll
-  for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  for (int mt = 0; mt < MT; ++mt) {
+    m_lo[mt] = m_hi[mt] = -CUDART_INF_F;
+    l_lo[mt] = l_hi[mt] = 0.f;
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) o[mt][i][0] = o[mt][i][1] = o[mt][i][2] = o[mt][i][3] = 0.f;
+  }
+  auto load_q_fragments = [&]() {
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int ks = 0; ks < KS_Q; ++ks)
+        ldmatrix_x4(qf[mt][ks][0], qf[mt][ks][1], qf[mt][ks][2], qf[mt][ks][3],
+                    sQ + (row_base + mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + ks * 16 +
+                        (lane >> 4) * 8);
+  };
+  const int k_lane_off = ((lane & 7) + (lane >> 4) * 8) * STRIDE + ((lane >> 3) & 1) * 8;
+  const int v_lane_off = ((lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + (lane >> 4) * 8;
 
-  // one tile of 64 keys against this warp's 16 rows
+  // one tile of 64 keys against this warp's rows
   auto process_tile = [&](int stage, int base) {
-    const bf16* tK = sK + stage * KT * STRIDE;
-    const bf16* tV = sV + stage * KT * STRIDE;
-    const int pos_lo = s_pos[row_base + r_lo], pos_hi = s_pos[row_base + r_hi];
+    const bf16* tK = sK + stage * KT * STRIDE + k_lane_off;
+    const bf16* tV = sV + stage * KT * STRIDE + v_lane_off;
 
-    // S = Q K^T for this warp's rows and keys
-    float s[NT_S][4];
+    // S = Q K^T
+    float s[MT][NT_S][4];
 #pragma unroll
-    for (int i = 0; i < NT_S; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int i = 0; i < NT_S; ++i) s[mt][i][0] = s[mt][i][1] = s[mt][i][2] = s[mt][i][3] = 0.f;
+    // The fragment loads and the mma instructions issue in program order, so the K fragments of
+    // step ks+1 are requested before the products of step ks: their latency hides behind them.
+    unsigned bk[2][NT_S / 2][4];
+    auto load_k = [&](int ks) {
+#pragma unroll
+      for (int np = 0; np < NT_S / 2; ++np)
+        ldmatrix_x4(bk[ks & 1][np][0], bk[ks & 1][np][1], bk[ks & 1][np][2], bk[ks & 1][np][3],
+                    tK + np * 16 * STRIDE + ks * 16);
+    };
+    load_k(0);
 #pragma unroll
     for (int ks = 0; ks < KS_Q; ++ks) {
-      unsigned a[4];
-      ldmatrix_x4(a[0], a[1], a[2], a[3],
-                  sQ + (row_base + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + ks * 16 + (lane >> 4) * 8);
+      if (ks + 1 < KS_Q) load_k(ks + 1);
 #pragma unroll
       for (int np = 0; np < NT_S / 2; ++np) {
-        unsigned b0, b1, b2, b3;
-        ldmatrix_x4(b0, b1, b2, b3,
-                    tK + (np * 16 + (lane & 7) + (lane >> 4) * 8) * STRIDE + ks * 16 + ((lane >> 3) & 1) * 8);
-        mma_bf16(s[2 * np], a, b0, b1);
-        mma_bf16(s[2 * np + 1], a, b2, b3);
-      }
-    }
-
-    // mask, scale, online softmax.  A tile that every row of the block may read in full
-    // (inside the split, before the first row's position, inside the last row's window) needs
-    // no mask.
-    float mx_lo = -CUDART_INF_F, mx_hi = -CUDART_INF_F;
-    const bool full = base >= k_begin && base + KT <= k_end && base + KT - 1 <= pos_min &&
-                      (window <= 0 || base >= pos_max - window + 1);  // rows beyond the tile are never written out
-    if (full) {
 #pragma unroll
-      for (int nt = 0; nt < NT_S; ++nt) {
-        s[nt][0] *= scale_log2;
-        s[nt][1] *= scale_log2;
-        s[nt][2] *= scale_log2;
-        s[nt][3] *= scale_log2;
-        mx_lo = fmaxf(mx_lo, fmaxf(s[nt][0], s[nt][1]));
-        mx_hi = fmaxf(mx_hi, fmaxf(s[nt][2], s[nt][3]));
-      }
-    } else {
-#pragma unroll
-      for (int nt = 0; nt < NT_S; ++nt) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int key = base + nt * 8 + (lane & 3) * 2 + (e & 1);
-          const int pos = (e < 2) ? pos_lo : pos_hi;
-          const int lo = window > 0 ? max(pos - window + 1, k_begin) : k_begin;
-          const bool ok = pos >= 0 && key <= pos && key >= lo && key < k_end;
-          const float v = ok ? s[nt][e] * scale_log2 : -CUDART_INF_F;
-          s[nt][e] = v;
-          if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
+        for (int mt = 0; mt < MT; ++mt) {
+          mma_bf16(s[mt][2 * np], qf[mt][ks], bk[ks & 1][np][0], bk[ks & 1][np][1]);
+          mma_bf16(s[mt][2 * np + 1], qf[mt][ks], bk[ks & 1][np][2], bk[ks & 1][np][3]);
         }
       }
     }
-    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
-    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
-    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
-    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-    const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
-    const float mu_lo = (mn_lo == -CUDART_INF_F) ? 0.f : mn_lo;
-    const float mu_hi = (mn_hi == -CUDART_INF_F) ? 0.f : mn_hi;
-    const float al_lo = exp2f(m_lo - mu_lo), al_hi = exp2f(m_hi - mu_hi);
-    m_lo = mn_lo;
-    m_hi = mn_hi;
-    float sum_lo = 0.f, sum_hi = 0.f;
+    // the first V fragments travel while the softmax is computed
+    unsigned bv[2][NT_O / 2][4];
+    auto load_v = [&](int kk) {
 #pragma unroll
-    for (int nt = 0; nt < NT_S; ++nt) {
-      s[nt][0] = exp2f(s[nt][0] - mu_lo);
-      s[nt][1] = exp2f(s[nt][1] - mu_lo);
-      s[nt][2] = exp2f(s[nt][2] - mu_hi);
-      s[nt][3] = exp2f(s[nt][3] - mu_hi);
-      sum_lo += s[nt][0] + s[nt][1];
-      sum_hi += s[nt][2] + s[nt][3];
-    }
-    l_lo = l_lo * al_lo + sum_lo;
-    l_hi = l_hi * al_hi + sum_hi;
+      for (int np = 0; np < NT_O / 2; ++np)
+        ldmatrix_x4_trans(bv[kk & 1][np][0], bv[kk & 1][np][1], bv[kk & 1][np][2], bv[kk & 1][np][3],
+                          tV + kk * 16 * STRIDE + np * 16);
+    };
+    load_v(0);
+
+    // mask and online softmax; the scale is applied inside the exponent (one fused multiply-add
+    // per score).  A tile that every row of the block may read in full (inside the split, before
+    // the first row's position, inside the last row's window) needs no mask.
+    const bool full = base >= k_begin && base + KT <= k_end && base + KT - 1 <= pos_min &&
+                      (window <= 0 || base >= pos_max - window + 1);  // rows beyond the tile are never written out
+    unsigned pa[MT][KT / 16][4];  // P as bfloat16 A fragments
 #pragma unroll
-    for (int i = 0; i < NT_O; ++i) {
-      o[i][0] *= al_lo;
-      o[i][1] *= al_lo;
-      o[i][2] *= al_hi;
-      o[i][3] *= al_hi;
+    for (int mt = 0; mt < MT; ++mt) {
+      if (!full) {
+        const int pos_lo = s_pos[row_base + mt * 16 + r_lo], pos_hi = s_pos[row_base + mt * 16 + r_hi];
+#pragma unroll
+        for (int nt = 0; nt < NT_S; ++nt) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int key = base + nt * 8 + (lane & 3) * 2 + (e & 1);
+            const int pos = (e < 2) ? pos_lo : pos_hi;
+            const int lo = window > 0 ? max(pos - window + 1, k_begin) : k_begin;
+            const bool ok = pos >= 0 && key <= pos && key >= lo && key < k_end;
+            if (!ok) s[mt][nt][e] = -CUDART_INF_F;
+          }
+        }
+      }
+      float mx_lo = -CUDART_INF_F, mx_hi = -CUDART_INF_F;
+#pragma unroll
+      for (int nt = 0; nt < NT_S; ++nt) {
+        mx_lo = fmaxf(mx_lo, fmaxf(s[mt][nt][0], s[mt][nt][1]));
+        mx_hi = fmaxf(mx_hi, fmaxf(s[mt][nt][2], s[mt][nt][3]));
+      }
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+      const float mn_lo = fmaxf(m_lo[mt], mx_lo * scale_log2), mn_hi = fmaxf(m_hi[mt], mx_hi * scale_log2);  // scale > 0
+      const float mu_lo = (mn_lo == -CUDART_INF_F) ? 0.f : mn_lo;
+      const float mu_hi = (mn_hi == -CUDART_INF_F) ? 0.f : mn_hi;
+      const float al_lo = ex2_approx(m_lo[mt] - mu_lo), al_hi = ex2_approx(m_hi[mt] - mu_hi);
+      m_lo[mt] = mn_lo;
+      m_hi[mt] = mn_hi;
+      float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < NT_S; ++nt) {
+        const float p0 = ex2_approx(fmaf(s[mt][nt][0], scale_log2, -mu_lo));
+        const float p1 = ex2_approx(fmaf(s[mt][nt][1], scale_log2, -mu_lo));
+        const float p2 = ex2_approx(fmaf(s[mt][nt][2], scale_log2, -mu_hi));
+        const float p3 = ex2_approx(fmaf(s[mt][nt][3], scale_log2, -mu_hi));
+        sum_lo += p0 + p1;
+        sum_hi += p2 + p3;
+        pa[mt][nt / 2][(nt & 1) * 2] = pack_bf16(p0, p1);
+        pa[mt][nt / 2][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);
+      }
+      l_lo[mt] = l_lo[mt] * al_lo + sum_lo;
+      l_hi[mt] = l_hi[mt] * al_hi + sum_hi;
+      if (__any_sync(0xffffffffu, al_lo != 1.f || al_hi != 1.f)) {  // some row's maximum moved
+#pragma unroll
+        for (int i = 0; i < NT_O; ++i) {
+          o[mt][i][0] *= al_lo;
+          o[mt][i][1] *= al_lo;
+          o[mt][i][2] *= al_hi;
+          o[mt][i][3] *= al_hi;
+        }
+      }
     }
 
     // O += P V
 #pragma unroll
-    for (int kk = 0; kk < WKEYS / 16; ++kk) {
-      unsigned a[4];
-      a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-      a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-      a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-      a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+    for (int kk = 0; kk < KT / 16; ++kk) {
+      if (kk + 1 < KT / 16) load_v(kk + 1);
 #pragma unroll
       for (int np = 0; np < NT_O / 2; ++np) {
-        unsigned b0, b1, b2, b3;
-        ldmatrix_x4_trans(b0, b1, b2, b3,
-                          tV + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + np * 16 + (lane >> 4) * 8);
-        mma_bf16(o[2 * np], a, b0, b1);
-        mma_bf16(o[2 * np + 1], a, b2, b3);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          mma_bf16(o[mt][2 * np], pa[mt][kk], bv[kk & 1][np][0], bv[kk & 1][np][1]);
+          mma_bf16(o[mt][2 * np + 1], pa[mt][kk], bv[kk & 1][np][2], bv[kk & 1][np][3]);
+        }
       }
     }
   };
@@ -284,21 +363,29 @@ __global__ void __launch_bounds__(128)
       cp_async_commit();  // the first group also carries the Q rows
       cp_async_wait<0>();
       __syncthreads();
+      if (round0 == 0) load_q_fragments();
       if (round0 + warp < n_tiles) process_tile(warp, first_tile + (round0 + warp) * KT);
       __syncthreads();  // the tiles are overwritten by the next round
     }
-  } else {
+  } else if (n_tiles > 0) {
+    // Prompt tiles walk their keys from the last tile (the masked one on the diagonal) down to
+    // the first: row tiles that start together then read different parts of the cache.
+    const int last_tile = first_tile + (n_tiles - 1) * KT;
+    cp_async_commit();  // group 0: the Q rows
 #pragma unroll
     for (int st = 0; st < NSTAGE - 1; ++st) {
-      if (st < n_tiles) load_tile(st, first_tile + st * KT);
-      cp_async_commit();  // the first group also carries the Q rows
+      if (st < n_tiles) load_tile(st, last_tile - st * KT);
+      cp_async_commit();
     }
+    cp_async_wait<NSTAGE - 1>();  // all but the newest NSTAGE-1 groups: the Q rows are there
+    __syncthreads();
+    load_q_fragments();
     for (int it = 0; it < n_tiles; ++it) {
-      const int base = first_tile + it * KT;
-      // groups so far: (NSTAGE-1) + it; tile `it` has landed when at most NSTAGE-2 newer ones are pending
+      const int base = last_tile - it * KT;
+      // tile groups so far: (NSTAGE-1) + it; tile `it` has landed when at most NSTAGE-2 newer ones are pending
       cp_async_wait<NSTAGE - 2>();
       __syncthreads();  // tile `it` is visible to all; everyone is done with tile it-1, whose stage is refilled now
-      if (it + NSTAGE - 1 < n_tiles) load_tile((it + NSTAGE - 1) % NSTAGE, base + (NSTAGE - 1) * KT);
+      if (it + NSTAGE - 1 < n_tiles) load_tile((it + NSTAGE - 1) % NSTAGE, base - (NSTAGE - 1) * KT);
       cp_async_commit();
       process_tile(it % NSTAGE, base);
     }
@@ -307,40 +394,42 @@ __global__ void __launch_bounds__(128)
   cp_async_wait<0>();
   __syncthreads();
 
-  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
-  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
-  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
-  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
   constexpr float kLn2 = 0.6931471805599453f;
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+    l_lo[mt] += __shfl_xor_sync(0xffffffffu, l_lo[mt], 1);
+    l_lo[mt] += __shfl_xor_sync(0xffffffffu, l_lo[mt], 2);
+    l_hi[mt] += __shfl_xor_sync(0xffffffffu, l_hi[mt], 1);
+    l_hi[mt] += __shfl_xor_sync(0xffffffffu, l_hi[mt], 2);
+  }
 
   if constexpr (!SPLITW) {
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int r = row_base + (half ? r_hi : r_lo);
-      if (r >= n_rows) continue;
-      const float m = half ? m_hi : m_lo, l = half ? l_hi : l_lo;
-      const int t = tok0 + r / G, hq = hk * G + r % G;
-      if (n_splits == 1) {
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        bf16* dst = out + (static_cast<size_t>(t) * Hq + hq) * DH;
+    for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
-        for (int nt = 0; nt < NT_O; ++nt) {
-          const int d = nt * 8 + (lane & 3) * 2;
-          *reinterpret_cast<__nv_bfloat162*>(dst + d) =
-              __floats2bfloat162_rn(o[nt][half * 2] * inv, o[nt][half * 2 + 1] * inv);
-        }
-      } else {
-        const size_t pi = (static_cast<size_t>(t) * Hq + hq) * n_splits + z;
-        float* dst = part_o + pi * DH;
+      for (int half = 0; half < 2; ++half) {
+        const int r = row_base + mt * 16 + (half ? r_hi : r_lo);
+        if (r >= n_rows) continue;
+        const float m = half ? m_hi[mt] : m_lo[mt], l = half ? l_hi[mt] : l_lo[mt];
+        const int t = tok0 + r / G, hq = hk * G + r % G;
+        if (n_splits == 1) {
+          const float inv = l > 0.f ? 1.f / l : 0.f;
+          bf16* dst = out + (static_cast<size_t>(t) * Hq + hq) * DH;
 #pragma unroll
-        for (int nt = 0; nt < NT_O; ++nt) {
-          const int d = nt * 8 + (lane & 3) * 2;
-          dst[d] = o[nt][half * 2];
-          dst[d + 1] = o[nt][half * 2 + 1];
-        }
-        if ((lane & 3) == 0) {
-          part_ml[pi * 2] = m * kLn2;
-          part_ml[pi * 2 + 1] = l;
+          for (int nt = 0; nt < NT_O; ++nt) {
+            const int d = nt * 8 + (lane & 3) * 2;
+            *reinterpret_cast<__nv_bfloat162*>(dst + d) =
+                __floats2bfloat162_rn(o[mt][nt][half * 2] * inv, o[mt][nt][half * 2 + 1] * inv);
+          }
+        } else {
+          const size_t pi = (static_cast<size_t>(t) * Hq + hq) * n_splits + z;
+          float* dst = part_o + pi * DH;
+#pragma unroll
+          for (int nt = 0; nt < NT_O; ++nt) {
+            const int d = nt * 8 + (lane & 3) * 2;
+            *reinterpret_cast<float2*>(dst + d) = make_float2(o[mt][nt][half * 2], o[mt][nt][half * 2 + 1]);
+          }
+          if ((lane & 3) == 0) *reinterpret_cast<float2*>(part_ml + pi * 2) = make_float2(m * kLn2, l);
         }
       }
     }
@@ -349,10 +438,10 @@ __global__ void __launch_bounds__(128)
     constexpr int SO = DH + 4;                 // padded row: rows g and g+1 fall into different banks
     float* sO = reinterpret_cast<float*>(sK);  // [4 warps][16][SO], K/V tiles are no longer needed
     if ((lane & 3) == 0) {
-      s_wm[warp][r_lo] = m_lo;
-      s_wm[warp][r_hi] = m_hi;
-      s_wl[warp][r_lo] = l_lo;
-      s_wl[warp][r_hi] = l_hi;
+      s_wm[warp][r_lo] = m_lo[0];
+      s_wm[warp][r_hi] = m_hi[0];
+      s_wl[warp][r_lo] = l_lo[0];
+      s_wl[warp][r_hi] = l_hi[0];
     }
     __syncthreads();
     if (tid < 16) {
@@ -368,13 +457,13 @@ __global__ void __launch_bounds__(128)
     {
       const float mu_lo = (s_M[r_lo] == -CUDART_INF_F) ? 0.f : s_M[r_lo];
       const float mu_hi = (s_M[r_hi] == -CUDART_INF_F) ? 0.f : s_M[r_hi];
-      const float f_lo = exp2f(m_lo - mu_lo), f_hi = exp2f(m_hi - mu_hi);
+      const float f_lo = exp2f(m_lo[0] - mu_lo), f_hi = exp2f(m_hi[0] - mu_hi);
       float* mine = sO + warp * 16 * SO;
 #pragma unroll
       for (int nt = 0; nt < NT_O; ++nt) {
         const int d = nt * 8 + (lane & 3) * 2;
-        *reinterpret_cast<float2*>(mine + r_lo * SO + d) = make_float2(o[nt][0] * f_lo, o[nt][1] * f_lo);
-        *reinterpret_cast<float2*>(mine + r_hi * SO + d) = make_float2(o[nt][2] * f_hi, o[nt][3] * f_hi);
+        *reinterpret_cast<float2*>(mine + r_lo * SO + d) = make_float2(o[0][nt][0] * f_lo, o[0][nt][1] * f_lo);
+        *reinterpret_cast<float2*>(mine + r_hi * SO + d) = make_float2(o[0][nt][2] * f_hi, o[0][nt][3] * f_hi);
       }
     }
     __syncthreads();
@@ -400,45 +489,57 @@ __global__ void __launch_bounds__(128)
   // second launch is needed.  The counter returns to zero for the next use.
   if (n_splits > 1 && split_counter != nullptr) {
     __shared__ int s_last;
-    __shared__ float s_w[4][64];
     __threadfence();
     __syncthreads();
-    int* counter = split_counter + static_cast<size_t>(blockIdx.x) * gridDim.y + hk;
+    int* counter = split_counter + static_cast<size_t>(tile_id) * gridDim.y + hk;
     if (tid == 0) s_last = (atomicAdd(counter, 1) == n_splits - 1);
     __syncthreads();
     if (!s_last) return;
     __threadfence();
     if (tid == 0) *counter = 0;
-    for (int r = warp; r < n_rows; r += 4) {
+    // pass 1, a thread per row: the largest maximum among the splits and the merged sum
+    if (tid < n_rows) {
+      const int t = tok0 + tid / G, hq = hk * G + tid % G;
+      const float* ml = part_ml + (static_cast<size_t>(t) * Hq + hq) * n_splits * 2;
+      float mx = -CUDART_INF_F;
+      for (int zz = 0; zz < n_splits; ++zz) {
+        const float2 v = __ldcg(reinterpret_cast<const float2*>(ml) + zz);
+        if (v.y > 0.f) mx = fmaxf(mx, v.x);
+      }
+      float tot = 0.f;
+      for (int zz = 0; zz < n_splits; ++zz) {
+        const float2 v = __ldcg(reinterpret_cast<const float2*>(ml) + zz);
+        if (v.y > 0.f) tot += expf(v.x - mx) * v.y;
+      }
+      s_M[tid] = mx;
+      s_L[tid] = tot > 0.f ? 1.f / tot : 0.f;
+    }
+    __syncthreads();
+    // pass 2, a thread per (row, four columns): the weighted sum over the splits
+    constexpr int C4 = DH / 4;
+    for (int i = tid; i < n_rows * C4; i += 128) {
+      const int r = i / C4, d = (i % C4) * 4;
       const int t = tok0 + r / G, hq = hk * G + r % G;
       const size_t row = static_cast<size_t>(t) * Hq + hq;
-      const float* ml = part_ml + row * n_splits * 2;
-      float mx = -CUDART_INF_F;
-      for (int zz = lane; zz < n_splits; zz += 32)
-        if (__ldcg(ml + 2 * zz + 1) > 0.f) mx = fmaxf(mx, __ldcg(ml + 2 * zz));
-      mx = warp_max(mx);
-      float tot = 0.f;
-      for (int zz = lane; zz < n_splits; zz += 32) {
-        const float l = __ldcg(ml + 2 * zz + 1);
-        const float wz = l > 0.f ? expf(__ldcg(ml + 2 * zz) - mx) : 0.f;
-        s_w[warp][zz] = wz;
-        tot += wz * l;
+      const float2* ml = reinterpret_cast<const float2*>(part_ml + row * n_splits * 2);
+      const float* po = part_o + row * n_splits * DH + d;
+      const float mx = s_M[r];
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+      for (int zz = 0; zz < n_splits; ++zz) {
+        const float2 v = __ldcg(ml + zz);
+        const float4 x = __ldcg(reinterpret_cast<const float4*>(po + static_cast<size_t>(zz) * DH));
+        const float w = v.y > 0.f ? expf(v.x - mx) : 0.f;
+        a.x += w * x.x;
+        a.y += w * x.y;
+        a.z += w * x.z;
+        a.w += w * x.w;
       }
-      tot = warp_sum(tot);
-      __syncwarp();
-      const float inv = tot > 0.f ? 1.f / tot : 0.f;
-      const float* po = part_o + row * n_splits * DH;
-      for (int d = lane; d < DH; d += 32) {
-        float a0 = 0.f, a1 = 0.f;
-        int zz = 0;
-        for (; zz + 2 <= n_splits; zz += 2) {
-          a0 += s_w[warp][zz] * __ldcg(po + static_cast<size_t>(zz) * DH + d);
-          a1 += s_w[warp][zz + 1] * __ldcg(po + static_cast<size_t>(zz + 1) * DH + d);
-        }
-        if (zz < n_splits) a0 += s_w[warp][zz] * __ldcg(po + static_cast<size_t>(zz) * DH + d);
-        out[row * DH + d] = __float2bfloat16_rn((a0 + a1) * inv);
-      }
-      __syncwarp();
+      const float inv = s_L[r];
+      uint2 packed;
+      packed.x = pack_bf16(a.x * inv, a.y * inv);
+      packed.y = pack_bf16(a.z * inv, a.w * inv);
+      *reinterpret_cast<uint2*>(out + row * DH + d) = packed;
     }
   }
 }
@@ -488,15 +589,15 @@ __global__ void __launch_bounds__(128)
   }
 }
 
-template <int DH, bool SPLITW>
+template <int DH, bool SPLITW, int MT>
 int launch_flash(const void* q, const void* pool, const int* block_table, int max_blocks,
                  const int* positions, const int* cu, void* out, float* part_o, float* part_ml,
                  float scale, int window, int split_len, int n_splits, int page_size, int n_seq,
                  int n_tiles, int Hq, int Hkv, int* split_counter, cudaStream_t stream) {
-  constexpr int M = SPLITW ? 16 : 64;
-  constexpr int NSTAGE = SPLITW ? 4 : 2;
+  constexpr int M = SPLITW ? 16 : 64 * MT;
+  constexpr int NSTAGE = flash_stages(DH, SPLITW);
   const size_t smem = static_cast<size_t>(M + 2 * NSTAGE * kFlashKeys) * (DH + 8) * sizeof(bf16);
-  auto kern = flash_paged_kernel<DH, SPLITW>;
+  auto kern = flash_paged_kernel<DH, SPLITW, MT>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
@@ -518,8 +619,8 @@ PMM_EXPORT int pmm_flash_supported(int Hq, int Hkv, int Dh) {
   return (Dh == 16 || Dh == 32 || Dh == 64 || Dh == 128) && G <= 64 ? 1 : 0;
 }
 
-// n_tiles: number of row tiles = sum over sequences of ceil(new tokens / (M / G)), with
-// M = 16 when rows16 != 0 (every sequence brings at most 16/G tokens) else 64.
+// tile_rows M: 16 (every sequence brings at most 16/G tokens: decode), 64, or 128 (head sizes
+// up to 64).  n_tiles: number of row tiles = sum over sequences of ceil(new tokens / (M / G)).
 // split_counter: nullptr (the caller merges key splits with pmm_flash_combine), or
 // n_tiles*Hkv ints that are zero between calls: then the last block of every tile merges
 // its splits (at most 64 of them) and writes `out` itself.
@@ -527,25 +628,34 @@ PMM_EXPORT int pmm_flash_paged_attention(const void* q, const void* pool, const 
                                          int max_blocks, const int* positions, const int* cu,
                                          void* out, float* part_o, float* part_ml, float scale,
                                          int window, int split_len, int n_splits, int page_size,
-                                         int n_seq, int n_tiles, int rows16, int Hq, int Hkv, int Dh,
+                                         int n_seq, int n_tiles, int tile_rows, int Hq, int Hkv, int Dh,
                                          int* split_counter, cudaStream_t stream) {
   if (n_seq <= 0 || n_tiles <= 0) return 0;
   if (!pmm_flash_supported(Hq, Hkv, Dh) || page_size <= 0 || n_splits < 1 || n_splits > 65535 ||
       Hkv > 65535)
     return PMM_ERR_BAD_ARGUMENT;
-  if (rows16 && Hq / Hkv > 16) return PMM_ERR_BAD_ARGUMENT;
+  if (tile_rows != 16 && tile_rows != 64 && tile_rows != 128) return PMM_ERR_BAD_ARGUMENT;
+  if (Hq / Hkv > tile_rows || (tile_rows == 128 && Dh > 64)) return PMM_ERR_BAD_ARGUMENT;
+  if (!(scale > 0.f)) return PMM_ERR_BAD_ARGUMENT;  // the maximum is taken before the scale is applied
   if (n_splits > 1 && (!part_o || !part_ml || split_len <= 0)) return PMM_ERR_BAD_ARGUMENT;
   if (split_counter && n_splits > 64) return PMM_ERR_BAD_ARGUMENT;
   if (n_splits == 1) split_len = 0x40000000;
   int rc;
-#define PMM_FLASH_CASE(DH)                                                                          \
-  rc = rows16 ? pmm::launch_flash<DH, true>(q, pool, block_table, max_blocks, positions, cu, out,   \
-                                            part_o, part_ml, scale, window, split_len, n_splits,    \
-                                            page_size, n_seq, n_tiles, Hq, Hkv, split_counter,      \
-                                            stream)                                                 \
-              : pmm::launch_flash<DH, false>(q, pool, block_table, max_blocks, positions, cu, out,  \
-                                             part_o, part_ml, scale, window, split_len, n_splits,   \
-                                             page_size, n_seq, n_tiles, Hq, Hkv, split_counter, stream)
+#define PMM_FLASH_ARGS                                                                                  \
+  q, pool, block_table, max_blocks, positions, cu, out, part_o, part_ml, scale, window, split_len,      \
+      n_splits, page_size, n_seq, n_tiles, Hq, Hkv, split_counter, stream
+#define PMM_FLASH_CASE(DH)                                                            \
+  rc = tile_rows == 16 ? pmm::launch_flash<DH, true, 1>(PMM_FLASH_ARGS)               \
+                       : pmm::launch_flash<DH, false, 1>(PMM_FLASH_ARGS)
+  if (tile_rows == 128) {
+    switch (Dh) {
+      case 16: rc = pmm::launch_flash<16, false, 2>(PMM_FLASH_ARGS); break;
+      case 32: rc = pmm::launch_flash<32, false, 2>(PMM_FLASH_ARGS); break;
+      case 64: rc = pmm::launch_flash<64, false, 2>(PMM_FLASH_ARGS); break;
+      default: return PMM_ERR_BAD_ARGUMENT;
+    }
+    return rc;
+  }
   switch (Dh) {
     case 16: PMM_FLASH_CASE(16); break;
     case 32: PMM_FLASH_CASE(32); break;
@@ -553,6 +663,7 @@ PMM_EXPORT int pmm_flash_paged_attention(const void* q, const void* pool, const 
     case 128: PMM_FLASH_CASE(128); break;
     default: return PMM_ERR_BAD_ARGUMENT;
   }
+#undef PMM_FLASH_ARGS
 #undef PMM_FLASH_CASE
   return rc;
 }

@@ -10,7 +10,7 @@ extern "C" int pmm_flash_paged_attention(const void* q, const void* pool, const 
                                          int max_blocks, const int* positions, const int* cu, void* out,
                                          float* part_o, float* part_ml, float scale, int window,
                                          int split_len, int n_splits, int page_size, int n_seq, int n_tiles,
-                                         int rows16, int Hq, int Hkv, int Dh, int* split_counter,
+                                         int tile_rows, int Hq, int Hkv, int Dh, int* split_counter,
                                          cudaStream_t stream);
 extern "C" int pmm_flash_combine(const float* part_o, const float* part_ml, void* out, int n_rows,
                                  int n_splits, int Dh, int dtype, cudaStream_t stream);
@@ -63,7 +63,7 @@ PMM_EXPORT int pmm_attention_noalloc(const void* q, const void* pool, const int*
     return fail(PMM_ERR_BAD_ARGUMENT, "head shape or split count outside what the kernel supports");
   if (n_splits == 1)  // no partial results, so no scratch: the regular path allocates nothing either
     return pmm_flash_paged_attention(q, pool, block_table, max_blocks, positions, cu, out, nullptr, nullptr,
-                                     scale, window, split_len, 1, page_size, n_seq, n_tiles, rows16, Hq, Hkv,
+                                     scale, window, split_len, 1, page_size, n_seq, n_tiles, rows16 ? 16 : 64, Hq, Hkv,
                                      Dh, nullptr, stream);
   const long long rows = static_cast<long long>(n_tokens) * Hq;
   const long long need = rows * n_splits * (Dh + 2);
@@ -77,7 +77,7 @@ PMM_EXPORT int pmm_attention_noalloc(const void* q, const void* pool, const int*
   float* part_o = scratch;
   float* part_ml = scratch + rows * n_splits * Dh;
   int rc = pmm_flash_paged_attention(q, pool, block_table, max_blocks, positions, cu, out, part_o, part_ml, scale,
-                                     window, split_len, n_splits, page_size, n_seq, n_tiles, rows16, Hq, Hkv, Dh,
+                                     window, split_len, n_splits, page_size, n_seq, n_tiles, rows16 ? 16 : 64, Hq, Hkv, Dh,
                                      nullptr, stream);
   if (rc != 0) return fail(rc, "attention launch failed (code %lld)", rc);
   rc = pmm_flash_combine(part_o, part_ml, out, static_cast<int>(rows), n_splits, Dh, PMM_DTYPE_BF16, stream);

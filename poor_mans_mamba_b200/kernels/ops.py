@@ -482,17 +482,33 @@ def flash_supported(n_q_heads: int, n_kv_heads: int, head_dim: int) -> bool:
     return bool(_fn("pmm_flash_supported")(n_q_heads, n_kv_heads, head_dim))
 
 
+def flash_tile_rows(n_q_heads: int, n_kv_heads: int, head_dim: int, new_lens: Sequence[int]) -> int:
+    """Rows of (token, query head of a group) that one block of the tensor-core attention kernel
+    takes: 16 when every sequence brings at most 16 of them (decode), 128 for long portions of
+    head sizes up to 64 (each key/value fragment then feeds two row tiles), else 64."""
+    group = n_q_heads // n_kv_heads
+    if group <= 16 and max(new_lens) * group <= 16:
+        return 16
+    if head_dim <= 64 and sum(new_lens) * n_q_heads >= _FLASH_128_FROM_ROWS:
+        return 128
+    return 64
+
+
+_FLASH_128_FROM_ROWS = 49152  # measured: 64 rows a block are faster at 16k rows, 128 at 64k
+
+
 def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Tensor, seq_of: Tensor,
                     out: Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int, softmax_scale: float,
                     window: int = 0, n_splits: int = 1, split_len: int = 0,
                     scratch: Optional[Tensor] = None, cu_seqlens: Optional[Tensor] = None,
                     new_lens: Optional[Sequence[int]] = None, use_tensor_cores: bool = True,
-                    split_counter: Optional[Tensor] = None) -> None:
+                    split_counter: Optional[Tensor] = None, tile_rows: Optional[int] = None) -> None:
     """Causal attention of every token over keys lo..pos of its request in the paged cache.
     With ``cu_seqlens`` and ``new_lens`` (tokens per sequence, host values) a bfloat16 cache of a
     supported shape goes to the tensor-core kernel; everything else to the float kernel.
     ``split_counter`` (int32, zero between calls, at least tiles x kv heads entries) lets the
-    tensor-core kernel merge its key splits itself instead of in a second launch."""
+    tensor-core kernel merge its key splits itself instead of in a second launch.  ``tile_rows``
+    (rows of (token, query head of a group) per block: 16, 64 or 128) defaults to flash_tile_rows."""
     _cuda(q, pool, block_table, positions, seq_of, out, scratch, cu_seqlens)
     check_head_dim(head_dim)
     T = q.shape[0]
@@ -518,8 +534,12 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
     if flash:
         _i32(cu_seqlens, "attention: cu_seqlens")
         group = n_q_heads // n_kv_heads
-        rows16 = group <= 16 and max(new_lens) * group <= 16
-        tokens_per_tile = (16 if rows16 else 64) // group
+        if tile_rows is None:
+            tile_rows = flash_tile_rows(n_q_heads, n_kv_heads, head_dim, new_lens)
+        _need(tile_rows in (16, 64, 128) and group <= tile_rows and (tile_rows < 128 or head_dim <= 64)
+              and (tile_rows > 16 or max(new_lens) * group <= 16),
+              f"attention: {tile_rows} rows per block do not fit this shape")
+        tokens_per_tile = tile_rows // group
         n_tiles = sum((n + tokens_per_tile - 1) // tokens_per_tile for n in new_lens)
         counter = None
         if (split_counter is not None and 1 < n_splits <= 64 and split_counter.numel() >= n_tiles * n_kv_heads):
@@ -529,7 +549,7 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
         _call("pmm_flash_paged_attention", q.data_ptr(), pool.data_ptr(), block_table.data_ptr(),
               block_table.shape[1], positions.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(), part_o,
               part_ml, float(softmax_scale), int(window), int(split_len), int(n_splits), pool.shape[2],
-              len(new_lens), n_tiles, int(rows16), n_q_heads, n_kv_heads, head_dim, counter, _stream())
+              len(new_lens), n_tiles, int(tile_rows), n_q_heads, n_kv_heads, head_dim, counter, _stream())
         if counter is not None:
             return
     else:

@@ -147,7 +147,7 @@ class PagedAttention(Mixer):
         when few tokens are in flight, one when the tokens alone do."""
         group = self.num_heads // self.num_kv_heads
         if dtype == torch.bfloat16 and K.flash_supported(self.num_heads, self.num_kv_heads, self.head_dim):
-            rows = 16 if (group <= 16 and max(new_lens) * group <= 16) else 64
+            rows = K.flash_tile_rows(self.num_heads, self.num_kv_heads, self.head_dim, new_lens)
             per_tile = rows // group
             blocks = sum((n + per_tile - 1) // per_tile for n in new_lens) * self.num_kv_heads
             min_len = 256 if rows == 16 else 64

@@ -34,7 +34,7 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, lon
     for (int i = 0; i < 4; ++i) {
       const float2 g = __bfloat1622float2(g2[i]);
       const float2 u = __bfloat1622float2(u2[i]);
-      o2[i] = __floats2bfloat162_rn(silu_f(g.x * gate_mult) * u.x, silu_f(g.y * gate_mult) * u.y);
+      o2[i] = __floats2bfloat162_rn(silu_fast(g.x * gate_mult) * u.x, silu_fast(g.y * gate_mult) * u.y);
     }
     *reinterpret_cast<uint4*>(o + f) = ov;
   }

@@ -45,6 +45,9 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+// For results that are stored as bfloat16: relative error about 1e-6, three instructions' worth
+// of special-function work instead of a full-precision exponential and division.
+__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.f + __expf(-x)); }
 
 // v if v>20; exp(v) if v<-20; log1p(exp(v)) otherwise.
 __device__ __forceinline__ float softplus_f(float v) {

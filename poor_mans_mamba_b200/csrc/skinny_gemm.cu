@@ -293,7 +293,7 @@ __global__ void __launch_bounds__(kSgThreads) skinny_gemm_kernel(const SkinnyArg
           const int f = n0 + g + (e >> 1) * 8, m = nt * 8 + t2 + (e & 1);
           if (f < args.N && m < M) {
             const float up = sRed[(g + (e >> 1) * 8) * MP + m];
-            args.y[static_cast<size_t>(m) * args.ldy + f] = __float2bfloat16_rn(silu_f(acc[nt][e] * pr.scale) * up);
+            args.y[static_cast<size_t>(m) * args.ldy + f] = __float2bfloat16_rn(silu_fast(acc[nt][e] * pr.scale) * up);
           }
         }
       }

@@ -6,9 +6,12 @@
 //   y_i   = sum_{j<=i} (C_i.B_j) exp(cs_i-cs_j) delta_j x_j  +  exp(cs_i) (C_i . S)  +  D x_i
 //   S_end = exp(cs_last) S  +  sum_j exp(cs_last-cs_j) delta_j B_j x_j^T
 // Three launches, all parallel over chunks except the cheap middle one:
-//   1. ssd_chunk_state:  local term of S_end and exp(cs_last) per (chunk, head)   -> scratch
-//   2. ssd_state_pass:   walks a sequence's chunks: scratch[c] <- state at the start of
-//                        chunk c (the request's saved state for c = 0), final state -> slot
+//   1. ssd_chunk_state:  local term of S_end and exp(cs_last) per (chunk, head)   -> scratch;
+//                        extra blocks of the same launch form C B^T per (chunk, group), which
+//                        all heads of a group share                                -> scratch
+//   2. ssd_state_pass:   walks a sequence's chunks in float: start[c] <- state at the start of
+//                        chunk c (the request's saved state for c = 0) as bfloat16, the form
+//                        in which phase 3 multiplies it; final state -> slot (float)
 //   3. ssd_chunk_output: y for every token from C, B, x and the chunk's start state
 // All differences of cs are <= 0, so no exponential overflows; delta, cs and every
 // accumulator are float; the start state is rounded to bfloat16 only as an MMA operand.
@@ -105,25 +108,75 @@ __device__ __forceinline__ void ssd_delta_cumsum(const bf16* __restrict__ dt_raw
 }
 
 // ----------------------------------------------------------------------------- phase 1
+// Blocks with blockIdx.y < H: the local state of (chunk, head).  Blocks with blockIdx.y >= H:
+// the products C_i . B_j of (chunk, group blockIdx.y - H), float [64][64], for phase 3.
 template <int P, int N>
 __global__ void __launch_bounds__(128)
     ssd_chunk_state_kernel(const bf16* __restrict__ xbc, int ld_xbc, const bf16* __restrict__ dt_raw,
                            long long ld_dt, float dt_scale, const float* __restrict__ dt_shift,
                            const float* __restrict__ a_log, const int* __restrict__ cu, int n_seq,
-                           float* __restrict__ chunk_state, float* __restrict__ chunk_decay, int H, int G) {
+                           float* __restrict__ chunk_state, float* __restrict__ chunk_decay,
+                           float* __restrict__ chunk_cb, int H, int G) {
   constexpr int SX = P + 8, SB = N + 8;
   constexpr int NB = N < 64 ? N : 64;  // columns of the state per work unit
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* sX = reinterpret_cast<bf16*>(smem_raw);
-  bf16* sB = sX + kQ * SX;
   __shared__ float s_delta[kQ], s_cs[kQ], s_w[kQ];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int c = blockIdx.x, h = blockIdx.y;
+  const int c = blockIdx.x;
   int seq, t0, len, first;
   if (!ssd_locate(cu, n_seq, c, seq, t0, len, first)) return;
-  const int I = H * P, g = h / (H / G);
+  const int I = H * P;
 
+  if (static_cast<int>(blockIdx.y) >= H) {
+    const int g = blockIdx.y - H;
+    bf16* sC = reinterpret_cast<bf16*>(smem_raw);
+    bf16* sBg = sC + kQ * SB;
+    for (int i = tid; i < kQ * (N / 8); i += 128) {
+      const int r = i / (N / 8), col = i % (N / 8);
+      const bool ok = r < len;
+      const size_t row = ok ? static_cast<size_t>(t0 + r) * ld_xbc : 0;
+      ssd_cp_async16(sBg + r * SB + col * 8, xbc + row + (ok ? I + g * N + col * 8 : 0), ok);
+      ssd_cp_async16(sC + r * SB + col * 8, xbc + row + (ok ? I + G * N + g * N + col * 8 : 0), ok);
+    }
+    ssd_cp_async_wait_all();
+    __syncthreads();
+    float gacc[kQ / 8][4];
+#pragma unroll
+    for (int i = 0; i < kQ / 8; ++i) gacc[i][0] = gacc[i][1] = gacc[i][2] = gacc[i][3] = 0.f;
+    const bf16* c_lane = sC + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SB + (lane >> 4) * 8;
+    const bf16* b_lane = sBg + ((lane & 7) + (lane >> 4) * 8) * SB + ((lane >> 3) & 1) * 8;
+#pragma unroll 2
+    for (int ks = 0; ks < N / 16; ++ks) {
+      unsigned a[4];
+      ssd_ldm(a[0], a[1], a[2], a[3], c_lane + ks * 16);
+#pragma unroll
+      for (int np = 0; np < kQ / 16; ++np) {
+        if (np <= warp) {  // only the tokens up to this warp's diagonal block are read later
+          unsigned b0, b1, b2, b3;
+          ssd_ldm(b0, b1, b2, b3, b_lane + np * 16 * SB + ks * 16);
+          ssd_mma(gacc[2 * np], a, b0, b1);
+          ssd_mma(gacc[2 * np + 1], a, b2, b3);
+        }
+      }
+    }
+    float* dst = chunk_cb + (static_cast<size_t>(c) * G + g) * kQ * kQ;
+    const int i_lo = warp * 16 + (lane >> 2);
+#pragma unroll
+    for (int nt = 0; nt < kQ / 8; ++nt) {
+      if (nt / 2 <= warp) {
+        const int j = nt * 8 + (lane & 3) * 2;
+        *reinterpret_cast<float2*>(dst + i_lo * kQ + j) = make_float2(gacc[nt][0], gacc[nt][1]);
+        *reinterpret_cast<float2*>(dst + (i_lo + 8) * kQ + j) = make_float2(gacc[nt][2], gacc[nt][3]);
+      }
+    }
+    return;
+  }
+
+  const int h = blockIdx.y;
+  const int g = h / (H / G);
+  bf16* sX = reinterpret_cast<bf16*>(smem_raw);
+  bf16* sB = sX + kQ * SX;
   for (int i = tid; i < kQ * (P / 8); i += 128) {
     const int r = i / (P / 8), col = i % (P / 8);
     const bool ok = r < len;
@@ -139,6 +192,13 @@ __global__ void __launch_bounds__(128)
   if (tid == 0) chunk_decay[static_cast<size_t>(c) * H + h] = expf(s_cs[kQ - 1]);
   ssd_cp_async_wait_all();
   __syncthreads();
+  // x_j <- w_j x_j once for the block (the product is rounded to bfloat16 as an mma operand)
+  for (int i = tid; i < kQ * (P / 2); i += 128) {
+    const int r = i / (P / 2), col = (i % (P / 2)) * 2;
+    unsigned* px = reinterpret_cast<unsigned*>(sX + r * SX + col);
+    *px = ssd_scale2(*px, s_w[r], s_w[r]);
+  }
+  __syncthreads();
 
   float* dst = chunk_state + (static_cast<size_t>(c) * H + h) * P * N;
   constexpr int UNITS = (P / 16) * (N / NB);
@@ -147,23 +207,25 @@ __global__ void __launch_bounds__(128)
     float acc[NB / 8][4];
 #pragma unroll
     for (int i = 0; i < NB / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    // fragments of step ks+1 are requested before the products of step ks
+    unsigned fa[2][4], fb[2][NB / 16][4];
+    auto load_frag = [&](int ks) {
+      // A[m = p][k = token] from sX[token][p]: transposed 8x8 loads
+      ssd_ldm_t(fa[ks & 1][0], fa[ks & 1][1], fa[ks & 1][2], fa[ks & 1][3],
+                sX + (ks * 16 + (lane >> 4) * 8 + (lane & 7)) * SX + mt * 16 + ((lane >> 3) & 1) * 8);
+#pragma unroll
+      for (int np = 0; np < NB / 16; ++np)
+        ssd_ldm_t(fb[ks & 1][np][0], fb[ks & 1][np][1], fb[ks & 1][np][2], fb[ks & 1][np][3],
+                  sB + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SB + nb * NB + np * 16 + (lane >> 4) * 8);
+    };
+    load_frag(0);
 #pragma unroll
     for (int ks = 0; ks < kQ / 16; ++ks) {
-      unsigned a[4];
-      // A[m = p][k = token] from sX[token][p]: transposed 8x8 loads
-      ssd_ldm_t(a[0], a[1], a[2], a[3], sX + (ks * 16 + (lane >> 4) * 8 + (lane & 7)) * SX + mt * 16 + ((lane >> 3) & 1) * 8);
-      const int k0 = ks * 16 + (lane & 3) * 2;
-      const float w0 = s_w[k0], w1 = s_w[k0 + 1], w8 = s_w[k0 + 8], w9 = s_w[k0 + 9];
-      a[0] = ssd_scale2(a[0], w0, w1);
-      a[1] = ssd_scale2(a[1], w0, w1);
-      a[2] = ssd_scale2(a[2], w8, w9);
-      a[3] = ssd_scale2(a[3], w8, w9);
+      if (ks + 1 < kQ / 16) load_frag(ks + 1);
 #pragma unroll
       for (int np = 0; np < NB / 16; ++np) {
-        unsigned b0, b1, b2, b3;
-        ssd_ldm_t(b0, b1, b2, b3, sB + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SB + nb * NB + np * 16 + (lane >> 4) * 8);
-        ssd_mma(acc[2 * np], a, b0, b1);
-        ssd_mma(acc[2 * np + 1], a, b2, b3);
+        ssd_mma(acc[2 * np], fa[ks & 1], fb[ks & 1][np][0], fb[ks & 1][np][1]);
+        ssd_mma(acc[2 * np + 1], fa[ks & 1], fb[ks & 1][np][2], fb[ks & 1][np][3]);
       }
     }
     const int p_lo = mt * 16 + (lane >> 2);
@@ -177,9 +239,9 @@ __global__ void __launch_bounds__(128)
 }
 
 // ----------------------------------------------------------------------------- phase 2
-__global__ void ssd_state_pass_kernel(float* __restrict__ chunk_state, const float* __restrict__ chunk_decay,
-                                      float* __restrict__ state, const int* __restrict__ cu,
-                                      const int* __restrict__ slots, int H, int PN) {
+__global__ void ssd_state_pass_kernel(const float* __restrict__ chunk_state, const float* __restrict__ chunk_decay,
+                                      bf16* __restrict__ start_state, float* __restrict__ state,
+                                      const int* __restrict__ cu, const int* __restrict__ slots, int H, int PN) {
   // four state elements per thread (P*N is a multiple of 4 for every compiled pair)
   const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
   const int h = blockIdx.y, seq = blockIdx.z;
@@ -190,8 +252,7 @@ __global__ void ssd_state_pass_kernel(float* __restrict__ chunk_state, const flo
   if (nc <= 0) return;
   float4* sp = reinterpret_cast<float4*>(state + (static_cast<size_t>(slots[seq]) * H + h) * PN + e);
   float4 s = *sp;
-  // The chain through s is short; the loads are what cost.  They are issued eight chunks
-  // ahead of the stores (each address is read before it is written, by this thread only).
+  // The chain through s is short; the loads are what cost: eight chunks are requested at a time.
   constexpr int kAhead = 8;
   for (int c0 = 0; c0 < nc; c0 += kAhead) {
     float4 local[kAhead];
@@ -207,7 +268,10 @@ __global__ void ssd_state_pass_kernel(float* __restrict__ chunk_state, const flo
     for (int i = 0; i < kAhead; ++i) {
       if (c0 + i < nc) {
         const size_t ch = static_cast<size_t>(first + c0 + i) * H + h;
-        *reinterpret_cast<float4*>(chunk_state + ch * PN + e) = s;  // the state at the start of this chunk
+        uint2 packed;  // the state at the start of this chunk
+        packed.x = ssd_pack(s.x, s.y);
+        packed.y = ssd_pack(s.z, s.w);
+        *reinterpret_cast<uint2*>(start_state + ch * PN + e) = packed;
         s.x = s.x * decay[i] + local[i].x;
         s.y = s.y * decay[i] + local[i].y;
         s.z = s.z * decay[i] + local[i].z;
@@ -224,15 +288,14 @@ __global__ void __launch_bounds__(128)
     ssd_chunk_output_kernel(const bf16* __restrict__ xbc, int ld_xbc, const bf16* __restrict__ dt_raw,
                             long long ld_dt, float dt_scale, const float* __restrict__ dt_shift,
                             const float* __restrict__ a_log, const float* __restrict__ d_skip,
-                            const int* __restrict__ cu, int n_seq, const float* __restrict__ chunk_state,
-                            bf16* __restrict__ y, int H, int G, const bf16* __restrict__ z_raw, long long ld_z,
+                            const int* __restrict__ cu, int n_seq, const bf16* __restrict__ start_state,
+                            const float* __restrict__ chunk_cb, bf16* __restrict__ y, int H, int G, const bf16* __restrict__ z_raw, long long ld_z,
                             float z_scale, const float* __restrict__ z_bias) {
   constexpr int SX = P + 8, SN = N + 8;
   constexpr int PB = P < 64 ? P : 64;  // output columns per pass
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sC = reinterpret_cast<bf16*>(smem_raw);
-  bf16* sB = sC + kQ * SN;
-  bf16* sS = sB + kQ * SN;   // [P][SN] start state, bfloat16
+  bf16* sS = sC + kQ * SN;   // [P][SN] start state, bfloat16
   bf16* sX = sS + P * SN;    // [kQ][SX]
   __shared__ float s_delta[kQ], s_cs[kQ];
 
@@ -246,7 +309,6 @@ __global__ void __launch_bounds__(128)
     const int r = i / (N / 8), col = i % (N / 8);
     const bool ok = r < len;
     const size_t row = ok ? static_cast<size_t>(t0 + r) * ld_xbc : 0;
-    ssd_cp_async16(sB + r * SN + col * 8, xbc + row + (ok ? I + g * N + col * 8 : 0), ok);
     ssd_cp_async16(sC + r * SN + col * 8, xbc + row + (ok ? I + G * N + g * N + col * 8 : 0), ok);
   }
   for (int i = tid; i < kQ * (P / 8); i += 128) {
@@ -255,25 +317,10 @@ __global__ void __launch_bounds__(128)
     ssd_cp_async16(sX + r * SX + col * 8, xbc + (ok ? static_cast<size_t>(t0 + r) * ld_xbc + h * P + col * 8 : 0), ok);
   }
   {
-    const float* src = chunk_state + (static_cast<size_t>(c) * H + h) * P * N;
-    constexpr int kQuads = P * N / 4;  // float4 pieces, a multiple of 4 * 128 for every compiled pair but (16,16)
-    for (int i0 = tid; i0 < kQuads; i0 += 4 * 128) {
-      float4 v[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int i = i0 + u * 128;
-        v[u] = i < kQuads ? __ldcs(reinterpret_cast<const float4*>(src) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int i = i0 + u * 128;
-        if (i < kQuads) {
-          const int p = (4 * i) / N, n = (4 * i) % N;
-          __nv_bfloat162* d = reinterpret_cast<__nv_bfloat162*>(sS + p * SN + n);
-          d[0] = __floats2bfloat162_rn(v[u].x, v[u].y);
-          d[1] = __floats2bfloat162_rn(v[u].z, v[u].w);
-        }
-      }
+    const bf16* src = start_state + (static_cast<size_t>(c) * H + h) * P * N;
+    for (int i = tid; i < P * (N / 8); i += 128) {
+      const int p = i / (N / 8), col = i % (N / 8);
+      ssd_cp_async16(sS + p * SN + col * 8, src + static_cast<size_t>(p) * N + col * 8, true);
     }
   }
   ssd_delta_cumsum(dt_raw, ld_dt, dt_scale, dt_shift[h], -expf(a_log[h]), t0, len, h, s_delta, s_cs);
@@ -283,26 +330,45 @@ __global__ void __launch_bounds__(128)
   const int i_lo = warp * 16 + (lane >> 2), i_hi = i_lo + 8;
   const float cs_lo = s_cs[i_lo], cs_hi = s_cs[i_hi];
 
-  // G = C B^T for this warp's 16 rows and the tokens up to its diagonal block; then the decayed,
-  // masked, delta-weighted matrix M as bfloat16 A-fragments
+  // The gate's inputs for this thread's outputs are requested now and used in the epilogue.
+  constexpr int NT_Y = PB / 8;
+  __nv_bfloat162 zreg[2][NT_Y];
+  auto load_z = [&](int pb) {
+    if (!z_raw) return;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int i = half ? i_hi : i_lo;
+#pragma unroll
+      for (int nt = 0; nt < NT_Y; ++nt) {
+        const int p = pb * PB + nt * 8 + (lane & 3) * 2;
+        zreg[half][nt] = i < len ? *reinterpret_cast<const __nv_bfloat162*>(
+                                       z_raw + static_cast<long long>(t0 + i) * ld_z + h * P + p)
+                                 : __floats2bfloat162_rn(0.f, 0.f);
+      }
+    }
+  };
+  load_z(0);
+
+  // Fragment loads and mma instructions issue in program order: the fragments of step k+1 are
+  // requested before the products of step k, so their latency hides behind them.
+  const bf16* c_lane = sC + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SN + (lane >> 4) * 8;
+
+  // C_i . B_j for this warp's 16 rows and the tokens up to its diagonal block, formed once per
+  // (chunk, group) by phase 1 and read here in accumulator layout; then the decayed, masked,
+  // delta-weighted matrix M as bfloat16 A-fragments
   unsigned mfrag[kQ / 16][4];
   {
     float gacc[kQ / 8][4];
+    const float* gsrc = chunk_cb + (static_cast<size_t>(c) * G + g) * kQ * kQ;
 #pragma unroll
-    for (int i = 0; i < kQ / 8; ++i) gacc[i][0] = gacc[i][1] = gacc[i][2] = gacc[i][3] = 0.f;
-#pragma unroll
-    for (int ks = 0; ks < N / 16; ++ks) {
-      unsigned a[4];
-      ssd_ldm(a[0], a[1], a[2], a[3], sC + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SN + ks * 16 + (lane >> 4) * 8);
-#pragma unroll
-      for (int np = 0; np < kQ / 16; ++np) {
-        if (np <= warp) {
-          unsigned b0, b1, b2, b3;
-          ssd_ldm(b0, b1, b2, b3, sB + (np * 16 + (lane & 7) + (lane >> 4) * 8) * SN + ks * 16 + ((lane >> 3) & 1) * 8);
-          ssd_mma(gacc[2 * np], a, b0, b1);
-          ssd_mma(gacc[2 * np + 1], a, b2, b3);
-        }
+    for (int nt = 0; nt < kQ / 8; ++nt) {
+      float2 lo = make_float2(0.f, 0.f), hi = lo;
+      if (nt / 2 <= warp) {
+        const int j = nt * 8 + (lane & 3) * 2;
+        lo = __ldg(reinterpret_cast<const float2*>(gsrc + i_lo * kQ + j));
+        hi = __ldg(reinterpret_cast<const float2*>(gsrc + i_hi * kQ + j));
       }
+      gacc[nt][0] = lo.x; gacc[nt][1] = lo.y; gacc[nt][2] = hi.x; gacc[nt][3] = hi.y;
     }
 #pragma unroll
     for (int kk = 0; kk < kQ / 16; ++kk) {
@@ -315,7 +381,8 @@ __global__ void __launch_bounds__(128)
           const int j = nt * 8 + (lane & 3) * 2 + (e & 1);
           const int i = (e < 2) ? i_lo : i_hi;
           const float csi = (e < 2) ? cs_lo : cs_hi;
-          m[half][e] = (j <= i) ? gacc[nt][e] * expf(csi - s_cs[j]) * s_delta[j] : 0.f;
+          // the result is rounded to bfloat16 next, so the fast exponential loses nothing
+          m[half][e] = (j <= i) ? gacc[nt][e] * __expf(csi - s_cs[j]) * s_delta[j] : 0.f;
         }
       }
       mfrag[kk][0] = ssd_pack(m[0][0], m[0][1]);
@@ -336,29 +403,48 @@ __global__ void __launch_bounds__(128)
       y2[i][0] = y2[i][1] = y2[i][2] = y2[i][3] = 0.f;
     }
     // within the chunk: M (delta x)
+    {
+      const bf16* x_lane = sX + ((lane & 7) + ((lane >> 3) & 1) * 8) * SX + pb * PB + (lane >> 4) * 8;
+      unsigned fx[2][PB / 16][4];
+      auto load_x = [&](int kk) {
 #pragma unroll
-    for (int kk = 0; kk < kQ / 16; ++kk) {
-      if (kk <= warp) {
+        for (int np = 0; np < PB / 16; ++np)
+          ssd_ldm_t(fx[kk & 1][np][0], fx[kk & 1][np][1], fx[kk & 1][np][2], fx[kk & 1][np][3],
+                    x_lane + kk * 16 * SX + np * 16);
+      };
+      load_x(0);
 #pragma unroll
-        for (int np = 0; np < PB / 16; ++np) {
-          unsigned b0, b1, b2, b3;
-          ssd_ldm_t(b0, b1, b2, b3, sX + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SX + pb * PB + np * 16 + (lane >> 4) * 8);
-          ssd_mma(y1[2 * np], mfrag[kk], b0, b1);
-          ssd_mma(y1[2 * np + 1], mfrag[kk], b2, b3);
+      for (int kk = 0; kk < kQ / 16; ++kk) {
+        if (kk <= warp) {
+          if (kk + 1 < kQ / 16 && kk + 1 <= warp) load_x(kk + 1);
+#pragma unroll
+          for (int np = 0; np < PB / 16; ++np) {
+            ssd_mma(y1[2 * np], mfrag[kk], fx[kk & 1][np][0], fx[kk & 1][np][1]);
+            ssd_mma(y1[2 * np + 1], mfrag[kk], fx[kk & 1][np][2], fx[kk & 1][np][3]);
+          }
         }
       }
     }
     // from before the chunk: C S^T
+    {
+      const bf16* s_lane = sS + (pb * PB + (lane & 7) + (lane >> 4) * 8) * SN + ((lane >> 3) & 1) * 8;
+      unsigned fa[2][4], fs[2][PB / 16][4];
+      auto load_s = [&](int ks) {
+        ssd_ldm(fa[ks & 1][0], fa[ks & 1][1], fa[ks & 1][2], fa[ks & 1][3], c_lane + ks * 16);
 #pragma unroll
-    for (int ks = 0; ks < N / 16; ++ks) {
-      unsigned a[4];
-      ssd_ldm(a[0], a[1], a[2], a[3], sC + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SN + ks * 16 + (lane >> 4) * 8);
+        for (int np = 0; np < PB / 16; ++np)
+          ssd_ldm(fs[ks & 1][np][0], fs[ks & 1][np][1], fs[ks & 1][np][2], fs[ks & 1][np][3],
+                  s_lane + np * 16 * SN + ks * 16);
+      };
+      load_s(0);
 #pragma unroll
-      for (int np = 0; np < PB / 16; ++np) {
-        unsigned b0, b1, b2, b3;
-        ssd_ldm(b0, b1, b2, b3, sS + (pb * PB + np * 16 + (lane & 7) + (lane >> 4) * 8) * SN + ks * 16 + ((lane >> 3) & 1) * 8);
-        ssd_mma(y2[2 * np], a, b0, b1);
-        ssd_mma(y2[2 * np + 1], a, b2, b3);
+      for (int ks = 0; ks < N / 16; ++ks) {
+        if (ks + 1 < N / 16) load_s(ks + 1);
+#pragma unroll
+        for (int np = 0; np < PB / 16; ++np) {
+          ssd_mma(y2[2 * np], fa[ks & 1], fs[ks & 1][np][0], fs[ks & 1][np][1]);
+          ssd_mma(y2[2 * np + 1], fa[ks & 1], fs[ks & 1][np][2], fs[ks & 1][np][3]);
+        }
       }
     }
 #pragma unroll
@@ -374,25 +460,26 @@ __global__ void __launch_bounds__(128)
         float v1 = y1[nt][2 * half + 1] + e * y2[nt][2 * half + 1] + Dh * xv.y;
         if (z_raw) {  // gate fused: y * silu(z), z = z_raw * z_scale + z_bias
           const int c = h * P + p;
-          const float2 zv = __bfloat1622float2(
-              *reinterpret_cast<const __nv_bfloat162*>(z_raw + static_cast<long long>(t0 + i) * ld_z + c));
-          v0 *= silu_f(zv.x * z_scale + (z_bias ? z_bias[c] : 0.f));
-          v1 *= silu_f(zv.y * z_scale + (z_bias ? z_bias[c + 1] : 0.f));
+          const float2 zv = __bfloat1622float2(zreg[half][nt]);
+          v0 *= silu_fast(zv.x * z_scale + (z_bias ? z_bias[c] : 0.f));
+          v1 *= silu_fast(zv.y * z_scale + (z_bias ? z_bias[c + 1] : 0.f));
         }
         *reinterpret_cast<__nv_bfloat162*>(y + static_cast<size_t>(t0 + i) * I + h * P + p) = __floats2bfloat162_rn(v0, v1);
       }
     }
+    if (pb + 1 < P / PB) load_z(pb + 1);
   }
 }
 
 template <int P, int N>
 int launch_ssd(const void* xbc, int ld_xbc, const void* dt_raw, long long ld_dt, float dt_scale,
                const float* dt_shift, const float* a_log, const float* d_skip, float* state,
-               const int* cu, const int* slots, void* y, float* chunk_state, float* chunk_decay,
-               int n_seq, int n_chunks, int H, int G, const void* z_raw, long long ld_z, float z_scale,
+               const int* cu, const int* slots, void* y, float* chunk_state, float* chunk_decay, bf16* start_state,
+               float* chunk_cb, int n_seq, int n_chunks, int H, int G, const void* z_raw, long long ld_z, float z_scale,
                const float* z_bias, cudaStream_t stream) {
-  const size_t smem1 = static_cast<size_t>(kQ) * ((P + 8) + (N + 8)) * sizeof(bf16);
-  const size_t smem3 = (static_cast<size_t>(kQ) * (2 * (N + 8) + (P + 8)) + static_cast<size_t>(P) * (N + 8)) * sizeof(bf16);
+  // phase 1: x and B of a (chunk, head), or C and B of a (chunk, group)
+  const size_t smem1 = static_cast<size_t>(kQ) * ((P > N ? P : N) + 8 + (N + 8)) * sizeof(bf16);
+  const size_t smem3 = (static_cast<size_t>(kQ) * ((N + 8) + (P + 8)) + static_cast<size_t>(P) * (N + 8)) * sizeof(bf16);
   auto k1 = ssd_chunk_state_kernel<P, N>;
   auto k3 = ssd_chunk_output_kernel<P, N>;
   if (smem1 > 48 * 1024) {
@@ -403,14 +490,14 @@ int launch_ssd(const void* xbc, int ld_xbc, const void* dt_raw, long long ld_dt,
     cudaError_t e = cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem3));
     if (e != cudaSuccess) return static_cast<int>(e);
   }
-  dim3 grid(n_chunks, H);
-  k1<<<grid, 128, smem1, stream>>>(static_cast<const bf16*>(xbc), ld_xbc, static_cast<const bf16*>(dt_raw), ld_dt,
-                                   dt_scale, dt_shift, a_log, cu, n_seq, chunk_state, chunk_decay, H, G);
+  dim3 grid(n_chunks, H), grid1(n_chunks, H + G);
+  k1<<<grid1, 128, smem1, stream>>>(static_cast<const bf16*>(xbc), ld_xbc, static_cast<const bf16*>(dt_raw), ld_dt,
+                                    dt_scale, dt_shift, a_log, cu, n_seq, chunk_state, chunk_decay, chunk_cb, H, G);
   const int PN = P * N;
   dim3 grid2((PN / 4 + 255) / 256, H, n_seq);
-  ssd_state_pass_kernel<<<grid2, 256, 0, stream>>>(chunk_state, chunk_decay, state, cu, slots, H, PN);
+  ssd_state_pass_kernel<<<grid2, 256, 0, stream>>>(chunk_state, chunk_decay, start_state, state, cu, slots, H, PN);
   k3<<<grid, 128, smem3, stream>>>(static_cast<const bf16*>(xbc), ld_xbc, static_cast<const bf16*>(dt_raw), ld_dt,
-                                   dt_scale, dt_shift, a_log, d_skip, cu, n_seq, chunk_state,
+                                   dt_scale, dt_shift, a_log, d_skip, cu, n_seq, start_state, chunk_cb,
                                    static_cast<bf16*>(y), H, G, static_cast<const bf16*>(z_raw), ld_z, z_scale, z_bias);
   return launch_status();
 }
@@ -423,22 +510,26 @@ PMM_EXPORT int pmm_ssd_supported(int P, int N) {
           (P == 64 && N == 256) || (P == 128 && N == 128) || (P == 128 && N == 256)) ? 1 : 0;
 }
 
-// chunk_state: n_chunks*H*P*N floats, chunk_decay: n_chunks*H floats of scratch;
+// Scratch: chunk_state n_chunks*H*P*N floats, chunk_decay n_chunks*H floats, start_state
+// n_chunks*H*P*N bfloat16 (16-byte aligned), chunk_cb n_chunks*G*64*64 floats (8-byte aligned);
 // n_chunks = sum over sequences of ceil(new tokens / 64).  bfloat16 activations only.
 PMM_EXPORT int pmm_ssd_chunked(const void* xbc, int ld_xbc, const void* dt_raw, long long ld_dt,
                                float dt_scale, const float* dt_shift, const float* a_log,
                                const float* d_skip, float* state, const int* cu, const int* slots,
-                               void* y, float* chunk_state, float* chunk_decay, int n_seq, int n_chunks,
-                               int H, int P, int N, int G, const void* z_raw, long long ld_z, float z_scale,
+                               void* y, float* chunk_state, float* chunk_decay, void* start_state,
+                               float* chunk_cb, int n_seq, int n_chunks, int H, int P, int N, int G, const void* z_raw, long long ld_z, float z_scale,
                                const float* z_bias, cudaStream_t stream) {
   if (n_seq <= 0 || n_chunks <= 0) return 0;
   if (!pmm_ssd_supported(P, N) || H <= 0 || G <= 0 || H % G || H > 65535 || n_seq > 65535 ||
-      !chunk_state || !chunk_decay)
+      !chunk_state || !chunk_decay || !start_state || reinterpret_cast<uintptr_t>(start_state) % 16 ||
+      !chunk_cb || reinterpret_cast<uintptr_t>(chunk_cb) % 8 || H + G > 65535)
     return PMM_ERR_BAD_ARGUMENT;
 #define PMM_SSD_CASE(PP, NN)                                                                             \
   if (P == PP && N == NN)                                                                                \
     return pmm::launch_ssd<PP, NN>(xbc, ld_xbc, dt_raw, ld_dt, dt_scale, dt_shift, a_log, d_skip, state, \
-                                   cu, slots, y, chunk_state, chunk_decay, n_seq, n_chunks, H, G, z_raw,   \
+                                   cu, slots, y, chunk_state, chunk_decay,                    \
+                                   static_cast<pmm::bf16*>(start_state), chunk_cb, n_seq, n_chunks, H, G,  \
+                                   z_raw,                                                                  \
                                    ld_z, z_scale, z_bias, stream)
   PMM_SSD_CASE(16, 16);
   PMM_SSD_CASE(32, 32);

@@ -234,8 +234,8 @@ __global__ void __launch_bounds__(kTcThreads)
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const float g0 = __uint_as_float(g[j + 2 * e]) * gate_mult, g1 = __uint_as_float(g[j + 2 * e + 1]) * gate_mult;
-                p2[e] = __floats2bfloat162_rn(silu_f(g0) * __uint_as_float(u[j + 2 * e]),
-                                              silu_f(g1) * __uint_as_float(u[j + 2 * e + 1]));
+                p2[e] = __floats2bfloat162_rn(silu_fast(g0) * __uint_as_float(u[j + 2 * e]),
+                                              silu_fast(g1) * __uint_as_float(u[j + 2 * e + 1]));
               }
               *reinterpret_cast<uint4*>(dst + j) = pack;
             }

@@ -31,7 +31,7 @@ _SIGNATURES = {
                         c_void_p, c_int, c_int, c_int, c_void_p],
     "pmm_scale_f32": [c_void_p, c_float, c_longlong, c_void_p],
     "pmm_cast_scale": [c_void_p, c_void_p, c_float, c_longlong, c_int, c_void_p],
-    "pmm_conv1d_fwd": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+    "pmm_conv1d_fwd": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                        c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_conv1d_window_update": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_void_p],
@@ -42,8 +42,8 @@ _SIGNATURES = {
                          c_int, c_void_p, c_longlong, c_float, c_void_p, c_int, c_void_p],
     "pmm_ssd_supported": [c_int, c_int],
     "pmm_ssd_chunked": [c_void_p, c_int, c_void_p, c_longlong, c_float, c_void_p, c_void_p, c_void_p,
-                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                        c_int, c_int, c_int, c_void_p, c_longlong, c_float, c_void_p, c_void_p],
+                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                        c_int, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_float, c_void_p, c_void_p],
     "pmm_gated_norm": [c_void_p, c_void_p, c_longlong, c_float, c_void_p, c_void_p, c_float, c_int,
                        c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_qkv_rope_store": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_float,
@@ -262,9 +262,11 @@ def _conv_common(x: Tensor, pre_scale: Tensor, pre_bias: Optional[Tensor], windo
 
 def conv1d_fwd(x: Tensor, pre_scale: Tensor, pre_bias: Optional[Tensor], weight: Tensor,
                bias: Optional[Tensor], window: Tensor, seq_of: Tensor, cu: Tensor, slots: Tensor,
-               out: Tensor) -> None:
-    """Causal depthwise conv + SiLU over all tokens of the step; reads the windows."""
-    _cuda(x, pre_scale, pre_bias, weight, bias, window, seq_of, cu, slots, out)
+               out: Tensor, weight_t: Optional[Tensor] = None) -> None:
+    """Causal depthwise conv + SiLU over all tokens of the step; reads the windows.
+    ``weight_t`` is the tap-major copy [K, C] of ``weight`` [C, K]; with it bfloat16 inputs take
+    the vector kernel."""
+    _cuda(x, pre_scale, pre_bias, weight, bias, window, seq_of, cu, slots, out, weight_t)
     ld = _rows_view(x, "conv1d: x")
     T = x.shape[0]
     _need(weight.dtype == torch.float32 and weight.dim() == 2 and weight.is_contiguous()
@@ -273,8 +275,10 @@ def conv1d_fwd(x: Tensor, pre_scale: Tensor, pre_bias: Optional[Tensor], weight:
     C = _conv_common(x, pre_scale, pre_bias, window, K)
     _f32vec(bias, C, "conv1d: bias")
     _need(out.shape == (T, C) and out.is_contiguous() and out.dtype == x.dtype, "conv1d: out must be [T, C]")
+    _need(weight_t is None or (weight_t.dtype == torch.float32 and weight_t.is_contiguous()
+                               and weight_t.shape == (K, C)), "conv1d: weight_t must be contiguous float32 [K, C]")
     _call("pmm_conv1d_fwd", x.data_ptr(), ld, pre_scale.data_ptr(), _ptr(pre_bias), weight.data_ptr(),
-          _ptr(bias), window.data_ptr(), seq_of.data_ptr(), cu.data_ptr(), slots.data_ptr(),
+          _ptr(weight_t), _ptr(bias), window.data_ptr(), seq_of.data_ptr(), cu.data_ptr(), slots.data_ptr(),
           out.data_ptr(), T, C, K, _dt(x), _stream())
 
 
@@ -353,8 +357,16 @@ def ssd_chunks(new_lens: Sequence[int]) -> int:
     return sum((n + SSD_CHUNK - 1) // SSD_CHUNK for n in new_lens)
 
 
-def ssd_scratch_floats(new_lens: Sequence[int], n_heads: int, d_head: int, d_state: int) -> int:
-    return ssd_chunks(new_lens) * n_heads * (d_head * d_state + 1)
+def ssd_scratch_floats(new_lens: Sequence[int], n_heads: int, d_head: int, d_state: int,
+                       n_groups: Optional[int] = None) -> int:
+    """Floats of scratch for the chunked scan: every chunk's local state (float), its decay, its
+    start state (bfloat16, on a 16-byte boundary) and the 64 x 64 products C.B of every
+    (chunk, group); without ``n_groups`` enough for one group per head."""
+    chunks = ssd_chunks(new_lens)
+    per_state = chunks * n_heads * d_head * d_state
+    decays = (chunks * n_heads + 3) // 4 * 4
+    starts = ((per_state + 1) // 2 + 3) // 4 * 4
+    return per_state + decays + starts + chunks * (n_groups or n_heads) * 64 * 64
 
 
 def ssm_scan_chunked(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Tensor, a_log: Tensor,
@@ -379,16 +391,19 @@ def ssm_scan_chunked(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Ten
     _need(out.shape == (xbc.shape[0], H * P) and out.is_contiguous() and out.dtype == xbc.dtype,
           "ssm_scan: out must be [T, H*P]")
     n_chunks = ssd_chunks(new_lens)
-    need = n_chunks * H * (P * N + 1)
-    _need(scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= need,
-          f"ssm_scan_chunked: needs {need} floats of scratch")
+    need = ssd_scratch_floats(new_lens, H, P, N, n_groups)
+    _need(scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= need
+          and scratch.data_ptr() % 16 == 0, f"ssm_scan_chunked: needs {need} floats of 16-byte aligned scratch")
     chunk_state = scratch.data_ptr()
     chunk_decay = chunk_state + 4 * n_chunks * H * P * N
+    start_state = chunk_decay + 4 * ((n_chunks * H + 3) // 4 * 4)
+    chunk_cb = start_state + 4 * (((n_chunks * H * P * N + 1) // 2 + 3) // 4 * 4)
     zp, ld_z, zs, zb = _gate_args(gate, out, "ssm_scan_chunked")
     _need(zp is None or (ld_z % 2 == 0 and zp % 4 == 0), "ssm_scan_chunked: z rows must be 4-byte aligned")
     _call("pmm_ssd_chunked", xbc.data_ptr(), ld_x, dt_raw.data_ptr(), ld_dt, float(dt_scale),
           dt_shift.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), cu.data_ptr(),
-          slots.data_ptr(), out.data_ptr(), chunk_state, chunk_decay, len(new_lens), n_chunks, H, P, N,
+          slots.data_ptr(), out.data_ptr(), chunk_state, chunk_decay, start_state, chunk_cb, len(new_lens), n_chunks,
+          H, P, N,
           n_groups, zp, ld_z, zs, zb, _stream())
 
 

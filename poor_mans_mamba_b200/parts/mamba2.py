@@ -93,6 +93,7 @@ class Mamba2Mixer(Mixer):
         self.w_in = params["in_proj.weight"].contiguous()
         self.w_out = params["out_proj.weight"].contiguous()
         self.conv_w = params["conv1d.weight"].reshape(self.conv_dim, self.d_conv).contiguous()
+        self.conv_w_t = self.conv_w.t().contiguous()  # tap-major copy for the vector kernel
         self.conv_b = params["conv1d.bias"].contiguous() if self.conv_bias else None
         self.a_log = params["A_log"].contiguous()
         self.d_skip = params["D"].contiguous()
@@ -161,7 +162,7 @@ class Mamba2Mixer(Mixer):
                             window, ctx.slots, xbc)
         else:
             K.conv1d_fwd(xbc_raw, self.conv_pre_scale, self.conv_pre_bias, self.conv_w, self.conv_b, window,
-                         ctx.seq_of, ctx.cu_seqlens, ctx.slots, xbc)
+                         ctx.seq_of, ctx.cu_seqlens, ctx.slots, xbc, weight_t=self.conv_w_t)
             K.conv1d_window_update(xbc_raw, self.conv_pre_scale, self.conv_pre_bias, window, ctx.cu_seqlens,
                                    ctx.slots, ctx.n_seq, self.d_conv)
 
@@ -171,8 +172,8 @@ class Mamba2Mixer(Mixer):
         if (not ctx.decode_only and proj.dtype == torch.bfloat16 and max(ctx.new_lens) >= _CHUNKED_FROM
                 and K.ssd_supported(self.d_head, self.d_state)):
             # prompt portions: chunks of 64 tokens on tensor cores
-            scratch = ws.alloc((K.ssd_scratch_floats(ctx.new_lens, self.n_heads, self.d_head, self.d_state),),
-                               torch.float32)
+            need = K.ssd_scratch_floats(ctx.new_lens, self.n_heads, self.d_head, self.d_state, self.n_groups)
+            scratch = ws.alloc((need,), torch.float32)
             K.ssm_scan_chunked(xbc, dt, self.dt_scale, self.dt_shift, self.a_log, self.d_skip, state,
                                ctx.cu_seqlens, ctx.slots, ctx.new_lens, y, self.n_groups, scratch, gate=gate)
         else:

@@ -86,7 +86,7 @@ def _batch(lens_steps):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("C,Kc,bias", [(200, 4, True), (33, 2, False), (130, 5, True)])
+@pytest.mark.parametrize("C,Kc,bias", [(200, 4, True), (33, 2, False), (130, 5, True), (64, 3, False)])
 def test_conv1d_varlen_with_window(dtype, C, Kc, bias):
     g = torch.Generator().manual_seed(C)
     portions = [[5, 1, 1, 7], [1, 2, 9], [3, 1, 1, 1, 1]]
@@ -117,7 +117,8 @@ def test_conv1d_varlen_with_window(dtype, C, Kc, bias):
         if all(n == 1 for _, _, n in seqs):
             K().conv1d_decode(x, dev(ps), dev(pb), dev(w), dev(cb), window, sl, out)
         else:
-            K().conv1d_fwd(x, dev(ps), dev(pb), dev(w), dev(cb), window, i32(seq_of), i32(cu), sl, out)
+            K().conv1d_fwd(x, dev(ps), dev(pb), dev(w), dev(cb), window, i32(seq_of), i32(cu), sl, out,
+                           weight_t=dev(w).t().contiguous())
             K().conv1d_window_update(x, dev(ps), dev(pb), window, i32(cu), sl, len(seqs), Kc)
         t0 = 0
         for i, a, n in seqs:

@@ -77,6 +77,26 @@ constexpr int kFlashKeys = 64;  // keys per tile
 // the rows are long and shared memory would limit the blocks per SM.
 __host__ __device__ constexpr int flash_stages(int dh, bool splitw) { return splitw ? 4 : (dh > 64 ? 2 : 3); }
 
+// Decode steps (every sequence brings exactly one token) can hand the kernel the unrotated
+// projections instead of prepared queries: the block then scales and rotates its query rows
+// itself, and the block whose key range holds the new position rotates the new key, writes key
+// and value into the cache page and into its own shared-memory tile.
+//   x' = x*scale;  ang = float(pos) * inv_freq[i];
+//   x'[i] <- x'[i] cos - x'[i+Dh/2] sin;  x'[i+Dh/2] <- x'[i+Dh/2] cos + x'[i] sin
+// (the formulas of the separate rotation kernel; reference src/ops/gpu/attention.cu:4-40)
+struct FlashDecodeInputs {
+  const bf16* q;          // [n_seq, ldq] unrotated queries, or nullptr: `q` of the kernel is ready
+  long long ldq;
+  const bf16* k;          // [n_seq, ldk] new keys, or nullptr: the cache holds them already
+  long long ldk;
+  const bf16* v;
+  long long ldv;
+  float q_scale, k_scale, v_scale;
+  const float* inv_freq;  // [Dh/2], or nullptr: no rotation
+  bf16* pool_w;           // the cache, writable
+  int one_token;          // tile index == sequence index == token index
+};
+
 // MT = row tiles of 16 per warp: 1 (64 rows a block) or 2 (128 rows a block, every K/V fragment
 // read from shared memory feeds two row tiles).  Decode blocks (SPLITW) have one 16-row tile.
 template <int DH, bool SPLITW, int MT>
@@ -86,7 +106,7 @@ __global__ void __launch_bounds__(128)
                        const int* __restrict__ positions, const int* __restrict__ cu,
                        bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                        float scale_log2, int window, int split_len, int n_splits, int page_size,
-                       int n_seq, int Hq, int Hkv, int* __restrict__ split_counter) {
+                       int n_seq, int Hq, int Hkv, int* __restrict__ split_counter, FlashDecodeInputs dec) {
   static_assert(!SPLITW || MT == 1, "decode tiles have 16 rows");
   constexpr int M = SPLITW ? 16 : 64 * MT;
   constexpr int KT = kFlashKeys;
@@ -106,8 +126,9 @@ __global__ void __launch_bounds__(128)
   __shared__ int s_bt[BT_CAP];
   __shared__ float s_wm[4][16], s_wl[4][16], s_M[128], s_L[128];
 
+  // Token positions, sequence bounds and block tables are inputs of the step, written before its
+  // first kernel: they are read before the wait for the previous kernel, whose tail hides them.
   pdl_launch_dependents();
-  pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = Hq / Hkv;
   const int tpt = M / G;  // tokens per tile (host guarantees G <= M)
@@ -117,16 +138,21 @@ __global__ void __launch_bounds__(128)
   // which sequence and which of its tokens this tile covers.  Blocks start in index order and
   // a sequence's last tiles walk the most keys, so the tiles are handed out from the back.
   const int tile_id = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
-  int seq = 0, acc = 0;
-  for (; seq < n_seq; ++seq) {
-    const int n = cu[seq + 1] - cu[seq];
-    const int nt = (n + tpt - 1) / tpt;
-    if (tile_id < acc + nt) break;
-    acc += nt;
+  int seq = 0, acc = 0, tok0, n_tok;
+  if (SPLITW && dec.one_token) {
+    seq = tok0 = tile_id;
+    n_tok = 1;
+  } else {
+    for (; seq < n_seq; ++seq) {
+      const int n = cu[seq + 1] - cu[seq];
+      const int nt = (n + tpt - 1) / tpt;
+      if (tile_id < acc + nt) break;
+      acc += nt;
+    }
+    if (seq >= n_seq) return;
+    tok0 = cu[seq] + (tile_id - acc) * tpt;
+    n_tok = min(cu[seq + 1], tok0 + tpt) - tok0;
   }
-  if (seq >= n_seq) return;
-  const int tok0 = cu[seq] + (tile_id - acc) * tpt;
-  const int n_tok = min(cu[seq + 1], tok0 + tpt) - tok0;
   const int n_rows = n_tok * G;
   const int* bt = block_table + static_cast<size_t>(seq) * max_blocks;
 
@@ -148,9 +174,74 @@ __global__ void __launch_bounds__(128)
     for (int i = tid; i < n_bt; i += 128) s_bt[i] = bt[bt_lo + i];
   __syncthreads();
   auto page_of = [&](int idx) { return bt_shared ? s_bt[idx - bt_lo] : bt[idx]; };
+  pdl_wait();  // from here on: queries, keys and values that earlier kernels of the step wrote
+
+  // the new token of a decode step: this block stores its key and value if its key range holds it
+  const int new_pos = pos_max;
+  const bool stores_new = SPLITW && dec.k != nullptr && n_tiles > 0 && new_pos >= k_begin && new_pos < k_end;
+  constexpr int HALF = DH / 2;
+  bf16 *k_dst = nullptr, *v_dst = nullptr, *k_sm = nullptr, *v_sm = nullptr;
+  int new_tile = -1;  // the new position's tile in this block's ring (the last tile of its range)
+  const bool single_round = n_tiles <= NSTAGE;  // else the ring slot is written in the tile's own round
+  if (SPLITW && stores_new) {
+    const int page = page_of(new_pos / page_size);
+    k_dst = dec.pool_w + (static_cast<size_t>(page) * 2 * page_size + new_pos % page_size) * kv_dim + hk * DH;
+    v_dst = k_dst + static_cast<size_t>(page_size) * kv_dim;
+    new_tile = (new_pos - first_tile) / KT;
+    k_sm = sK + (new_tile % NSTAGE) * KT * STRIDE + (new_pos - first_tile - new_tile * KT) * STRIDE;
+    v_sm = sV + (new_tile % NSTAGE) * KT * STRIDE + (new_pos - first_tile - new_tile * KT) * STRIDE;
+  }
+  // Runs after the first tiles' copies have been requested, so that their latency covers it.
+  auto prepare_decode_inputs = [&]() {
+    if (SPLITW && stores_new) {
+      for (int i = tid; i < HALF; i += 128) {
+        const bf16* src = dec.k + static_cast<long long>(tok0) * dec.ldk + hk * DH;
+        const float x1 = __bfloat162float(src[i]) * dec.k_scale, x2 = __bfloat162float(src[i + HALF]) * dec.k_scale;
+        float o1 = x1, o2 = x2;
+        if (dec.inv_freq) {
+          const float ang = static_cast<float>(new_pos) * dec.inv_freq[i];
+          const float c = cosf(ang), sn = sinf(ang);
+          o1 = x1 * c - x2 * sn;
+          o2 = x2 * c + x1 * sn;
+        }
+        const bf16 b1 = __float2bfloat16_rn(o1), b2 = __float2bfloat16_rn(o2);
+        k_dst[i] = b1;
+        k_dst[i + HALF] = b2;
+        if (single_round) {
+          k_sm[i] = b1;
+          k_sm[i + HALF] = b2;
+        }
+      }
+      for (int i = tid; i < DH; i += 128) {
+        const bf16 b = __float2bfloat16_rn(__bfloat162float(dec.v[static_cast<long long>(tok0) * dec.ldv + hk * DH + i]) * dec.v_scale);
+        v_dst[i] = b;
+        if (single_round) v_sm[i] = b;
+      }
+    }
+    if (SPLITW && dec.q != nullptr && n_tiles > 0) {
+      for (int idx = tid; idx < M * HALF; idx += 128) {
+        const int r = idx / HALF, i = idx % HALF;
+        float o1 = 0.f, o2 = 0.f;
+        if (r < n_rows) {
+          const bf16* src = dec.q + static_cast<long long>(tok0 + r / G) * dec.ldq + (hk * G + r % G) * DH;
+          const float x1 = __bfloat162float(src[i]) * dec.q_scale, x2 = __bfloat162float(src[i + HALF]) * dec.q_scale;
+          o1 = x1;
+          o2 = x2;
+          if (dec.inv_freq) {
+            const float ang = static_cast<float>(s_pos[r]) * dec.inv_freq[i];
+            const float c = cosf(ang), sn = sinf(ang);
+            o1 = x1 * c - x2 * sn;
+            o2 = x2 * c + x1 * sn;
+          }
+        }
+        sQ[r * STRIDE + i] = __float2bfloat16_rn(o1);
+        sQ[r * STRIDE + i + HALF] = __float2bfloat16_rn(o2);
+      }
+    }
+  };
 
   // Q rows -> shared memory (rows beyond the tile are zero)
-  if (n_tiles > 0) {
+  if (n_tiles > 0 && !(SPLITW && dec.q != nullptr)) {
     for (int c = tid; c < M * CHUNKS; c += 128) {
       const int r = c / CHUNKS, col = c % CHUNKS;
       const bool ok = r < n_rows;
@@ -174,7 +265,8 @@ __global__ void __launch_bounds__(128)
       const int page = page_of(base / page_size);
       const bf16* src = pool + (static_cast<size_t>(page) * 2 * page_size + base % page_size + ld_r0) * kv_dim +
                         hk * DH + ld_col;
-      if (base >= k_begin && base + KT <= k_end) {  // every key of the tile is wanted
+      const bool holds_new = SPLITW && stores_new && new_pos >= base && new_pos < base + KT;
+      if (base >= k_begin && base + KT <= k_end && !holds_new) {  // every key of the tile is wanted
 #pragma unroll
         for (int j = 0; j < PIECES; ++j) {
           cp_async16_all(dK + j * RSTEP * STRIDE, src + static_cast<size_t>(j * RSTEP) * kv_dim);
@@ -184,6 +276,7 @@ __global__ void __launch_bounds__(128)
 #pragma unroll
         for (int j = 0; j < PIECES; ++j) {
           const int key = base + ld_r0 + j * RSTEP;
+          if (holds_new && key == new_pos) continue;  // this block writes that row itself
           const bool ok = key >= k_begin && key < k_end;
           const bf16* sj = ok ? src + static_cast<size_t>(j * RSTEP) * kv_dim : pool;
           cp_async16(dK + j * RSTEP * STRIDE, sj, ok);
@@ -194,6 +287,7 @@ __global__ void __launch_bounds__(128)
 #pragma unroll
       for (int j = 0; j < PIECES; ++j) {
         const int key = base + ld_r0 + j * RSTEP;
+        if (SPLITW && stores_new && key == new_pos) continue;  // this block writes that row itself
         const bool ok = key >= k_begin && key < k_end;
         size_t src = 0;
         if (ok) {
@@ -360,7 +454,16 @@ __global__ void __launch_bounds__(128)
 #pragma unroll
       for (int st = 0; st < NSTAGE; ++st)
         if (round0 + st < n_tiles) load_tile(st, first_tile + (round0 + st) * KT);
+      if (stores_new && !single_round && new_tile >= round0 && new_tile < round0 + NSTAGE) {
+        // the new key and value, read back from where this thread put them in the cache
+        for (int i = tid; i < HALF; i += 128) {
+          k_sm[i] = k_dst[i];
+          k_sm[i + HALF] = k_dst[i + HALF];
+        }
+        for (int i = tid; i < DH; i += 128) v_sm[i] = v_dst[i];
+      }
       cp_async_commit();  // the first group also carries the Q rows
+      if (round0 == 0) prepare_decode_inputs();
       cp_async_wait<0>();
       __syncthreads();
       if (round0 == 0) load_q_fragments();
@@ -497,45 +600,42 @@ __global__ void __launch_bounds__(128)
     if (!s_last) return;
     __threadfence();
     if (tid == 0) *counter = 0;
-    // pass 1, a thread per row: the largest maximum among the splits and the merged sum
-    if (tid < n_rows) {
-      const int t = tok0 + tid / G, hq = hk * G + tid % G;
-      const float* ml = part_ml + (static_cast<size_t>(t) * Hq + hq) * n_splits * 2;
-      float mx = -CUDART_INF_F;
-      for (int zz = 0; zz < n_splits; ++zz) {
-        const float2 v = __ldcg(reinterpret_cast<const float2*>(ml) + zz);
-        if (v.y > 0.f) mx = fmaxf(mx, v.x);
-      }
-      float tot = 0.f;
-      for (int zz = 0; zz < n_splits; ++zz) {
-        const float2 v = __ldcg(reinterpret_cast<const float2*>(ml) + zz);
-        if (v.y > 0.f) tot += expf(v.x - mx) * v.y;
-      }
-      s_M[tid] = mx;
-      s_L[tid] = tot > 0.f ? 1.f / tot : 0.f;
-    }
-    __syncthreads();
-    // pass 2, a thread per (row, four columns): the weighted sum over the splits
+    // A thread per (row, four columns) merges the splits in one pass with a running maximum,
+    // eight splits' loads in flight at a time.
     constexpr int C4 = DH / 4;
+    constexpr int kBatch = 8;
     for (int i = tid; i < n_rows * C4; i += 128) {
       const int r = i / C4, d = (i % C4) * 4;
       const int t = tok0 + r / G, hq = hk * G + r % G;
       const size_t row = static_cast<size_t>(t) * Hq + hq;
       const float2* ml = reinterpret_cast<const float2*>(part_ml + row * n_splits * 2);
       const float* po = part_o + row * n_splits * DH + d;
-      const float mx = s_M[r];
+      float mx = -CUDART_INF_F, tot = 0.f;
       float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-      for (int zz = 0; zz < n_splits; ++zz) {
-        const float2 v = __ldcg(ml + zz);
-        const float4 x = __ldcg(reinterpret_cast<const float4*>(po + static_cast<size_t>(zz) * DH));
-        const float w = v.y > 0.f ? expf(v.x - mx) : 0.f;
-        a.x += w * x.x;
-        a.y += w * x.y;
-        a.z += w * x.z;
-        a.w += w * x.w;
+      for (int z0 = 0; z0 < n_splits; z0 += kBatch) {
+        float2 v[kBatch];
+        float4 x[kBatch];
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+          const int zz = min(z0 + u, n_splits - 1);
+          v[u] = __ldcg(ml + zz);
+          x[u] = __ldcg(reinterpret_cast<const float4*>(po + static_cast<size_t>(zz) * DH));
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+          if (z0 + u < n_splits && v[u].y > 0.f) {
+            const float mn = fmaxf(mx, v[u].x);
+            const float keep = expf(mx - mn), w = expf(v[u].x - mn);  // mx = -inf: keep = 0
+            a.x = a.x * keep + w * x[u].x;
+            a.y = a.y * keep + w * x[u].y;
+            a.z = a.z * keep + w * x[u].z;
+            a.w = a.w * keep + w * x[u].w;
+            tot = tot * keep + w * v[u].y;
+            mx = mn;
+          }
+        }
       }
-      const float inv = s_L[r];
+      const float inv = tot > 0.f ? 1.f / tot : 0.f;
       uint2 packed;
       packed.x = pack_bf16(a.x * inv, a.y * inv);
       packed.y = pack_bf16(a.z * inv, a.w * inv);
@@ -593,7 +693,8 @@ template <int DH, bool SPLITW, int MT>
 int launch_flash(const void* q, const void* pool, const int* block_table, int max_blocks,
                  const int* positions, const int* cu, void* out, float* part_o, float* part_ml,
                  float scale, int window, int split_len, int n_splits, int page_size, int n_seq,
-                 int n_tiles, int Hq, int Hkv, int* split_counter, cudaStream_t stream) {
+                 int n_tiles, int Hq, int Hkv, int* split_counter, const FlashDecodeInputs& dec,
+                 cudaStream_t stream) {
   constexpr int M = SPLITW ? 16 : 64 * MT;
   constexpr int NSTAGE = flash_stages(DH, SPLITW);
   const size_t smem = static_cast<size_t>(M + 2 * NSTAGE * kFlashKeys) * (DH + 8) * sizeof(bf16);
@@ -606,7 +707,7 @@ int launch_flash(const void* q, const void* pool, const int* block_table, int ma
   dim3 grid(n_tiles, Hkv, n_splits);
   launch_pdl(kern, grid, dim3(128), smem, stream, static_cast<const bf16*>(q), static_cast<const bf16*>(pool),
              block_table, max_blocks, positions, cu, static_cast<bf16*>(out), part_o, part_ml,
-             scale * 1.4426950408889634f, window, split_len, n_splits, page_size, n_seq, Hq, Hkv, split_counter);
+             scale * 1.4426950408889634f, window, split_len, n_splits, page_size, n_seq, Hq, Hkv, split_counter, dec);
   return launch_status();
 }
 
@@ -619,17 +720,12 @@ PMM_EXPORT int pmm_flash_supported(int Hq, int Hkv, int Dh) {
   return (Dh == 16 || Dh == 32 || Dh == 64 || Dh == 128) && G <= 64 ? 1 : 0;
 }
 
-// tile_rows M: 16 (every sequence brings at most 16/G tokens: decode), 64, or 128 (head sizes
-// up to 64).  n_tiles: number of row tiles = sum over sequences of ceil(new tokens / (M / G)).
-// split_counter: nullptr (the caller merges key splits with pmm_flash_combine), or
-// n_tiles*Hkv ints that are zero between calls: then the last block of every tile merges
-// its splits (at most 64 of them) and writes `out` itself.
-PMM_EXPORT int pmm_flash_paged_attention(const void* q, const void* pool, const int* block_table,
-                                         int max_blocks, const int* positions, const int* cu,
-                                         void* out, float* part_o, float* part_ml, float scale,
-                                         int window, int split_len, int n_splits, int page_size,
-                                         int n_seq, int n_tiles, int tile_rows, int Hq, int Hkv, int Dh,
-                                         int* split_counter, cudaStream_t stream) {
+namespace pmm {
+int flash_dispatch(const void* q, const void* pool, const int* block_table, int max_blocks,
+                   const int* positions, const int* cu, void* out, float* part_o, float* part_ml,
+                   float scale, int window, int split_len, int n_splits, int page_size, int n_seq,
+                   int n_tiles, int tile_rows, int Hq, int Hkv, int Dh, int* split_counter,
+                   const FlashDecodeInputs& dec, cudaStream_t stream) {
   if (n_seq <= 0 || n_tiles <= 0) return 0;
   if (!pmm_flash_supported(Hq, Hkv, Dh) || page_size <= 0 || n_splits < 1 || n_splits > 65535 ||
       Hkv > 65535)
@@ -643,15 +739,15 @@ PMM_EXPORT int pmm_flash_paged_attention(const void* q, const void* pool, const 
   int rc;
 #define PMM_FLASH_ARGS                                                                                  \
   q, pool, block_table, max_blocks, positions, cu, out, part_o, part_ml, scale, window, split_len,      \
-      n_splits, page_size, n_seq, n_tiles, Hq, Hkv, split_counter, stream
-#define PMM_FLASH_CASE(DH)                                                            \
-  rc = tile_rows == 16 ? pmm::launch_flash<DH, true, 1>(PMM_FLASH_ARGS)               \
-                       : pmm::launch_flash<DH, false, 1>(PMM_FLASH_ARGS)
+      n_splits, page_size, n_seq, n_tiles, Hq, Hkv, split_counter, dec, stream
+#define PMM_FLASH_CASE(DH)                                                       \
+  rc = tile_rows == 16 ? launch_flash<DH, true, 1>(PMM_FLASH_ARGS)               \
+                       : launch_flash<DH, false, 1>(PMM_FLASH_ARGS)
   if (tile_rows == 128) {
     switch (Dh) {
-      case 16: rc = pmm::launch_flash<16, false, 2>(PMM_FLASH_ARGS); break;
-      case 32: rc = pmm::launch_flash<32, false, 2>(PMM_FLASH_ARGS); break;
-      case 64: rc = pmm::launch_flash<64, false, 2>(PMM_FLASH_ARGS); break;
+      case 16: rc = launch_flash<16, false, 2>(PMM_FLASH_ARGS); break;
+      case 32: rc = launch_flash<32, false, 2>(PMM_FLASH_ARGS); break;
+      case 64: rc = launch_flash<64, false, 2>(PMM_FLASH_ARGS); break;
       default: return PMM_ERR_BAD_ARGUMENT;
     }
     return rc;
@@ -666,6 +762,58 @@ PMM_EXPORT int pmm_flash_paged_attention(const void* q, const void* pool, const 
 #undef PMM_FLASH_ARGS
 #undef PMM_FLASH_CASE
   return rc;
+}
+}  // namespace pmm
+
+// tile_rows M: 16 (every sequence brings at most 16/G tokens: decode), 64, or 128 (head sizes
+// up to 64).  n_tiles: number of row tiles = sum over sequences of ceil(new tokens / (M / G)).
+// split_counter: nullptr (the caller merges key splits with pmm_flash_combine), or
+// n_tiles*Hkv ints that are zero between calls: then the last block of every tile merges
+// its splits (at most 64 of them) and writes `out` itself.
+PMM_EXPORT int pmm_flash_paged_attention(const void* q, const void* pool, const int* block_table,
+                                         int max_blocks, const int* positions, const int* cu,
+                                         void* out, float* part_o, float* part_ml, float scale,
+                                         int window, int split_len, int n_splits, int page_size,
+                                         int n_seq, int n_tiles, int tile_rows, int Hq, int Hkv, int Dh,
+                                         int* split_counter, cudaStream_t stream) {
+  pmm::FlashDecodeInputs dec{};
+  return pmm::flash_dispatch(q, pool, block_table, max_blocks, positions, cu, out, part_o, part_ml, scale,
+                             window, split_len, n_splits, page_size, n_seq, n_tiles, tile_rows, Hq, Hkv, Dh,
+                             split_counter, dec, stream);
+}
+
+// Decode step, every sequence one token (token t belongs to sequence t): attention straight from
+// the projections.  q_src/k_src/v_src: [n_seq, ld*] unrotated slices; queries and keys are scaled
+// and rotated (inv_freq [Dh/2], or nullptr for no rotation) as the separate rotation kernel does,
+// and the new key and value are written into the cache page of their position.  k_src == nullptr:
+// the cache holds the new keys already (a layer that reads another layer's cache).
+// Needs Hq/Hkv <= 16; positions[t] is the new token's position.
+PMM_EXPORT int pmm_flash_decode_attention(const void* q_src, long long ldq, const void* k_src, long long ldk,
+                                          const void* v_src, long long ldv, float q_scale, float k_scale,
+                                          float v_scale, const float* inv_freq, void* pool,
+                                          const int* block_table, int max_blocks, const int* positions,
+                                          void* out, float* part_o, float* part_ml, float scale, int window,
+                                          int split_len, int n_splits, int page_size, int n_seq, int Hq,
+                                          int Hkv, int Dh, int* split_counter, cudaStream_t stream) {
+  if (!q_src || (k_src == nullptr) != (v_src == nullptr) || Hkv <= 0 || Hq % Hkv || Hq / Hkv > 16)
+    return PMM_ERR_BAD_ARGUMENT;
+  if (n_splits > 1 && !split_counter) return PMM_ERR_BAD_ARGUMENT;  // the separate merge is not wired here
+  pmm::FlashDecodeInputs dec{};
+  dec.q = static_cast<const pmm::bf16*>(q_src);
+  dec.ldq = ldq;
+  dec.k = static_cast<const pmm::bf16*>(k_src);
+  dec.ldk = ldk;
+  dec.v = static_cast<const pmm::bf16*>(v_src);
+  dec.ldv = ldv;
+  dec.q_scale = q_scale;
+  dec.k_scale = k_scale;
+  dec.v_scale = v_scale;
+  dec.inv_freq = inv_freq;
+  dec.pool_w = static_cast<pmm::bf16*>(pool);
+  dec.one_token = 1;
+  return pmm::flash_dispatch(nullptr, pool, block_table, max_blocks, positions, nullptr, out, part_o, part_ml,
+                             scale, window, split_len, n_splits, page_size, n_seq, n_seq, 16, Hq, Hkv, Dh,
+                             split_counter, dec, stream);
 }
 
 // Merge of key splits: part_o [rows, n_splits, Dh], part_ml [rows, n_splits, 2] -> out [rows, Dh].

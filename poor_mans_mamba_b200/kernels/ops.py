@@ -59,6 +59,10 @@ _SIGNATURES = {
     "pmm_flash_paged_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
                                   c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "pmm_flash_decode_attention": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_float,
+                                   c_float, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                   c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                   c_int, c_void_p, c_void_p],
     "pmm_flash_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_skinny_gemm": [c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_int,
                         c_float, c_void_p, c_longlong, c_void_p, c_int, c_float, c_void_p, c_longlong, c_void_p,
@@ -575,6 +579,56 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
     if n_splits > 1:
         _call("pmm_flash_combine", part_o, part_ml, out.data_ptr(), T * n_q_heads, int(n_splits), head_dim,
               _dt(out), _stream())
+
+
+def flash_decode_supported(n_q_heads: int, n_kv_heads: int, head_dim: int) -> bool:
+    """Whether flash_decode_attention takes this head shape (bfloat16, at most 16 query heads a group)."""
+    return flash_supported(n_q_heads, n_kv_heads, head_dim) and n_q_heads // n_kv_heads <= 16
+
+
+def flash_decode_attention(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], q_scale: float, k_scale: float,
+                           v_scale: float, inv_freq: Optional[Tensor], pool: Tensor, block_table: Tensor,
+                           positions: Tensor, out: Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int,
+                           softmax_scale: float, window: int = 0, n_splits: int = 1, split_len: int = 0,
+                           scratch: Optional[Tensor] = None, split_counter: Optional[Tensor] = None) -> None:
+    """A decode step's attention straight from the projections (token t is sequence t's one new
+    token): scales and rotates queries and new keys, writes the new keys and values into their
+    cache pages and attends over the cache, in one launch.  ``k``/``v`` None: the cache has them."""
+    _cuda(q, k, v, inv_freq, pool, block_table, positions, out, scratch, split_counter)
+    n_seq = q.shape[0]
+    kv_dim = n_kv_heads * head_dim
+    _need(q.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+          and flash_decode_supported(n_q_heads, n_kv_heads, head_dim), "decode attention: bfloat16 and a supported shape")
+    ldq = _rows_view(q, "decode attention: q")
+    _need(q.shape[1] == n_q_heads * head_dim and out.is_contiguous() and out.shape == (n_seq, n_q_heads * head_dim),
+          "decode attention: q/out must be [n_seq, Hq*Dh]")
+    ldk = ldv = 0
+    if k is not None or v is not None:
+        _need(k is not None and v is not None and k.dtype == v.dtype == torch.bfloat16
+              and k.shape == (n_seq, kv_dim) and v.shape == (n_seq, kv_dim), "decode attention: k/v must be [n_seq, Hkv*Dh]")
+        ldk, ldv = _rows_view(k, "decode attention: k"), _rows_view(v, "decode attention: v")
+    _f32vec(inv_freq, head_dim // 2, "decode attention: inv_freq")
+    _need(pool.dim() == 4 and pool.shape[1] == 2 and pool.shape[3] == kv_dim and pool.is_contiguous(),
+          "decode attention: pool must be contiguous [pages, 2, page_size, Hkv*Dh]")
+    _i32(block_table, "decode attention: block_table")
+    _i32(positions, "decode attention: positions")
+    _need(block_table.shape[0] >= n_seq and positions.numel() >= n_seq, "decode attention: one table row and position per sequence")
+    part_o = part_ml = counter = None
+    if n_splits > 1:
+        need = attention_scratch_floats(n_seq, n_q_heads, head_dim, n_splits)
+        _need(scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous()
+              and scratch.numel() >= need, f"decode attention: split keys need {need} floats of scratch")
+        _need(split_len > 0 and split_len % 32 == 0 and n_splits <= 64, "decode attention: bad key split")
+        _need(split_counter is not None and split_counter.numel() >= n_seq * n_kv_heads,
+              "decode attention: split keys need a counter per (sequence, key/value head)")
+        _i32(split_counter, "decode attention: split_counter")
+        part_o = scratch.data_ptr()
+        part_ml = part_o + 4 * n_seq * n_q_heads * n_splits * head_dim
+        counter = split_counter.data_ptr()
+    _call("pmm_flash_decode_attention", q.data_ptr(), ldq, _ptr(k), ldk, _ptr(v), ldv, float(q_scale), float(k_scale),
+          float(v_scale), _ptr(inv_freq), pool.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+          positions.data_ptr(), out.data_ptr(), part_o, part_ml, float(softmax_scale), int(window), int(split_len),
+          int(n_splits), pool.shape[2], n_seq, n_q_heads, n_kv_heads, head_dim, counter, _stream())
 
 
 SKINNY_MAX_TOKENS = 16  # beyond this the activations no longer fit beside a deep weight pipeline

@@ -102,11 +102,30 @@ class PagedAttention(Mixer):
         ws = ctx.workspace
         kv = cache.paged(f"{self.name}.kv")
         q = proj[:, :self.q_dim]
-        q_rot = ws.alloc((T, self.q_dim), proj.dtype)
         s_in = self.in_multiplier
         pe = self.position_encoding
         fused = hasattr(pe, "inv_freq")  # rotary (or none): one kernel with the page write
         inv_freq = pe.inv_freq if fused else None
+        scale = 1.0 / math.sqrt(float(self.head_dim))
+        counter = getattr(self, "_split_counter", None)
+        if (fused and ctx.decode_only and proj.dtype == torch.bfloat16 and counter is not None
+                and K.flash_decode_supported(self.num_heads, self.num_kv_heads, self.head_dim)):
+            n_splits, split_len = self.plan_splits(ctx.new_lens, ctx.kv_len_bound, proj.dtype)
+            if n_splits <= 64 and counter.numel() >= T * self.num_kv_heads:
+                # decode step: rotation, page write and attention in one launch
+                scratch = None
+                if n_splits > 1:
+                    scratch = ws.alloc((K.attention_scratch_floats(T, self.num_heads, self.head_dim, n_splits),),
+                                       torch.float32)
+                attn = ws.alloc((T, self.q_dim), proj.dtype)
+                k = None if self.shared_kv else proj[:, self.q_dim:self.q_dim + self.kv_dim]
+                v = None if self.shared_kv else proj[:, self.q_dim + self.kv_dim:]
+                K.flash_decode_attention(q, k, v, s_in, s_in * self.key_multiplier, s_in, inv_freq, kv.pool,
+                                         kv.block_table, ctx.positions, attn, self.num_heads, self.num_kv_heads,
+                                         self.head_dim, scale, window=self.window, n_splits=n_splits,
+                                         split_len=split_len, scratch=scratch, split_counter=counter)
+                return attn
+        q_rot = ws.alloc((T, self.q_dim), proj.dtype)
         if self.shared_kv:  # queries only; keys and values are the cache owner's
             K.qkv_rope_store(q, None, None, s_in, 0.0, 0.0, inv_freq, ctx.positions, ctx.seq_of, None, None,
                              q_rot, None, None, self.num_heads, 0, self.head_dim)
@@ -136,10 +155,10 @@ class PagedAttention(Mixer):
                                torch.float32)
         attn = ws.alloc((T, self.q_dim), proj.dtype)
         K.paged_attention(q_rot, kv.pool, kv.block_table, ctx.positions, ctx.seq_of, attn, self.num_heads,
-                          self.num_kv_heads, self.head_dim, 1.0 / math.sqrt(float(self.head_dim)),
+                          self.num_kv_heads, self.head_dim, scale,
                           window=self.window, n_splits=n_splits, split_len=split_len, scratch=scratch,
                           cu_seqlens=ctx.cu_seqlens, new_lens=ctx.new_lens,
-                          split_counter=getattr(self, "_split_counter", None))
+                          split_counter=counter)
         return attn
 
     def plan_splits(self, new_lens, kv_len_bound: int, dtype: torch.dtype):

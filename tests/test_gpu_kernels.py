@@ -228,9 +228,11 @@ def test_gated_norm(dtype, mode):
 
 
 def _attention_case(dtype, Hq, Hkv, Dh, page_size, lens_steps, window=0, planted=True, n_splits=1, theta=1e4, seed=0,
-                    tensor_cores=True, fused_merge=False):
+                    tensor_cores=True, fused_merge=False, fused_decode=False):
     """Runs qkv_rope_store + paged_attention over a script of portions with scattered pages and
-    compares with the plain rope + causal attention on the whole sequences."""
+    compares with the plain rope + causal attention on the whole sequences.  ``fused_decode``:
+    steps in which every sequence brings one token go through flash_decode_attention instead
+    (rotation, page write and attention in one launch)."""
     g = torch.Generator().manual_seed(seed)
     ops = K()
     lens = [sum(p) for p in lens_steps]
@@ -296,6 +298,21 @@ def _attention_case(dtype, Hq, Hkv, Dh, page_size, lens_steps, window=0, planted
             t0 += n
         q_rot = torch.empty(T, qd, dtype=dtype, device=DEV)
         out = torch.empty(T, qd, dtype=dtype, device=DEV)
+        if fused_decode and all(n == 1 for _, _, n in seqs):
+            split_len, scratch, ns = 0, None, 1
+            if n_splits > 1:
+                split_len = ((max(pos) + 1 + n_splits - 1) // n_splits + 31) // 32 * 32
+                ns = (max(pos) + 1 + split_len - 1) // split_len
+                scratch = torch.full((ops.attention_scratch_floats(T, Hq, Dh, ns),), float("nan"), device=DEV)
+            ops.flash_decode_attention(buf[:, 8:8 + qd], buf[:, 8 + qd:8 + qd + kvd], buf[:, 8 + qd + kvd:], q_scale,
+                                       k_scale, v_scale, inv_freq.to(DEV), pool, bt.to(DEV), i32(pos), out, Hq, Hkv, Dh,
+                                       1.0 / math.sqrt(Dh), window=window, n_splits=ns, split_len=split_len,
+                                       scratch=scratch, split_counter=counter)
+            t0 = 0
+            for i, a, n in seqs:
+                got[i][a:a + n] = out[t0:t0 + n].cpu()
+                t0 += n
+            continue
         ops.qkv_rope_store(buf[:, 8:8 + qd], buf[:, 8 + qd:8 + qd + kvd], buf[:, 8 + qd + kvd:], q_scale, k_scale,
                            v_scale, inv_freq.to(DEV), i32(pos), i32(seq_of), bt.to(DEV), pool, q_rot, None, None,
                            Hq, Hkv, Dh)
@@ -343,6 +360,18 @@ def test_paged_attention_split_keys(dtype, tensor_cores):
         _attention_case(dtype, 8, 2, 64, 64, steps, n_splits=4, seed=5, fused_merge=True)
         _attention_case(dtype, 6, 2, 128, 16, steps, n_splits=9, seed=8, fused_merge=True)
         _attention_case(dtype, 4, 2, 32, 16, [[40, 1, 1, 30], [5, 1, 60]], window=24, n_splits=3, seed=9, fused_merge=True)
+
+
+@pytest.mark.parametrize("Hq,Hkv,Dh,page", [(8, 2, 64, 64), (6, 2, 128, 16), (4, 4, 32, 32), (16, 1, 16, 16), (12, 2, 128, 64)])
+def test_flash_decode_attention_from_projections(Hq, Hkv, Dh, page):
+    """Decode steps that rotate, store and attend in one launch: after prompts of several lengths
+    (page edges, tile edges), one key range and several, more than four tiles in one block (the
+    new key's tile is then loaded in a later round), and a window."""
+    steps = [[page + 1] + [1] * 6, [63] + [1] * 6, [300] + [1] * 6, [1] * 7]
+    _attention_case(torch.bfloat16, Hq, Hkv, Dh, page, steps, seed=Hq, fused_decode=True)
+    _attention_case(torch.bfloat16, Hq, Hkv, Dh, page, steps, seed=Hq + 1, n_splits=3, fused_decode=True)
+    _attention_case(torch.bfloat16, Hq, Hkv, Dh, page, steps, seed=Hq + 2, window=40, n_splits=2, fused_decode=True)
+    _attention_case(torch.bfloat16, Hq, Hkv, Dh, page, steps, seed=Hq + 3, window=70, fused_decode=True)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

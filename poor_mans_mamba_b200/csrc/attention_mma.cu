@@ -699,6 +699,7 @@ int launch_flash(const void* q, const void* pool, const int* block_table, int ma
   constexpr int NSTAGE = flash_stages(DH, SPLITW);
   const size_t smem = static_cast<size_t>(M + 2 * NSTAGE * kFlashKeys) * (DH + 8) * sizeof(bf16);
   auto kern = flash_paged_kernel<DH, SPLITW, MT>;
+  cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));

@@ -329,6 +329,7 @@ int launch_skinny(const SkinnyArgs& a, int k_max, cudaStream_t stream) {
   if (smem > 220 * 1024) return PMM_ERR_BAD_ARGUMENT;
   auto kern = skinny_gemm_kernel<MT, MODE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
   if (e != cudaSuccess) return static_cast<int>(e);
   const int cols_per_block = MODE == kSgSwiglu ? 16 : kSgRows;
   dim3 grid((a.N + cols_per_block - 1) / cols_per_block, (k_max + a.k_slice - 1) / a.k_slice, a.n_problems);

@@ -21,6 +21,8 @@ class StepContext:
     (token rows whose logits are wanted).  ``decode_only``: every sequence brings exactly one
     token.  ``kv_len_bound``: an upper bound of position+1 over the step (host value, for
     launch decisions only).  ``new_lens`` / ``past_lens``: host copies per sequence.
+    ``fetch_ahead``: while a layer runs, the matrices of the layer after it (set by the model;
+    a layer that streams its weights once may ask the memory system for them early).
     """
     n_tokens: int
     n_seq: int
@@ -37,3 +39,4 @@ class StepContext:
     workspace: Workspace
     new_lens: List[int] = field(default_factory=list)
     past_lens: List[int] = field(default_factory=list)
+    fetch_ahead: Optional[List[Tensor]] = None

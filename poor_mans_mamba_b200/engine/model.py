@@ -9,6 +9,8 @@ The forward pass is the same for every architecture:
 """
 from __future__ import annotations
 
+import os
+
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -27,6 +29,7 @@ class Model:
         self.hidden_size = spec.hidden_size
         self.vocab_size = spec.vocab_size
         self.layers = []
+        self._fetch_ahead = os.environ.get("PMM_FETCH_AHEAD", "1") == "1"
         for ls in spec.layers:
             factory = _REGISTRIES["arrangement"].get(ls.arrangement)
             if factory is None:
@@ -107,8 +110,13 @@ class Model:
         h = ws.alloc((T, D), torch.float32)
         K.embed(h, self.embedding, ctx.tokens, self.spec.embedding_multiplier)
         stream = ResidualStream(h, ctx, self._branch_buffers)
-        for call in self.spec.order:
+        order = self.spec.order
+        for i, call in enumerate(order):
+            # a layer that streams its weights once may fetch the next layer's ahead of time
+            nxt = self.layers[order[i + 1].layer] if i + 1 < len(order) else None
+            ctx.fetch_ahead = nxt.streamed_weights() if self._fetch_ahead and hasattr(nxt, "streamed_weights") else None
             self.layers[call.layer].forward(stream, ctx, caches[call.cache_of])
+        ctx.fetch_ahead = None
         if ctx.n_rows == 0:
             stream.flush()
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=h.device)

@@ -59,6 +59,7 @@ _SIGNATURES = {
     "pmm_flash_paged_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
                                   c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "pmm_l2_prefetch": [c_void_p, c_void_p, c_int, c_void_p],
     "pmm_flash_decode_attention": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_float,
                                    c_float, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -796,6 +797,22 @@ def sample_rows(logits: Tensor, temperature: Optional[Tensor], seeds: Optional[T
         _i32(steps, "sample: steps")
     _call("pmm_sample_rows", logits.data_ptr(), ld, _ptr(temperature), _ptr(seeds), _ptr(steps),
           out.data_ptr(), n, V, _stream())
+
+
+def l2_prefetch(tensors: Sequence[Tensor]) -> None:
+    """Asks the memory system to bring these tensors (contiguous, at most 8 per call, further
+    ones in further launches) into L2; nothing waits for it."""
+    import ctypes
+    ts = [t for t in tensors if t is not None and t.numel() > 0]
+    for i in range(0, len(ts), 8):
+        part = ts[i:i + 8]
+        _cuda(*part)
+        for t in part:
+            _need(t.is_contiguous() and t.data_ptr() % 16 == 0, "l2_prefetch: tensors must be contiguous and 16-byte aligned")
+        ptrs = (ctypes.c_void_p * len(part))(*[t.data_ptr() for t in part])
+        sizes = (ctypes.c_longlong * len(part))(*[t.numel() * t.element_size() for t in part])
+        _call("pmm_l2_prefetch", ctypes.cast(ptrs, ctypes.c_void_p), ctypes.cast(sizes, ctypes.c_void_p), len(part),
+              _stream())
 
 
 def ensure_built() -> str:

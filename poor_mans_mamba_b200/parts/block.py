@@ -135,18 +135,31 @@ class ParallelPreNormBlock(Part):
             cls._SIDE_STREAMS[device] = st
         return st
 
+    def streamed_weights(self) -> List[Tensor]:
+        """The matrices a step of few tokens reads once: what the layer before this one may
+        ask the memory system to fetch ahead."""
+        ws = [self._fused_in] + [m.output_weight() for m in self.mixers]
+        if self.ffn is not None:
+            ws += [getattr(self.ffn, "gate_up", None), getattr(self.ffn, "down", None)]
+        return [w for w in ws if w is not None]
+
     def _forward_few_tokens(self, stream: ResidualStream, ctx, cache: LayerCache) -> None:
         ws = ctx.workspace
         mark = ws.mark()
         h = stream.flush()
         T = h.shape[0]
+        side = self._side_stream(h.device) if len(self.mixers) > 1 else None
+        main = torch.cuda.current_stream(h.device)
+        ahead = getattr(ctx, "fetch_ahead", None)  # the next layer's weights, set by the model
+        if ahead:
+            # beside this layer's first kernel: on the side stream when there is one
+            with torch.cuda.stream(side if side is not None else main):
+                K.l2_prefetch(ahead)
         proj = ws.alloc((T, self._fused_in.shape[0]), ctx.dtype)
         K.skinny_linear_norm(h, self.mixer_norm.weight, self.mixer_norm.eps, self._fused_in, proj)
         # The mixers only share their input: the first runs on a side stream beside the others
         # (in a captured step the two become parallel branches of the graph).
         products = [None] * len(self.mixers)
-        side = self._side_stream(h.device) if len(self.mixers) > 1 else None
-        main = torch.cuda.current_stream(h.device)
         if side is not None:
             side.wait_stream(main)
             with torch.cuda.stream(side):

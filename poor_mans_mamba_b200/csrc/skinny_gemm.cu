@@ -74,52 +74,47 @@ __device__ __forceinline__ void sg_mma(float* d, const unsigned* a, unsigned b0,
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// MT: token tiles of 8 (2, 4 or 8 -> up to 16, 32, 64 tokens).
+// What a block needs to know about its place: which rows of W, which slice of K, which product.
 template <int MT, int MODE>
-__global__ void __launch_bounds__(kSgThreads) skinny_gemm_kernel(const SkinnyArgs args) {
-  constexpr int MP = MT * 8;  // padded tokens
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  const SkinnyProblem& pr = args.p[blockIdx.z];
-  const int K = pr.K;
-  const int k0 = blockIdx.y * args.k_slice;
-  if (k0 >= K) return;
-  const int k1 = min(K, k0 + args.k_slice);
-  const int kx = (k1 - k0 + kSgChunk - 1) / kSgChunk * kSgChunk;  // slice length, whole chunks
-  const int xs = kx + 8;                                          // row stride of x in shared memory
-  bf16* sW = reinterpret_cast<bf16*>(smem_raw);                   // [stages][32][264]
-  bf16* sX = sW + kSgStages * kSgRows * kSgWStride;               // [MP][xs]
-  float* sRed = reinterpret_cast<float*>(sX + MP * xs);           // [3][32][MP] column quarters, then up rows
-  float* sNw = sRed + 3 * 32 * MP;                                // [kx] norm weights of the slice (norm prologue)
-
-  pdl_launch_dependents();
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int M = args.M;
-  const int n0 = blockIdx.x * (MODE == kSgSwiglu ? 16 : kSgRows);  // first output column of the block
-  const int n_chunks = kx / kSgChunk;
-
-  // global row of W behind row r of the block's tile (SWIGLU: 16 gate rows, then their 16 up rows)
-  auto w_row = [&](int r) -> int {
-    if (MODE == kSgSwiglu) return r < 16 ? n0 + r : args.N + n0 + (r - 16);
-    return n0 + r;
-  };
-  const int w_rows_total = MODE == kSgSwiglu ? 2 * args.N : args.N;
-  auto w_row_ok = [&](int r) -> bool {
-    if (MODE == kSgSwiglu) return n0 + (r & 15) < args.N;
-    return n0 + r < args.N;
-  };
-  (void)w_rows_total;
-
-  // every thread copies the same pieces (row r, 16-byte column c8) of every chunk
-  const int c8 = tid & 31;
+struct SkinnyBlock {
+  static constexpr int MP = MT * 8;  // padded tokens
+  const SkinnyArgs& args;
+  const SkinnyProblem& pr;
+  int K, k0, k1, kx, xs, n0, n_chunks;
+  bf16* sW;     // [stages][32][264]
+  bf16* sX;     // [MP][xs]
+  float* sRed;  // [3][32][MP] column quarters, then up rows
+  float* sNw;   // [kx] norm weights of the slice (norm prologue)
   const bf16* src[kSgPieces];
   bool row_ok[kSgPieces];
+
+  __device__ SkinnyBlock(const SkinnyArgs& a, int bx, int by, int bz, unsigned char* smem_raw)
+      : args(a), pr(a.p[bz]) {
+    K = pr.K;
+    k0 = by * a.k_slice;
+    k1 = min(K, k0 + a.k_slice);
+    kx = k0 < K ? (k1 - k0 + kSgChunk - 1) / kSgChunk * kSgChunk : 0;  // slice length, whole chunks
+    xs = kx + 8;                                                       // row stride of x in shared memory
+    sW = reinterpret_cast<bf16*>(smem_raw);
+    sX = sW + kSgStages * kSgRows * kSgWStride;
+    sRed = reinterpret_cast<float*>(sX + MP * xs);
+    sNw = sRed + 3 * 32 * MP;
+    n0 = bx * (MODE == kSgSwiglu ? 16 : kSgRows);  // first output column of the block
+    n_chunks = kx / kSgChunk;
+    // every thread copies the same pieces (row r, 16-byte column c8) of every chunk
+    const int tid = threadIdx.x, c8 = tid & 31;
 #pragma unroll
-  for (int j = 0; j < kSgPieces; ++j) {
-    const int r = (tid >> 5) + j * (kSgThreads / 32);
-    row_ok[j] = w_row_ok(r);
-    src[j] = pr.w + (row_ok[j] ? static_cast<size_t>(w_row(r)) * K : 0) + k0 + c8 * 8;
+    for (int j = 0; j < kSgPieces; ++j) {
+      const int r = (tid >> 5) + j * (kSgThreads / 32);
+      // global row of W behind row r of the block's tile (SWIGLU: 16 gate rows, then their 16 up rows)
+      const int wr = MODE == kSgSwiglu ? (r < 16 ? n0 + r : a.N + n0 + (r - 16)) : n0 + r;
+      row_ok[j] = MODE == kSgSwiglu ? n0 + (r & 15) < a.N : n0 + r < a.N;
+      src[j] = pr.w + (row_ok[j] ? static_cast<size_t>(wr) * K : 0) + k0 + c8 * 8;
+    }
   }
-  auto load_chunk = [&](int stage, int chunk) {
+
+  __device__ __forceinline__ void load_chunk(int stage, int chunk) const {
+    const int tid = threadIdx.x, c8 = tid & 31;
     bf16* dst = sW + stage * kSgRows * kSgWStride + (tid >> 5) * kSgWStride + c8 * 8;
     const bool col_ok = k0 + chunk * kSgChunk + c8 * 8 < k1;
 #pragma unroll
@@ -127,17 +122,26 @@ __global__ void __launch_bounds__(kSgThreads) skinny_gemm_kernel(const SkinnyArg
       const bool ok = row_ok[j] && col_ok;
       sg_cp16(dst + j * (kSgThreads / 32) * kSgWStride, ok ? src[j] + chunk * kSgChunk : pr.w, ok);
     }
-  };
-
-  // groups 0..stages-2: the first weight chunks.  They depend on nothing an earlier kernel
-  // writes, so they are requested before this kernel waits for its predecessor.
-#pragma unroll
-  for (int s = 0; s < kSgStages - 1; ++s) {
-    if (s < n_chunks) load_chunk(s, s);
-    sg_commit();
   }
 
-  pdl_wait();
+  // groups 0..stages-2: the first weight chunks.  They depend on nothing that an earlier kernel
+  // or phase writes, so they are requested before the wait for it.
+  __device__ __forceinline__ void request_weights() const {
+#pragma unroll
+    for (int s = 0; s < kSgStages - 1; ++s) {
+      if (s < n_chunks) load_chunk(s, s);
+      sg_commit();
+    }
+  }
+
+  __device__ void run() const;  // everything after the weights have been requested
+};
+
+template <int MT, int MODE>
+__device__ void SkinnyBlock<MT, MODE>::run() const {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int M = args.M;
+  if (kx == 0) return;
   // next group: the activations when they are read as bfloat16, else the norm weights
   if (pr.h_in == nullptr) {
     for (int i = tid; i < MP * (kx / 8); i += kSgThreads) {
@@ -155,6 +159,7 @@ __global__ void __launch_bounds__(kSgThreads) skinny_gemm_kernel(const SkinnyArg
   // norm prologue: x = h * rsqrt(mean(h^2) + eps) * w for this K slice -> shared memory as
   // bfloat16 (rows >= M and columns >= K zero), while the weight chunks are in flight
   if (pr.h_in != nullptr) {
+    // (The stream is read past L1: in a chain of products other blocks have just added to it.)
     // One warp per token, two tokens at a time, 8 float4 per lane and token in flight: for
     // widths up to 1024 a token's row is read once and stays in registers between the sum of
     // squares and the scaling.
@@ -173,7 +178,7 @@ __global__ void __launch_bounds__(kSgThreads) skinny_gemm_kernel(const SkinnyArg
 #pragma unroll
             for (int i = 0; i < kV; ++i) {
               const int k = kb + (i * 32 + lane) * 4;
-              keep[j][i] = (k < K) ? *reinterpret_cast<const float4*>(row + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+              keep[j][i] = (k < K) ? __ldcg(reinterpret_cast<const float4*>(row + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
 #pragma unroll
             for (int i = 0; i < kV; ++i)
@@ -198,7 +203,7 @@ __global__ void __launch_bounds__(kSgThreads) skinny_gemm_kernel(const SkinnyArg
             if (k >= k0 + kx) continue;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (m < M && k < k1) {
-              v = (K <= kPass && k0 == 0) ? keep[j][i] : *reinterpret_cast<const float4*>(row + k);
+              v = (K <= kPass && k0 == 0) ? keep[j][i] : __ldcg(reinterpret_cast<const float4*>(row + k));
               const float4 w4 = *reinterpret_cast<const float4*>(sNw + (k - k0));
               v.x = v.x * inv[j] * w4.x;
               v.y = v.y * inv[j] * w4.y;
@@ -319,13 +324,120 @@ __global__ void __launch_bounds__(kSgThreads) skinny_gemm_kernel(const SkinnyArg
   }
 }
 
+// MT: token tiles of 8 (2, 4 or 8 -> up to 16, 32, 64 tokens).
+template <int MT, int MODE>
+__global__ void __launch_bounds__(kSgThreads) skinny_gemm_kernel(const SkinnyArgs args) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  pdl_launch_dependents();
+  const SkinnyBlock<MT, MODE> blk(args, blockIdx.x, blockIdx.y, blockIdx.z, smem_raw);
+  blk.request_weights();
+  pdl_wait();
+  blk.run();
+}
+
+// ---------------------------------------------------------------------------------------------
+// A chain of products in one launch: phase p+1 reads what phase p wrote (the residual stream, an
+// activation), so the phases are separated by barriers over the whole grid, and every block
+// requests the first weight chunks of its next phase before it waits at the barrier: the weights
+// stream while the grid synchronises.  One block per SM at most (the grid never exceeds what is
+// resident at once, so every block reaches every barrier); the wait is bounded all the same and
+// records a status instead of spinning for ever.
+constexpr int kChainPhases = 4;
+constexpr unsigned kChainSpinLimit = 1u << 24;
+constexpr unsigned long long kChainPerLaunch = 4096;  // what every launch adds to the counter (> 3 * 1024 arrivals)
+
+struct SkinnyChain {
+  SkinnyArgs phase[kChainPhases];
+  int mode[kChainPhases];
+  int gx[kChainPhases], gy[kChainPhases], gz[kChainPhases];
+  int n_phases;
+  unsigned long long* counter;  // grows by kChainPerLaunch per launch, whatever its grid
+  int* status;                  // set to 1 when a barrier wait gave up
+};
+
+__device__ __forceinline__ unsigned long long chain_load(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];\n" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+template <int MT>
+__global__ void __launch_bounds__(kSgThreads) skinny_chain_kernel(const SkinnyChain ch) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ unsigned long long s_base;
+  pdl_launch_dependents();
+  const int G = gridDim.x;
+  auto for_block = [&](int p, int v, auto&& fn) {
+    const int bx = v % ch.gx[p], by = (v / ch.gx[p]) % ch.gy[p], bz = v / (ch.gx[p] * ch.gy[p]);
+    switch (ch.mode[p]) {
+      case kSgStore: fn(SkinnyBlock<MT, kSgStore>(ch.phase[p], bx, by, bz, smem_raw)); break;
+      case kSgSwiglu: fn(SkinnyBlock<MT, kSgSwiglu>(ch.phase[p], bx, by, bz, smem_raw)); break;
+      default: fn(SkinnyBlock<MT, kSgResidual>(ch.phase[p], bx, by, bz, smem_raw)); break;
+    }
+  };
+  auto n_blocks = [&](int p) { return ch.gx[p] * ch.gy[p] * ch.gz[p]; };
+
+  bool requested = false;
+  if (static_cast<int>(blockIdx.x) < n_blocks(0)) {
+    for_block(0, blockIdx.x, [](const auto& blk) { blk.request_weights(); });
+    requested = true;
+  }
+  pdl_wait();
+  // every launch adds kChainPerLaunch in total, so the count at the start is a multiple of it
+  // (plus the arrivals of faster blocks of this launch, fewer than that)
+  if (threadIdx.x == 0) s_base = chain_load(ch.counter) / kChainPerLaunch * kChainPerLaunch;
+  __syncthreads();
+  const unsigned long long base = s_base;
+
+  for (int p = 0; p < ch.n_phases; ++p) {
+    for (int v = blockIdx.x; v < n_blocks(p); v += G) {
+      for_block(p, v, [&](const auto& blk) {
+        if (!requested) blk.request_weights();
+        blk.run();
+      });
+      requested = false;
+      __syncthreads();  // shared memory is free for the next block of work
+    }
+    if (p + 1 < ch.n_phases) {
+      if (static_cast<int>(blockIdx.x) < n_blocks(p + 1)) {
+        for_block(p + 1, blockIdx.x, [](const auto& blk) { blk.request_weights(); });
+        requested = true;
+      }
+      // barrier p: everything written so far is visible to every block afterwards
+      if (threadIdx.x == 0) {
+        __threadfence();
+        atomicAdd(ch.counter, 1ULL);
+        const unsigned long long target = base + static_cast<unsigned long long>(p + 1) * G;
+        unsigned spins = 0;
+        while (chain_load(ch.counter) < target) {
+          if (++spins > kChainSpinLimit) {
+            atomicExch(ch.status, 1);
+            break;
+          }
+          __nanosleep(40);  // a hundred and more blocks poll one line: leave room for the arrivals
+        }
+        __threadfence();
+      }
+      __syncthreads();
+    }
+  }
+  // Block 0 is past the last barrier, so every arrival of this launch has been counted: it adds
+  // what is missing to the next multiple.
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    atomicAdd(ch.counter, kChainPerLaunch - static_cast<unsigned long long>(ch.n_phases - 1) * G);
+}
+
+inline size_t skinny_smem(int MP, int kx) {
+  return static_cast<size_t>(kSgStages) * kSgRows * kSgWStride * sizeof(bf16) +
+         static_cast<size_t>(MP) * (kx + 8) * sizeof(bf16) + 3 * 32 * MP * sizeof(float) +
+         static_cast<size_t>(kx) * sizeof(float);
+}
+
 template <int MT, int MODE>
 int launch_skinny(const SkinnyArgs& a, int k_max, cudaStream_t stream) {
   constexpr int MP = MT * 8;
   const int kx = (min(a.k_slice, k_max) + kSgChunk - 1) / kSgChunk * kSgChunk;
-  const size_t smem = static_cast<size_t>(kSgStages) * kSgRows * kSgWStride * sizeof(bf16) +
-                      static_cast<size_t>(MP) * (kx + 8) * sizeof(bf16) + 3 * 32 * MP * sizeof(float) +
-                      static_cast<size_t>(kx) * sizeof(float);
+  const size_t smem = skinny_smem(MP, kx);
   if (smem > 220 * 1024) return PMM_ERR_BAD_ARGUMENT;
   auto kern = skinny_gemm_kernel<MT, MODE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -343,6 +455,21 @@ int dispatch_skinny(const SkinnyArgs& a, int k_max, cudaStream_t stream) {
   if (a.M <= 32) return launch_skinny<4, MODE>(a, k_max, stream);
   if (a.M <= 64) return launch_skinny<8, MODE>(a, k_max, stream);
   return PMM_ERR_BAD_ARGUMENT;
+}
+
+template <int MT>
+int launch_chain(const SkinnyChain& ch, size_t smem, int grid, cudaStream_t stream) {
+  auto kern = skinny_chain_kernel<MT>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  // every block must be resident at once: the barriers wait for all of them
+  int per_sm = 0;
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kSgThreads, smem);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (per_sm < 1) return PMM_ERR_BAD_ARGUMENT;
+  launch_pdl(kern, dim3(grid), dim3(kSgThreads), smem, stream, ch);
+  return launch_status();
 }
 
 }  // namespace pmm
@@ -382,4 +509,97 @@ PMM_EXPORT int pmm_skinny_gemm(int mode, int M, int N, const void* x0, long long
     case pmm::kSgResidual: return pmm::dispatch_skinny<pmm::kSgResidual>(a, k_max, stream);
     default: return PMM_ERR_BAD_ARGUMENT;
   }
+}
+
+// One phase of pmm_skinny_chain: the arguments of pmm_skinny_gemm without M, k_split and stream.
+struct PmmSkinnyPhase {
+  int mode, N;
+  const void* x0;
+  long long ldx0;
+  const float* h_in;
+  const float* norm_w;
+  float eps;
+  const void* w0;
+  int K0;
+  float scale0;
+  const void* x1;
+  long long ldx1;
+  const void* w1;
+  int K1;
+  float scale1;
+  void* y;
+  long long ldy;
+  float* h_out;
+};
+
+// Up to 4 products in one launch, each reading what the one before it wrote, separated by
+// barriers over the grid (at most 16 tokens).  `counter` (one 64-bit integer, zero at first use,
+// owned by these launches) and `status` (an int that becomes 1 if a barrier wait ever gave up;
+// the results of that launch are then not to be used) live in device memory.
+PMM_EXPORT int pmm_skinny_chain(const PmmSkinnyPhase* phases, int n_phases, int M, unsigned long long* counter,
+                                int* status, cudaStream_t stream) {
+  if (M <= 0 || n_phases <= 0) return 0;
+  if (n_phases > pmm::kChainPhases || M > 16 || !counter || !status) return PMM_ERR_BAD_ARGUMENT;
+  static int n_sm = 0;
+  if (n_sm == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0)
+      return PMM_ERR_BAD_ARGUMENT;
+  }
+  pmm::SkinnyChain ch{};
+  ch.n_phases = n_phases;
+  ch.counter = counter;
+  ch.status = status;
+  size_t smem = 0;
+  int most = 1;
+  for (int p = 0; p < n_phases; ++p) {
+    const PmmSkinnyPhase& ph = phases[p];
+    if (ph.N <= 0 || ph.K0 <= 0 || ph.K0 % 8 || (ph.w1 && (ph.K1 <= 0 || ph.K1 % 8 || !ph.x1))) return PMM_ERR_BAD_ARGUMENT;
+    if ((ph.x0 == nullptr) == (ph.h_in == nullptr)) return PMM_ERR_BAD_ARGUMENT;
+    if (ph.mode != pmm::kSgResidual && (ph.w1 != nullptr || !ph.y)) return PMM_ERR_BAD_ARGUMENT;
+    if (ph.mode == pmm::kSgResidual && !ph.h_out) return PMM_ERR_BAD_ARGUMENT;
+    if (ph.mode < 0 || ph.mode > 2) return PMM_ERR_BAD_ARGUMENT;
+    pmm::SkinnyArgs& a = ch.phase[p];
+    a.p[0] = {static_cast<const pmm::bf16*>(ph.x0), ph.ldx0, ph.h_in, ph.norm_w, ph.eps,
+              static_cast<const pmm::bf16*>(ph.w0), ph.K0, ph.scale0};
+    a.n_problems = 1;
+    int k_max = ph.K0;
+    if (ph.w1) {
+      a.p[1] = {static_cast<const pmm::bf16*>(ph.x1), ph.ldx1, nullptr, nullptr, 0.f,
+                static_cast<const pmm::bf16*>(ph.w1), ph.K1, ph.scale1};
+      a.n_problems = 2;
+      k_max = ph.K0 > ph.K1 ? ph.K0 : ph.K1;
+    }
+    a.M = M;
+    a.N = ph.N;
+    a.y = static_cast<pmm::bf16*>(ph.y);
+    a.ldy = ph.ldy;
+    a.h_out = ph.h_out;
+    const int cols = ph.mode == pmm::kSgSwiglu ? 16 : pmm::kSgRows;
+    const int gx = (ph.N + cols - 1) / cols;
+    const int chunks = (k_max + pmm::kSgChunk - 1) / pmm::kSgChunk;
+    // only the residual add can split K over blocks; as many slices as keep the phase within one
+    // block per SM (a product with the norm prologue keeps its whole rows)
+    int k_split = 1;
+    if (ph.mode == pmm::kSgResidual && !ph.h_in) {
+      k_split = n_sm / (gx * a.n_problems);
+      if (k_split < 1) k_split = 1;
+      if (k_split > chunks) k_split = chunks;
+    }
+    a.k_slice = ((chunks + k_split - 1) / k_split) * pmm::kSgChunk;
+    ch.mode[p] = ph.mode;
+    ch.gx[p] = gx;
+    ch.gy[p] = (k_max + a.k_slice - 1) / a.k_slice;
+    ch.gz[p] = a.n_problems;
+    const int kx = (a.k_slice < k_max ? a.k_slice : (k_max + pmm::kSgChunk - 1) / pmm::kSgChunk * pmm::kSgChunk);
+    const size_t need = pmm::skinny_smem(16, kx);
+    if (need > smem) smem = need;
+    const int blocks = ch.gx[p] * ch.gy[p] * ch.gz[p];
+    if (blocks > most) most = blocks;
+  }
+  if (smem > 220 * 1024) return PMM_ERR_BAD_ARGUMENT;
+  int grid = most < n_sm ? most : n_sm;
+  if (grid > 1024) grid = 1024;  // the counter arithmetic allows 3 * 1024 arrivals a launch
+  return pmm::launch_chain<2>(ch, smem, grid, stream);
 }

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import c_float, c_int, c_longlong, c_void_p
-from typing import List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -60,6 +60,7 @@ _SIGNATURES = {
                                   c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
                                   c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "pmm_l2_prefetch": [c_void_p, c_void_p, c_int, c_void_p],
+    "pmm_skinny_chain": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "pmm_flash_decode_attention": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_float,
                                    c_float, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -708,6 +709,85 @@ def skinny_residual(h: Tensor, products: Sequence[Tuple[Tensor, Tensor, float]])
           a1[4], None, 0, h.data_ptr(), k_split, _stream())
 
 
+class _SkinnyPhase(ctypes.Structure):
+    """One product of skinny_chain; mirrors PmmSkinnyPhase of csrc/skinny_gemm.cu."""
+    _fields_ = [("mode", ctypes.c_int), ("N", ctypes.c_int), ("x0", ctypes.c_void_p), ("ldx0", ctypes.c_longlong),
+                ("h_in", ctypes.c_void_p), ("norm_w", ctypes.c_void_p), ("eps", ctypes.c_float),
+                ("w0", ctypes.c_void_p), ("K0", ctypes.c_int), ("scale0", ctypes.c_float),
+                ("x1", ctypes.c_void_p), ("ldx1", ctypes.c_longlong), ("w1", ctypes.c_void_p), ("K1", ctypes.c_int),
+                ("scale1", ctypes.c_float), ("y", ctypes.c_void_p), ("ldy", ctypes.c_longlong),
+                ("h_out", ctypes.c_void_p)]
+
+
+_CHAIN_STATE: Dict[torch.device, Tuple[Tensor, Tensor]] = {}
+SKINNY_CHAIN_MAX = 4
+
+
+def _chain_state(device: torch.device) -> Tuple[Tensor, Tensor]:
+    st = _CHAIN_STATE.get(device)
+    if st is None:
+        st = (torch.zeros(1, dtype=torch.int64, device=device), torch.zeros(1, dtype=torch.int32, device=device))
+        _CHAIN_STATE[device] = st
+    return st
+
+
+def skinny_chain_status(device) -> int:
+    """0, or 1 when a barrier wait of a skinny_chain launch on this device ever gave up (synchronises)."""
+    st = _CHAIN_STATE.get(torch.device(device))
+    return 0 if st is None else int(st[1].item())
+
+
+def skinny_chain(h: Tensor, phases: Sequence[Tuple]) -> None:
+    """Up to 4 weight-streaming products over the float32 stream ``h`` [M <= 16, D] in ONE launch,
+    each reading what the one before it wrote (barriers over the grid in between, the next
+    product's weights requested before each barrier).  Phases:
+      ("residual", [(x, w, scale), ...])                      h += sum scale * x @ w^T      (1 or 2 products)
+      ("swiglu", norm_weight, eps, gate_up, gate_mult, out)   out = silu(g * gate_mult) * u, [g|u] = norm(h) @ gate_up^T
+      ("store", norm_weight, eps, weight, out)                out = norm(h) @ weight^T
+    """
+    _cuda(h)
+    M, D = h.shape
+    _need(h.dtype == torch.float32 and h.is_contiguous() and M <= 16, "skinny_chain: h must be contiguous float32 [<=16, D]")
+    _need(1 <= len(phases) <= SKINNY_CHAIN_MAX, f"skinny_chain: 1 to {SKINNY_CHAIN_MAX} phases")
+    arr = (_SkinnyPhase * len(phases))()
+    for ph, slot in zip(phases, arr):
+        kind = ph[0]
+        if kind == "residual":
+            products = ph[1]
+            _need(1 <= len(products) <= 2, "skinny_chain: one or two products per residual phase")
+            slot.mode, slot.N, slot.h_out = 2, D, h.data_ptr()
+            for i, (x, w, sc) in enumerate(products):
+                _cuda(x, w)
+                K = x.shape[1]
+                _need(x.dtype == torch.bfloat16 and x.shape[0] == M and x.stride(1) == 1 and x.stride(0) % 8 == 0
+                      and x.data_ptr() % 16 == 0, "skinny_chain: x must be bfloat16 [M, K] with 16-byte aligned rows")
+                _skinny_check(M, w, K, "skinny_chain")
+                _need(w.shape[0] == D, "skinny_chain: weight rows must equal the stream width")
+                if i == 0:
+                    slot.x0, slot.ldx0, slot.w0, slot.K0, slot.scale0 = x.data_ptr(), x.stride(0), w.data_ptr(), K, float(sc)
+                else:
+                    slot.x1, slot.ldx1, slot.w1, slot.K1, slot.scale1 = x.data_ptr(), x.stride(0), w.data_ptr(), K, float(sc)
+        elif kind in ("swiglu", "store"):
+            norm_w, eps, w = ph[1], ph[2], ph[3]
+            out = ph[-1]
+            _cuda(norm_w, w, out)
+            _skinny_check(M, w, D, "skinny_chain")
+            _need(skinny_fits(M, D), f"skinny_chain: {M} tokens x {D} columns do not fit in shared memory")
+            _f32vec(norm_w, D, "skinny_chain: norm weight")
+            n_out = w.shape[0] // 2 if kind == "swiglu" else w.shape[0]
+            _need(out.dtype == torch.bfloat16 and out.shape == (M, n_out) and out.stride(1) == 1
+                  and (kind == "store" or w.shape[0] == 2 * n_out), "skinny_chain: out must be bfloat16 [M, N]")
+            slot.mode, slot.N = (1 if kind == "swiglu" else 0), n_out
+            slot.h_in, slot.norm_w, slot.eps = h.data_ptr(), norm_w.data_ptr(), float(eps)
+            slot.w0, slot.K0, slot.scale0 = w.data_ptr(), D, (float(ph[4]) if kind == "swiglu" else 1.0)
+            slot.y, slot.ldy = out.data_ptr(), out.stride(0)
+        else:
+            raise KernelError(f"skinny_chain: unknown phase {kind!r}")
+    counter, status = _chain_state(h.device)
+    _call("pmm_skinny_chain", ctypes.cast(arr, ctypes.c_void_p), len(phases), M, counter.data_ptr(), status.data_ptr(),
+          _stream())
+
+
 _TC_STATUS = {}
 
 
@@ -802,7 +882,6 @@ def sample_rows(logits: Tensor, temperature: Optional[Tensor], seeds: Optional[T
 def l2_prefetch(tensors: Sequence[Tensor]) -> None:
     """Asks the memory system to bring these tensors (contiguous, at most 8 per call, further
     ones in further launches) into L2; nothing waits for it."""
-    import ctypes
     ts = [t for t in tensors if t is not None and t.numel() > 0]
     for i in range(0, len(ts), 8):
         part = ts[i:i + 8]

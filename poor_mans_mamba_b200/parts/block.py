@@ -12,6 +12,7 @@ writes the stream once.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -22,6 +23,13 @@ from .base import (FeedForward, LayerCache, LayerSpec, Mixer, Norm, ParamSpec, P
 from .norm import fold_branches
 
 Tensor = torch.Tensor
+
+
+# The products after the mixers as ONE launch with barriers over the grid (K.skinny_chain).  Off by
+# default: measured at 8 tokens a barrier costs about 3.5 us (fence, arrival, poll), a launch with
+# programmatic dependent launch about 1.2 us, so the chain takes 17.8 us where the three separate
+# launches take 10.7 us.
+_CHAINED = os.environ.get("PMM_SKINNY_CHAIN", "0") == "1"
 
 
 class ResidualStream:
@@ -170,12 +178,21 @@ class ParallelPreNormBlock(Part):
                 products[i] = (m.pre_output(proj[:, c0:c1], ctx, cache), m.output_weight(), m.out_scale)
         if side is not None:
             main.wait_stream(side)
-        K.skinny_residual(h, products)  # h = (h + s0 * y0 W0^T) + s1 * y1 W1^T, in one launch
-        if self.ffn is not None:
-            act = ws.alloc((T, self.ffn.intermediate_size), ctx.dtype)
-            K.skinny_swiglu_norm(h, self.ffn_norm.weight, self.ffn_norm.eps, self.ffn.gate_up,
-                                 self.ffn.gate_multiplier, act)
-            K.skinny_residual(h, [(act, self.ffn.down, self.ffn.out_scale)])
+        # h = (h + s0 * y0 W0^T) + s1 * y1 W1^T in one launch, then the feed-forward
+        act = ws.alloc((T, self.ffn.intermediate_size), ctx.dtype) if self.ffn is not None else None
+        if _CHAINED:
+            phases = [("residual", products)]
+            if self.ffn is not None:
+                phases += [("swiglu", self.ffn_norm.weight, self.ffn_norm.eps, self.ffn.gate_up,
+                            self.ffn.gate_multiplier, act),
+                           ("residual", [(act, self.ffn.down, self.ffn.out_scale)])]
+            K.skinny_chain(h, phases)
+        else:
+            K.skinny_residual(h, products)
+            if self.ffn is not None:
+                K.skinny_swiglu_norm(h, self.ffn_norm.weight, self.ffn_norm.eps, self.ffn.gate_up,
+                                     self.ffn.gate_multiplier, act)
+                K.skinny_residual(h, [(act, self.ffn.down, self.ffn.out_scale)])
         ws.release(mark)
 
     def forward(self, stream: ResidualStream, ctx, cache: LayerCache) -> None:

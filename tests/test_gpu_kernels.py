@@ -467,6 +467,57 @@ def test_unsupported_sizes_are_refused():
                      torch.zeros(2, 2, dtype=torch.float16, device=DEV))
 
 
+@pytest.mark.parametrize("M,D,F,I2", [(8, 1024, 2048, 512), (1, 96, 160, 64), (16, 520, 264, 1544), (5, 1280, 3072, 768)])
+def test_skinny_chain_matches_separate_products(M, D, F, I2):
+    """Mixer output projections into the stream, norm + gate/up + SwiGLU, down projection into
+    the stream and the next norm + projection, as one launch with grid barriers, against float64."""
+    g = torch.Generator().manual_seed(M * D)
+    bf = torch.bfloat16
+    r = lambda *sh: torch.randn(*sh, generator=g)
+    h0 = r(M, D)
+    y1, y2 = (r(M, 768) * 0.5).to(bf), (r(M, I2) * 0.5).to(bf)
+    w1, w2 = (r(D, 768) * 0.05).to(bf), (r(D, I2) * 0.05).to(bf)
+    nw1, nw2 = torch.rand(D, generator=g) + 0.5, torch.rand(D, generator=g) + 0.5
+    gu, down = (r(2 * F, D) * 0.05).to(bf), (r(D, F) * 0.05).to(bf)
+    w_next = (r(200, D) * 0.05).to(bf)
+    eps = 1e-5
+
+    def norm(x, w):
+        return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w.double()
+
+    h_mid = h0.double() + 0.9 * (y1.double() @ w1.double().T) + 1.1 * (y2.double() @ w2.double().T)
+    gate_up = norm(h_mid, nw1).to(bf).double() @ gu.double().T
+    act = torch.nn.functional.silu(gate_up[:, :F] * 1.3) * gate_up[:, F:]
+
+    hd = h0.to(DEV).contiguous()
+    act_d = torch.empty(M, F, dtype=bf, device=DEV)
+    nxt_d = torch.empty(M, 200, dtype=bf, device=DEV)
+    dev = lambda t: t.to(DEV)
+
+    def check(what):
+        torch.cuda.synchronize()
+        assert K().skinny_chain_status(DEV) == 0
+        close(act_d, act, bf, what=f"{what}: activation")
+        # the stream and the next projection, from the activation the kernel itself rounded
+        h_end = h_mid + 0.7 * (act_d.double().cpu() @ down.double().T)
+        close(hd, h_end, torch.float32, scale=30.0, what=f"{what}: stream")
+        return h_end
+
+    for rep in range(2):  # twice: the barrier counter carries over from launch to launch
+        hd.copy_(h0)
+        K().skinny_chain(hd, [("residual", [(dev(y1), dev(w1), 0.9), (dev(y2), dev(w2), 1.1)]),
+                              ("swiglu", dev(nw1), eps, dev(gu), 1.3, act_d),
+                              ("residual", [(act_d, dev(down), 0.7)]),
+                              ("store", dev(nw2), eps, dev(w_next), nxt_d)])
+        h_end = check(f"run {rep}")
+        close(nxt_d, norm(h_end, nw2).to(bf).double() @ w_next.double().T, bf, what="next projection")
+    # chains of one and of two phases leave the counter consistent for the next launch
+    hd.copy_(h0)
+    K().skinny_chain(hd, [("residual", [(dev(y1), dev(w1), 0.9), (dev(y2), dev(w2), 1.1)])])
+    K().skinny_chain(hd, [("swiglu", dev(nw1), eps, dev(gu), 1.3, act_d), ("residual", [(act_d, dev(down), 0.7)])])
+    check("two shorter chains")
+
+
 @pytest.mark.parametrize("M", [1, 7, 16, 17, 40, 64])
 @pytest.mark.parametrize("N,Kd", [(50, 96), (1024, 1000), (4120, 1024), (200, 2048)])
 def test_skinny_gemm_modes(M, N, Kd):

@@ -39,7 +39,7 @@ _SIGNATURES = {
                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_ssm_scan_seq": [c_void_p, c_int, c_void_p, c_longlong, c_float, c_void_p, c_void_p,
                          c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                         c_int, c_void_p, c_longlong, c_float, c_void_p, c_int, c_void_p],
+                         c_int, c_void_p, c_longlong, c_float, c_void_p, c_int, c_int, c_void_p],
     "pmm_ssd_supported": [c_int, c_int],
     "pmm_ssd_chunked": [c_void_p, c_int, c_void_p, c_longlong, c_float, c_void_p, c_void_p, c_void_p,
                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -329,9 +329,10 @@ def _gate_args(gate, out: Tensor, what: str):
 
 def ssm_scan_seq(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Tensor, a_log: Tensor,
                  d_skip: Tensor, state: Tensor, cu: Tensor, slots: Tensor, n_seq: int, out: Tensor,
-                 n_groups: int, gate=None) -> None:
+                 n_groups: int, gate=None, one_token: bool = False) -> None:
     """Token-serial Mamba2 recurrence from the saved state; state[slots, H, P, N] is updated.
-    ``gate`` = (z view [T, I], z_scale, z_bias or None): the output is y * silu(z*z_scale + z_bias)."""
+    ``gate`` = (z view [T, I], z_scale, z_bias or None): the output is y * silu(z*z_scale + z_bias).
+    ``one_token``: sequence s brings exactly token s (a decode step); ``cu`` is then not read."""
     _cuda(xbc, dt_raw, dt_shift, a_log, d_skip, state, cu, slots, out)
     _need(state.dtype == torch.float32 and state.dim() == 4 and state.is_contiguous(),
           "ssm_scan: state must be contiguous float32 [slots, H, P, N]")
@@ -348,7 +349,8 @@ def ssm_scan_seq(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Tensor,
     zp, ld_z, zs, zb = _gate_args(gate, out, "ssm_scan")
     _call("pmm_ssm_scan_seq", xbc.data_ptr(), ld_x, dt_raw.data_ptr(), ld_dt, float(dt_scale),
           dt_shift.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), cu.data_ptr(),
-          slots.data_ptr(), out.data_ptr(), n_seq, H, P, N, n_groups, zp, ld_z, zs, zb, _dt(xbc), _stream())
+          slots.data_ptr(), out.data_ptr(), n_seq, H, P, N, n_groups, zp, ld_z, zs, zb, int(bool(one_token)),
+          _dt(xbc), _stream())
 
 
 SSD_CHUNK = 64  # tokens per chunk of the tensor-core scan

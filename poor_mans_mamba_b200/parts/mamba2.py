@@ -178,7 +178,8 @@ class Mamba2Mixer(Mixer):
                                ctx.cu_seqlens, ctx.slots, ctx.new_lens, y, self.n_groups, scratch, gate=gate)
         else:
             K.ssm_scan_seq(xbc, dt, self.dt_scale, self.dt_shift, self.a_log, self.d_skip, state,
-                           ctx.cu_seqlens, ctx.slots, ctx.n_seq, y, self.n_groups, gate=gate)
+                           ctx.cu_seqlens, ctx.slots, ctx.n_seq, y, self.n_groups, gate=gate,
+                           one_token=ctx.decode_only)
         if gate is not None:
             return y
         gated = ws.alloc((T, i_dim), proj.dtype)

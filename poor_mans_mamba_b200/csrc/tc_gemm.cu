@@ -2,16 +2,21 @@
 //   act[t, f] = silu((x W_gate^T)[t, f] * gate_mult) * (x W_up^T)[t, f]         (bfloat16 out)
 // or, in plain mode, y = x W^T.  x [T, K] and W [rows, K] are bfloat16, K-major.
 //
-// One block computes a 128-token x 64-feature tile of act (a 128 x 128 accumulator: the 64
-// gate columns next to their 64 up columns) with the fifth-generation tensor cores:
+// One block computes a 256-token x 128-feature tile of act (two 128 x 256 accumulators, one per
+// half of the tokens: the 128 gate columns next to their 128 up columns) with the
+// fifth-generation tensor cores.  The tile is that large because operand traffic decides: a
+// 256 x 256 tile needs 1 MB of operands from L2 for 134 MFLOP, half of what 128 x 256 needs, and a
+// 2,048 x 4,096 product is 128 such tiles, one per SM in a single wave.
 //   * operands are brought into shared memory by TMA (cp.async.bulk.tensor.2d, 128-byte
-//     swizzle, out-of-range rows read as zero), four stages deep, signalled by mbarriers;
-//   * one elected thread issues tcgen05.mma (M = 128, N = 128, K = 16 per instruction, four
-//     per 64-column stage) with the accumulator in tensor memory (128 lanes x 128 columns);
-//     tcgen05.commit releases a stage back to the producer and finally publishes the tile;
-//   * four epilogue warps read the accumulator with tcgen05.ld (each warp its own 32 lanes),
-//     apply the activation in float and store bfloat16 rows.
-// Warp roles: 0 = TMA producer, 1 = tensor-memory owner and MMA issuer, 2..5 = epilogue.
+//     swizzle, out-of-range rows read as zero), three stages of 64 KB, signalled by mbarriers;
+//   * one elected thread issues tcgen05.mma (M = 128, N = 256, K = 16 per instruction, two token
+//     halves x four per 64-column stage) with the accumulators in tensor memory (all 512
+//     columns: 128 lanes x 256 columns for each half); tcgen05.commit releases a stage back to
+//     the producer and finally publishes the tile;
+//   * eight epilogue warps read the accumulators with tcgen05.ld (a warp reads the 32 lanes of
+//     its quarter; four warps per token half), apply the activation in float and store
+//     bfloat16 rows.
+// Warp roles: 0 = TMA producer, 1 = tensor-memory owner and MMA issuer, 2..9 = epilogue.
 // Every wait on an mbarrier is bounded: after kSpinLimit polls the waiter records a code in
 // *status, raises the block's abort flag and all roles leave their loops; the block still
 // waits (bounded) for its own copies in flight and frees its tensor memory before it exits.
@@ -25,14 +30,16 @@ namespace pmm {
 
 using bf16 = __nv_bfloat16;
 
-constexpr int kTcM = 128;        // tokens per tile
-constexpr int kTcN = 128;        // accumulator columns per tile
+constexpr int kTcM = 256;        // tokens per tile: two halves of 128, one MMA row block each
+constexpr int kTcMH = 128;       // rows of one MMA
+constexpr int kTcN = 256;        // accumulator columns per tile
 constexpr int kTcK = 64;         // K per stage: one 128-byte swizzle row of bfloat16
-constexpr int kTcStages = 4;
-constexpr int kTcThreads = 192;
+constexpr int kTcStages = 3;
+constexpr int kTcThreads = 320;
+constexpr int kTcTmemCols = 512; // both accumulators: all of an SM's tensor memory (one block per SM, by shared memory)
 constexpr unsigned kSpinLimit = 1u << 22;
-constexpr int kTcABytes = kTcM * kTcK * 2;  // 16 KB
-constexpr int kTcBBytes = kTcN * kTcK * 2;  // 16 KB
+constexpr int kTcABytes = kTcM * kTcK * 2;  // 32 KB
+constexpr int kTcBBytes = kTcN * kTcK * 2;  // 32 KB
 constexpr size_t kTcSmem = static_cast<size_t>(kTcStages) * (kTcABytes + kTcBBytes) + 1024 /*alignment*/;
 
 enum { kTcPlain = 0, kTcSwiglu = 1 };
@@ -83,7 +90,7 @@ __device__ __forceinline__ unsigned long long umma_desc(const void* tile) {
 }
 
 // kind::f16 instruction descriptor: float accumulate, bfloat16 A and B, both K-major, N, M.
-constexpr unsigned kTcIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kTcN >> 3) << 17) | ((kTcM >> 4) << 24);
+constexpr unsigned kTcIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kTcN >> 3) << 17) | ((kTcMH >> 4) << 24);
 
 __device__ __forceinline__ void umma_f16(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc,
                                          unsigned idesc, unsigned accumulate) {
@@ -140,8 +147,8 @@ __global__ void __launch_bounds__(kTcThreads)
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (warp == 1) {  // tensor memory for the 128 x 128 float accumulator
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&s_tmem_base)), "r"(kTcN) : "memory");
+  if (warp == 1) {  // tensor memory for the two 128 x 256 float accumulators
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&s_tmem_base)), "r"(kTcTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -163,7 +170,8 @@ __global__ void __launch_bounds__(kTcThreads)
           break;
         }
         mbar_expect_tx(&bar_full[s], kTcABytes + kTcBBytes);
-        tma_load_2d(sA + s * kTcABytes, &map_x, kb * kTcK, m0, &bar_full[s]);
+        tma_load_2d(sA + s * kTcABytes, &map_x, kb * kTcK, m0, &bar_full[s]);                               // tokens 0..127
+        tma_load_2d(sA + s * kTcABytes + kTcABytes / 2, &map_x, kb * kTcK, m0 + kTcMH, &bar_full[s]);      // tokens 128..255
         if (MODE == kTcSwiglu) {
           tma_load_2d(sB + s * kTcBBytes, &map_w, kb * kTcK, n0, &bar_full[s]);                      // gate rows
           tma_load_2d(sB + s * kTcBBytes + kTcBBytes / 2, &map_w, kb * kTcK, F + n0, &bar_full[s]);  // up rows
@@ -195,20 +203,24 @@ __global__ void __launch_bounds__(kTcThreads)
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const unsigned long long a_desc = umma_desc(sA + s * kTcABytes);
         const unsigned long long b_desc = umma_desc(sB + s * kTcBBytes);
 #pragma unroll
-        for (int k = 0; k < kTcK / 16; ++k) {
-          // 16 columns further along K inside the swizzled row: 32 bytes = 2 units of 16 bytes
-          umma_f16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, kTcIdesc, (kb > 0 || k > 0) ? 1u : 0u);
+        for (int half = 0; half < 2; ++half) {
+          const unsigned long long a_desc = umma_desc(sA + s * kTcABytes + half * (kTcABytes / 2));
+#pragma unroll
+          for (int k = 0; k < kTcK / 16; ++k) {
+            // 16 columns further along K inside the swizzled row: 32 bytes = 2 units of 16 bytes
+            umma_f16(tmem_base + half * kTcN, a_desc + 2 * k, b_desc + 2 * k, kTcIdesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
         }
         umma_commit(&bar_empty[s]);  // the stage is free once these MMAs have read it
       }
       if (ok) umma_commit(&bar_accum);  // the tile is complete once all MMAs have finished
     }
   } else {
-    // ---------------------------------------------------------------- epilogue (warps 2..5)
-    const int quad = warp & 3;  // a warp may only read tensor-memory lanes 32*(warp % 4) ...
+    // ---------------------------------------------------------------- epilogue (warps 2..9)
+    const int quad = warp & 3;          // a warp may only read tensor-memory lanes 32*(warp % 4) ...
+    const int mhalf = (warp - 2) >> 2;  // which token half, i.e. which accumulator
     bool ok = mbar_wait(&bar_accum, 0, abort_flag);
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) {
@@ -216,17 +228,17 @@ __global__ void __launch_bounds__(kTcThreads)
       s_abort = 1;
     } else {
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      const int m = m0 + quad * 32 + lane;  // this thread's token row
-      const unsigned lane_base = tmem_base + (static_cast<unsigned>(quad * 32) << 16);
+      const int m = m0 + mhalf * kTcMH + quad * 32 + lane;  // this thread's token row
+      const unsigned lane_base = tmem_base + (static_cast<unsigned>(quad * 32) << 16) + mhalf * kTcN;
       if (MODE == kTcSwiglu) {
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
+#pragma unroll 1
+        for (int c = 0; c < kTcN / 64; ++c) {
           unsigned g[32], u[32];
-          tmem_ld32(lane_base + half * 32, g);
-          tmem_ld32(lane_base + 64 + half * 32, u);
+          tmem_ld32(lane_base + c * 32, g);
+          tmem_ld32(lane_base + kTcN / 2 + c * 32, u);
           asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
           if (m < T) {
-            bf16* dst = out + static_cast<long long>(m) * ld_out + n0 + half * 32;
+            bf16* dst = out + static_cast<long long>(m) * ld_out + n0 + c * 32;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               uint4 pack;
@@ -242,8 +254,8 @@ __global__ void __launch_bounds__(kTcThreads)
           }
         }
       } else {
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
+#pragma unroll 1
+        for (int q = 0; q < kTcN / 32; ++q) {
           unsigned v[32];
           tmem_ld32(lane_base + q * 32, v);
           asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
@@ -268,7 +280,7 @@ __global__ void __launch_bounds__(kTcThreads)
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTcN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTcTmemCols) : "memory");
   }
 }
 
@@ -304,10 +316,10 @@ inline bool make_map(CUtensorMap* map, const void* base, long long rows, long lo
 }  // namespace pmm
 
 // Whether the tensor-core product takes these sizes: K a multiple of 64, output columns a
-// multiple of 64 (SwiGLU: F) or 128 (plain), 16-byte aligned rows.
+// multiple of 128 (SwiGLU: F) or 256 (plain), 16-byte aligned rows.
 PMM_EXPORT int pmm_tc_gemm_supported(int mode, int K, int n_out, long long ldx, long long ld_out) {
   if (K <= 0 || K % pmm::kTcK || ldx % 8 || ld_out % 8) return 0;
-  return mode == pmm::kTcSwiglu ? (n_out % 64 == 0) : (n_out % 128 == 0);
+  return mode == pmm::kTcSwiglu ? (n_out % 128 == 0) : (n_out % 256 == 0);
 }
 
 // mode 1: out[T, F] = silu((x Wg^T) * gate_mult) * (x Wu^T) with w = [Wg; Wu] ([2F, K]).
@@ -320,7 +332,7 @@ PMM_EXPORT int pmm_tc_gemm(int mode, const void* x, long long ldx, const void* w
     return PMM_ERR_BAD_ARGUMENT;
   CUtensorMap map_x, map_w;
   const long long w_rows = mode == pmm::kTcSwiglu ? 2LL * n_out : n_out;
-  if (!pmm::make_map(&map_x, x, T, K, ldx, pmm::kTcM) || !pmm::make_map(&map_w, w, w_rows, K, K, pmm::kTcN / 2))
+  if (!pmm::make_map(&map_x, x, T, K, ldx, pmm::kTcMH) || !pmm::make_map(&map_w, w, w_rows, K, K, pmm::kTcN / 2))
     return PMM_ERR_BAD_ARGUMENT;
   const int cols_per_block = mode == pmm::kTcSwiglu ? pmm::kTcN / 2 : pmm::kTcN;
   dim3 grid((T + pmm::kTcM - 1) / pmm::kTcM, n_out / cols_per_block);

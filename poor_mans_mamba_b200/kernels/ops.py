@@ -809,7 +809,7 @@ def tc_gemm_status(device) -> int:
 
 def tc_gemm_supported(x: Tensor, weight: Tensor, n_out: int, swiglu: bool) -> bool:
     """Whether the tcgen05 product takes these operands (bfloat16, K a multiple of 64, output
-    columns a multiple of 64 for SwiGLU or 128 otherwise, 16-byte aligned rows)."""
+    columns a multiple of 128 for SwiGLU or 256 otherwise, 16-byte aligned rows)."""
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or not x.is_cuda:
         return False
     if x.dim() != 2 or x.stride(1) != 1 or not weight.is_contiguous() or x.data_ptr() % 16 or weight.data_ptr() % 16:

@@ -17,13 +17,15 @@ from .base import FeedForward, ParamSpec, register_feed_forward
 
 Tensor = torch.Tensor
 
-# The fused tcgen05 kernel (gate/up projection with the activation in its epilogue) is correct
-# and tested but, with 128 x 128 tiles fed by one block, bound by the L2-to-SM operand rate
-# (about 360-690 TFLOP/s measured against the library's 960-1460 on the same shapes), so the
-# library product plus the activation kernel stays the default until the two-block 256 x 256
-# form exists.  PMM_TCGEN05_FFN=1 switches it on for portions of at least this many tokens.
-_TC_FROM_TOKENS = 128
-_TC_ENABLED = os.environ.get("PMM_TCGEN05_FFN", "0") == "1"
+# Gate/up projection with the activation in the epilogue of one tcgen05 kernel (256 x 256 tiles,
+# TMA operands, accumulators in tensor memory): the [T, 2F] intermediate is never written.
+# Measured against the library product plus the activation kernel: 21.6 vs 34.7 us at 2,048 x
+# 1,024 -> 2 x 2,048 (launch-bound timing; 19-20 us each inside a step graph), 71 vs 72 us at
+# 8,192 tokens, 239 vs 236 us at 2,048 x 3,072 -> 2 x 12,288 (1,290 TFLOP/s).  It runs one tile
+# per block in a single wave, so it is used from about 96 tiles on; below that the library's
+# smaller tiles fill the GPU better.  PMM_TCGEN05_FFN=0 switches it off.
+_TC_FROM_TILES = 96
+_TC_ENABLED = os.environ.get("PMM_TCGEN05_FFN", "1") == "1"
 
 
 class SwiGLU(FeedForward):
@@ -49,9 +51,8 @@ class SwiGLU(FeedForward):
         T = x.shape[0]
         f = self.intermediate_size
         act = ctx.workspace.alloc((T, f), x.dtype)
-        if _TC_ENABLED and T >= _TC_FROM_TOKENS and K.tc_gemm_supported(x, self.gate_up, f, True):
-            # prompt portions in bfloat16: gate and up projection with the activation in the
-            # epilogue of one tcgen05 kernel; the [T, 2F] intermediate is never written
+        tiles = ((T + 255) // 256) * (f // 128)
+        if _TC_ENABLED and tiles >= _TC_FROM_TILES and K.tc_gemm_supported(x, self.gate_up, f, True):
             K.tc_gemm_swiglu(x, self.gate_up, self.gate_multiplier, act)
         else:
             gu = ctx.workspace.alloc((T, 2 * f), x.dtype)

@@ -562,10 +562,11 @@ def test_skinny_gemm_modes(M, N, Kd):
     close(hd, ref2, torch.float32, scale=30.0, what="skinny residual two products")
 
 
-@pytest.mark.parametrize("T,Kd,F", [(200, 128, 192), (128, 64, 64), (2048, 1024, 2048), (333, 1024, 448)])
+@pytest.mark.parametrize("T,Kd,F", [(200, 128, 128), (128, 64, 256), (2048, 1024, 2048), (333, 1024, 384), (700, 3072, 640)])
 def test_tcgen05_gemm_swiglu_and_plain(T, Kd, F):
     """The tcgen05 / TMA / tensor-memory product: SwiGLU epilogue and plain store, token counts
-    that are no multiple of the 128-row tile, several K stages (more than the pipeline is deep)."""
+    that are no multiple of the 256-row tile (and below its half), several K stages (more than
+    the pipeline is deep), and a refusal of feature counts off the tile."""
     g = torch.Generator().manual_seed(T + Kd + F)
     ops = K()
     bf = torch.bfloat16
@@ -578,7 +579,8 @@ def test_tcgen05_gemm_swiglu_and_plain(T, Kd, F):
     assert ops.tc_gemm_status(DEV) == 0
     gu = x.double() @ w.double().t()
     close(act, P.silu(gu[:, :F] * 1.5) * gu[:, F:], bf, what="tcgen05 swiglu")
-    if (2 * F) % 128 == 0:
+    assert not ops.tc_gemm_supported(x.to(DEV), w.to(DEV)[:2 * (F - 64)], F - 64, True)  # F no multiple of 128
+    if (2 * F) % 256 == 0:
         y = torch.full((T, 2 * F), float("nan"), dtype=bf, device=DEV)
         ops.tc_gemm(x.to(DEV), w.to(DEV), y)
         torch.cuda.synchronize()

@@ -8,8 +8,10 @@ A "step" is one decode step of the whole batch.  Default: Falcon-H1-0.5B layer s
 random weights (seed 2), bfloat16, batch 8, every request at a context that ends at 4,096
 tokens.  Prints ONE JSON line:
   value    decoded tokens/s over K steps, timed on the device with CUDA events;
-  e2e      the same through the Python entry point (Engine.step: scheduler, host token ids
-           in from pinned memory, sampled ids back to the host every step);
+  e2e      the same through the Python entry point (Engine.step: scheduler, the step's indices
+           in from pinned memory and the sampled ids back to the host every step; the engine
+           launches a decode step before the previous step's ids have arrived, feeding it the
+           ids that are still on the device, so the two copies overlap the next step);
   prefill  one 2,048-token prompt in one step: tokens/s, ms, fraction of the bf16 peak;
   roofline bytes the decode step must read (every weight once, the cache of the live
            requests) / its time, against the HBM copy peak;

@@ -23,7 +23,7 @@ import torch
 
 from ..kernels import ops as K
 from .context import StepContext
-from .workspace import Workspace
+from .workspace import Workspace, quiet_capture
 
 Tensor = torch.Tensor
 
@@ -140,7 +140,7 @@ class GraphDecoder:
         bk.workspace.freeze()
         graph = torch.cuda.CUDAGraph()
         before = K.launch_count
-        with torch.cuda.graph(graph):
+        with quiet_capture(graph):
             self._run(bk)
         bk.kernels_per_replay = K.launch_count - before
         bk.graph = graph

@@ -23,7 +23,7 @@ from ..cache.manager import CacheManager
 from ..cache.pages import OutOfPages
 from .context import StepContext
 from .model import Model
-from .workspace import Workspace
+from .workspace import Workspace, quiet_capture
 
 Tensor = torch.Tensor
 
@@ -146,7 +146,7 @@ class ModelRunner:
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         before = K.launch_count
-        with torch.cuda.graph(graph):
+        with quiet_capture(graph):
             logits = self.model.forward(ctx, self.cache.layer_caches(tables))
         entry.update(graph=graph, meta=meta, workspace=workspace, logits=logits, kernels=K.launch_count - before)
 

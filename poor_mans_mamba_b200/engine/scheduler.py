@@ -153,6 +153,8 @@ class Scheduler:
             self.cache.release(req.id)
         if req in self.running:
             self.running.remove(req)
+        if req in self.waiting:  # preempted, then found to have ended (a stop token read late)
+            self.waiting.remove(req)
         req.status = status
         if plan is not None:
             plan.ended.append(req.id)
@@ -256,5 +258,44 @@ class Scheduler:
             hit_eos = r.params.eos_id >= 0 and tok == r.params.eos_id
             if hit_eos or len(r.output) >= r.params.max_new_tokens:
                 self._end(r, "done")
+                finished.append(r)
+        return finished
+
+    # ------------------------------------------------------------------ results that arrive late
+    # A decode step whose sampled ids are still on their way to the host can be digested in two
+    # halves, so that the next step is planned and launched meanwhile: `advance` does everything
+    # that needs no token value (lengths, counters, ending by length) and leaves PENDING in the
+    # outputs; `resolve` fills the values in and applies the stop token, one step late.
+    PENDING = -1
+
+    def advance(self, plan: StepPlan) -> List[Tuple[Request, int]]:
+        """First half of `complete` for a step whose ids are not known yet.  Returns, for every
+        sampling entry in plan order, (request, index in its output) for `resolve`."""
+        self.counters["steps"] += 1
+        slots: List[Tuple[Request, int]] = []
+        for e in plan.entries:
+            r = e.req
+            r.n_computed += e.count
+            self.counters["decode_tokens" if e.count == 1 and r.output else "prefill_tokens"] += e.count
+            if not e.samples:
+                continue
+            slots.append((r, len(r.output)))
+            r.output.append(self.PENDING)
+            if len(r.output) >= r.params.max_new_tokens:
+                self._end(r, "done")
+        return slots
+
+    def resolve(self, slots: List[Tuple[Request, int]], sampled: List[int]) -> List[Request]:
+        """Second half: the ids of the entries that `advance` listed.  A request that hits its
+        stop token ends now; tokens it was given by later steps meanwhile are dropped."""
+        finished: List[Request] = []
+        for (r, idx), tok in zip(slots, sampled):
+            if idx >= len(r.output) or r.output[idx] != self.PENDING:
+                continue  # cut off by a stop token that an earlier step produced
+            r.output[idx] = int(tok)
+            if r.params.eos_id >= 0 and int(tok) == r.params.eos_id:
+                del r.output[idx + 1:]
+                if r.status != "done":
+                    self._end(r, "done")
                 finished.append(r)
         return finished

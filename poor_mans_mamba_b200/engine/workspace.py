@@ -7,6 +7,9 @@ more than any step before it (it then adds a chunk, and merges the chunks at the
 """
 from __future__ import annotations
 
+import contextlib
+import gc
+
 from typing import List, Tuple
 
 import torch
@@ -82,3 +85,19 @@ class Workspace:
                 raise RuntimeError("workspace is frozen and too small for this step")
             grow = max(size, self.capacity(), 1 << 20)
             self._chunks.append(torch.empty(grow, dtype=torch.uint8, device=self.device))
+
+
+@contextlib.contextmanager
+def quiet_capture(graph: "torch.cuda.CUDAGraph"):
+    """``torch.cuda.graph(graph)`` with the garbage collector held back: a collection that runs in
+    the middle of a capture may destroy CUDA graphs of objects that died earlier, and destroying a
+    graph while a stream is capturing invalidates the capture."""
+    gc.collect()
+    was_enabled = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph):
+            yield
+    finally:
+        if was_enabled:
+            gc.enable()

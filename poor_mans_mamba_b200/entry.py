@@ -35,13 +35,14 @@ class Engine:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", device: str = "cuda:0",
                  max_tokens: int = 65536, max_seqs: int = 64, page_size: int = 64,
                  max_batched_tokens: int = 2048, max_seq_len: int = 8192, cuda_graphs: bool = True,
-                 warm_graphs: bool = False):
+                 warm_graphs: bool = False, run_ahead: bool = True):
         """``max_tokens``: capacity of the key/value cache in tokens (whole pages);
         ``max_seqs``: most requests alive at a time (= number of fixed-state slots);
         ``max_batched_tokens``: token budget of one step; ``max_seq_len``: longest context
         served by the CUDA-graph decode path (longer requests decode through plain launches);
         ``cuda_graphs``: capture decode-only steps into CUDA graphs (``warm_graphs``: all
-        batch-size buckets at once here, else each at its first use)."""
+        batch-size buckets at once here, else each at its first use); ``run_ahead``: launch a
+        decode step before the previous one's ids have reached the host (see `step`)."""
         if not torch.cuda.is_available():
             raise RuntimeError("poor_mans_mamba_b200 runs on a CUDA device only; there is no CPU path")
         K.ensure_built()
@@ -59,6 +60,10 @@ class Engine:
         self.scheduler = Scheduler(self.cache, max_batched_tokens=max_batched_tokens, max_seqs=max_seqs)
         self.sampler = Sampler(self.device)
         self._next_id = 0
+        self.run_ahead = run_ahead and cuda_graphs
+        self._inflight = None   # (request ids, output slots, id fetch) of a launched decode step
+        self._fetch_bufs = [None, None, None]
+        self._fetch_turn = 0
 
     # ------------------------------------------------------------------ submit / step / poll
     def submit(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
@@ -73,41 +78,97 @@ class Engine:
         return rid
 
     def step(self) -> StepPlan:
-        """Plan and run one step; returns the plan (empty when nothing could run)."""
+        """Plan and run one step; returns the plan (empty when nothing could run).
+
+        Decode-only steps through the CUDA-graph path run one step ahead of the host: the step
+        is launched, its ids start their way to the host, and the call returns; the next call
+        plans and launches the following step (fed with the ids still on the device) before it
+        waits for the earlier ones.  A stop token is therefore seen one step late (the extra
+        token is dropped); `poll` and the end of `generate` wait for everything in flight."""
         plan = self.scheduler.plan()
         if not plan.entries:
-            return plan
+            if self._inflight is None:
+                return plan
+            self._resolve_inflight()
+            plan = self.scheduler.plan()
+            if not plan.entries:
+                return plan
+        pure = all(e.count == 1 and e.samples for e in plan.entries)
+        ids = [e.req.id for e in plan.entries]
+        ahead = (pure and self._inflight is not None and self._inflight[0] == ids and self._graph_decodable(ids))
+        if self._inflight is not None and not ahead:
+            # everything known first; a request that has just ended leaves the plan
+            self._resolve_inflight()
+            plan.entries = [e for e in plan.entries if not e.req.finished]
+            if not plan.entries:
+                return plan
+            ids = [e.req.id for e in plan.entries]
         entries = []
         temps, seeds, steps = [], [], []
         for e in plan.entries:
             r = e.req
             n_prompt = len(r.prompt)
-            if e.start >= n_prompt:
-                toks = r.output[e.start - n_prompt:e.start - n_prompt + e.count]
-            else:
-                toks = r.tokens[e.start:e.start + e.count]
-            entries.append(StepEntry(r.id, toks, [e.count - 1] if e.samples else []))
+            toks = None
+            if not ahead:
+                if e.start >= n_prompt:
+                    toks = r.output[e.start - n_prompt:e.start - n_prompt + e.count]
+                else:
+                    toks = r.tokens[e.start:e.start + e.count]
+            entries.append((r.id, toks, [e.count - 1] if e.samples else []))
             if e.samples:
                 temps.append(r.params.temperature)
                 seeds.append(r.params.seed)
                 steps.append(len(r.output))
         with torch.cuda.device(self.device):
-            if all(e.count == 1 and e.samples for e in plan.entries):
-                ids = self.runner.decode_tokens([e.req.id for e in plan.entries],
-                                                [en.tokens[0] for en in entries], temps, seeds, steps)
-                sampled = self.sampler.to_host(ids)
+            if pure and self._graph_decodable(ids):
+                tokens = None if ahead else [t[0] for _, t, _ in entries]
+                dev_ids = self.runner.decode_tokens(ids, tokens, temps, seeds, steps)
+                fetch = self._fetch_async(dev_ids)
+                slots = self.scheduler.advance(plan)
+                if ahead:
+                    self._resolve_inflight()  # the earlier step's ids; the GPU is busy with this one
+                self._inflight = (ids, slots, fetch)
+            elif pure:
+                dev_ids = self.runner.decode_tokens(ids, [t[0] for _, t, _ in entries], temps, seeds, steps)
+                self.scheduler.complete(plan, self.sampler.to_host(dev_ids))
             else:
-                logits = self.runner.step(entries)
-                sampled = self.sampler.sample(logits, temps, seeds, steps)
-        self.scheduler.complete(plan, sampled)
+                logits = self.runner.step([StepEntry(i, t, w) for i, t, w in entries])
+                self.scheduler.complete(plan, self.sampler.sample(logits, temps, seeds, steps))
         return plan
 
+    def _graph_decodable(self, ids) -> bool:
+        g = self.runner.graphs
+        return (self.run_ahead and g is not None and len(ids) <= g.bucket_sizes[-1]
+                and all(self.cache.lengths[i] + 1 <= g.max_seq_len for i in ids))
+
+    def _fetch_async(self, dev_ids: torch.Tensor):
+        """Starts the copy of a step's ids into pinned memory; (buffer, count, event)."""
+        n = dev_ids.numel()
+        i = self._fetch_turn
+        self._fetch_turn = (i + 1) % len(self._fetch_bufs)
+        if self._fetch_bufs[i] is None or self._fetch_bufs[i].numel() < n:
+            self._fetch_bufs[i] = torch.empty(max(n, 64), dtype=torch.int32, pin_memory=True)
+        buf = self._fetch_bufs[i]
+        buf[:n].copy_(dev_ids, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        return buf, n, ev
+
+    def _resolve_inflight(self) -> None:
+        if self._inflight is None:
+            return
+        _, slots, (buf, n, ev) = self._inflight
+        self._inflight = None
+        ev.synchronize()
+        self.scheduler.resolve(slots, buf[:n].tolist())
+
     def poll(self, rid: Hashable) -> Response:
+        self._resolve_inflight()
         r = self.scheduler.requests[rid]
         return Response(list(r.output), r.finished, r.status, r.preemptions)
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._inflight is not None
 
     # ------------------------------------------------------------------ one-call generation
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 16, temperature: float = 0.0,
@@ -118,6 +179,6 @@ class Engine:
         ids = [self.submit(p, SamplingParams(max_new_tokens=max_new_tokens, eos_id=eos,
                                              temperature=temperature, seed=seed + i))
                for i, p in enumerate(prompts)]
-        while self.scheduler.has_work():
+        while self.has_work():
             self.step()
         return [self.poll(i).tokens for i in ids]

@@ -113,3 +113,40 @@ def test_smoke_entry():
     sys.path.insert(0, ROOT)
     import __graft_entry__
     __graft_entry__.smoke()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_one_step_ahead_gives_the_same_tokens(case, dtype):
+    """The decode path launches a step before the previous one's ids have reached the host: greedy
+    and sampled outputs, stop tokens (seen a step late), requests of different lengths and a poll in
+    the middle all equal the step-by-step engine."""
+    from poor_mans_mamba_b200.engine.scheduler import SamplingParams
+    from poor_mans_mamba_b200.entry import Engine
+    which, d, cfg, weights = case
+    prompts, _ = prompts_of(which)
+
+    def run(run_ahead, params, poll_at=None):
+        eng = Engine(d, dtype=dtype, max_tokens=2048, max_seqs=4, page_size=16, run_ahead=run_ahead)
+        ids = [eng.submit(p, sp) for p, sp in zip(prompts, params)]
+        n = 0
+        while eng.has_work():
+            eng.step()
+            n += 1
+            if poll_at is not None and n == poll_at:
+                assert all(-1 not in eng.poll(i).tokens for i in ids)
+        out = [eng.poll(i) for i in ids]
+        assert eng.cache.free_slots == 4 and eng.cache.min_free_pages() == eng.cache.groups[next(iter(eng.cache.groups))].num_pages
+        return [(r.tokens, r.status) for r in out], eng
+
+    lens = [24, 9, 17, 30][:len(prompts)]
+    greedy = [SamplingParams(max_new_tokens=n, eos_id=-1) for n in lens]
+    base, _ = run(False, greedy)
+    ahead, eng = run(True, greedy)
+    assert ahead == base and eng.runner.graphs.replays > 0
+    assert run(True, greedy, poll_at=7)[0] == base
+    # stop tokens taken from the free-running outputs: in the middle of one request, at the end of another
+    stops = [base[0][0][len(base[0][0]) // 2], -1, base[2][0][-1] if len(base) > 2 else -1, -1][:len(prompts)]
+    with_stop = [SamplingParams(max_new_tokens=n, eos_id=e) for n, e in zip(lens, stops)]
+    assert run(True, with_stop)[0] == run(False, with_stop)[0]
+    sampled = [SamplingParams(max_new_tokens=n, eos_id=-1, temperature=0.8, seed=5 + i) for i, n in enumerate(lens)]
+    assert run(True, sampled)[0] == run(False, sampled)[0]

@@ -172,3 +172,84 @@ def test_random_traffic(seed):
         else:
             assert r.status in ("oom", "cache_full") and r.output == want[i][:len(r.output)]
     assert cache.free_slots == 3 and cache.min_free_pages() == cache.groups[(2, 4, 0)].num_pages
+
+
+def run_one_step_ahead(sched, cache, max_steps=10000):
+    """Drives the scheduler the way the engine's decode path does: a decode-only step whose
+    requests equal the previous step's is 'launched' (its tokens computed from what the device
+    knows) before the previous step's ids are handed to the scheduler."""
+    truth = {}      # request id -> every token the device has seen or produced (never PENDING)
+    inflight = None  # (ids, slots, sampled)
+    steps = 0
+
+    def settle():
+        nonlocal inflight
+        if inflight is not None:
+            _, slots, sampled = inflight
+            inflight = None
+            sched.resolve(slots, sampled)
+
+    while sched.has_work() or inflight is not None:
+        plan = sched.plan()
+        if not plan.entries:
+            settle()
+            plan = sched.plan()
+            if not plan.entries:
+                continue
+        pure = all(e.count == 1 and e.samples for e in plan.entries)
+        ids = [e.req.id for e in plan.entries]
+        ahead = pure and inflight is not None and inflight[0] == ids
+        if inflight is not None and not ahead:
+            settle()
+            plan.entries = [e for e in plan.entries if not e.req.finished]
+            if not plan.entries:
+                continue
+        sampled = []
+        for e in plan.entries:
+            r = e.req
+            cache.grow(r.id, e.start + e.count)
+            cache.advance(r.id, e.count)
+            if not ahead:  # the host feeds these tokens: none of them may be a placeholder
+                fed = r.tokens[e.start:e.start + e.count]
+                assert Scheduler.PENDING not in fed
+                truth[r.id] = r.tokens[:e.start + e.count]
+            if e.samples:
+                tok = next_token(truth[r.id])
+                truth[r.id] = truth[r.id] + [tok]
+                sampled.append(tok)
+        if pure:
+            slots = sched.advance(plan)
+            if ahead:
+                settle()
+            inflight = ([e.req.id for e in plan.entries], slots, sampled)
+        else:
+            sched.complete(plan, sampled)
+        cache.check()
+        steps += 1
+        assert steps < max_steps
+    return steps
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_one_step_ahead_gives_the_same_outputs(seed):
+    """Stop tokens seen one step late, requests ending by length, preemption and admission while
+    a step is in flight: outputs equal the step-by-step ones, nothing stays held."""
+    rng = random.Random(100 + seed)
+    cache, s = make(num_pages=rng.choice([6, 10, 20]), num_slots=3, budget=rng.choice([4, 9, 32]), max_seqs=3)
+    want = {}
+    for i in range(12):
+        p = [rng.randrange(1, 90) for _ in range(rng.choice([1, 2, 5, 11, 17]))]
+        n = rng.choice([1, 3, 8, 14])
+        free_run = expected(p, n)
+        eos = rng.choice([-1, -1, free_run[len(free_run) // 2], free_run[-1]])  # in the middle, at the end, never
+        s.add(i, p, SamplingParams(max_new_tokens=n, eos_id=eos))
+        want[i] = expected(p, n, eos)
+    run_one_step_ahead(s, cache)
+    for i, r in s.requests.items():
+        assert Scheduler.PENDING not in r.output
+        if r.status == "done":
+            assert r.output == want[i], (i, r.output, want[i])
+        else:
+            assert r.status in ("oom", "cache_full") and r.output == want[i][:len(r.output)]
+    assert cache.free_slots == 3 and cache.min_free_pages() == cache.groups[(2, 4, 0)].num_pages
+    assert not s.running and not s.waiting

@@ -1,20 +1,23 @@
 // Weights of the next layer pulled into L2 while the current layer runs.
 //
 // A decode step of few tokens reads every weight once; each kernel alone moves a few megabytes
-// and is over before DRAM reaches its steady rate.  One small launch per layer, beside the
-// layer's own kernels, asks the memory system for the next layer's weights with
-// cp.async.bulk.prefetch.L2 (a hint: nothing waits for it and nothing depends on it), so that
-// the kernels of that layer find them in the 126 MB L2.  The requests pass through each SM's
-// copy engine, whose rate is limited: one warp on every SM, never many warps on a few
-// (two blocks took 35 us a layer).  The first third of the blocks issues all requests: measured,
-// a request stream that is spread over every SM pulls faster and slows the layer's own first
-// kernel by more than the next layer gains (1.29 against 1.23 ms a step).
+// and is over before DRAM reaches its steady rate.  One small launch per layer asks the memory
+// system for the next layer's weights with cp.async.bulk.prefetch.L2 (a hint: nothing waits for
+// it and nothing depends on it), so that the kernels of that layer find them in the 126 MB L2.
+// It is issued beside the products that follow the mixers (latency-bound, memory idle), not
+// beside the mixers (which read caches and states at the memory's full rate: there it cost more
+// than it gained).  The requests pass through each SM's copy engine, whose rate is limited: a
+// warp on each of some tens of SMs (two blocks took 35 us a layer; a request stream spread over
+// all 148 SMs with scattered chunks per SM slowed the products beside it).  Also measured: asking
+// for the next layer's cache pages and states in the same way makes the step slower (1.43 against
+// 1.19 ms): 48 MB a layer no longer fit beside the current layer's own traffic.
 #include "common.cuh"
 
 namespace pmm {
 
 constexpr int kPrefetchRanges = 8;
 constexpr unsigned kPrefetchChunk = 16 * 1024;  // bytes per request
+constexpr int kPrefetchBlocks = 50;              // one warp each; 24 to 100 measured alike
 
 struct PrefetchArgs {
   const char* ptr[kPrefetchRanges];
@@ -48,6 +51,6 @@ PMM_EXPORT int pmm_l2_prefetch(const void* const* ptrs, const long long* bytes, 
     a.ptr[i] = static_cast<const char*>(ptrs[i]);
     a.bytes[i] = static_cast<unsigned long long>(bytes[i]) / 16 * 16;
   }
-  pmm::l2_prefetch_kernel<<<148, 32, 0, stream>>>(a);
+  pmm::l2_prefetch_kernel<<<pmm::kPrefetchBlocks, 32, 0, stream>>>(a);
   return pmm::launch_status();
 }

@@ -159,10 +159,8 @@ class ParallelPreNormBlock(Part):
         side = self._side_stream(h.device) if len(self.mixers) > 1 else None
         main = torch.cuda.current_stream(h.device)
         ahead = getattr(ctx, "fetch_ahead", None)  # the next layer's weights, set by the model
-        if ahead:
-            # beside this layer's first kernel: on the side stream when there is one
-            with torch.cuda.stream(side if side is not None else main):
-                K.l2_prefetch(ahead)
+        if ahead and side is None:
+            K.l2_prefetch(ahead)
         proj = ws.alloc((T, self._fused_in.shape[0]), ctx.dtype)
         K.skinny_linear_norm(h, self.mixer_norm.weight, self.mixer_norm.eps, self._fused_in, proj)
         # The mixers only share their input: the first runs on a side stream beside the others
@@ -178,6 +176,13 @@ class ParallelPreNormBlock(Part):
                 products[i] = (m.pre_output(proj[:, c0:c1], ctx, cache), m.output_weight(), m.out_scale)
         if side is not None:
             main.wait_stream(side)
+            if ahead:
+                # The mixers' phase reads the caches and states at the memory's full rate; the products
+                # that follow are latency-bound and leave it idle: the next layer's weights are
+                # requested beside them (the side branch joins again at the next layer's mixers).
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    K.l2_prefetch(ahead)
         # h = (h + s0 * y0 W0^T) + s1 * y1 W1^T in one launch, then the feed-forward
         act = ws.alloc((T, self.ffn.intermediate_size), ctx.dtype) if self.ffn is not None else None
         if _CHAINED:

@@ -160,7 +160,7 @@ def main() -> int:
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "the reference is a CMake C++ project without setup.py/pyproject.toml: pip install "
-                          "--no-index of /root/reference fails ('not installable'), and its CMake build fetches "
+                          "--no-index of its source tree fails ('not installable'), and its CMake build fetches "
                           "Eigen, nlohmann_json, safetensors-cpp and tokenizers-cpp from the network"}))
         return 0
     if args.gpus != 1:

@@ -25,7 +25,9 @@ using bf16 = __nv_bfloat16;
 
 constexpr int kSgRows = 32;     // weight rows per block
 constexpr int kSgChunk = 256;   // columns per pipeline stage
-constexpr int kSgStages = 5;    // K = 1024 is four chunks: all of a block's weights are requested at once
+// Pipeline stages: five for up to 32 tokens (K = 1024 is four chunks: all of a block's weights are
+// requested at once); three for 33..64 tokens, whose activations take most of the shared memory.
+__host__ __device__ constexpr int sg_stages(int mt) { return mt > 4 ? 3 : 5; }
 constexpr int kSgWStride = kSgChunk + 8;
 constexpr int kSgThreads = 256;
 constexpr int kSgPieces = kSgRows * (kSgChunk / 8) / kSgThreads;  // 16-byte pieces per thread and chunk
@@ -78,6 +80,7 @@ __device__ __forceinline__ void sg_mma(float* d, const unsigned* a, unsigned b0,
 template <int MT, int MODE>
 struct SkinnyBlock {
   static constexpr int MP = MT * 8;  // padded tokens
+  static constexpr int kSgStages = sg_stages(MT);
   const SkinnyArgs& args;
   const SkinnyProblem& pr;
   int K, k0, k1, kx, xs, n0, n_chunks;
@@ -428,7 +431,7 @@ __global__ void __launch_bounds__(kSgThreads) skinny_chain_kernel(const SkinnyCh
 }
 
 inline size_t skinny_smem(int MP, int kx) {
-  return static_cast<size_t>(kSgStages) * kSgRows * kSgWStride * sizeof(bf16) +
+  return static_cast<size_t>(sg_stages(MP / 8)) * kSgRows * kSgWStride * sizeof(bf16) +
          static_cast<size_t>(MP) * (kx + 8) * sizeof(bf16) + 3 * 32 * MP * sizeof(float) +
          static_cast<size_t>(kx) * sizeof(float);
 }

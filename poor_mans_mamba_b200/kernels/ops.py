@@ -9,6 +9,7 @@ reduced-precision matrix mode is switched off for the call.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -635,7 +636,8 @@ def flash_decode_attention(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], 
           int(n_splits), pool.shape[2], n_seq, n_q_heads, n_kv_heads, head_dim, counter, _stream())
 
 
-SKINNY_MAX_TOKENS = 16  # beyond this the activations no longer fit beside a deep weight pipeline
+SKINNY_MAX_TOKENS = 64  # the weight-streaming products take up to 64 tokens (where their shared memory fits)
+SKINNY_NORM_MAX_TOKENS = 16  # every block redoes the norm of all rows: beyond this a norm launch of its own is cheaper
 
 
 def _skinny_check(M: int, w: Tensor, K: int, what: str) -> None:
@@ -649,7 +651,8 @@ def skinny_fits(M: int, K: int) -> bool:
     (the products that cannot split K keep the whole row block resident)."""
     mp = 16 if M <= 16 else 32 if M <= 32 else 64
     kx = (K + 255) // 256 * 256
-    return M <= 64 and 5 * 32 * 264 * 2 + mp * (kx + 8) * 2 + 3 * 32 * mp * 4 + kx * 4 <= 220 * 1024
+    stages = 3 if mp > 32 else 5
+    return M <= 64 and stages * 32 * 264 * 2 + mp * (kx + 8) * 2 + 3 * 32 * mp * 4 + kx * 4 <= 220 * 1024
 
 
 def skinny_linear_norm(h: Tensor, norm_weight: Tensor, eps: float, weight: Tensor, out: Tensor) -> None:
@@ -664,6 +667,38 @@ def skinny_linear_norm(h: Tensor, norm_weight: Tensor, eps: float, weight: Tenso
     _need(out.dtype == torch.bfloat16 and out.shape == (M, N) and out.stride(1) == 1, "skinny_linear_norm: out [M, N] bfloat16")
     _call("pmm_skinny_gemm", 0, M, N, None, 0, h.data_ptr(), norm_weight.data_ptr(), float(eps), weight.data_ptr(), K,
           1.0, None, 0, None, 0, 0.0, out.data_ptr(), out.stride(0), None, 1, _stream())
+
+
+def _skinny_x(x: Tensor, M: int, K: int, what: str) -> None:
+    _need(x.dtype == torch.bfloat16 and x.shape == (M, K) and x.stride(1) == 1 and x.stride(0) % 8 == 0
+          and x.data_ptr() % 16 == 0, f"{what}: x must be bfloat16 [M, K] with 16-byte aligned rows")
+
+
+def skinny_linear(x: Tensor, weight: Tensor, out: Tensor) -> None:
+    """out[M, N] = x @ weight^T for M <= 64 rows of bfloat16 activations (weights streamed once)."""
+    _cuda(x, weight, out)
+    M, K = x.shape
+    _skinny_check(M, weight, K, "skinny_linear")
+    _skinny_x(x, M, K, "skinny_linear")
+    _need(skinny_fits(M, K), f"skinny_linear: {M} tokens x {K} columns do not fit in shared memory")
+    N = weight.shape[0]
+    _need(out.dtype == torch.bfloat16 and out.shape == (M, N) and out.stride(1) == 1, "skinny_linear: out [M, N] bfloat16")
+    _call("pmm_skinny_gemm", 0, M, N, x.data_ptr(), x.stride(0), None, None, 0.0, weight.data_ptr(), K,
+          1.0, None, 0, None, 0, 0.0, out.data_ptr(), out.stride(0), None, 1, _stream())
+
+
+def skinny_swiglu(x: Tensor, gate_up: Tensor, gate_mult: float, out: Tensor) -> None:
+    """out[M, F] = silu(gate * gate_mult) * up with [gate | up] = x @ gate_up^T, x bfloat16."""
+    _cuda(x, gate_up, out)
+    M, K = x.shape
+    _skinny_check(M, gate_up, K, "skinny_swiglu")
+    _skinny_x(x, M, K, "skinny_swiglu")
+    _need(skinny_fits(M, K), f"skinny_swiglu: {M} tokens x {K} columns do not fit in shared memory")
+    F = gate_up.shape[0] // 2
+    _need(gate_up.shape[0] == 2 * F and out.dtype == torch.bfloat16 and out.shape == (M, F) and out.is_contiguous(),
+          "skinny_swiglu: out [M, F] bfloat16 for gate_up [2F, K]")
+    _call("pmm_skinny_gemm", 1, M, F, x.data_ptr(), x.stride(0), None, None, 0.0, gate_up.data_ptr(), K,
+          float(gate_mult), None, 0, None, 0, 0.0, out.data_ptr(), out.stride(0), None, 1, _stream())
 
 
 def skinny_swiglu_norm(h: Tensor, norm_weight: Tensor, eps: float, gate_up: Tensor, gate_mult: float,

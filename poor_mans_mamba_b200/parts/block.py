@@ -162,7 +162,13 @@ class ParallelPreNormBlock(Part):
         if ahead and side is None:
             K.l2_prefetch(ahead)
         proj = ws.alloc((T, self._fused_in.shape[0]), ctx.dtype)
-        K.skinny_linear_norm(h, self.mixer_norm.weight, self.mixer_norm.eps, self._fused_in, proj)
+        fused_norm = T <= K.SKINNY_NORM_MAX_TOKENS
+        if fused_norm:
+            K.skinny_linear_norm(h, self.mixer_norm.weight, self.mixer_norm.eps, self._fused_in, proj)
+        else:
+            x = ws.alloc((T, self.hidden_size), ctx.dtype)
+            K.add_rmsnorm(h, [], self.mixer_norm.weight, self.mixer_norm.eps, x)
+            K.skinny_linear(x, self._fused_in, proj)
         # The mixers only share their input: the first runs on a side stream beside the others
         # (in a captured step the two become parallel branches of the graph).
         products = [None] * len(self.mixers)
@@ -195,8 +201,12 @@ class ParallelPreNormBlock(Part):
         else:
             K.skinny_residual(h, products)
             if self.ffn is not None:
-                K.skinny_swiglu_norm(h, self.ffn_norm.weight, self.ffn_norm.eps, self.ffn.gate_up,
-                                     self.ffn.gate_multiplier, act)
+                if fused_norm:
+                    K.skinny_swiglu_norm(h, self.ffn_norm.weight, self.ffn_norm.eps, self.ffn.gate_up,
+                                         self.ffn.gate_multiplier, act)
+                else:
+                    K.add_rmsnorm(h, [], self.ffn_norm.weight, self.ffn_norm.eps, x)
+                    K.skinny_swiglu(x, self.ffn.gate_up, self.ffn.gate_multiplier, act)
                 K.skinny_residual(h, [(act, self.ffn.down, self.ffn.out_scale)])
         ws.release(mark)
 

@@ -23,8 +23,7 @@
 // No cluster multicast is used anywhere.
 // (reference: gate and up are two cublasSgemm calls followed by scale, silu and mul launches,
 // src/ops/cuda_backend.cu:311-338.)
-#include "common.cuh"
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 namespace pmm {
 
@@ -37,86 +36,14 @@ constexpr int kTcK = 64;         // K per stage: one 128-byte swizzle row of bfl
 constexpr int kTcStages = 3;
 constexpr int kTcThreads = 320;
 constexpr int kTcTmemCols = 512; // both accumulators: all of an SM's tensor memory (one block per SM, by shared memory)
-constexpr unsigned kSpinLimit = 1u << 22;
 constexpr int kTcABytes = kTcM * kTcK * 2;  // 32 KB
 constexpr int kTcBBytes = kTcN * kTcK * 2;  // 32 KB
 constexpr size_t kTcSmem = static_cast<size_t>(kTcStages) * (kTcABytes + kTcBBytes) + 1024 /*alignment*/;
 
 enum { kTcPlain = 0, kTcSwiglu = 1 };
 
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
-  unsigned ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false when it gave up or when another role has raised the abort flag.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* abort_flag) {
-  for (unsigned i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63) == 63 && *abort_flag) return false;
-  }
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, unsigned long long* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-      :
-      : "r"(smem_u32(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-      : "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
-// 8-row groups 1024 bytes apart (stride byte offset), leading byte offset unused (1), version 1.
-__device__ __forceinline__ unsigned long long umma_desc(const void* tile) {
-  const unsigned addr = smem_u32(tile);
-  const unsigned lo = ((addr & 0x3FFFFu) >> 4) | (1u << 16);
-  const unsigned hi = (1024u >> 4) | (1u << 14) | (2u << 29);
-  return (static_cast<unsigned long long>(hi) << 32) | lo;
-}
-
 // kind::f16 instruction descriptor: float accumulate, bfloat16 A and B, both K-major, N, M.
 constexpr unsigned kTcIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kTcN >> 3) << 17) | ((kTcMH >> 4) << 24);
-
-__device__ __forceinline__ void umma_f16(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc,
-                                         unsigned idesc, unsigned accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-      :
-      : "r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
 
 template <int MODE>
 __global__ void __launch_bounds__(kTcThreads)
@@ -282,22 +209,6 @@ __global__ void __launch_bounds__(kTcThreads)
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTcTmemCols) : "memory");
   }
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-inline EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
 }
 
 // bfloat16 matrix [rows, cols] with row stride ld (elements); box = 64 columns x box_rows rows.

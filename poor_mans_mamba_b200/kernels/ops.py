@@ -61,6 +61,10 @@ _SIGNATURES = {
                                   c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
                                   c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "pmm_l2_prefetch": [c_void_p, c_void_p, c_int, c_void_p],
+    "pmm_attention_tc_supported": [c_int, c_int, c_int, c_int],
+    "pmm_attention_tc": [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                         c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                         c_void_p, c_void_p],
     "pmm_skinny_chain": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "pmm_flash_decode_attention": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_float,
                                    c_float, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -875,6 +879,53 @@ def tc_gemm(x: Tensor, weight: Tensor, out: Tensor) -> None:
     _need(tc_gemm_supported(x, weight, N, False), "tc_gemm: sizes or alignment outside what the kernel takes")
     _call("pmm_tc_gemm", 0, x.data_ptr(), x.stride(0), weight.data_ptr(), out.data_ptr(), out.stride(0), T, K, N,
           1.0, _tc_status(x.device).data_ptr(), _stream())
+
+
+def attention_tc_supported(n_q_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    """Whether the tcgen05 attention for prompt portions takes this shape (bfloat16, head size 64,
+    a group size that divides 128, pages of a multiple of 64 tokens)."""
+    return bool(_fn("pmm_attention_tc_supported")(n_q_heads, n_kv_heads, head_dim, page_size))
+
+
+def attention_tc(q: Tensor, pool: Tensor, block_table: Tensor, positions: Tensor, cu_seqlens: Tensor,
+                 new_lens: Sequence[int], out: Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int,
+                 softmax_scale: float, window: int = 0, n_splits: int = 1, split_len: int = 0,
+                 scratch: Optional[Tensor] = None, split_counter: Optional[Tensor] = None) -> None:
+    """Causal attention of prompt portions over the paged cache on the fifth-generation tensor cores
+    (TMA tiles straight from the pages, scores and P V in tensor memory, one thread per query row
+    for the softmax).  Same contract as paged_attention with rotated queries and a cache that holds
+    the step's keys already; 128 rows of (token, query head of a group) per block."""
+    _cuda(q, pool, block_table, positions, cu_seqlens, out, scratch, split_counter)
+    T = q.shape[0]
+    _need(q.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+          and q.is_contiguous() and out.is_contiguous() and q.shape == (T, n_q_heads * head_dim) and out.shape == q.shape,
+          "attention_tc: q and out must be contiguous bfloat16 [T, Hq*Dh]")
+    _need(pool.dim() == 4 and pool.shape[1] == 2 and pool.shape[3] == n_kv_heads * head_dim and pool.is_contiguous(),
+          "attention_tc: pool must be contiguous [pages, 2, page_size, Hkv*Dh]")
+    _need(attention_tc_supported(n_q_heads, n_kv_heads, head_dim, pool.shape[2]),
+          "attention_tc: head size 64, a group size that divides 128 and pages of a multiple of 64 tokens")
+    _i32(block_table, "attention_tc: block_table")
+    _i32(positions, "attention_tc: positions")
+    _i32(cu_seqlens, "attention_tc: cu_seqlens")
+    per_tile = 128 // (n_q_heads // n_kv_heads)
+    n_tiles = sum((n + per_tile - 1) // per_tile for n in new_lens)
+    part_o = part_ml = counter = None
+    if n_splits > 1:
+        need = attention_scratch_floats(T, n_q_heads, head_dim, n_splits)
+        _need(scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous()
+              and scratch.numel() >= need and scratch.data_ptr() % 16 == 0,
+              f"attention_tc: split keys need {need} floats of scratch")
+        _need(split_len > 0 and split_len % 64 == 0 and n_splits <= 64, "attention_tc: split_len must be a multiple of 64")
+        _need(split_counter is not None and split_counter.numel() >= n_tiles * n_kv_heads,
+              "attention_tc: split keys need a counter per (row tile, key/value head)")
+        _i32(split_counter, "attention_tc: split_counter")
+        part_o = scratch.data_ptr()
+        part_ml = part_o + 4 * T * n_q_heads * n_splits * head_dim
+        counter = split_counter.data_ptr()
+    _call("pmm_attention_tc", q.data_ptr(), pool.data_ptr(), pool.shape[0], block_table.data_ptr(), block_table.shape[1],
+          positions.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(), part_o, part_ml, float(softmax_scale), int(window),
+          int(split_len), int(n_splits), pool.shape[2], len(new_lens), n_tiles, n_q_heads, n_kv_heads, head_dim, counter,
+          _tc_status(q.device).data_ptr(), _stream())
 
 
 def silu_mul(gate_up: Tensor, gate_mult: float, out: Tensor) -> None:

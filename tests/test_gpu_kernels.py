@@ -228,11 +228,11 @@ def test_gated_norm(dtype, mode):
 
 
 def _attention_case(dtype, Hq, Hkv, Dh, page_size, lens_steps, window=0, planted=True, n_splits=1, theta=1e4, seed=0,
-                    tensor_cores=True, fused_merge=False, fused_decode=False):
+                    tensor_cores=True, fused_merge=False, fused_decode=False, tc=False):
     """Runs qkv_rope_store + paged_attention over a script of portions with scattered pages and
     compares with the plain rope + causal attention on the whole sequences.  ``fused_decode``:
     steps in which every sequence brings one token go through flash_decode_attention instead
-    (rotation, page write and attention in one launch)."""
+    (rotation, page write and attention in one launch).  ``tc``: the tcgen05 kernel for every step."""
     g = torch.Generator().manual_seed(seed)
     ops = K()
     lens = [sum(p) for p in lens_steps]
@@ -326,6 +326,18 @@ def _attention_case(dtype, Hq, Hkv, Dh, page_size, lens_steps, window=0, planted
         cu = [0]
         for _, _, n in seqs:
             cu.append(cu[-1] + n)
+        if tc:
+            if ns > 1:
+                split_len = (split_len + 63) // 64 * 64
+                ns = (max(pos) + 1 + split_len - 1) // split_len
+            ops.attention_tc(q_rot, pool, bt.to(DEV), i32(pos), i32(cu), [n for _, _, n in seqs], out, Hq, Hkv, Dh,
+                             1.0 / math.sqrt(Dh), window=window, n_splits=ns, split_len=split_len if ns > 1 else 0,
+                             scratch=scratch, split_counter=counter)
+            t0 = 0
+            for i, a, n in seqs:
+                got[i][a:a + n] = out[t0:t0 + n].cpu()
+                t0 += n
+            continue
         ops.paged_attention(q_rot, pool, bt.to(DEV), i32(pos), i32(seq_of), out, Hq, Hkv, Dh, 1.0 / math.sqrt(Dh),
                             window=window, n_splits=ns, split_len=split_len, scratch=scratch, cu_seqlens=i32(cu),
                             new_lens=[n for _, _, n in seqs], use_tensor_cores=tensor_cores,
@@ -372,6 +384,22 @@ def test_flash_decode_attention_from_projections(Hq, Hkv, Dh, page):
     _attention_case(torch.bfloat16, Hq, Hkv, Dh, page, steps, seed=Hq + 1, n_splits=3, fused_decode=True)
     _attention_case(torch.bfloat16, Hq, Hkv, Dh, page, steps, seed=Hq + 2, window=40, n_splits=2, fused_decode=True)
     _attention_case(torch.bfloat16, Hq, Hkv, Dh, page, steps, seed=Hq + 3, window=70, fused_decode=True)
+
+
+@pytest.mark.parametrize("Hq,Hkv,page", [(8, 2, 64), (4, 4, 128), (16, 1, 64), (16, 2, 64)])
+def test_tcgen05_attention_over_the_paged_cache(Hq, Hkv, page):
+    """The tcgen05 / TMA / tensor-memory attention for prompt portions: portions that start and end
+    off the 128-key tiles and the 64-key boxes, portions over a long cached prefix, single tokens,
+    several sequences in a step, key splits merged by the last block, and a window."""
+    bf = torch.bfloat16
+    steps = [[page + 1, 1, 200, page - 2, 1], [3, 2 * page, 1, 130], [1, 1, 1, 1], [70, 1, 333]]
+    _attention_case(bf, Hq, Hkv, 64, page, steps, seed=Hq, tc=True)
+    _attention_case(bf, Hq, Hkv, 64, page, steps, seed=Hq + 1, n_splits=3, tc=True)
+    _attention_case(bf, Hq, Hkv, 64, page, steps, seed=Hq + 2, window=100, tc=True)
+    _attention_case(bf, Hq, Hkv, 64, page, steps, seed=Hq + 3, window=150, n_splits=2, tc=True)
+    assert K().tc_gemm_status(DEV) == 0
+    assert not K().attention_tc_supported(Hq, Hkv, 128, page) and not K().attention_tc_supported(6, 2, 64, page)
+    assert not K().attention_tc_supported(Hq, Hkv, 64, 16)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -11,15 +11,18 @@
 //   P  = softmax   four warps, ONE THREAD PER ROW: tcgen05.ld of the row (twice: maximum, then
 //                  exponentials), no shuffles; P goes to shared memory as bfloat16, swizzled as an
 //                  mma operand, and is handed over with fence.proxy.async + mbarrier;
-//   PV = P V       tcgen05.mma with the V tile as an MN-major operand (rows = keys, as the cache
-//                  stores them) into a second tensor-memory range that is NOT accumulated: each
-//                  thread reads its row of P V and folds it into the row's running output in
-//                  registers (o = o * alpha + pv), so that the rescaling of online softmax costs
-//                  no tensor-memory round trip.
-// Warp roles: 0 = TMA producer (K and V have one shared-memory stage each; a tile's copy is
-// requested the moment the product that read its predecessor has finished), 1 = tensor-memory
-// owner and MMA issuer, 2..5 = softmax and output.  80 KB of shared memory and 256 columns of
-// tensor memory a block: two blocks per SM overlap each other's softmax and products.
+//   O += P V       tcgen05.mma with the V tile as an MN-major operand (rows = keys, as the cache
+//                  stores them), accumulated in a second tensor-memory range over all tiles.  The
+//                  running maximum that the exponentials are taken against is only raised when a
+//                  row's true maximum exceeds it by more than 8 (a factor 256, harmless in
+//                  bfloat16 and float); only then the accumulated O and sum are rescaled (a
+//                  tensor-memory load, multiply and store by the row's thread).  The result is
+//                  exact: P, the sum and O always refer to the same maximum.
+// Warp roles: 0 = TMA producer (two stages for K, one for V; a tile's copy is requested the moment
+// the product that read the stage before has finished), 1 = tensor-memory owner and MMA issuer
+// (S of the next tile is issued as soon as the softmax threads have taken the current S into
+// registers, so the tensor core works while they compute), 2..5 = softmax and output.  96 KB of
+// shared memory and 256 columns of tensor memory a block: two blocks per SM.
 // With several key splits the block writes (max, sum, unnormalised output) and the last block of
 // a row tile merges them, as in the mma.sync kernel.  Every mbarrier wait is bounded (status
 // codes 11..15 in *status, the block then leaves its loops, waits for its copies in flight and
@@ -38,12 +41,13 @@ constexpr int kAtKeys = 128;    // keys per tile
 constexpr int kAtBox = 64;      // keys per TMA box (inside one page)
 constexpr int kAtDh = 64;       // head size
 constexpr int kAtThreads = 192;
-constexpr int kAtTmemCols = 256;  // S: columns 0..127, P V: columns 128..191
+constexpr int kAtTmemCols = 256;  // S: columns 0..127, O: columns 128..191
+constexpr float kAtLazy = 8.f;    // how far (log2) a row's maximum may run ahead of the one in use
 constexpr int kAtBtCap = 512;
 constexpr int kAtQBytes = kAtM * kAtDh * 2;         // 16 KB
 constexpr int kAtKBytes = kAtKeys * kAtDh * 2;      // 16 KB
 constexpr int kAtPBytes = kAtM * kAtKeys * 2;       // 32 KB: two sub-tiles of 64 keys
-constexpr size_t kAtSmem = kAtQBytes + 2 * kAtKBytes + kAtPBytes + 1024 /*alignment*/;
+constexpr size_t kAtSmem = kAtQBytes + 3 * kAtKBytes + kAtPBytes + 1024 /*alignment*/;  // Q, K x 2, V, P
 
 // kind::f16 instruction descriptors: float accumulate, bfloat16 operands, A K-major.
 constexpr unsigned kAtIdescS = (1u << 4) | (1u << 7) | (1u << 10) | ((kAtKeys >> 3) << 17) | ((kAtM >> 4) << 24);               // B = K tile, K-major
@@ -73,7 +77,7 @@ __global__ void __launch_bounds__(kAtThreads, 2)
                         int* __restrict__ status) {
   constexpr int DH = kAtDh;
   extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long bar_q, bar_kfull, bar_vfull, bar_s, bar_p, bar_pv;
+  __shared__ __align__(8) unsigned long long bar_q, bar_kfull[2], bar_vfull, bar_s, bar_sfree, bar_p, bar_pv;
   __shared__ unsigned s_tmem_base;
   __shared__ int s_abort, s_last;
   __shared__ int s_bt[kAtBtCap];
@@ -81,7 +85,7 @@ __global__ void __launch_bounds__(kAtThreads, 2)
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sQ = tiles;
   unsigned char* sK = sQ + kAtQBytes;
-  unsigned char* sV = sK + kAtKBytes;
+  unsigned char* sV = sK + 2 * kAtKBytes;
   unsigned char* sP = sV + kAtKBytes;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -115,9 +119,11 @@ __global__ void __launch_bounds__(kAtThreads, 2)
 
   if (tid == 0) {
     mbar_init(&bar_q, 128);
-    mbar_init(&bar_kfull, 1);
+    mbar_init(&bar_kfull[0], 1);
+    mbar_init(&bar_kfull[1], 1);
     mbar_init(&bar_vfull, 1);
     mbar_init(&bar_s, 1);
+    mbar_init(&bar_sfree, 128);
     mbar_init(&bar_p, 128);
     mbar_init(&bar_pv, 1);
     s_abort = 0;
@@ -140,12 +146,7 @@ __global__ void __launch_bounds__(kAtThreads, 2)
     s_abort = 1;
   };
 
-  // softmax-role state (declared here so that the epilogue below can use it)
   const int row = ((warp & 3) << 5) + lane;  // the tensor-memory lane a thread of warps 2..5 may read = its row
-  float m_run = -CUDART_INF_F, l_run = 0.f;
-  float o[DH];
-#pragma unroll
-  for (int i = 0; i < DH; ++i) o[i] = 0.f;
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -158,13 +159,13 @@ __global__ void __launch_bounds__(kAtThreads, 2)
         const int b0 = base, b1 = (base + kAtBox < k_end) ? base + kAtBox : base;
         const int r0 = page_of(b0 / page_size) * 2 * page_size + b0 % page_size;
         const int r1 = page_of(b1 / page_size) * 2 * page_size + b1 % page_size;
-        if (j > 0 && !mbar_wait(&bar_s, (j - 1) & 1, abort_flag)) {  // S_{j-1} done: the K stage is free
-          give_up(11);
-          break;
-        }
-        mbar_expect_tx(&bar_kfull, kAtKBytes);
-        tma_load_2d(sK, &map_kv, hk * DH, r0, &bar_kfull);
-        tma_load_2d(sK + kAtKBytes / 2, &map_kv, hk * DH, r1, &bar_kfull);
+        // The K stage of tile j was read by S_{j-2}.  The tensor core works in issue order (S_{j-2},
+        // S_{j-1}, P V_{j-2}, ...), so P V_{j-2}, which the previous round of this loop waited for
+        // before it requested V_{j-1}, finished after S_{j-2}: the stage is free.
+        unsigned char* kd = sK + (j & 1) * kAtKBytes;
+        mbar_expect_tx(&bar_kfull[j & 1], kAtKBytes);
+        tma_load_2d(kd, &map_kv, hk * DH, r0, &bar_kfull[j & 1]);
+        tma_load_2d(kd + kAtKBytes / 2, &map_kv, hk * DH, r1, &bar_kfull[j & 1]);
         k_issued = j + 1;
         if (j > 0 && !mbar_wait(&bar_pv, (j - 1) & 1, abort_flag)) {  // P V_{j-1} done: the V stage is free
           give_up(12);
@@ -177,8 +178,8 @@ __global__ void __launch_bounds__(kAtThreads, 2)
       }
       if (s_abort) {
         // copies already requested still write into this block's shared memory: wait for them
-        if (k_issued > 0)
-          for (unsigned i = 0; i < kSpinLimit && !mbar_try_wait(&bar_kfull, (k_issued - 1) & 1); ++i) {
+        for (int j = max(0, k_issued - 2); j < k_issued; ++j)
+          for (unsigned i = 0; i < kSpinLimit && !mbar_try_wait(&bar_kfull[j & 1], (j >> 1) & 1); ++i) {
           }
         if (v_issued > 0)
           for (unsigned i = 0; i < kSpinLimit && !mbar_try_wait(&bar_vfull, (v_issued - 1) & 1); ++i) {
@@ -188,32 +189,43 @@ __global__ void __launch_bounds__(kAtThreads, 2)
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0 && n_tiles > 0) {
-      bool ok = mbar_wait(&bar_q, 0, abort_flag);
-      if (!ok) give_up(13);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        if (!mbar_wait(&bar_kfull, j & 1, abort_flag)) {
-          give_up(13);
-          break;
-        }
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        {  // S_j = Q K_j^T: the previous S has been read (its threads arrived at bar_p before this point)
-          const unsigned long long a_desc = umma_desc(sQ), b_desc = umma_desc(sK);
+      const unsigned long long q_desc = umma_desc(sQ);
+      auto issue_s = [&](int j) {  // S_j = Q K_j^T
+        const unsigned long long b_desc = umma_desc(sK + (j & 1) * kAtKBytes);
 #pragma unroll
-          for (int k = 0; k < DH / 16; ++k) umma_f16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, kAtIdescS, k > 0 ? 1u : 0u);
-          umma_commit(&bar_s);
+        for (int k = 0; k < DH / 16; ++k) umma_f16(tmem_base, q_desc + 2 * k, b_desc + 2 * k, kAtIdescS, k > 0 ? 1u : 0u);
+        umma_commit(&bar_s);
+      };
+      bool ok = mbar_wait(&bar_q, 0, abort_flag) && mbar_wait(&bar_kfull[0], 0, abort_flag);
+      if (!ok) give_up(13);
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        issue_s(0);
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) {
+          // the softmax threads hold S_j in registers: the next S may overwrite it, and the
+          // tensor core works on it while they compute
+          if (!mbar_wait(&bar_sfree, j & 1, abort_flag) ||
+              !mbar_wait(&bar_kfull[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) {
+            give_up(13);
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          issue_s(j + 1);
         }
         if (!mbar_wait(&bar_p, j & 1, abort_flag) || !mbar_wait(&bar_vfull, j & 1, abort_flag)) {
           give_up(14);
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        {  // P V_j: A = P (two sub-tiles of 64 keys), B = V rows as they lie in the cache (MN-major):
-           // 16 keys further = 16 rows of 128 bytes
+        {  // O += P V_j: A = P (two sub-tiles of 64 keys), B = V rows as they lie in the cache
+           // (MN-major): 16 keys further = 16 rows of 128 bytes
           const unsigned long long v_desc = umma_desc(sV);
 #pragma unroll
           for (int k = 0; k < kAtKeys / 16; ++k) {
             const unsigned long long a_desc = umma_desc(sP + (k / 4) * (kAtPBytes / 2)) + 2 * (k % 4);
-            umma_f16(tmem_base + kAtKeys, a_desc, v_desc + ((k * 16 * 128) >> 4), kAtIdescO, k > 0 ? 1u : 0u);
+            umma_f16(tmem_base + kAtKeys, a_desc, v_desc + ((k * 16 * 128) >> 4), kAtIdescO, (j > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&bar_pv);
         }
@@ -225,6 +237,8 @@ __global__ void __launch_bounds__(kAtThreads, 2)
     const bool row_ok = row < n_rows;
     const int my_pos = row_ok ? positions[tok0 + row / G] : -1;
     const int my_lo = window > 0 ? max(my_pos - window + 1, k_begin) : k_begin;
+    float m_run = -CUDART_INF_F, l_run = 0.f;  // the maximum in use (exponent's unit) and the sum against it
+    bool alive = true;
     if (n_tiles > 0) {
       // this thread's query row -> shared memory, swizzled (rows beyond the tile are zero)
       const bf16* src = q + (static_cast<size_t>(tok0 + row / G) * Hq + hk * G + row % G) * DH;
@@ -242,92 +256,112 @@ __global__ void __launch_bounds__(kAtThreads, 2)
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         if (lane == 0) give_up(15);
+        alive = false;
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      // the whole row of S into registers, then the tensor memory is free for the next S
+      unsigned v[kAtKeys];
+#pragma unroll
+      for (int c = 0; c < kAtKeys / 32; ++c) tmem_ld32(lane_base + c * 32, v + c * 32);
+      asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      mbar_arrive(&bar_sfree);
       // a tile that every row of the block may read in full needs no mask
       const bool full = base >= k_begin && base + kAtKeys <= k_end && base + kAtKeys - 1 <= pos_min &&
                         (window <= 0 || base >= pos_max - window + 1);
-      // pass 1: the row's maximum (four running maxima: the chain through one would be 128 long)
+      if (!full) {
+#pragma unroll
+        for (int e = 0; e < kAtKeys; ++e) {
+          const int key = base + e;
+          if (!(key <= my_pos && key >= my_lo && key < k_end)) v[e] = __float_as_uint(-CUDART_INF_F);
+        }
+      }
       float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-#pragma unroll 1
-      for (int c = 0; c < kAtKeys / 32; ++c) {
-        unsigned v[32];
-        tmem_ld32(lane_base + c * 32, v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-        if (full) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(v[e]));
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int key = base + c * 32 + e;
-            if (key <= my_pos && key >= my_lo && key < k_end) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(v[e]));
-          }
+      for (int e = 0; e < kAtKeys; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(v[e]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;  // scale > 0
+      // raise the maximum in use only when the row's maximum has run ahead of it by more than kAtLazy
+      float alpha = 1.f;
+      if (mx > m_run + kAtLazy || m_run == -CUDART_INF_F) {
+        if (mx != -CUDART_INF_F) {
+          alpha = at_ex2(m_run - mx);  // 0 for the first visible tile
+          m_run = mx;
         }
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      const float mn = fmaxf(m_run, mx * scale_log2);  // scale > 0; maxima are kept in the exponent's unit
-      const float mu = (mn == -CUDART_INF_F) ? 0.f : mn;
-      const float alpha = at_ex2(m_run - mu);
-      m_run = mn;
-      // pass 2: exponentials -> P (bfloat16, operand layout), their sum
+      const bool rescale = j > 0 && alpha != 1.f;
+      if (j > 0) {
+        // P V_{j-1} must have finished: it read the P tile that is written below, and it wrote O
+        ok = mbar_wait(&bar_pv, (j - 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) give_up(15);
+          alive = false;
+          break;
+        }
+      }
+      if (__any_sync(0xffffffffu, rescale)) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+        for (int c = 0; c < DH / 32; ++c) {
+          unsigned ov[32];
+          tmem_ld32(lane_base + kAtKeys + c * 32, ov);
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+          for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
+          tmem_st32(lane_base + kAtKeys + c * 32, ov);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+      }
+      l_run *= alpha;
+      const float mu = (m_run == -CUDART_INF_F) ? 0.f : m_run;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
-      for (int c = 0; c < kAtKeys / 32; ++c) {
-        unsigned v[32];
-        tmem_ld32(lane_base + c * 32, v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-        float p[32];
-        if (full) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) p[e] = at_ex2(fmaf(__uint_as_float(v[e]), scale_log2, -mu));
-        } else {
+      for (int c8 = 0; c8 < kAtKeys / 8; ++c8) {
+        float p[8];
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int key = base + c * 32 + e;
-            const bool vis = key <= my_pos && key >= my_lo && key < k_end;
-            p[e] = vis ? at_ex2(fmaf(__uint_as_float(v[e]), scale_log2, -mu)) : 0.f;
-          }
+        for (int e = 0; e < 8; ++e) {
+          p[e] = at_ex2(fmaf(__uint_as_float(v[c8 * 8 + e]), scale_log2, -mu));  // masked: ex2(-inf) = 0
+          sum4[e & 3] += p[e];
         }
-        unsigned char* sub = sP + (c >> 1) * (kAtPBytes / 2);
-#pragma unroll
-        for (int g4 = 0; g4 < 4; ++g4) {
-          uint4 pk;
-          pk.x = at_pack(p[g4 * 8 + 0], p[g4 * 8 + 1]);
-          pk.y = at_pack(p[g4 * 8 + 2], p[g4 * 8 + 3]);
-          pk.z = at_pack(p[g4 * 8 + 4], p[g4 * 8 + 5]);
-          pk.w = at_pack(p[g4 * 8 + 6], p[g4 * 8 + 7]);
-          *reinterpret_cast<uint4*>(sub + at_swizzled(row, (c & 1) * 4 + g4)) = pk;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) sum4[e & 3] += p[g4 * 8 + e];
-        }
+        uint4 pk;
+        pk.x = at_pack(p[0], p[1]);
+        pk.y = at_pack(p[2], p[3]);
+        pk.z = at_pack(p[4], p[5]);
+        pk.w = at_pack(p[6], p[7]);
+        *reinterpret_cast<uint4*>(sP + (c8 >> 3) * (kAtPBytes / 2) + at_swizzled(row, c8 & 7)) = pk;
       }
-      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");  // the loads of S are done before S is overwritten
+      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
       fence_proxy_async();
       mbar_arrive(&bar_p);
-      l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-      ok = mbar_wait(&bar_pv, j & 1, abort_flag);
+    }
+
+    // ---- this block's result: O from tensor memory once the last product has finished
+    constexpr float kLn2 = 0.6931471805599453f;
+    float o[DH];
+#pragma unroll
+    for (int i = 0; i < DH; ++i) o[i] = 0.f;
+    if (alive && n_tiles > 0) {
+      bool ok = mbar_wait(&bar_pv, (n_tiles - 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         if (lane == 0) give_up(15);
-        break;
-      }
-      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        alive = false;
+      } else {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll
-      for (int c = 0; c < DH / 32; ++c) {
-        unsigned v[32];
-        tmem_ld32(lane_base + kAtKeys + c * 32, v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+        for (int c = 0; c < DH / 32; ++c) {
+          unsigned ov[32];
+          tmem_ld32(lane_base + kAtKeys + c * 32, ov);
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
-        for (int e = 0; e < 32; ++e) o[c * 32 + e] = o[c * 32 + e] * alpha + __uint_as_float(v[e]);
+          for (int e = 0; e < 32; ++e) o[c * 32 + e] = __uint_as_float(ov[e]);
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
       }
-      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     }
-
-    // ---- this block's result
-    constexpr float kLn2 = 0.6931471805599453f;
-    if (row_ok && !s_abort) {
+    if (row_ok && alive && !s_abort) {
       const int t = tok0 + row / G, hq = hk * G + row % G;
       if (n_splits == 1) {
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;

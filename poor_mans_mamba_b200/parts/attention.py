@@ -10,6 +10,7 @@ every token to the last ``window`` keys (and lets the cache manager give older p
 from __future__ import annotations
 
 import math
+import os
 from typing import Any, Dict, List, Optional
 
 import torch
@@ -21,6 +22,9 @@ Tensor = torch.Tensor
 
 # Key splits are sized so that a step launches about this many attention blocks.
 _TARGET_BLOCKS = 592
+_TC_BLOCKS = 148        # blocks the tcgen05 prompt kernel is planned for (one per SM)
+_TC_FROM_TOKENS = 256   # shorter steps stay on the mma.sync kernel (few 128-row tiles)
+_TC_ATTENTION = os.environ.get("PMM_TCGEN05_ATTENTION", "1") == "1"
 
 
 class PagedAttention(Mixer):
@@ -148,18 +152,47 @@ class PagedAttention(Mixer):
                          k_lin.view(T, self.num_kv_heads, self.head_dim), ctx.positions)
                 K.kv_store(k_lin, v_lin, ctx.positions, ctx.seq_of, kv.block_table, kv.pool)
 
+        attn = ws.alloc((T, self.q_dim), proj.dtype)
+        if (_TC_ATTENTION and proj.dtype == torch.bfloat16 and not ctx.decode_only and counter is not None
+                and sum(ctx.new_lens) >= _TC_FROM_TOKENS
+                and K.attention_tc_supported(self.num_heads, self.num_kv_heads, self.head_dim, kv.pool.shape[2])):
+            # prompt portions: scores and P V on the fifth-generation tensor cores
+            n_splits, split_len = self.plan_splits_tc(ctx.new_lens, ctx.kv_len_bound)
+            per_tile = 128 // (self.num_heads // self.num_kv_heads)
+            tiles = sum((n + per_tile - 1) // per_tile for n in ctx.new_lens)
+            if n_splits <= 64 and counter.numel() >= tiles * self.num_kv_heads:
+                scratch = None
+                if n_splits > 1:
+                    scratch = ws.alloc((K.attention_scratch_floats(T, self.num_heads, self.head_dim, n_splits),),
+                                       torch.float32)
+                K.attention_tc(q_rot, kv.pool, kv.block_table, ctx.positions, ctx.cu_seqlens, ctx.new_lens, attn,
+                               self.num_heads, self.num_kv_heads, self.head_dim, scale, window=self.window,
+                               n_splits=n_splits, split_len=split_len, scratch=scratch, split_counter=counter)
+                return attn
         n_splits, split_len = self.plan_splits(ctx.new_lens, ctx.kv_len_bound, proj.dtype)
         scratch = None
         if n_splits > 1:
             scratch = ws.alloc((K.attention_scratch_floats(T, self.num_heads, self.head_dim, n_splits),),
                                torch.float32)
-        attn = ws.alloc((T, self.q_dim), proj.dtype)
         K.paged_attention(q_rot, kv.pool, kv.block_table, ctx.positions, ctx.seq_of, attn, self.num_heads,
                           self.num_kv_heads, self.head_dim, scale,
                           window=self.window, n_splits=n_splits, split_len=split_len, scratch=scratch,
                           cu_seqlens=ctx.cu_seqlens, new_lens=ctx.new_lens,
                           split_counter=counter)
         return attn
+
+    def plan_splits_tc(self, new_lens, kv_len_bound: int):
+        """Key ranges for the tcgen05 kernel (128 rows a block, two blocks an SM): one range when
+        the row tiles alone give a block per SM, else enough ranges of at least 256 keys to get there."""
+        per_tile = 128 // (self.num_heads // self.num_kv_heads)
+        blocks = sum((n + per_tile - 1) // per_tile for n in new_lens) * self.num_kv_heads
+        reach = min(kv_len_bound, self.window) if self.window > 0 else kv_len_bound
+        want = min(_TC_BLOCKS // max(blocks, 1), (reach + 255) // 256)
+        if want <= 1:
+            return 1, 0
+        split_len = ((kv_len_bound + want - 1) // want + 63) // 64 * 64
+        n_splits = (kv_len_bound + split_len - 1) // split_len
+        return (n_splits, split_len) if n_splits > 1 else (1, 0)
 
     def plan_splits(self, new_lens, kv_len_bound: int, dtype: torch.dtype):
         """How many key ranges every block's keys are cut into: enough blocks to fill the GPU

@@ -78,3 +78,53 @@ def test_decode_graph_at_larger_shapes(shaped):
         top2 = torch.topk(ref[29], 2).values
         if float(top2[0] - top2[1]) > 0.05 * float(ref[29].abs().max()):  # only where bfloat16 cannot flip it
             assert got[0] == int(ref[29].argmax())
+
+
+# ---------------------------------------------------------------------------------------------
+# A small model whose attention takes the tcgen05 kernel (head size 64, pages of 64 tokens, steps
+# of 256 tokens and more).
+H64 = _shape(hidden_size=128, num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=256,
+             vocab_size=301, mamba_d_ssm=128, mamba_n_heads=2, mamba_d_head=64, mamba_d_state=128, mamba_n_groups=1,
+             mamba_d_conv=4, mamba_chunk_size=64, num_hidden_layers=2)
+
+
+@pytest.fixture(scope="module")
+def h64(tmp_path_factory):
+    from model_dirs import make_loud
+    d = str(tmp_path_factory.mktemp("shape_h64"))
+    write_random_model(H64, 13, d)
+    make_loud(d)  # so that a wrong key, page or rotation moves the logits
+    files = ModelFiles(d)
+    weights = {k: files.tensor(k).float() for k in files.keys()}
+    files.close()
+    rng = random.Random(7)
+    seqs = [[rng.randrange(H64["vocab_size"]) for _ in range(n)] for n in (700, 300, 521)]
+    return d, seqs, H.reference_logits(seqs, weights, H64)
+
+
+@pytest.mark.parametrize("cutting", ["whole", "two portions", "three requests in one step", "prefix then long portion"])
+def test_prompt_steps_through_the_tcgen05_attention(h64, cutting, monkeypatch):
+    d, seqs, refs = h64
+    from poor_mans_mamba_b200.kernels import ops as K
+    calls = []
+    original = K.attention_tc
+    monkeypatch.setattr(K, "attention_tc", lambda *a, **k: (calls.append(1), original(*a, **k))[1])
+    runner = H.make_runner(d, "bfloat16", page_size=64, num_pages=40, num_slots=4)
+    if cutting == "whole":
+        script = H.script_whole(seqs)
+    elif cutting == "two portions":
+        script = []
+        for i, s in enumerate(seqs):
+            cut = min(len(s), 290 + 7 * i)
+            script.append(([(i, 0, cut)], [] if cut < len(s) else [i]))
+            if cut < len(s):
+                script.append(([(i, cut, len(s) - cut)], [i]))
+    elif cutting == "three requests in one step":
+        script = [([(0, 0, 260), (1, 0, 300), (2, 0, 270)], [1]), ([(0, 260, 440), (2, 270, 251)], [0, 2])]
+    else:
+        script = [([(0, 0, 70)], []), ([(0, 70, 630)], [0]), ([(1, 0, 3)], []), ([(1, 3, 297)], [1]),
+                  ([(2, 0, 129)], []), ([(2, 129, 392)], [2])]
+    out = H.run_script(runner, seqs, script)
+    for i, ref in enumerate(refs):
+        H.check_rows(out[i], ref, "bfloat16", f"h64 {cutting} seq {i}")
+    assert K.tc_gemm_status("cuda:0") == 0 and len(calls) >= 2 * 2  # two layers, at least two long steps

@@ -274,6 +274,96 @@ def test_toy_mixer_with_its_own_state_is_registered_built_and_stepped(toy_regist
     H.check_rows(cut, ref, "float32", "toy model in portions")
 
 
+class Top1RoutedFeedForward:
+    """A toy feed-forward with routing: a float32 router picks one of E small two-matrix experts
+    per token; out_t = gate_t * W2[e_t] relu(W1[e_t] x_t), gate_t the softmax weight of the pick."""
+
+    def __new__(cls, *a, **k):
+        from poor_mans_mamba_b200.parts import FeedForward
+
+        class _Impl(FeedForward):
+            def __init__(self, hidden_size, experts, width):
+                self.hidden_size, self.experts, self.width, self.out_scale = hidden_size, experts, width, 1.0
+
+            def param_specs(self):
+                from poor_mans_mamba_b200.parts import ParamSpec
+                specs = [ParamSpec("router.weight", (self.experts, self.hidden_size))]
+                for e in range(self.experts):
+                    specs += [ParamSpec(f"experts.{e}.w1.weight", (self.width, self.hidden_size)),
+                              ParamSpec(f"experts.{e}.w2.weight", (self.hidden_size, self.width))]
+                return specs
+
+            def bind(self, params):
+                self.router = params["router.weight"]
+                self.w1 = [params[f"experts.{e}.w1.weight"] for e in range(self.experts)]
+                self.w2 = [params[f"experts.{e}.w2.weight"] for e in range(self.experts)]
+
+            def forward(self, x, ctx, out):
+                xf = x.float()
+                prob = torch.softmax(xf @ self.router.float().t(), -1)
+                gate, pick = prob.max(-1)
+                res = torch.zeros_like(xf)
+                for e in range(self.experts):
+                    rows = (pick == e).nonzero().flatten()
+                    if rows.numel():
+                        hid = torch.relu(xf[rows] @ self.w1[e].float().t())
+                        res[rows] = gate[rows, None] * (hid @ self.w2[e].float().t())
+                out.copy_(res.to(out.dtype))
+
+        return _Impl(*a, **k)
+
+
+def test_toy_routed_feed_forward_in_one_layer_and_a_dense_one_in_the_next():
+    """Feed-forwards are chosen layer by layer: a routed toy in layer 0, the dense SwiGLU in layer 1."""
+    from poor_mans_mamba_b200.parts import LayerSpec, PartSpec, register_feed_forward, registered
+    register_feed_forward("test_top1_routed", Top1RoutedFeedForward)
+    assert "test_top1_routed" in registered("feed_forward")
+    dtype = torch.float32
+    attn = PartSpec("paged_attention", "attn", {"num_heads": 3, "num_kv_heads": 1, "head_dim": 16,
+                                                "position_encoding": {"kind": "rotary", "theta": 100.0}})
+    norm1, norm2 = PartSpec("rmsnorm", "norm1", {"eps": 1e-5}), PartSpec("rmsnorm", "norm2", {"eps": 1e-5})
+    layers = [LayerSpec("parallel_prenorm", "layers.0.", norm1, (attn,), norm2,
+                        PartSpec("test_top1_routed", "moe", {"experts": 3, "width": 24})),
+              LayerSpec("parallel_prenorm", "layers.1.", norm1, (attn,), norm2,
+                        PartSpec("swiglu", "ff", {"intermediate_size": 40}))]
+    model = _single_layer_model(None, layer_specs=layers)
+    names = set(model.param_specs())
+    assert "layers.0.moe.experts.2.w2.weight" in names and "layers.1.ff.down_proj.weight" in names
+    dev, w = _random_tensors(model, 11, dtype, scale=6.0)
+    model.bind(dev, dtype, DEV)
+    w64 = {k: v.double() for k, v in w.items()}
+
+    cfg = {"num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 16, "rope_theta": 100.0}
+
+    def attention(n, pre):
+        return P.attention_mixer(n, w64, pre + "attn.", cfg)
+
+    picks = []
+
+    def layer(h, i):
+        pre = f"layers.{i}."
+        h = h + attention(P.rms_norm(h, w64[pre + "norm1.weight"], 1e-5), pre)
+        n = P.rms_norm(h, w64[pre + "norm2.weight"], 1e-5)
+        if i == 1:
+            return h + P.swiglu_mlp(n, w64, pre + "ff.", {})
+        prob = torch.softmax(n @ w64[pre + "moe.router.weight"].t(), -1)
+        gate, pick = prob.max(-1)
+        picks.append(pick)
+        res = torch.zeros_like(n)
+        for t in range(n.shape[0]):
+            e = int(pick[t])
+            hid = torch.relu(w64[pre + f"moe.experts.{e}.w1.weight"] @ n[t])
+            res[t] = gate[t] * (w64[pre + f"moe.experts.{e}.w2.weight"] @ hid)
+        return h + res
+
+    tokens = [int(t) for t in torch.randint(0, 50, (29,), generator=torch.Generator().manual_seed(3))]
+    ref = _plain_shell(tokens, w, layer, n_layers=2)
+    assert len(set(picks[0].tolist())) >= 2, "the routing is trivial for these weights"
+    whole, cut = _two_cuttings(_runner_for(model, dtype), tokens)
+    H.check_rows(whole, ref, "float32", "routed toy whole")
+    H.check_rows(cut, ref, "float32", "routed toy in portions")
+
+
 def test_order_may_run_a_layer_twice_and_share_a_cache():
     """Order [L0 on cache 0, L1 reading cache 0's keys/values, L0 again on cache 2]."""
     from poor_mans_mamba_b200.parts import LayerCall, LayerSpec, PartSpec

@@ -30,6 +30,9 @@ Tensor = torch.Tensor
 # programmatic dependent launch about 1.2 us, so the chain takes 17.8 us where the three separate
 # launches take 10.7 us.
 _CHAINED = os.environ.get("PMM_SKINNY_CHAIN", "0") == "1"
+# The mixers of a layer on parallel streams in steps of many tokens too (PMM_PARALLEL_MIXERS=0: one
+# after the other).
+_PARALLEL_MIXERS = os.environ.get("PMM_PARALLEL_MIXERS", "1") == "1"
 
 
 class ResidualStream:
@@ -220,9 +223,22 @@ class ParallelPreNormBlock(Part):
         if self._fused_in is not None:
             proj = ws.alloc((n.shape[0], self._fused_in.shape[0]), n.dtype)
             K.linear(n, self._fused_in, proj)
-            for m, (c0, c1) in zip(self.mixers, self._fused_cols):
-                out = stream.take_branch()
-                m.forward_projected(proj[:, c0:c1], ctx, cache, out)
+            # The mixers only share their input.  With several, the first runs on a side stream
+            # beside the others (parallel branches of a captured step): a prompt portion's scan and
+            # attention are each a chain of launches with few blocks, and together they fill the GPU.
+            outs = [stream.take_branch() for _ in self.mixers]
+            side = self._side_stream(proj.device) if len(self.mixers) > 1 and _PARALLEL_MIXERS else None
+            main = torch.cuda.current_stream(proj.device)
+            for i, (m, (c0, c1)) in enumerate(zip(self.mixers, self._fused_cols)):
+                if i == 0 and side is not None:
+                    side.wait_stream(main)
+                    with torch.cuda.stream(side):
+                        m.forward_projected(proj[:, c0:c1], ctx, cache, outs[i])
+                else:
+                    m.forward_projected(proj[:, c0:c1], ctx, cache, outs[i])
+            if side is not None:
+                main.wait_stream(side)
+            for m, out in zip(self.mixers, outs):
                 stream.add(out, m.out_scale)
         else:
             for m in self.mixers:

@@ -75,6 +75,8 @@ __global__ void __launch_bounds__(kAtThreads, 2)
                         float* __restrict__ part_ml, float scale_log2, int window, int split_len, int n_splits,
                         int page_size, int n_seq, int Hq, int Hkv, int* __restrict__ split_counter,
                         int* __restrict__ status) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int DH = kAtDh;
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long bar_q, bar_kfull[2], bar_vfull, bar_s, bar_sfree, bar_p, bar_pv;
@@ -491,7 +493,7 @@ PMM_EXPORT int pmm_attention_tc(const void* q, const void* pool, long long pool_
   if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
   if (e != cudaSuccess) return static_cast<int>(e);
   dim3 grid(n_tiles, Hkv, n_splits);
-  kern<<<grid, pmm::kAtThreads, pmm::kAtSmem, stream>>>(
+  pmm::launch_pdl(kern, grid, dim3(pmm::kAtThreads), pmm::kAtSmem, stream,
       static_cast<const pmm::bf16*>(q), map, block_table, max_blocks, positions, cu, static_cast<pmm::bf16*>(out), part_o,
       part_ml, scale * 1.4426950408889634f, window, split_len, n_splits, page_size, n_seq, Hq, Hkv, split_counter, status);
   return pmm::launch_status();

@@ -24,6 +24,8 @@ __global__ void conv1d_fwd_kernel(const S* __restrict__ x, long long ldx,
                                   const int* __restrict__ seq_of, const int* __restrict__ cu,
                                   const int* __restrict__ slots, S* __restrict__ y, int T, int C,
                                   int K) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   const int t = blockIdx.x;
   if (c >= C || t >= T) return;
@@ -55,6 +57,8 @@ __global__ void conv1d_window_update_kernel(const S* __restrict__ x, long long l
                                             float* __restrict__ window,
                                             const int* __restrict__ cu,
                                             const int* __restrict__ slots, int n_seq, int C, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   const int s = blockIdx.y;
   if (c >= C || s >= n_seq) return;
@@ -93,6 +97,8 @@ __global__ void __launch_bounds__(128)
                           const float* __restrict__ bias, const float* __restrict__ window,
                           const int* __restrict__ seq_of, const int* __restrict__ cu,
                           const int* __restrict__ slots, __nv_bfloat16* __restrict__ y, int T, int C) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int L = K - 1;
   constexpr int R = kConvStrip + L;
   const int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
@@ -231,13 +237,13 @@ PMM_EXPORT int pmm_conv1d_fwd(const void* x, long long ldx, const float* pre_sca
     dim3 vgrid((T + pmm::kConvStrip - 1) / pmm::kConvStrip, (C / 8 + 127) / 128);
     const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
     __nv_bfloat16* yb = static_cast<__nv_bfloat16*>(y);
-    if (K == 2) pmm::conv1d_fwd_vec_kernel<2><<<vgrid, 128, 0, stream>>>(xb, ldx, pre_scale, pre_bias, w_t, bias, window, seq_of, cu, slots, yb, T, C);
-    if (K == 3) pmm::conv1d_fwd_vec_kernel<3><<<vgrid, 128, 0, stream>>>(xb, ldx, pre_scale, pre_bias, w_t, bias, window, seq_of, cu, slots, yb, T, C);
-    if (K == 4) pmm::conv1d_fwd_vec_kernel<4><<<vgrid, 128, 0, stream>>>(xb, ldx, pre_scale, pre_bias, w_t, bias, window, seq_of, cu, slots, yb, T, C);
+    if (K == 2) pmm::launch_pdl(pmm::conv1d_fwd_vec_kernel<2>, vgrid, dim3(128), 0, stream, xb, ldx, pre_scale, pre_bias, w_t, bias, window, seq_of, cu, slots, yb, T, C);
+    if (K == 3) pmm::launch_pdl(pmm::conv1d_fwd_vec_kernel<3>, vgrid, dim3(128), 0, stream, xb, ldx, pre_scale, pre_bias, w_t, bias, window, seq_of, cu, slots, yb, T, C);
+    if (K == 4) pmm::launch_pdl(pmm::conv1d_fwd_vec_kernel<4>, vgrid, dim3(128), 0, stream, xb, ldx, pre_scale, pre_bias, w_t, bias, window, seq_of, cu, slots, yb, T, C);
     return pmm::launch_status();
   }
   dim3 grid(T, (C + 127) / 128);
-  PMM_DISPATCH_DTYPE(dtype, S, pmm::conv1d_fwd_kernel<S><<<grid, 128, 0, stream>>>(
+  PMM_DISPATCH_DTYPE(dtype, S, pmm::launch_pdl(pmm::conv1d_fwd_kernel<S>, grid, dim3(128), 0, stream,
                                    static_cast<const S*>(x), ldx, pre_scale, pre_bias, w, bias,
                                    window, seq_of, cu, slots, static_cast<S*>(y), T, C, K));
   return pmm::launch_status();
@@ -250,7 +256,7 @@ PMM_EXPORT int pmm_conv1d_window_update(const void* x, long long ldx, const floa
   if (n_seq <= 0) return 0;
   if (K < 2 || C <= 0 || n_seq > 65535) return PMM_ERR_BAD_ARGUMENT;
   dim3 grid((C + 127) / 128, n_seq);
-  PMM_DISPATCH_DTYPE(dtype, S, pmm::conv1d_window_update_kernel<S><<<grid, 128, 0, stream>>>(
+  PMM_DISPATCH_DTYPE(dtype, S, pmm::launch_pdl(pmm::conv1d_window_update_kernel<S>, grid, dim3(128), 0, stream,
                                    static_cast<const S*>(x), ldx, pre_scale, pre_bias, window, cu,
                                    slots, n_seq, C, K));
   return pmm::launch_status();

@@ -11,13 +11,16 @@
 //                       blocks, and up to two products with their own x, W, K and scale can
 //                       share one launch: the mixers' output projections).
 // Tensor-core form: the weights are the 16-row MMA operand (A), the tokens the 8-column one
-// (B), mma.sync m16n8k16 with float accumulation.  A block of 8 warps owns 32 weight rows;
-// W arrives in chunks of 256 columns through a 5-stage cp.async pipeline (16 KB a stage,
-// every thread copies the same four 16-byte pieces of each chunk, so the addresses are made
-// once); warps split a chunk 2 (rows) x 4 (columns) and the column quarters are added at the end.
+// (B), mma.sync m16n8k16 with float accumulation.  A block of 8 warps works on tiles of 32 weight
+// rows; W arrives in chunks of 256 columns through a 5-stage cp.async pipeline (16 KB a stage);
+// warps split a chunk 2 (rows) x 4 (columns) and the column quarters are added at the end.
+// The grid is no larger than what is resident at once: a block prepares its activations once
+// (for a wide model that is as much traffic as a tile of weights) and then walks its row tiles
+// bx, bx + gridDim.x, ... with the copy pipeline running on across the tile boundaries.
 // (reference: linear layers are cublasSgemm calls, src/ops/gpu/linear.cu:3-21, the
 // multipliers, SiLU and adds separate launches, src/ops/cuda_backend.cu:311-338.)
 #include "common.cuh"
+#include <algorithm>
 
 namespace pmm {
 
@@ -32,7 +35,7 @@ constexpr int kSgWStride = kSgChunk + 8;
 constexpr int kSgThreads = 256;
 constexpr int kSgPieces = kSgRows * (kSgChunk / 8) / kSgThreads;  // 16-byte pieces per thread and chunk
 
-enum { kSgStore = 0, kSgSwiglu = 1, kSgResidual = 2 };
+enum { kSgStore = 0, kSgSwiglu = 1, kSgResidual = 2, kSgStoreF32 = 3 };
 
 struct SkinnyProblem {
   const bf16* x;       // [M, ldx] activations, or nullptr when the norm prologue is used
@@ -53,6 +56,8 @@ struct SkinnyArgs {
   bf16* y;             // STORE / SWIGLU output
   long long ldy;
   float* h_out;        // RESIDUAL target [M, N]
+  float* y32;          // STORE_F32: y32[m, n] = y_scale * y
+  float y_scale;
 };
 
 __device__ __forceinline__ void sg_cp16(void* smem, const void* gmem, bool pred) {
@@ -76,22 +81,24 @@ __device__ __forceinline__ void sg_mma(float* d, const unsigned* a, unsigned b0,
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// What a block needs to know about its place: which rows of W, which slice of K, which product.
+// What a block needs to know about its place: which slice of K, which product, which row tiles.
 template <int MT, int MODE>
 struct SkinnyBlock {
   static constexpr int MP = MT * 8;  // padded tokens
   static constexpr int kSgStages = sg_stages(MT);
+  static constexpr int kTileCols = MODE == kSgSwiglu ? 16 : kSgRows;  // output columns of a row tile
   const SkinnyArgs& args;
   const SkinnyProblem& pr;
-  int K, k0, k1, kx, xs, n0, n_chunks;
+  int K, k0, k1, kx, xs, n_chunks;
+  int t0, t_step, my_tiles, total;  // row tiles t0, t0 + t_step, ...; total = my_tiles * n_chunks copies
   bf16* sW;     // [stages][32][264]
   bf16* sX;     // [MP][xs]
   float* sRed;  // [3][32][MP] column quarters, then up rows
   float* sNw;   // [kx] norm weights of the slice (norm prologue)
-  const bf16* src[kSgPieces];
-  bool row_ok[kSgPieces];
+  const bf16* src[kSgPieces];  // this thread's pieces of chunk 0 of the block's first tile
+  size_t tile_stride;          // elements of W between one of the block's tiles and the next
 
-  __device__ SkinnyBlock(const SkinnyArgs& a, int bx, int by, int bz, unsigned char* smem_raw)
+  __device__ SkinnyBlock(const SkinnyArgs& a, int bx, int bx_step, int by, int bz, unsigned char* smem_raw)
       : args(a), pr(a.p[bz]) {
     K = pr.K;
     k0 = by * a.k_slice;
@@ -102,49 +109,68 @@ struct SkinnyBlock {
     sX = sW + kSgStages * kSgRows * kSgWStride;
     sRed = reinterpret_cast<float*>(sX + MP * xs);
     sNw = sRed + 3 * 32 * MP;
-    n0 = bx * (MODE == kSgSwiglu ? 16 : kSgRows);  // first output column of the block
     n_chunks = kx / kSgChunk;
+    const int n_tx = (a.N + kTileCols - 1) / kTileCols;
+    t0 = bx;
+    t_step = bx_step;
+    my_tiles = bx < n_tx ? (bx + bx_step < n_tx ? (n_tx - 1 - bx) / bx_step + 1 : 1) : 0;
+    total = my_tiles * n_chunks;
+    tile_stride = static_cast<size_t>(bx_step) * kTileCols * K;
     // every thread copies the same pieces (row r, 16-byte column c8) of every chunk
-    const int tid = threadIdx.x, c8 = tid & 31;
+    const int tid = threadIdx.x, c8 = tid & 31, n0 = bx * kTileCols;
 #pragma unroll
     for (int j = 0; j < kSgPieces; ++j) {
       const int r = (tid >> 5) + j * (kSgThreads / 32);
-      // global row of W behind row r of the block's tile (SWIGLU: 16 gate rows, then their 16 up rows)
+      // global row of W behind row r of a tile (SWIGLU: 16 gate rows, then their 16 up rows)
       const int wr = MODE == kSgSwiglu ? (r < 16 ? n0 + r : a.N + n0 + (r - 16)) : n0 + r;
-      row_ok[j] = MODE == kSgSwiglu ? n0 + (r & 15) < a.N : n0 + r < a.N;
-      src[j] = pr.w + (row_ok[j] ? static_cast<size_t>(wr) * K : 0) + k0 + c8 * 8;
+      src[j] = pr.w + static_cast<size_t>(wr) * K + k0 + c8 * 8;
     }
   }
 
-  __device__ __forceinline__ void load_chunk(int stage, int chunk) const {
+  // Chunk `chunk` of the block's tile number `ti` -> pipeline stage `stage`: a thread copies four
+  // 16-byte pieces, the same ones (row r, column piece c8) of every chunk.
+  __device__ __forceinline__ void load_chunk(int stage, int ti, int chunk) const {
     const int tid = threadIdx.x, c8 = tid & 31;
+    const int n0 = (t0 + ti * t_step) * kTileCols;
     bf16* dst = sW + stage * kSgRows * kSgWStride + (tid >> 5) * kSgWStride + c8 * 8;
     const bool col_ok = k0 + chunk * kSgChunk + c8 * 8 < k1;
+    const size_t off = ti * tile_stride + chunk * kSgChunk;
 #pragma unroll
     for (int j = 0; j < kSgPieces; ++j) {
-      const bool ok = row_ok[j] && col_ok;
-      sg_cp16(dst + j * (kSgThreads / 32) * kSgWStride, ok ? src[j] + chunk * kSgChunk : pr.w, ok);
+      const int r = (tid >> 5) + j * (kSgThreads / 32);
+      const bool ok = col_ok && (MODE == kSgSwiglu ? n0 + (r & 15) < args.N : n0 + r < args.N);
+      sg_cp16(dst + j * (kSgThreads / 32) * kSgWStride, ok ? src[j] + off : pr.w, ok);
     }
   }
 
   // groups 0..stages-2: the first weight chunks.  They depend on nothing that an earlier kernel
   // or phase writes, so they are requested before the wait for it.
   __device__ __forceinline__ void request_weights() const {
+    int ti = 0, ch = 0;
 #pragma unroll
     for (int s = 0; s < kSgStages - 1; ++s) {
-      if (s < n_chunks) load_chunk(s, s);
+      if (s < total) load_chunk(s, ti, ch);
       sg_commit();
+      if (++ch == n_chunks) {
+        ch = 0;
+        ++ti;
+      }
     }
   }
 
-  __device__ void run() const;  // everything after the weights have been requested
+  // everything after the weights have been requested; ONE: the block has exactly one row tile
+  // (known when the kernel is chosen: every size of a small model), which keeps the loop plain
+  template <bool ONE>
+  __device__ void run() const;
+  __device__ void finish_tile(float (&acc)[MT][4], int n0) const;
 };
 
 template <int MT, int MODE>
+template <bool ONE>
 __device__ void SkinnyBlock<MT, MODE>::run() const {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int M = args.M;
-  if (kx == 0) return;
+  if (total == 0) return;
   // next group: the activations when they are read as bfloat16, else the norm weights
   if (pr.h_in == nullptr) {
     for (int i = tid; i < MP * (kx / 8); i += kSgThreads) {
@@ -224,18 +250,38 @@ __device__ void SkinnyBlock<MT, MODE>::run() const {
 
   const int ft = warp & 1, kh = warp >> 1;  // row half, column quarter of a chunk
   float acc[MT][4];
+  int c = 0, tile_i = 0;                                                       // chunk and tile being multiplied
+  int ld_tile = 0, ld_chunk = 0;                                               // ... and being requested
 #pragma unroll
-  for (int i = 0; i < MT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-
-  for (int c = 0; c < n_chunks; ++c) {
-    // groups committed so far: (stages-1) chunks, then x, then one per iteration; chunk c and x are
-    // complete when at most stages-2 of the newest groups are still in flight (for c = 0 the x
+  for (int q = 0; q < kSgStages - 1; ++q)
+    if (++ld_chunk == n_chunks) {
+      ld_chunk = 0;
+      ++ld_tile;
+    }
+  const int n_copies = ONE ? n_chunks : total;
+  for (int i = 0; i < n_copies; ++i) {
+    // groups committed so far: (stages-1) chunks, then x, then one per iteration; copy i and x are
+    // complete when at most stages-2 of the newest groups are still in flight (for i = 0 the x
     // group is the newest, so everything must have landed)
-    if (c == 0) sg_wait<0>(); else sg_wait<kSgStages - 2>();
+    if (i == 0) sg_wait<0>(); else sg_wait<kSgStages - 2>();
     __syncthreads();
-    if (c + kSgStages - 1 < n_chunks) load_chunk((c + kSgStages - 1) % kSgStages, c + kSgStages - 1);
-    sg_commit();
-    const bf16* tW = sW + (c % kSgStages) * kSgRows * kSgWStride;
+    if (ONE) {
+      if (i + kSgStages - 1 < n_copies) load_chunk((i + kSgStages - 1) % kSgStages, 0, i + kSgStages - 1);
+      sg_commit();
+    } else {
+      if (i + kSgStages - 1 < n_copies) load_chunk((i + kSgStages - 1) % kSgStages, ld_tile, ld_chunk);
+      sg_commit();
+      if (++ld_chunk == n_chunks) {
+        ld_chunk = 0;
+        ++ld_tile;
+      }
+    }
+    if (ONE ? i == 0 : c == 0) {
+#pragma unroll
+      for (int q = 0; q < MT; ++q) acc[q][0] = acc[q][1] = acc[q][2] = acc[q][3] = 0.f;
+    }
+    if (ONE) c = i;
+    const bf16* tW = sW + (i % kSgStages) * kSgRows * kSgWStride;
 #pragma unroll
     for (int ks = 0; ks < kSgChunk / 64; ++ks) {  // this warp's quarter of the chunk: 4 steps of 16
       const int kcol = kh * (kSgChunk / 4) + ks * 16;
@@ -250,9 +296,23 @@ __device__ void SkinnyBlock<MT, MODE>::run() const {
         sg_mma(acc[2 * np + 1], a, b2, b3);
       }
     }
+    if (!ONE && ++c == n_chunks) {
+      c = 0;
+      finish_tile(acc, (t0 + tile_i * t_step) * kTileCols);
+      ++tile_i;
+    }
   }
   sg_wait<0>();
-  __syncthreads();
+  if (ONE) finish_tile(acc, t0 * kTileCols);
+}
+
+// The sums of one row tile -> their place (the next tile's copies are in flight meanwhile).
+template <int MT, int MODE>
+__device__ void SkinnyBlock<MT, MODE>::finish_tile(float (&acc)[MT][4], int n0) const {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int M = args.M;
+  const int ft = warp & 1, kh = warp >> 1;
+  __syncthreads();  // (the tile before this one has been taken out of sRed)
 
   // add the four column quarters: warps 2..7 hand their sums to warps 0,1
   const int g = lane >> 2, t2 = (lane & 3) * 2;
@@ -306,7 +366,7 @@ __device__ void SkinnyBlock<MT, MODE>::run() const {
         }
       }
     }
-    return;
+    return;  // (of this tile)
   }
 
   if (kh == 0) {
@@ -318,6 +378,8 @@ __device__ void SkinnyBlock<MT, MODE>::run() const {
         if (n < args.N && m < M) {
           if (MODE == kSgStore) {
             args.y[static_cast<size_t>(m) * args.ldy + n] = __float2bfloat16_rn(acc[nt][e]);
+          } else if (MODE == kSgStoreF32) {
+            args.y32[static_cast<size_t>(m) * args.ldy + n] = args.y_scale * acc[nt][e];
           } else {
             atomicAdd(args.h_out + static_cast<size_t>(m) * args.N + n, pr.scale * acc[nt][e]);
           }
@@ -328,14 +390,14 @@ __device__ void SkinnyBlock<MT, MODE>::run() const {
 }
 
 // MT: token tiles of 8 (2, 4 or 8 -> up to 16, 32, 64 tokens).
-template <int MT, int MODE>
+template <int MT, int MODE, bool ONE>
 __global__ void __launch_bounds__(kSgThreads) skinny_gemm_kernel(const SkinnyArgs args) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   pdl_launch_dependents();
-  const SkinnyBlock<MT, MODE> blk(args, blockIdx.x, blockIdx.y, blockIdx.z, smem_raw);
+  const SkinnyBlock<MT, MODE> blk(args, blockIdx.x, gridDim.x, blockIdx.y, blockIdx.z, smem_raw);
   blk.request_weights();
   pdl_wait();
-  blk.run();
+  blk.template run<ONE>();
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -346,6 +408,7 @@ __global__ void __launch_bounds__(kSgThreads) skinny_gemm_kernel(const SkinnyArg
 // resident at once, so every block reaches every barrier); the wait is bounded all the same and
 // records a status instead of spinning for ever.
 constexpr int kChainPhases = 4;
+constexpr int kOneTile = 0x40000000;  // tile step of a block that takes exactly one row tile
 constexpr unsigned kChainSpinLimit = 1u << 24;
 constexpr unsigned long long kChainPerLaunch = 4096;  // what every launch adds to the counter (> 3 * 1024 arrivals)
 
@@ -373,9 +436,9 @@ __global__ void __launch_bounds__(kSgThreads) skinny_chain_kernel(const SkinnyCh
   auto for_block = [&](int p, int v, auto&& fn) {
     const int bx = v % ch.gx[p], by = (v / ch.gx[p]) % ch.gy[p], bz = v / (ch.gx[p] * ch.gy[p]);
     switch (ch.mode[p]) {
-      case kSgStore: fn(SkinnyBlock<MT, kSgStore>(ch.phase[p], bx, by, bz, smem_raw)); break;
-      case kSgSwiglu: fn(SkinnyBlock<MT, kSgSwiglu>(ch.phase[p], bx, by, bz, smem_raw)); break;
-      default: fn(SkinnyBlock<MT, kSgResidual>(ch.phase[p], bx, by, bz, smem_raw)); break;
+      case kSgStore: fn(SkinnyBlock<MT, kSgStore>(ch.phase[p], bx, kOneTile, by, bz, smem_raw)); break;
+      case kSgSwiglu: fn(SkinnyBlock<MT, kSgSwiglu>(ch.phase[p], bx, kOneTile, by, bz, smem_raw)); break;
+      default: fn(SkinnyBlock<MT, kSgResidual>(ch.phase[p], bx, kOneTile, by, bz, smem_raw)); break;
     }
   };
   auto n_blocks = [&](int p) { return ch.gx[p] * ch.gy[p] * ch.gz[p]; };
@@ -396,7 +459,7 @@ __global__ void __launch_bounds__(kSgThreads) skinny_chain_kernel(const SkinnyCh
     for (int v = blockIdx.x; v < n_blocks(p); v += G) {
       for_block(p, v, [&](const auto& blk) {
         if (!requested) blk.request_weights();
-        blk.run();
+        blk.template run<true>();
       });
       requested = false;
       __syncthreads();  // shared memory is free for the next block of work
@@ -442,13 +505,31 @@ int launch_skinny(const SkinnyArgs& a, int k_max, cudaStream_t stream) {
   const int kx = (min(a.k_slice, k_max) + kSgChunk - 1) / kSgChunk * kSgChunk;
   const size_t smem = skinny_smem(MP, kx);
   if (smem > 220 * 1024) return PMM_ERR_BAD_ARGUMENT;
-  auto kern = skinny_gemm_kernel<MT, MODE>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-  if (e != cudaSuccess) return static_cast<int>(e);
-  const int cols_per_block = MODE == kSgSwiglu ? 16 : kSgRows;
-  dim3 grid((a.N + cols_per_block - 1) / cols_per_block, (k_max + a.k_slice - 1) / a.k_slice, a.n_problems);
-  launch_pdl(kern, grid, dim3(kSgThreads), smem, stream, a);
+  auto kern = skinny_gemm_kernel<MT, MODE, false>;
+  auto kern_one = skinny_gemm_kernel<MT, MODE, true>;
+  for (auto k : {kern, kern_one}) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  // no more blocks than are resident at once; each walks the row tiles bx, bx + gridDim.x, ...
+  static size_t seen_smem = ~size_t(0);
+  static int slots = 0;
+  if (seen_smem != smem) {
+    int per_sm = 0, n_sm = 0, dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kSgThreads, smem) != cudaSuccess || per_sm < 1)
+      return PMM_ERR_BAD_ARGUMENT;
+    slots = per_sm * n_sm;
+    seen_smem = smem;
+  }
+  const int cols_per_tile = MODE == kSgSwiglu ? 16 : kSgRows;
+  const int n_tx = (a.N + cols_per_tile - 1) / cols_per_tile;
+  const int gy = (k_max + a.k_slice - 1) / a.k_slice;
+  const int gx = std::min(n_tx, std::max(1, slots / (gy * a.n_problems)));
+  dim3 grid(gx, gy, a.n_problems);
+  launch_pdl(gx == n_tx ? kern_one : kern, grid, dim3(kSgThreads), smem, stream, a);
   return launch_status();
 }
 
@@ -512,6 +593,24 @@ PMM_EXPORT int pmm_skinny_gemm(int mode, int M, int N, const void* x0, long long
     case pmm::kSgResidual: return pmm::dispatch_skinny<pmm::kSgResidual>(a, k_max, stream);
     default: return PMM_ERR_BAD_ARGUMENT;
   }
+}
+
+// y32[M, ldy] (float32) = scale * (x[M, K] W[N, K]^T) for up to 64 rows of bfloat16 activations: the
+// output head of steps that ask for few rows of logits.
+PMM_EXPORT int pmm_skinny_gemm_f32out(int M, int N, const void* x, long long ldx, const void* w, int K, float scale,
+                                      float* y32, long long ldy, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 64 || K <= 0 || K % 8 || !x || !w || !y32) return PMM_ERR_BAD_ARGUMENT;
+  pmm::SkinnyArgs a{};
+  a.p[0] = {static_cast<const pmm::bf16*>(x), ldx, nullptr, nullptr, 0.f, static_cast<const pmm::bf16*>(w), K, 1.f};
+  a.n_problems = 1;
+  a.M = M;
+  a.N = N;
+  a.k_slice = (K + pmm::kSgChunk - 1) / pmm::kSgChunk * pmm::kSgChunk;
+  a.ldy = ldy;
+  a.y32 = y32;
+  a.y_scale = scale;
+  return pmm::dispatch_skinny<pmm::kSgStoreF32>(a, K, stream);
 }
 
 // One phase of pmm_skinny_chain: the arguments of pmm_skinny_gemm without M, k_split and stream.

@@ -119,6 +119,8 @@ __global__ void __launch_bounds__(128)
                            float* __restrict__ chunk_cb, int H, int G) {
   constexpr int SX = P + 8, SB = N + 8;
   constexpr int NB = N < 64 ? N : 64;  // columns of the state per work unit
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ float s_delta[kQ], s_cs[kQ], s_w[kQ];
 
@@ -242,6 +244,8 @@ __global__ void __launch_bounds__(128)
 __global__ void ssd_state_pass_kernel(const float* __restrict__ chunk_state, const float* __restrict__ chunk_decay,
                                       bf16* __restrict__ start_state, float* __restrict__ state,
                                       const int* __restrict__ cu, const int* __restrict__ slots, int H, int PN) {
+  pdl_launch_dependents();
+  pdl_wait();
   // four state elements per thread (P*N is a multiple of 4 for every compiled pair)
   const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
   const int h = blockIdx.y, seq = blockIdx.z;
@@ -293,6 +297,8 @@ __global__ void __launch_bounds__(128)
                             float z_scale, const float* __restrict__ z_bias) {
   constexpr int SX = P + 8, SN = N + 8;
   constexpr int PB = P < 64 ? P : 64;  // output columns per pass
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sC = reinterpret_cast<bf16*>(smem_raw);
   bf16* sS = sC + kQ * SN;   // [P][SN] start state, bfloat16
@@ -491,12 +497,12 @@ int launch_ssd(const void* xbc, int ld_xbc, const void* dt_raw, long long ld_dt,
     if (e != cudaSuccess) return static_cast<int>(e);
   }
   dim3 grid(n_chunks, H), grid1(n_chunks, H + G);
-  k1<<<grid1, 128, smem1, stream>>>(static_cast<const bf16*>(xbc), ld_xbc, static_cast<const bf16*>(dt_raw), ld_dt,
+  launch_pdl(k1, grid1, dim3(128), smem1, stream, static_cast<const bf16*>(xbc), ld_xbc, static_cast<const bf16*>(dt_raw), ld_dt,
                                     dt_scale, dt_shift, a_log, cu, n_seq, chunk_state, chunk_decay, chunk_cb, H, G);
   const int PN = P * N;
   dim3 grid2((PN / 4 + 255) / 256, H, n_seq);
-  ssd_state_pass_kernel<<<grid2, 256, 0, stream>>>(chunk_state, chunk_decay, start_state, state, cu, slots, H, PN);
-  k3<<<grid, 128, smem3, stream>>>(static_cast<const bf16*>(xbc), ld_xbc, static_cast<const bf16*>(dt_raw), ld_dt,
+  launch_pdl(ssd_state_pass_kernel, grid2, dim3(256), 0, stream, chunk_state, chunk_decay, start_state, state, cu, slots, H, PN);
+  launch_pdl(k3, grid, dim3(128), smem3, stream, static_cast<const bf16*>(xbc), ld_xbc, static_cast<const bf16*>(dt_raw), ld_dt,
                                    dt_scale, dt_shift, a_log, d_skip, cu, n_seq, start_state, chunk_cb,
                                    static_cast<bf16*>(y), H, G, static_cast<const bf16*>(z_raw), ld_z, z_scale, z_bias);
   return launch_status();

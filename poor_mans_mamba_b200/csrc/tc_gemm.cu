@@ -50,6 +50,8 @@ __global__ void __launch_bounds__(kTcThreads)
     tc_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                    bf16* __restrict__ out, long long ld_out, int T, int K, int F, float gate_mult,
                    int* __restrict__ status) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long bar_full[kTcStages], bar_empty[kTcStages], bar_accum;
   __shared__ unsigned s_tmem_base;
@@ -252,14 +254,14 @@ PMM_EXPORT int pmm_tc_gemm(int mode, const void* x, long long ldx, const void* w
     auto kern = pmm::tc_gemm_kernel<pmm::kTcSwiglu>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pmm::kTcSmem));
     if (e != cudaSuccess) return static_cast<int>(e);
-    kern<<<grid, pmm::kTcThreads, pmm::kTcSmem, stream>>>(map_x, map_w, static_cast<pmm::bf16*>(out), ld_out, T, K,
-                                                          n_out, gate_mult, status);
+    pmm::launch_pdl(kern, grid, dim3(pmm::kTcThreads), pmm::kTcSmem, stream, map_x, map_w, static_cast<pmm::bf16*>(out), ld_out, T,
+                    K, n_out, gate_mult, status);
   } else {
     auto kern = pmm::tc_gemm_kernel<pmm::kTcPlain>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pmm::kTcSmem));
     if (e != cudaSuccess) return static_cast<int>(e);
-    kern<<<grid, pmm::kTcThreads, pmm::kTcSmem, stream>>>(map_x, map_w, static_cast<pmm::bf16*>(out), ld_out, T, K,
-                                                          n_out, gate_mult, status);
+    pmm::launch_pdl(kern, grid, dim3(pmm::kTcThreads), pmm::kTcSmem, stream, map_x, map_w, static_cast<pmm::bf16*>(out), ld_out, T,
+                    K, n_out, gate_mult, status);
   }
   return pmm::launch_status();
 }

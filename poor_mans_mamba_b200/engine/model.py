@@ -20,6 +20,10 @@ from ..parts.base import LayerCache, ModelSpec, ParamSpec, Part, StateSpec, buil
 from ..parts.block import ResidualStream
 from .context import StepContext
 
+# The output head of steps with few wanted rows through the weight-streaming product (PMM_SKINNY_HEAD=0:
+# the library product).
+_SKINNY_HEAD = os.environ.get("PMM_SKINNY_HEAD", "1") == "1"
+
 Tensor = torch.Tensor
 
 
@@ -132,6 +136,11 @@ class Model:
             K.linear(normed, self.head, logits)
             if mult != 1.0:
                 K.scale_f32_(logits, mult)
+        elif (_SKINNY_HEAD and n_rows <= K.SKINNY_MAX_TOKENS and self.hidden_size % 8 == 0
+              and K.skinny_fits(n_rows, self.hidden_size)):
+            # few rows of logits: the table is read once at memory speed by this repository's
+            # weight-streaming product (float32 out, multiplier in the epilogue)
+            K.skinny_linear_f32(normed, self.head, logits, mult)
         else:
             low = None if K.mm_has_f32_out() else ws.alloc((n_rows, V), normed.dtype)
             K.linear_f32_out(normed, self.head, logits, low, mult)

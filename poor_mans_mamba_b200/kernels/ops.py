@@ -74,6 +74,8 @@ _SIGNATURES = {
     "pmm_skinny_gemm": [c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_int,
                         c_float, c_void_p, c_longlong, c_void_p, c_int, c_float, c_void_p, c_longlong, c_void_p,
                         c_int, c_void_p],
+    "pmm_skinny_gemm_f32out": [c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_float, c_void_p, c_longlong,
+                               c_void_p],
     "pmm_tc_gemm_supported": [c_int, c_int, c_int, c_longlong, c_longlong],
     "pmm_tc_gemm": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_float,
                     c_void_p, c_void_p],
@@ -689,6 +691,20 @@ def skinny_linear(x: Tensor, weight: Tensor, out: Tensor) -> None:
     _need(out.dtype == torch.bfloat16 and out.shape == (M, N) and out.stride(1) == 1, "skinny_linear: out [M, N] bfloat16")
     _call("pmm_skinny_gemm", 0, M, N, x.data_ptr(), x.stride(0), None, None, 0.0, weight.data_ptr(), K,
           1.0, None, 0, None, 0, 0.0, out.data_ptr(), out.stride(0), None, 1, _stream())
+
+
+def skinny_linear_f32(x: Tensor, weight: Tensor, out: Tensor, scale: float) -> None:
+    """out[M, N] (float32) = scale * (x @ weight^T) for M <= 64 rows of bfloat16 activations: the
+    output head of a step that asks for few rows of logits (the table is streamed once)."""
+    _cuda(x, weight, out)
+    M, K = x.shape
+    _skinny_check(M, weight, K, "skinny_linear_f32")
+    _skinny_x(x, M, K, "skinny_linear_f32")
+    _need(skinny_fits(M, K), f"skinny_linear_f32: {M} tokens x {K} columns do not fit in shared memory")
+    N = weight.shape[0]
+    _need(out.dtype == torch.float32 and out.shape == (M, N) and out.stride(1) == 1, "skinny_linear_f32: out [M, N] float32")
+    _call("pmm_skinny_gemm_f32out", M, N, x.data_ptr(), x.stride(0), weight.data_ptr(), K, float(scale),
+          out.data_ptr(), out.stride(0), _stream())
 
 
 def skinny_swiglu(x: Tensor, gate_up: Tensor, gate_mult: float, out: Tensor) -> None:

@@ -547,10 +547,11 @@ def test_skinny_chain_matches_separate_products(M, D, F, I2):
 
 
 @pytest.mark.parametrize("M", [1, 7, 16, 17, 40, 64])
-@pytest.mark.parametrize("N,Kd", [(50, 96), (1024, 1000), (4120, 1024), (200, 2048)])
+@pytest.mark.parametrize("N,Kd", [(50, 96), (1024, 1000), (4120, 1024), (200, 2048), (9002, 3072), (20010, 520)])
 def test_skinny_gemm_modes(M, N, Kd):
     """The weight-streaming product for few tokens: norm prologue + store, norm + SwiGLU, and
-    residual accumulation of one and two products, at widths on and off the chunk size."""
+    residual accumulation of one and two products, at widths on and off the chunk size, and with
+    more row tiles than blocks are resident (a block then walks several tiles)."""
     g = torch.Generator().manual_seed(M * 131 + N + Kd)
     ops = K()
     bf = torch.bfloat16
@@ -588,6 +589,21 @@ def test_skinny_gemm_modes(M, N, Kd):
     ops.skinny_residual(hd, [(xa.to(DEV), wa.to(DEV), -0.3), (xb.to(DEV), wb.to(DEV), 1.1)])
     ref2 = ref1 - 0.3 * (xa.double() @ wa.double().t()) + 1.1 * (xb.double() @ wb.double().t())
     close(hd, ref2, torch.float32, scale=30.0, what="skinny residual two products")
+
+
+@pytest.mark.parametrize("M,N,Kd", [(1, 301, 64), (8, 32784, 1024), (33, 13001, 768), (64, 5000, 1024), (16, 5000, 3072)])
+def test_skinny_product_with_float32_output_for_the_head(M, N, Kd):
+    """scale * (x W^T) as float32 rows (the output head of steps that want few rows of logits),
+    written into rows of a wider buffer; vocabularies that are no multiple of the 32-row tile."""
+    g = torch.Generator().manual_seed(M + N + Kd)
+    ops = K()
+    bf = torch.bfloat16
+    x = torch.randn(M, Kd, generator=g).to(bf)
+    w = (torch.randn(N, Kd, generator=g) * 0.05).to(bf)
+    out = torch.full((M, N + 3), float("nan"), device=DEV)
+    ops.skinny_linear_f32(x.to(DEV), w.to(DEV), out[:, :N], 0.7)
+    close(out[:, :N], 0.7 * (x.double() @ w.double().t()), torch.float32, scale=30.0, what="skinny float32 head")
+    assert bool(torch.isnan(out[:, N:]).all())
 
 
 @pytest.mark.parametrize("T,Kd,F", [(200, 128, 128), (128, 64, 256), (2048, 1024, 2048), (333, 1024, 384), (700, 3072, 640)])

@@ -644,6 +644,7 @@ def flash_decode_attention(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], 
 
 SKINNY_MAX_TOKENS = 64  # the weight-streaming products take up to 64 tokens (where their shared memory fits)
 SKINNY_NORM_MAX_TOKENS = 16  # every block redoes the norm of all rows: beyond this a norm launch of its own is cheaper
+SKINNY_NORM_MAX_WIDTH = 1024  # ... and so it is for rows wider than a warp keeps in registers (they are read twice)
 
 
 def _skinny_check(M: int, w: Tensor, K: int, what: str) -> None:

@@ -165,7 +165,7 @@ class ParallelPreNormBlock(Part):
         if ahead and side is None:
             K.l2_prefetch(ahead)
         proj = ws.alloc((T, self._fused_in.shape[0]), ctx.dtype)
-        fused_norm = T <= K.SKINNY_NORM_MAX_TOKENS
+        fused_norm = T <= K.SKINNY_NORM_MAX_TOKENS and self.hidden_size <= K.SKINNY_NORM_MAX_WIDTH
         if fused_norm:
             K.skinny_linear_norm(h, self.mixer_norm.weight, self.mixer_norm.eps, self._fused_in, proj)
         else:

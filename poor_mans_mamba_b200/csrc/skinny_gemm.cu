@@ -73,6 +73,10 @@ __device__ __forceinline__ void sg_ldm(unsigned& r0, unsigned& r1, unsigned& r2,
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
 }
+__device__ __forceinline__ void sg_ldm2(unsigned& r0, unsigned& r1, const void* p) {
+  const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(s));
+}
 __device__ __forceinline__ void sg_mma(float* d, const unsigned* a, unsigned b0, unsigned b1) {
   asm volatile(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
@@ -194,11 +198,12 @@ __device__ void SkinnyBlock<MT, MODE>::run() const {
     // squares and the scaling.
     constexpr int kV = 8;                 // float4 per lane per pass
     constexpr int kPass = kV * 32 * 4;    // 1024 columns per pass
-    for (int m0 = warp * 2; m0 < MP; m0 += 2 * (kSgThreads / 32)) {
-      float inv[2];
-      float4 keep[2][kV];
+    constexpr int kTok = MP >= 2 * (kSgThreads / 32) ? 2 : 1;  // tokens per warp and round: all warps busy, and every warp walks the loop equally often
+    for (int m0 = warp * kTok; m0 < MP; m0 += kTok * (kSgThreads / 32)) {
+      float inv[kTok];
+      float4 keep[kTok][kV];
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
+      for (int j = 0; j < kTok; ++j) {
         const int m = m0 + j;
         float ss = 0.f;
         if (m < M) {
@@ -221,7 +226,7 @@ __device__ void SkinnyBlock<MT, MODE>::run() const {
       sg_wait<0>();  // the norm weights (and, incidentally, the first weight chunks) have landed
       __syncthreads();           // ... and everyone else's; every warp walks this loop equally often
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
+      for (int j = 0; j < kTok; ++j) {
         const int m = m0 + j;
         if (m >= MP) continue;
         const float* row = pr.h_in + static_cast<size_t>(m < M ? m : 0) * K;
@@ -288,6 +293,11 @@ __device__ void SkinnyBlock<MT, MODE>::run() const {
       unsigned a[4];
       sg_ldm(a[0], a[1], a[2], a[3], tW + (ft * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kSgWStride + kcol + (lane >> 4) * 8);
       const int kx_col = c * kSgChunk + kcol;
+      if (MT == 1) {  // up to 8 tokens: one 8-column operand
+        unsigned b0, b1;
+        sg_ldm2(b0, b1, sX + (lane & 7) * xs + kx_col + ((lane >> 3) & 1) * 8);
+        sg_mma(acc[0], a, b0, b1);
+      }
 #pragma unroll
       for (int np = 0; np < MT / 2; ++np) {
         unsigned b0, b1, b2, b3;
@@ -389,7 +399,7 @@ __device__ void SkinnyBlock<MT, MODE>::finish_tile(float (&acc)[MT][4], int n0) 
   }
 }
 
-// MT: token tiles of 8 (2, 4 or 8 -> up to 16, 32, 64 tokens).
+// MT: token tiles of 8 (1, 2, 4 or 8 -> up to 8, 16, 32, 64 tokens).
 template <int MT, int MODE, bool ONE>
 __global__ void __launch_bounds__(kSgThreads) skinny_gemm_kernel(const SkinnyArgs args) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -535,6 +545,7 @@ int launch_skinny(const SkinnyArgs& a, int k_max, cudaStream_t stream) {
 
 template <int MODE>
 int dispatch_skinny(const SkinnyArgs& a, int k_max, cudaStream_t stream) {
+  if (a.M <= 8) return launch_skinny<1, MODE>(a, k_max, stream);
   if (a.M <= 16) return launch_skinny<2, MODE>(a, k_max, stream);
   if (a.M <= 32) return launch_skinny<4, MODE>(a, k_max, stream);
   if (a.M <= 64) return launch_skinny<8, MODE>(a, k_max, stream);

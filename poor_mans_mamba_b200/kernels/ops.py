@@ -656,7 +656,7 @@ def _skinny_check(M: int, w: Tensor, K: int, what: str) -> None:
 def skinny_fits(M: int, K: int) -> bool:
     """Whether M tokens x K columns of activations fit in shared memory beside the weight pipeline
     (the products that cannot split K keep the whole row block resident)."""
-    mp = 16 if M <= 16 else 32 if M <= 32 else 64
+    mp = 8 if M <= 8 else 16 if M <= 16 else 32 if M <= 32 else 64
     kx = (K + 255) // 256 * 256
     stages = 3 if mp > 32 else 5
     return M <= 64 and stages * 32 * 264 * 2 + mp * (kx + 8) * 2 + 3 * 32 * mp * 4 + kx * 4 <= 220 * 1024

@@ -23,10 +23,12 @@ L2 flush is needed between timed iterations.
 from __future__ import annotations
 
 import argparse
+import atexit
 import gc
 import json
 import os
 import random
+import shutil
 import statistics
 import subprocess
 import sys
@@ -187,6 +189,7 @@ def main() -> int:
     vocab = cfg["vocab_size"]
 
     tmp = tempfile.mkdtemp(prefix="pmm_bench_")
+    atexit.register(shutil.rmtree, tmp, ignore_errors=True)  # the model folder goes when the run ends
     t0 = time.time()
     write_random_model(cfg, seed=2, out_dir=tmp)
     print(f"[bench] wrote random model in {time.time() - t0:.1f}s", file=sys.stderr, flush=True)

@@ -537,7 +537,9 @@ int launch_skinny(const SkinnyArgs& a, int k_max, cudaStream_t stream) {
   const int cols_per_tile = MODE == kSgSwiglu ? 16 : kSgRows;
   const int n_tx = (a.N + cols_per_tile - 1) / cols_per_tile;
   const int gy = (k_max + a.k_slice - 1) / a.k_slice;
-  const int gx = std::min(n_tx, std::max(1, slots / (gy * a.n_problems)));
+  int busy = 0;  // (K slice, product) pairs that have work: a product with a shorter K leaves its last slices empty
+  for (int p = 0; p < a.n_problems; ++p) busy += (a.p[p].K + a.k_slice - 1) / a.k_slice;
+  const int gx = std::min(n_tx, std::max(1, slots / std::max(busy, 1)));
   dim3 grid(gx, gy, a.n_problems);
   launch_pdl(gx == n_tx ? kern_one : kern, grid, dim3(kSgThreads), smem, stream, a);
   return launch_status();

@@ -136,10 +136,11 @@ class Model:
             K.linear(normed, self.head, logits)
             if mult != 1.0:
                 K.scale_f32_(logits, mult)
-        elif (_SKINNY_HEAD and n_rows <= K.SKINNY_MAX_TOKENS and self.hidden_size % 8 == 0
+        elif (_SKINNY_HEAD and n_rows <= K.SKINNY_NORM_MAX_TOKENS and self.hidden_size % 8 == 0
               and K.skinny_fits(n_rows, self.hidden_size)):
-            # few rows of logits: the table is read once at memory speed by this repository's
-            # weight-streaming product (float32 out, multiplier in the epilogue)
+            # up to 16 rows of logits: the table is read once at memory speed by this repository's
+            # weight-streaming product (float32 out, multiplier in the epilogue); beyond that the
+            # library product was measured slightly faster
             K.skinny_linear_f32(normed, self.head, logits, mult)
         else:
             low = None if K.mm_has_f32_out() else ws.alloc((n_rows, V), normed.dtype)

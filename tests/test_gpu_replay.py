@@ -168,7 +168,7 @@ def test_decode_through_cuda_graphs(case, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_repeated_step_shapes_replay_from_graphs(case, dtype):
+def test_repeated_step_shapes_replay_from_graphs(case, dtype, tmp_path):
     """A step shape that comes again is recorded into a CUDA graph and replayed from then on:
     same logits as the plain implementation for different requests, contents, slots and pages."""
     from poor_mans_mamba_b200.engine import StepEntry
@@ -176,8 +176,7 @@ def test_repeated_step_shapes_replay_from_graphs(case, dtype):
     rng = random.Random(7)
     v = cfg["vocab_size"]
     from model_dirs import make_model_dir  # weights of the case again, for fresh references
-    import tempfile
-    _, _, weights = make_model_dir(which, tempfile.mkdtemp())
+    _, _, weights = make_model_dir(which, str(tmp_path))
     runner = H.make_runner(d, dtype, page_size=16, num_pages=64, num_slots=3)
     runner.enable_graphs(max_seq_len=512)
     for rep in range(4):

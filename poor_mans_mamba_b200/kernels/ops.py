@@ -76,6 +76,9 @@ _SIGNATURES = {
                         c_int, c_void_p],
     "pmm_skinny_gemm_f32out": [c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_float, c_void_p, c_longlong,
                                c_void_p],
+    "pmm_skinny_tc_supported": [c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong],
+    "pmm_skinny_tc": [c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_float, c_void_p, c_longlong,
+                      c_void_p, c_int, c_float, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p],
     "pmm_tc_gemm_supported": [c_int, c_int, c_int, c_longlong, c_longlong],
     "pmm_tc_gemm": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_float,
                     c_void_p, c_void_p],
@@ -644,6 +647,7 @@ def flash_decode_attention(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], 
 
 SKINNY_MAX_TOKENS = 64  # the weight-streaming products take up to 64 tokens (where their shared memory fits)
 SKINNY_NORM_MAX_TOKENS = 16  # every block redoes the norm of all rows: beyond this a norm launch of its own is cheaper
+SKINNY_TC_FROM_TOKENS = 33   # from here on the tcgen05 form (skinny_tc_*) is faster than the mma.sync form (measured at 17/32/64 tokens)
 SKINNY_NORM_MAX_WIDTH = 1024  # ... and so it is for rows wider than a warp keeps in registers (they are read twice)
 
 
@@ -861,6 +865,68 @@ def tc_gemm_status(device) -> int:
     """0 unless a bounded wait inside a tensor-core product gave up (1 producer, 2 MMA issuer,
     3 epilogue).  Reading it waits for the device."""
     return int(_tc_status(torch.device(device)).item())
+
+
+def _skinny_tc_operand(x: Tensor, w: Tensor) -> bool:
+    return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2
+            and x.stride(1) == 1 and w.is_contiguous() and x.shape[1] == w.shape[1] and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0)
+
+
+def skinny_tc_supported(kind: str, x: Tensor, weight: Tensor, out: Optional[Tensor] = None) -> bool:
+    """Whether the tcgen05 weight-streaming product (1..64 tokens) takes these operands; kind is
+    "store", "swiglu" (both keep all of K resident: at most 1,024 columns) or "residual"."""
+    if not _skinny_tc_operand(x, weight):
+        return False
+    mode = {"store": 0, "swiglu": 1, "residual": 2}[kind]
+    T, K = x.shape
+    n = weight.shape[0] // 2 if kind == "swiglu" else weight.shape[0]
+    ldy = 8
+    if out is not None and kind != "residual":
+        if out.dtype != torch.bfloat16 or out.stride(1) != 1 or out.data_ptr() % 16:
+            return False
+        ldy = out.stride(0)
+    return bool(_fn("pmm_skinny_tc_supported")(mode, T, n, K, 0, x.stride(0), 0, ldy))
+
+
+def skinny_tc_linear(x: Tensor, weight: Tensor, out: Tensor) -> None:
+    """out[T, N] (bfloat16) = x @ weight^T for up to 64 tokens on the tcgen05 tensor cores."""
+    _cuda(x, weight, out)
+    _need(skinny_tc_supported("store", x, weight, out) and out.shape == (x.shape[0], weight.shape[0]),
+          "skinny_tc_linear: operands not supported (bfloat16, <= 64 tokens, K <= 1024 and a multiple of 8, aligned rows)")
+    T, K = x.shape
+    _call("pmm_skinny_tc", 0, T, weight.shape[0], x.data_ptr(), x.stride(0), weight.data_ptr(), K, 1.0, None, 0, None, 0,
+          0.0, out.data_ptr(), out.stride(0), None, _tc_status(x.device).data_ptr(), _stream())
+
+
+def skinny_tc_swiglu(x: Tensor, gate_up: Tensor, gate_mult: float, out: Tensor) -> None:
+    """out[T, F] = silu(gate * gate_mult) * up with [gate | up] = x @ gate_up^T (tcgen05, up to 64 tokens)."""
+    _cuda(x, gate_up, out)
+    F = gate_up.shape[0] // 2
+    _need(gate_up.shape[0] == 2 * F and skinny_tc_supported("swiglu", x, gate_up, out) and out.shape == (x.shape[0], F),
+          "skinny_tc_swiglu: operands not supported (bfloat16, <= 64 tokens, K <= 1024 and a multiple of 8, aligned rows)")
+    T, K = x.shape
+    _call("pmm_skinny_tc", 1, T, F, x.data_ptr(), x.stride(0), gate_up.data_ptr(), K, float(gate_mult), None, 0, None, 0,
+          0.0, out.data_ptr(), out.stride(0), None, _tc_status(x.device).data_ptr(), _stream())
+
+
+def skinny_tc_residual(h: Tensor, products: Sequence[Tuple[Tensor, Tensor, float]]) -> None:
+    """h[T, N] += sum_i scale_i * (x_i @ w_i^T) for one or two products (tcgen05, up to 64 tokens;
+    float32 atomics, K in slices of at most 1,024 columns)."""
+    _need(1 <= len(products) <= 2, "skinny_tc_residual: one or two products")
+    _cuda(h)
+    T, N = h.shape
+    _need(h.dtype == torch.float32 and h.is_contiguous(), "skinny_tc_residual: h must be contiguous float32")
+    flat = []
+    for x, w, sc in products:
+        _cuda(x, w)
+        _need(skinny_tc_supported("residual", x, w) and x.shape[0] == T and w.shape[0] == N,
+              "skinny_tc_residual: operands not supported (bfloat16, <= 64 tokens, K a multiple of 8, aligned rows)")
+        flat.append((x.data_ptr(), x.stride(0), w.data_ptr(), x.shape[1], float(sc)))
+    a0 = flat[0]
+    a1 = flat[1] if len(flat) > 1 else (None, 0, None, 0, 0.0)
+    _call("pmm_skinny_tc", 2, T, N, a0[0], a0[1], a0[2], a0[3], a0[4], a1[0], a1[1], a1[2], a1[3], a1[4], None, 0,
+          h.data_ptr(), _tc_status(h.device).data_ptr(), _stream())
 
 
 def tc_gemm_supported(x: Tensor, weight: Tensor, n_out: int, swiglu: bool) -> bool:

@@ -33,6 +33,9 @@ _CHAINED = os.environ.get("PMM_SKINNY_CHAIN", "0") == "1"
 # The mixers of a layer on parallel streams in steps of many tokens too (PMM_PARALLEL_MIXERS=0: one
 # after the other).
 _PARALLEL_MIXERS = os.environ.get("PMM_PARALLEL_MIXERS", "1") == "1"
+# The tcgen05 form of the weight-streaming products for the larger few-token steps (PMM_TC_SKINNY=0:
+# the mma.sync form throughout).
+_TC_SKINNY = os.environ.get("PMM_TC_SKINNY", "1") == "1"
 
 
 class ResidualStream:
@@ -166,12 +169,17 @@ class ParallelPreNormBlock(Part):
             K.l2_prefetch(ahead)
         proj = ws.alloc((T, self._fused_in.shape[0]), ctx.dtype)
         fused_norm = T <= K.SKINNY_NORM_MAX_TOKENS and self.hidden_size <= K.SKINNY_NORM_MAX_WIDTH
+        # beyond 32 tokens the tcgen05 form of the products is the faster one (where it takes the sizes)
+        tensor_core = _TC_SKINNY and T >= K.SKINNY_TC_FROM_TOKENS
         if fused_norm:
             K.skinny_linear_norm(h, self.mixer_norm.weight, self.mixer_norm.eps, self._fused_in, proj)
         else:
             x = ws.alloc((T, self.hidden_size), ctx.dtype)
             K.add_rmsnorm(h, [], self.mixer_norm.weight, self.mixer_norm.eps, x)
-            K.skinny_linear(x, self._fused_in, proj)
+            if tensor_core and K.skinny_tc_supported("store", x, self._fused_in, proj):
+                K.skinny_tc_linear(x, self._fused_in, proj)
+            else:
+                K.skinny_linear(x, self._fused_in, proj)
         # The mixers only share their input: the first runs on a side stream beside the others
         # (in a captured step the two become parallel branches of the graph).
         products = [None] * len(self.mixers)
@@ -202,15 +210,24 @@ class ParallelPreNormBlock(Part):
                            ("residual", [(act, self.ffn.down, self.ffn.out_scale)])]
             K.skinny_chain(h, phases)
         else:
-            K.skinny_residual(h, products)
+            def add_products(prods):
+                if tensor_core and all(K.skinny_tc_supported("residual", px, pw) for px, pw, _ in prods):
+                    K.skinny_tc_residual(h, prods)
+                else:
+                    K.skinny_residual(h, prods)
+
+            add_products(products)
             if self.ffn is not None:
                 if fused_norm:
                     K.skinny_swiglu_norm(h, self.ffn_norm.weight, self.ffn_norm.eps, self.ffn.gate_up,
                                          self.ffn.gate_multiplier, act)
                 else:
                     K.add_rmsnorm(h, [], self.ffn_norm.weight, self.ffn_norm.eps, x)
-                    K.skinny_swiglu(x, self.ffn.gate_up, self.ffn.gate_multiplier, act)
-                K.skinny_residual(h, [(act, self.ffn.down, self.ffn.out_scale)])
+                    if tensor_core and K.skinny_tc_supported("swiglu", x, self.ffn.gate_up, act):
+                        K.skinny_tc_swiglu(x, self.ffn.gate_up, self.ffn.gate_multiplier, act)
+                    else:
+                        K.skinny_swiglu(x, self.ffn.gate_up, self.ffn.gate_multiplier, act)
+                add_products([(act, self.ffn.down, self.ffn.out_scale)])
         ws.release(mark)
 
     def forward(self, stream: ResidualStream, ctx, cache: LayerCache) -> None:

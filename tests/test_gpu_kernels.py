@@ -606,6 +606,51 @@ def test_skinny_product_with_float32_output_for_the_head(M, N, Kd):
     assert bool(torch.isnan(out[:, N:]).all())
 
 
+@pytest.mark.parametrize("T", [1, 17, 40, 64])
+@pytest.mark.parametrize("N,Kd", [(50, 96), (1024, 1000), (4120, 1024), (6000, 512), (304, 72)])
+def test_tcgen05_weight_streaming_product(T, N, Kd):
+    """The tcgen05 form of the weight-streaming product (17..64 tokens; fewer work too): store,
+    SwiGLU, and residual accumulation of one and two products with K in slices, at sizes on and
+    off the boxes of 64 columns and tiles of 32 rows, with more row tiles than blocks (a block then
+    walks several tiles through both accumulators), into column slices of wider buffers."""
+    g = torch.Generator().manual_seed(T * 131 + N + Kd)
+    ops = K()
+    bf = torch.bfloat16
+    xw = torch.randn(T, Kd + 8, generator=g).to(bf).to(DEV)
+    x = xw[:, :Kd]                                       # rows with a stride of their own
+    w = (torch.randn(N, Kd, generator=g) * 0.05).to(bf).to(DEV)
+    ref = x.double().cpu() @ w.double().cpu().t()
+    buf = torch.zeros(T, (N + 16 + 7) // 8 * 8, dtype=bf, device=DEV)  # rows of 16-byte multiples
+    assert ops.skinny_tc_supported("store", x, w, buf[:, 8:8 + N])
+    ops.skinny_tc_linear(x, w, buf[:, 8:8 + N])
+    close(buf[:, 8:8 + N], ref, bf, what="tcgen05 skinny store")
+    assert float(buf[:, :8].abs().sum()) == 0 and float(buf[:, 8 + N:].abs().sum()) == 0
+    if N % 16 == 0:  # (rows of the output are 16-byte multiples)
+        F = N // 2
+        act = torch.full((T, F), float("nan"), dtype=bf, device=DEV)
+        ops.skinny_tc_swiglu(x, w, 1.5, act)
+        close(act, P.silu(ref[:, :F] * 1.5) * ref[:, F:], bf, what="tcgen05 skinny swiglu")
+    # residual: one product whose K needs three slices, then two products of different inner sizes
+    K1, K2 = 2304, 136
+    xa = torch.randn(T, K1, generator=g).to(bf).to(DEV)
+    xb = torch.randn(T, K2, generator=g).to(bf).to(DEV)
+    wa = (torch.randn(N, K1, generator=g) * 0.05).to(bf).to(DEV)
+    wb = (torch.randn(N, K2, generator=g) * 0.05).to(bf).to(DEV)
+    hres = torch.randn(T, N, generator=g)
+    hd = hres.clone().to(DEV)
+    ops.skinny_tc_residual(hd, [(xa, wa, 0.6)])
+    ref1 = hres.double() + 0.6 * (xa.double().cpu() @ wa.double().cpu().t())
+    close(hd, ref1, torch.float32, scale=60.0, what="tcgen05 skinny residual one product")
+    ops.skinny_tc_residual(hd, [(xa, wa, -0.3), (xb, wb, 1.1)])
+    ref2 = ref1 - 0.3 * (xa.double().cpu() @ wa.double().cpu().t()) + 1.1 * (xb.double().cpu() @ wb.double().cpu().t())
+    close(hd, ref2, torch.float32, scale=60.0, what="tcgen05 skinny residual two products")
+    torch.cuda.synchronize()
+    assert ops.tc_gemm_status(DEV) == 0
+    # refusals: too many tokens, K not resident for a store
+    assert not ops.skinny_tc_supported("store", torch.zeros(65, Kd, dtype=bf, device=DEV), w)
+    assert not ops.skinny_tc_supported("store", xa, wa) and ops.skinny_tc_supported("residual", xa, wa)
+
+
 @pytest.mark.parametrize("T,Kd,F", [(200, 128, 128), (128, 64, 256), (2048, 1024, 2048), (333, 1024, 384), (700, 3072, 640)])
 def test_tcgen05_gemm_swiglu_and_plain(T, Kd, F):
     """The tcgen05 / TMA / tensor-memory product: SwiGLU epilogue and plain store, token counts

@@ -128,3 +128,23 @@ def test_prompt_steps_through_the_tcgen05_attention(h64, cutting, monkeypatch):
     for i, ref in enumerate(refs):
         H.check_rows(out[i], ref, "bfloat16", f"h64 {cutting} seq {i}")
     assert K.tc_gemm_status("cuda:0") == 0 and len(calls) >= 2 * 2  # two layers, at least two long steps
+
+
+def test_steps_of_33_to_64_tokens_take_the_tcgen05_products(h64, monkeypatch):
+    """Portions and mixed steps of 33..64 tokens run their SwiGLU and residual products on the
+    tcgen05 weight-streaming kernel; the logits match the plain implementation all the same."""
+    d, seqs, refs = h64
+    from poor_mans_mamba_b200.kernels import ops as K
+    calls = {"swiglu": 0, "residual": 0}
+    for name in calls:
+        original = getattr(K, f"skinny_tc_{name}")
+        monkeypatch.setattr(K, f"skinny_tc_{name}",
+                            lambda *a, _o=original, _n=name, **k: (calls.__setitem__(_n, calls[_n] + 1), _o(*a, **k))[1])
+    runner = H.make_runner(d, "bfloat16", page_size=64, num_pages=40, num_slots=4)
+    script = [([(0, 0, 48)], []), ([(0, 48, 64)], []), ([(0, 112, 33)], []), ([(1, 0, 30), (2, 0, 20)], []),
+              ([(0, 145, 555)], [0]), ([(1, 30, 40), (2, 20, 24)], []), ([(1, 70, 230)], [1]), ([(2, 44, 477)], [2])]
+    out = H.run_script(runner, seqs, script)
+    for i, ref in enumerate(refs):
+        H.check_rows(out[i], ref, "bfloat16", f"h64 steps of 33..64 tokens seq {i}")
+    assert K.tc_gemm_status("cuda:0") == 0
+    assert calls["swiglu"] == 5 * 2 and calls["residual"] == 5 * 2 * 2  # five such steps, two layers

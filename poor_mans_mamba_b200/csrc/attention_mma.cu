@@ -174,7 +174,13 @@ __global__ void __launch_bounds__(128)
     for (int i = tid; i < n_bt; i += 128) s_bt[i] = bt[bt_lo + i];
   __syncthreads();
   auto page_of = [&](int idx) { return bt_shared ? s_bt[idx - bt_lo] : bt[idx]; };
-  pdl_wait();  // from here on: queries, keys and values that earlier kernels of the step wrote
+  // A decode step that reads the projections itself is the only writer of the cache pages in its
+  // step: the keys and values of earlier positions may be requested before the wait for the
+  // kernel before this one (their latency then hides behind that kernel's tail); only the new
+  // token's projections need it.  Every other form waits here: the rotation kernel before it wrote
+  // queries and pages.
+  const bool late_wait = SPLITW && dec.q != nullptr && dec.k != nullptr;
+  if (!late_wait) pdl_wait();
 
   // the new token of a decode step: this block stores its key and value if its key range holds it
   const int new_pos = pos_max;
@@ -463,7 +469,10 @@ __global__ void __launch_bounds__(128)
         for (int i = tid; i < DH; i += 128) v_sm[i] = v_dst[i];
       }
       cp_async_commit();  // the first group also carries the Q rows
-      if (round0 == 0) prepare_decode_inputs();
+      if (round0 == 0) {
+        if (late_wait) pdl_wait();
+        prepare_decode_inputs();
+      }
       cp_async_wait<0>();
       __syncthreads();
       if (round0 == 0) load_q_fragments();
@@ -496,6 +505,7 @@ __global__ void __launch_bounds__(128)
   cp_async_commit();
   cp_async_wait<0>();
   __syncthreads();
+  if (late_wait && n_tiles == 0) pdl_wait();  // (a block without keys writes its empty part only then, too)
 
   constexpr float kLn2 = 0.6931471805599453f;
 #pragma unroll

@@ -1,4 +1,5 @@
-// Weight-streaming matrix product for steps of 17..64 tokens on the fifth-generation tensor cores:
+// Weight-streaming matrix product for steps of 33..64 tokens (it takes 1..64) on the fifth-generation
+// tensor cores:
 //   y[T, N] = x[T, K] W[N, K]^T, bfloat16 operands, float accumulation,
 // with the same epilogues as the mma.sync form for fewer tokens (skinny_gemm.cu): STORE (bfloat16),
 // SWIGLU (W = [gate rows; up rows], act = silu(gate * mult) * up) and RESIDUAL (h += scale * y with

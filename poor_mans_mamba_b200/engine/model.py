@@ -34,6 +34,7 @@ class Model:
         self.vocab_size = spec.vocab_size
         self.layers = []
         self._fetch_ahead = os.environ.get("PMM_FETCH_AHEAD", "1") == "1"
+        self._fetch_lists: Dict[int, tuple] = {}
         for ls in spec.layers:
             factory = _REGISTRIES["arrangement"].get(ls.arrangement)
             if factory is None:
@@ -118,7 +119,7 @@ class Model:
         for i, call in enumerate(order):
             # a layer that streams its weights once may fetch the next layer's ahead of time
             nxt = self.layers[order[i + 1].layer] if i + 1 < len(order) else None
-            ctx.fetch_ahead = nxt.streamed_weights() if self._fetch_ahead and hasattr(nxt, "streamed_weights") else None
+            ctx.fetch_ahead = self._weights_to_fetch(nxt, h.device) if self._fetch_ahead else None
             self.layers[call.layer].forward(stream, ctx, caches[call.cache_of])
         ctx.fetch_ahead = None
         if ctx.n_rows == 0:
@@ -126,6 +127,22 @@ class Model:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=h.device)
         normed = stream.normed(self.final_norm, rows=ctx.logit_rows)
         return self._head(normed, ctx)
+
+    def _weights_to_fetch(self, layer, device) -> Optional[List[Tensor]]:
+        """The matrices of ``layer`` to request into L2 while the layer before it runs, or None.
+        Only a layer whose matrices take at most a third of the L2 is fetched ahead: measured
+        +4% tokens/s at 26 MB a layer, nothing at 50 MB, and -16% at 365 MB (the lines are
+        evicted before they are used, and read twice)."""
+        if layer is None or not hasattr(layer, "streamed_weights"):
+            return None
+        cached = self._fetch_lists.get(id(layer))
+        if cached is None:
+            ws = layer.streamed_weights()
+            l2 = torch.cuda.get_device_properties(device).L2_cache_size if device.type == "cuda" else 0
+            size = sum(w.numel() * w.element_size() for w in ws)
+            cached = (ws if 0 < size <= l2 // 3 else None,)
+            self._fetch_lists[id(layer)] = cached
+        return cached[0]
 
     def _head(self, normed: Tensor, ctx: StepContext) -> Tensor:
         n_rows, V = normed.shape[0], self.vocab_size

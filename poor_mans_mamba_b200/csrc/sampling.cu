@@ -24,12 +24,27 @@ __device__ __forceinline__ float gumbel_noise(unsigned long long seed, unsigned 
   return -logf(-logf(u));
 }
 
-__global__ void sample_rows_kernel(const float* __restrict__ logits, long long ld,
-                                   const float* __restrict__ temperature,
-                                   const long long* __restrict__ seeds,
-                                   const int* __restrict__ steps, int* __restrict__ out, int V) {
-  __shared__ float best_v[32];
-  __shared__ int best_i[32];
+// Order-preserving map of a float onto unsigned integers (larger float -> larger integer).
+__device__ __forceinline__ unsigned sample_orderable(float x) {
+  const unsigned b = __float_as_uint(x);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+constexpr int kSampleThreads = 256;
+constexpr int kSampleLoads = 8;                                   // independent loads per thread and pass
+constexpr int kSampleSpan = 2 * kSampleLoads * kSampleThreads;    // vocabulary entries per block: two passes
+
+// A row is shared by ceil(V / kSampleSpan) blocks (a single block per row took 20 us for a
+// vocabulary of 130,000).  A block finds the best (value, index) of its span and merges it into
+// the row's 64-bit slot with atomicMax: value in the high word, ~index in the low word, so the
+// larger value wins and among equal values the smaller index.  The block that takes the row's
+// last ticket writes the token and leaves slot and ticket at zero for the next launch.
+__global__ void __launch_bounds__(kSampleThreads)
+    sample_rows_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ temperature,
+                       const long long* __restrict__ seeds, const int* __restrict__ steps, int* __restrict__ out,
+                       int V, unsigned long long* __restrict__ slots, int* __restrict__ tickets) {
+  __shared__ float best_v[kSampleThreads / 32];
+  __shared__ int best_i[kSampleThreads / 32];
   pdl_launch_dependents();
   pdl_wait();
   const int r = blockIdx.x;
@@ -41,19 +56,18 @@ __global__ void sample_rows_kernel(const float* __restrict__ logits, long long l
   const unsigned step = steps ? static_cast<unsigned>(steps[r]) : 0u;
   float bv = -CUDART_INF_F;
   int bi = 0x7fffffff;
-  // eight independent loads per thread and pass, so a row costs few memory round trips
-  constexpr int kU = 8;
-  for (int base = 0; base < V; base += kU * blockDim.x) {
-    float v[kU];
+  const int span_lo = blockIdx.y * kSampleSpan, span_hi = min(V, span_lo + kSampleSpan);
+  for (int base = span_lo; base < span_hi; base += kSampleLoads * kSampleThreads) {
+    float v[kSampleLoads];
 #pragma unroll
-    for (int u = 0; u < kU; ++u) {
-      const int i = base + u * blockDim.x + threadIdx.x;
-      v[u] = i < V ? row[i] : -CUDART_INF_F;
+    for (int u = 0; u < kSampleLoads; ++u) {
+      const int i = base + u * kSampleThreads + threadIdx.x;
+      v[u] = i < span_hi ? row[i] : -CUDART_INF_F;
     }
 #pragma unroll
-    for (int u = 0; u < kU; ++u) {
-      const int i = base + u * blockDim.x + threadIdx.x;
-      if (i >= V) continue;
+    for (int u = 0; u < kSampleLoads; ++u) {
+      const int i = base + u * kSampleThreads + threadIdx.x;
+      if (i >= span_hi) continue;
       float x = v[u];
       if (!greedy) x = x * inv_t + gumbel_noise(seed, step, static_cast<unsigned>(i));
       if (x > bv || (x == bv && i < bi) || bi == 0x7fffffff) {
@@ -78,7 +92,7 @@ __global__ void sample_rows_kernel(const float* __restrict__ logits, long long l
   }
   __syncthreads();
   if (warp == 0) {
-    const int nwarp = blockDim.x >> 5;
+    constexpr int nwarp = kSampleThreads / 32;
     bv = lane < nwarp ? best_v[lane] : -CUDART_INF_F;
     bi = lane < nwarp ? best_i[lane] : 0x7fffffff;
     for (int o = 16; o > 0; o >>= 1) {
@@ -89,18 +103,37 @@ __global__ void sample_rows_kernel(const float* __restrict__ logits, long long l
         bi = oi;
       }
     }
-    if (lane == 0) out[r] = bi == 0x7fffffff ? 0 : bi;
+    if (lane == 0) {
+      if (gridDim.y == 1) {
+        out[r] = bi == 0x7fffffff ? 0 : bi;
+      } else {
+        if (bi != 0x7fffffff)
+          atomicMax(slots + r, (static_cast<unsigned long long>(sample_orderable(bv)) << 32) |
+                                   (0xffffffffu - static_cast<unsigned>(bi)));
+        __threadfence();
+        if (atomicAdd(tickets + r, 1) == static_cast<int>(gridDim.y) - 1) {  // every span of the row is in
+          __threadfence();
+          const unsigned long long best = atomicExch(slots + r, 0ull);
+          tickets[r] = 0;
+          out[r] = best == 0ull ? 0 : static_cast<int>(0xffffffffu - static_cast<unsigned>(best & 0xffffffffu));
+        }
+      }
+    }
   }
 }
 
 }  // namespace pmm
 
+// slots (64-bit) and tickets (32-bit): one of each per row, zero before the first use and left
+// zero by every launch; needed when the vocabulary is wider than one block's span (4,096).
 PMM_EXPORT int pmm_sample_rows(const float* logits, long long ld, const float* temperature,
                                const long long* seeds, const int* steps, int* out, int n_rows, int V,
-                               cudaStream_t stream) {
+                               unsigned long long* slots, int* tickets, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (V <= 0) return PMM_ERR_BAD_ARGUMENT;
-  pmm::launch_pdl(pmm::sample_rows_kernel, dim3(n_rows), dim3(1024), 0, stream, logits, ld, temperature, seeds, steps,
-                  out, V);
+  const int parts = (V + pmm::kSampleSpan - 1) / pmm::kSampleSpan;
+  if (parts > 65535 || (parts > 1 && (!slots || !tickets))) return PMM_ERR_BAD_ARGUMENT;
+  pmm::launch_pdl(pmm::sample_rows_kernel, dim3(n_rows, parts), dim3(pmm::kSampleThreads), 0, stream, logits, ld,
+                  temperature, seeds, steps, out, V, slots, tickets);
   return pmm::launch_status();
 }

@@ -74,6 +74,7 @@ class GraphDecoder:
         self._rows: Dict[Hashable, Tuple[List[np.ndarray], List[int], int]] = {}  # request -> its block-table rows (host copies)
         self.replays = 0
         self.kernels_replayed = 0
+        K.ensure_sample_scratch(self.device, max(self.bucket_sizes))  # before any step is recorded
 
     # ------------------------------------------------------------------ capture
     def _context(self, bk: _Bucket) -> Tuple[StepContext, Dict]:

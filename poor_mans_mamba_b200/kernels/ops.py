@@ -85,7 +85,7 @@ _SIGNATURES = {
     "pmm_silu_mul": [c_void_p, c_longlong, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
     "pmm_add_row_bias": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "pmm_sample_rows": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                        c_void_p],
+                        c_void_p, c_void_p, c_void_p],
 }
 
 _FUNCS = {}
@@ -1030,6 +1030,25 @@ def add_row_bias_(x: Tensor, bias: Tensor) -> None:
     _call("pmm_add_row_bias", x.data_ptr(), bias.data_ptr(), x.shape[0], x.shape[1], _dt(x), _stream())
 
 
+_SAMPLE_SCRATCH: Dict[torch.device, Tuple[Tensor, Tensor]] = {}
+
+
+def ensure_sample_scratch(device, rows: int = 4096) -> Tuple[Tensor, Tensor]:
+    """A 64-bit slot and a ticket per row for the blocks that share a row of sample_rows: one pair of
+    buffers per device, zero when made and left zero by every launch (launches that use them are
+    expected on one stream at a time).  Call it before a step is recorded into a CUDA graph:
+    memory cannot be taken for it while a recording is under way."""
+    device = torch.device(device)
+    have = _SAMPLE_SCRATCH.get(device)
+    if have is None or have[0].numel() < rows:
+        _need(not torch.cuda.is_current_stream_capturing(),
+              "sample_rows: its scratch must exist before a CUDA graph is recorded (ensure_sample_scratch)")
+        n = max(4096, rows)
+        have = (torch.zeros(n, dtype=torch.int64, device=device), torch.zeros(n, dtype=torch.int32, device=device))
+        _SAMPLE_SCRATCH[device] = have
+    return have
+
+
 def sample_rows(logits: Tensor, temperature: Optional[Tensor], seeds: Optional[Tensor],
                 steps: Optional[Tensor], out: Tensor) -> None:
     """out[r] = argmax (first index on ties) where temperature[r] <= 0, else a draw from
@@ -1046,8 +1065,9 @@ def sample_rows(logits: Tensor, temperature: Optional[Tensor], seeds: Optional[T
               "sample: seeds must be int64 [rows]")
         _need(steps is not None and steps.numel() == n, "sample: steps must be int32 [rows]")
         _i32(steps, "sample: steps")
+    slots, tickets = ensure_sample_scratch(logits.device, n)
     _call("pmm_sample_rows", logits.data_ptr(), ld, _ptr(temperature), _ptr(seeds), _ptr(steps),
-          out.data_ptr(), n, V, _stream())
+          out.data_ptr(), n, V, slots.data_ptr(), tickets.data_ptr(), _stream())
 
 
 def l2_prefetch(tensors: Sequence[Tensor]) -> None:

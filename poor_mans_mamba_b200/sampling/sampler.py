@@ -20,6 +20,8 @@ class Sampler:
         self.device = torch.device(device)
         self._out: Optional[torch.Tensor] = None
         self._host: Optional[torch.Tensor] = None
+        if self.device.type == "cuda":
+            K.ensure_sample_scratch(self.device)
 
     def _buffers(self, n: int):
         if self._out is None or self._out.numel() < n:

@@ -478,6 +478,40 @@ def test_sampling_greedy_ties_and_temperature():
     assert set(out2.tolist()) == {0}
 
 
+@pytest.mark.parametrize("V", [4096, 4097, 32784, 130049])
+def test_sampling_over_a_vocabulary_shared_by_several_blocks(V):
+    """A row wider than one block's span is reduced by several blocks: greedy ties across spans
+    (the first index wins), negative rows, repeated launches (slots and tickets are left clean), and
+    temperature draws that equal those of the whole-row rule, argmax(logits / T + g_i)."""
+    ops = K()
+    g = torch.Generator().manual_seed(V)
+    logits = torch.randn(6, V, generator=g)
+    logits[0, 3] = logits[0, V - 1] = 9.0          # tie between the first and the last span
+    logits[1] = -5.0                                # all equal and negative: index 0
+    logits[2, V - 2] = 11.0
+    logits[3, min(4096, V - 1)] = 12.0              # first entry of the second span (or the last)
+    dev = logits.to(DEV)
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    for _ in range(3):
+        ops.sample_rows(dev, None, None, None, out)
+        want = logits.argmax(dim=1).tolist()
+        want[0], want[1] = 3, 0
+        assert out.tolist() == want
+    temps = torch.tensor([0.8, 1.3, 0.0, 0.5, 2.0, 1.0], device=DEV)
+    seeds = torch.arange(6, dtype=torch.int64, device=DEV) + 77
+    steps = torch.arange(6, dtype=torch.int32, device=DEV)
+    a = torch.empty(6, dtype=torch.int32, device=DEV)
+    b = torch.empty(6, dtype=torch.int32, device=DEV)
+    ops.sample_rows(dev, temps, seeds, steps, a)
+    ops.sample_rows(dev, temps, seeds, steps, b)
+    assert torch.equal(a, b) and int(a[2]) == V - 2   # same keys -> same draws; T = 0 is greedy
+    # one row at a time (another grid, same per-entry noise) draws the same tokens
+    for r in range(6):
+        one = torch.empty(1, dtype=torch.int32, device=DEV)
+        ops.sample_rows(dev[r:r + 1], temps[r:r + 1], seeds[r:r + 1], steps[r:r + 1], one)
+        assert int(one) == int(a[r])
+
+
 def test_unsupported_sizes_are_refused():
     from poor_mans_mamba_b200.kernels.ops import KernelError
     from poor_mans_mamba_b200.parts.attention import PagedAttention

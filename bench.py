@@ -58,6 +58,17 @@ CONFIG_05B = {
 }
 FULL_LAYERS = 36
 
+# Other Falcon-H1 layer sizes (BASELINE.json configs[3] and configs[4]) for measurements beside the
+# benchmark's own configuration: `--sizes 7b --layers 4`.  name -> (changed keys, layers of the full model)
+OTHER_SIZES = {
+    "1.5b-deep": (dict(hidden_size=1280, num_attention_heads=6, num_key_value_heads=2, head_dim=128,
+                       intermediate_size=3072, vocab_size=65537, mamba_d_ssm=2560, mamba_n_heads=40, mamba_d_head=64,
+                       mamba_d_state=256, mamba_chunk_size=256), 66),
+    "7b": (dict(hidden_size=3072, num_attention_heads=12, num_key_value_heads=2, head_dim=128,
+                intermediate_size=12288, vocab_size=130049, mamba_d_ssm=6144, mamba_n_heads=48, mamba_d_head=128,
+                mamba_d_state=256, mamba_chunk_size=256), 44),
+}
+
 
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -149,7 +160,10 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096, help="context length at which decoding ends")
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration has "
+    ap.add_argument("--sizes", default="0.5b", choices=["0.5b"] + sorted(OTHER_SIZES),
+                    help="layer sizes; 0.5b is the benchmark's configuration, the others are for measurements "
+                         "beside it (give --layers: a few layers of them already fill the memory system)")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has "
                     "(same layer sizes) where memory or time needs it")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
@@ -181,6 +195,12 @@ def main() -> int:
 
     peaks = load_peaks()
     cfg = dict(CONFIG_05B)
+    full_layers = FULL_LAYERS
+    if args.sizes != "0.5b":
+        cfg.update(OTHER_SIZES[args.sizes][0])
+        full_layers = OTHER_SIZES[args.sizes][1]
+    if args.layers is None:
+        args.layers = full_layers
     cfg["num_hidden_layers"] = args.layers
     nums = model_numbers(cfg)
     K_steps, W = args.steps, args.warmup
@@ -323,11 +343,11 @@ def main() -> int:
                 torch.cuda.empty_cache()
 
     result = {
-        "metric": "decode tokens/s (Falcon-H1-0.5B layer sizes, random weights)", "value": round(tok_s, 1),
+        "metric": f"decode tokens/s (Falcon-H1-{args.sizes.upper()} layer sizes, random weights)", "value": round(tok_s, 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": K_steps, "warmup": W, "ms_per_step": round(ms_step, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
         "data": "synthetic: uniform random token ids (seed 2), random-init weights (seed 2)",
-        "config": {"model": "falcon-h1-0.5b-sizes", "layers": args.layers, "layers_full": FULL_LAYERS,
+        "config": {"model": f"falcon-h1-{args.sizes}-sizes", "layers": args.layers, "layers_full": full_layers,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": vocab, "d_ssm": cfg["mamba_d_ssm"],

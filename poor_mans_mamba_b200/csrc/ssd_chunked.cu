@@ -256,11 +256,10 @@ __global__ void ssd_state_pass_kernel(const float* __restrict__ chunk_state, con
   if (nc <= 0) return;
   float4* sp = reinterpret_cast<float4*>(state + (static_cast<size_t>(slots[seq]) * H + h) * PN + e);
   float4 s = *sp;
-  // The chain through s is short; the loads are what cost: eight chunks are requested at a time.
+  // The chain through s is short; the loads are what cost: eight chunks are requested at a time,
+  // and the next eight while these are folded in, so a walk costs about one round trip to L2.
   constexpr int kAhead = 8;
-  for (int c0 = 0; c0 < nc; c0 += kAhead) {
-    float4 local[kAhead];
-    float decay[kAhead];
+  auto request = [&](float4 (&local)[kAhead], float (&decay)[kAhead], int c0) {
 #pragma unroll
     for (int i = 0; i < kAhead; ++i) {
       const int c = min(c0 + i, nc - 1);
@@ -268,6 +267,8 @@ __global__ void ssd_state_pass_kernel(const float* __restrict__ chunk_state, con
       local[i] = __ldcs(reinterpret_cast<const float4*>(chunk_state + ch * PN + e));
       decay[i] = chunk_decay[ch];
     }
+  };
+  auto fold = [&](const float4 (&local)[kAhead], const float (&decay)[kAhead], int c0) {
 #pragma unroll
     for (int i = 0; i < kAhead; ++i) {
       if (c0 + i < nc) {
@@ -281,6 +282,18 @@ __global__ void ssd_state_pass_kernel(const float* __restrict__ chunk_state, con
         s.z = s.z * decay[i] + local[i].z;
         s.w = s.w * decay[i] + local[i].w;
       }
+    }
+  };
+  float4 la[kAhead], lb[kAhead];
+  float da[kAhead], db[kAhead];
+  request(la, da, 0);
+  for (int c0 = 0; c0 < nc; c0 += 2 * kAhead) {
+    const bool second = c0 + kAhead < nc;
+    if (second) request(lb, db, c0 + kAhead);
+    fold(la, da, c0);
+    if (second) {
+      if (c0 + 2 * kAhead < nc) request(la, da, c0 + 2 * kAhead);
+      fold(lb, db, c0 + kAhead);
     }
   }
   *sp = s;

@@ -151,6 +151,102 @@ def model_numbers(cfg):
         "params": L * (layer_mat + layer_vec) + 2 * V * D + D,
     }
 
+def sized_config(args):
+    """config.json dict of the run and the layer count of the full model."""
+    cfg = dict(CONFIG_05B)
+    full_layers = FULL_LAYERS
+    if args.sizes != "0.5b":
+        cfg.update(OTHER_SIZES[args.sizes][0])
+        full_layers = OTHER_SIZES[args.sizes][1]
+    if args.layers is None:
+        args.layers = full_layers
+    cfg["num_hidden_layers"] = args.layers
+    return cfg, full_layers
+
+
+def config_record(cfg, args, full_layers):
+    """The flat `config` of the JSON line: every size of the run, the same keys for both arms."""
+    return {"model": f"falcon-h1-{args.sizes}-sizes", "layers": args.layers, "layers_full": full_layers,
+            "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+            "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+            "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "d_ssm": cfg["mamba_d_ssm"],
+            "ssm_heads": cfg["mamba_n_heads"], "d_state": cfg["mamba_d_state"], "d_conv": cfg["mamba_d_conv"],
+            "chunk": cfg["mamba_chunk_size"], "global_batch": args.batch, "seq_len": args.context,
+            "parallelism": "single-gpu", "page_size": 64, "l2": "inputs exceed L2 (no flush)"}
+
+
+def reference_arm(args) -> int:
+    """`--impl reference`: the UNMODIFIED CUDA path of the reference (FalconH1Runner + CUDABackend +
+    src/ops/gpu/*.cu: FP32, cublasSgemm, one request per cache slot), built with nvcc and cuBLAS by
+    baseline/build_reference.py and driven by baseline/ref_driver.cu.  Same layer sizes, layer
+    count, batch, context, step count and warm-up as this repository's arm; random weights made by
+    the driver.  Batch B > 1 is B slots on B streams, the way the reference's worker runs them
+    (src/runtime/worker.cpp:121-142); batch 1 follows benchmarks/generate_bench.cpp:329-367.
+    `value` is timed with CUDA events on the slots' streams; `e2e` is the wall clock of the same
+    steps, which include, every step, the token ids going to the device and the logits coming back
+    for the host argmax (the reference samples on the host).  Nothing under
+    poor_mans_mamba_b200/ is imported."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("build_reference",
+                                                  os.path.join(ROOT, "baseline", "build_reference.py"))
+    builder = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(builder)
+    try:
+        binary = builder.build()
+    except RuntimeError as exc:
+        first = str(exc).strip().splitlines()
+        print(json.dumps({"impl": "reference", "unavailable": "the reference's CUDA path could not be built with "
+                          "nvcc and cuBLAS here: " + " | ".join(first[:3])[:400]}))
+        return 0
+    cfg, full_layers = sized_config(args)
+    tmp = tempfile.mkdtemp(prefix="pmm_ref_bench_")
+    atexit.register(shutil.rmtree, tmp, ignore_errors=True)
+    with open(os.path.join(tmp, "config.json"), "w") as fh:
+        json.dump(cfg, fh)
+
+    def run(batch, steps, run_prompts, prefill_len):
+        cmd = [binary, "bench", "--config", tmp, "--batch", str(batch), "--context", str(args.context),
+               "--steps", str(steps), "--warmup", str(args.warmup), "--run-prompts", "1" if run_prompts else "0",
+               "--prefill-len", str(prefill_len), "--seed", "2"]
+        proc = subprocess.run(cmd, capture_output=True, text=True, timeout=1500)
+        if proc.returncode != 0:
+            raise RuntimeError(f"ref_driver exited {proc.returncode}: {proc.stderr.strip()[-400:]}")
+        return json.loads(proc.stdout.strip().splitlines()[-1])
+
+    try:
+        with ClockSampler() as clocks:
+            main_run = run(args.batch, args.steps, True, 2048)
+        points = {}
+        if not args.no_points:
+            for b in (1, 64):
+                if b == args.batch:
+                    continue
+                # the caches of these points keep the zeros the pool starts with instead of running
+                # b prompts of ~4,000 tokens (8 s each): the decode kernels' time does not depend on values
+                points[f"decode_b{b}"] = round(run(b, min(args.steps, 32 if b == 1 else 8), False, 0)
+                                               ["decode_tok_s_device"], 1)
+    except (RuntimeError, subprocess.SubprocessError, ValueError) as exc:
+        print(json.dumps({"impl": "reference", "unavailable": f"the built reference driver failed: {exc}"[:500]}))
+        return 0
+    result = {
+        "metric": f"decode tokens/s (Falcon-H1-{args.sizes.upper()} layer sizes, random weights)",
+        "value": round(main_run["decode_tok_s_device"], 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(main_run["device_ms"] / args.steps, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp32",
+        "data": "synthetic: uniform random token ids, random-init weights made by the driver (seed 2)",
+        "config": config_record(cfg, args, full_layers), "clocks": clocks.summary(),
+        "e2e": {"value": round(main_run["decode_tok_s_e2e"], 2), "unit": "tokens/s",
+                "h2d_bytes_per_step": 4 * args.batch, "d2h_bytes_per_step": main_run["logit_bytes_d2h_per_step"]},
+        "itl_ms": {"mean": main_run["itl_mean_ms"], "p50": main_run["itl_p50_ms"], "p95": main_run["itl_p95_ms"]},
+        "prefill": {"value": round(2048 / (main_run["prefill_ms"] / 1e3), 1), "tokens": 2048,
+                    "ms": round(main_run["prefill_ms"], 3)},
+        "points": points, "impl": "reference",
+        "how": "unmodified reference CUDA path (FalconH1Runner, CUDABackend, FP32, cublasSgemm), one slot and "
+               "stream per request; host argmax over logits copied back every step",
+    }
+    print(json.dumps(result))
+    return 0
+
 
 def main() -> int:
     ap = argparse.ArgumentParser()
@@ -173,17 +269,13 @@ def main() -> int:
                          "(no CUDA graphs) between cudaProfilerStart and cudaProfilerStop; use with --layers 2")
     args = ap.parse_args()
 
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is a CMake C++ project without setup.py/pyproject.toml: pip install "
-                          "--no-index of its source tree fails ('not installable'), and its CMake build fetches "
-                          "Eigen, nlohmann_json, safetensors-cpp and tokenizers-cpp from the network"}))
-        return 0
     if args.gpus != 1:
         print(f"bench.py: this engine serves from one GPU; --gpus {args.gpus} is not supported")
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.impl == "reference":
+        return reference_arm(args)
 
     import torch
 
@@ -194,14 +286,7 @@ def main() -> int:
     from poor_mans_mamba_b200.weights import write_random_model
 
     peaks = load_peaks()
-    cfg = dict(CONFIG_05B)
-    full_layers = FULL_LAYERS
-    if args.sizes != "0.5b":
-        cfg.update(OTHER_SIZES[args.sizes][0])
-        full_layers = OTHER_SIZES[args.sizes][1]
-    if args.layers is None:
-        args.layers = full_layers
-    cfg["num_hidden_layers"] = args.layers
+    cfg, full_layers = sized_config(args)
     nums = model_numbers(cfg)
     K_steps, W = args.steps, args.warmup
     ctx_len = args.context
@@ -347,13 +432,7 @@ def main() -> int:
         "unit": "tokens/s", "n_gpus": 1, "steps": K_steps, "warmup": W, "ms_per_step": round(ms_step, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
         "data": "synthetic: uniform random token ids (seed 2), random-init weights (seed 2)",
-        "config": {"model": f"falcon-h1-{args.sizes}-sizes", "layers": args.layers, "layers_full": full_layers,
-                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
-                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
-                   "intermediate": cfg["intermediate_size"], "vocab": vocab, "d_ssm": cfg["mamba_d_ssm"],
-                   "ssm_heads": cfg["mamba_n_heads"], "d_state": cfg["mamba_d_state"], "d_conv": cfg["mamba_d_conv"],
-                   "chunk": cfg["mamba_chunk_size"], "global_batch": args.batch, "seq_len": ctx_len,
-                   "parallelism": "single-gpu", "page_size": 64, "l2": "inputs exceed L2 (no flush)"},
+        "config": config_record(cfg, args, full_layers),
         "clocks": clock_summary, "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items()},
         "gpu_launches": int(launches), "roofline": roofline, "impl": "ours",
     }

@@ -1,10 +1,10 @@
 """Writes tests/golden/plain_tiny.json: a few logits of the plain implementation on the two
 tiny random models, as a regression anchor for the oracle itself.
 
-These numbers rest on the formulas of AlterHoodie/poor_mans_mamba as restated in
-tests/plain/falcon_h1_plain.py, not on a run of that project's binaries: its CPU model
-code needs Eigen, nlohmann_json and safetensors-cpp, which its CMake build fetches from
-the network, so it cannot be compiled in this environment.
+These numbers pin the oracle against itself (both tiny configurations as they stand, with the
+gated mixer norm and the projection biases that the reference's Falcon-H1 runner does not have).
+The anchor on the reference's own binaries is reference_cuda_tiny.json, written by
+make_reference_golden.py.
 
     python tests/golden/make_golden.py
 """

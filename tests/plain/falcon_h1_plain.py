@@ -5,13 +5,15 @@ reads ``config.json`` keys from a plain dict, takes weights as a ``name -> tenso
 dict, and runs every formula directly on the CPU in one floating-point type
 (float64 by default, float32 on request).
 
-It rests on the formulas of AlterHoodie/poor_mans_mamba (file:line cited at every
-function, paths inside that project).  That project's own CPU model code cannot be
-compiled in this environment (it needs Eigen, nlohmann_json and safetensors-cpp,
-fetched from the network by its CMake build), so there is no numeric anchor from its
-binaries; where the reference leaves a case undefined (Falcon-H1 with the gated
-mixer norm, projection biases) the definition written here is the one the engine is
-held to.
+It is written from the formulas of AlterHoodie/poor_mans_mamba (file:line cited at every
+function, paths inside that project).  That project's CPU model code cannot be compiled
+offline (it needs Eigen, nlohmann_json and safetensors-cpp, fetched from the network by its
+CMake build), but its CUDA path needs only nvcc and cuBLAS: tests/golden/reference_cuda_tiny.json
+holds logits computed by that unmodified code on a B200 (tests/golden/make_reference_golden.py),
+tests/test_reference_golden.py compares this file with them on the CPU, and
+tests/test_gpu_reference_anchor.py runs the reference's binaries again on the GPU.  The
+reference's Falcon-H1 runner has neither projection biases nor the gated mixer norm; for those
+two options the definition written here is the one the engine is held to.
 """
 from __future__ import annotations
 

@@ -9,7 +9,8 @@ and the order of layers).  The parts themselves do not know this architecture.
 from __future__ import annotations
 
 from ..config.falcon_h1 import FalconH1Config
-from ..parts.base import LayerCall, LayerSpec, ModelSpec, PartSpec
+from ..parts.base import LayerCall, ModelSpec, PartSpec
+from ..parts.block import prenorm_layer
 
 
 def model_spec(cfg: FalconH1Config) -> ModelSpec:
@@ -34,8 +35,7 @@ def model_spec(cfg: FalconH1Config) -> ModelSpec:
             "intermediate_size": cfg.intermediate_size, "gate_multiplier": s.mlp[0],
             "down_multiplier": s.mlp[1],
         })
-        layers.append(LayerSpec(
-            arrangement="parallel_prenorm",
+        layers.append(prenorm_layer(
             prefix=f"model.layers.{i}.",
             mixer_norm=PartSpec("rmsnorm", "input_layernorm", dict(norm)),
             mixers=(mamba, attn),  # joined in this order: (h + mamba) + attention

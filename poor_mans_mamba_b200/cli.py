@@ -3,8 +3,13 @@
     python -m poor_mans_mamba_b200 [model_dir] [max_seq] [CPU|GPU] [n_workers] [n_prompts] [max_new_tokens]
 
 with the same positional meanings and defaults (max_seq 2048, n_workers 1, n_prompts 4,
-max_new_tokens 16).  This engine runs on one GPU: ``CPU`` and ``n_workers`` other than 1
-are refused.  The reference encodes fixed demo prompts with the model's tokenizer; here a
+max_new_tokens 16).  ``max_seq`` is what it is there: the longest context of one request; a
+request that reaches it ends with what it has.  This engine runs on one GPU: ``CPU`` and
+``n_workers`` other than 1 are refused.  The reference sizes one cache slot of max_seq tokens
+per request; here the cache is a pool of pages, sized by default for n_prompts requests of
+max_seq tokens: ``--max-tokens`` (or ``--num-pages``), ``--page-size``, ``--max-seqs`` and
+``--max-seq-len`` set the pool's capacity in tokens, the page size, the number of live requests
+and the per-request limit on their own.  The reference encodes fixed demo prompts with the model's tokenizer; here a
 ``tokenizer.json`` in the model folder is used the same way when the ``tokenizers``
 package is importable, otherwise (or with --prompt-len / --prompt-ids) prompts are token
 ids: the bos token repeated, as the reference's generate harness does
@@ -48,7 +53,14 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--prompt-ids", action="append", help="comma-separated token ids (repeatable)")
     ap.add_argument("--prompt-len", type=int, default=0, help="bos-filled prompts of this length")
     ap.add_argument("--random", metavar="CONFIG_JSON", help="write a random-weights model for this config first")
-    ap.add_argument("--max-batched-tokens", type=int, default=2048)
+    ap.add_argument("--max-batched-tokens", type=int, default=2048, help="token budget of one step")
+    ap.add_argument("--page-size", type=int, default=64, help="tokens per cache page")
+    ap.add_argument("--max-tokens", type=int, default=None,
+                    help="capacity of the key/value pool in tokens (default: max_seq x n_prompts)")
+    ap.add_argument("--num-pages", type=int, default=None, help="the same capacity given in pages")
+    ap.add_argument("--max-seqs", type=int, default=None, help="most requests alive at a time (default: n_prompts)")
+    ap.add_argument("--max-seq-len", type=int, default=None,
+                    help="longest context of one request (default: the positional max_seq)")
     args = ap.parse_args(argv)
 
     if args.device == "CPU":
@@ -60,6 +72,20 @@ def main(argv: Optional[List[str]] = None) -> int:
     if args.n_prompts <= 0 or args.max_new_tokens <= 0 or args.max_seq <= 0:
         print("n_prompts, max_new_tokens and max_seq must be > 0", file=sys.stderr)
         return 1
+    if args.max_tokens is not None and args.num_pages is not None:
+        print("give --max-tokens or --num-pages, not both", file=sys.stderr)
+        return 1
+    for name in ("page_size", "max_tokens", "num_pages", "max_seqs", "max_seq_len", "max_batched_tokens"):
+        if getattr(args, name) is not None and getattr(args, name) <= 0:
+            print(f"--{name.replace('_', '-')} must be > 0", file=sys.stderr)
+            return 1
+    max_seq_len = args.max_seq_len if args.max_seq_len is not None else args.max_seq
+    if args.num_pages is not None:
+        max_tokens = args.num_pages * args.page_size
+    elif args.max_tokens is not None:
+        max_tokens = args.max_tokens
+    else:
+        max_tokens = -(-max_seq_len // args.page_size) * args.page_size * args.n_prompts
 
     from .entry import Engine
     from .weights import write_random_model
@@ -72,8 +98,9 @@ def main(argv: Optional[List[str]] = None) -> int:
         tmp = tempfile.TemporaryDirectory()
         model_dir = write_random_model(cfg, args.seed, tmp.name)
     try:
-        eng = Engine(model_dir, dtype=args.dtype, max_tokens=args.max_seq * args.n_prompts,
-                     max_seqs=max(args.n_prompts, 1), max_batched_tokens=args.max_batched_tokens)
+        eng = Engine(model_dir, dtype=args.dtype, max_tokens=max_tokens, page_size=args.page_size,
+                     max_seqs=args.max_seqs if args.max_seqs is not None else args.n_prompts,
+                     max_batched_tokens=args.max_batched_tokens, max_seq_len=max_seq_len)
         tok = None if (args.prompt_ids or args.prompt_len) else _tokenizer(model_dir)
         prompts: List[List[int]] = []
         texts: List[Optional[str]] = []

@@ -120,7 +120,7 @@ class FalconH1Config:
             conv_bias=r.bool("mamba_conv_bias", True),
             proj_bias=r.bool("mamba_proj_bias", False),
             rms_norm=r.bool("mamba_rms_norm", False),
-            norm_before_gate=r.bool("mamba_norm_before_gate", False),
+            norm_before_gate=cls._norm_before_gate(r),
         )
         mult = Multipliers(
             embedding=r.float("embedding_multiplier", 1.0),
@@ -153,6 +153,18 @@ class FalconH1Config:
         )
         cfg.validate()
         return cfg
+
+    @staticmethod
+    def _norm_before_gate(r: KeyReader) -> bool:
+        """``mamba_norm_before_gate``.  The order of gate and norm changes the result, the
+        reference never reads the key (its gated norm is gate first, then norm,
+        src/ops/cpu_backend.cpp:286-304), and writers of configurations disagree on what an absent
+        key means.  So with the gated norm on the key must be there; with it off the key has no
+        effect and defaults to false."""
+        if r.bool("mamba_rms_norm", False) and "mamba_norm_before_gate" not in r.data:
+            raise ConfigError("config field 'mamba_norm_before_gate': required when mamba_rms_norm is true "
+                              "(false: gate, then norm, as the reference computes it; true: norm, then gate)")
+        return r.bool("mamba_norm_before_gate", False)
 
     def validate(self) -> None:
         a, m = self.attention, self.mamba

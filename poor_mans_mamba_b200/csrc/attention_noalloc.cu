@@ -3,6 +3,7 @@
 #include "attention_noalloc.h"
 #include "common.cuh"
 #include <stdio.h>
+#include <mutex>
 
 // The regular launchers (attention_mma.cu); this file only supplies their scratch.
 extern "C" int pmm_flash_supported(int Hq, int Hkv, int Dh);
@@ -24,7 +25,9 @@ static __device__ __align__(256) float g_noalloc_scratch[PMM_NOALLOC_SCRATCH_FLO
 constexpr int kMaxDevices = 64;
 // In host code g_noalloc_scratch is only a handle for the runtime, not an address a kernel
 // can use; the device address is asked for once per device and kept here.
+// Host threads may make their first calls at the same time: the table is filled under a lock.
 float* g_scratch_addr[kMaxDevices] = {};
+std::mutex g_scratch_addr_lock;
 thread_local char g_last_error[256] = "";
 
 int fail(int code, const char* fmt, long long a = 0, long long b = 0) {
@@ -39,6 +42,7 @@ int scratch_for_current_device(float** out) {
   if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices)
     return fail(PMM_ERR_NOALLOC_SETUP, "cannot tell the current device (cuda error %lld, device %lld)",
                 static_cast<long long>(e), dev);
+  std::lock_guard<std::mutex> guard(g_scratch_addr_lock);
   if (!g_scratch_addr[dev]) {
     float* p = nullptr;
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch);
@@ -59,12 +63,28 @@ PMM_EXPORT int pmm_attention_noalloc(const void* q, const void* pool, const int*
                                      int n_tiles, int rows16, int Hq, int Hkv, int Dh, cudaStream_t stream) {
   g_last_error[0] = 0;
   if (n_seq <= 0 || n_tokens <= 0 || n_tiles <= 0) return 0;
-  if (!pmm_flash_supported(Hq, Hkv, Dh) || n_splits < 1)
-    return fail(PMM_ERR_BAD_ARGUMENT, "head shape or split count outside what the kernel supports");
-  if (n_splits == 1)  // no partial results, so no scratch: the regular path allocates nothing either
-    return pmm_flash_paged_attention(q, pool, block_table, max_blocks, positions, cu, out, nullptr, nullptr,
-                                     scale, window, split_len, 1, page_size, n_seq, n_tiles, rows16 ? 16 : 64, Hq, Hkv,
-                                     Dh, nullptr, stream);
+  // Everything the two launchers would refuse is refused here, before anything is launched, so
+  // that a refused call never leaves half its work behind and always leaves a sentence.
+  const int tile_rows = rows16 ? 16 : 64;
+  if (!pmm_flash_supported(Hq, Hkv, Dh))
+    return fail(PMM_ERR_BAD_ARGUMENT, "head shape (%lld query heads of size %lld) outside what the kernel supports",
+                Hq, Dh);
+  if (Hq / Hkv > tile_rows)
+    return fail(PMM_ERR_BAD_ARGUMENT, "%lld query heads per key head do not fit a row tile of %lld", Hq / Hkv,
+                tile_rows);
+  if (n_splits < 1 || n_splits > PMM_NOALLOC_MAX_SPLITS)
+    return fail(PMM_ERR_BAD_ARGUMENT, "n_splits is %lld; 1 to %lld are supported", n_splits, PMM_NOALLOC_MAX_SPLITS);
+  if (!(scale > 0.f) || page_size <= 0 || Hkv > 65535 || (n_splits > 1 && split_len <= 0))
+    return fail(PMM_ERR_BAD_ARGUMENT, "scale, page_size and split_len must be positive (page_size %lld, split_len %lld)",
+                page_size, split_len);
+  if (!q || !pool || !block_table || !positions || !cu || !out)
+    return fail(PMM_ERR_BAD_ARGUMENT, "a null pointer among the inputs and outputs");
+  if (n_splits == 1) {  // no partial results, so no scratch: the regular path allocates nothing either
+    int rc1 = pmm_flash_paged_attention(q, pool, block_table, max_blocks, positions, cu, out, nullptr, nullptr, scale,
+                                        window, split_len, 1, page_size, n_seq, n_tiles, tile_rows, Hq, Hkv, Dh,
+                                        nullptr, stream);
+    return rc1 == 0 ? 0 : fail(rc1, "attention launch failed (code %lld)", rc1);
+  }
   const long long rows = static_cast<long long>(n_tokens) * Hq;
   const long long need = rows * n_splits * (Dh + 2);
   if (need > PMM_NOALLOC_SCRATCH_FLOATS)
@@ -77,7 +97,7 @@ PMM_EXPORT int pmm_attention_noalloc(const void* q, const void* pool, const int*
   float* part_o = scratch;
   float* part_ml = scratch + rows * n_splits * Dh;
   int rc = pmm_flash_paged_attention(q, pool, block_table, max_blocks, positions, cu, out, part_o, part_ml, scale,
-                                     window, split_len, n_splits, page_size, n_seq, n_tiles, rows16 ? 16 : 64, Hq, Hkv, Dh,
+                                     window, split_len, n_splits, page_size, n_seq, n_tiles, tile_rows, Hq, Hkv, Dh,
                                      nullptr, stream);
   if (rc != 0) return fail(rc, "attention launch failed (code %lld)", rc);
   rc = pmm_flash_combine(part_o, part_ml, out, static_cast<int>(rows), n_splits, Dh, PMM_DTYPE_BF16, stream);

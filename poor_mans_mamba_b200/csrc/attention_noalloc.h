@@ -13,8 +13,10 @@
 // GPU that loads the library, and a call needs
 //     tokens * query_heads * n_splits * (head_dim + 2)
 // of them; a larger call is refused with PMM_ERR_NOALLOC_TOO_LARGE and nothing is launched.
-// pmm_attention_noalloc_last_error() returns a sentence describing the last refusal made on
-// the calling thread.
+// The same holds for every other refusal (a head shape the kernel does not take, more than
+// PMM_NOALLOC_MAX_SPLITS key splits, a scale that is not positive, a null pointer): all checks
+// run before the first launch.  pmm_attention_noalloc_last_error() returns a sentence describing
+// the last refusal or failed launch on the calling thread.
 //
 // All calls share the one array, and it keeps whatever the last call left in it.  Nothing in
 // it has to start at zero: every (row, split) cell that the merge reads is written by the same
@@ -23,7 +25,8 @@
 // them on one stream or with events.
 //
 // The first call on each device looks up the array's device address (a one-time set-up that
-// is not a stream operation).  Make that first call outside of any stream capture.
+// is not a stream operation).  Make that first call outside of any stream capture.  Host threads
+// may call concurrently; the look-up is done under a lock.
 #pragma once
 #include <cuda_runtime.h>
 
@@ -32,6 +35,7 @@ extern "C" {
 #endif
 
 #define PMM_NOALLOC_SCRATCH_FLOATS (1 << 20)
+#define PMM_NOALLOC_MAX_SPLITS 12288  /* the merge kernel keeps one weight per split in 48 KB of shared memory */
 #define PMM_ERR_NOALLOC_TOO_LARGE 1002
 #define PMM_ERR_NOALLOC_SETUP 1003
 

@@ -23,6 +23,9 @@ class StepContext:
     launch decisions only).  ``new_lens`` / ``past_lens``: host copies per sequence.
     ``fetch_ahead``: while a layer runs, the matrices of the layer after it (set by the model;
     a layer that streams its weights once may ask the memory system for them early).
+    ``unjoined_stream``: a side stream on which a layer left work running that nothing has waited
+    for yet (a fetch-ahead beside its products); the model joins it before a layer that would not
+    (`joins_side_stream`) and at the end of the step.
     """
     n_tokens: int
     n_seq: int
@@ -40,3 +43,4 @@ class StepContext:
     new_lens: List[int] = field(default_factory=list)
     past_lens: List[int] = field(default_factory=list)
     fetch_ahead: Optional[List[Tensor]] = None
+    unjoined_stream: Optional["torch.cuda.Stream"] = None

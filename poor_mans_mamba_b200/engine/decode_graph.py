@@ -11,8 +11,10 @@ Per bucket of b sequences the index buffer (int32) holds
   tokens[b] | positions[b] | slots[b] | temperature[b] (float bits) | steps[b] | seeds[2b] (int64) | block tables
 and the constants seq_of = cu_seqlens = logit_rows = 0..b never change.  Rows beyond the
 live sequences point at the spare slot and the spare page that no request owns.  The
-split of the keys in attention is planned for the longest context the engine allows, so
-the captured launch shapes fit every step.
+split of the keys in attention is planned for a bound on the context: the smallest power of
+two (from 1,024 on, capped at the longest context the engine allows) that holds every live
+request, so a graph is captured per (batch-size bucket, context bucket) and short contexts do
+not pay for empty key ranges.
 """
 from __future__ import annotations
 
@@ -53,6 +55,7 @@ class _Bucket:
         self.sampled = torch.zeros(b, dtype=torch.int32, device=device)
         self.workspace = Workspace(device)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.kv_bound = 0  # the context bound the captured launches were planned for
         self.logits: Optional[Tensor] = None
         self.kernels_per_replay = 0
 
@@ -70,20 +73,34 @@ class GraphDecoder:
         self.bucket_sizes = sorted(set(int(b) for b in buckets if b <= cap))
         self.groups = list(self.cache.groups.values())
         self.widths = [g.blocks_for(self.max_seq_len) for g in self.groups]
-        self.buckets: Dict[int, _Bucket] = {}
+        self.buckets: Dict[Tuple[int, int], _Bucket] = {}
+        self._last: Optional[_Bucket] = None  # the bucket of the last step: its sampled ids feed the next
         self._rows: Dict[Hashable, Tuple[List[np.ndarray], List[int], int]] = {}  # request -> its block-table rows (host copies)
         self.replays = 0
         self.kernels_replayed = 0
         K.ensure_sample_scratch(self.device, max(self.bucket_sizes))  # before any step is recorded
 
     # ------------------------------------------------------------------ capture
+    _KV_BUCKET_MIN = 1024
+
+    def kv_bucket(self, kv_len: int) -> int:
+        """The context bound a step with ``kv_len`` keys in its longest request is planned for."""
+        return min(self.max_seq_len, max(self._KV_BUCKET_MIN, 1 << (max(kv_len, 1) - 1).bit_length()))
+
+    def kv_buckets(self) -> List[int]:
+        out, b = [], self._KV_BUCKET_MIN
+        while b < self.max_seq_len:
+            out.append(b)
+            b *= 2
+        return out + [self.max_seq_len]
+
     def _context(self, bk: _Bucket) -> Tuple[StepContext, Dict]:
         b, d = bk.b, bk.dev
         tables = {g.key: d[o:o + b * w].view(b, w) for g, w, o in zip(self.groups, bk.widths, bk.o_tabs)}
         ctx = StepContext(
             n_tokens=b, n_seq=b, tokens=d[bk.o_tok:bk.o_tok + b], positions=d[bk.o_pos:bk.o_pos + b],
             seq_of=bk.arange[:b], cu_seqlens=bk.arange, slots=d[bk.o_slot:bk.o_slot + b],
-            logit_rows=bk.arange[:b], n_rows=b, decode_only=True, kv_len_bound=self.max_seq_len,
+            logit_rows=bk.arange[:b], n_rows=b, decode_only=True, kv_len_bound=bk.kv_bound,
             dtype=self.runner.dtype, workspace=bk.workspace, new_lens=[1] * b, past_lens=[0] * b)
         return ctx, tables
 
@@ -109,22 +126,27 @@ class GraphDecoder:
         for g, w, o in zip(self.groups, bk.widths, bk.o_tabs):
             buf[o + start * w:o + b * w] = g.num_pages
 
-    def bucket_for(self, n: int) -> Optional[_Bucket]:
+    def bucket_for(self, n: int, kv_len: Optional[int] = None) -> Optional[_Bucket]:
+        """The captured step for ``n`` sequences whose longest context (this step's token included)
+        is ``kv_len`` (None: the longest the engine allows)."""
+        kv = self.kv_bucket(self.max_seq_len if kv_len is None else kv_len)
         for size in self.bucket_sizes:
             if size >= n:
-                if size not in self.buckets:
-                    self.buckets[size] = self._capture(size)
-                return self.buckets[size]
+                if (size, kv) not in self.buckets:
+                    self.buckets[(size, kv)] = self._capture(size, kv)
+                return self.buckets[(size, kv)]
         return None
 
     def capture_all(self) -> None:
         """Capture every bucket now, so that no step pays for a capture while serving."""
         for size in self.bucket_sizes:
-            if size not in self.buckets:
-                self.buckets[size] = self._capture(size)
+            for kv in self.kv_buckets():
+                if (size, kv) not in self.buckets:
+                    self.buckets[(size, kv)] = self._capture(size, kv)
 
-    def _capture(self, b: int) -> _Bucket:
+    def _capture(self, b: int, kv_bound: int) -> _Bucket:
         bk = _Bucket(b, self.widths, self.device)
+        bk.kv_bound = kv_bound
         host = bk.host[0].numpy()
         self._pad(bk, host, 0)
         bk.dev.copy_(bk.host[0])
@@ -176,10 +198,10 @@ class GraphDecoder:
         the id sampled for the same row by the previous call (same requests, same order).
         Returns the sampled ids [n] int32 on the device, or None if no bucket fits."""
         n = len(reqs)
-        bk = self.bucket_for(n)
+        cache = self.cache
+        bk = self.bucket_for(n, max(cache.lengths[r] for r in reqs) + 1)
         if bk is None:
             return None
-        cache = self.cache
         for r in reqs:
             new_len = cache.lengths[r] + 1
             if new_len > self.max_seq_len:
@@ -207,7 +229,9 @@ class GraphDecoder:
                 buf[o + s * w:o + (s + 1) * w] = row
         self._pad(bk, buf, n)
         if tokens is None:  # keep the device-side ids of the last step as this step's tokens
-            bk.dev[bk.o_tok:bk.o_tok + b].copy_(bk.sampled)
+            if self._last is None or self._last.b < n:
+                raise ValueError("no earlier step's ids to feed: give the tokens")
+            bk.dev[bk.o_tok:bk.o_tok + n].copy_(self._last.sampled[:n])
             bk.dev[bk.o_pos:].copy_(bk.host[i][bk.o_pos:], non_blocking=True)
             self.h2d_bytes_last = 4 * (bk.n_ints - bk.o_pos)
         else:
@@ -217,6 +241,7 @@ class GraphDecoder:
         ev.record()
         bk.events[i] = ev
         bk.graph.replay()
+        self._last = bk
         self.replays += 1
         self.kernels_replayed += bk.kernels_per_replay
         for r in reqs:
@@ -224,5 +249,7 @@ class GraphDecoder:
         return bk.sampled[:n]
 
     def last_logits(self, n: int) -> Tensor:
-        """Logits [n, V] of the last replay of the bucket that serves n sequences."""
-        return self.bucket_for(n).logits[:n]
+        """Logits [n, V] of the last replayed step (its first n rows)."""
+        if self._last is None or self._last.b < n:
+            raise ValueError("no step of that many sequences has been replayed")
+        return self._last.logits[:n]

@@ -120,13 +120,24 @@ class Model:
             # a layer that streams its weights once may fetch the next layer's ahead of time
             nxt = self.layers[order[i + 1].layer] if i + 1 < len(order) else None
             ctx.fetch_ahead = self._weights_to_fetch(nxt, h.device) if self._fetch_ahead else None
-            self.layers[call.layer].forward(stream, ctx, caches[call.cache_of])
+            layer = self.layers[call.layer]
+            if ctx.unjoined_stream is not None and not getattr(layer, "joins_side_stream", lambda c: False)(ctx):
+                self._join(ctx, h.device)
+            layer.forward(stream, ctx, caches[call.cache_of])
         ctx.fetch_ahead = None
+        self._join(ctx, h.device)
         if ctx.n_rows == 0:
             stream.flush()
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=h.device)
         normed = stream.normed(self.final_norm, rows=ctx.logit_rows)
         return self._head(normed, ctx)
+
+    @staticmethod
+    def _join(ctx: StepContext, device) -> None:
+        """Wait for what a layer left running on a side stream (so that a recorded step ends joined)."""
+        if ctx.unjoined_stream is not None:
+            torch.cuda.current_stream(device).wait_stream(ctx.unjoined_stream)
+            ctx.unjoined_stream = None
 
     def _weights_to_fetch(self, layer, device) -> Optional[List[Tensor]]:
         """The matrices of ``layer`` to request into L2 while the layer before it runs, or None.

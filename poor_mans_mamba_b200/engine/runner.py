@@ -21,6 +21,7 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..cache.pages import OutOfPages
+from ..kernels import ops as K
 from .context import StepContext
 from .model import Model
 from .workspace import Workspace, quiet_capture
@@ -137,7 +138,6 @@ class ModelRunner:
 
     def _capture_step(self, entry: dict, total: int, fill, context) -> None:
         """Record the forward pass of one step shape into a CUDA graph over buffers of its own."""
-        from ..kernels import ops as K
         meta = torch.zeros(total, dtype=torch.int32, device=self.device)
         self._staging.upload(total, fill, dev=meta)
         workspace = Workspace(self.device, initial_bytes=self.workspace.high_water + (8 << 20))
@@ -153,14 +153,18 @@ class ModelRunner:
     def kernels_launched_since(self, launch_count_before: int) -> int:
         """Own kernels launched since ``launch_count_before`` (a value of kernels.ops.launch_count),
         graph replays counted by the kernels they hold."""
-        from ..kernels import ops as K
         n = K.launch_count - launch_count_before
         return n + (self.graphs.kernels_replayed - getattr(self, "_replayed_mark", 0) if self.graphs else 0)
 
     def mark_launches(self) -> int:
-        from ..kernels import ops as K
         self._replayed_mark = self.graphs.kernels_replayed if self.graphs else 0
         return K.launch_count
+
+    def check_kernels(self, wait: bool = False) -> None:
+        """Raises KernelError if a kernel of an earlier step abandoned a bounded wait (its output
+        rows are then incomplete).  Without ``wait`` it looks at the status copy that came to the
+        host with the last step the host has waited for; with it, it waits for the device first."""
+        K.check_status(self.device, wait=wait)
 
     def length(self, req: Hashable) -> int:
         return self.cache.lengths[req]
@@ -292,6 +296,7 @@ class ModelRunner:
             ctx, block_tables = context(dev, self.workspace)
             logits = self.model.forward(ctx, cache.layer_caches(block_tables))
         self.h2d_bytes += 4 * total
+        K.status_snapshot(self.device)  # read by check_kernels once the host has waited for this step
 
         for e, n in zip(entries, new_lens):
             cache.advance(e.req, n)

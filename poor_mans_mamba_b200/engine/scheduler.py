@@ -17,14 +17,18 @@ Decisions, in order, every step:
     fails at once (status ``oom``; the reference rejects a submit when no slot is free,
     src/runtime/cluster_scheduler.cpp:262-267).
  A request ends on its eos token (kept in the output) or at max_new_tokens
- (src/runtime/cluster_scheduler.cpp:474-499).
+ (src/runtime/cluster_scheduler.cpp:474-499), or, with what it has and status ``max_seq``, when
+ its context has reached ``max_seq_len`` and the token just sampled can no longer be fed (the
+ reference: KV overflow on decode -> done with a partial result,
+ src/runtime/cluster_scheduler.cpp:645-651).  A prompt longer than ``max_seq_len`` ends at once
+ with status ``max_seq`` and no output (there the prefill fails, src/ops/cuda_backend.cu:578-579).
 The plan is deterministic given the arrival order.
 """
 from __future__ import annotations
 
 import collections
 from dataclasses import dataclass, field
-from typing import Deque, Dict, Hashable, List, Optional, Tuple
+from typing import Callable, Deque, Dict, Hashable, List, Optional, Tuple
 
 from ..cache.manager import CacheManager
 
@@ -44,7 +48,7 @@ class Request:
     params: SamplingParams
     output: List[int] = field(default_factory=list)
     n_computed: int = 0      # tokens of prompt+output whose state is in the cache
-    status: str = "waiting"  # waiting | running | done | cache_full | oom
+    status: str = "waiting"  # waiting | running | done | max_seq | cache_full | oom
     preemptions: int = 0
     admitted_at: int = -1
 
@@ -58,7 +62,7 @@ class Request:
 
     @property
     def finished(self) -> bool:
-        return self.status in ("done", "cache_full", "oom")
+        return self.status in ("done", "max_seq", "cache_full", "oom")
 
 
 @dataclass
@@ -81,10 +85,20 @@ class StepPlan:
 
 
 class Scheduler:
-    def __init__(self, cache: CacheManager, max_batched_tokens: int = 2048, max_seqs: int = 64):
+    def __init__(self, cache: CacheManager, max_batched_tokens: int = 2048, max_seqs: int = 64,
+                 max_seq_len: Optional[int] = None, release: Optional[Callable[[Hashable], None]] = None):
+        """``max_seq_len``: longest context (prompt + generated) a request may reach; a request that
+        would pass it ends with what it has (status ``max_seq``).  ``release``: called with a
+        request id to give back everything the request holds (default: the cache manager's
+        release); an engine passes its runner's `finish` so that per-request records kept beside
+        the cache go too."""
         if max_batched_tokens <= 0 or max_seqs <= 0:
             raise ValueError("max_batched_tokens and max_seqs must be positive")
+        if max_seq_len is not None and max_seq_len <= 0:
+            raise ValueError("max_seq_len must be positive")
         self.cache = cache
+        self.max_seq_len = max_seq_len
+        self._release = release if release is not None else cache.release
         self.max_batched_tokens = int(max_batched_tokens)
         self.max_seqs = min(int(max_seqs), cache.num_slots)
         self.waiting: Deque[Request] = collections.deque()
@@ -139,7 +153,7 @@ class Scheduler:
         return any(g.blocks_for(total) > g.num_pages for g in self.cache.groups.values() if g.window <= 0)
 
     def _preempt(self, req: Request, plan: StepPlan) -> None:
-        self.cache.release(req.id)
+        self._release(req.id)
         self.running.remove(req)
         req.n_computed = 0
         req.status = "waiting"
@@ -150,7 +164,7 @@ class Scheduler:
 
     def _end(self, req: Request, status: str, plan: Optional[StepPlan] = None) -> None:
         if self.cache.has(req.id):
-            self.cache.release(req.id)
+            self._release(req.id)
         if req in self.running:
             self.running.remove(req)
         if req in self.waiting:  # preempted, then found to have ended (a stop token read late)
@@ -220,6 +234,11 @@ class Scheduler:
         free_slots = self.cache.free_slots
         while self.waiting and budget > 0 and len(self.running) < self.max_seqs and free_slots > 0:
             r = self.waiting[0]
+            if self.max_seq_len is not None and len(r.prompt) + len(r.output) > self.max_seq_len:
+                self.waiting.popleft()
+                self.counters["rejects"] += 1
+                self._end(r, "max_seq", plan)
+                continue
             if self._never_fits(r):
                 self.waiting.popleft()
                 self.counters["rejects"] += 1
@@ -259,7 +278,14 @@ class Scheduler:
             if hit_eos or len(r.output) >= r.params.max_new_tokens:
                 self._end(r, "done")
                 finished.append(r)
+            elif self._at_max_seq(r):
+                self._end(r, "max_seq")
+                finished.append(r)
         return finished
+
+    def _at_max_seq(self, r: Request) -> bool:
+        """The cache holds max_seq_len tokens of this request: its next token cannot be computed."""
+        return self.max_seq_len is not None and r.n_computed >= self.max_seq_len
 
     # ------------------------------------------------------------------ results that arrive late
     # A decode step whose sampled ids are still on their way to the host can be digested in two
@@ -283,6 +309,8 @@ class Scheduler:
             r.output.append(self.PENDING)
             if len(r.output) >= r.params.max_new_tokens:
                 self._end(r, "done")
+            elif self._at_max_seq(r):
+                self._end(r, "max_seq")
         return slots
 
     def resolve(self, slots: List[Tuple[Request, int]], sampled: List[int]) -> List[Request]:
@@ -295,7 +323,7 @@ class Scheduler:
             r.output[idx] = int(tok)
             if r.params.eos_id >= 0 and int(tok) == r.params.eos_id:
                 del r.output[idx + 1:]
-                if r.status != "done":
+                if r.status != "done":  # still running, or ended by length meanwhile: the stop token decides
                     self._end(r, "done")
                 finished.append(r)
         return finished

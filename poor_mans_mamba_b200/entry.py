@@ -34,12 +34,14 @@ class Response:
 class Engine:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", device: str = "cuda:0",
                  max_tokens: int = 65536, max_seqs: int = 64, page_size: int = 64,
-                 max_batched_tokens: int = 2048, max_seq_len: int = 8192, cuda_graphs: bool = True,
+                 max_batched_tokens: int = 2048, max_seq_len: Optional[int] = None, cuda_graphs: bool = True,
                  warm_graphs: bool = False, run_ahead: bool = True):
         """``max_tokens``: capacity of the key/value cache in tokens (whole pages);
         ``max_seqs``: most requests alive at a time (= number of fixed-state slots);
-        ``max_batched_tokens``: token budget of one step; ``max_seq_len``: longest context
-        served by the CUDA-graph decode path (longer requests decode through plain launches);
+        ``max_batched_tokens``: token budget of one step; ``max_seq_len``: longest context (prompt
+        plus generated tokens) of one request, the reference's ``max_seq`` (src/main.cpp:112-129): a
+        request that reaches it ends with what it has, status ``max_seq`` (there: KV overflow ->
+        done with a partial result, src/runtime/cluster_scheduler.cpp:645-651); None: the whole pool;
         ``cuda_graphs``: capture decode-only steps into CUDA graphs (``warm_graphs``: all
         batch-size buckets at once here, else each at its first use); ``run_ahead``: launch a
         decode step before the previous one's ids have reached the host (see `step`)."""
@@ -52,12 +54,18 @@ class Engine:
                                   num_pages=max(1, max_tokens // page_size), num_slots=max_seqs,
                                   dtype=self.model.dtype, device=self.device)
         self.runner = ModelRunner(self.model, self.cache)
+        pool_tokens = max(1, max_tokens // page_size) * page_size
+        max_seq_len = pool_tokens if max_seq_len is None else min(int(max_seq_len), pool_tokens)
+        if max_seq_len <= 0:
+            raise ValueError("max_seq_len must be positive")
+        self.max_seq_len = max_seq_len
         if cuda_graphs:
             self.runner.enable_graphs(max_seq_len)
             if warm_graphs:
                 with torch.cuda.device(self.device):
                     self.runner.graphs.capture_all()
-        self.scheduler = Scheduler(self.cache, max_batched_tokens=max_batched_tokens, max_seqs=max_seqs)
+        self.scheduler = Scheduler(self.cache, max_batched_tokens=max_batched_tokens, max_seqs=max_seqs,
+                                   max_seq_len=max_seq_len, release=self.runner.finish)
         self.sampler = Sampler(self.device)
         self._next_id = 0
         self.run_ahead = run_ahead and cuda_graphs
@@ -150,6 +158,7 @@ class Engine:
             self._fetch_bufs[i] = torch.empty(max(n, 64), dtype=torch.int32, pin_memory=True)
         buf = self._fetch_bufs[i]
         buf[:n].copy_(dev_ids, non_blocking=True)
+        K.status_snapshot(self.device)  # the kernels' status words come to the host with the ids
         ev = torch.cuda.Event()
         ev.record()
         return buf, n, ev
@@ -160,6 +169,7 @@ class Engine:
         _, slots, (buf, n, ev) = self._inflight
         self._inflight = None
         ev.synchronize()
+        K.check_status(self.device)  # raises if a bounded wait inside a kernel of that step gave up
         self.scheduler.resolve(slots, buf[:n].tolist())
 
     def poll(self, rid: Hashable) -> Response:

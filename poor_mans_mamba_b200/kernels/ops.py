@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import weakref
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -135,6 +136,75 @@ def _ptr(t: Optional[Tensor]) -> Optional[int]:
 def _need(cond: bool, msg: str) -> None:
     if not cond:
         raise KernelError(msg)
+
+
+
+# ----------------------------------------------------------------------------- status of bounded waits
+class _StatusWatch:
+    """The status words of one device and their host copy.
+
+    Kernels whose threads wait on one another (mbarrier waits of the tcgen05 kernels, the grid
+    barrier of skinny_chain) bound every wait; a wait that gives up writes a code into a status
+    word, the block abandons its tile and returns, and the output of that launch is incomplete.
+    ``words[0]`` is shared by the tensor-core kernels, ``words[1]`` by the chain.  The engine
+    copies the words to pinned memory with the results it fetches anyway (`snapshot`) and looks
+    at the copy once the host has waited for that fetch (`check`)."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.words = torch.zeros(2, dtype=torch.int32, device=device)
+        self.host = torch.zeros(2, dtype=torch.int32, pin_memory=True)
+        self.counters: "weakref.WeakSet" = weakref.WeakSet()
+
+    def snapshot(self) -> None:
+        self.host.copy_(self.words, non_blocking=True)
+
+    def check(self) -> None:
+        tc, chain = int(self.host[0]), int(self.host[1])
+        if tc == 0 and chain == 0:
+            return
+        # leave the device usable: clear the words and whatever a half-finished launch left behind
+        self.words.zero_()
+        self.host.zero_()
+        for c in list(self.counters):
+            c.zero_()
+        raise KernelError(f"a bounded wait inside a kernel gave up on {self.device} (tensor-core kernels: code {tc}; "
+                          f"grid-barrier chain: code {chain}): the step's results are incomplete and were discarded")
+
+
+_WATCHES: Dict[torch.device, _StatusWatch] = {}
+
+
+def _watch(device: torch.device) -> _StatusWatch:
+    device = torch.device(device)
+    if device.index is None and device.type == "cuda":
+        device = torch.device("cuda", torch.cuda.current_device())
+    w = _WATCHES.get(device)
+    if w is None:
+        w = _StatusWatch(device)
+        _WATCHES[device] = w
+    return w
+
+
+def watch_split_counter(counter: Tensor) -> None:
+    """Registers an attention split counter (zero between launches) to be cleared when a launch
+    was abandoned half-way."""
+    _watch(counter.device).counters.add(counter)
+
+
+def status_snapshot(device) -> None:
+    """Enqueue the copy of the device's status words to pinned memory on the current stream."""
+    _watch(device).snapshot()
+
+
+def check_status(device, wait: bool = False) -> None:
+    """Raise KernelError if the last snapshot that has reached the host shows an abandoned wait.
+    ``wait``: take a snapshot now and wait for the current stream first."""
+    w = _watch(device)
+    if wait:
+        w.snapshot()
+        torch.cuda.current_stream(w.device).synchronize()
+    w.check()
 
 
 def _cuda(*tensors: Optional[Tensor]) -> None:
@@ -788,15 +858,14 @@ SKINNY_CHAIN_MAX = 4
 def _chain_state(device: torch.device) -> Tuple[Tensor, Tensor]:
     st = _CHAIN_STATE.get(device)
     if st is None:
-        st = (torch.zeros(1, dtype=torch.int64, device=device), torch.zeros(1, dtype=torch.int32, device=device))
+        st = (torch.zeros(1, dtype=torch.int64, device=device), _watch(device).words[1:2])
         _CHAIN_STATE[device] = st
     return st
 
 
 def skinny_chain_status(device) -> int:
     """0, or 1 when a barrier wait of a skinny_chain launch on this device ever gave up (synchronises)."""
-    st = _CHAIN_STATE.get(torch.device(device))
-    return 0 if st is None else int(st[1].item())
+    return int(_watch(torch.device(device)).words[1].item())
 
 
 def skinny_chain(h: Tensor, phases: Sequence[Tuple]) -> None:
@@ -850,20 +919,13 @@ def skinny_chain(h: Tensor, phases: Sequence[Tuple]) -> None:
           _stream())
 
 
-_TC_STATUS = {}
-
-
 def _tc_status(device: torch.device) -> Tensor:
-    t = _TC_STATUS.get(device)
-    if t is None:
-        t = torch.zeros(1, dtype=torch.int32, device=device)
-        _TC_STATUS[device] = t
-    return t
+    return _watch(device).words[0:1]
 
 
 def tc_gemm_status(device) -> int:
-    """0 unless a bounded wait inside a tensor-core product gave up (1 producer, 2 MMA issuer,
-    3 epilogue).  Reading it waits for the device."""
+    """0 unless a bounded wait inside a tensor-core kernel gave up (tc_gemm: 1 producer, 2 MMA
+    issuer, 3 epilogue; attention_tc: 11..15; skinny_tc: 21..24).  Reading it waits for the device."""
     return int(_tc_status(torch.device(device)).item())
 
 

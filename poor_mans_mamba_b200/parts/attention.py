@@ -78,6 +78,8 @@ class PagedAttention(Mixer):
         self.position_encoding.finalize(dtype, device)
         # tickets of the key splits (zero between steps): the last block of a tile merges them
         self._split_counter = torch.zeros(4096, dtype=torch.int32, device=device) if device.type == "cuda" else None
+        if self._split_counter is not None:
+            K.watch_split_counter(self._split_counter)  # cleared if a launch is ever abandoned half-way
 
     # -- shared input projection
     def input_rows(self) -> int:

@@ -11,7 +11,7 @@ turn the names into parts, so a new part is one ``register_*`` call away.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+from typing import Any, Callable, Dict, List, Mapping, Optional, Sequence, Tuple
 
 import torch
 
@@ -117,6 +117,12 @@ class Norm(Part):
     def forward(self, h: Tensor, pending, out: Tensor, rows: Optional[Tensor], ctx) -> None:
         raise NotImplementedError
 
+    def rms_prologue(self) -> Optional[Tuple[Tensor, float]]:
+        """(weight [D] float32, eps) if this norm is y = x / sqrt(mean(x^2) + eps) * weight, which
+        the weight-streaming products of few-token steps can apply in their prologue; None for any
+        other norm (it is then launched on its own through `forward`)."""
+        return None
+
 
 class PositionEncoding(Part):
     """Applied by a mixer to its queries and keys at absolute positions."""
@@ -174,6 +180,19 @@ class FeedForward(Part):
     def forward(self, x: Tensor, ctx, out: Tensor) -> None:
         raise NotImplementedError
 
+    # Optional path for steps of few tokens in bfloat16, where every product is a read of its
+    # weights.  An arrangement that takes that path for its mixers asks the feed-forward to do the
+    # same: ``forward_few_tokens(h, norm, ctx)`` adds out_scale * ffn(norm(h)) into the float32
+    # stream h [T, D] in place, with the operations of parts/streaming.py (norm in the prologue of
+    # the first product, the residual add in the epilogue of the last), and returns True; the
+    # default declines and the arrangement runs `forward` on the general path.
+    def forward_few_tokens(self, h: Tensor, norm: "Norm", ctx) -> bool:
+        return False
+
+    def streamed_weights(self) -> List[Tensor]:
+        """The matrices a few-token step reads once (what the layer before may fetch ahead)."""
+        return []
+
 
 # ----------------------------------------------------------------------------- specs (data)
 @dataclass(frozen=True)
@@ -186,13 +205,17 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: an arrangement of a norm, parallel mixers, and a normed feed-forward."""
+    """One layer as data: the arrangement that orders its parts, the prefix of its tensor names,
+    and the part specs under the names the arrangement defines (a PartSpec, a tuple of them, or
+    None).  ``parallel_prenorm`` reads "mixer_norm", "mixers", "ffn_norm" and "ffn"
+    (`parts.block.prenorm_layer` builds such a spec); another arrangement (post-norms, sandwich
+    norms, two feed-forwards) names its own."""
     arrangement: str
     prefix: str
-    mixer_norm: PartSpec
-    mixers: Tuple[PartSpec, ...]
-    ffn_norm: Optional[PartSpec] = None
-    ffn: Optional[PartSpec] = None
+    parts: Mapping[str, Any] = field(default_factory=dict)
+
+    def part(self, name: str, default: Any = None) -> Any:
+        return self.parts.get(name, default)
 
 
 @dataclass(frozen=True)

@@ -18,24 +18,24 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..kernels import ops as K
-from .base import (FeedForward, LayerCache, LayerSpec, Mixer, Norm, ParamSpec, Part, StateSpec,
+from . import streaming
+from .base import (FeedForward, LayerCache, LayerSpec, Mixer, Norm, ParamSpec, Part, PartSpec, StateSpec,
                    build_part, register_arrangement)
 from .norm import fold_branches
 
 Tensor = torch.Tensor
 
 
-# The products after the mixers as ONE launch with barriers over the grid (K.skinny_chain).  Off by
-# default: measured at 8 tokens a barrier costs about 3.5 us (fence, arrival, poll), a launch with
-# programmatic dependent launch about 1.2 us, so the chain takes 17.8 us where the three separate
-# launches take 10.7 us.
-_CHAINED = os.environ.get("PMM_SKINNY_CHAIN", "0") == "1"
 # The mixers of a layer on parallel streams in steps of many tokens too (PMM_PARALLEL_MIXERS=0: one
 # after the other).
 _PARALLEL_MIXERS = os.environ.get("PMM_PARALLEL_MIXERS", "1") == "1"
-# The tcgen05 form of the weight-streaming products for the larger few-token steps (PMM_TC_SKINNY=0:
-# the mma.sync form throughout).
-_TC_SKINNY = os.environ.get("PMM_TC_SKINNY", "1") == "1"
+
+
+def prenorm_layer(prefix: str, mixer_norm: PartSpec, mixers, ffn_norm: Optional[PartSpec] = None,
+                  ffn: Optional[PartSpec] = None) -> LayerSpec:
+    """The LayerSpec of a ``parallel_prenorm`` layer: norm -> parallel mixers -> norm -> feed-forward."""
+    return LayerSpec("parallel_prenorm", prefix, {"mixer_norm": mixer_norm, "mixers": tuple(mixers),
+                                                  "ffn_norm": ffn_norm, "ffn": ffn})
 
 
 class ResidualStream:
@@ -81,15 +81,19 @@ class ParallelPreNormBlock(Part):
     def __init__(self, spec: LayerSpec, hidden_size: int):
         self.prefix = spec.prefix
         self.hidden_size = hidden_size
-        self.mixer_norm: Norm = build_part("norm", spec.mixer_norm, width=hidden_size)
-        self.mixers: List[Mixer] = [build_part("mixer", m, hidden_size=hidden_size) for m in spec.mixers]
+        unknown = set(spec.parts) - {"mixer_norm", "mixers", "ffn_norm", "ffn"}
+        if unknown or spec.part("mixer_norm") is None or not spec.part("mixers"):
+            raise ValueError("parallel_prenorm takes the parts mixer_norm, mixers (at least one), ffn_norm and ffn"
+                             + (f"; got also {sorted(unknown)}" if unknown else ""))
+        self.mixer_norm: Norm = build_part("norm", spec.part("mixer_norm"), width=hidden_size)
+        self.mixers: List[Mixer] = [build_part("mixer", m, hidden_size=hidden_size) for m in spec.part("mixers")]
         self.ffn_norm: Optional[Norm] = None
         self.ffn: Optional[FeedForward] = None
-        if spec.ffn is not None:
-            if spec.ffn_norm is None:
+        if spec.part("ffn") is not None:
+            if spec.part("ffn_norm") is None:
                 raise ValueError("a feed-forward needs its norm")
-            self.ffn_norm = build_part("norm", spec.ffn_norm, width=hidden_size)
-            self.ffn = build_part("feed_forward", spec.ffn, hidden_size=hidden_size)
+            self.ffn_norm = build_part("norm", spec.part("ffn_norm"), width=hidden_size)
+            self.ffn = build_part("feed_forward", spec.part("ffn"), hidden_size=hidden_size)
         self._fused_in: Optional[Tensor] = None
         self._fused_cols: List[Tuple[int, int]] = []
 
@@ -122,22 +126,15 @@ class ParallelPreNormBlock(Part):
 
     def _few_tokens_path(self, ctx) -> bool:
         """Steps of few tokens in bfloat16 are reads of the weights: they take the fused
-        weight-streaming products (norm in the prologue, SwiGLU or the residual add in the
-        epilogue) instead of library products with separate element-wise launches."""
-        from .ffn import SwiGLU
-        from .norm import RMSNorm
-        if (ctx.dtype != torch.bfloat16 or ctx.n_tokens > K.SKINNY_MAX_TOKENS or self.hidden_size % 8
-                or not K.skinny_fits(ctx.n_tokens, self.hidden_size)):
-            return False
-        if self._fused_in is None or not isinstance(self.mixer_norm, RMSNorm):
+        weight-streaming products (norm in the prologue, the residual add in the epilogue) instead
+        of library products with separate element-wise launches.  Needs mixers that share one
+        input projection and expose their output projections; any norm and any feed-forward do
+        (a feed-forward without a few-token path of its own runs its general `forward`)."""
+        if not streaming.eligible(ctx, self.hidden_size) or self._fused_in is None:
             return False
         if any(m.output_weight() is None or m.output_bias() is not None for m in self.mixers):
             return False
-        if len(self.mixers) > 2:
-            return False
-        if self.ffn is not None and not (isinstance(self.ffn, SwiGLU) and isinstance(self.ffn_norm, RMSNorm)):
-            return False
-        return True
+        return len(self.mixers) <= 2
 
     _SIDE_STREAMS: Dict[torch.device, "torch.cuda.Stream"] = {}
 
@@ -154,7 +151,7 @@ class ParallelPreNormBlock(Part):
         ask the memory system to fetch ahead."""
         ws = [self._fused_in] + [m.output_weight() for m in self.mixers]
         if self.ffn is not None:
-            ws += [getattr(self.ffn, "gate_up", None), getattr(self.ffn, "down", None)]
+            ws += list(self.ffn.streamed_weights())
         return [w for w in ws if w is not None]
 
     def _forward_few_tokens(self, stream: ResidualStream, ctx, cache: LayerCache) -> None:
@@ -168,23 +165,13 @@ class ParallelPreNormBlock(Part):
         if ahead and side is None:
             K.l2_prefetch(ahead)
         proj = ws.alloc((T, self._fused_in.shape[0]), ctx.dtype)
-        fused_norm = T <= K.SKINNY_NORM_MAX_TOKENS and self.hidden_size <= K.SKINNY_NORM_MAX_WIDTH
-        # beyond 32 tokens the tcgen05 form of the products is the faster one (where it takes the sizes)
-        tensor_core = _TC_SKINNY and T >= K.SKINNY_TC_FROM_TOKENS
-        if fused_norm:
-            K.skinny_linear_norm(h, self.mixer_norm.weight, self.mixer_norm.eps, self._fused_in, proj)
-        else:
-            x = ws.alloc((T, self.hidden_size), ctx.dtype)
-            K.add_rmsnorm(h, [], self.mixer_norm.weight, self.mixer_norm.eps, x)
-            if tensor_core and K.skinny_tc_supported("store", x, self._fused_in, proj):
-                K.skinny_tc_linear(x, self._fused_in, proj)
-            else:
-                K.skinny_linear(x, self._fused_in, proj)
+        streaming.normed_linear(h, self.mixer_norm, self._fused_in, proj, ctx)
         # The mixers only share their input: the first runs on a side stream beside the others
         # (in a captured step the two become parallel branches of the graph).
         products = [None] * len(self.mixers)
         if side is not None:
             side.wait_stream(main)
+            ctx.unjoined_stream = None  # what an earlier layer left on the side stream is joined below
             with torch.cuda.stream(side):
                 m, (c0, c1) = self.mixers[0], self._fused_cols[0]
                 products[0] = (m.pre_output(proj[:, c0:c1], ctx, cache), m.output_weight(), m.out_scale)
@@ -200,35 +187,20 @@ class ParallelPreNormBlock(Part):
                 side.wait_stream(main)
                 with torch.cuda.stream(side):
                     K.l2_prefetch(ahead)
+                ctx.unjoined_stream = side  # joined by the next layer's mixers, or by the model
         # h = (h + s0 * y0 W0^T) + s1 * y1 W1^T in one launch, then the feed-forward
-        act = ws.alloc((T, self.ffn.intermediate_size), ctx.dtype) if self.ffn is not None else None
-        if _CHAINED:
-            phases = [("residual", products)]
-            if self.ffn is not None:
-                phases += [("swiglu", self.ffn_norm.weight, self.ffn_norm.eps, self.ffn.gate_up,
-                            self.ffn.gate_multiplier, act),
-                           ("residual", [(act, self.ffn.down, self.ffn.out_scale)])]
-            K.skinny_chain(h, phases)
-        else:
-            def add_products(prods):
-                if tensor_core and all(K.skinny_tc_supported("residual", px, pw) for px, pw, _ in prods):
-                    K.skinny_tc_residual(h, prods)
-                else:
-                    K.skinny_residual(h, prods)
-
-            add_products(products)
-            if self.ffn is not None:
-                if fused_norm:
-                    K.skinny_swiglu_norm(h, self.ffn_norm.weight, self.ffn_norm.eps, self.ffn.gate_up,
-                                         self.ffn.gate_multiplier, act)
-                else:
-                    K.add_rmsnorm(h, [], self.ffn_norm.weight, self.ffn_norm.eps, x)
-                    if tensor_core and K.skinny_tc_supported("swiglu", x, self.ffn.gate_up, act):
-                        K.skinny_tc_swiglu(x, self.ffn.gate_up, self.ffn.gate_multiplier, act)
-                    else:
-                        K.skinny_swiglu(x, self.ffn.gate_up, self.ffn.gate_multiplier, act)
-                add_products([(act, self.ffn.down, self.ffn.out_scale)])
+        streaming.add_products(h, products, ctx)
+        if self.ffn is not None and not self.ffn.forward_few_tokens(h, self.ffn_norm, ctx):
+            f = stream.normed(self.ffn_norm)   # a feed-forward without a few-token path of its own
+            out = stream.take_branch()
+            self.ffn.forward(f, ctx, out)
+            stream.add(out, self.ffn.out_scale)
         ws.release(mark)
+
+    def joins_side_stream(self, ctx) -> bool:
+        """Whether this layer's own fork and join of its mixers will wait for what an earlier
+        layer left running on the side stream (``ctx.unjoined_stream``)."""
+        return len(self.mixers) > 1 and self._few_tokens_path(ctx)
 
     def forward(self, stream: ResidualStream, ctx, cache: LayerCache) -> None:
         if self._few_tokens_path(ctx):

@@ -13,6 +13,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..kernels import ops as K
+from . import streaming
 from .base import FeedForward, ParamSpec, register_feed_forward
 
 Tensor = torch.Tensor
@@ -59,6 +60,19 @@ class SwiGLU(FeedForward):
             K.linear(x, self.gate_up, gu)
             K.silu_mul(gu, self.gate_multiplier, act)
         K.linear(act, self.down, out)
+
+    def forward_few_tokens(self, h: Tensor, norm, ctx) -> bool:
+        """h += down_multiplier * (silu(g) * u) Wd^T with [g | u] = norm(h) [Wg; Wu]^T in two
+        weight-streaming launches."""
+        if not streaming.eligible(ctx, self.hidden_size):
+            return False
+        act = ctx.workspace.alloc((h.shape[0], self.intermediate_size), ctx.dtype)
+        streaming.normed_swiglu(h, norm, self.gate_up, self.gate_multiplier, act, ctx)
+        streaming.add_products(h, [(act, self.down, self.out_scale)], ctx)
+        return True
+
+    def streamed_weights(self) -> List[Tensor]:
+        return [self.gate_up, self.down]
 
 
 register_feed_forward("swiglu", SwiGLU)

@@ -35,6 +35,9 @@ class RMSNorm(Norm):
     def bind(self, params: Dict[str, Tensor]) -> None:
         self.weight = params["weight"]
 
+    def rms_prologue(self):
+        return self.weight, self.eps
+
     def forward(self, h: Tensor, pending, out: Tensor, rows: Optional[Tensor], ctx) -> None:
         items = list(pending)
         while len(items) > 2:  # more than two branches: fold the surplus first

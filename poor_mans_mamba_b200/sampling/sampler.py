@@ -48,8 +48,15 @@ class Sampler:
         """Device token ids -> python ints through a pinned buffer (waits for the step)."""
         n = ids.numel()
         _, host = self._buffers(n)
-        host.copy_(ids, non_blocking=False)
+        self._fetch(host, ids)
         return host.tolist()
+
+    def _fetch(self, host: torch.Tensor, ids: torch.Tensor) -> None:
+        """Blocking copy of the ids; the kernels' status words travel with them and a step in
+        which a bounded wait gave up raises here instead of handing out its tokens."""
+        K.status_snapshot(self.device)
+        host.copy_(ids, non_blocking=False)
+        K.check_status(self.device)
 
     def sample(self, logits: torch.Tensor, temperatures: Optional[Sequence[float]] = None,
                seeds: Optional[Sequence[int]] = None, steps: Optional[Sequence[int]] = None) -> List[int]:
@@ -58,5 +65,5 @@ class Sampler:
             return []
         out = self.sample_device(logits, temperatures, seeds, steps)
         _, host = self._buffers(n)
-        host.copy_(out, non_blocking=False)
+        self._fetch(host, out)
         return host.tolist()

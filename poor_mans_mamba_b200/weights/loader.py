@@ -2,9 +2,13 @@
 
 Every tensor the model's parts declare is looked up by its full name; the file's shapes
 are checked against the configuration before anything is copied, and one error lists
-everything that is wrong: missing tensors, tensors nobody asked for, wrong shapes and
-unusable dtypes (the reference reports only the first missing name,
+everything that is wrong: missing tensors, wrong shapes and unusable dtypes, and beside them
+the tensors nobody asked for (the reference reports only the first missing name,
 src/io/model_loader.cpp:43-45, and checks shapes per call, src/ops/cpu_backend.cpp:98-105).
+Tensors nobody asked for are not an error by themselves: the reference loads by name and never
+looks at the rest (src/model/falconh1_loader.cpp:27-58), so an exporter's extra buffers, or a
+tied checkpoint that still carries its output head, load with their names listed on stderr;
+``strict=True`` refuses them.
 
 Types on the device: matrices and embeddings keep bfloat16 in the bfloat16 mode (a
 float32-stored matrix is rounded once, with a note on stderr) and are widened to float32
@@ -46,7 +50,10 @@ class WeightsError(ValueError):
         super().__init__("\n".join(lines))
 
 
-def check_tensors(specs: Dict[str, ParamSpec], ignored: List[str], files: ModelFiles) -> None:
+def check_tensors(specs: Dict[str, ParamSpec], ignored: List[str], files: ModelFiles,
+                  strict: bool = False) -> List[str]:
+    """Raises one WeightsError for everything that is wrong; returns the names of tensors that
+    nobody asked for (an error only with ``strict``)."""
     present = set(files.keys())
     missing = sorted(n for n in specs if n not in present)
     unexpected = sorted(n for n in present if n not in specs and n not in set(ignored))
@@ -60,19 +67,24 @@ def check_tensors(specs: Dict[str, ParamSpec], ignored: List[str], files: ModelF
         ok = dt in _INT_NAMES if spec.kind == "table" else dt in _FLOAT_NAMES
         if not ok:
             wrong_dtype.append((name, dt))
-    if missing or unexpected or wrong_shape or wrong_dtype:
+    if missing or wrong_shape or wrong_dtype or (strict and unexpected):
         raise WeightsError(missing, unexpected, wrong_shape, wrong_dtype)
+    return unexpected
 
 
 def load_tensors(model_dir: str, specs: Dict[str, ParamSpec], ignored: List[str],
-                 dtype: torch.dtype, device: torch.device) -> Dict[str, torch.Tensor]:
+                 dtype: torch.dtype, device: torch.device, strict: bool = False) -> Dict[str, torch.Tensor]:
     """name -> tensor on ``device`` in the policy type of its spec, shaped as the spec says."""
     try:
         files = ModelFiles(model_dir)
     except SafetensorsError as exc:
         raise WeightsError([f"(no readable weights: {exc})"], [], [], []) from exc
     try:
-        check_tensors(specs, ignored, files)
+        unexpected = check_tensors(specs, ignored, files, strict)
+        if unexpected:
+            shown = ", ".join(unexpected[:20]) + (f", ... ({len(unexpected) - 20} more)" if len(unexpected) > 20 else "")
+            print(f"[poor_mans_mamba_b200] note: {len(unexpected)} tensors of the model folder are not used by "
+                  f"this configuration and were ignored: {shown}", file=sys.stderr)
         out: Dict[str, torch.Tensor] = {}
         rounded = 0
         for name, spec in specs.items():

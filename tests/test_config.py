@@ -107,10 +107,12 @@ def test_model_spec_is_data_taken_from_the_config():
     assert len(spec.layers) == 3 and [c.layer for c in spec.order] == [0, 1, 2]
     assert spec.head_name == "lm_head.weight" and spec.head_multiplier == 0.5
     layer = spec.layers[1]
-    assert layer.prefix == "model.layers.1." and [m.kind for m in layer.mixers] == ["mamba2", "paged_attention"]
-    assert layer.mixers[0].params["chunk_multipliers"] == (0.5, 1.1, 0.9, 1.3, 0.7)
-    assert layer.mixers[1].params["position_encoding"] == {"kind": "rotary", "theta": 1e11}
-    assert layer.mixer_norm.params["eps"] == 1e-6
+    mixers = layer.part("mixers")
+    assert layer.arrangement == "parallel_prenorm" and set(layer.parts) == {"mixer_norm", "mixers", "ffn_norm", "ffn"}
+    assert layer.prefix == "model.layers.1." and [m.kind for m in mixers] == ["mamba2", "paged_attention"]
+    assert mixers[0].params["chunk_multipliers"] == (0.5, 1.1, 0.9, 1.3, 0.7)
+    assert mixers[1].params["position_encoding"] == {"kind": "rotary", "theta": 1e11}
+    assert layer.part("mixer_norm").params["eps"] == 1e-6 and layer.part("ffn").kind == "swiglu"
     assert model_spec(FalconH1Config.from_dict(tiny_config("A"))).head_name is None
 
 
@@ -127,3 +129,18 @@ def test_parts_are_built_from_specs_by_name():
     assert shared.state_specs() == [] and [p.name for p in shared.param_specs()] == ["q_proj.weight", "o_proj.weight"]
     with pytest.raises(KeyError, match="unknown mixer"):
         build_part("mixer", PartSpec("nope", "x", {}), hidden_size=8)
+
+
+def test_gate_and_norm_order_must_be_stated_when_the_gated_norm_is_on():
+    from poor_mans_mamba_b200.config import ConfigError
+    from poor_mans_mamba_b200.config.falcon_h1 import FalconH1Config
+    from tiny_configs import tiny_config
+    a = tiny_config("A")            # gated norm on
+    del a["mamba_norm_before_gate"]
+    with pytest.raises(ConfigError, match="mamba_norm_before_gate"):
+        FalconH1Config.from_dict(a)
+    a["mamba_norm_before_gate"] = True
+    assert FalconH1Config.from_dict(a).mamba.norm_before_gate is True
+    b = tiny_config("B")            # gated norm off: the key has no effect and may be absent
+    del b["mamba_norm_before_gate"]
+    assert FalconH1Config.from_dict(b).mamba.norm_before_gate is False

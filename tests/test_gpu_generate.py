@@ -104,6 +104,15 @@ def test_command_line(case):
     assert proc.returncode == 0, proc.stderr[-2000:]
     lines = [l for l in proc.stdout.splitlines() if l.startswith("req_id=")]
     assert len(lines) == 2 and all(f"tokens={want}" in l for l in lines), proc.stdout
+    # the cache geometry from the command line: a pool of 4 pages of 16 tokens, one request alive at
+    # a time, at most 6 tokens of context each (3 prompt tokens + 3 fed back: 4 tokens come out)
+    proc = subprocess.run([sys.executable, "-m", "poor_mans_mamba_b200", d, "256", "GPU", "1", "2", "5",
+                           "--dtype", "float32", "--prompt-ids", "5,9,2", "--page-size", "16", "--num-pages", "4",
+                           "--max-seqs", "1", "--max-seq-len", "6", "--max-batched-tokens", "2"], cwd=ROOT,
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [l for l in proc.stdout.splitlines() if l.startswith("req_id=")]
+    assert len(lines) == 2 and all(f"status=max_seq tokens={want[:4]}" in l for l in lines), proc.stdout
     bad = subprocess.run([sys.executable, "-m", "poor_mans_mamba_b200", d, "256", "CPU"], cwd=ROOT,
                          capture_output=True, text=True, timeout=120)
     assert bad.returncode == 1 and "no CPU path" in bad.stderr
@@ -150,3 +159,59 @@ def test_decoding_one_step_ahead_gives_the_same_tokens(case, dtype):
     assert run(True, with_stop)[0] == run(False, with_stop)[0]
     sampled = [SamplingParams(max_new_tokens=n, eos_id=-1, temperature=0.8, seed=5 + i) for i, n in enumerate(lens)]
     assert run(True, sampled)[0] == run(False, sampled)[0]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_max_seq_len_ends_a_request_in_the_middle_of_decoding(case, dtype):
+    """One of three requests reaches max_seq_len while the engine runs a step ahead of the host: it
+    ends with what it has (status max_seq), the others go on, the tokens equal the step-by-step
+    engine's, and nothing the graph decoder kept for a request outlives it."""
+    from poor_mans_mamba_b200.engine.scheduler import SamplingParams
+    from poor_mans_mamba_b200.entry import Engine
+    which, d, cfg, weights = case
+    prompts, _ = prompts_of(which)
+    prompts = prompts[-3:]
+    limit = len(prompts[-1]) + 9   # the longest prompt may be fed 9 of its own tokens
+
+    def run(run_ahead):
+        eng = Engine(d, dtype=dtype, max_tokens=2048, max_seqs=4, page_size=16, run_ahead=run_ahead, max_seq_len=limit)
+        ids = [eng.submit(p, SamplingParams(max_new_tokens=20, eos_id=-1)) for p in prompts]
+        while eng.has_work():
+            eng.step()
+        out = [eng.poll(i) for i in ids]
+        assert eng.cache.free_slots == 4
+        if eng.runner.graphs is not None:
+            assert len(eng.runner.graphs._rows) == 0
+        return [(r.tokens, r.status) for r in out], eng
+
+    base, _ = run(False)
+    ahead, eng = run(True)
+    assert ahead == base and eng.runner.graphs.replays > 0
+    assert base[-1][1] == "max_seq" and len(base[-1][0]) == 10   # 9 fed back, the 10th sampled at the last place
+    assert all(s == "done" and len(t) == 20 for t, s in base[:-1])
+    if dtype == "float32":
+        want = greedy_generate(prompts[-1], 10, weights, cfg)
+        assert base[-1][0] == want
+    too_long = eng.submit(list(range(1, limit + 2)))
+    while eng.has_work():
+        eng.step()
+    assert eng.poll(too_long).status == "max_seq" and eng.poll(too_long).tokens == []
+
+
+def test_an_abandoned_wait_inside_a_kernel_is_reported(case):
+    """Kernels with bounded waits record a code in a status word when a wait gives up.  The word is
+    set from the host here (no kernel is made to wait): the next result the host fetches raises,
+    the word is cleared, and the engine serves on."""
+    from poor_mans_mamba_b200.entry import Engine
+    from poor_mans_mamba_b200.kernels import ops as K
+    which, d, cfg, weights = case
+    prompts, _ = prompts_of(which)
+    for run_ahead in (False, True):
+        eng = Engine(d, dtype="bfloat16", max_tokens=1024, max_seqs=4, page_size=16, run_ahead=run_ahead)
+        good = eng.generate(prompts[:2], max_new_tokens=6, eos_token_id=-1)
+        K._watch(eng.device).words[0] = 13
+        with pytest.raises(K.KernelError, match="code 13"):
+            eng.generate(prompts[:2], max_new_tokens=6, eos_token_id=-1)
+        assert K.tc_gemm_status(eng.device) == 0
+        eng2 = Engine(d, dtype="bfloat16", max_tokens=1024, max_seqs=4, page_size=16, run_ahead=run_ahead)
+        assert eng2.generate(prompts[:2], max_new_tokens=6, eos_token_id=-1) == good

@@ -37,9 +37,9 @@ def _random_tensors(model, seed, dtype, scale=None):
 
 def _single_layer_model(mixers, ffn=None, hidden=48, vocab=50, order=None, n_layers=1, layer_specs=None):
     from poor_mans_mamba_b200.engine.model import Model
-    from poor_mans_mamba_b200.parts import LayerCall, LayerSpec, ModelSpec, PartSpec
+    from poor_mans_mamba_b200.parts import LayerCall, ModelSpec, PartSpec, prenorm_layer
     norm = PartSpec("rmsnorm", "norm1", {"eps": 1e-5})
-    layers = layer_specs or [LayerSpec("parallel_prenorm", f"layers.{i}.", norm, tuple(mixers),
+    layers = layer_specs or [prenorm_layer(f"layers.{i}.", norm, tuple(mixers),
                                        PartSpec("rmsnorm", "norm2", {"eps": 1e-5}) if ffn else None, ffn)
                              for i in range(n_layers)]
     spec = ModelSpec(hidden_size=hidden, vocab_size=vocab, embedding_name="embed.weight", embedding_multiplier=1.0,
@@ -315,16 +315,16 @@ class Top1RoutedFeedForward:
 
 def test_toy_routed_feed_forward_in_one_layer_and_a_dense_one_in_the_next():
     """Feed-forwards are chosen layer by layer: a routed toy in layer 0, the dense SwiGLU in layer 1."""
-    from poor_mans_mamba_b200.parts import LayerSpec, PartSpec, register_feed_forward, registered
+    from poor_mans_mamba_b200.parts import PartSpec, prenorm_layer, register_feed_forward, registered
     register_feed_forward("test_top1_routed", Top1RoutedFeedForward)
     assert "test_top1_routed" in registered("feed_forward")
     dtype = torch.float32
     attn = PartSpec("paged_attention", "attn", {"num_heads": 3, "num_kv_heads": 1, "head_dim": 16,
                                                 "position_encoding": {"kind": "rotary", "theta": 100.0}})
     norm1, norm2 = PartSpec("rmsnorm", "norm1", {"eps": 1e-5}), PartSpec("rmsnorm", "norm2", {"eps": 1e-5})
-    layers = [LayerSpec("parallel_prenorm", "layers.0.", norm1, (attn,), norm2,
+    layers = [prenorm_layer("layers.0.", norm1, (attn,), norm2,
                         PartSpec("test_top1_routed", "moe", {"experts": 3, "width": 24})),
-              LayerSpec("parallel_prenorm", "layers.1.", norm1, (attn,), norm2,
+              prenorm_layer("layers.1.", norm1, (attn,), norm2,
                         PartSpec("swiglu", "ff", {"intermediate_size": 40}))]
     model = _single_layer_model(None, layer_specs=layers)
     names = set(model.param_specs())
@@ -366,13 +366,13 @@ def test_toy_routed_feed_forward_in_one_layer_and_a_dense_one_in_the_next():
 
 def test_order_may_run_a_layer_twice_and_share_a_cache():
     """Order [L0 on cache 0, L1 reading cache 0's keys/values, L0 again on cache 2]."""
-    from poor_mans_mamba_b200.parts import LayerCall, LayerSpec, PartSpec
+    from poor_mans_mamba_b200.parts import LayerCall, PartSpec, prenorm_layer
     dtype = torch.float32
     rot = {"kind": "rotary", "theta": 100.0}
     attn = {"num_heads": 4, "num_kv_heads": 2, "head_dim": 16, "position_encoding": rot}
     n1 = PartSpec("rmsnorm", "norm1", {"eps": 1e-5})
-    l0 = LayerSpec("parallel_prenorm", "layers.0.", n1, (PartSpec("paged_attention", "attn", attn),))
-    l1 = LayerSpec("parallel_prenorm", "layers.1.", n1,
+    l0 = prenorm_layer("layers.0.", n1, (PartSpec("paged_attention", "attn", attn),))
+    l1 = prenorm_layer("layers.1.", n1,
                    (PartSpec("paged_attention", "attn", dict(attn, shared_kv=True)),))
     model = _single_layer_model(None, layer_specs=[l0, l1],
                                 order=[LayerCall(0, 0), LayerCall(1, 0), LayerCall(0, 2)])
@@ -411,13 +411,13 @@ def test_order_may_run_a_layer_twice_and_share_a_cache():
 def test_sliding_window_layers_give_pages_back(dtype, tmp_path):
     """A model whose second layer attends to a window: its pages are of a group of their own
     and return to the pool while the sequence goes on; logits match a windowed plain model."""
-    from poor_mans_mamba_b200.parts import LayerSpec, PartSpec
+    from poor_mans_mamba_b200.parts import PartSpec, prenorm_layer
     tdt = torch.float32 if dtype == "float32" else torch.bfloat16
     rot = {"kind": "rotary", "theta": 1000.0}
     base = {"num_heads": 4, "num_kv_heads": 2, "head_dim": 16, "position_encoding": rot}
     n1 = PartSpec("rmsnorm", "norm1", {"eps": 1e-5})
-    layers = [LayerSpec("parallel_prenorm", "layers.0.", n1, (PartSpec("paged_attention", "attn", base),)),
-              LayerSpec("parallel_prenorm", "layers.1.", n1, (PartSpec("paged_attention", "attn", dict(base, window=20)),))]
+    layers = [prenorm_layer("layers.0.", n1, (PartSpec("paged_attention", "attn", base),)),
+              prenorm_layer("layers.1.", n1, (PartSpec("paged_attention", "attn", dict(base, window=20)),))]
     model = _single_layer_model(None, layer_specs=layers)
     dev, w = _random_tensors(model, 9, tdt, scale=8.0)
     model.bind(dev, tdt, DEV)
@@ -450,3 +450,193 @@ def test_sliding_window_layers_give_pages_back(dtype, tmp_path):
     win = runner.cache.groups[(2, 32, 20)]
     assert win.pool.n_held <= 3 and runner.cache.groups[(2, 32, 0)].pool.n_held == 6
     H.check_rows(torch.cat(rows), ref, dtype, "windowed layers")
+
+
+# ----------------------------------------------------------------------------- another arrangement, another feed-forward
+def _squared_relu_feed_forward(*a, **k):
+    """out = relu(x W1^T)^2 W2^T: not SwiGLU, with a few-token path of its own built from the
+    weight-streaming operations that the framework offers to parts."""
+    from poor_mans_mamba_b200.kernels import ops as K
+    from poor_mans_mamba_b200.parts import FeedForward, ParamSpec, streaming
+
+    class _Impl(FeedForward):
+        def __init__(self, hidden_size, width, out_multiplier=1.0):
+            self.hidden_size, self.width, self.out_scale = hidden_size, width, float(out_multiplier)
+
+        def param_specs(self):
+            return [ParamSpec("w1.weight", (self.width, self.hidden_size)),
+                    ParamSpec("w2.weight", (self.hidden_size, self.width))]
+
+        def bind(self, params):
+            self.w1, self.w2 = params["w1.weight"].contiguous(), params["w2.weight"].contiguous()
+
+        def forward(self, x, ctx, out):
+            mid = ctx.workspace.alloc((x.shape[0], self.width), x.dtype)
+            K.linear(x, self.w1, mid)
+            mid.copy_(torch.relu(mid.float()).square().to(mid.dtype))
+            K.linear(mid, self.w2, out)
+
+        def forward_few_tokens(self, h, norm, ctx):
+            if not streaming.eligible(ctx, self.hidden_size):
+                return False
+            _squared_relu_feed_forward.few_token_calls += 1
+            mid = ctx.workspace.alloc((h.shape[0], self.width), ctx.dtype)
+            streaming.normed_linear(h, norm, self.w1, mid, ctx)
+            mid.copy_(torch.relu(mid.float()).square().to(mid.dtype))
+            streaming.add_products(h, [(mid, self.w2, self.out_scale)], ctx)
+            return True
+
+        def streamed_weights(self):
+            return [self.w1, self.w2]
+
+    return _Impl(*a, **k)
+
+
+_squared_relu_feed_forward.few_token_calls = 0
+
+
+def _centered_norm(*a, **k):
+    """y = (x - mean) / sqrt(var + eps) * w: a norm the streaming products cannot take into their
+    prologue (rms_prologue stays None), so it is launched on its own."""
+    from poor_mans_mamba_b200.parts import Norm, ParamSpec
+    from poor_mans_mamba_b200.parts.norm import fold_branches
+
+    class _Impl(Norm):
+        def __init__(self, width, eps):
+            self.width, self.eps = width, eps
+
+        def param_specs(self):
+            return [ParamSpec("weight", (self.width,), kind="vector", init=("ones",))]
+
+        def bind(self, params):
+            self.weight = params["weight"]
+
+        def forward(self, h, pending, out, rows, ctx):
+            if rows is None:
+                fold_branches(h, pending)
+                x = h
+            else:
+                x = h.index_select(0, rows.long())
+                for branch, scale in pending:
+                    x = x + scale * branch.index_select(0, rows.long()).float()
+            c = x - x.mean(-1, keepdim=True)
+            out.copy_((c * torch.rsqrt(c.square().mean(-1, keepdim=True) + self.eps) * self.weight).to(out.dtype))
+
+    return _Impl(*a, **k)
+
+
+def _plain_centered_norm(x, w, eps):
+    c = x - x.mean(-1, keepdim=True)
+    return c / torch.sqrt(c.square().mean(-1, keepdim=True) + eps) * w
+
+
+def test_another_feed_forward_and_norm_take_the_few_token_path():
+    """A feed-forward that is not SwiGLU, behind a norm that is not RMSNorm, in a layer of two
+    parallel attention mixers: bfloat16 decode steps run it through its own few-token path (the
+    arrangement asks the part, it does not test for a class), prompt portions through `forward`."""
+    from poor_mans_mamba_b200.engine import StepEntry
+    from poor_mans_mamba_b200.parts import PartSpec, prenorm_layer, register_feed_forward, register_norm
+    register_feed_forward("test_squared_relu", _squared_relu_feed_forward)
+    register_norm("test_centered", _centered_norm)
+    dtype = torch.bfloat16
+    attn = {"num_heads": 2, "num_kv_heads": 1, "head_dim": 32, "position_encoding": {"kind": "rotary", "theta": 100.0}}
+    layers = [prenorm_layer(f"layers.{i}.", PartSpec("rmsnorm", "norm1", {"eps": 1e-5}),
+                            (PartSpec("paged_attention", "attn_a", attn), PartSpec("paged_attention", "attn_b", attn)),
+                            PartSpec("test_centered", "norm2", {"eps": 1e-4}),
+                            PartSpec("test_squared_relu", "ff", {"width": 72, "out_multiplier": 0.5}))
+              for i in range(2)]
+    model = _single_layer_model(None, hidden=64, layer_specs=layers)
+    dev, w = _random_tensors(model, 21, dtype, scale=6.0)
+    model.bind(dev, dtype, DEV)
+    w64 = {k: v.double() for k, v in w.items()}
+    cfg = {"num_attention_heads": 2, "num_key_value_heads": 1, "head_dim": 32, "rope_theta": 100.0}
+
+    def layer(h, i):
+        pre = f"layers.{i}."
+        n = P.rms_norm(h, w64[pre + "norm1.weight"], 1e-5)
+        h = (h + P.attention_mixer(n, w64, pre + "attn_a.", cfg)) + P.attention_mixer(n, w64, pre + "attn_b.", cfg)
+        f = _plain_centered_norm(h, w64[pre + "norm2.weight"], 1e-4)
+        return h + 0.5 * (torch.relu(f @ w64[pre + "ff.w1.weight"].t()).square() @ w64[pre + "ff.w2.weight"].t())
+
+    tokens = [int(t) for t in torch.randint(0, 50, (37,), generator=torch.Generator().manual_seed(5))]
+    ref = _plain_shell(tokens, w, layer, n_layers=2)
+    runner = _runner_for(model, dtype)
+    impl = _squared_relu_feed_forward
+    whole = runner.step([StepEntry("w", tokens, list(range(len(tokens))))]).cpu().clone()   # 37 tokens: also few
+    runner.finish("w")
+    before = impl.few_token_calls
+    rows = [runner.step([StepEntry("c", tokens[:20], list(range(20)))]).cpu().clone()]
+    rows += [runner.step([StepEntry("c", [t], [0])]).cpu().clone() for t in tokens[20:]]
+    assert impl.few_token_calls - before == 2 * (1 + len(tokens) - 20)
+    H.check_rows(whole, ref, "bfloat16", "other feed-forward whole")
+    H.check_rows(torch.cat(rows), ref, "bfloat16", "other feed-forward token by token")
+
+
+def _post_norm_block(spec, hidden_size):
+    """h <- norm_a(h + mixer(h)); h <- norm_b(h + ffn(h)): the norms come after the residual sums.
+    Described by a LayerSpec with part names of its own; nothing of the framework knows them."""
+    from poor_mans_mamba_b200.parts import Part, build_part
+
+    class _Impl(Part):
+        def __init__(self):
+            self.prefix = spec.prefix
+            self.mixer = build_part("mixer", spec.part("mixer"), hidden_size=hidden_size)
+            self.norm_a = build_part("norm", spec.part("after_mixer"), width=hidden_size)
+            self.ffn = build_part("feed_forward", spec.part("ffn"), hidden_size=hidden_size)
+            self.norm_b = build_part("norm", spec.part("after_ffn"), width=hidden_size)
+
+        def parts(self):
+            return [self.mixer, self.norm_a, self.ffn, self.norm_b]
+
+        def branch_buffers_needed(self):
+            return 1
+
+        def state_specs(self):
+            return [(f"{self.mixer.name}.{s.name}", s) for s in self.mixer.state_specs()]
+
+        def finalize(self, dtype, device):
+            for p in self.parts():
+                p.finalize(dtype, device)
+
+        def forward(self, stream, ctx, cache):
+            for part, norm in ((self.mixer, self.norm_a), (self.ffn, self.norm_b)):
+                h = stream.flush()
+                out = stream.take_branch()
+                x = h.to(ctx.dtype)
+                if part is self.mixer:
+                    part.forward(x, ctx, cache, out)
+                else:
+                    part.forward(x, ctx, out)
+                stream.add(out, part.out_scale)
+                h.copy_(stream.normed(norm))   # folds the branch in, then the stream goes on from the norm
+
+    return _Impl()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32])
+def test_post_norm_arrangement_described_by_named_parts(dtype):
+    from poor_mans_mamba_b200.parts import LayerSpec, PartSpec, register_arrangement, registered
+    register_arrangement("test_post_norm", _post_norm_block)
+    assert "test_post_norm" in registered("arrangement")
+    attn = {"num_heads": 3, "num_kv_heads": 3, "head_dim": 16, "position_encoding": {"kind": "rotary", "theta": 50.0}}
+    layers = [LayerSpec("test_post_norm", f"layers.{i}.", {
+        "mixer": PartSpec("paged_attention", "attn", attn), "after_mixer": PartSpec("rmsnorm", "ln_a", {"eps": 1e-5}),
+        "ffn": PartSpec("swiglu", "ff", {"intermediate_size": 56}), "after_ffn": PartSpec("rmsnorm", "ln_b", {"eps": 1e-5})})
+        for i in range(2)]
+    model = _single_layer_model(None, layer_specs=layers)
+    assert "layers.1.ln_b.weight" in model.param_specs()
+    dev, w = _random_tensors(model, 31, dtype, scale=6.0)
+    model.bind(dev, dtype, DEV)
+    w64 = {k: v.double() for k, v in w.items()}
+    cfg = {"num_attention_heads": 3, "num_key_value_heads": 3, "head_dim": 16, "rope_theta": 50.0}
+
+    def layer(h, i):
+        pre = f"layers.{i}."
+        h = P.rms_norm(h + P.attention_mixer(h, w64, pre + "attn.", cfg), w64[pre + "ln_a.weight"], 1e-5)
+        return P.rms_norm(h + P.swiglu_mlp(h, w64, pre + "ff.", {}), w64[pre + "ln_b.weight"], 1e-5)
+
+    tokens = [int(t) for t in torch.randint(0, 50, (33,), generator=torch.Generator().manual_seed(8))]
+    ref = _plain_shell(tokens, w, layer, n_layers=2)
+    whole, cut = _two_cuttings(_runner_for(model, dtype), tokens)
+    H.check_rows(whole, ref, "float32", "post-norm arrangement whole")
+    H.check_rows(cut, ref, "float32", "post-norm arrangement in portions")

@@ -253,3 +253,57 @@ def test_one_step_ahead_gives_the_same_outputs(seed):
             assert r.status in ("oom", "cache_full") and r.output == want[i][:len(r.output)]
     assert cache.free_slots == 3 and cache.min_free_pages() == cache.groups[(2, 4, 0)].num_pages
     assert not s.running and not s.waiting
+
+
+def test_request_ends_with_partial_output_when_it_reaches_max_seq_len():
+    """Reference: KV overflow on decode ends the session as done with what it has
+    (src/runtime/cluster_scheduler.cpp:645-651)."""
+    cache = CacheManager(SPECS, page_size=4, num_pages=16, num_slots=4, dtype=torch.float32, device="cpu")
+    s = Scheduler(cache, max_batched_tokens=16, max_seqs=4, max_seq_len=10)
+    a = s.add("a", list(range(1, 8)), SamplingParams(max_new_tokens=50))      # 7 + 3 fed tokens fill 10 places
+    b = s.add("b", [5, 6], SamplingParams(max_new_tokens=4))                   # ends by length first
+    c = s.add("c", list(range(1, 12)), SamplingParams(max_new_tokens=4))       # prompt alone is too long
+    run(s, cache)
+    # positions 0..9 are computed; the token sampled at position 9 is still handed out
+    assert a.status == "max_seq" and a.output == expected(a.prompt, 4) and a.n_computed == 10
+    assert b.status == "done" and b.output == expected(b.prompt, 4)
+    assert c.status == "max_seq" and c.output == []
+    assert cache.min_free_pages() == 16 and cache.free_slots == 4
+
+
+def test_max_seq_len_with_late_results():
+    """The two-halves digestion (advance / resolve) ends a request at max_seq_len too."""
+    cache = CacheManager(SPECS, page_size=4, num_pages=16, num_slots=4, dtype=torch.float32, device="cpu")
+    s = Scheduler(cache, max_batched_tokens=16, max_seqs=4, max_seq_len=6)
+    a = s.add("a", [1, 2, 3, 4], SamplingParams(max_new_tokens=50))
+    pending = None
+    while s.has_work():
+        plan = s.plan()
+        toks = []
+        for e in plan.entries:
+            cache.grow(e.req.id, e.start + e.count), cache.advance(e.req.id, e.count)
+            known = [t for t in e.req.tokens if t != Scheduler.PENDING]
+            toks.append(next_token(known + ([pending[1][0]] if pending else [])))
+        slots = s.advance(plan)
+        if pending is not None:
+            s.resolve(*pending)
+        pending = (slots, toks)
+    s.resolve(*pending)
+    assert a.status == "max_seq" and a.output == expected(a.prompt, 3) and a.n_computed == 6
+
+
+def test_requests_are_given_back_through_the_release_callback():
+    cache = CacheManager(SPECS, page_size=4, num_pages=3, num_slots=4, dtype=torch.float32, device="cpu")
+    released = []
+
+    def release(rid):
+        released.append(rid)
+        cache.release(rid)
+
+    s = Scheduler(cache, max_batched_tokens=16, max_seqs=4, release=release)
+    s.add("a", [1, 2, 3, 4, 5], SamplingParams(max_new_tokens=6))
+    s.add("b", [1, 2, 3], SamplingParams(max_new_tokens=6))
+    run(s, cache)
+    assert s.counters["preemptions"] >= 1           # 3 pages cannot hold both to the end
+    assert sorted(set(released)) == ["a", "b"] and len(released) == 2 + s.counters["preemptions"]
+    assert cache.min_free_pages() == 3

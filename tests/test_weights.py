@@ -148,3 +148,25 @@ def test_missing_weight_file(tmp_path):
     model = _model_for(str(d))
     with pytest.raises(WeightsError, match="no readable weights"):
         load_tensors(str(d), model.param_specs(), [], torch.float32, torch.device("cpu"))
+
+
+def test_tensors_nobody_asked_for_are_listed_not_refused(tmp_path, capsys):
+    """The reference loads by name and never looks at the rest (src/model/falconh1_loader.cpp:27-58):
+    a tied checkpoint that still carries lm_head.weight, or an exporter's extra buffer, loads."""
+    cfg = tiny_config("A")  # tied embeddings
+    d = write_random_model(cfg, 0, str(tmp_path / "m"))
+    files = ModelFiles(d)
+    tensors = {k: files.tensor(k) for k in files.keys()}
+    files.close()
+    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    save_file(tensors, os.path.join(d, "model.safetensors"))
+    model = _model_for(d)
+    out = load_tensors(d, model.param_specs(), model.ignored_names(), torch.float32, torch.device("cpu"))
+    assert "lm_head.weight" not in out and len(out) == len(model.param_specs())
+    err = capsys.readouterr().err
+    assert "2 tensors" in err and "lm_head.weight" in err and "rotary_emb.inv_freq" in err
+    with pytest.raises(WeightsError) as ei:
+        load_tensors(d, model.param_specs(), model.ignored_names(), torch.float32, torch.device("cpu"), strict=True)
+    assert ei.value.unexpected == ["lm_head.weight", "model.layers.0.self_attn.rotary_emb.inv_freq"]
+    assert not ei.value.missing

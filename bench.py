@@ -175,6 +175,38 @@ def config_record(cfg, args, full_layers):
             "parallelism": "single-gpu", "page_size": 64, "l2": "inputs exceed L2 (no flush)"}
 
 
+def check_against_plain(cfg, args) -> dict:
+    """The engine against the plain implementation of the test-suite on the first two layers of
+    the run's model (same seed, so the same tensors as the timed model's layers 0 and 1, scaled
+    loud as the tests' models are so that a wrong key range, page or state moves the logits) and
+    on the benchmark's schedule.  Raises AssertionError at the first row beyond the tolerance."""
+    import torch
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import parity_at_sizes
+    from model_dirs import make_loud
+
+    from poor_mans_mamba_b200.weights import ModelFiles, write_random_model
+
+    small = dict(cfg)
+    small["num_hidden_layers"] = min(2, cfg["num_hidden_layers"])
+    ctx = args.context
+    contexts = sorted({max(16, int(ctx * f)) - 6 for f in (0.075, 0.13, 0.25, 0.32, 0.5, 0.56, 0.76, 1.0)})
+    t0 = time.time()
+    with tempfile.TemporaryDirectory(prefix="pmm_bench_check_") as d:
+        write_random_model(small, seed=2, out_dir=d)
+        make_loud(d, hidden_size=small["hidden_size"])
+        files = ModelFiles(d)
+        weights = {k: files.tensor(k).float() for k in files.keys()}
+        files.close()
+        with torch.cuda.device(0):
+            summary = parity_at_sizes.run_parity(d, small, weights, args.dtype, prompt_len=min(2048, ctx // 2),
+                                                 contexts=contexts, decode_steps=6, max_seq_len=ctx + 64)
+        torch.cuda.empty_cache()
+    return {"layers": small["num_hidden_layers"], "rows": summary["rows"],
+            "worst_error_over_tolerance": summary["worst_error_over_tolerance"], "seconds": round(time.time() - t0, 1)}
+
+
 def reference_arm(args) -> int:
     """`--impl reference`: the UNMODIFIED CUDA path of the reference (FalconH1Runner + CUDABackend +
     src/ops/gpu/*.cu: FP32, cublasSgemm, one request per cache slot), built with nvcc and cuBLAS by
@@ -263,6 +295,11 @@ def main() -> int:
                     "(same layer sizes) where memory or time needs it")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--no-check", dest="check", action="store_false",
+                    help="skip the comparison with the plain implementation that runs before the timing: the first "
+                         "two layers of the run's model, in the run's dtype, on the benchmark's schedule (a "
+                         "2,048-token prompt step twice, then decode steps of a batch of 8 at contexts spread up to "
+                         "--context through the CUDA graphs), every row against float64")
     ap.add_argument("--profile-steps", action="store_true",
                     help="small workload for a profiler instead of the benchmark: after an untimed set-up, one "
                          "2,048-token prefill step and two decode steps of the batch, issued kernel by kernel "
@@ -319,6 +356,11 @@ def main() -> int:
             torch.cuda.profiler.stop()
         print(json.dumps({"profile_steps": "done", "layers": args.layers, "batch": args.batch, "context": ctx_len}))
         return 0
+
+    checked = None
+    if args.check:
+        checked = check_against_plain(cfg, args)
+        print(f"[bench] checked against the plain implementation: {checked}", file=sys.stderr, flush=True)
 
     def make_engine(batch):
         return Engine(tmp, dtype=args.dtype, max_tokens=batch * (ctx_len + 64), max_seqs=batch, page_size=64,
@@ -436,6 +478,9 @@ def main() -> int:
         "clocks": clock_summary, "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items()},
         "gpu_launches": int(launches), "roofline": roofline, "impl": "ours",
     }
+    result["checked"] = checked is not None
+    if checked is not None:
+        result["check"] = checked
     if prefill is not None:
         result["prefill"] = prefill
     if points:

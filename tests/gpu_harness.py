@@ -29,12 +29,17 @@ def reference_logits(seqs: Sequence[Sequence[int]], weights, cfg) -> List[torch.
     return [forward_logits(s, weights, cfg, torch.float64) for s in seqs]
 
 
-def check_rows(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: str) -> float:
+def check_rows(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: str, f32_frac: float = 0.0) -> float:
+    """``f32_frac`` > 0 (models with rows of thousands of products, whose float32 sums differ from
+    the float64 ones by more than the tiny models' absolute bound): the float32 bound is that
+    fraction of the largest logit instead."""
     got = got.detach().double().cpu()
     assert got.shape == ref.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(ref.shape)}"
     assert torch.isfinite(got).all(), f"{what}: non-finite logits"
     err = (got - ref).abs()
     tol = F32_ATOL if dtype == "float32" else BF16_FRAC * float(ref.abs().max())
+    if dtype == "float32" and f32_frac > 0.0:
+        tol = f32_frac * max(1.0, float(ref.abs().max()))
     worst = float(err.max())
     if worst > tol:
         r, c = divmod(int(err.argmax()), err.shape[1])

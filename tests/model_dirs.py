@@ -21,15 +21,32 @@ from poor_mans_mamba_b200.weights import ModelFiles, save_file, write_random_mod
 LOUD = {"mamba.in_proj.weight": 8.0, "mamba.in_proj.bias": 8.0, "conv1d.weight": 16.0, "q_proj.weight": 8.0,
         "k_proj.weight": 8.0}
 LOUD_OTHER_MATRICES = 2.0
+_FROM_THE_STREAM = ("mamba.in_proj.weight", "mamba.in_proj.bias", "q_proj.weight", "k_proj.weight")
 
 
-def make_loud(model_dir: str) -> None:
+def loud_scales(hidden_size: int = 0) -> dict:
+    """The factors by tensor-name suffix.  The factor 8 of the projections that read the normalised
+    stream suits the tiny widths (a row of N(0, 0.02) weights times 64..96 unit inputs has a standard
+    deviation of 0.16..0.2); at a width of ``hidden_size`` the same loudness (about 1.3) needs the
+    power of two nearest to 1.3 / (0.02 sqrt(width)): 2 at 1,024 and 1,280, 1 at 3,072."""
+    scales = dict(LOUD)
+    if hidden_size > 0:
+        import math
+        s = 2.0 ** round(math.log2(1.3 / (0.02 * math.sqrt(hidden_size))))
+        for k in _FROM_THE_STREAM:
+            scales[k] = s
+    return scales
+
+
+def make_loud(model_dir: str, hidden_size: int = 0) -> None:
+    """``hidden_size`` > 0: factors for that width (see `loud_scales`); 0: the tiny models' factors."""
     files = ModelFiles(model_dir)
     tensors = {k: files.tensor(k) for k in files.keys()}
     files.close()
+    loud = loud_scales(hidden_size)
     for k in list(tensors):
         scale = None
-        for suffix, s in LOUD.items():
+        for suffix, s in loud.items():
             if k.endswith(suffix):
                 scale = s
         if scale is None and tensors[k].dim() >= 2 and "embed" not in k and "lm_head" not in k:

@@ -246,6 +246,21 @@ def forward_logits(tokens: Sequence[int], weights: Dict[str, Tensor], cfg: dict,
     return linear(h, head) * cfg.get("lm_head_multiplier", 1.0)
 
 
+def forward_logits_at(tokens: Sequence[int], weights: Dict[str, Tensor], cfg: dict, rows: Sequence[int],
+                      dtype: torch.dtype = torch.float64) -> Tensor:
+    """The rows ``rows`` of `forward_logits` without forming the others: the same blocks over the
+    whole sequence, final norm and head on the chosen positions only (the reference keeps one row,
+    src/runtime/runner/falconh1_runner.cpp:154-214).  For vocabularies where [T, V] is too large."""
+    w = {k: v.to(dtype) for k, v in weights.items()}
+    h = embedding(tokens, w["model.embed_tokens.weight"], cfg.get("embedding_multiplier", 1.0))
+    for layer in range(cfg["num_hidden_layers"]):
+        h = decoder_block(h, w, layer, cfg)
+    h = rms_norm(h[torch.tensor(list(rows), dtype=torch.long)], w["model.final_layernorm.weight"],
+                 cfg.get("rms_norm_eps", 1e-5))
+    head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else w["lm_head.weight"]
+    return linear(h, head) * cfg.get("lm_head_multiplier", 1.0)
+
+
 def greedy_generate(prompt: Sequence[int], n_new: int, weights: Dict[str, Tensor], cfg: dict,
                     dtype: torch.dtype = torch.float64) -> List[int]:
     """Greedy continuation by re-running the whole sequence each step; the first index wins

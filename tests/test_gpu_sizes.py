@@ -42,12 +42,20 @@ def shaped(request, tmp_path_factory):
     cfg = SHAPES[name]
     d = str(tmp_path_factory.mktemp(f"shape_{name}"))
     write_random_model(cfg, 11, d)
+    from model_dirs import make_loud
+    make_loud(d, hidden_size=cfg["hidden_size"])  # so that a lost state, a wrong page or rotation moves the logits
     files = ModelFiles(d)
     weights = {k: files.tensor(k).float() for k in files.keys()}
     files.close()
     rng = random.Random(5)
     seqs = [[rng.randrange(cfg["vocab_size"]) for _ in range(n)] for n in (150, 41)]
     refs = H.reference_logits(seqs, weights, cfg)
+    # the comparison below can fail: without the state-space branch, or without the attention branch,
+    # the logits move by far more than the bfloat16 tolerance
+    tol = H.BF16_FRAC * float(refs[1].abs().max())
+    for suffix in ("mamba.out_proj.weight", "self_attn.o_proj.weight"):
+        broken = {k: (torch.zeros_like(v) if k.endswith(suffix) else v) for k, v in weights.items()}
+        assert float((H.reference_logits(seqs[1:], broken, cfg)[0] - refs[1]).abs().max()) > 3 * tol, suffix
     return name, d, cfg, seqs, refs
 
 
@@ -60,24 +68,29 @@ def test_larger_layer_shapes_agree_with_plain(shaped, dtype, cutting):
               "tail": lambda s: H.script_tail_one_by_one(s, tail=12)}[cutting](seqs)
     out = H.run_script(runner, seqs, script)
     for i, ref in enumerate(refs):
-        H.check_rows(out[i], ref, dtype, f"{name} {dtype} {cutting} seq {i}")
+        # float32: products over 3,072 to 12,288 terms and loud weights; the bound is 2e-5 of the largest logit
+        H.check_rows(out[i], ref, dtype, f"{name} {dtype} {cutting} seq {i}", f32_frac=2e-5)
 
 
 def test_decode_graph_at_larger_shapes(shaped):
     """The fused decode path (weight-streaming products, attention from the projections) and its
-    CUDA graph at these widths: greedy continuation equals the step-by-step one."""
+    CUDA graph at these widths: the logits of 12 decoded tokens, two requests a step, row by row
+    against the plain implementation."""
     name, d, cfg, seqs, refs = shaped
-    from poor_mans_mamba_b200.entry import Engine
-    outs = []
-    for graphs in (False, True):
-        eng = Engine(d, dtype="bfloat16", max_tokens=1024, max_seqs=4, page_size=64, max_seq_len=512, cuda_graphs=graphs)
-        outs.append(eng.generate([s[:30] for s in seqs], max_new_tokens=6, temperature=0.0, eos_token_id=-1))
-    assert outs[0] == outs[1]
-    # and the first generated token is the plain implementation's argmax at the prompt's end
-    for s, ref, got in zip(seqs, refs, outs[0]):
-        top2 = torch.topk(ref[29], 2).values
-        if float(top2[0] - top2[1]) > 0.05 * float(ref[29].abs().max()):  # only where bfloat16 cannot flip it
-            assert got[0] == int(ref[29].argmax())
+    from poor_mans_mamba_b200.engine import StepEntry
+    runner = H.make_runner(d, "bfloat16", page_size=64, num_pages=8, num_slots=2)
+    runner.enable_graphs(max_seq_len=256)
+    starts = [len(s) - 12 for s in seqs]
+    reqs = [("r", i) for i in range(len(seqs))]
+    for r, s, a in zip(reqs, seqs, starts):
+        got = runner.step([StepEntry(r, s[:a], [a - 1])])
+        H.check_rows(got, refs[r[1]][a - 1:a], "bfloat16", f"{name} prompt of request {r[1]}")
+    for j in range(12):
+        runner.decode_tokens(reqs, [s[a + j] for s, a in zip(seqs, starts)])
+        logits = runner.graphs.last_logits(len(reqs)).cpu()
+        for i, a in enumerate(starts):
+            H.check_rows(logits[i:i + 1], refs[i][a + j:a + j + 1], "bfloat16", f"{name} decode step {j} request {i}")
+    assert runner.graphs.replays == 12
 
 
 # ---------------------------------------------------------------------------------------------

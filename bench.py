@@ -280,6 +280,116 @@ def reference_arm(args) -> int:
     return 0
 
 
+def mixed_workload(args, cfg, full_layers, nums, peaks, model_dir, checked) -> int:
+    """`--workload mixed`: one step that mixes 32 decoding requests (contexts spread over
+    1,024..4,096 tokens) with four prompt portions of 512 tokens (at depths 0, 512, 1,024 and 1,536
+    of 2,048-token prompts; a prompt that ends is replaced by a new one, so every timed step has the
+    same shape: 2,080 tokens, 33 rows of logits).  Token ids uniform from seed 3.  `value` is the
+    step's tokens/s timed on the device; `e2e` the same with host token ids in from pinned memory and
+    the sampled ids back on the host every step.  The roofline is the slower of the step's bytes
+    (weights once, keys/values and states of the live requests) at the measured copy rate and its
+    flops at the measured bf16 rate."""
+    import torch
+
+    from poor_mans_mamba_b200.engine.runner import StepEntry
+    from poor_mans_mamba_b200.entry import Engine
+
+    n_dec, n_pf, chunk, prompt_total = 32, 4, 512, 2048
+    K_steps, W = args.steps, args.warmup
+    rng = random.Random(3)
+    vocab = cfg["vocab_size"]
+    hi = args.context - K_steps - W - 2
+    contexts = [1024 + (hi - 1024) * i // (n_dec - 1) for i in range(n_dec)]
+    with torch.cuda.device(0):
+        eng = Engine(model_dir, dtype=args.dtype, max_tokens=n_dec * (args.context + 64) + (n_pf + 1) * (prompt_total + 64),
+                     max_seqs=n_dec + n_pf + 1, page_size=64, max_batched_tokens=8192, max_seq_len=args.context + 64)
+        runner = eng.runner
+        dec = [("dec", i) for i in range(n_dec)]
+        for r, c in zip(dec, contexts):
+            runner.step([StepEntry(r, [rng.randrange(vocab) for _ in range(c)], [])])
+        serial = [0]
+
+        def new_prompt():
+            serial[0] += 1
+            return [("pf", serial[0]), [rng.randrange(vocab) for _ in range(prompt_total)], 0]
+
+        prompts = []
+        for j in range(n_pf):  # prompt j starts j portions deep
+            p = new_prompt()
+            for _ in range(j):
+                runner.step([StepEntry(p[0], p[1][p[2]:p[2] + chunk], [])])
+                p[2] += chunk
+            prompts.append(p)
+
+        def one_step(fetch: bool):
+            entries = [StepEntry(r, [rng.randrange(vocab)], [0]) for r in dec]
+            for p in prompts:
+                last = p[2] + chunk == prompt_total
+                entries.append(StepEntry(p[0], p[1][p[2]:p[2] + chunk], [chunk - 1] if last else []))
+            logits = runner.step(entries)
+            ids = eng.sampler.sample(logits) if fetch else eng.sampler.sample_device(logits)
+            for j, p in enumerate(prompts):
+                p[2] += chunk
+                if p[2] == prompt_total:
+                    runner.finish(p[0])
+                    prompts[j] = new_prompt()
+            return ids
+
+        for _ in range(W + 2):  # the second occurrence of the shape records its graph
+            one_step(False)
+        torch.cuda.synchronize()
+        launches0 = runner.mark_launches()
+        with ClockSampler() as clocks:
+            marks = [torch.cuda.Event(enable_timing=True) for _ in range(K_steps + 1)]
+            marks[0].record()
+            for s in range(K_steps):
+                one_step(False)
+                marks[s + 1].record()
+            torch.cuda.synchronize()
+        ms = marks[0].elapsed_time(marks[-1]) / K_steps
+        launches = runner.kernels_launched_since(launches0)
+        h2d0 = runner.h2d_bytes
+        t0 = time.perf_counter()
+        for _ in range(K_steps):
+            one_step(True)
+        e2e_s = (time.perf_counter() - t0) / K_steps
+        h2d = (runner.h2d_bytes - h2d0) // K_steps
+        runner.check_kernels(wait=True)
+
+    T = n_dec + n_pf * chunk
+    ctx_mid = [c + W + 2 + K_steps // 2 for c in contexts]
+    depths = [k * chunk for k in range(n_pf)]
+    L, Hq, Dh = cfg["num_hidden_layers"], cfg["num_attention_heads"], cfg["head_dim"]
+    read_bytes = (nums["weight_bytes_per_step"] + sum(nums["kv_bytes_per_token"] * c for c in ctx_mid)
+                  + sum(nums["kv_bytes_per_token"] * d for d in depths) + (n_dec + n_pf) * nums["state_bytes_per_seq"])
+    attn_flops = L * 4 * Hq * Dh * (sum(ctx_mid) + sum(chunk * d + chunk * (chunk + 1) // 2 for d in depths))
+    flops = T * (nums["flops_per_token_matmul"] + nums["ssd_flops_per_token"]) + attn_flops + 33 * nums["head_flops_per_row"]
+    t_bytes = read_bytes / (peaks["hbm_gbs"] * 1e9)
+    t_flops = flops / (peaks["bf16_tflops"] * 1e12)
+    bound = "hbm" if t_bytes >= t_flops else "tensor"
+    record = config_record(cfg, args, full_layers)
+    record.update({"global_batch": n_dec + n_pf, "decode_requests": n_dec, "prompt_portions": n_pf, "portion_tokens": chunk})
+    result = {
+        "metric": f"mixed-step tokens/s (32 decoding requests + 4 x 512 prompt tokens, Falcon-H1-{args.sizes.upper()} layer sizes)",
+        "value": round(T / (ms / 1e3), 1), "unit": "tokens/s", "n_gpus": 1, "steps": K_steps, "warmup": W,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
+        "data": "synthetic: uniform random token ids (seed 3), random-init weights (seed 2)",
+        "config": record, "clocks": clocks.summary(),
+        "e2e": {"value": round(T / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4 * 33},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": bound, "ms_at_peak": round(max(t_bytes, t_flops) * 1e3, 4),
+                     "frac": round(max(t_bytes, t_flops) * 1e3 / ms, 4), "read_gb": round(read_bytes / 1e9, 3),
+                     "tflop": round(flops / 1e12, 3), "frac_hbm": round(t_bytes * 1e3 / ms, 4),
+                     "frac_tensor": round(t_flops * 1e3 / ms, 4), "peak_source": peaks["source"]},
+        "impl": "ours", "checked": checked is not None,
+    }
+    if checked is not None:
+        result["check"] = checked
+    print(json.dumps(result))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -288,13 +398,17 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096, help="context length at which decoding ends")
-    ap.add_argument("--sizes", default="0.5b", choices=["0.5b"] + sorted(OTHER_SIZES),
+    ap.add_argument("--sizes", default=None, choices=["0.5b"] + sorted(OTHER_SIZES),
                     help="layer sizes; 0.5b is the benchmark's configuration, the others are for measurements "
                          "beside it (give --layers: a few layers of them already fill the memory system)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has "
                     "(same layer sizes) where memory or time needs it")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed"],
+                    help="decode: the benchmark (decode steps of a batch, with prefill and other points beside it); "
+                         "mixed: one step of 32 decoding requests at contexts of 1,024..4,096 tokens beside four "
+                         "prompt portions of 512 tokens, by default at Falcon-H1-1.5B-Deep layer sizes")
     ap.add_argument("--no-check", dest="check", action="store_false",
                     help="skip the comparison with the plain implementation that runs before the timing: the first "
                          "two layers of the run's model, in the run's dtype, on the benchmark's schedule (a "
@@ -306,6 +420,8 @@ def main() -> int:
                          "(no CUDA graphs) between cudaProfilerStart and cudaProfilerStop; use with --layers 2")
     args = ap.parse_args()
 
+    if args.sizes is None:
+        args.sizes = "1.5b-deep" if args.workload == "mixed" else "0.5b"
     if args.gpus != 1:
         print(f"bench.py: this engine serves from one GPU; --gpus {args.gpus} is not supported")
         return 2
@@ -362,42 +478,87 @@ def main() -> int:
         checked = check_against_plain(cfg, args)
         print(f"[bench] checked against the plain implementation: {checked}", file=sys.stderr, flush=True)
 
-    def make_engine(batch):
-        return Engine(tmp, dtype=args.dtype, max_tokens=batch * (ctx_len + 64), max_seqs=batch, page_size=64,
-                      max_batched_tokens=8192, max_seq_len=ctx_len + 64)
+    def make_engine(batch, end_context=None):
+        end = ctx_len if end_context is None else end_context
+        return Engine(tmp, dtype=args.dtype, max_tokens=batch * (end + 64), max_seqs=batch, page_size=64,
+                      max_batched_tokens=8192, max_seq_len=end + 64)
 
-    def decode_device_timed(eng, batch, steps, warmup):
+    def percentile(sorted_ms, p):
+        """Linear interpolation between the two nearest ranks (benchmarks/generate_bench.cpp:96-107)."""
+        if not sorted_ms:
+            return 0.0
+        idx = (p / 100.0) * (len(sorted_ms) - 1)
+        lo, hi = int(idx), min(int(idx) + 1, len(sorted_ms) - 1)
+        return sorted_ms[lo] * (1.0 - (idx - lo)) + sorted_ms[hi] * (idx - lo)
+
+    def decode_device_timed(eng, batch, steps, warmup, end_context=None):
         """tokens/s with CUDA events around `steps` decode steps of `batch` requests whose context
-        ends at ctx_len; host work (index packing, launches) runs concurrently and is not waited for."""
-        prompt_len = ctx_len - steps - warmup
+        ends at `end_context` (default: --context); host work (index packing, launches) runs
+        concurrently and is not waited for.  An event after every step gives the time between
+        tokens (mean, p50, p95 as the reference's harness reports them)."""
+        end = ctx_len if end_context is None else end_context
+        prompt_len = end - steps - warmup
         runner = eng.runner
         reqs = [("bench", i) for i in range(batch)]
         for r in reqs:  # prefill, untimed, in portions of <= 8192 tokens per step
             toks = [rng.randrange(vocab) for _ in range(prompt_len)]
-            runner.step([StepEntry(r, toks, [])])
+            for a in range(0, prompt_len, 8192):
+                runner.step([StepEntry(r, toks[a:a + 8192], [])])
         feed = [[rng.randrange(vocab) for _ in range(batch)] for _ in range(steps + warmup)]
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
         launches0 = None
         for s in range(steps + warmup):
             if s == warmup:
                 torch.cuda.synchronize()
                 launches0 = runner.mark_launches()
-                start.record()
+                marks[0].record()
             # the first step feeds host ids, the others the ids the device just sampled
             runner.decode_tokens(reqs, feed[s] if s == 0 else None)
-        stop.record()
+            if s >= warmup:
+                marks[s - warmup + 1].record()
         torch.cuda.synchronize()
-        ms = start.elapsed_time(stop)
+        ms = marks[0].elapsed_time(marks[-1])
+        gaps = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(steps))
+        itl = {"mean": round(ms / steps, 4), "p50": round(percentile(gaps, 50.0), 4),
+               "p95": round(percentile(gaps, 95.0), 4)}
         launches = runner.kernels_launched_since(launches0)
         for r in reqs:
             runner.finish(r)
-        return batch * steps / (ms / 1e3), ms / steps, launches
+        return batch * steps / (ms / 1e3), ms / steps, launches, itl
+
+    def prefill_timed(eng, n_tokens, portions=1, reps=3):
+        """Median device time of one prompt of n_tokens fed as `portions` equal steps, the wanted
+        row being the last one (the reference's prefill returns that row's logits)."""
+        toks = [rng.randrange(vocab) for _ in range(n_tokens)]
+        cut = n_tokens // portions
+        times = []
+        for it in range(W + reps):
+            s_ev, e_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            s_ev.record()
+            for k in range(portions):
+                last = k == portions - 1
+                part = toks[k * cut:] if last else toks[k * cut:(k + 1) * cut]
+                eng.runner.step([StepEntry(("pf", n_tokens, portions, it), part, [len(part) - 1] if last else [])])
+            e_ev.record()
+            torch.cuda.synchronize()
+            eng.runner.finish(("pf", n_tokens, portions, it))
+            if it >= W:
+                times.append(s_ev.elapsed_time(e_ev))
+        return statistics.median(times)
+
+    def prefill_flops(T):
+        return (T * (nums["flops_per_token_matmul"] + nums["ssd_flops_per_token"]) + nums["attn_flops"](T)
+                + nums["head_flops_per_row"])
+
+    if args.workload == "mixed":
+        return mixed_workload(args, cfg, full_layers, nums, peaks, tmp, checked)
 
     result = {}
     with torch.cuda.device(0):
         eng = make_engine(args.batch)
         with ClockSampler() as clocks:
-            tok_s, ms_step, launches = decode_device_timed(eng, args.batch, K_steps, W)
+            tok_s, ms_step, launches, itl = decode_device_timed(eng, args.batch, K_steps, W)
         clock_summary = clocks.summary()
 
         # end to end through the entry point: scheduler + pinned host ids in + sampled ids out
@@ -438,36 +599,48 @@ def main() -> int:
         roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": round(achieved / peaks["hbm_gbs"], 4), "peak_source": peaks["source"]}
 
-        prefill, points = None, {}
+        prefill, points, extra = None, {}, {}
         if not args.no_points:
             T = 2048
-            toks = [rng.randrange(vocab) for _ in range(T)]
-            times = []
-            for it in range(W + 3):
-                s_ev, e_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                torch.cuda.synchronize()
-                s_ev.record()
-                eng.runner.step([StepEntry(("pf", it), toks, [T - 1])])
-                e_ev.record()
-                torch.cuda.synchronize()
-                eng.runner.finish(("pf", it))
-                if it >= W:
-                    times.append(s_ev.elapsed_time(e_ev))
-            pf_ms = statistics.median(times)
-            flops = (T * (nums["flops_per_token_matmul"] + nums["ssd_flops_per_token"]) + nums["attn_flops"](T)
-                     + nums["head_flops_per_row"])
+            pf_ms = prefill_timed(eng, T)
+            flops = prefill_flops(T)
             prefill = {"value": round(T / (pf_ms / 1e3), 1), "tokens": T, "ms": round(pf_ms, 3),
                        "frac": round(flops / (pf_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4),
                        "flops": flops, "peak_tflops": peaks["bf16_tflops"], "peak_source": peaks["source"]}
+            # the same prompt as four portions of 512 tokens, and the prompt lengths of the reference's
+            # harness (benchmarks/generate_bench.cpp:45-47), each as one step
+            ms4 = prefill_timed(eng, T, portions=4)
+            extra["prefill_4x512"] = {"value": round(T / (ms4 / 1e3), 1), "ms": round(ms4, 3)}
+            sweep = {}
+            for n in (32, 128, 512, 1024):
+                ms_n = prefill_timed(eng, n)
+                sweep[str(n)] = {"value": round(n / (ms_n / 1e3), 1), "ms": round(ms_n, 3)}
+            sweep[str(T)] = {"value": prefill["value"], "ms": prefill["ms"]}
+            extra["prefill_by_length"] = sweep
             del eng
             torch.cuda.empty_cache()
+            itl_points = {f"decode_b{args.batch}": itl}
             for b in (1, 64):
+                if b == args.batch:
+                    continue
                 e = make_engine(b)
                 steps_b = min(K_steps, 32)
-                v, _, _ = decode_device_timed(e, b, steps_b, W)
+                v, _, _, itl_b = decode_device_timed(e, b, steps_b, W)
                 points[f"decode_b{b}"] = round(v, 1)
+                itl_points[f"decode_b{b}"] = itl_b
                 del e
                 torch.cuda.empty_cache()
+            # the batch again right after a 2,048-token prompt (context 2,048 -> 2,048 + steps)
+            short_end = 2048 + K_steps + W
+            e = make_engine(args.batch, short_end)
+            v, _, _, itl_short = decode_device_timed(e, args.batch, K_steps, W, short_end)
+            points[f"decode_b{args.batch}_ctx2048"] = round(v, 1)
+            itl_points[f"decode_b{args.batch}_ctx2048"] = itl_short
+            del e
+            torch.cuda.empty_cache()
+            extra["itl_ms"] = itl_points
+        else:
+            extra["itl_ms"] = {f"decode_b{args.batch}": itl}
 
     result = {
         "metric": f"decode tokens/s (Falcon-H1-{args.sizes.upper()} layer sizes, random weights)", "value": round(tok_s, 1),
@@ -478,6 +651,7 @@ def main() -> int:
         "clocks": clock_summary, "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items()},
         "gpu_launches": int(launches), "roofline": roofline, "impl": "ours",
     }
+    result.update(extra)
     result["checked"] = checked is not None
     if checked is not None:
         result["check"] = checked

@@ -243,7 +243,7 @@ __global__ void __launch_bounds__(128)
 // ----------------------------------------------------------------------------- phase 2
 __global__ void ssd_state_pass_kernel(const float* __restrict__ chunk_state, const float* __restrict__ chunk_decay,
                                       bf16* __restrict__ start_state, float* __restrict__ state,
-                                      const int* __restrict__ cu, const int* __restrict__ slots, int H, int PN) {
+                                      const int* __restrict__ cu, const int* __restrict__ slots, int H, int PN, int q) {
   pdl_launch_dependents();
   pdl_wait();
   // four state elements per thread (P*N is a multiple of 4 for every compiled pair)
@@ -251,8 +251,8 @@ __global__ void ssd_state_pass_kernel(const float* __restrict__ chunk_state, con
   const int h = blockIdx.y, seq = blockIdx.z;
   if (e >= PN) return;
   int first = 0;
-  for (int s = 0; s < seq; ++s) first += (cu[s + 1] - cu[s] + kQ - 1) / kQ;
-  const int nc = (cu[seq + 1] - cu[seq] + kQ - 1) / kQ;
+  for (int s = 0; s < seq; ++s) first += (cu[s + 1] - cu[s] + q - 1) / q;  // q: tokens per chunk
+  const int nc = (cu[seq + 1] - cu[seq] + q - 1) / q;
   if (nc <= 0) return;
   float4* sp = reinterpret_cast<float4*>(state + (static_cast<size_t>(slots[seq]) * H + h) * PN + e);
   float4 s = *sp;
@@ -490,6 +490,16 @@ __global__ void __launch_bounds__(128)
   }
 }
 
+// The state pass alone, for chunks of `q` tokens (the tcgen05 scan of ssd_tc.cu uses it with 128).
+int launch_ssd_state_pass(const float* chunk_state, const float* chunk_decay, bf16* start_state, float* state,
+                          const int* cu, const int* slots, int n_seq, int H, int PN, int q, cudaStream_t stream) {
+  if (PN % 4 || n_seq > 65535 || H > 65535 || q <= 0) return PMM_ERR_BAD_ARGUMENT;
+  dim3 grid((PN / 4 + 255) / 256, H, n_seq);
+  launch_pdl(ssd_state_pass_kernel, grid, dim3(256), 0, stream, chunk_state, chunk_decay, start_state, state, cu, slots, H,
+             PN, q);
+  return launch_status();
+}
+
 template <int P, int N>
 int launch_ssd(const void* xbc, int ld_xbc, const void* dt_raw, long long ld_dt, float dt_scale,
                const float* dt_shift, const float* a_log, const float* d_skip, float* state,
@@ -514,7 +524,7 @@ int launch_ssd(const void* xbc, int ld_xbc, const void* dt_raw, long long ld_dt,
                                     dt_scale, dt_shift, a_log, cu, n_seq, chunk_state, chunk_decay, chunk_cb, H, G);
   const int PN = P * N;
   dim3 grid2((PN / 4 + 255) / 256, H, n_seq);
-  launch_pdl(ssd_state_pass_kernel, grid2, dim3(256), 0, stream, chunk_state, chunk_decay, start_state, state, cu, slots, H, PN);
+  launch_pdl(ssd_state_pass_kernel, grid2, dim3(256), 0, stream, chunk_state, chunk_decay, start_state, state, cu, slots, H, PN, kQ);
   launch_pdl(k3, grid, dim3(128), smem3, stream, static_cast<const bf16*>(xbc), ld_xbc, static_cast<const bf16*>(dt_raw), ld_dt,
                                    dt_scale, dt_shift, a_log, d_skip, cu, n_seq, start_state, chunk_cb,
                                    static_cast<bf16*>(y), H, G, static_cast<const bf16*>(z_raw), ld_z, z_scale, z_bias);

@@ -155,6 +155,24 @@ class Model:
             self._fetch_lists[id(layer)] = cached
         return cached[0]
 
+    def _head_row_group(self, n_rows: int) -> int:
+        """Rows per launch of the weight-streaming head product, or 0 for the library product.
+        Measured (table read once, 8..64 rows): with a vocabulary that is a multiple of 8 the
+        library reads the table at 3 TB/s and wins from 17 rows on (23 vs 32 us at 32,784 x 1,024);
+        with any other vocabulary it falls to a slow kernel (163 vs 62 us at 65,537 x 1,280 and 32
+        rows; 780 vs 176 us at 130,049 x 3,072), so there the streaming product is used even when
+        the rows need up to four passes over the table."""
+        D = self.hidden_size
+        if D % 8:
+            return 0
+        group = next((m for m in (64, 32, 16, 8) if K.skinny_fits(m, D)), 0)
+        if group == 0:
+            return 0
+        if n_rows <= min(group, K.SKINNY_NORM_MAX_TOKENS):
+            return n_rows
+        passes = -(-n_rows // group)
+        return group if self.vocab_size % 8 and passes <= 4 else 0
+
     def _head(self, normed: Tensor, ctx: StepContext) -> Tensor:
         n_rows, V = normed.shape[0], self.vocab_size
         ws = ctx.workspace
@@ -164,12 +182,12 @@ class Model:
             K.linear(normed, self.head, logits)
             if mult != 1.0:
                 K.scale_f32_(logits, mult)
-        elif (_SKINNY_HEAD and n_rows <= K.SKINNY_NORM_MAX_TOKENS and self.hidden_size % 8 == 0
-              and K.skinny_fits(n_rows, self.hidden_size)):
-            # up to 16 rows of logits: the table is read once at memory speed by this repository's
-            # weight-streaming product (float32 out, multiplier in the epilogue); beyond that the
-            # library product was measured slightly faster
-            K.skinny_linear_f32(normed, self.head, logits, mult)
+        elif _SKINNY_HEAD and self._head_row_group(n_rows) > 0:
+            # the table is read at memory speed by this repository's weight-streaming product
+            # (float32 out, multiplier in the epilogue), once per group of rows that fits its shared memory
+            group = self._head_row_group(n_rows)
+            for r0 in range(0, n_rows, group):
+                K.skinny_linear_f32(normed[r0:r0 + group], self.head, logits[r0:r0 + group], mult)
         else:
             low = None if K.mm_has_f32_out() else ws.alloc((n_rows, V), normed.dtype)
             K.linear_f32_out(normed, self.head, logits, low, mult)

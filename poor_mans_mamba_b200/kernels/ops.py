@@ -46,6 +46,10 @@ _SIGNATURES = {
     "pmm_ssd_chunked": [c_void_p, c_int, c_void_p, c_longlong, c_float, c_void_p, c_void_p, c_void_p,
                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                         c_int, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_float, c_void_p, c_void_p],
+    "pmm_ssd_tc_supported": [c_int, c_int],
+    "pmm_ssd_tc": [c_void_p, c_int, c_void_p, c_longlong, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                   c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                   c_longlong, c_float, c_void_p, c_void_p, c_void_p],
     "pmm_gated_norm": [c_void_p, c_void_p, c_longlong, c_float, c_void_p, c_void_p, c_float, c_int,
                        c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_qkv_rope_store": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_float,
@@ -493,6 +497,60 @@ def ssm_scan_chunked(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Ten
           slots.data_ptr(), out.data_ptr(), chunk_state, chunk_decay, start_state, chunk_cb, len(new_lens), n_chunks,
           H, P, N,
           n_groups, zp, ld_z, zs, zb, _stream())
+
+
+SSD_TC_CHUNK = 128  # tokens per chunk of the tcgen05 scan
+
+
+def ssd_tc_supported(d_head: int, d_state: int) -> bool:
+    """Whether the tcgen05 scan takes this head size / state size (multiples of 16 up to 128 / 256)."""
+    return bool(_fn("pmm_ssd_tc_supported")(d_head, d_state))
+
+
+def ssd_tc_scratch_floats(new_lens: Sequence[int], n_heads: int, d_head: int, d_state: int) -> int:
+    """Floats of scratch for the tcgen05 scan: every 128-token chunk's local state (float), its
+    decay, delta and cs of its tokens per head, and its start state (bfloat16, on a 16-byte boundary)."""
+    chunks = sum((n + SSD_TC_CHUNK - 1) // SSD_TC_CHUNK for n in new_lens)
+    per_state = chunks * n_heads * d_head * d_state
+    return (per_state + (chunks * n_heads + 3) // 4 * 4 + chunks * n_heads * 2 * SSD_TC_CHUNK
+            + ((per_state + 1) // 2 + 3) // 4 * 4)
+
+
+def ssm_scan_tc(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Tensor, a_log: Tensor, d_skip: Tensor,
+                state: Tensor, cu: Tensor, slots: Tensor, new_lens: Sequence[int], out: Tensor, n_groups: int,
+                scratch: Tensor, gate=None) -> None:
+    """The Mamba2 recurrence over prompt portions in chunks of 128 tokens on the tcgen05 tensor
+    cores (bfloat16 activations); same contract as ssm_scan_seq.  ``scratch``: float32, at least
+    ssd_tc_scratch_floats(...) elements."""
+    _cuda(xbc, dt_raw, dt_shift, a_log, d_skip, state, cu, slots, out, scratch)
+    _need(state.dtype == torch.float32 and state.dim() == 4 and state.is_contiguous(),
+          "ssm_scan: state must be contiguous float32 [slots, H, P, N]")
+    _, H, P, N = state.shape
+    _need(xbc.dtype == torch.bfloat16 and ssd_tc_supported(P, N),
+          f"ssm_scan_tc: needs bfloat16, a head size that is a multiple of 16 up to 128 and a state size that is a "
+          f"multiple of 16 up to 256, got {xbc.dtype} ({P}, {N})")
+    ld_x = _rows_view(xbc, "ssm_scan: xbc")
+    _need(xbc.shape[1] == H * P + 2 * n_groups * N and ld_x % 8 == 0 and xbc.data_ptr() % 16 == 0,
+          "ssm_scan_tc: xbc must hold [x | B | C] in rows that start on 16-byte boundaries")
+    ld_dt = _rows_view(dt_raw, "ssm_scan: dt")
+    _need(dt_raw.shape[1] == H and dt_raw.dtype == xbc.dtype, "ssm_scan: dt must be [T, H]")
+    for v, nm in ((dt_shift, "dt_shift"), (a_log, "A_log"), (d_skip, "D")):
+        _f32vec(v, H, f"ssm_scan: {nm}")
+    _need(out.shape == (xbc.shape[0], H * P) and out.is_contiguous() and out.dtype == xbc.dtype
+          and out.data_ptr() % 16 == 0, "ssm_scan: out must be [T, H*P] on a 16-byte boundary")
+    n_chunks = sum((n + SSD_TC_CHUNK - 1) // SSD_TC_CHUNK for n in new_lens)
+    need = ssd_tc_scratch_floats(new_lens, H, P, N)
+    _need(scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= need
+          and scratch.data_ptr() % 16 == 0, f"ssm_scan_tc: needs {need} floats of 16-byte aligned scratch")
+    chunk_state = scratch.data_ptr()
+    chunk_decay = chunk_state + 4 * n_chunks * H * P * N
+    chunk_dt = chunk_decay + 4 * ((n_chunks * H + 3) // 4 * 4)
+    start_state = chunk_dt + 4 * n_chunks * H * 2 * SSD_TC_CHUNK
+    zp, ld_z, zs, zb = _gate_args(gate, out, "ssm_scan_tc")
+    _call("pmm_ssd_tc", xbc.data_ptr(), ld_x, dt_raw.data_ptr(), ld_dt, float(dt_scale), dt_shift.data_ptr(),
+          a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), cu.data_ptr(), slots.data_ptr(), out.data_ptr(),
+          chunk_state, chunk_decay, chunk_dt, start_state, len(new_lens), n_chunks, H, P, N, n_groups, zp, ld_z, zs, zb,
+          _tc_status(xbc.device).data_ptr(), _stream())
 
 
 def gated_norm(y: Tensor, z_raw: Tensor, z_scale: float, z_bias: Optional[Tensor],

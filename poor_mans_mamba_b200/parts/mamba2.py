@@ -15,6 +15,8 @@ K-1 conv inputs) and ``ssm`` [H, P, N].
 """
 from __future__ import annotations
 
+import os
+import sys
 from typing import Dict, List, Optional, Sequence
 
 import torch
@@ -26,6 +28,19 @@ Tensor = torch.Tensor
 
 # Steps whose longest portion has at least this many tokens use the chunked scan.
 _CHUNKED_FROM = 8
+# The chunked scan on the tcgen05 tensor cores (PMM_TCGEN05_SCAN=0: the mma.sync form, for the
+# seven size pairs it is compiled for).
+_TC_SCAN = os.environ.get("PMM_TCGEN05_SCAN", "1") == "1"
+_NOTED = set()
+
+
+def _note_serial(d_head: int, d_state: int) -> None:
+    """Says once that prompts of this shape are scanned token by token."""
+    if (d_head, d_state) not in _NOTED:
+        _NOTED.add((d_head, d_state))
+        print(f"[poor_mans_mamba_b200] note: the tensor-core scan takes head sizes that are multiples of 16 up to 128 "
+              f"and state sizes that are multiples of 16 up to 256; with d_head={d_head}, d_state={d_state} prompt "
+              f"portions run the token-serial scan", file=sys.stderr)
 
 
 class Mamba2Mixer(Mixer):
@@ -169,14 +184,22 @@ class Mamba2Mixer(Mixer):
         y = ws.alloc((T, i_dim), proj.dtype)
         # without a norm the gate y * silu(z) is the scan kernels' epilogue
         gate = (z, self.z_scale, self.z_bias) if self.norm_w is None else None
-        if (not ctx.decode_only and proj.dtype == torch.bfloat16 and max(ctx.new_lens) >= _CHUNKED_FROM
-                and K.ssd_supported(self.d_head, self.d_state)):
-            # prompt portions: chunks of 64 tokens on tensor cores
+        chunked = not ctx.decode_only and proj.dtype == torch.bfloat16 and max(ctx.new_lens) >= _CHUNKED_FROM
+        if chunked and _TC_SCAN and K.ssd_tc_supported(self.d_head, self.d_state):
+            # prompt portions: chunks of 128 tokens on the tcgen05 tensor cores
+            need = K.ssd_tc_scratch_floats(ctx.new_lens, self.n_heads, self.d_head, self.d_state)
+            scratch = ws.alloc((need,), torch.float32)
+            K.ssm_scan_tc(xbc, dt, self.dt_scale, self.dt_shift, self.a_log, self.d_skip, state, ctx.cu_seqlens,
+                          ctx.slots, ctx.new_lens, y, self.n_groups, scratch, gate=gate)
+        elif chunked and K.ssd_supported(self.d_head, self.d_state):
+            # the mma.sync form: chunks of 64 tokens
             need = K.ssd_scratch_floats(ctx.new_lens, self.n_heads, self.d_head, self.d_state, self.n_groups)
             scratch = ws.alloc((need,), torch.float32)
             K.ssm_scan_chunked(xbc, dt, self.dt_scale, self.dt_shift, self.a_log, self.d_skip, state,
                                ctx.cu_seqlens, ctx.slots, ctx.new_lens, y, self.n_groups, scratch, gate=gate)
         else:
+            if chunked:
+                _note_serial(self.d_head, self.d_state)
             K.ssm_scan_seq(xbc, dt, self.dt_scale, self.dt_shift, self.a_log, self.d_skip, state,
                            ctx.cu_seqlens, ctx.slots, ctx.n_seq, y, self.n_groups, gate=gate,
                            one_token=ctx.decode_only)

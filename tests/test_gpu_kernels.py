@@ -212,6 +212,69 @@ def test_ssd_chunked_scan(H, Pd, N, G):
     assert float(state[1].abs().sum()) == 0.0
 
 
+@pytest.mark.parametrize("H,Pd,N,G,gated", [(6, 16, 16, 3, False), (4, 32, 48, 2, True), (3, 64, 64, 1, False),
+                                            (24, 64, 128, 1, True), (5, 64, 256, 1, False), (2, 128, 128, 2, True),
+                                            (2, 128, 256, 1, False), (3, 48, 80, 1, True), (2, 96, 112, 2, False)])
+def test_ssd_tcgen05_scan(H, Pd, N, G, gated):
+    """The tcgen05 scan over portions that start from a saved state, end inside a chunk, span several
+    128-token chunks and share a step with single tokens, at head and state sizes the engine's
+    models do not use (any multiples of 16); outputs against the plain recurrence, final states
+    against the serial kernel; with and without the fused gate."""
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(H * N + Pd)
+    portions = [[150, 1, 128, 9], [3, 260, 1], [128, 8, 130]]
+    lens = [sum(p) for p in portions]
+    I, conv_dim = H * Pd, H * Pd + 2 * G * N
+    xbcs = [q(torch.randn(n, conv_dim, generator=g), dtype) for n in lens]
+    dts = [q(torch.randn(n, H, generator=g), dtype) for n in lens]
+    zs = [q(torch.randn(n, I, generator=g), dtype) for n in lens]
+    zb = torch.randn(I, generator=g)
+    a_log, d_skip, shift = torch.rand(H, generator=g) * 2, torch.randn(H, generator=g), torch.randn(H, generator=g) - 1.0
+    refs = []
+    for x, dt, z in zip(xbcs, dts, zs):
+        yy = P.ssm_recurrence(x[:, :I].double().view(-1, H, Pd), x[:, I:I + G * N].double().view(-1, G, N),
+                              x[:, I + G * N:].double().view(-1, G, N), dt.double() * 0.7, a_log.double(),
+                              d_skip.double(), shift.double()).reshape(-1, I)
+        refs.append(yy * P.silu(z.double() * 1.3 + zb.double()) if gated else yy)
+    state = torch.zeros(4, H, Pd, N, device=DEV)
+    state_seq = torch.zeros(4, H, Pd, N, device=DEV)
+    slots = [2, 0, 3]
+    got = [torch.empty(n, I, dtype=dtype) for n in lens]
+    for seqs in _batch(portions):
+        T = sum(n for _, _, n in seqs)
+        xbc = torch.cat([xbcs[i][a:a + n] for i, a, n in seqs]).to(DEV)
+        dtbuf = torch.zeros(T, H + 8, dtype=dtype, device=DEV)
+        dtbuf[:, 8:] = torch.cat([dts[i][a:a + n] for i, a, n in seqs]).to(DEV)
+        zbuf = torch.cat([zs[i][a:a + n] for i, a, n in seqs]).to(DEV)
+        cu = [0]
+        for _, _, n in seqs:
+            cu.append(cu[-1] + n)
+        new_lens = [n for _, _, n in seqs]
+        out = torch.empty(T, I, dtype=dtype, device=DEV)
+        out_seq = torch.empty(T, I, dtype=dtype, device=DEV)
+        sl = i32([slots[i] for i, _, _ in seqs])
+        gate = (zbuf, 1.3, zb.to(DEV)) if gated else None
+        scratch = torch.full((K().ssd_tc_scratch_floats(new_lens, H, Pd, N),), float("nan"), device=DEV)
+        K().ssm_scan_tc(xbc, dtbuf[:, 8:], 0.7, shift.to(DEV), a_log.to(DEV), d_skip.to(DEV), state, i32(cu), sl,
+                        new_lens, out, G, scratch, gate=gate)
+        K().ssm_scan_seq(xbc, dtbuf[:, 8:], 0.7, shift.to(DEV), a_log.to(DEV), d_skip.to(DEV), state_seq, i32(cu), sl,
+                         len(seqs), out_seq, G, gate=gate)
+        t0 = 0
+        for i, a, n in seqs:
+            got[i][a:a + n] = out[t0:t0 + n].cpu()
+            t0 += n
+    assert K().tc_gemm_status(DEV) == 0
+    for i in range(3):
+        close(got[i], refs[i], dtype, what=f"tcgen05 scan seq {i}")
+    close(state, state_seq, dtype, what="final states of the tcgen05 and the serial scan")
+    assert float(state[1].abs().sum()) == 0.0
+
+
+def test_ssd_tcgen05_scan_refuses_other_sizes():
+    assert not K().ssd_tc_supported(20, 24) and not K().ssd_tc_supported(64, 272) and not K().ssd_tc_supported(144, 64)
+    assert K().ssd_tc_supported(112, 16)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("mode", ["gate", "gate_then_norm", "norm_then_gate"])
 def test_gated_norm(dtype, mode):

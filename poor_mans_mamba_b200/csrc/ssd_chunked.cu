@@ -243,17 +243,34 @@ __global__ void __launch_bounds__(128)
 // ----------------------------------------------------------------------------- phase 2
 __global__ void ssd_state_pass_kernel(const float* __restrict__ chunk_state, const float* __restrict__ chunk_decay,
                                       bf16* __restrict__ start_state, float* __restrict__ state,
-                                      const int* __restrict__ cu, const int* __restrict__ slots, int H, int PN, int q) {
+                                      const int* __restrict__ cu, const int* __restrict__ slots, int H, int PN, int q,
+                                      int n_seq, int seqs_per_block, int skip_single) {
   pdl_launch_dependents();
   pdl_wait();
   // four state elements per thread (P*N is a multiple of 4 for every compiled pair)
   const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
-  const int h = blockIdx.y, seq = blockIdx.z;
-  if (e >= PN) return;
+  const int h = blockIdx.y, seq0 = blockIdx.z * seqs_per_block;
+  // chunks of the sequences before the block's first one: the threads share the sequences, so the
+  // loads of their bounds go out together (a step may hold hundreds of sequences)
+  __shared__ int s_first[32];
+  int mine = 0;
+  for (int s = threadIdx.x; s < seq0; s += blockDim.x) mine += (cu[s + 1] - cu[s] + q - 1) / q;  // q: tokens per chunk
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+  if ((threadIdx.x & 31) == 0) s_first[threadIdx.x >> 5] = mine;
+  __syncthreads();
   int first = 0;
-  for (int s = 0; s < seq; ++s) first += (cu[s + 1] - cu[s] + q - 1) / q;  // q: tokens per chunk
-  const int nc = (cu[seq + 1] - cu[seq] + q - 1) / q;
-  if (nc <= 0) return;
+  for (int w = 0; w < static_cast<int>(blockDim.x >> 5); ++w) first += s_first[w];
+  if (e >= PN) return;
+  // a block takes several sequences in turn when a step holds many (mostly short) ones
+  for (int seq = seq0; seq < min(n_seq, seq0 + seqs_per_block); ++seq) {
+  const int n_tok = cu[seq + 1] - cu[seq];
+  const int nc = (n_tok + q - 1) / q;
+  if (nc <= 0) continue;
+  if (skip_single && n_tok == 1) {  // left to the token-serial kernel
+    first += nc;
+    continue;
+  }
   float4* sp = reinterpret_cast<float4*>(state + (static_cast<size_t>(slots[seq]) * H + h) * PN + e);
   float4 s = *sp;
   // The chain through s is short; the loads are what cost: eight chunks are requested at a time,
@@ -297,6 +314,8 @@ __global__ void ssd_state_pass_kernel(const float* __restrict__ chunk_state, con
     }
   }
   *sp = s;
+  first += nc;
+  }
 }
 
 // ----------------------------------------------------------------------------- phase 3
@@ -492,11 +511,16 @@ __global__ void __launch_bounds__(128)
 
 // The state pass alone, for chunks of `q` tokens (the tcgen05 scan of ssd_tc.cu uses it with 128).
 int launch_ssd_state_pass(const float* chunk_state, const float* chunk_decay, bf16* start_state, float* state,
-                          const int* cu, const int* slots, int n_seq, int H, int PN, int q, cudaStream_t stream) {
+                          const int* cu, const int* slots, int n_seq, int H, int PN, int q, int skip_single,
+                          cudaStream_t stream) {
   if (PN % 4 || n_seq > 65535 || H > 65535 || q <= 0) return PMM_ERR_BAD_ARGUMENT;
-  dim3 grid((PN / 4 + 255) / 256, H, n_seq);
+  // about a thousand blocks: with many sequences a block takes several of them in turn
+  const int per_seq = ((PN / 4 + 255) / 256) * H;
+  int spb = static_cast<int>((static_cast<long long>(n_seq) * per_seq + 1023) / 1024);
+  if (spb < 1) spb = 1;
+  dim3 grid((PN / 4 + 255) / 256, H, (n_seq + spb - 1) / spb);
   launch_pdl(ssd_state_pass_kernel, grid, dim3(256), 0, stream, chunk_state, chunk_decay, start_state, state, cu, slots, H,
-             PN, q);
+             PN, q, n_seq, spb, skip_single);
   return launch_status();
 }
 
@@ -524,7 +548,8 @@ int launch_ssd(const void* xbc, int ld_xbc, const void* dt_raw, long long ld_dt,
                                     dt_scale, dt_shift, a_log, cu, n_seq, chunk_state, chunk_decay, chunk_cb, H, G);
   const int PN = P * N;
   dim3 grid2((PN / 4 + 255) / 256, H, n_seq);
-  launch_pdl(ssd_state_pass_kernel, grid2, dim3(256), 0, stream, chunk_state, chunk_decay, start_state, state, cu, slots, H, PN, kQ);
+  launch_pdl(ssd_state_pass_kernel, grid2, dim3(256), 0, stream, chunk_state, chunk_decay, start_state, state, cu, slots, H, PN, kQ,
+             n_seq, 1, 0);
   launch_pdl(k3, grid, dim3(128), smem3, stream, static_cast<const bf16*>(xbc), ld_xbc, static_cast<const bf16*>(dt_raw), ld_dt,
                                    dt_scale, dt_shift, a_log, d_skip, cu, n_seq, start_state, chunk_cb,
                                    static_cast<bf16*>(y), H, G, static_cast<const bf16*>(z_raw), ld_z, z_scale, z_bias);

@@ -40,7 +40,8 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 // Launches the state pass of ssd_chunked.cu for chunks of `q` tokens.
 int launch_ssd_state_pass(const float* chunk_state, const float* chunk_decay, bf16* start_state, float* state,
-                          const int* cu, const int* slots, int n_seq, int H, int PN, int q, cudaStream_t stream);
+                          const int* cu, const int* slots, int n_seq, int H, int PN, int q, int skip_single,
+                          cudaStream_t stream);
 
 __device__ __forceinline__ int tq_swz(int row, int chunk) {
   return (row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4);
@@ -70,20 +71,60 @@ __device__ __forceinline__ void tmem_ld16(unsigned taddr, unsigned* r) {
       : "memory");
 }
 
-// Which (sequence, first token, length) chunk `c` is; chunk ids run over the sequences in order.
-__device__ __forceinline__ bool tq_locate(const int* __restrict__ cu, int n_seq, int c, int& t0, int& len) {
-  int acc = 0;
-  for (int seq = 0; seq < n_seq; ++seq) {
-    const int n = cu[seq + 1] - cu[seq];
-    const int nc = (n + kTQ - 1) / kTQ;
-    if (c < acc + nc) {
-      t0 = cu[seq] + (c - acc) * kTQ;
-      len = min(kTQ, cu[seq + 1] - t0);
-      return true;
+// Which (first token, length) chunk `c` is; chunk ids run over the sequences in order.  Called by
+// all threads of the block (a multiple of 32, at most 1,024); `sh` is shared memory for 36 ints.
+// Every thread takes sequences tid, tid + blockDim, ...: the loads of the sequence bounds go out
+// together instead of one after the other (a step may hold hundreds of sequences).
+__device__ __forceinline__ bool tq_locate(const int* __restrict__ cu, int n_seq, int c, int& t0, int& len, int& seq_tokens,
+                                          int* sh) {
+  if (n_seq <= 4) {  // few sequences: every thread walks them itself
+    int acc = 0;
+    for (int seq = 0; seq < n_seq; ++seq) {
+      const int lo = cu[seq], hi = cu[seq + 1];
+      const int nc = (hi - lo + kTQ - 1) / kTQ;
+      if (c < acc + nc) {
+        t0 = lo + (c - acc) * kTQ;
+        len = min(kTQ, hi - t0);
+        seq_tokens = hi - lo;
+        return true;
+      }
+      acc += nc;
     }
-    acc += nc;
+    return false;
   }
-  return false;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
+  if (tid == 0) sh[34] = -1;
+  int base = 0;  // chunks of the sequences before this round
+  for (int s0 = 0; s0 < n_seq; s0 += blockDim.x) {
+    const int s = s0 + tid;
+    int lo = 0, hi = 0;
+    if (s < n_seq) lo = cu[s], hi = cu[s + 1];
+    const int nc = (hi - lo + kTQ - 1) / kTQ;
+    int incl = nc;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    if (lane == 31) sh[warp] = incl;
+    __syncthreads();
+    int before = base;
+    for (int w = 0; w < warp; ++w) before += sh[w];
+    const int first = before + incl - nc;
+    if (s < n_seq && c >= first && c < first + nc) {
+      sh[34] = lo + (c - first) * kTQ;
+      sh[35] = hi;
+      sh[33] = hi - lo;
+    }
+    for (int w = 0; w < n_warps; ++w) base += sh[w];
+    __syncthreads();
+    if (sh[34] >= 0 || base > c) break;  // the same decision in every thread
+  }
+  if (sh[34] < 0) return false;
+  t0 = sh[34];
+  len = min(kTQ, sh[35] - t0);
+  seq_tokens = sh[33];
+  return true;
 }
 
 // 128 consecutive threads (four warps, `t` = 0..127 the thread's token): delta_t and cs_t (inclusive
@@ -161,7 +202,7 @@ __global__ void __launch_bounds__(kTState)
                         float dt_scale, const float* __restrict__ dt_shift, const float* __restrict__ a_log,
                         const int* __restrict__ cu, int n_seq, float* __restrict__ chunk_state,
                         float* __restrict__ chunk_decay, float* __restrict__ chunk_dt, int H, int P, int N, int G,
-                        int slabs_per_group, int tmem_cols, int* __restrict__ status) {
+                        int slabs_per_group, int tmem_cols, int skip_single, int* __restrict__ status) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ unsigned char smem_raw[];
@@ -174,7 +215,10 @@ __global__ void __launch_bounds__(kTState)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int c = blockIdx.x;
   int t0, len;
-  if (!tq_locate(cu, n_seq, c, t0, len)) return;
+  __shared__ int s_loc[36];
+  int seq_tokens;
+  if (!tq_locate(cu, n_seq, c, t0, len, seq_tokens, s_loc)) return;
+  if (skip_single && seq_tokens == 1) return;  // lone tokens of a mixed step are the token-serial kernel's
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sA = tiles;                 // [128 tokens][128 channels]: two atoms of 64 channels
   unsigned char* sB = tiles + 2 * kTSub;     // [128 tokens][N]: one atom per 64 state columns
@@ -185,6 +229,38 @@ __global__ void __launch_bounds__(kTState)
   const int n_ch = min(kTQ, ch_per_group - slab * kTQ);
   const int head0 = ch0 / P;
   const int n_heads = (ch0 + n_ch - 1) / P - head0 + 1;  // <= 8: a head has at least 16 channels
+
+  if (len == 1) {
+    // A lone token (a decoding request in a mixed step): S_local[ch][n] = delta x[ch] B[n], no product
+    // worth a tensor core.  Thread = (channel, quarter of the state columns).
+    if (tid < n_heads) {
+      const int h = head0 + tid;
+      const float d = softplus_f(__bfloat162float(dt_raw[static_cast<long long>(t0) * ld_dt + h]) * dt_scale + dt_shift[h]);
+      const float a = -expf(a_log[h]) * d;
+      s_w[tid][0] = d;
+      if (h * P >= ch0) {
+        float* dtp = chunk_dt + (static_cast<size_t>(c) * H + h) * (2 * kTQ);
+        dtp[0] = d;
+        dtp[kTQ] = a * kLog2e;
+        chunk_decay[static_cast<size_t>(c) * H + h] = expf(a);
+      }
+    }
+    __syncthreads();
+    const int ch = tid & (kTQ - 1), quarter = tid >> 7;
+    if (ch < n_ch) {
+      const bf16* rowp = xbc + static_cast<size_t>(t0) * ld_xbc;
+      const float xv = __bfloat162float(rowp[ch0 + ch]) * s_w[(ch0 + ch) / P - head0][0];
+      const bf16* bp = rowp + I + g * N;
+      float* dst = chunk_state + (static_cast<size_t>(c) * I + ch0 + ch) * N;
+      for (int n = quarter * (N / 4); n < (quarter + 1) * (N / 4); n += 4) {
+        const uint2 braw = *reinterpret_cast<const uint2*>(bp + n);
+        const float2 b01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&braw.x));
+        const float2 b23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&braw.y));
+        *reinterpret_cast<float4*>(dst + n) = make_float4(xv * b01.x, xv * b01.y, xv * b23.x, xv * b23.y);
+      }
+    }
+    return;
+  }
 
   if (tid == 0) {
     mbar_init(&bar, 1);
@@ -338,7 +414,7 @@ __global__ void __launch_bounds__(kTOut, 2)
                          const float* __restrict__ d_skip, const int* __restrict__ cu, int n_seq,
                          const bf16* __restrict__ start_state, bf16* __restrict__ y, int H, int P, int N, int G, int PB,
                          const bf16* __restrict__ z_raw, long long ld_z, float z_scale, const float* __restrict__ z_bias,
-                         int z_vec, int* __restrict__ status) {
+                         int z_vec, int skip_single, int* __restrict__ status) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ unsigned char smem_raw[];
@@ -351,7 +427,10 @@ __global__ void __launch_bounds__(kTOut, 2)
   const int row = tid & (kTQ - 1), part = tid >> 7, rw = warp & 3;
   const int c = blockIdx.x;
   int t0, len;
-  if (!tq_locate(cu, n_seq, c, t0, len)) return;
+  __shared__ int s_loc[36];
+  int seq_tokens;
+  if (!tq_locate(cu, n_seq, c, t0, len, seq_tokens, s_loc)) return;
+  if (skip_single && seq_tokens == 1) return;  // lone tokens of a mixed step are the token-serial kernel's
   const int slabs = P / PB;
   const int h = blockIdx.y / slabs, p0 = (blockIdx.y % slabs) * PB;
   const int I = H * P, g = h / (H / G);
@@ -362,6 +441,63 @@ __global__ void __launch_bounds__(kTOut, 2)
   unsigned char* sBS = sC + (nb > 2 ? nb : 2) * kTSub;        // [128 tokens + PB channels][N], K-major; later z [128][PB]
   unsigned char* sX = sBS + nb * bs_sub;                      // [128 tokens][PB], MN-major; later y, in place
   const size_t col0 = static_cast<size_t>(h) * P + p0;
+
+  if (len == 1) {
+    // A lone token: y[p] = (C.B) delta x[p] + exp(cs_0) C.S[p] + D x[p], a warp per channel.
+    const float* dtp = chunk_dt + (static_cast<size_t>(c) * H + h) * (2 * kTQ);
+    const float d0 = dtp[0], e0 = tq_ex2(dtp[kTQ]), Dh1 = d_skip[h];
+    const bf16* rowp = xbc + static_cast<size_t>(t0) * ld_xbc;
+    const bf16* bp = rowp + I + g * N;
+    const bf16* cp = bp + G * N;
+    float cb = 0.f;
+    float cv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (lane * 8 < N) {
+      const uint4 cq = *reinterpret_cast<const uint4*>(cp + lane * 8), bq = *reinterpret_cast<const uint4*>(bp + lane * 8);
+      const unsigned cw[4] = {cq.x, cq.y, cq.z, cq.w}, bw[4] = {bq.x, bq.y, bq.z, bq.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 cf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&cw[e]));
+        const float2 bf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bw[e]));
+        cv[2 * e] = cf.x, cv[2 * e + 1] = cf.y;
+        cb += cf.x * bf.x + cf.y * bf.y;
+      }
+    }
+    cb = warp_sum(cb);
+    constexpr int kW = kTOut / 32;
+    for (int pbase = warp; pbase < PB; pbase += 4 * kW) {  // four channels of this warp at a time: their loads go out together
+      uint4 sq[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int p = pbase + u * kW;
+        sq[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (p < PB && lane * 8 < N)
+          sq[u] = *reinterpret_cast<const uint4*>(start_state + (static_cast<size_t>(c) * I + col0 + p) * N + lane * 8);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int p = pbase + u * kW;
+        if (p >= PB) break;  // the same in every lane
+        const unsigned sw[4] = {sq[u].x, sq[u].y, sq[u].z, sq[u].w};
+        float acc = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 sf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&sw[e]));
+          acc += cv[2 * e] * sf.x + cv[2 * e + 1] * sf.y;
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) {
+          const float xv = __bfloat162float(rowp[col0 + p]);
+          float v = cb * d0 * xv + e0 * acc + Dh1 * xv;
+          if (z_raw) {
+            const float zv = __bfloat162float(z_raw[static_cast<long long>(t0) * ld_z + col0 + p]);
+            v *= silu_fast(zv * z_scale + (z_bias ? z_bias[col0 + p] : 0.f));
+          }
+          y[static_cast<size_t>(t0) * I + col0 + p] = __float2bfloat16_rn(v);
+        }
+      }
+    }
+    return;
+  }
 
   if (tid == 0) {
     mbar_init(&bar1, 1);
@@ -545,12 +681,14 @@ PMM_EXPORT int pmm_ssd_tc_supported(int P, int N) {
 // n_chunks*H*256 floats, start_state n_chunks*H*P*N bfloat16 (16-byte aligned); n_chunks = sum over
 // sequences of ceil(new tokens / 128).
 // z_raw (or nullptr): the gate's input [T, ld_z], y <- y * silu(z_raw * z_scale + z_bias).
+// skip_single: sequences that bring exactly one token are left alone (state and y): in a mixed step
+// the token-serial kernel takes them (pmm_ssm_scan_seq with one_token = 2).
 // status: one int in device memory that stays 0 unless a bounded wait gave up.
 PMM_EXPORT int pmm_ssd_tc(const void* xbc, int ld_xbc, const void* dt_raw, long long ld_dt, float dt_scale,
                           const float* dt_shift, const float* a_log, const float* d_skip, float* state, const int* cu,
                           const int* slots, void* y, float* chunk_state, float* chunk_decay, float* chunk_dt,
                           void* start_state, int n_seq, int n_chunks, int H, int P, int N, int G, const void* z_raw, long long ld_z,
-                          float z_scale, const float* z_bias, int* status, cudaStream_t stream) {
+                          float z_scale, const float* z_bias, int skip_single, int* status, cudaStream_t stream) {
   using namespace pmm;
   if (n_seq <= 0 || n_chunks <= 0) return 0;
   if (!pmm_ssd_tc_supported(P, N) || H <= 0 || G <= 0 || H % G || n_seq > 65535 || !chunk_state || !chunk_decay ||
@@ -583,12 +721,12 @@ PMM_EXPORT int pmm_ssd_tc(const void* xbc, int ld_xbc, const void* dt_raw, long 
   const bf16* dtb = static_cast<const bf16*>(dt_raw);
   launch_pdl(ssd_tc_state_kernel, dim3(n_chunks, G * slabs_per_group), dim3(kTState), smem1, stream, xb, ld_xbc, dtb, ld_dt,
              dt_scale, dt_shift, a_log, cu, n_seq, chunk_state, chunk_decay, chunk_dt, H, P, N, G, slabs_per_group, tmem_cols,
-             status);
+             skip_single, status);
   int rc = launch_ssd_state_pass(chunk_state, chunk_decay, static_cast<bf16*>(start_state), state, cu, slots, n_seq, H,
-                                 P * N, kTQ, stream);
+                                 P * N, kTQ, skip_single, stream);
   if (rc != 0) return rc;
   launch_pdl(ssd_tc_output_kernel, dim3(n_chunks, H * (P / PB)), dim3(kTOut), smem3, stream, xb, ld_xbc,
              static_cast<const float*>(chunk_dt), d_skip, cu, n_seq, static_cast<const bf16*>(start_state),
-             static_cast<bf16*>(y), H, P, N, G, PB, static_cast<const bf16*>(z_raw), ld_z, z_scale, z_bias, z_vec, status);
+             static_cast<bf16*>(y), H, P, N, G, PB, static_cast<const bf16*>(z_raw), ld_z, z_scale, z_bias, z_vec, skip_single, status);
   return launch_status();
 }

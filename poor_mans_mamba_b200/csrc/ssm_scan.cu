@@ -27,7 +27,7 @@ __global__ void __launch_bounds__(kScanRows* kScanTpr)
                         float* __restrict__ state, const int* __restrict__ cu,
                         const int* __restrict__ slots, S* __restrict__ y, int H, int P, int N,
                         int G, const S* __restrict__ z_raw, long long ld_z, float z_scale,
-                        const float* __restrict__ z_bias) {
+                        const float* __restrict__ z_bias, int one_token) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane_n = threadIdx.x % kScanTpr;
@@ -36,6 +36,7 @@ __global__ void __launch_bounds__(kScanRows* kScanTpr)
   const int s = blockIdx.z;
   const int t0 = cu[s], t1 = cu[s + 1];
   if (t1 <= t0) return;
+  if (one_token == 2 && t1 - t0 != 1) return;  // only the lone tokens of a mixed step
   const bool row_ok = p < P;
   const int I = H * P;
   const int g = h / (H / G);
@@ -94,8 +95,9 @@ __global__ void __launch_bounds__(kScanRows* kScanTpr)
 // The same walk with four neighbouring state columns per thread and access: state rows move as
 // 16-byte pieces (a warp touches four whole 128-byte lines per instruction), B and C as four
 // values at a time.  Needs N % 4 == 0 and rows of xbc whose B and C parts start on 8-byte
-// (bfloat16) / 16-byte (float) boundaries.  one_token: sequence s brings exactly token s (decode),
-// so nothing waits for the sequence bounds.
+// (bfloat16) / 16-byte (float) boundaries.  one_token 1: sequence s brings exactly token s (decode),
+// so nothing waits for the sequence bounds.  one_token 2: only the sequences that bring exactly one
+// token are walked (the lone tokens of a mixed step; the chunked scan takes the others).
 __device__ __forceinline__ float4 scan_ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ float4 scan_ld4(const __nv_bfloat16* p) {
   const uint2 raw = *reinterpret_cast<const uint2*>(p);
@@ -130,12 +132,13 @@ __global__ void __launch_bounds__(kScanRows* kScanTpr)
   const float shift = dt_shift[h];
   const int slot = slots[s];
   int t0 = s, t1 = s + 1;
-  if (!one_token) {
+  if (one_token != 1) {
     t0 = cu[s];
     t1 = cu[s + 1];
   }
   pdl_wait();
   if (t1 <= t0) return;
+  if (one_token == 2 && t1 - t0 != 1) return;  // only the lone tokens of a mixed step
 
   float4 st[NV];
   float* srow = state + ((static_cast<size_t>(slot) * H + h) * P + (row_ok ? p : 0)) * N;
@@ -267,7 +270,7 @@ int launch_scan(const void* xbc, int ld_xbc, const void* dt_raw, long long ld_dt
 #define PMM_SCAN_CASE(NPT)                                                                         \
   launch_pdl(ssm_scan_seq_kernel<S, NPT>, grid, block, 0, stream, static_cast<const S*>(xbc), ld_xbc,  \
              static_cast<const S*>(dt_raw), ld_dt, dt_scale, dt_shift, a_log, d_skip, state, cu, slots, \
-             static_cast<S*>(y), H, P, N, G, static_cast<const S*>(z_raw), ld_z, z_scale, z_bias)
+             static_cast<S*>(y), H, P, N, G, static_cast<const S*>(z_raw), ld_z, z_scale, z_bias, one_token)
   if (npt <= 1) PMM_SCAN_CASE(1);
   else if (npt <= 2) PMM_SCAN_CASE(2);
   else if (npt <= 4) PMM_SCAN_CASE(4);

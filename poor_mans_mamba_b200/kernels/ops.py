@@ -49,7 +49,7 @@ _SIGNATURES = {
     "pmm_ssd_tc_supported": [c_int, c_int],
     "pmm_ssd_tc": [c_void_p, c_int, c_void_p, c_longlong, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                   c_longlong, c_float, c_void_p, c_void_p, c_void_p],
+                   c_longlong, c_float, c_void_p, c_int, c_void_p, c_void_p],
     "pmm_gated_norm": [c_void_p, c_void_p, c_longlong, c_float, c_void_p, c_void_p, c_float, c_int,
                        c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_qkv_rope_store": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_float,
@@ -413,10 +413,12 @@ def _gate_args(gate, out: Tensor, what: str):
 
 def ssm_scan_seq(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Tensor, a_log: Tensor,
                  d_skip: Tensor, state: Tensor, cu: Tensor, slots: Tensor, n_seq: int, out: Tensor,
-                 n_groups: int, gate=None, one_token: bool = False) -> None:
+                 n_groups: int, gate=None, one_token: bool = False, only_single: bool = False) -> None:
     """Token-serial Mamba2 recurrence from the saved state; state[slots, H, P, N] is updated.
     ``gate`` = (z view [T, I], z_scale, z_bias or None): the output is y * silu(z*z_scale + z_bias).
-    ``one_token``: sequence s brings exactly token s (a decode step); ``cu`` is then not read."""
+    ``one_token``: sequence s brings exactly token s (a decode step); ``cu`` is then not read.
+    ``only_single``: only the sequences that bring exactly one token are walked (the lone tokens of
+    a mixed step, whose longer portions the chunked scan takes); the others are left alone."""
     _cuda(xbc, dt_raw, dt_shift, a_log, d_skip, state, cu, slots, out)
     _need(state.dtype == torch.float32 and state.dim() == 4 and state.is_contiguous(),
           "ssm_scan: state must be contiguous float32 [slots, H, P, N]")
@@ -433,7 +435,7 @@ def ssm_scan_seq(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Tensor,
     zp, ld_z, zs, zb = _gate_args(gate, out, "ssm_scan")
     _call("pmm_ssm_scan_seq", xbc.data_ptr(), ld_x, dt_raw.data_ptr(), ld_dt, float(dt_scale),
           dt_shift.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), cu.data_ptr(),
-          slots.data_ptr(), out.data_ptr(), n_seq, H, P, N, n_groups, zp, ld_z, zs, zb, int(bool(one_token)),
+          slots.data_ptr(), out.data_ptr(), n_seq, H, P, N, n_groups, zp, ld_z, zs, zb, 2 if only_single else int(bool(one_token)),
           _dt(xbc), _stream())
 
 
@@ -518,10 +520,11 @@ def ssd_tc_scratch_floats(new_lens: Sequence[int], n_heads: int, d_head: int, d_
 
 def ssm_scan_tc(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Tensor, a_log: Tensor, d_skip: Tensor,
                 state: Tensor, cu: Tensor, slots: Tensor, new_lens: Sequence[int], out: Tensor, n_groups: int,
-                scratch: Tensor, gate=None) -> None:
+                scratch: Tensor, gate=None, skip_single: bool = False) -> None:
     """The Mamba2 recurrence over prompt portions in chunks of 128 tokens on the tcgen05 tensor
     cores (bfloat16 activations); same contract as ssm_scan_seq.  ``scratch``: float32, at least
-    ssd_tc_scratch_floats(...) elements."""
+    ssd_tc_scratch_floats(...) elements.  ``skip_single``: sequences that bring exactly one token are
+    left alone (their rows of ``out`` and their states): ssm_scan_seq(only_single=True) takes them."""
     _cuda(xbc, dt_raw, dt_shift, a_log, d_skip, state, cu, slots, out, scratch)
     _need(state.dtype == torch.float32 and state.dim() == 4 and state.is_contiguous(),
           "ssm_scan: state must be contiguous float32 [slots, H, P, N]")
@@ -550,7 +553,7 @@ def ssm_scan_tc(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Tensor, 
     _call("pmm_ssd_tc", xbc.data_ptr(), ld_x, dt_raw.data_ptr(), ld_dt, float(dt_scale), dt_shift.data_ptr(),
           a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), cu.data_ptr(), slots.data_ptr(), out.data_ptr(),
           chunk_state, chunk_decay, chunk_dt, start_state, len(new_lens), n_chunks, H, P, N, n_groups, zp, ld_z, zs, zb,
-          _tc_status(xbc.device).data_ptr(), _stream())
+          int(bool(skip_single)), _tc_status(xbc.device).data_ptr(), _stream())
 
 
 def gated_norm(y: Tensor, z_raw: Tensor, z_scale: float, z_bias: Optional[Tensor],

@@ -189,8 +189,14 @@ class Mamba2Mixer(Mixer):
             # prompt portions: chunks of 128 tokens on the tcgen05 tensor cores
             need = K.ssd_tc_scratch_floats(ctx.new_lens, self.n_heads, self.d_head, self.d_state)
             scratch = ws.alloc((need,), torch.float32)
+            # in a mixed step the lone tokens (decoding requests) go through the token-serial kernel: a
+            # 128-token chunk for one token is two tile-sized blocks of work for nothing
+            lone = ctx.n_seq > 1 and any(n == 1 for n in ctx.new_lens)
             K.ssm_scan_tc(xbc, dt, self.dt_scale, self.dt_shift, self.a_log, self.d_skip, state, ctx.cu_seqlens,
-                          ctx.slots, ctx.new_lens, y, self.n_groups, scratch, gate=gate)
+                          ctx.slots, ctx.new_lens, y, self.n_groups, scratch, gate=gate, skip_single=lone)
+            if lone:
+                K.ssm_scan_seq(xbc, dt, self.dt_scale, self.dt_shift, self.a_log, self.d_skip, state,
+                               ctx.cu_seqlens, ctx.slots, ctx.n_seq, y, self.n_groups, gate=gate, only_single=True)
         elif chunked and K.ssd_supported(self.d_head, self.d_state):
             # the mma.sync form: chunks of 64 tokens
             need = K.ssd_scratch_floats(ctx.new_lens, self.n_heads, self.d_head, self.d_state, self.n_groups)

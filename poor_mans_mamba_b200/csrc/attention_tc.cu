@@ -1,5 +1,5 @@
 // Paged grouped-query attention for prompt portions on the fifth-generation tensor cores
-// (bfloat16 storage, float accumulate, head size 64, page sizes that are multiples of 64).
+// (bfloat16 storage, float accumulate, head size 64 or 128, page sizes that are multiples of 64).
 //
 // One block = 128 query rows of ONE sequence and ONE key/value head (a row is a (token, query
 // head of the group) pair, as in the mma.sync kernel) and one key split.  It walks its keys in
@@ -21,8 +21,10 @@
 // Warp roles: 0 = TMA producer (two stages for K, one for V; a tile's copy is requested the moment
 // the product that read the stage before has finished), 1 = tensor-memory owner and MMA issuer
 // (S of the next tile is issued as soon as the softmax threads have taken the current S into
-// registers, so the tensor core works while they compute), 2..5 = softmax and output.  96 KB of
-// shared memory and 256 columns of tensor memory a block: two blocks per SM.
+// registers, so the tensor core works while they compute), 2..5 = softmax and output.  Head size
+// 64: 96 KB of shared memory and 256 columns of tensor memory a block, two blocks per SM.  Head
+// size 128: every tile is two sub-tiles of 64 head-size columns (Q, K and V each 32 KB a stage,
+// 160 KB a block, O in 128 columns), one block per SM.
 // With several key splits the block writes (max, sum, unnormalised output) and the last block of
 // a row tile merges them, as in the mma.sync kernel.  Every mbarrier wait is bounded (status
 // codes 11..15 in *status, the block then leaves its loops, waits for its copies in flight and
@@ -39,19 +41,20 @@ using bf16 = __nv_bfloat16;
 constexpr int kAtM = 128;       // query rows per block
 constexpr int kAtKeys = 128;    // keys per tile
 constexpr int kAtBox = 64;      // keys per TMA box (inside one page)
-constexpr int kAtDh = 64;       // head size
+constexpr int kAtDhBlock = 64;  // head-size columns per sub-tile (128 bytes of bfloat16)
 constexpr int kAtThreads = 192;
-constexpr int kAtTmemCols = 256;  // S: columns 0..127, O: columns 128..191
+constexpr int kAtTmemCols = 256;  // S: columns 0..127, O: columns 128..128+head size
 constexpr float kAtLazy = 8.f;    // how far (log2) a row's maximum may run ahead of the one in use
 constexpr int kAtBtCap = 512;
-constexpr int kAtQBytes = kAtM * kAtDh * 2;         // 16 KB
-constexpr int kAtKBytes = kAtKeys * kAtDh * 2;      // 16 KB
+constexpr int kAtSubBytes = kAtM * kAtDhBlock * 2;  // 16 KB: 128 rows (queries or keys) x 64 head-size columns
 constexpr int kAtPBytes = kAtM * kAtKeys * 2;       // 32 KB: two sub-tiles of 64 keys
-constexpr size_t kAtSmem = kAtQBytes + 3 * kAtKBytes + kAtPBytes + 1024 /*alignment*/;  // Q, K x 2, V, P
+constexpr size_t at_smem(int dh) {  // Q, K x 2, V (each head size / 64 sub-tiles), P
+  return static_cast<size_t>(4 * (dh / kAtDhBlock)) * kAtSubBytes + kAtPBytes + 1024 /*alignment*/;
+}
 
 // kind::f16 instruction descriptors: float accumulate, bfloat16 operands, A K-major.
 constexpr unsigned kAtIdescS = (1u << 4) | (1u << 7) | (1u << 10) | ((kAtKeys >> 3) << 17) | ((kAtM >> 4) << 24);               // B = K tile, K-major
-constexpr unsigned kAtIdescO = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((kAtDh >> 3) << 17) | ((kAtM >> 4) << 24);   // B = V tile, MN-major
+constexpr unsigned kAtIdescO = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((kAtDhBlock >> 3) << 17) | ((kAtM >> 4) << 24);   // B = 64 columns of the V tile, MN-major
 
 __device__ __forceinline__ float at_ex2(float x) {
   float y;
@@ -68,7 +71,8 @@ __device__ __forceinline__ int at_swizzled(int row, int chunk) {
   return (row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4);
 }
 
-__global__ void __launch_bounds__(kAtThreads, 2)
+template <int DH>
+__global__ void __launch_bounds__(kAtThreads, DH == 64 ? 2 : 1)
     attention_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ CUtensorMap map_kv,
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ positions,
                         const int* __restrict__ cu, bf16* __restrict__ out, float* __restrict__ part_o,
@@ -77,7 +81,9 @@ __global__ void __launch_bounds__(kAtThreads, 2)
                         int* __restrict__ status) {
   pdl_launch_dependents();
   pdl_wait();
-  constexpr int DH = kAtDh;
+  constexpr int NSUB = DH / kAtDhBlock;            // sub-tiles of 64 head-size columns
+  constexpr int kAtQBytes = NSUB * kAtSubBytes;    // Q, a K stage, the V stage
+  constexpr int kAtKBytes = NSUB * kAtSubBytes;
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long bar_q, bar_kfull[2], bar_vfull, bar_s, bar_sfree, bar_p, bar_pv;
   __shared__ unsigned s_tmem_base;
@@ -92,7 +98,7 @@ __global__ void __launch_bounds__(kAtThreads, 2)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = Hq / Hkv;
-  const int tpt = kAtM / G;  // tokens per tile (host guarantees that G divides 128)
+  const int tpt = kAtM / G;  // tokens per tile; rows beyond tpt * G stay empty when G does not divide 128
   const int hk = blockIdx.y, z = blockIdx.z;
 
   // which sequence and which of its tokens this tile covers (heavy tiles first, as in the mma.sync kernel)
@@ -166,16 +172,22 @@ __global__ void __launch_bounds__(kAtThreads, 2)
         // before it requested V_{j-1}, finished after S_{j-2}: the stage is free.
         unsigned char* kd = sK + (j & 1) * kAtKBytes;
         mbar_expect_tx(&bar_kfull[j & 1], kAtKBytes);
-        tma_load_2d(kd, &map_kv, hk * DH, r0, &bar_kfull[j & 1]);
-        tma_load_2d(kd + kAtKBytes / 2, &map_kv, hk * DH, r1, &bar_kfull[j & 1]);
+#pragma unroll
+        for (int d = 0; d < NSUB; ++d) {  // a sub-tile = 64 head-size columns of 128 keys: two boxes of 64 keys
+          tma_load_2d(kd + d * kAtSubBytes, &map_kv, hk * DH + d * kAtDhBlock, r0, &bar_kfull[j & 1]);
+          tma_load_2d(kd + d * kAtSubBytes + kAtSubBytes / 2, &map_kv, hk * DH + d * kAtDhBlock, r1, &bar_kfull[j & 1]);
+        }
         k_issued = j + 1;
         if (j > 0 && !mbar_wait(&bar_pv, (j - 1) & 1, abort_flag)) {  // P V_{j-1} done: the V stage is free
           give_up(12);
           break;
         }
         mbar_expect_tx(&bar_vfull, kAtKBytes);
-        tma_load_2d(sV, &map_kv, hk * DH, r0 + page_size, &bar_vfull);
-        tma_load_2d(sV + kAtKBytes / 2, &map_kv, hk * DH, r1 + page_size, &bar_vfull);
+#pragma unroll
+        for (int d = 0; d < NSUB; ++d) {
+          tma_load_2d(sV + d * kAtSubBytes, &map_kv, hk * DH + d * kAtDhBlock, r0 + page_size, &bar_vfull);
+          tma_load_2d(sV + d * kAtSubBytes + kAtSubBytes / 2, &map_kv, hk * DH + d * kAtDhBlock, r1 + page_size, &bar_vfull);
+        }
         v_issued = j + 1;
       }
       if (s_abort) {
@@ -191,11 +203,12 @@ __global__ void __launch_bounds__(kAtThreads, 2)
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0 && n_tiles > 0) {
-      const unsigned long long q_desc = umma_desc(sQ);
       auto issue_s = [&](int j) {  // S_j = Q K_j^T
-        const unsigned long long b_desc = umma_desc(sK + (j & 1) * kAtKBytes);
+        unsigned char* kst = sK + (j & 1) * kAtKBytes;
 #pragma unroll
-        for (int k = 0; k < DH / 16; ++k) umma_f16(tmem_base, q_desc + 2 * k, b_desc + 2 * k, kAtIdescS, k > 0 ? 1u : 0u);
+        for (int k = 0; k < DH / 16; ++k)  // 16 head-size columns a step, four steps a sub-tile
+          umma_f16(tmem_base, umma_desc(sQ + (k >> 2) * kAtSubBytes) + 2 * (k & 3), umma_desc(kst + (k >> 2) * kAtSubBytes) + 2 * (k & 3),
+                   kAtIdescS, k > 0 ? 1u : 0u);
         umma_commit(&bar_s);
       };
       bool ok = mbar_wait(&bar_q, 0, abort_flag) && mbar_wait(&bar_kfull[0], 0, abort_flag);
@@ -223,11 +236,15 @@ __global__ void __launch_bounds__(kAtThreads, 2)
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         {  // O += P V_j: A = P (two sub-tiles of 64 keys), B = V rows as they lie in the cache
            // (MN-major): 16 keys further = 16 rows of 128 bytes
-          const unsigned long long v_desc = umma_desc(sV);
 #pragma unroll
-          for (int k = 0; k < kAtKeys / 16; ++k) {
-            const unsigned long long a_desc = umma_desc(sP + (k / 4) * (kAtPBytes / 2)) + 2 * (k % 4);
-            umma_f16(tmem_base + kAtKeys, a_desc, v_desc + ((k * 16 * 128) >> 4), kAtIdescO, (j > 0 || k > 0) ? 1u : 0u);
+          for (int d = 0; d < NSUB; ++d) {  // 64 head-size columns of O an instruction
+            const unsigned long long v_desc = umma_desc(sV + d * kAtSubBytes);
+#pragma unroll
+            for (int k = 0; k < kAtKeys / 16; ++k) {
+              const unsigned long long a_desc = umma_desc(sP + (k / 4) * (kAtPBytes / 2)) + 2 * (k % 4);
+              umma_f16(tmem_base + kAtKeys + d * kAtDhBlock, a_desc, v_desc + ((k * 16 * 128) >> 4), kAtIdescO,
+                       (j > 0 || k > 0) ? 1u : 0u);
+            }
           }
           umma_commit(&bar_pv);
         }
@@ -247,7 +264,7 @@ __global__ void __launch_bounds__(kAtThreads, 2)
 #pragma unroll
       for (int c = 0; c < DH / 8; ++c) {
         const uint4 v = row_ok ? *reinterpret_cast<const uint4*>(src + c * 8) : make_uint4(0u, 0u, 0u, 0u);
-        *reinterpret_cast<uint4*>(sQ + at_swizzled(row, c)) = v;
+        *reinterpret_cast<uint4*>(sQ + (c >> 3) * kAtSubBytes + at_swizzled(row, c & 7)) = v;
       }
       fence_proxy_async();
       mbar_arrive(&bar_q);
@@ -450,12 +467,13 @@ __global__ void __launch_bounds__(kAtThreads, 2)
 
 }  // namespace pmm
 
-// Whether the tcgen05 attention takes this shape: head size 64, a group size that divides 128,
-// pages that hold whole boxes of 64 keys.
+// Whether the tcgen05 attention takes this shape: head size 64 or 128, up to 64 query heads per
+// key/value head (a tile holds floor(128 / group) tokens; with a group size that does not divide
+// 128 its last rows stay empty), pages that hold whole boxes of 64 keys.
 PMM_EXPORT int pmm_attention_tc_supported(int Hq, int Hkv, int Dh, int page_size) {
   if (Hkv <= 0 || Hq % Hkv) return 0;
   const int G = Hq / Hkv;
-  return (Dh == pmm::kAtDh && pmm::kAtM % G == 0 && page_size > 0 && page_size % pmm::kAtBox == 0) ? 1 : 0;
+  return ((Dh == 64 || Dh == 128) && G <= 64 && page_size > 0 && page_size % pmm::kAtBox == 0) ? 1 : 0;
 }
 
 // q [T, Hq*64] rotated queries; pool [n_pages + spare, 2, page_size, Hkv*64]; n_tiles = sum over
@@ -475,25 +493,26 @@ PMM_EXPORT int pmm_attention_tc(const void* q, const void* pool, long long pool_
   if (n_splits > 1 && (!part_o || !part_ml || !split_counter || split_len <= 0 || split_len % pmm::kAtBox))
     return PMM_ERR_BAD_ARGUMENT;
   if (n_splits == 1) split_len = 0x40000000;
-  // the whole pool as a matrix [pages * 2 * page_size, Hkv * 64]; a box is 64 rows x 64 columns
+  // the whole pool as a matrix [pages * 2 * page_size, Hkv * head size]; a box is 64 rows x 64 columns
   pmm::EncodeTiledFn fn = pmm::encode_tiled_fn();
   if (!fn) return PMM_ERR_BAD_ARGUMENT;
   CUtensorMap map;
   const long long kv_dim = static_cast<long long>(Hkv) * Dh;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(kv_dim), static_cast<cuuint64_t>(pool_pages * 2 * page_size)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(kv_dim) * 2};
-  const cuuint32_t box[2] = {pmm::kAtDh, pmm::kAtBox};
+  const cuuint32_t box[2] = {pmm::kAtDhBlock, pmm::kAtBox};
   const cuuint32_t elem[2] = {1, 1};
   if (fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, elem,
          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return PMM_ERR_BAD_ARGUMENT;
-  auto kern = pmm::attention_tc_kernel;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pmm::kAtSmem));
+  auto kern = Dh == 64 ? pmm::attention_tc_kernel<64> : pmm::attention_tc_kernel<128>;
+  const size_t smem = pmm::at_smem(Dh);
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
   if (e != cudaSuccess) return static_cast<int>(e);
   dim3 grid(n_tiles, Hkv, n_splits);
-  pmm::launch_pdl(kern, grid, dim3(pmm::kAtThreads), pmm::kAtSmem, stream,
+  pmm::launch_pdl(kern, grid, dim3(pmm::kAtThreads), smem, stream,
       static_cast<const pmm::bf16*>(q), map, block_table, max_blocks, positions, cu, static_cast<pmm::bf16*>(out), part_o,
       part_ml, scale * 1.4426950408889634f, window, split_len, n_splits, page_size, n_seq, Hq, Hkv, split_counter, status);
   return pmm::launch_status();

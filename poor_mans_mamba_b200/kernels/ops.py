@@ -1109,7 +1109,7 @@ def attention_tc(q: Tensor, pool: Tensor, block_table: Tensor, positions: Tensor
     _need(pool.dim() == 4 and pool.shape[1] == 2 and pool.shape[3] == n_kv_heads * head_dim and pool.is_contiguous(),
           "attention_tc: pool must be contiguous [pages, 2, page_size, Hkv*Dh]")
     _need(attention_tc_supported(n_q_heads, n_kv_heads, head_dim, pool.shape[2]),
-          "attention_tc: head size 64, a group size that divides 128 and pages of a multiple of 64 tokens")
+          "attention_tc: head size 64 or 128, at most 64 query heads per key/value head and pages of a multiple of 64 tokens")
     _i32(block_table, "attention_tc: block_table")
     _i32(positions, "attention_tc: positions")
     _i32(cu_seqlens, "attention_tc: cu_seqlens")

@@ -453,20 +453,22 @@ def test_flash_decode_attention_from_projections(Hq, Hkv, Dh, page):
     _attention_case(torch.bfloat16, Hq, Hkv, Dh, page, steps, seed=Hq + 3, window=70, fused_decode=True)
 
 
-@pytest.mark.parametrize("Hq,Hkv,page", [(8, 2, 64), (4, 4, 128), (16, 1, 64), (16, 2, 64)])
-def test_tcgen05_attention_over_the_paged_cache(Hq, Hkv, page):
+@pytest.mark.parametrize("Hq,Hkv,page,Dh", [(8, 2, 64, 64), (4, 4, 128, 64), (16, 1, 64, 64), (16, 2, 64, 64),
+                                            (8, 2, 64, 128), (4, 1, 128, 128), (2, 2, 64, 128), (6, 2, 64, 128),
+                                            (12, 2, 64, 128), (3, 1, 64, 64)])
+def test_tcgen05_attention_over_the_paged_cache(Hq, Hkv, page, Dh):
     """The tcgen05 / TMA / tensor-memory attention for prompt portions: portions that start and end
     off the 128-key tiles and the 64-key boxes, portions over a long cached prefix, single tokens,
     several sequences in a step, key splits merged by the last block, and a window."""
     bf = torch.bfloat16
     steps = [[page + 1, 1, 200, page - 2, 1], [3, 2 * page, 1, 130], [1, 1, 1, 1], [70, 1, 333]]
-    _attention_case(bf, Hq, Hkv, 64, page, steps, seed=Hq, tc=True)
-    _attention_case(bf, Hq, Hkv, 64, page, steps, seed=Hq + 1, n_splits=3, tc=True)
-    _attention_case(bf, Hq, Hkv, 64, page, steps, seed=Hq + 2, window=100, tc=True)
-    _attention_case(bf, Hq, Hkv, 64, page, steps, seed=Hq + 3, window=150, n_splits=2, tc=True)
+    _attention_case(bf, Hq, Hkv, Dh, page, steps, seed=Hq, tc=True)
+    _attention_case(bf, Hq, Hkv, Dh, page, steps, seed=Hq + 1, n_splits=3, tc=True)
+    _attention_case(bf, Hq, Hkv, Dh, page, steps, seed=Hq + 2, window=100, tc=True)
+    _attention_case(bf, Hq, Hkv, Dh, page, steps, seed=Hq + 3, window=150, n_splits=2, tc=True)
     assert K().tc_gemm_status(DEV) == 0
-    assert not K().attention_tc_supported(Hq, Hkv, 128, page) and not K().attention_tc_supported(6, 2, 64, page)
-    assert not K().attention_tc_supported(Hq, Hkv, 64, 16)
+    assert not K().attention_tc_supported(Hq, Hkv, 96, page) and not K().attention_tc_supported(130, 2, 64, page)
+    assert not K().attention_tc_supported(Hq, Hkv, Dh, 16)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

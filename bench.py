@@ -562,9 +562,16 @@ def main() -> int:
         clock_summary = clocks.summary()
 
         # end to end through the entry point: scheduler + pinned host ids in + sampled ids out
-        prompt_len = ctx_len - K_steps - W - 32  # no request ends (and no batch shrinks) inside the timed steps
+        # No request may end (and no batch shrink) inside the timed steps.  Requests whose prompts are
+        # done early decode while the others' prompts still run in portions, one token per such step,
+        # so every request is allowed that many more tokens, and its prompt is that much shorter.
+        prefill_steps = -(-args.batch * ctx_len // 8192) + args.batch
+        new_tokens = K_steps + W + 32 + prefill_steps
+        prompt_len = ctx_len - new_tokens
+        if prompt_len < 1:
+            raise SystemExit("bench.py: --context is too short for this batch's prompts to be cut into portions")
         ids = [eng.submit([rng.randrange(vocab) for _ in range(prompt_len)],
-                          SamplingParams(max_new_tokens=K_steps + W + 32, eos_id=-1)) for _ in range(args.batch)]
+                          SamplingParams(max_new_tokens=new_tokens, eos_id=-1)) for _ in range(args.batch)]
         while any(r.pending > 1 or r.status == "waiting" for r in eng.scheduler.requests.values() if not r.finished):
             eng.step()
         for _ in range(W):
@@ -573,6 +580,8 @@ def main() -> int:
         gc.collect()
         gc.disable()  # a collection of the whole heap inside the timed loop costs tens of milliseconds
         h2d0 = eng.runner.h2d_bytes
+        decoded0 = eng.scheduler.counters["decode_tokens"]
+        replays0 = eng.runner.graphs.replays if eng.runner.graphs is not None else 0
         t1 = time.perf_counter()
         step_times = []
         for _ in range(K_steps - 1):
@@ -585,12 +594,17 @@ def main() -> int:
         if os.environ.get("PMM_BENCH_DEBUG"):
             print("[bench] e2e step ms:", " ".join(f"{t * 1e3:.2f}" for t in step_times), file=sys.stderr)
             print("[bench] preemptions:", eng.scheduler.counters, file=sys.stderr)
+            print("[bench] graph replays in the timed end-to-end steps:",
+                  (eng.runner.graphs.replays - replays0) if eng.runner.graphs is not None else None,
+                  "lengths", sorted(set(eng.cache.lengths.values()))[:4], file=sys.stderr)
         e2e_steps = K_steps - 1
+        e2e_tokens = eng.scheduler.counters["decode_tokens"] - decoded0  # what the timed steps really decoded
+        assert e2e_tokens == args.batch * e2e_steps, (e2e_tokens, args.batch, e2e_steps)
         h2d_per_step = (eng.runner.h2d_bytes - h2d0) // e2e_steps
         while eng.has_work():
             eng.step()
-        assert all(len(eng.poll(i).tokens) == K_steps + W + 32 for i in ids)
-        e2e = {"value": args.batch * e2e_steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d_per_step),
+        assert all(len(eng.poll(i).tokens) == new_tokens for i in ids)
+        e2e = {"value": e2e_tokens / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d_per_step),
                "d2h_bytes_per_step": 4 * args.batch}
 
         read_bytes = nums["weight_bytes_per_step"] + args.batch * (

@@ -19,6 +19,11 @@ _ITEMSIZE = {torch.float32: 4, torch.bfloat16: 2, torch.float16: 2, torch.int32:
              torch.float64: 8, torch.int8: 1, torch.int16: 2, torch.bool: 1}
 
 
+def _padded_rows(n_rows: int) -> int:
+    from ..kernels.ops import padded_rows
+    return padded_rows(n_rows)
+
+
 class Workspace:
     def __init__(self, device: torch.device, initial_bytes: int = 0):
         self.device = torch.device(device)
@@ -57,12 +62,19 @@ class Workspace:
         return sum(c.numel() for c in self._chunks[:self._chunk]) + self._offset
 
     def alloc(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        """A tensor of ``shape``.  Behind a matrix of more than 64 rows the arena keeps scratch rows up
+        to `kernels.ops.padded_rows`, so that a library product over it can be issued with a row
+        count that recurs from step to step."""
         shape = tuple(shape)
         numel = 1
         for s in shape:
             numel *= s
         nbytes = numel * _ITEMSIZE[dtype]
-        size = (max(nbytes, 1) + _ALIGN - 1) // _ALIGN * _ALIGN
+        reserve, rows = nbytes, 0
+        if len(shape) == 2 and shape[0] > 64:
+            rows = _padded_rows(shape[0])
+            reserve = rows * shape[1] * _ITEMSIZE[dtype]
+        size = (max(reserve, 1) + _ALIGN - 1) // _ALIGN * _ALIGN
         while True:
             if self._chunk < len(self._chunks):
                 chunk = self._chunks[self._chunk]
@@ -72,6 +84,8 @@ class Workspace:
                     view = self._views.get(key)
                     if view is None:
                         view = chunk[off:off + nbytes].view(dtype).view(shape)
+                        if rows > shape[0]:
+                            view._scratch_rows = rows  # read by kernels.ops._mm; the storage is the whole chunk
                         self._views[key] = view
                     self._offset = off + size
                     used = self._used()

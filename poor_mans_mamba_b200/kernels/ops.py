@@ -121,7 +121,14 @@ def _call(name: str, *args) -> None:
         raise KernelError(f"{name}: CUDA error {rc} at launch")
 
 
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current stream's handle.  Asked for at every launch: the raw getter takes 0.3 us where
+    building a torch.cuda.Stream object takes 3 to 15."""
+    if _RAW_STREAM is not None:
+        return _RAW_STREAM(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -234,6 +241,41 @@ def _i32(t: Tensor, what: str) -> None:
 
 
 # ----------------------------------------------------------------------------- library GEMM
+def padded_rows(n_rows: int) -> int:
+    """The row count a library product of ``n_rows`` rows is issued with.  The library chooses a
+    kernel per (M, N, K) and the first call with a new M costs about 1.4 ms on the host (measured:
+    18 us once the shape is known); a server sees a new token count in almost every step.  Rounded
+    up to a multiple of 64 (128 from 1,024 rows, 256 from 4,096) the shapes recur.  The extra rows
+    are scratch: the step's arena reserves them behind every matrix it hands out."""
+    if n_rows <= 64:
+        return n_rows
+    step = 64 if n_rows < 1024 else (128 if n_rows < 4096 else 256)
+    return (n_rows + step - 1) // step * step
+
+
+def _with_rows(t: Tensor, rows: int) -> Optional[Tensor]:
+    """``t`` [T, n] seen with ``rows`` >= T rows of the same stride, if its storage reaches that far."""
+    if t.dim() != 2 or t.stride(1) != 1:
+        return None
+    last = t.storage_offset() + (rows - 1) * t.stride(0) + t.shape[1]
+    if last * t.element_size() > t.untyped_storage().nbytes():
+        return None
+    return t.as_strided((rows, t.shape[1]), t.stride())
+
+
+def _mm(x: Tensor, weight: Tensor, out: Tensor, **kw) -> None:
+    """The library product; with `padded_rows(T)` rows where ``out`` is a whole matrix of the step's
+    arena (which marks it with the rows it keeps behind it) and x's storage reaches as far.  What
+    the extra rows of x hold does not matter, rows being independent, and nothing reads the extra
+    rows of out."""
+    rows = padded_rows(x.shape[0])
+    if rows != x.shape[0] and getattr(out, "_scratch_rows", 0) >= rows:
+        xp, op = _with_rows(x, rows), _with_rows(out, rows)
+        if xp is not None and op is not None:
+            x, out = xp, op
+    torch.mm(x, weight.t(), out=out, **kw)
+
+
 def linear(x: Tensor, weight: Tensor, out: Tensor) -> Tensor:
     """out[T, N] = x[T, K] @ weight[N, K]^T through the GEMM library."""
     _cuda(x, weight, out)
@@ -242,11 +284,11 @@ def linear(x: Tensor, weight: Tensor, out: Tensor) -> Tensor:
         prev = torch.backends.cuda.matmul.allow_tf32
         torch.backends.cuda.matmul.allow_tf32 = False
         try:
-            torch.mm(x, weight.t(), out=out)
+            _mm(x, weight, out)
         finally:
             torch.backends.cuda.matmul.allow_tf32 = prev
     else:
-        torch.mm(x, weight.t(), out=out)
+        _mm(x, weight, out)
     return out
 
 
@@ -272,7 +314,7 @@ def linear_f32_out(x: Tensor, weight: Tensor, out: Tensor, scratch_low: Optional
     that is widened (and scaled) by cast_scale."""
     _cuda(x, weight, out)
     if mm_has_f32_out():
-        torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+        _mm(x, weight, out, out_dtype=torch.float32)
         if scale != 1.0:
             scale_f32_(out, scale)
     else:
@@ -998,7 +1040,7 @@ def _skinny_tc_operand(x: Tensor, w: Tensor) -> bool:
 
 def skinny_tc_supported(kind: str, x: Tensor, weight: Tensor, out: Optional[Tensor] = None) -> bool:
     """Whether the tcgen05 weight-streaming product (1..64 tokens) takes these operands; kind is
-    "store", "swiglu" (both keep all of K resident: at most 1,024 columns) or "residual"."""
+    "store", "swiglu" or "residual"."""
     if not _skinny_tc_operand(x, weight):
         return False
     mode = {"store": 0, "swiglu": 1, "residual": 2}[kind]
@@ -1006,7 +1048,7 @@ def skinny_tc_supported(kind: str, x: Tensor, weight: Tensor, out: Optional[Tens
     n = weight.shape[0] // 2 if kind == "swiglu" else weight.shape[0]
     ldy = 8
     if out is not None and kind != "residual":
-        if out.dtype != torch.bfloat16 or out.stride(1) != 1 or out.data_ptr() % 16:
+        if out.dtype != torch.bfloat16 or out.stride(1) != 1:
             return False
         ldy = out.stride(0)
     return bool(_fn("pmm_skinny_tc_supported")(mode, T, n, K, 0, x.stride(0), 0, ldy))
@@ -1016,7 +1058,7 @@ def skinny_tc_linear(x: Tensor, weight: Tensor, out: Tensor) -> None:
     """out[T, N] (bfloat16) = x @ weight^T for up to 64 tokens on the tcgen05 tensor cores."""
     _cuda(x, weight, out)
     _need(skinny_tc_supported("store", x, weight, out) and out.shape == (x.shape[0], weight.shape[0]),
-          "skinny_tc_linear: operands not supported (bfloat16, <= 64 tokens, K <= 1024 and a multiple of 8, aligned rows)")
+          "skinny_tc_linear: operands not supported (bfloat16, <= 64 tokens, K a multiple of 8, aligned rows)")
     T, K = x.shape
     _call("pmm_skinny_tc", 0, T, weight.shape[0], x.data_ptr(), x.stride(0), weight.data_ptr(), K, 1.0, None, 0, None, 0,
           0.0, out.data_ptr(), out.stride(0), None, _tc_status(x.device).data_ptr(), _stream())
@@ -1027,7 +1069,7 @@ def skinny_tc_swiglu(x: Tensor, gate_up: Tensor, gate_mult: float, out: Tensor) 
     _cuda(x, gate_up, out)
     F = gate_up.shape[0] // 2
     _need(gate_up.shape[0] == 2 * F and skinny_tc_supported("swiglu", x, gate_up, out) and out.shape == (x.shape[0], F),
-          "skinny_tc_swiglu: operands not supported (bfloat16, <= 64 tokens, K <= 1024 and a multiple of 8, aligned rows)")
+          "skinny_tc_swiglu: operands not supported (bfloat16, <= 64 tokens, K a multiple of 8, aligned rows)")
     T, K = x.shape
     _call("pmm_skinny_tc", 1, T, F, x.data_ptr(), x.stride(0), gate_up.data_ptr(), K, float(gate_mult), None, 0, None, 0,
           0.0, out.data_ptr(), out.stride(0), None, _tc_status(x.device).data_ptr(), _stream())
@@ -1035,7 +1077,7 @@ def skinny_tc_swiglu(x: Tensor, gate_up: Tensor, gate_mult: float, out: Tensor) 
 
 def skinny_tc_residual(h: Tensor, products: Sequence[Tuple[Tensor, Tensor, float]]) -> None:
     """h[T, N] += sum_i scale_i * (x_i @ w_i^T) for one or two products (tcgen05, up to 64 tokens;
-    float32 atomics, K in slices of at most 1,024 columns)."""
+    float32 atomics, K in slices over blocks)."""
     _need(1 <= len(products) <= 2, "skinny_tc_residual: one or two products")
     _cuda(h)
     T, N = h.shape

@@ -514,6 +514,34 @@ def test_library_linear_in_true_float32():
     assert float((lo.double().cpu() - ref).abs().max()) < 0.3
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_library_linear_with_padded_rows(dtype):
+    """A product over whole matrices of the step's arena is issued with the row count rounded up
+    (the arena keeps scratch rows behind them): the result is that of the exact product, rows that
+    another tensor holds stay as they were, and a slice of rows is never padded."""
+    from poor_mans_mamba_b200.engine import Workspace
+    ops = K()
+    g = torch.Generator().manual_seed(9)
+    T, Kd, N = 100, 96, 72
+    assert ops.padded_rows(T) == 128 and ops.padded_rows(64) == 64 and ops.padded_rows(1025) == 1152
+    ws = Workspace(DEV, 1 << 22)
+    x = ws.alloc((T, Kd), dtype)
+    out = ws.alloc((T, N), dtype)
+    after = ws.alloc((4, N), dtype)
+    assert after.data_ptr() - out.data_ptr() >= 128 * N * out.element_size()
+    xs, w = q(torch.randn(T, Kd, generator=g), dtype), q(torch.randn(N, Kd, generator=g), dtype).to(DEV)
+    x.copy_(xs)
+    after.fill_(7.0)
+    ops.linear(x, w, out)
+    close(out, xs.double() @ w.double().cpu().t(), dtype, what="padded product")
+    assert bool((after == 7.0).all())
+    # rows 10..90 of the same buffers: the rows behind belong to the tensor itself and must stay
+    out.fill_(3.0)
+    ops.linear(x[10:90], w, out[10:90])
+    assert bool((out[:10] == 3.0).all()) and bool((out[90:] == 3.0).all())
+    close(out[10:90], xs[10:90].double() @ w.double().cpu().t(), dtype, what="row slice")
+
+
 def test_sampling_greedy_ties_and_temperature():
     ops = K()
     V = 1000
@@ -712,10 +740,11 @@ def test_skinny_product_with_float32_output_for_the_head(M, N, Kd):
 @pytest.mark.parametrize("T", [1, 17, 40, 64])
 @pytest.mark.parametrize("N,Kd", [(50, 96), (1024, 1000), (4120, 1024), (6000, 512), (304, 72)])
 def test_tcgen05_weight_streaming_product(T, N, Kd):
-    """The tcgen05 form of the weight-streaming product (17..64 tokens; fewer work too): store,
-    SwiGLU, and residual accumulation of one and two products with K in slices, at sizes on and
-    off the boxes of 64 columns and tiles of 32 rows, with more row tiles than blocks (a block then
-    walks several tiles through both accumulators), into column slices of wider buffers."""
+    """The tcgen05 form of the weight-streaming product (up to 64 tokens): store, SwiGLU (K in
+    slices over the blocks of a cluster where the row tiles are few, one block per tile where they
+    are many, more tiles than blocks so that a block walks several through both accumulators) and
+    residual accumulation of one and two products, at sizes on and off the boxes of 64 columns and
+    the tiles of 128 rows, into column slices of wider buffers."""
     g = torch.Generator().manual_seed(T * 131 + N + Kd)
     ops = K()
     bf = torch.bfloat16
@@ -723,12 +752,12 @@ def test_tcgen05_weight_streaming_product(T, N, Kd):
     x = xw[:, :Kd]                                       # rows with a stride of their own
     w = (torch.randn(N, Kd, generator=g) * 0.05).to(bf).to(DEV)
     ref = x.double().cpu() @ w.double().cpu().t()
-    buf = torch.zeros(T, (N + 16 + 7) // 8 * 8, dtype=bf, device=DEV)  # rows of 16-byte multiples
+    buf = torch.zeros(T, N + 16 + 3, dtype=bf, device=DEV)
     assert ops.skinny_tc_supported("store", x, w, buf[:, 8:8 + N])
     ops.skinny_tc_linear(x, w, buf[:, 8:8 + N])
     close(buf[:, 8:8 + N], ref, bf, what="tcgen05 skinny store")
     assert float(buf[:, :8].abs().sum()) == 0 and float(buf[:, 8 + N:].abs().sum()) == 0
-    if N % 16 == 0:  # (rows of the output are 16-byte multiples)
+    if N % 2 == 0:
         F = N // 2
         act = torch.full((T, F), float("nan"), dtype=bf, device=DEV)
         ops.skinny_tc_swiglu(x, w, 1.5, act)
@@ -749,9 +778,14 @@ def test_tcgen05_weight_streaming_product(T, N, Kd):
     close(hd, ref2, torch.float32, scale=60.0, what="tcgen05 skinny residual two products")
     torch.cuda.synchronize()
     assert ops.tc_gemm_status(DEV) == 0
-    # refusals: too many tokens, K not resident for a store
+    # a long K for a store (more stages than the ring holds, in every slice), and the refusals
+    long_out = torch.empty(T, N, dtype=bf, device=DEV)
+    ops.skinny_tc_linear(xa, wa, long_out)
+    close(long_out, xa.double().cpu() @ wa.double().cpu().t(), bf, what="tcgen05 skinny store, K = 2304")
+    torch.cuda.synchronize()
+    assert ops.tc_gemm_status(DEV) == 0
     assert not ops.skinny_tc_supported("store", torch.zeros(65, Kd, dtype=bf, device=DEV), w)
-    assert not ops.skinny_tc_supported("store", xa, wa) and ops.skinny_tc_supported("residual", xa, wa)
+    assert not ops.skinny_tc_supported("store", xa[:, :132], wa[:, :132].contiguous())  # rows of K off 16 bytes
 
 
 @pytest.mark.parametrize("T,Kd,F", [(200, 128, 128), (128, 64, 256), (2048, 1024, 2048), (333, 1024, 384), (700, 3072, 640)])

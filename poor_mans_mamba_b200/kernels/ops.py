@@ -75,6 +75,11 @@ _SIGNATURES = {
                                    c_float, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                    c_int, c_void_p, c_void_p],
+    "pmm_decode_attention_tma_supported": [c_int, c_int, c_int, c_int],
+    "pmm_decode_attention_tma": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_float, c_float,
+                                 c_float, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                 c_void_p, c_void_p],
     "pmm_flash_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_skinny_gemm": [c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_int,
                         c_float, c_void_p, c_longlong, c_void_p, c_int, c_float, c_void_p, c_longlong, c_void_p,
@@ -768,6 +773,10 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
               _dt(out), _stream())
 
 
+# Decode attention with TMA tile loads where the sizes allow (PMM_TMA_DECODE=0: cp.async gathers throughout).
+_TMA_DECODE = os.environ.get("PMM_TMA_DECODE", "1") == "1"
+
+
 def flash_decode_supported(n_q_heads: int, n_kv_heads: int, head_dim: int) -> bool:
     """Whether flash_decode_attention takes this head shape (bfloat16, at most 16 query heads a group)."""
     return flash_supported(n_q_heads, n_kv_heads, head_dim) and n_q_heads // n_kv_heads <= 16
@@ -812,6 +821,15 @@ def flash_decode_attention(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], 
         part_o = scratch.data_ptr()
         part_ml = part_o + 4 * n_seq * n_q_heads * n_splits * head_dim
         counter = split_counter.data_ptr()
+    if (_TMA_DECODE and (n_splits == 1 or split_len % 64 == 0)
+            and _fn("pmm_decode_attention_tma_supported")(n_q_heads, n_kv_heads, head_dim, pool.shape[2])):
+        # the copy engine brings the tiles (pages of a multiple of 64 positions, head sizes 64 and 128)
+        _call("pmm_decode_attention_tma", q.data_ptr(), ldq, _ptr(k), ldk, _ptr(v), ldv, float(q_scale), float(k_scale),
+              float(v_scale), _ptr(inv_freq), pool.data_ptr(), pool.shape[0], block_table.data_ptr(),
+              block_table.shape[1], positions.data_ptr(), out.data_ptr(), part_o, part_ml, float(softmax_scale),
+              int(window), int(split_len), int(n_splits), pool.shape[2], n_seq, n_q_heads, n_kv_heads, head_dim, counter,
+              _tc_status(q.device).data_ptr(), _stream())
+        return
     _call("pmm_flash_decode_attention", q.data_ptr(), ldq, _ptr(k), ldk, _ptr(v), ldv, float(q_scale), float(k_scale),
           float(v_scale), _ptr(inv_freq), pool.data_ptr(), block_table.data_ptr(), block_table.shape[1],
           positions.data_ptr(), out.data_ptr(), part_o, part_ml, float(softmax_scale), int(window), int(split_len),
@@ -1028,7 +1046,7 @@ def _tc_status(device: torch.device) -> Tensor:
 
 def tc_gemm_status(device) -> int:
     """0 unless a bounded wait inside a tensor-core kernel gave up (tc_gemm: 1 producer, 2 MMA
-    issuer, 3 epilogue; attention_tc: 11..15; skinny_tc: 21..24).  Reading it waits for the device."""
+    issuer, 3 epilogue; attention_tc: 11..15; skinny_tc: 21..24; decode attention: 31, 32).  Reading it waits for the device."""
     return int(_tc_status(torch.device(device)).item())
 
 
@@ -1040,7 +1058,7 @@ def _skinny_tc_operand(x: Tensor, w: Tensor) -> bool:
 
 def skinny_tc_supported(kind: str, x: Tensor, weight: Tensor, out: Optional[Tensor] = None) -> bool:
     """Whether the tcgen05 weight-streaming product (1..64 tokens) takes these operands; kind is
-    "store", "swiglu" or "residual"."""
+    "store", "swiglu" (both keep all of K resident: at most 1,024 columns) or "residual"."""
     if not _skinny_tc_operand(x, weight):
         return False
     mode = {"store": 0, "swiglu": 1, "residual": 2}[kind]
@@ -1048,7 +1066,7 @@ def skinny_tc_supported(kind: str, x: Tensor, weight: Tensor, out: Optional[Tens
     n = weight.shape[0] // 2 if kind == "swiglu" else weight.shape[0]
     ldy = 8
     if out is not None and kind != "residual":
-        if out.dtype != torch.bfloat16 or out.stride(1) != 1:
+        if out.dtype != torch.bfloat16 or out.stride(1) != 1 or out.data_ptr() % 16:
             return False
         ldy = out.stride(0)
     return bool(_fn("pmm_skinny_tc_supported")(mode, T, n, K, 0, x.stride(0), 0, ldy))
@@ -1058,7 +1076,7 @@ def skinny_tc_linear(x: Tensor, weight: Tensor, out: Tensor) -> None:
     """out[T, N] (bfloat16) = x @ weight^T for up to 64 tokens on the tcgen05 tensor cores."""
     _cuda(x, weight, out)
     _need(skinny_tc_supported("store", x, weight, out) and out.shape == (x.shape[0], weight.shape[0]),
-          "skinny_tc_linear: operands not supported (bfloat16, <= 64 tokens, K a multiple of 8, aligned rows)")
+          "skinny_tc_linear: operands not supported (bfloat16, <= 64 tokens, K <= 1024 and a multiple of 8, aligned rows)")
     T, K = x.shape
     _call("pmm_skinny_tc", 0, T, weight.shape[0], x.data_ptr(), x.stride(0), weight.data_ptr(), K, 1.0, None, 0, None, 0,
           0.0, out.data_ptr(), out.stride(0), None, _tc_status(x.device).data_ptr(), _stream())
@@ -1069,7 +1087,7 @@ def skinny_tc_swiglu(x: Tensor, gate_up: Tensor, gate_mult: float, out: Tensor) 
     _cuda(x, gate_up, out)
     F = gate_up.shape[0] // 2
     _need(gate_up.shape[0] == 2 * F and skinny_tc_supported("swiglu", x, gate_up, out) and out.shape == (x.shape[0], F),
-          "skinny_tc_swiglu: operands not supported (bfloat16, <= 64 tokens, K a multiple of 8, aligned rows)")
+          "skinny_tc_swiglu: operands not supported (bfloat16, <= 64 tokens, K <= 1024 and a multiple of 8, aligned rows)")
     T, K = x.shape
     _call("pmm_skinny_tc", 1, T, F, x.data_ptr(), x.stride(0), gate_up.data_ptr(), K, float(gate_mult), None, 0, None, 0,
           0.0, out.data_ptr(), out.stride(0), None, _tc_status(x.device).data_ptr(), _stream())
@@ -1077,7 +1095,7 @@ def skinny_tc_swiglu(x: Tensor, gate_up: Tensor, gate_mult: float, out: Tensor) 
 
 def skinny_tc_residual(h: Tensor, products: Sequence[Tuple[Tensor, Tensor, float]]) -> None:
     """h[T, N] += sum_i scale_i * (x_i @ w_i^T) for one or two products (tcgen05, up to 64 tokens;
-    float32 atomics, K in slices over blocks)."""
+    float32 atomics, K in slices of at most 1,024 columns)."""
     _need(1 <= len(products) <= 2, "skinny_tc_residual: one or two products")
     _cuda(h)
     T, N = h.shape

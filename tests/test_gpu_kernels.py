@@ -368,7 +368,7 @@ def _attention_case(dtype, Hq, Hkv, Dh, page_size, lens_steps, window=0, planted
         if fused_decode and all(n == 1 for _, _, n in seqs):
             split_len, scratch, ns = 0, None, 1
             if n_splits > 1:
-                split_len = ((max(pos) + 1 + n_splits - 1) // n_splits + 31) // 32 * 32
+                split_len = ((max(pos) + 1 + n_splits - 1) // n_splits + 63) // 64 * 64
                 ns = (max(pos) + 1 + split_len - 1) // split_len
                 scratch = torch.full((ops.attention_scratch_floats(T, Hq, Dh, ns),), float("nan"), device=DEV)
             ops.flash_decode_attention(buf[:, 8:8 + qd], buf[:, 8 + qd:8 + qd + kvd], buf[:, 8 + qd + kvd:], q_scale,
@@ -441,16 +441,30 @@ def test_paged_attention_split_keys(dtype, tensor_cores):
         _attention_case(dtype, 4, 2, 32, 16, [[40, 1, 1, 30], [5, 1, 60]], window=24, n_splits=3, seed=9, fused_merge=True)
 
 
-@pytest.mark.parametrize("Hq,Hkv,Dh,page", [(8, 2, 64, 64), (6, 2, 128, 16), (4, 4, 32, 32), (16, 1, 16, 16), (12, 2, 128, 64)])
-def test_flash_decode_attention_from_projections(Hq, Hkv, Dh, page):
+@pytest.mark.parametrize("tma", [True, False])
+@pytest.mark.parametrize("Hq,Hkv,Dh,page", [(8, 2, 64, 64), (6, 2, 128, 16), (4, 4, 32, 32), (16, 1, 16, 16), (12, 2, 128, 64),
+                                            (3, 1, 64, 128), (16, 1, 128, 64)])
+def test_flash_decode_attention_from_projections(Hq, Hkv, Dh, page, tma, monkeypatch):
     """Decode steps that rotate, store and attend in one launch: after prompts of several lengths
-    (page edges, tile edges), one key range and several, more than four tiles in one block (the
-    new key's tile is then loaded in a later round), and a window."""
-    steps = [[page + 1] + [1] * 6, [63] + [1] * 6, [300] + [1] * 6, [1] * 7]
+    (page edges, tile edges), one key range and several, more tiles in one block than its ring
+    holds (the new key's tile then comes in a later round), and a window.  Both forms: tiles
+    brought by the copy engine (pages of a multiple of 64 positions, head sizes 64 and 128) and
+    gathered with cp.async."""
+    ops = K()
+    monkeypatch.setattr(ops, "_TMA_DECODE", tma)
+    calls = []
+    original = ops._call
+    monkeypatch.setattr(ops, "_call", lambda name, *a: (calls.append(name), original(name, *a))[1])
+    steps = [[page + 1] + [1] * 6, [63] + [1] * 6, [300] + [1] * 6, [1] * 7, [700] + [1] * 3]
     _attention_case(torch.bfloat16, Hq, Hkv, Dh, page, steps, seed=Hq, fused_decode=True)
     _attention_case(torch.bfloat16, Hq, Hkv, Dh, page, steps, seed=Hq + 1, n_splits=3, fused_decode=True)
     _attention_case(torch.bfloat16, Hq, Hkv, Dh, page, steps, seed=Hq + 2, window=40, n_splits=2, fused_decode=True)
     _attention_case(torch.bfloat16, Hq, Hkv, Dh, page, steps, seed=Hq + 3, window=70, fused_decode=True)
+    torch.cuda.synchronize()
+    assert ops.tc_gemm_status(DEV) == 0
+    by_copy_engine = tma and page % 64 == 0 and Dh in (64, 128)
+    assert ("pmm_decode_attention_tma" in calls) == by_copy_engine
+    assert ("pmm_flash_decode_attention" in calls) == (not by_copy_engine)
 
 
 @pytest.mark.parametrize("Hq,Hkv,page,Dh", [(8, 2, 64, 64), (4, 4, 128, 64), (16, 1, 64, 64), (16, 2, 64, 64),
@@ -740,11 +754,10 @@ def test_skinny_product_with_float32_output_for_the_head(M, N, Kd):
 @pytest.mark.parametrize("T", [1, 17, 40, 64])
 @pytest.mark.parametrize("N,Kd", [(50, 96), (1024, 1000), (4120, 1024), (6000, 512), (304, 72)])
 def test_tcgen05_weight_streaming_product(T, N, Kd):
-    """The tcgen05 form of the weight-streaming product (up to 64 tokens): store, SwiGLU (K in
-    slices over the blocks of a cluster where the row tiles are few, one block per tile where they
-    are many, more tiles than blocks so that a block walks several through both accumulators) and
-    residual accumulation of one and two products, at sizes on and off the boxes of 64 columns and
-    the tiles of 128 rows, into column slices of wider buffers."""
+    """The tcgen05 form of the weight-streaming product (17..64 tokens; fewer work too): store,
+    SwiGLU, and residual accumulation of one and two products with K in slices, at sizes on and
+    off the boxes of 64 columns and tiles of 32 rows, with more row tiles than blocks (a block then
+    walks several tiles through both accumulators), into column slices of wider buffers."""
     g = torch.Generator().manual_seed(T * 131 + N + Kd)
     ops = K()
     bf = torch.bfloat16
@@ -752,12 +765,12 @@ def test_tcgen05_weight_streaming_product(T, N, Kd):
     x = xw[:, :Kd]                                       # rows with a stride of their own
     w = (torch.randn(N, Kd, generator=g) * 0.05).to(bf).to(DEV)
     ref = x.double().cpu() @ w.double().cpu().t()
-    buf = torch.zeros(T, N + 16 + 3, dtype=bf, device=DEV)
+    buf = torch.zeros(T, (N + 16 + 7) // 8 * 8, dtype=bf, device=DEV)  # rows of 16-byte multiples
     assert ops.skinny_tc_supported("store", x, w, buf[:, 8:8 + N])
     ops.skinny_tc_linear(x, w, buf[:, 8:8 + N])
     close(buf[:, 8:8 + N], ref, bf, what="tcgen05 skinny store")
     assert float(buf[:, :8].abs().sum()) == 0 and float(buf[:, 8 + N:].abs().sum()) == 0
-    if N % 2 == 0:
+    if N % 16 == 0:  # (rows of the output are 16-byte multiples)
         F = N // 2
         act = torch.full((T, F), float("nan"), dtype=bf, device=DEV)
         ops.skinny_tc_swiglu(x, w, 1.5, act)
@@ -778,14 +791,9 @@ def test_tcgen05_weight_streaming_product(T, N, Kd):
     close(hd, ref2, torch.float32, scale=60.0, what="tcgen05 skinny residual two products")
     torch.cuda.synchronize()
     assert ops.tc_gemm_status(DEV) == 0
-    # a long K for a store (more stages than the ring holds, in every slice), and the refusals
-    long_out = torch.empty(T, N, dtype=bf, device=DEV)
-    ops.skinny_tc_linear(xa, wa, long_out)
-    close(long_out, xa.double().cpu() @ wa.double().cpu().t(), bf, what="tcgen05 skinny store, K = 2304")
-    torch.cuda.synchronize()
-    assert ops.tc_gemm_status(DEV) == 0
+    # refusals: too many tokens, K not resident for a store
     assert not ops.skinny_tc_supported("store", torch.zeros(65, Kd, dtype=bf, device=DEV), w)
-    assert not ops.skinny_tc_supported("store", xa[:, :132], wa[:, :132].contiguous())  # rows of K off 16 bytes
+    assert not ops.skinny_tc_supported("store", xa, wa) and ops.skinny_tc_supported("residual", xa, wa)
 
 
 @pytest.mark.parametrize("T,Kd,F", [(200, 128, 128), (128, 64, 256), (2048, 1024, 2048), (333, 1024, 384), (700, 3072, 640)])

@@ -338,6 +338,13 @@ def mixed_workload(args, cfg, full_layers, nums, peaks, model_dir, checked) -> i
         for _ in range(W + 2):  # the second occurrence of the shape records its graph
             one_step(False)
         torch.cuda.synchronize()
+        if args.profile_steps:  # one step between the profiler's marks, for `ncu --profile-from-start off`
+            torch.cuda.profiler.start()
+            one_step(False)
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+            print(json.dumps({"profile_steps": "done", "workload": "mixed", "layers": cfg["num_hidden_layers"]}))
+            return 0
         launches0 = runner.mark_launches()
         with ClockSampler() as clocks:
             marks = [torch.cuda.Event(enable_timing=True) for _ in range(K_steps + 1)]
@@ -452,7 +459,7 @@ def main() -> int:
     write_random_model(cfg, seed=2, out_dir=tmp)
     print(f"[bench] wrote random model in {time.time() - t0:.1f}s", file=sys.stderr, flush=True)
 
-    if args.profile_steps:
+    if args.profile_steps and args.workload == "decode":
         with torch.cuda.device(0):
             eng = Engine(tmp, dtype=args.dtype, max_tokens=args.batch * (ctx_len + 64) + 4096, max_seqs=args.batch + 1,
                          page_size=64, max_batched_tokens=8192, max_seq_len=ctx_len + 64, cuda_graphs=False)

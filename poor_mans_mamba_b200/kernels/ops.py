@@ -838,7 +838,9 @@ def flash_decode_attention(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], 
 
 SKINNY_MAX_TOKENS = 64  # the weight-streaming products take up to 64 tokens (where their shared memory fits)
 SKINNY_NORM_MAX_TOKENS = 16  # every block redoes the norm of all rows: beyond this a norm launch of its own is cheaper
-SKINNY_TC_FROM_TOKENS = 33   # from here on the tcgen05 form (skinny_tc_*) is faster than the mma.sync form (measured at 17/32/64 tokens)
+# from here on the tcgen05 form (skinny_tc_*) is the faster one inside a decode step (0.5B sizes, ms a step,
+# mma.sync / tcgen05: 32 tokens 1.87 / 2.09, 40 tokens 2.35 / 2.26, 48 tokens 2.63 / 2.51); PMM_TC_SKINNY_FROM moves it
+SKINNY_TC_FROM_TOKENS = int(os.environ.get("PMM_TC_SKINNY_FROM", "33"))
 SKINNY_NORM_MAX_WIDTH = 1024  # ... and so it is for rows wider than a warp keeps in registers (they are read twice)
 
 

@@ -32,6 +32,16 @@ _CHUNKED_FROM = 8
 # seven size pairs it is compiled for).
 _TC_SCAN = os.environ.get("PMM_TCGEN05_SCAN", "1") == "1"
 _NOTED = set()
+_LONE_STREAMS: Dict[torch.device, "torch.cuda.Stream"] = {}
+
+
+def _lone_stream(device: torch.device) -> "torch.cuda.Stream":
+    """The stream on which a mixed step's lone tokens are scanned beside the prompt portions."""
+    st = _LONE_STREAMS.get(device)
+    if st is None:
+        st = torch.cuda.Stream(device=device)
+        _LONE_STREAMS[device] = st
+    return st
 
 
 def _note_serial(d_head: int, d_state: int) -> None:
@@ -192,11 +202,21 @@ class Mamba2Mixer(Mixer):
             # in a mixed step the lone tokens (decoding requests) go through the token-serial kernel: a
             # 128-token chunk for one token is two tile-sized blocks of work for nothing
             lone = ctx.n_seq > 1 and any(n == 1 for n in ctx.new_lens)
+            if lone:
+                # The two scans touch different sequences (their states, their rows of y).  The lone
+                # tokens' scan is a read and write of their states at the memory's rate, the chunked one
+                # a chain of three tensor-core launches: they run side by side (parallel branches of a
+                # captured step).
+                here = torch.cuda.current_stream(xbc.device)
+                side = _lone_stream(xbc.device)
+                side.wait_stream(here)
+                with torch.cuda.stream(side):
+                    K.ssm_scan_seq(xbc, dt, self.dt_scale, self.dt_shift, self.a_log, self.d_skip, state,
+                                   ctx.cu_seqlens, ctx.slots, ctx.n_seq, y, self.n_groups, gate=gate, only_single=True)
             K.ssm_scan_tc(xbc, dt, self.dt_scale, self.dt_shift, self.a_log, self.d_skip, state, ctx.cu_seqlens,
                           ctx.slots, ctx.new_lens, y, self.n_groups, scratch, gate=gate, skip_single=lone)
             if lone:
-                K.ssm_scan_seq(xbc, dt, self.dt_scale, self.dt_shift, self.a_log, self.d_skip, state,
-                               ctx.cu_seqlens, ctx.slots, ctx.n_seq, y, self.n_groups, gate=gate, only_single=True)
+                here.wait_stream(side)
         elif chunked and K.ssd_supported(self.d_head, self.d_state):
             # the mma.sync form: chunks of 64 tokens
             need = K.ssd_scratch_floats(ctx.new_lens, self.n_heads, self.d_head, self.d_state, self.n_groups)

@@ -23,7 +23,7 @@ from .context import StepContext
 # The output head of steps with few wanted rows through the weight-streaming product (PMM_SKINNY_HEAD=0:
 # the library product).
 _SKINNY_HEAD = os.environ.get("PMM_SKINNY_HEAD", "1") == "1"
-_FETCH_FROM_TOKENS, _FETCH_TO_TOKENS = 2, 16
+_FETCH_FROM_TOKENS, _FETCH_TO_TOKENS = 1, 16
 
 Tensor = torch.Tensor
 
@@ -119,8 +119,7 @@ class Model:
         order = self.spec.order
         # Fetching the next layer's weights beside a layer's products pays where the mixers' phase is
         # long enough to cover it and the products still wait for their weights: measured on the 0.5B
-        # sizes it takes 4 to 9 % off steps of 2 to 16 tokens, adds 15 % to a step of one token (the
-        # next layer's mixers then wait for the fetch) and 1 % beyond 24.
+        # sizes it takes 4 to 9 % off steps of up to 16 tokens and adds 1 % beyond 24.
         fetch = self._fetch_ahead and _FETCH_FROM_TOKENS <= T <= _FETCH_TO_TOKENS
         for i, call in enumerate(order):
             # a layer that streams its weights once may fetch the next layer's ahead of time

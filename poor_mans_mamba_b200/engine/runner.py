@@ -38,10 +38,16 @@ class StepEntry:
     want: Sequence[int] = field(default_factory=list)
 
 
-# Steps of at least this many tokens are candidates for the step-graph cache (smaller mixed
-# steps change shape too often to be worth recording); the cache keeps this many shapes.
+# Prompt steps whose shape (token counts per request, wanted rows, key-length bucket) comes a second
+# time are recorded into a CUDA graph and replayed from then on.  Two caches, so that a stream of
+# short steps of ever new shapes cannot push out the few large shapes of chunked prefill: steps of at
+# least _STEP_GRAPH_MIN_TOKENS tokens (their workspaces are large: few of them are kept), and shorter
+# ones down to _STEP_GRAPH_SMALL_FROM tokens (a short prompt costs the host 9 ms of launches when it is
+# not replayed, 36 layers of the 0.5B sizes).
 _STEP_GRAPH_MIN_TOKENS = 256
 _STEP_GRAPH_CAPACITY = 6
+_STEP_GRAPH_SMALL_FROM = 2
+_STEP_GRAPH_SMALL_CAPACITY = 24
 
 
 class _Staging:
@@ -97,6 +103,7 @@ class ModelRunner:
         self.graphs = None
         self._sampler = None
         self._step_graphs: "collections.OrderedDict" = collections.OrderedDict()
+        self._small_step_graphs: "collections.OrderedDict" = collections.OrderedDict()
 
     def enable_graphs(self, max_seq_len: int, buckets=None) -> None:
         """Serve decode-only steps from CUDA graphs (captured per batch-size bucket on first use).
@@ -225,7 +232,7 @@ class ModelRunner:
         # fixed width and a key-length bound rounded up to a power of two, so that the launch
         # shapes depend on the key only.
         graph_key = None
-        if self.graphs is not None and kv_len <= self.graphs.max_seq_len and T >= _STEP_GRAPH_MIN_TOKENS:
+        if self.graphs is not None and kv_len <= self.graphs.max_seq_len and T >= _STEP_GRAPH_SMALL_FROM:
             kv_len = min(self.graphs.max_seq_len, 1 << (kv_len - 1).bit_length())
             graph_key = (tuple(new_lens), n_rows, kv_len)
             widths = [g.blocks_for(self.graphs.max_seq_len) for g in groups]
@@ -278,19 +285,21 @@ class ModelRunner:
                 decode_only=all(n == 1 for n in new_lens), kv_len_bound=kv_len,
                 dtype=self.dtype, workspace=workspace, new_lens=new_lens, past_lens=past), tables
 
-        entry = self._step_graphs.get(graph_key) if graph_key is not None else None
+        large = T >= _STEP_GRAPH_MIN_TOKENS
+        shapes = self._step_graphs if large else self._small_step_graphs
+        entry = shapes.get(graph_key) if graph_key is not None else None
         if entry is not None and entry.get("graph") is None and entry["seen"] >= 1:
             self._capture_step(entry, total, fill, context)  # second time this shape comes: capture it
         if entry is not None and entry.get("graph") is not None:
-            self._step_graphs.move_to_end(graph_key)
+            shapes.move_to_end(graph_key)
             self._staging.upload(total, fill, dev=entry["meta"])
             entry["graph"].replay()
             logits = entry["logits"]
         else:
             if graph_key is not None:
-                self._step_graphs[graph_key] = {"seen": 1}
-                while len(self._step_graphs) > _STEP_GRAPH_CAPACITY:
-                    self._step_graphs.popitem(last=False)
+                shapes[graph_key] = {"seen": 1}
+                while len(shapes) > (_STEP_GRAPH_CAPACITY if large else _STEP_GRAPH_SMALL_CAPACITY):
+                    shapes.popitem(last=False)
             dev = self._staging.upload(total, fill)
             self.workspace.reset()
             ctx, block_tables = context(dev, self.workspace)

@@ -195,3 +195,7 @@ def test_repeated_step_shapes_replay_from_graphs(case, dtype, tmp_path):
         runner.cache.check()
     recorded = [k for k, e in runner._step_graphs.items() if e.get("graph") is not None]
     assert any(k[0] == (280, 20) for k in recorded)
+    # the short second step (20 + 20 tokens) has a cache of its own: recorded there, and the many
+    # fillers of ever new lengths did not push the large shape out
+    small = [k for k, e in runner._small_step_graphs.items() if e.get("graph") is not None]
+    assert any(k[0] == (20, 20) for k in small) and not any(k[0] == (20, 20) for k in runner._step_graphs)

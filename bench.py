@@ -421,6 +421,11 @@ def main() -> int:
                          "two layers of the run's model, in the run's dtype, on the benchmark's schedule (a "
                          "2,048-token prompt step twice, then decode steps of a batch of 8 at contexts spread up to "
                          "--context through the CUDA graphs), every row against float64")
+    ap.add_argument("--without", default="",
+                    help="comma-separated names of kernel wrappers of poor_mans_mamba_b200.kernels.ops (for instance "
+                         "flash_decode_attention,ssm_scan_seq) that are turned into no-ops: the results are wrong, "
+                         "the shape of the step stays, and the difference in time shows what lies on the step's "
+                         "critical chain (implies --no-check; the line says \"invalid\": \"without ...\")")
     ap.add_argument("--profile-steps", action="store_true",
                     help="small workload for a profiler instead of the benchmark: after an untimed set-up, one "
                          "2,048-token prefill step and two decode steps of the batch, issued kernel by kernel "
@@ -444,6 +449,15 @@ def main() -> int:
     from poor_mans_mamba_b200.entry import Engine
     from poor_mans_mamba_b200.kernels import ops as K
     from poor_mans_mamba_b200.weights import write_random_model
+
+    without = [n for n in args.without.split(",") if n]
+    for name in without:
+        if not callable(getattr(K, name, None)):
+            print(f"bench.py: --without {name}: poor_mans_mamba_b200.kernels.ops has no such function")
+            return 2
+        setattr(K, name, lambda *a, **k: None)
+    if without:
+        args.check = False
 
     peaks = load_peaks()
     cfg, full_layers = sized_config(args)
@@ -673,6 +687,8 @@ def main() -> int:
         "gpu_launches": int(launches), "roofline": roofline, "impl": "ours",
     }
     result.update(extra)
+    if without:
+        result["invalid"] = "without " + ",".join(without)
     result["checked"] = checked is not None
     if checked is not None:
         result["check"] = checked

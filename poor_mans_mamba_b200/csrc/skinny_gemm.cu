@@ -99,6 +99,7 @@ struct SkinnyBlock {
   bf16* sX;     // [MP][xs]
   float* sRed;  // [3][32][MP] column quarters, then up rows
   float* sNw;   // [kx] norm weights of the slice (norm prologue)
+  float* sInv;  // [MP] rsqrt(mean(h^2) + eps) of each row (norm prologue): applied to the sums in the epilogue
   const bf16* src[kSgPieces];  // this thread's pieces of chunk 0 of the block's first tile
   size_t tile_stride;          // elements of W between one of the block's tiles and the next
 
@@ -113,6 +114,7 @@ struct SkinnyBlock {
     sX = sW + kSgStages * kSgRows * kSgWStride;
     sRed = reinterpret_cast<float*>(sX + MP * xs);
     sNw = sRed + 3 * 32 * MP;
+    sInv = sNw + kx;
     n_chunks = kx / kSgChunk;
     const int n_tx = (a.N + kTileCols - 1) / kTileCols;
     t0 = bx;
@@ -189,60 +191,56 @@ __device__ void SkinnyBlock<MT, MODE>::run() const {
     }
   }
   sg_commit();
-  // norm prologue: x = h * rsqrt(mean(h^2) + eps) * w for this K slice -> shared memory as
-  // bfloat16 (rows >= M and columns >= K zero), while the weight chunks are in flight
+  // norm prologue: the products run on x' = h * w (bfloat16, rows >= M and columns >= K zero) and
+  // the row's factor rsqrt(mean(h^2) + eps) multiplies the float sums in the epilogue:
+  //   (h * inv * w) W^T = inv * ((h * w) W^T).
+  // So a row goes to shared memory as soon as it has been read, and its statistic is reduced
+  // beside that instead of standing between the read and the products.
   if (pr.h_in != nullptr) {
     // (The stream is read past L1: in a chain of products other blocks have just added to it.)
-    // One warp per token, two tokens at a time, 8 float4 per lane and token in flight: for
-    // widths up to 1024 a token's row is read once and stays in registers between the sum of
-    // squares and the scaling.
+    // One warp per token, two tokens at a time, 8 float4 per lane and token in flight.
     constexpr int kV = 8;                 // float4 per lane per pass
     constexpr int kPass = kV * 32 * 4;    // 1024 columns per pass
     constexpr int kTok = MP >= 2 * (kSgThreads / 32) ? 2 : 1;  // tokens per warp and round: all warps busy, and every warp walks the loop equally often
+    bool weights_in = false;
     for (int m0 = warp * kTok; m0 < MP; m0 += kTok * (kSgThreads / 32)) {
-      float inv[kTok];
-      float4 keep[kTok][kV];
+      float ss[kTok];
 #pragma unroll
-      for (int j = 0; j < kTok; ++j) {
-        const int m = m0 + j;
-        float ss = 0.f;
-        if (m < M) {
-          const float* row = pr.h_in + static_cast<size_t>(m) * K;
-          for (int kb = 0; kb < K; kb += kPass) {
+      for (int j = 0; j < kTok; ++j) ss[j] = 0.f;
+      for (int kb = 0; kb < max(K, k0 + kx); kb += kPass) {
+        float4 keep[kTok][kV];
 #pragma unroll
-            for (int i = 0; i < kV; ++i) {
-              const int k = kb + (i * 32 + lane) * 4;
-              keep[j][i] = (k < K) ? __ldcg(reinterpret_cast<const float4*>(row + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int i = 0; i < kV; ++i)
-              ss += keep[j][i].x * keep[j][i].x + keep[j][i].y * keep[j][i].y + keep[j][i].z * keep[j][i].z +
-                    keep[j][i].w * keep[j][i].w;
-          }
-        }
-        ss = warp_sum(ss);
-        inv[j] = 1.0f / sqrtf(ss / static_cast<float>(K) + pr.eps);
-      }
-      sg_wait<0>();  // the norm weights (and, incidentally, the first weight chunks) have landed
-      __syncthreads();           // ... and everyone else's; every warp walks this loop equally often
-#pragma unroll
-      for (int j = 0; j < kTok; ++j) {
-        const int m = m0 + j;
-        if (m >= MP) continue;
-        const float* row = pr.h_in + static_cast<size_t>(m < M ? m : 0) * K;
-        for (int kb = k0; kb < k0 + kx; kb += kPass) {
+        for (int j = 0; j < kTok; ++j) {
+          const int m = m0 + j;
+          const float* row = pr.h_in + static_cast<size_t>(m < M ? m : 0) * K;
 #pragma unroll
           for (int i = 0; i < kV; ++i) {
             const int k = kb + (i * 32 + lane) * 4;
-            if (k >= k0 + kx) continue;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (m < M && k < k1) {
-              v = (K <= kPass && k0 == 0) ? keep[j][i] : __ldcg(reinterpret_cast<const float4*>(row + k));
+            keep[j][i] = (m < M && k < K) ? __ldcg(reinterpret_cast<const float4*>(row + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+        if (!weights_in) {
+          sg_wait<0>();     // the norm weights (and, incidentally, the first weight chunks) have landed
+          __syncthreads();  // ... and everyone else's; every warp comes here once, in its first round
+          weights_in = true;
+        }
+#pragma unroll
+        for (int j = 0; j < kTok; ++j) {
+          const int m = m0 + j;
+#pragma unroll
+          for (int i = 0; i < kV; ++i) {
+            const int k = kb + (i * 32 + lane) * 4;
+            float4 v = keep[j][i];
+            ss[j] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            if (m >= MP || k < k0 || k >= k0 + kx) continue;
+            if (k < k1) {
               const float4 w4 = *reinterpret_cast<const float4*>(sNw + (k - k0));
-              v.x = v.x * inv[j] * w4.x;
-              v.y = v.y * inv[j] * w4.y;
-              v.z = v.z * inv[j] * w4.z;
-              v.w = v.w * inv[j] * w4.w;
+              v.x *= w4.x;
+              v.y *= w4.y;
+              v.z *= w4.z;
+              v.w *= w4.w;
+            } else {
+              v = make_float4(0.f, 0.f, 0.f, 0.f);
             }
             bf16* dst = sX + m * xs + (k - k0);
             *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(v.x, v.y);
@@ -250,6 +248,15 @@ __device__ void SkinnyBlock<MT, MODE>::run() const {
           }
         }
       }
+#pragma unroll
+      for (int j = 0; j < kTok; ++j) {
+        const float tot = warp_sum(ss[j]);
+        if (lane == 0 && m0 + j < MP) sInv[m0 + j] = 1.0f / sqrtf(tot / static_cast<float>(K) + pr.eps);
+      }
+    }
+    if (!weights_in) {  // (a warp without a token of its own: MP < warps)
+      sg_wait<0>();
+      __syncthreads();
     }
   }
 
@@ -370,8 +377,9 @@ __device__ void SkinnyBlock<MT, MODE>::finish_tile(float (&acc)[MT][4], int n0) 
         for (int e = 0; e < 4; ++e) {
           const int f = n0 + g + (e >> 1) * 8, m = nt * 8 + t2 + (e & 1);
           if (f < args.N && m < M) {
-            const float up = sRed[(g + (e >> 1) * 8) * MP + m];
-            args.y[static_cast<size_t>(m) * args.ldy + f] = __float2bfloat16_rn(silu_fast(acc[nt][e] * pr.scale) * up);
+            const float inv = pr.h_in ? sInv[m] : 1.f;  // the row's norm factor (norm prologue)
+            const float up = sRed[(g + (e >> 1) * 8) * MP + m] * inv;
+            args.y[static_cast<size_t>(m) * args.ldy + f] = __float2bfloat16_rn(silu_fast(acc[nt][e] * inv * pr.scale) * up);
           }
         }
       }
@@ -387,7 +395,8 @@ __device__ void SkinnyBlock<MT, MODE>::finish_tile(float (&acc)[MT][4], int n0) 
         const int n = n0 + ft * 16 + g + (e >> 1) * 8, m = nt * 8 + t2 + (e & 1);
         if (n < args.N && m < M) {
           if (MODE == kSgStore) {
-            args.y[static_cast<size_t>(m) * args.ldy + n] = __float2bfloat16_rn(acc[nt][e]);
+            const float inv = pr.h_in ? sInv[m] : 1.f;  // the row's norm factor (norm prologue)
+            args.y[static_cast<size_t>(m) * args.ldy + n] = __float2bfloat16_rn(acc[nt][e] * inv);
           } else if (MODE == kSgStoreF32) {
             args.y32[static_cast<size_t>(m) * args.ldy + n] = args.y_scale * acc[nt][e];
           } else {
@@ -506,7 +515,7 @@ __global__ void __launch_bounds__(kSgThreads) skinny_chain_kernel(const SkinnyCh
 inline size_t skinny_smem(int MP, int kx) {
   return static_cast<size_t>(sg_stages(MP / 8)) * kSgRows * kSgWStride * sizeof(bf16) +
          static_cast<size_t>(MP) * (kx + 8) * sizeof(bf16) + 3 * 32 * MP * sizeof(float) +
-         static_cast<size_t>(kx) * sizeof(float);
+         static_cast<size_t>(kx + MP) * sizeof(float);
 }
 
 template <int MT, int MODE>

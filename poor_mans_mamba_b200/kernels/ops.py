@@ -856,7 +856,7 @@ def skinny_fits(M: int, K: int) -> bool:
     mp = 8 if M <= 8 else 16 if M <= 16 else 32 if M <= 32 else 64
     kx = (K + 255) // 256 * 256
     stages = 3 if mp > 32 else 5
-    return M <= 64 and stages * 32 * 264 * 2 + mp * (kx + 8) * 2 + 3 * 32 * mp * 4 + kx * 4 <= 220 * 1024
+    return M <= 64 and stages * 32 * 264 * 2 + mp * (kx + 8) * 2 + 3 * 32 * mp * 4 + (kx + mp) * 4 <= 220 * 1024
 
 
 def skinny_linear_norm(h: Tensor, norm_weight: Tensor, eps: float, weight: Tensor, out: Tensor) -> None:

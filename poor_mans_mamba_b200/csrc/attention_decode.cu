@@ -22,9 +22,14 @@
 //   x'[i] <- x'[i] cos - x'[i+Dh/2] sin;  x'[i+Dh/2] <- x'[i+Dh/2] cos + x'[i] sin
 //   sc[s] = (q.K[s]) * scale;  p = exp(sc - max);  o = sum p V / sum p
 // (reference src/ops/gpu/attention.cu:4-40 and :44-105), keys lo..pos, lo from the window.
-// With several key splits the block that finishes a (sequence, head)'s last split merges them.
+// Several key splits of a (sequence, head) are merged without a second launch.  Up to 16 splits run
+// as one thread-block cluster: every block writes its (maximum, sum, unnormalised output) into the
+// first block's shared memory and arrives on a barrier there; the first block merges and stores.
+// More splits (or results too large for that buffer) go through global memory and a counter: the
+// block that finishes the last split merges them.
 // Every mbarrier wait is bounded; a wait that gives up writes a code (31: a tile never landed,
-// 32: a stage never came free) to *status, and the step's results are discarded by the host.
+// 32: a stage never came free, 33: another block's result never came) to *status, and the step's
+// results are discarded by the host.
 #include "mma_helpers.cuh"
 #include "tcgen05.cuh"
 #include <math_constants.h>
@@ -40,6 +45,12 @@ __host__ __device__ constexpr int da_stages(int dh) { return dh > 64 ? 3 : 4; }
 __host__ __device__ constexpr size_t da_smem(int dh) {
   return 1024 /*alignment*/ + static_cast<size_t>(2 * da_stages(dh)) * kDaKeys * dh * 2 + 16 * (dh + 8) * 2;
 }
+// what the first block of a cluster receives: (splits - 1) x G rows of (Dh values, maximum, sum)
+__host__ __device__ constexpr size_t da_parts_bytes(int dh, int G, int n_splits) {
+  return static_cast<size_t>(n_splits - 1) * G * (dh + 2) * sizeof(float);
+}
+constexpr size_t kDaPartsMax = 24 * 1024;  // (the V ring is 32 KB at head size 64, 48 KB at 128)
+constexpr int kDaClusterMax = 16;
 
 struct DecodeAttnArgs {
   const bf16* q;          // [n_seq, ldq] unrotated queries
@@ -61,7 +72,39 @@ struct DecodeAttnArgs {
   int window, split_len, n_splits, page_size, Hq, Hkv;
   int* split_counter;
   int* status;
+  int clustered;          // the key splits of a (sequence, head) are one cluster (gridDim.z blocks)
 };
+
+// Address of a shared-memory location of this block in block `rank` of the cluster.
+__device__ __forceinline__ unsigned cluster_addr(unsigned smem_addr, unsigned rank) {
+  unsigned r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(unsigned addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(addr), "f"(v) : "memory");
+}
+// Arrival on a barrier of another block of the cluster; this thread's earlier writes into that
+// block's shared memory are visible to whoever has waited for the barrier.
+__device__ __forceinline__ void mbar_arrive_remote(unsigned cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_bar) : "memory");
+}
+// Bounded wait on a barrier of this block on which other blocks of the cluster arrive.
+__device__ __forceinline__ bool mbar_wait_cluster(unsigned long long* bar, unsigned parity, volatile int* abort_flag) {
+  for (unsigned i = 0; i < kSpinLimit; ++i) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if (abort_flag && (i & 63) == 63 && *abort_flag) return false;
+  }
+  return false;
+}
 
 template <int DH>
 __global__ void __launch_bounds__(kDaThreads)
@@ -78,7 +121,7 @@ __global__ void __launch_bounds__(kDaThreads)
   constexpr int CHUNKS = DH / 8;             // 16-byte pieces per row
 
   extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long bar_full[NSTAGE], bar_empty[NSTAGE];
+  __shared__ __align__(8) unsigned long long bar_full[NSTAGE], bar_empty[NSTAGE], bar_parts;
   __shared__ int s_bt[kDaBtCap];
   __shared__ __align__(16) bf16 s_new_k[DH], s_new_v[DH];
   __shared__ float s_wm[4][16], s_wl[4][16], s_M[16], s_L[16];
@@ -104,16 +147,21 @@ __global__ void __launch_bounds__(kDaThreads)
   unsigned char* sK = ring;
   unsigned char* sV = ring + NSTAGE * TILE;
   bf16* sQ = reinterpret_cast<bf16*>(ring + 2 * NSTAGE * TILE);
+  float* sParts = reinterpret_cast<float*>(sV);  // (clustered, in the first block, once every block's tiles are done) [split - 1][G][DH + 2]
 
   if (tid == 0) {
     for (int s = 0; s < NSTAGE; ++s) {
       mbar_init(&bar_full[s], 1);
       mbar_init(&bar_empty[s], 4);
     }
+    mbar_init(&bar_parts, 128 * (a.n_splits > 1 ? a.n_splits - 1 : 1));
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncthreads();
+  // (clustered) every block has its barrier ready before another block arrives on it: the arrival
+  // is here, the wait before the first access to the first block's shared memory
+  if (a.clustered) asm volatile("barrier.cluster.arrive.relaxed.aligned;\n" ::: "memory");
   volatile int* abort_flag = &s_abort;
   auto give_up = [&](int code) {
     if (!*abort_flag) atomicExch(a.status, code);
@@ -343,6 +391,13 @@ __global__ void __launch_bounds__(kDaThreads)
     if (lane == 0) mbar_arrive(&bar_empty[s]);  // this warp is done with the stage
   }
   sync_compute();  // every warp is done with the ring (it is reused below)
+  if (a.clustered) {
+    // Second round of the cluster barrier: this block's tiles are done (all of them have landed and
+    // been used: nothing writes into its ring any more).  Behind it the first block's V ring takes
+    // the other blocks' results.
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;\n" ::: "memory");
+  }
 
   constexpr float kLn2 = 0.6931471805599453f;
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
@@ -353,7 +408,14 @@ __global__ void __launch_bounds__(kDaThreads)
   // merge the four warps (each saw a quarter of the keys) through shared memory
   constexpr int SO = DH + 4;                 // padded row: rows g and g+1 fall into different banks
   float* sO = reinterpret_cast<float*>(sK);  // [4 warps][16][SO]; a gave-up block may still have copies in
-  if (*abort_flag) return;                   // flight into the ring: it leaves its part unwritten
+  if (*abort_flag) {                         // flight into the ring: it leaves its part unwritten
+    // (clustered) the first block stays until the others have sent: its shared memory must outlive their writes
+    if (a.clustered && z == 0) {
+      asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+      mbar_wait_cluster(&bar_parts, 0, nullptr);
+    }
+    return;  // (a block that gave up has arrived twice like every other: nobody waits for it)
+  }
   if ((lane & 3) == 0) {
     s_wm[warp][r_lo] = m_lo;
     s_wm[warp][r_hi] = m_hi;
@@ -385,6 +447,51 @@ __global__ void __launch_bounds__(kDaThreads)
   }
   sync_compute();
   const int n_splits = a.n_splits;
+  if (a.clustered) {
+    // ---- the splits of this (sequence, head) are one cluster: block z sends its part to block 0
+    constexpr int PW = DH + 2;  // a row of a part: Dh values, maximum (exponent's unit), sum
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");  // every block's tiles are done
+    if (z > 0) {
+      const unsigned dst = cluster_addr(smem_u32(sParts), 0) + static_cast<unsigned>((z - 1) * G * PW) * 4u;
+      for (int i = tid; i < G * DH; i += 128) {
+        const int r = i / DH, d = i % DH;
+        const float sum = (sO[r * SO + d] + sO[(16 + r) * SO + d]) + (sO[(32 + r) * SO + d] + sO[(48 + r) * SO + d]);
+        st_cluster_f32(dst + static_cast<unsigned>(r * PW + d) * 4u, sum);
+        if (d == 0) {
+          st_cluster_f32(dst + static_cast<unsigned>(r * PW + DH) * 4u, s_M[r]);
+          st_cluster_f32(dst + static_cast<unsigned>(r * PW + DH + 1) * 4u, s_L[r]);
+        }
+      }
+      mbar_arrive_remote(cluster_addr(smem_u32(&bar_parts), 0));  // releases this thread's writes above
+      return;
+    }
+    // block 0: its own part is in sO / s_M / s_L; the others arrive in sParts
+    if (!mbar_wait_cluster(&bar_parts, 0, abort_flag)) {
+      if (lane == 0) give_up(33);
+      return;
+    }
+    for (int i = tid; i < G * (DH / 2); i += 128) {  // a thread per (row, two columns)
+      const int r = i / (DH / 2), d = (i % (DH / 2)) * 2;
+      float mx = s_M[r];
+      for (int p = 0; p < n_splits - 1; ++p) mx = fmaxf(mx, sParts[(p * G + r) * PW + DH]);
+      const float mu = (mx == -CUDART_INF_F) ? 0.f : mx;
+      float w = exp2f(s_M[r] - mu);  // (-inf - 0 -> 0: a part without keys)
+      float tot = w * s_L[r];
+      float a0 = w * ((sO[r * SO + d] + sO[(16 + r) * SO + d]) + (sO[(32 + r) * SO + d] + sO[(48 + r) * SO + d]));
+      float a1 = w * ((sO[r * SO + d + 1] + sO[(16 + r) * SO + d + 1]) + (sO[(32 + r) * SO + d + 1] + sO[(48 + r) * SO + d + 1]));
+      for (int p = 0; p < n_splits - 1; ++p) {
+        const float* part = sParts + (p * G + r) * PW;
+        w = exp2f(part[DH] - mu);
+        tot += w * part[DH + 1];
+        a0 += w * part[d];
+        a1 += w * part[d + 1];
+      }
+      const float inv = tot > 0.f ? 1.f / tot : 0.f;
+      *reinterpret_cast<__nv_bfloat162*>(a.out + (static_cast<size_t>(seq) * a.Hq + hk * G + r) * DH + d) =
+          __floats2bfloat162_rn(a0 * inv, a1 * inv);
+    }
+    return;
+  }
   for (int i = tid; i < G * DH; i += 128) {
     const int r = i / DH, d = i % DH;
     const int hq = hk * G + r;
@@ -456,13 +563,46 @@ __global__ void __launch_bounds__(kDaThreads)
 }
 
 template <int DH>
-int launch_decode_attention(const CUtensorMap& map, const DecodeAttnArgs& a, int n_seq, cudaStream_t stream) {
+int launch_decode_attention(const CUtensorMap& map, DecodeAttnArgs a, int n_seq, cudaStream_t stream) {
   auto kern = decode_attention_kernel<DH>;
-  const size_t smem = da_smem(DH);
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-  if (e != cudaSuccess) return static_cast<int>(e);
-  launch_pdl(kern, dim3(n_seq, a.Hkv, a.n_splits), dim3(kDaThreads), smem, stream, map, a);
+  const int G = a.Hq / a.Hkv;
+  // the key splits as one cluster where they are few enough and their results fit beside the ring
+  const size_t parts = a.n_splits > 1 ? (da_parts_bytes(DH, G, a.n_splits) + 15) / 16 * 16 : 0;
+  a.clustered = a.n_splits > 1 && a.n_splits <= kDaClusterMax && parts <= kDaPartsMax ? 1 : 0;
+  const size_t smem = da_smem(DH);  // (the results of a cluster's blocks go into the first block's idle V ring)
+  static bool attrs_set = false;
+  if (!attrs_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attrs_set = true;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(n_seq, a.Hkv, a.n_splits);
+  cfg.blockDim = dim3(kDaThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = 1;
+  if (a.clustered) {
+    attrs[1].id = cudaLaunchAttributeClusterDimension;
+    attrs[1].val.clusterDim.x = 1;
+    attrs[1].val.clusterDim.y = 1;
+    attrs[1].val.clusterDim.z = a.n_splits;
+    cfg.numAttrs = 2;
+    int fit = 0;  // a cluster this large may not find room (shared memory, blocks of one GPC): then through the counter
+    if (cudaOccupancyMaxActiveClusters(&fit, kern, &cfg) != cudaSuccess || fit < 1) {
+      (void)cudaGetLastError();
+      a.clustered = 0;
+      cfg.numAttrs = 1;
+    }
+  }
+  if (!a.clustered && a.n_splits > 1 && (!a.part_o || !a.part_ml || !a.split_counter)) return PMM_ERR_BAD_ARGUMENT;
+  cudaLaunchKernelEx(&cfg, kern, map, a);
   return launch_status();
 }
 

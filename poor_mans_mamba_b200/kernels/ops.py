@@ -1048,7 +1048,7 @@ def _tc_status(device: torch.device) -> Tensor:
 
 def tc_gemm_status(device) -> int:
     """0 unless a bounded wait inside a tensor-core kernel gave up (tc_gemm: 1 producer, 2 MMA
-    issuer, 3 epilogue; attention_tc: 11..15; skinny_tc: 21..24; decode attention: 31, 32).  Reading it waits for the device."""
+    issuer, 3 epilogue; attention_tc: 11..15; skinny_tc: 21..24; decode attention: 31..33).  Reading it waits for the device."""
     return int(_tc_status(torch.device(device)).item())
 
 

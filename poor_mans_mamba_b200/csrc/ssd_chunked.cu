@@ -241,37 +241,12 @@ __global__ void __launch_bounds__(128)
 }
 
 // ----------------------------------------------------------------------------- phase 2
-__global__ void ssd_state_pass_kernel(const float* __restrict__ chunk_state, const float* __restrict__ chunk_decay,
-                                      bf16* __restrict__ start_state, float* __restrict__ state,
-                                      const int* __restrict__ cu, const int* __restrict__ slots, int H, int PN, int q,
-                                      int n_seq, int seqs_per_block, int skip_single) {
-  pdl_launch_dependents();
-  pdl_wait();
-  // four state elements per thread (P*N is a multiple of 4 for every compiled pair)
-  const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
-  const int h = blockIdx.y, seq0 = blockIdx.z * seqs_per_block;
-  // chunks of the sequences before the block's first one: the threads share the sequences, so the
-  // loads of their bounds go out together (a step may hold hundreds of sequences)
-  __shared__ int s_first[32];
-  int mine = 0;
-  for (int s = threadIdx.x; s < seq0; s += blockDim.x) mine += (cu[s + 1] - cu[s] + q - 1) / q;  // q: tokens per chunk
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
-  if ((threadIdx.x & 31) == 0) s_first[threadIdx.x >> 5] = mine;
-  __syncthreads();
-  int first = 0;
-  for (int w = 0; w < static_cast<int>(blockDim.x >> 5); ++w) first += s_first[w];
-  if (e >= PN) return;
-  // a block takes several sequences in turn when a step holds many (mostly short) ones
-  for (int seq = seq0; seq < min(n_seq, seq0 + seqs_per_block); ++seq) {
-  const int n_tok = cu[seq + 1] - cu[seq];
-  const int nc = (n_tok + q - 1) / q;
-  if (nc <= 0) continue;
-  if (skip_single && n_tok == 1) {  // left to the token-serial kernel
-    first += nc;
-    continue;
-  }
-  float4* sp = reinterpret_cast<float4*>(state + (static_cast<size_t>(slots[seq]) * H + h) * PN + e);
+// One sequence's chunks folded into its state, four state elements `e .. e+3` of head h per thread:
+// the state before each chunk goes to start_state (bfloat16), the state after the last to `state`.
+__device__ __forceinline__ void ssd_pass_sequence(const float* __restrict__ chunk_state, const float* __restrict__ chunk_decay,
+                                                  bf16* __restrict__ start_state, float* __restrict__ state, int slot, int H,
+                                                  int PN, int h, int e, int first, int nc) {
+  float4* sp = reinterpret_cast<float4*>(state + (static_cast<size_t>(slot) * H + h) * PN + e);
   float4 s = *sp;
   // The chain through s is short; the loads are what cost: eight chunks are requested at a time,
   // and the next eight while these are folded in, so a walk costs about one round trip to L2.
@@ -314,8 +289,96 @@ __global__ void ssd_state_pass_kernel(const float* __restrict__ chunk_state, con
     }
   }
   *sp = s;
-  first += nc;
+}
+
+__global__ void ssd_state_pass_kernel(const float* __restrict__ chunk_state, const float* __restrict__ chunk_decay,
+                                      bf16* __restrict__ start_state, float* __restrict__ state,
+                                      const int* __restrict__ cu, const int* __restrict__ slots, int H, int PN, int q,
+                                      int n_seq, int seqs_per_block, int skip_single) {
+  pdl_launch_dependents();
+  pdl_wait();
+  // four state elements per thread (P*N is a multiple of 4 for every compiled pair)
+  const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  const int h = blockIdx.y, seq0 = blockIdx.z * seqs_per_block;
+  // chunks of the sequences before the block's first one: the threads share the sequences, so the
+  // loads of their bounds go out together (a step may hold hundreds of sequences)
+  __shared__ int s_first[32];
+  int mine = 0;
+  for (int s = threadIdx.x; s < seq0; s += blockDim.x) mine += (cu[s + 1] - cu[s] + q - 1) / q;  // q: tokens per chunk
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+  if ((threadIdx.x & 31) == 0) s_first[threadIdx.x >> 5] = mine;
+  __syncthreads();
+  int first = 0;
+  for (int w = 0; w < static_cast<int>(blockDim.x >> 5); ++w) first += s_first[w];
+  if (e >= PN) return;
+  // a block takes several sequences in turn when a step holds many (mostly short) ones
+  for (int seq = seq0; seq < min(n_seq, seq0 + seqs_per_block); ++seq) {
+    const int n_tok = cu[seq + 1] - cu[seq];
+    const int nc = (n_tok + q - 1) / q;
+    if (nc <= 0) continue;
+    if (!(skip_single && n_tok == 1))  // (a lone token is left to the token-serial kernel)
+      ssd_pass_sequence(chunk_state, chunk_decay, start_state, state, slots[seq], H, PN, h, e, first, nc);
+    first += nc;
   }
+}
+
+// The same pass for a mixed step, in which most sequences bring one token and are none of this
+// pass's business (the token-serial kernel takes them): block z takes the z-th sequence that brings
+// more than one token.  Every block finds it by itself: the threads read the bounds of all sequences
+// at once (a run of sequences per thread), a scan over the 256 runs gives each run's place among the
+// sequences with more than one token and among the chunks, and the thread whose run holds number z
+// announces it.  (A block that walked the sequences in turn paid a round trip to L2 for each of the
+// 32 lone ones: 33 us a layer in a step of 36 sequences, against 8 for the four that matter.)
+__global__ void __launch_bounds__(256)
+    ssd_state_pass_multi_kernel(const float* __restrict__ chunk_state, const float* __restrict__ chunk_decay,
+                                bf16* __restrict__ start_state, float* __restrict__ state, const int* __restrict__ cu,
+                                const int* __restrict__ slots, int H, int PN, int q, int n_seq) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ int s_multi[256], s_chunks[256];
+  __shared__ int s_seq, s_first, s_nc;
+  const int tid = threadIdx.x;
+  const int per = (n_seq + 255) / 256;
+  const int lo = min(n_seq, tid * per), hi = min(n_seq, lo + per);
+  int multi = 0, chunks = 0;
+  for (int s = lo; s < hi; ++s) {
+    const int n = cu[s + 1] - cu[s];
+    multi += n > 1 ? 1 : 0;
+    chunks += (n + q - 1) / q;
+  }
+  s_multi[tid] = multi;
+  s_chunks[tid] = chunks;
+  if (tid == 0) s_seq = -1;
+  __syncthreads();
+  for (int o = 1; o < 256; o <<= 1) {  // inclusive scan over the runs
+    const int a = tid >= o ? s_multi[tid - o] : 0, b = tid >= o ? s_chunks[tid - o] : 0;
+    __syncthreads();
+    s_multi[tid] += a;
+    s_chunks[tid] += b;
+    __syncthreads();
+  }
+  const int want = blockIdx.z;
+  int m = s_multi[tid] - multi, c = s_chunks[tid] - chunks;  // before this thread's run
+  if (want >= m && want < m + multi) {
+    for (int s = lo; s < hi; ++s) {
+      const int n = cu[s + 1] - cu[s];
+      const int nc = (n + q - 1) / q;
+      if (n > 1) {
+        if (m == want) {
+          s_seq = s;
+          s_first = c;
+          s_nc = nc;
+        }
+        ++m;
+      }
+      c += nc;
+    }
+  }
+  __syncthreads();
+  const int e = (blockIdx.x * blockDim.x + tid) * 4;
+  if (s_seq < 0 || e >= PN) return;
+  ssd_pass_sequence(chunk_state, chunk_decay, start_state, state, slots[s_seq], H, PN, blockIdx.y, e, s_first, s_nc);
 }
 
 // ----------------------------------------------------------------------------- phase 3
@@ -510,10 +573,16 @@ __global__ void __launch_bounds__(128)
 }
 
 // The state pass alone, for chunks of `q` tokens (the tcgen05 scan of ssd_tc.cu uses it with 128).
+// n_multi: with skip_single, the number of sequences that bring more than one token (0: not known).
 int launch_ssd_state_pass(const float* chunk_state, const float* chunk_decay, bf16* start_state, float* state,
-                          const int* cu, const int* slots, int n_seq, int H, int PN, int q, int skip_single,
+                          const int* cu, const int* slots, int n_seq, int H, int PN, int q, int skip_single, int n_multi,
                           cudaStream_t stream) {
-  if (PN % 4 || n_seq > 65535 || H > 65535 || q <= 0) return PMM_ERR_BAD_ARGUMENT;
+  if (PN % 4 || n_seq > 65535 || H > 65535 || q <= 0 || n_multi < 0 || n_multi > n_seq) return PMM_ERR_BAD_ARGUMENT;
+  if (skip_single && n_multi > 0) {
+    launch_pdl(ssd_state_pass_multi_kernel, dim3((PN / 4 + 255) / 256, H, n_multi), dim3(256), 0, stream, chunk_state, chunk_decay,
+               start_state, state, cu, slots, H, PN, q, n_seq);
+    return launch_status();
+  }
   // about a thousand blocks: with many sequences a block takes several of them in turn
   const int per_seq = ((PN / 4 + 255) / 256) * H;
   int spb = static_cast<int>((static_cast<long long>(n_seq) * per_seq + 1023) / 1024);

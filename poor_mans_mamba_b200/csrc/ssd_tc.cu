@@ -40,7 +40,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 // Launches the state pass of ssd_chunked.cu for chunks of `q` tokens.
 int launch_ssd_state_pass(const float* chunk_state, const float* chunk_decay, bf16* start_state, float* state,
-                          const int* cu, const int* slots, int n_seq, int H, int PN, int q, int skip_single,
+                          const int* cu, const int* slots, int n_seq, int H, int PN, int q, int skip_single, int n_multi,
                           cudaStream_t stream);
 
 __device__ __forceinline__ int tq_swz(int row, int chunk) {
@@ -682,13 +682,15 @@ PMM_EXPORT int pmm_ssd_tc_supported(int P, int N) {
 // sequences of ceil(new tokens / 128).
 // z_raw (or nullptr): the gate's input [T, ld_z], y <- y * silu(z_raw * z_scale + z_bias).
 // skip_single: sequences that bring exactly one token are left alone (state and y): in a mixed step
-// the token-serial kernel takes them (pmm_ssm_scan_seq with one_token = 2).
+// the token-serial kernel takes them (pmm_ssm_scan_seq with one_token = 2); n_multi is then the
+// number of sequences that bring more than one token (0: not known).
 // status: one int in device memory that stays 0 unless a bounded wait gave up.
 PMM_EXPORT int pmm_ssd_tc(const void* xbc, int ld_xbc, const void* dt_raw, long long ld_dt, float dt_scale,
                           const float* dt_shift, const float* a_log, const float* d_skip, float* state, const int* cu,
                           const int* slots, void* y, float* chunk_state, float* chunk_decay, float* chunk_dt,
                           void* start_state, int n_seq, int n_chunks, int H, int P, int N, int G, const void* z_raw, long long ld_z,
-                          float z_scale, const float* z_bias, int skip_single, int* status, cudaStream_t stream) {
+                          float z_scale, const float* z_bias, int skip_single, int n_multi, int* status,
+                          cudaStream_t stream) {
   using namespace pmm;
   if (n_seq <= 0 || n_chunks <= 0) return 0;
   if (!pmm_ssd_tc_supported(P, N) || H <= 0 || G <= 0 || H % G || n_seq > 65535 || !chunk_state || !chunk_decay ||
@@ -723,7 +725,7 @@ PMM_EXPORT int pmm_ssd_tc(const void* xbc, int ld_xbc, const void* dt_raw, long 
              dt_scale, dt_shift, a_log, cu, n_seq, chunk_state, chunk_decay, chunk_dt, H, P, N, G, slabs_per_group, tmem_cols,
              skip_single, status);
   int rc = launch_ssd_state_pass(chunk_state, chunk_decay, static_cast<bf16*>(start_state), state, cu, slots, n_seq, H,
-                                 P * N, kTQ, skip_single, stream);
+                                 P * N, kTQ, skip_single, n_multi, stream);
   if (rc != 0) return rc;
   launch_pdl(ssd_tc_output_kernel, dim3(n_chunks, H * (P / PB)), dim3(kTOut), smem3, stream, xb, ld_xbc,
              static_cast<const float*>(chunk_dt), d_skip, cu, n_seq, static_cast<const bf16*>(start_state),

@@ -49,7 +49,7 @@ _SIGNATURES = {
     "pmm_ssd_tc_supported": [c_int, c_int],
     "pmm_ssd_tc": [c_void_p, c_int, c_void_p, c_longlong, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                   c_longlong, c_float, c_void_p, c_int, c_void_p, c_void_p],
+                   c_longlong, c_float, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "pmm_gated_norm": [c_void_p, c_void_p, c_longlong, c_float, c_void_p, c_void_p, c_float, c_int,
                        c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_qkv_rope_store": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_float,
@@ -600,7 +600,8 @@ def ssm_scan_tc(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Tensor, 
     _call("pmm_ssd_tc", xbc.data_ptr(), ld_x, dt_raw.data_ptr(), ld_dt, float(dt_scale), dt_shift.data_ptr(),
           a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), cu.data_ptr(), slots.data_ptr(), out.data_ptr(),
           chunk_state, chunk_decay, chunk_dt, start_state, len(new_lens), n_chunks, H, P, N, n_groups, zp, ld_z, zs, zb,
-          int(bool(skip_single)), _tc_status(xbc.device).data_ptr(), _stream())
+          int(bool(skip_single)), sum(1 for n in new_lens if n > 1) if skip_single else 0,
+          _tc_status(xbc.device).data_ptr(), _stream())
 
 
 def gated_norm(y: Tensor, z_raw: Tensor, z_scale: float, z_bias: Optional[Tensor],

@@ -594,9 +594,15 @@ int launch_decode_attention(const CUtensorMap& map, DecodeAttnArgs a, int n_seq,
     attrs[1].val.clusterDim.y = 1;
     attrs[1].val.clusterDim.z = a.n_splits;
     cfg.numAttrs = 2;
-    int fit = 0;  // a cluster this large may not find room (shared memory, blocks of one GPC): then through the counter
-    if (cudaOccupancyMaxActiveClusters(&fit, kern, &cfg) != cudaSuccess || fit < 1) {
-      (void)cudaGetLastError();
+    // a cluster this large may not find room (shared memory, blocks of one GPC): then through the counter
+    static signed char fits[kDaClusterMax + 1] = {};  // per cluster size: 0 not asked yet, 1 fits, -1 does not
+    if (fits[a.n_splits] == 0) {
+      int n = 0;
+      const bool ok = cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n >= 1;
+      if (!ok) (void)cudaGetLastError();
+      fits[a.n_splits] = ok ? 1 : -1;
+    }
+    if (fits[a.n_splits] < 0) {
       a.clustered = 0;
       cfg.numAttrs = 1;
     }

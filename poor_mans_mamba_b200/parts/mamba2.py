@@ -32,15 +32,16 @@ _CHUNKED_FROM = 8
 # seven size pairs it is compiled for).
 _TC_SCAN = os.environ.get("PMM_TCGEN05_SCAN", "1") == "1"
 _NOTED = set()
-_LONE_STREAMS: Dict[torch.device, "torch.cuda.Stream"] = {}
+_BRANCH_STREAMS: Dict[tuple, "torch.cuda.Stream"] = {}
 
 
-def _lone_stream(device: torch.device) -> "torch.cuda.Stream":
-    """The stream on which a mixed step's lone tokens are scanned beside the prompt portions."""
-    st = _LONE_STREAMS.get(device)
+def _branch_stream(device: torch.device, what: str) -> "torch.cuda.Stream":
+    """A stream for work that runs beside the scan's chain of launches: "lone" (a mixed step's lone
+    tokens beside the prompt portions), "window" (the convolution windows' update)."""
+    st = _BRANCH_STREAMS.get((device, what))
     if st is None:
         st = torch.cuda.Stream(device=device)
-        _LONE_STREAMS[device] = st
+        _BRANCH_STREAMS[(device, what)] = st
     return st
 
 
@@ -182,14 +183,22 @@ class Mamba2Mixer(Mixer):
         state = cache.fixed(f"{self.name}.ssm")
 
         xbc = ws.alloc((T, self.conv_dim), proj.dtype)
+        window_updating = None
         if ctx.decode_only:
             K.conv1d_decode(xbc_raw, self.conv_pre_scale, self.conv_pre_bias, self.conv_w, self.conv_b,
                             window, ctx.slots, xbc)
         else:
             K.conv1d_fwd(xbc_raw, self.conv_pre_scale, self.conv_pre_bias, self.conv_w, self.conv_b, window,
                          ctx.seq_of, ctx.cu_seqlens, ctx.slots, xbc, weight_t=self.conv_w_t)
-            K.conv1d_window_update(xbc_raw, self.conv_pre_scale, self.conv_pre_bias, window, ctx.cu_seqlens,
-                                   ctx.slots, ctx.n_seq, self.d_conv)
+            # The window is next read by the next step: its update leaves the scan's chain (a branch
+            # of its own in a captured step, joined before this mixer returns).
+            here = torch.cuda.current_stream(xbc.device)
+            update = _branch_stream(xbc.device, "window")
+            update.wait_stream(here)
+            with torch.cuda.stream(update):
+                K.conv1d_window_update(xbc_raw, self.conv_pre_scale, self.conv_pre_bias, window, ctx.cu_seqlens,
+                                       ctx.slots, ctx.n_seq, self.d_conv)
+            window_updating = (here, update)
 
         y = ws.alloc((T, i_dim), proj.dtype)
         # without a norm the gate y * silu(z) is the scan kernels' epilogue
@@ -208,7 +217,7 @@ class Mamba2Mixer(Mixer):
                 # a chain of three tensor-core launches: they run side by side (parallel branches of a
                 # captured step).
                 here = torch.cuda.current_stream(xbc.device)
-                side = _lone_stream(xbc.device)
+                side = _branch_stream(xbc.device, "lone")
                 side.wait_stream(here)
                 with torch.cuda.stream(side):
                     K.ssm_scan_seq(xbc, dt, self.dt_scale, self.dt_shift, self.a_log, self.d_skip, state,
@@ -229,6 +238,8 @@ class Mamba2Mixer(Mixer):
             K.ssm_scan_seq(xbc, dt, self.dt_scale, self.dt_shift, self.a_log, self.d_skip, state,
                            ctx.cu_seqlens, ctx.slots, ctx.n_seq, y, self.n_groups, gate=gate,
                            one_token=ctx.decode_only)
+        if window_updating is not None:
+            window_updating[0].wait_stream(window_updating[1])
         if gate is not None:
             return y
         gated = ws.alloc((T, i_dim), proj.dtype)

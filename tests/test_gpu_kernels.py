@@ -467,6 +467,58 @@ def test_flash_decode_attention_from_projections(Hq, Hkv, Dh, page, tma, monkeyp
     assert ("pmm_flash_decode_attention" in calls) == (not by_copy_engine)
 
 
+@pytest.mark.parametrize("n_splits", [1, 5, 40])
+def test_decode_attention_over_a_long_context(n_splits):
+    """One decoded token over 33,100 cached positions in pages scattered over the pool: one key
+    range (more block-table entries than the kernel keeps in shared memory), a cluster of five, and
+    forty ranges (too many for a cluster: merged through global memory and the counter); a planted
+    far key that takes the whole softmax, then random keys."""
+    ops = K()
+    bf = torch.bfloat16
+    g = torch.Generator().manual_seed(n_splits)
+    Hq, Hkv, Dh, page, ctx = 8, 2, 64, 64, 33100
+    G, kvd, qd = Hq // Hkv, Hkv * Dh, Hq * Dh
+    n_blocks = (ctx + page) // page + 1
+    pool = (torch.randn(n_blocks + 3, 2, page, kvd, generator=g) * 0.5).to(bf).to(DEV)
+    table = torch.randperm(n_blocks + 3, generator=g)[:n_blocks].int()
+    bt = table.view(1, -1).contiguous().to(DEV)
+    pos = torch.tensor([ctx - 1], dtype=torch.int32, device=DEV)
+    for planted in (True, False):
+        proj = (torch.randn(1, qd + 2 * kvd, generator=g) * 0.5).to(bf).to(DEV)
+        if planted:  # key 7 of the context equals 16 x the first query head's query: that score stands out
+            pg, off = int(table[7 // page]), 7 % page
+            pool[pg, 0, off, :Dh] = (proj[0, :Dh].float() * 16).to(bf)
+        out = torch.empty(1, qd, dtype=bf, device=DEV)
+        split_len = ((ctx + n_splits - 1) // n_splits + 63) // 64 * 64 if n_splits > 1 else 0
+        ns = (ctx + split_len - 1) // split_len if n_splits > 1 else 1
+        scratch = torch.empty(ops.attention_scratch_floats(1, Hq, Dh, ns), device=DEV) if ns > 1 else None
+        counter = torch.zeros(Hkv, dtype=torch.int32, device=DEV)
+        before = pool.clone()
+        ops.flash_decode_attention(proj[:, :qd], proj[:, qd:qd + kvd], proj[:, qd + kvd:], 1.0, 1.0, 1.0, None, pool, bt, pos, out,
+                                   Hq, Hkv, Dh, Dh ** -0.5, n_splits=ns, split_len=split_len, scratch=scratch,
+                                   split_counter=counter)
+        torch.cuda.synchronize()
+        assert ops.tc_gemm_status(DEV) == 0 and int(counter.abs().sum()) == 0
+        # the new token's key and value went into its page, nothing else changed
+        pg, off = int(table[(ctx - 1) // page]), (ctx - 1) % page
+        assert torch.equal(pool[pg, 0, off], proj[0, qd:qd + kvd]) and torch.equal(pool[pg, 1, off], proj[0, qd + kvd:])
+        before[pg, :, off] = pool[pg, :, off]
+        assert torch.equal(before, pool)
+        # plain attention of the one token over the gathered context
+        idx = table[: (ctx + page - 1) // page].long()
+        kv = pool[idx.to(DEV)].double().cpu()                                    # [blocks, 2, page, kvd]
+        keys = kv[:, 0].reshape(-1, Hkv, Dh)[:ctx]
+        vals = kv[:, 1].reshape(-1, Hkv, Dh)[:ctx]
+        q = proj[0, :qd].double().cpu().view(Hq, Dh)
+        ref = torch.empty(Hq, Dh, dtype=torch.float64)
+        for h in range(Hq):
+            sc = (keys[:, h // G] @ q[h]) * Dh ** -0.5
+            ref[h] = torch.softmax(sc, 0) @ vals[:, h // G]
+        close(out.view(Hq, Dh), ref, bf, what=f"long-context decode attention, {ns} ranges, planted={planted}")
+        if planted:
+            assert float((out.view(Hq, Dh)[0].double().cpu() - vals[7, 0]).abs().max()) < 0.02
+
+
 @pytest.mark.parametrize("Hq,Hkv,page,Dh", [(8, 2, 64, 64), (4, 4, 128, 64), (16, 1, 64, 64), (16, 2, 64, 64),
                                             (8, 2, 64, 128), (4, 1, 128, 128), (2, 2, 64, 128), (6, 2, 64, 128),
                                             (12, 2, 64, 128), (3, 1, 64, 64)])

@@ -309,9 +309,12 @@ def mixed_workload(args, cfg, full_layers, nums, peaks, model_dir, checked) -> i
             runner.step([StepEntry(r, [rng.randrange(vocab) for _ in range(c)], [])])
         serial = [0]
 
+        # every prompt's token ids exist on the host before the timed regions, as a request's do
+        prompt_ids = [[rng.randrange(vocab) for _ in range(prompt_total)] for _ in range(2 * K_steps + W + n_pf + 4)]
+
         def new_prompt():
             serial[0] += 1
-            return [("pf", serial[0]), [rng.randrange(vocab) for _ in range(prompt_total)], 0]
+            return [("pf", serial[0]), prompt_ids[serial[0] % len(prompt_ids)], 0]
 
         prompts = []
         for j in range(n_pf):  # prompt j starts j portions deep

@@ -104,6 +104,7 @@ class ModelRunner:
         self._sampler = None
         self._step_graphs: "collections.OrderedDict" = collections.OrderedDict()
         self._small_step_graphs: "collections.OrderedDict" = collections.OrderedDict()
+        self._step_kernels_replayed = 0  # kernels inside the step graphs replayed so far
 
     def enable_graphs(self, max_seq_len: int, buckets=None) -> None:
         """Serve decode-only steps from CUDA graphs (captured per batch-size bucket on first use).
@@ -161,10 +162,13 @@ class ModelRunner:
         """Own kernels launched since ``launch_count_before`` (a value of kernels.ops.launch_count),
         graph replays counted by the kernels they hold."""
         n = K.launch_count - launch_count_before
-        return n + (self.graphs.kernels_replayed - getattr(self, "_replayed_mark", 0) if self.graphs else 0)
+        return n + self._kernels_replayed() - getattr(self, "_replayed_mark", 0)
+
+    def _kernels_replayed(self) -> int:
+        return self._step_kernels_replayed + (self.graphs.kernels_replayed if self.graphs else 0)
 
     def mark_launches(self) -> int:
-        self._replayed_mark = self.graphs.kernels_replayed if self.graphs else 0
+        self._replayed_mark = self._kernels_replayed()
         return K.launch_count
 
     def check_kernels(self, wait: bool = False) -> None:
@@ -198,6 +202,7 @@ class ModelRunner:
         if not entries:
             raise ValueError("a step needs at least one entry")
         seen = set()
+        token_arrays: List[np.ndarray] = []
         vocab = self.model.vocab_size
         for e in entries:
             if e.req in seen:
@@ -208,6 +213,7 @@ class ModelRunner:
             toks = np.asarray(e.tokens)
             if toks.dtype.kind not in "iu" or int(toks.min()) < 0 or int(toks.max()) >= vocab:
                 raise ValueError("token id out of range")
+            token_arrays.append(toks)
             for w in e.want:
                 if not 0 <= int(w) < len(e.tokens):
                     raise ValueError(f"request {e.req!r}: wanted place {w} is outside its tokens")
@@ -257,7 +263,7 @@ class ModelRunner:
             buf[o_cu] = 0
             for s, e in enumerate(entries):
                 n = new_lens[s]
-                buf[o_tok + t0:o_tok + t0 + n] = np.asarray(e.tokens, dtype=np.int32)
+                buf[o_tok + t0:o_tok + t0 + n] = token_arrays[s]
                 buf[o_pos + t0:o_pos + t0 + n] = np.arange(past[s], past[s] + n, dtype=np.int32)
                 buf[o_seq + t0:o_seq + t0 + n] = s
                 buf[o_cu + s + 1] = t0 + n
@@ -294,6 +300,7 @@ class ModelRunner:
             shapes.move_to_end(graph_key)
             self._staging.upload(total, fill, dev=entry["meta"])
             entry["graph"].replay()
+            self._step_kernels_replayed += entry["kernels"]
             logits = entry["logits"]
         else:
             if graph_key is not None:

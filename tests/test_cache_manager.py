@@ -85,7 +85,32 @@ def test_slots_run_out_and_are_zeroed_on_admit():
     c.release("a")
     assert c.admit("c") == s
     assert all(float(t[s].abs().sum()) == 0.0 for t in c._fixed.values())
+    other = c.slot("b")
+    assert all(float(t[other].abs().sum()) == 0.0 for t in c._fixed.values())
     c.check()
+
+
+def test_fixed_states_of_one_kind_share_storage_and_stay_contiguous():
+    """States of the same shape and dtype lie in one tensor [member, slot, *shape] (a request's slot
+    is cleared with one fill per kind); each layer still sees a contiguous [slot, *shape] of its
+    own, and clearing one request's slot leaves the other slots of every layer alone."""
+    c = make(num_slots=3)
+    assert len(c._fixed_stores) == 2  # (2, 3) and (3, 5), three layers each
+    assert sorted(tuple(st.shape) for st in c._fixed_stores) == [(3, 4, 2, 3), (3, 4, 3, 5)]
+    ptrs = set()
+    for (layer, name), t in c._fixed.items():
+        assert t.is_contiguous() and t.shape[0] == 4
+        ptrs.add(t.data_ptr())
+    assert len(ptrs) == 6
+    a, b = c.admit("a"), c.admit("b")
+    for k, t in enumerate(c._fixed.values()):
+        t[a].fill_(1.0 + k)
+        t[b].fill_(-1.0 - k)
+    c.release("a")
+    assert c.admit("again") == a
+    for k, t in enumerate(c._fixed.values()):
+        assert float(t[a].abs().sum()) == 0.0
+        assert bool((t[b] == -1.0 - k).all())
 
 
 def test_window_gives_pages_back_as_it_passes():

@@ -31,7 +31,7 @@ class Workspace:
         self._chunk = 0
         self._offset = 0
         self._frozen = False
-        self._views = {}  # (chunk index, offset, shape, dtype) -> tensor: the same requests recur layer after layer
+        self._views = {}  # (chunk index, offset, shape, dtype) -> (tensor, bytes taken)
         self.high_water = 0
         if initial_bytes > 0:
             self._chunks.append(torch.empty(int(initial_bytes), dtype=torch.uint8, device=self.device))
@@ -66,6 +66,16 @@ class Workspace:
         to `kernels.ops.padded_rows`, so that a library product over it can be issued with a row
         count that recurs from step to step."""
         shape = tuple(shape)
+        hit = self._views.get((self._chunk, self._offset, shape, dtype))
+        if hit is not None:  # the same requests recur layer after layer and step after step
+            view, size = hit
+            self._offset += size
+            if self._chunk == 0:
+                if self._offset > self.high_water:
+                    self.high_water = self._offset
+            else:
+                self.high_water = max(self.high_water, self._used())
+            return view
         numel = 1
         for s in shape:
             numel *= s
@@ -80,13 +90,12 @@ class Workspace:
                 chunk = self._chunks[self._chunk]
                 off = self._offset
                 if off + size <= chunk.numel():
-                    key = (self._chunk, off, shape, dtype)
-                    view = self._views.get(key)
-                    if view is None:
-                        view = chunk[off:off + nbytes].view(dtype).view(shape)
-                        if rows > shape[0]:
-                            view._scratch_rows = rows  # read by kernels.ops._mm; the storage is the whole chunk
-                        self._views[key] = view
+                    view = chunk[off:off + nbytes].view(dtype).view(shape)
+                    if rows > shape[0]:
+                        # read by kernels.ops._mm: the matrix with its scratch rows (the storage is the chunk)
+                        view._scratch_rows = rows
+                        view._with_scratch_rows = chunk[off:off + reserve].view(dtype).view((rows, shape[1]))
+                    self._views[(self._chunk, off, shape, dtype)] = (view, size)
                     self._offset = off + size
                     used = self._used()
                     if used > self.high_water:

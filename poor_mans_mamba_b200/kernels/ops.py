@@ -149,11 +149,6 @@ def _ptr(t: Optional[Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
 
-def _need(cond: bool, msg: str) -> None:
-    if not cond:
-        raise KernelError(msg)
-
-
 
 # ----------------------------------------------------------------------------- status of bounded waits
 class _StatusWatch:
@@ -231,18 +226,20 @@ def _cuda(*tensors: Optional[Tensor]) -> None:
 
 def _rows_view(t: Tensor, what: str) -> int:
     """Row stride (elements) of a 2-D view whose rows are contiguous."""
-    _need(t.dim() == 2 and t.stride(1) == 1, f"{what}: need a 2-D view with unit column stride")
+    if not (t.dim() == 2 and t.stride(1) == 1):
+        raise KernelError(f"{what}: need a 2-D view with unit column stride")
     return t.stride(0)
 
 
 def _f32vec(t: Optional[Tensor], n: int, what: str) -> None:
     if t is not None:
-        _need(t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n,
-              f"{what}: need a contiguous float32 vector of {n}")
+        if not (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n):
+            raise KernelError(f"{what}: need a contiguous float32 vector of {n}")
 
 
 def _i32(t: Tensor, what: str) -> None:
-    _need(t.dtype == torch.int32 and t.is_contiguous(), f"{what}: need contiguous int32")
+    if not (t.dtype == torch.int32 and t.is_contiguous()):
+        raise KernelError(f"{what}: need contiguous int32")
 
 
 # ----------------------------------------------------------------------------- library GEMM
@@ -273,18 +270,23 @@ def _mm(x: Tensor, weight: Tensor, out: Tensor, **kw) -> None:
     arena (which marks it with the rows it keeps behind it) and x's storage reaches as far.  What
     the extra rows of x hold does not matter, rows being independent, and nothing reads the extra
     rows of out."""
-    rows = padded_rows(x.shape[0])
-    if rows != x.shape[0] and getattr(out, "_scratch_rows", 0) >= rows:
-        xp, op = _with_rows(x, rows), _with_rows(out, rows)
-        if xp is not None and op is not None:
-            x, out = xp, op
+    n = x.shape[0]
+    if n > 64:
+        rows = padded_rows(n)
+        if rows != n and getattr(out, "_scratch_rows", 0) >= rows:
+            # matrices of the arena carry the padded view with them; a slice of one is widened here
+            xp = x._with_scratch_rows if getattr(x, "_scratch_rows", 0) == rows else _with_rows(x, rows)
+            op = out._with_scratch_rows if out._scratch_rows == rows else _with_rows(out, rows)
+            if xp is not None and op is not None:
+                x, out = xp, op
     torch.mm(x, weight.t(), out=out, **kw)
 
 
 def linear(x: Tensor, weight: Tensor, out: Tensor) -> Tensor:
     """out[T, N] = x[T, K] @ weight[N, K]^T through the GEMM library."""
     _cuda(x, weight, out)
-    _need(x.dtype == weight.dtype, f"linear: activation {x.dtype} vs weight {weight.dtype}")
+    if not (x.dtype == weight.dtype):
+        raise KernelError(f"linear: activation {x.dtype} vs weight {weight.dtype}")
     if x.dtype == torch.float32:
         prev = torch.backends.cuda.matmul.allow_tf32
         torch.backends.cuda.matmul.allow_tf32 = False
@@ -323,7 +325,8 @@ def linear_f32_out(x: Tensor, weight: Tensor, out: Tensor, scratch_low: Optional
         if scale != 1.0:
             scale_f32_(out, scale)
     else:
-        _need(scratch_low is not None, "linear_f32_out: needs a low-precision scratch buffer")
+        if not (scratch_low is not None):
+            raise KernelError("linear_f32_out: needs a low-precision scratch buffer")
         torch.mm(x, weight.t(), out=scratch_low)
         cast_scale(out, scratch_low, scale)
 
@@ -332,10 +335,13 @@ def linear_f32_out(x: Tensor, weight: Tensor, out: Tensor, scratch_low: Optional
 def embed(out: Tensor, table: Tensor, tokens: Tensor, mult: float) -> None:
     _cuda(out, table, tokens)
     T, D = out.shape
-    _need(out.dtype == torch.float32 and out.is_contiguous(), "embed: out must be contiguous float32")
-    _need(table.dim() == 2 and table.shape[1] == D and table.is_contiguous(), "embed: table must be [V, D]")
+    if not (out.dtype == torch.float32 and out.is_contiguous()):
+        raise KernelError("embed: out must be contiguous float32")
+    if not (table.dim() == 2 and table.shape[1] == D and table.is_contiguous()):
+        raise KernelError("embed: table must be [V, D]")
     _i32(tokens, "embed: tokens")
-    _need(tokens.numel() == T, "embed: one token per output row")
+    if not (tokens.numel() == T):
+        raise KernelError("embed: one token per output row")
     _call("pmm_embed", out.data_ptr(), table.data_ptr(), tokens.data_ptr(), float(mult), T, D,
           table.shape[0], _dt(table), _stream())
 
@@ -345,29 +351,36 @@ def add_rmsnorm(h: Tensor, branches: Sequence[Tuple[Tensor, float]], weight: Opt
     """h <- (h + s0*b0) + s1*b1 (rows is None), then out = rmsnorm(h) * weight.
     With ``rows`` (int32 row indices) h is left as it is and out[r] comes from row rows[r]."""
     _cuda(h, weight, out, rows)
-    _need(h.dtype == torch.float32 and h.dim() == 2 and h.is_contiguous(),
-          "add_rmsnorm: the residual stream must be contiguous float32 [T, D]")
+    if not (h.dtype == torch.float32 and h.dim() == 2 and h.is_contiguous()):
+        raise KernelError("add_rmsnorm: the residual stream must be contiguous float32 [T, D]")
     T, D = h.shape
-    _need(len(branches) <= 2, "add_rmsnorm: at most two branches")
-    _need(D * 4 <= 200 * 1024, f"add_rmsnorm: width {D} exceeds one block's shared memory")
+    if not (len(branches) <= 2):
+        raise KernelError("add_rmsnorm: at most two branches")
+    if not (D * 4 <= 200 * 1024):
+        raise KernelError(f"add_rmsnorm: width {D} exceeds one block's shared memory")
     ptrs: List[Optional[int]] = [None, None]
     scales = [0.0, 0.0]
     dtype = None
     for i, (b, s) in enumerate(branches):
         _cuda(b)
-        _need(b.shape == h.shape and b.is_contiguous(), "add_rmsnorm: branch must be contiguous [T, D]")
+        if not (b.shape == h.shape and b.is_contiguous()):
+            raise KernelError("add_rmsnorm: branch must be contiguous [T, D]")
         ptrs[i], scales[i] = b.data_ptr(), float(s)
         dtype = _dt(b) if dtype is None else dtype
-        _need(_dt(b) == dtype, "add_rmsnorm: branches of different storage types")
+        if not (_dt(b) == dtype):
+            raise KernelError("add_rmsnorm: branches of different storage types")
     R = T
     if rows is not None:
         _i32(rows, "add_rmsnorm: rows")
         R = rows.numel()
     if out is not None:
-        _need(weight is not None, "add_rmsnorm: a norm needs its weight")
+        if not (weight is not None):
+            raise KernelError("add_rmsnorm: a norm needs its weight")
         _f32vec(weight, D, "add_rmsnorm: weight")
-        _need(out.shape == (R, D) and out.is_contiguous(), "add_rmsnorm: out must be contiguous [rows, D]")
-        _need(dtype is None or _dt(out) == dtype, "add_rmsnorm: out and branches differ in storage type")
+        if not (out.shape == (R, D) and out.is_contiguous()):
+            raise KernelError("add_rmsnorm: out must be contiguous [rows, D]")
+        if not (dtype is None or _dt(out) == dtype):
+            raise KernelError("add_rmsnorm: out and branches differ in storage type")
         dtype = _dt(out)
     if dtype is None:
         return  # nothing to add and nothing to write
@@ -377,14 +390,16 @@ def add_rmsnorm(h: Tensor, branches: Sequence[Tuple[Tensor, float]], weight: Opt
 
 def scale_f32_(x: Tensor, s: float) -> None:
     _cuda(x)
-    _need(x.dtype == torch.float32 and x.is_contiguous(), "scale_f32_: contiguous float32 only")
+    if not (x.dtype == torch.float32 and x.is_contiguous()):
+        raise KernelError("scale_f32_: contiguous float32 only")
     _call("pmm_scale_f32", x.data_ptr(), float(s), x.numel(), _stream())
 
 
 def cast_scale(out: Tensor, src: Tensor, s: float) -> None:
     _cuda(out, src)
-    _need(out.dtype == torch.float32 and out.is_contiguous() and src.is_contiguous()
-          and out.numel() == src.numel(), "cast_scale: contiguous tensors of equal size, float32 out")
+    if not (out.dtype == torch.float32 and out.is_contiguous() and src.is_contiguous()
+            and out.numel() == src.numel()):
+        raise KernelError("cast_scale: contiguous tensors of equal size, float32 out")
     _call("pmm_cast_scale", out.data_ptr(), src.data_ptr(), float(s), src.numel(), _dt(src), _stream())
 
 
@@ -392,8 +407,9 @@ def _conv_common(x: Tensor, pre_scale: Tensor, pre_bias: Optional[Tensor], windo
     C = x.shape[1]
     _f32vec(pre_scale, C, "conv1d: pre_scale")
     _f32vec(pre_bias, C, "conv1d: pre_bias")
-    _need(window.dtype == torch.float32 and window.is_contiguous() and window.dim() == 3
-          and tuple(window.shape[1:]) == (K - 1, C), "conv1d: window must be float32 [slots, K-1, C]")
+    if not (window.dtype == torch.float32 and window.is_contiguous() and window.dim() == 3
+            and tuple(window.shape[1:]) == (K - 1, C)):
+        raise KernelError("conv1d: window must be float32 [slots, K-1, C]")
     return C
 
 
@@ -406,14 +422,17 @@ def conv1d_fwd(x: Tensor, pre_scale: Tensor, pre_bias: Optional[Tensor], weight:
     _cuda(x, pre_scale, pre_bias, weight, bias, window, seq_of, cu, slots, out, weight_t)
     ld = _rows_view(x, "conv1d: x")
     T = x.shape[0]
-    _need(weight.dtype == torch.float32 and weight.dim() == 2 and weight.is_contiguous()
-          and weight.shape[0] == x.shape[1], "conv1d: weight must be contiguous float32 [C, K]")
+    if not (weight.dtype == torch.float32 and weight.dim() == 2 and weight.is_contiguous()
+            and weight.shape[0] == x.shape[1]):
+        raise KernelError("conv1d: weight must be contiguous float32 [C, K]")
     K = weight.shape[1]
     C = _conv_common(x, pre_scale, pre_bias, window, K)
     _f32vec(bias, C, "conv1d: bias")
-    _need(out.shape == (T, C) and out.is_contiguous() and out.dtype == x.dtype, "conv1d: out must be [T, C]")
-    _need(weight_t is None or (weight_t.dtype == torch.float32 and weight_t.is_contiguous()
-                               and weight_t.shape == (K, C)), "conv1d: weight_t must be contiguous float32 [K, C]")
+    if not (out.shape == (T, C) and out.is_contiguous() and out.dtype == x.dtype):
+        raise KernelError("conv1d: out must be [T, C]")
+    if not (weight_t is None or (weight_t.dtype == torch.float32 and weight_t.is_contiguous()
+            and weight_t.shape == (K, C))):
+        raise KernelError("conv1d: weight_t must be contiguous float32 [K, C]")
     _call("pmm_conv1d_fwd", x.data_ptr(), ld, pre_scale.data_ptr(), _ptr(pre_bias), weight.data_ptr(),
           _ptr(weight_t), _ptr(bias), window.data_ptr(), seq_of.data_ptr(), cu.data_ptr(), slots.data_ptr(),
           out.data_ptr(), T, C, K, _dt(x), _stream())
@@ -437,10 +456,11 @@ def conv1d_decode(x: Tensor, pre_scale: Tensor, pre_bias: Optional[Tensor], weig
     n_seq = x.shape[0]
     K = weight.shape[1]
     C = _conv_common(x, pre_scale, pre_bias, window, K)
-    _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.shape[0] == C,
-          "conv1d: weight must be contiguous float32 [C, K]")
+    if not (weight.dtype == torch.float32 and weight.is_contiguous() and weight.shape[0] == C):
+        raise KernelError("conv1d: weight must be contiguous float32 [C, K]")
     _f32vec(bias, C, "conv1d: bias")
-    _need(out.shape == (n_seq, C) and out.is_contiguous() and out.dtype == x.dtype, "conv1d: out must be [T, C]")
+    if not (out.shape == (n_seq, C) and out.is_contiguous() and out.dtype == x.dtype):
+        raise KernelError("conv1d: out must be [T, C]")
     _call("pmm_conv1d_decode", x.data_ptr(), ld, pre_scale.data_ptr(), _ptr(pre_bias),
           weight.data_ptr(), _ptr(bias), window.data_ptr(), slots.data_ptr(), out.data_ptr(), n_seq, C,
           K, _dt(x), _stream())
@@ -453,7 +473,8 @@ def _gate_args(gate, out: Tensor, what: str):
     z, z_scale, z_bias = gate
     _cuda(z, z_bias)
     ld_z = _rows_view(z, f"{what}: z")
-    _need(z.shape == out.shape and z.dtype == out.dtype, f"{what}: z must match the output")
+    if not (z.shape == out.shape and z.dtype == out.dtype):
+        raise KernelError(f"{what}: z must match the output")
     _f32vec(z_bias, out.shape[1], f"{what}: z_bias")
     return z.data_ptr(), ld_z, float(z_scale), _ptr(z_bias)
 
@@ -467,18 +488,21 @@ def ssm_scan_seq(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Tensor,
     ``only_single``: only the sequences that bring exactly one token are walked (the lone tokens of
     a mixed step, whose longer portions the chunked scan takes); the others are left alone."""
     _cuda(xbc, dt_raw, dt_shift, a_log, d_skip, state, cu, slots, out)
-    _need(state.dtype == torch.float32 and state.dim() == 4 and state.is_contiguous(),
-          "ssm_scan: state must be contiguous float32 [slots, H, P, N]")
+    if not (state.dtype == torch.float32 and state.dim() == 4 and state.is_contiguous()):
+        raise KernelError("ssm_scan: state must be contiguous float32 [slots, H, P, N]")
     _, H, P, N = state.shape
-    _need(N <= 256, f"ssm_scan: d_state {N} above 256 is not supported")
+    if not (N <= 256):
+        raise KernelError(f"ssm_scan: d_state {N} above 256 is not supported")
     ld_x = _rows_view(xbc, "ssm_scan: xbc")
-    _need(xbc.shape[1] == H * P + 2 * n_groups * N, "ssm_scan: xbc must hold [x | B | C]")
+    if not (xbc.shape[1] == H * P + 2 * n_groups * N):
+        raise KernelError("ssm_scan: xbc must hold [x | B | C]")
     ld_dt = _rows_view(dt_raw, "ssm_scan: dt")
-    _need(dt_raw.shape[1] == H and dt_raw.dtype == xbc.dtype, "ssm_scan: dt must be [T, H]")
+    if not (dt_raw.shape[1] == H and dt_raw.dtype == xbc.dtype):
+        raise KernelError("ssm_scan: dt must be [T, H]")
     for v, nm in ((dt_shift, "dt_shift"), (a_log, "A_log"), (d_skip, "D")):
         _f32vec(v, H, f"ssm_scan: {nm}")
-    _need(out.shape == (xbc.shape[0], H * P) and out.is_contiguous() and out.dtype == xbc.dtype,
-          "ssm_scan: out must be [T, H*P]")
+    if not (out.shape == (xbc.shape[0], H * P) and out.is_contiguous() and out.dtype == xbc.dtype):
+        raise KernelError("ssm_scan: out must be [T, H*P]")
     zp, ld_z, zs, zb = _gate_args(gate, out, "ssm_scan")
     _call("pmm_ssm_scan_seq", xbc.data_ptr(), ld_x, dt_raw.data_ptr(), ld_dt, float(dt_scale),
           dt_shift.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), cu.data_ptr(),
@@ -517,30 +541,34 @@ def ssm_scan_chunked(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Ten
     (bfloat16 activations); same contract as ssm_scan_seq.  ``scratch``: float32, at least
     ssd_scratch_floats(...) elements."""
     _cuda(xbc, dt_raw, dt_shift, a_log, d_skip, state, cu, slots, out, scratch)
-    _need(state.dtype == torch.float32 and state.dim() == 4 and state.is_contiguous(),
-          "ssm_scan: state must be contiguous float32 [slots, H, P, N]")
+    if not (state.dtype == torch.float32 and state.dim() == 4 and state.is_contiguous()):
+        raise KernelError("ssm_scan: state must be contiguous float32 [slots, H, P, N]")
     _, H, P, N = state.shape
-    _need(xbc.dtype == torch.bfloat16 and ssd_supported(P, N),
-          f"ssm_scan_chunked: needs bfloat16 and a compiled (d_head, d_state) pair, got {xbc.dtype} ({P}, {N})")
+    if not (xbc.dtype == torch.bfloat16 and ssd_supported(P, N)):
+        raise KernelError(f"ssm_scan_chunked: needs bfloat16 and a compiled (d_head, d_state) pair, got {xbc.dtype} "
+                          f"({P}, {N})")
     ld_x = _rows_view(xbc, "ssm_scan: xbc")
-    _need(xbc.shape[1] == H * P + 2 * n_groups * N and ld_x % 8 == 0 and xbc.data_ptr() % 16 == 0,
-          "ssm_scan_chunked: xbc must hold [x | B | C] in rows that start on 16-byte boundaries")
+    if not (xbc.shape[1] == H * P + 2 * n_groups * N and ld_x % 8 == 0 and xbc.data_ptr() % 16 == 0):
+        raise KernelError("ssm_scan_chunked: xbc must hold [x | B | C] in rows that start on 16-byte boundaries")
     ld_dt = _rows_view(dt_raw, "ssm_scan: dt")
-    _need(dt_raw.shape[1] == H and dt_raw.dtype == xbc.dtype, "ssm_scan: dt must be [T, H]")
+    if not (dt_raw.shape[1] == H and dt_raw.dtype == xbc.dtype):
+        raise KernelError("ssm_scan: dt must be [T, H]")
     for v, nm in ((dt_shift, "dt_shift"), (a_log, "A_log"), (d_skip, "D")):
         _f32vec(v, H, f"ssm_scan: {nm}")
-    _need(out.shape == (xbc.shape[0], H * P) and out.is_contiguous() and out.dtype == xbc.dtype,
-          "ssm_scan: out must be [T, H*P]")
+    if not (out.shape == (xbc.shape[0], H * P) and out.is_contiguous() and out.dtype == xbc.dtype):
+        raise KernelError("ssm_scan: out must be [T, H*P]")
     n_chunks = ssd_chunks(new_lens)
     need = ssd_scratch_floats(new_lens, H, P, N, n_groups)
-    _need(scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= need
-          and scratch.data_ptr() % 16 == 0, f"ssm_scan_chunked: needs {need} floats of 16-byte aligned scratch")
+    if not (scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= need
+            and scratch.data_ptr() % 16 == 0):
+        raise KernelError(f"ssm_scan_chunked: needs {need} floats of 16-byte aligned scratch")
     chunk_state = scratch.data_ptr()
     chunk_decay = chunk_state + 4 * n_chunks * H * P * N
     start_state = chunk_decay + 4 * ((n_chunks * H + 3) // 4 * 4)
     chunk_cb = start_state + 4 * (((n_chunks * H * P * N + 1) // 2 + 3) // 4 * 4)
     zp, ld_z, zs, zb = _gate_args(gate, out, "ssm_scan_chunked")
-    _need(zp is None or (ld_z % 2 == 0 and zp % 4 == 0), "ssm_scan_chunked: z rows must be 4-byte aligned")
+    if not (zp is None or (ld_z % 2 == 0 and zp % 4 == 0)):
+        raise KernelError("ssm_scan_chunked: z rows must be 4-byte aligned")
     _call("pmm_ssd_chunked", xbc.data_ptr(), ld_x, dt_raw.data_ptr(), ld_dt, float(dt_scale),
           dt_shift.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), cu.data_ptr(),
           slots.data_ptr(), out.data_ptr(), chunk_state, chunk_decay, start_state, chunk_cb, len(new_lens), n_chunks,
@@ -573,25 +601,28 @@ def ssm_scan_tc(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Tensor, 
     ssd_tc_scratch_floats(...) elements.  ``skip_single``: sequences that bring exactly one token are
     left alone (their rows of ``out`` and their states): ssm_scan_seq(only_single=True) takes them."""
     _cuda(xbc, dt_raw, dt_shift, a_log, d_skip, state, cu, slots, out, scratch)
-    _need(state.dtype == torch.float32 and state.dim() == 4 and state.is_contiguous(),
-          "ssm_scan: state must be contiguous float32 [slots, H, P, N]")
+    if not (state.dtype == torch.float32 and state.dim() == 4 and state.is_contiguous()):
+        raise KernelError("ssm_scan: state must be contiguous float32 [slots, H, P, N]")
     _, H, P, N = state.shape
-    _need(xbc.dtype == torch.bfloat16 and ssd_tc_supported(P, N),
-          f"ssm_scan_tc: needs bfloat16, a head size that is a multiple of 16 up to 128 and a state size that is a "
-          f"multiple of 16 up to 256, got {xbc.dtype} ({P}, {N})")
+    if not (xbc.dtype == torch.bfloat16 and ssd_tc_supported(P, N)):
+        raise KernelError(f"ssm_scan_tc: needs bfloat16, a head size that is a multiple of 16 up to 128 and a state size that is a "
+                          f"multiple of 16 up to 256, got {xbc.dtype} ({P}, {N})")
     ld_x = _rows_view(xbc, "ssm_scan: xbc")
-    _need(xbc.shape[1] == H * P + 2 * n_groups * N and ld_x % 8 == 0 and xbc.data_ptr() % 16 == 0,
-          "ssm_scan_tc: xbc must hold [x | B | C] in rows that start on 16-byte boundaries")
+    if not (xbc.shape[1] == H * P + 2 * n_groups * N and ld_x % 8 == 0 and xbc.data_ptr() % 16 == 0):
+        raise KernelError("ssm_scan_tc: xbc must hold [x | B | C] in rows that start on 16-byte boundaries")
     ld_dt = _rows_view(dt_raw, "ssm_scan: dt")
-    _need(dt_raw.shape[1] == H and dt_raw.dtype == xbc.dtype, "ssm_scan: dt must be [T, H]")
+    if not (dt_raw.shape[1] == H and dt_raw.dtype == xbc.dtype):
+        raise KernelError("ssm_scan: dt must be [T, H]")
     for v, nm in ((dt_shift, "dt_shift"), (a_log, "A_log"), (d_skip, "D")):
         _f32vec(v, H, f"ssm_scan: {nm}")
-    _need(out.shape == (xbc.shape[0], H * P) and out.is_contiguous() and out.dtype == xbc.dtype
-          and out.data_ptr() % 16 == 0, "ssm_scan: out must be [T, H*P] on a 16-byte boundary")
+    if not (out.shape == (xbc.shape[0], H * P) and out.is_contiguous() and out.dtype == xbc.dtype
+            and out.data_ptr() % 16 == 0):
+        raise KernelError("ssm_scan: out must be [T, H*P] on a 16-byte boundary")
     n_chunks = sum((n + SSD_TC_CHUNK - 1) // SSD_TC_CHUNK for n in new_lens)
     need = ssd_tc_scratch_floats(new_lens, H, P, N)
-    _need(scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= need
-          and scratch.data_ptr() % 16 == 0, f"ssm_scan_tc: needs {need} floats of 16-byte aligned scratch")
+    if not (scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= need
+            and scratch.data_ptr() % 16 == 0):
+        raise KernelError(f"ssm_scan_tc: needs {need} floats of 16-byte aligned scratch")
     chunk_state = scratch.data_ptr()
     chunk_decay = chunk_state + 4 * n_chunks * H * P * N
     chunk_dt = chunk_decay + 4 * ((n_chunks * H + 3) // 4 * 4)
@@ -610,22 +641,24 @@ def gated_norm(y: Tensor, z_raw: Tensor, z_scale: float, z_bias: Optional[Tensor
     """out = y*silu(z), optionally RMS-normalised per group of channels (before or after the gate)."""
     _cuda(y, z_raw, z_bias, weight, out)
     T, I = y.shape
-    _need(y.is_contiguous() and out.is_contiguous() and out.shape == y.shape and out.dtype == y.dtype,
-          "gated_norm: y and out must be contiguous [T, I] of one type")
+    if not (y.is_contiguous() and out.is_contiguous() and out.shape == y.shape and out.dtype == y.dtype):
+        raise KernelError("gated_norm: y and out must be contiguous [T, I] of one type")
     ld_z = _rows_view(z_raw, "gated_norm: z")
-    _need(z_raw.shape == y.shape and z_raw.dtype == y.dtype, "gated_norm: z must match y")
+    if not (z_raw.shape == y.shape and z_raw.dtype == y.dtype):
+        raise KernelError("gated_norm: z must match y")
     _f32vec(z_bias, I, "gated_norm: z_bias")
     _f32vec(weight, I, "gated_norm: weight")
     groups = n_groups if weight is not None else 1
-    _need(I % groups == 0, "gated_norm: width must be a multiple of the group count")
+    if not (I % groups == 0):
+        raise KernelError("gated_norm: width must be a multiple of the group count")
     _call("pmm_gated_norm", y.data_ptr(), z_raw.data_ptr(), ld_z, float(z_scale), _ptr(z_bias),
           _ptr(weight), float(eps), int(bool(norm_before_gate)), out.data_ptr(), T, I, groups, _dt(y),
           _stream())
 
 
 def check_head_dim(head_dim: int) -> None:
-    _need(head_dim % 16 == 0 and 16 <= head_dim <= 256,
-          f"attention kernels take head sizes 16..256 in steps of 16, got {head_dim}")
+    if not (head_dim % 16 == 0 and 16 <= head_dim <= 256):
+        raise KernelError(f"attention kernels take head sizes 16..256 in steps of 16, got {head_dim}")
 
 
 def qkv_rope_store(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], q_scale: float, k_scale: float,
@@ -640,30 +673,35 @@ def qkv_rope_store(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], q_scale:
     check_head_dim(head_dim)
     T = q.shape[0]
     ldq = _rows_view(q, "qkv: q")
-    _need(q.shape[1] == n_q_heads * head_dim and q.dtype == q_out.dtype, "qkv: q width or type")
-    _need(q_out.is_contiguous() and q_out.shape == (T, n_q_heads * head_dim), "qkv: q_out must be [T, Hq*Dh]")
+    if not (q.shape[1] == n_q_heads * head_dim and q.dtype == q_out.dtype):
+        raise KernelError("qkv: q width or type")
+    if not (q_out.is_contiguous() and q_out.shape == (T, n_q_heads * head_dim)):
+        raise KernelError("qkv: q_out must be [T, Hq*Dh]")
     _f32vec(inv_freq, head_dim // 2, "qkv: inv_freq")
     _i32(positions, "qkv: positions")
     _i32(seq_of, "qkv: seq_of")
     page_size, max_blocks, ldk, ldv = 0, 0, 0, 0
     if k is None or v is None:
-        _need(k is None and v is None and n_kv_heads == 0, "qkv: queries only means no k, no v, no kv heads")
+        if not (k is None and v is None and n_kv_heads == 0):
+            raise KernelError("qkv: queries only means no k, no v, no kv heads")
         pool = block_table = k_out = v_out = None
     else:
         ldk, ldv = _rows_view(k, "qkv: k"), _rows_view(v, "qkv: v")
         kv_dim = n_kv_heads * head_dim
-        _need(k.shape[1] == kv_dim and v.shape[1] == kv_dim and q.dtype == k.dtype == v.dtype,
-              "qkv: slice widths do not match the head counts")
+        if not (k.shape[1] == kv_dim and v.shape[1] == kv_dim and q.dtype == k.dtype == v.dtype):
+            raise KernelError("qkv: slice widths do not match the head counts")
         if pool is not None:
-            _need(block_table is not None, "qkv: a pool needs a block table")
+            if not (block_table is not None):
+                raise KernelError("qkv: a pool needs a block table")
             _i32(block_table, "qkv: block_table")
-            _need(pool.dim() == 4 and pool.shape[1] == 2 and pool.shape[3] == kv_dim and pool.is_contiguous()
-                  and pool.dtype == q.dtype, "qkv: pool must be contiguous [pages, 2, page_size, Hkv*Dh]")
+            if not (pool.dim() == 4 and pool.shape[1] == 2 and pool.shape[3] == kv_dim and pool.is_contiguous()
+                    and pool.dtype == q.dtype):
+                raise KernelError("qkv: pool must be contiguous [pages, 2, page_size, Hkv*Dh]")
             page_size, max_blocks = pool.shape[2], block_table.shape[1]
         else:
-            _need(k_out is not None and v_out is not None and k_out.is_contiguous() and v_out.is_contiguous()
-                  and k_out.shape == (T, kv_dim) and v_out.shape == (T, kv_dim),
-                  "qkv: k_out/v_out must be [T, Hkv*Dh]")
+            if not (k_out is not None and v_out is not None and k_out.is_contiguous() and v_out.is_contiguous()
+                    and k_out.shape == (T, kv_dim) and v_out.shape == (T, kv_dim)):
+                raise KernelError("qkv: k_out/v_out must be [T, Hkv*Dh]")
     _call("pmm_qkv_rope_store", q.data_ptr(), ldq, _ptr(k), ldk, _ptr(v), ldv, float(q_scale),
           float(k_scale), float(v_scale), _ptr(inv_freq), positions.data_ptr(), seq_of.data_ptr(),
           _ptr(block_table), max_blocks, _ptr(pool), page_size, q_out.data_ptr(), _ptr(k_out),
@@ -675,10 +713,10 @@ def kv_store(k: Tensor, v: Tensor, positions: Tensor, seq_of: Tensor, block_tabl
     """Copies contiguous k/v rows [T, Hkv*Dh] into the pages of ``pool``."""
     _cuda(k, v, positions, seq_of, block_table, pool)
     T, kv_dim = k.shape
-    _need(k.is_contiguous() and v.is_contiguous() and v.shape == k.shape and k.dtype == v.dtype == pool.dtype,
-          "kv_store: k and v must be contiguous [T, Hkv*Dh] of the pool's type")
-    _need(pool.dim() == 4 and pool.shape[1] == 2 and pool.shape[3] == kv_dim and pool.is_contiguous(),
-          "kv_store: pool must be contiguous [pages, 2, page_size, Hkv*Dh]")
+    if not (k.is_contiguous() and v.is_contiguous() and v.shape == k.shape and k.dtype == v.dtype == pool.dtype):
+        raise KernelError("kv_store: k and v must be contiguous [T, Hkv*Dh] of the pool's type")
+    if not (pool.dim() == 4 and pool.shape[1] == 2 and pool.shape[3] == kv_dim and pool.is_contiguous()):
+        raise KernelError("kv_store: pool must be contiguous [pages, 2, page_size, Hkv*Dh]")
     _i32(block_table, "kv_store: block_table")
     _call("pmm_kv_store", k.data_ptr(), v.data_ptr(), positions.data_ptr(), seq_of.data_ptr(),
           block_table.data_ptr(), block_table.shape[1], pool.data_ptr(), pool.shape[2], T, kv_dim,
@@ -724,21 +762,25 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
     _cuda(q, pool, block_table, positions, seq_of, out, scratch, cu_seqlens)
     check_head_dim(head_dim)
     T = q.shape[0]
-    _need(q.is_contiguous() and out.is_contiguous() and q.shape == (T, n_q_heads * head_dim)
-          and out.shape == q.shape and q.dtype == out.dtype == pool.dtype,
-          "attention: q and out must be contiguous [T, Hq*Dh] of the pool's type")
-    _need(n_q_heads % n_kv_heads == 0, "attention: query heads must be a multiple of key/value heads")
-    _need(pool.dim() == 4 and pool.shape[1] == 2 and pool.shape[3] == n_kv_heads * head_dim
-          and pool.is_contiguous(), "attention: pool must be contiguous [pages, 2, page_size, Hkv*Dh]")
+    if not (q.is_contiguous() and out.is_contiguous() and q.shape == (T, n_q_heads * head_dim)
+            and out.shape == q.shape and q.dtype == out.dtype == pool.dtype):
+        raise KernelError("attention: q and out must be contiguous [T, Hq*Dh] of the pool's type")
+    if not (n_q_heads % n_kv_heads == 0):
+        raise KernelError("attention: query heads must be a multiple of key/value heads")
+    if not (pool.dim() == 4 and pool.shape[1] == 2 and pool.shape[3] == n_kv_heads * head_dim
+            and pool.is_contiguous()):
+        raise KernelError("attention: pool must be contiguous [pages, 2, page_size, Hkv*Dh]")
     _i32(block_table, "attention: block_table")
     _i32(positions, "attention: positions")
     _i32(seq_of, "attention: seq_of")
     part_o = part_ml = None
     if n_splits > 1:
         need = attention_scratch_floats(T, n_q_heads, head_dim, n_splits)
-        _need(scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous()
-              and scratch.numel() >= need, f"attention: split keys need {need} floats of scratch")
-        _need(split_len > 0 and split_len % 32 == 0, "attention: split_len must be a positive multiple of 32")
+        if not (scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous()
+                and scratch.numel() >= need):
+            raise KernelError(f"attention: split keys need {need} floats of scratch")
+        if not (split_len > 0 and split_len % 32 == 0):
+            raise KernelError("attention: split_len must be a positive multiple of 32")
         part_o = scratch.data_ptr()
         part_ml = part_o + 4 * T * n_q_heads * n_splits * head_dim
     flash = (use_tensor_cores and q.dtype == torch.bfloat16 and cu_seqlens is not None and new_lens is not None
@@ -748,9 +790,9 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
         group = n_q_heads // n_kv_heads
         if tile_rows is None:
             tile_rows = flash_tile_rows(n_q_heads, n_kv_heads, head_dim, new_lens)
-        _need(tile_rows in (16, 64, 128) and group <= tile_rows and (tile_rows < 128 or head_dim <= 64)
-              and (tile_rows > 16 or max(new_lens) * group <= 16),
-              f"attention: {tile_rows} rows per block do not fit this shape")
+        if not (tile_rows in (16, 64, 128) and group <= tile_rows and (tile_rows < 128 or head_dim <= 64)
+                and (tile_rows > 16 or max(new_lens) * group <= 16)):
+            raise KernelError(f"attention: {tile_rows} rows per block do not fit this shape")
         tokens_per_tile = tile_rows // group
         n_tiles = sum((n + tokens_per_tile - 1) // tokens_per_tile for n in new_lens)
         counter = None
@@ -794,30 +836,35 @@ def flash_decode_attention(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], 
     _cuda(q, k, v, inv_freq, pool, block_table, positions, out, scratch, split_counter)
     n_seq = q.shape[0]
     kv_dim = n_kv_heads * head_dim
-    _need(q.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
-          and flash_decode_supported(n_q_heads, n_kv_heads, head_dim), "decode attention: bfloat16 and a supported shape")
+    if not (q.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+            and flash_decode_supported(n_q_heads, n_kv_heads, head_dim)):
+        raise KernelError("decode attention: bfloat16 and a supported shape")
     ldq = _rows_view(q, "decode attention: q")
-    _need(q.shape[1] == n_q_heads * head_dim and out.is_contiguous() and out.shape == (n_seq, n_q_heads * head_dim),
-          "decode attention: q/out must be [n_seq, Hq*Dh]")
+    if not (q.shape[1] == n_q_heads * head_dim and out.is_contiguous() and out.shape == (n_seq, n_q_heads * head_dim)):
+        raise KernelError("decode attention: q/out must be [n_seq, Hq*Dh]")
     ldk = ldv = 0
     if k is not None or v is not None:
-        _need(k is not None and v is not None and k.dtype == v.dtype == torch.bfloat16
-              and k.shape == (n_seq, kv_dim) and v.shape == (n_seq, kv_dim), "decode attention: k/v must be [n_seq, Hkv*Dh]")
+        if not (k is not None and v is not None and k.dtype == v.dtype == torch.bfloat16
+                and k.shape == (n_seq, kv_dim) and v.shape == (n_seq, kv_dim)):
+            raise KernelError("decode attention: k/v must be [n_seq, Hkv*Dh]")
         ldk, ldv = _rows_view(k, "decode attention: k"), _rows_view(v, "decode attention: v")
     _f32vec(inv_freq, head_dim // 2, "decode attention: inv_freq")
-    _need(pool.dim() == 4 and pool.shape[1] == 2 and pool.shape[3] == kv_dim and pool.is_contiguous(),
-          "decode attention: pool must be contiguous [pages, 2, page_size, Hkv*Dh]")
+    if not (pool.dim() == 4 and pool.shape[1] == 2 and pool.shape[3] == kv_dim and pool.is_contiguous()):
+        raise KernelError("decode attention: pool must be contiguous [pages, 2, page_size, Hkv*Dh]")
     _i32(block_table, "decode attention: block_table")
     _i32(positions, "decode attention: positions")
-    _need(block_table.shape[0] >= n_seq and positions.numel() >= n_seq, "decode attention: one table row and position per sequence")
+    if not (block_table.shape[0] >= n_seq and positions.numel() >= n_seq):
+        raise KernelError("decode attention: one table row and position per sequence")
     part_o = part_ml = counter = None
     if n_splits > 1:
         need = attention_scratch_floats(n_seq, n_q_heads, head_dim, n_splits)
-        _need(scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous()
-              and scratch.numel() >= need, f"decode attention: split keys need {need} floats of scratch")
-        _need(split_len > 0 and split_len % 32 == 0 and n_splits <= 64, "decode attention: bad key split")
-        _need(split_counter is not None and split_counter.numel() >= n_seq * n_kv_heads,
-              "decode attention: split keys need a counter per (sequence, key/value head)")
+        if not (scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous()
+                and scratch.numel() >= need):
+            raise KernelError(f"decode attention: split keys need {need} floats of scratch")
+        if not (split_len > 0 and split_len % 32 == 0 and n_splits <= 64):
+            raise KernelError("decode attention: bad key split")
+        if not (split_counter is not None and split_counter.numel() >= n_seq * n_kv_heads):
+            raise KernelError("decode attention: split keys need a counter per (sequence, key/value head)")
         _i32(split_counter, "decode attention: split_counter")
         part_o = scratch.data_ptr()
         part_ml = part_o + 4 * n_seq * n_q_heads * n_splits * head_dim
@@ -846,9 +893,10 @@ SKINNY_NORM_MAX_WIDTH = 1024  # ... and so it is for rows wider than a warp keep
 
 
 def _skinny_check(M: int, w: Tensor, K: int, what: str) -> None:
-    _need(M <= 64, f"{what}: at most 64 tokens")
-    _need(w.dtype == torch.bfloat16 and w.dim() == 2 and w.is_contiguous() and w.shape[1] == K and K % 8 == 0,
-          f"{what}: weights must be contiguous bfloat16 [rows, K] with K a multiple of 8")
+    if not (M <= 64):
+        raise KernelError(f"{what}: at most 64 tokens")
+    if not (w.dtype == torch.bfloat16 and w.dim() == 2 and w.is_contiguous() and w.shape[1] == K and K % 8 == 0):
+        raise KernelError(f"{what}: weights must be contiguous bfloat16 [rows, K] with K a multiple of 8")
 
 
 def skinny_fits(M: int, K: int) -> bool:
@@ -864,19 +912,23 @@ def skinny_linear_norm(h: Tensor, norm_weight: Tensor, eps: float, weight: Tenso
     """out[M, N] = (rmsnorm(h) * norm_weight) @ weight^T for M <= 64 rows of the float32 stream."""
     _cuda(h, norm_weight, weight, out)
     M, K = h.shape
-    _need(h.dtype == torch.float32 and h.is_contiguous(), "skinny_linear_norm: h must be contiguous float32")
+    if not (h.dtype == torch.float32 and h.is_contiguous()):
+        raise KernelError("skinny_linear_norm: h must be contiguous float32")
     _skinny_check(M, weight, K, "skinny_linear_norm")
-    _need(skinny_fits(M, K), f"skinny_linear_norm: {M} tokens x {K} columns do not fit in shared memory")
+    if not (skinny_fits(M, K)):
+        raise KernelError(f"skinny_linear_norm: {M} tokens x {K} columns do not fit in shared memory")
     _f32vec(norm_weight, K, "skinny_linear_norm: norm weight")
     N = weight.shape[0]
-    _need(out.dtype == torch.bfloat16 and out.shape == (M, N) and out.stride(1) == 1, "skinny_linear_norm: out [M, N] bfloat16")
+    if not (out.dtype == torch.bfloat16 and out.shape == (M, N) and out.stride(1) == 1):
+        raise KernelError("skinny_linear_norm: out [M, N] bfloat16")
     _call("pmm_skinny_gemm", 0, M, N, None, 0, h.data_ptr(), norm_weight.data_ptr(), float(eps), weight.data_ptr(), K,
           1.0, None, 0, None, 0, 0.0, out.data_ptr(), out.stride(0), None, 1, _stream())
 
 
 def _skinny_x(x: Tensor, M: int, K: int, what: str) -> None:
-    _need(x.dtype == torch.bfloat16 and x.shape == (M, K) and x.stride(1) == 1 and x.stride(0) % 8 == 0
-          and x.data_ptr() % 16 == 0, f"{what}: x must be bfloat16 [M, K] with 16-byte aligned rows")
+    if not (x.dtype == torch.bfloat16 and x.shape == (M, K) and x.stride(1) == 1 and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0):
+        raise KernelError(f"{what}: x must be bfloat16 [M, K] with 16-byte aligned rows")
 
 
 def skinny_linear(x: Tensor, weight: Tensor, out: Tensor) -> None:
@@ -885,9 +937,11 @@ def skinny_linear(x: Tensor, weight: Tensor, out: Tensor) -> None:
     M, K = x.shape
     _skinny_check(M, weight, K, "skinny_linear")
     _skinny_x(x, M, K, "skinny_linear")
-    _need(skinny_fits(M, K), f"skinny_linear: {M} tokens x {K} columns do not fit in shared memory")
+    if not (skinny_fits(M, K)):
+        raise KernelError(f"skinny_linear: {M} tokens x {K} columns do not fit in shared memory")
     N = weight.shape[0]
-    _need(out.dtype == torch.bfloat16 and out.shape == (M, N) and out.stride(1) == 1, "skinny_linear: out [M, N] bfloat16")
+    if not (out.dtype == torch.bfloat16 and out.shape == (M, N) and out.stride(1) == 1):
+        raise KernelError("skinny_linear: out [M, N] bfloat16")
     _call("pmm_skinny_gemm", 0, M, N, x.data_ptr(), x.stride(0), None, None, 0.0, weight.data_ptr(), K,
           1.0, None, 0, None, 0, 0.0, out.data_ptr(), out.stride(0), None, 1, _stream())
 
@@ -899,9 +953,11 @@ def skinny_linear_f32(x: Tensor, weight: Tensor, out: Tensor, scale: float) -> N
     M, K = x.shape
     _skinny_check(M, weight, K, "skinny_linear_f32")
     _skinny_x(x, M, K, "skinny_linear_f32")
-    _need(skinny_fits(M, K), f"skinny_linear_f32: {M} tokens x {K} columns do not fit in shared memory")
+    if not (skinny_fits(M, K)):
+        raise KernelError(f"skinny_linear_f32: {M} tokens x {K} columns do not fit in shared memory")
     N = weight.shape[0]
-    _need(out.dtype == torch.float32 and out.shape == (M, N) and out.stride(1) == 1, "skinny_linear_f32: out [M, N] float32")
+    if not (out.dtype == torch.float32 and out.shape == (M, N) and out.stride(1) == 1):
+        raise KernelError("skinny_linear_f32: out [M, N] float32")
     _call("pmm_skinny_gemm_f32out", M, N, x.data_ptr(), x.stride(0), weight.data_ptr(), K, float(scale),
           out.data_ptr(), out.stride(0), _stream())
 
@@ -912,10 +968,11 @@ def skinny_swiglu(x: Tensor, gate_up: Tensor, gate_mult: float, out: Tensor) -> 
     M, K = x.shape
     _skinny_check(M, gate_up, K, "skinny_swiglu")
     _skinny_x(x, M, K, "skinny_swiglu")
-    _need(skinny_fits(M, K), f"skinny_swiglu: {M} tokens x {K} columns do not fit in shared memory")
+    if not (skinny_fits(M, K)):
+        raise KernelError(f"skinny_swiglu: {M} tokens x {K} columns do not fit in shared memory")
     F = gate_up.shape[0] // 2
-    _need(gate_up.shape[0] == 2 * F and out.dtype == torch.bfloat16 and out.shape == (M, F) and out.is_contiguous(),
-          "skinny_swiglu: out [M, F] bfloat16 for gate_up [2F, K]")
+    if not (gate_up.shape[0] == 2 * F and out.dtype == torch.bfloat16 and out.shape == (M, F) and out.is_contiguous()):
+        raise KernelError("skinny_swiglu: out [M, F] bfloat16 for gate_up [2F, K]")
     _call("pmm_skinny_gemm", 1, M, F, x.data_ptr(), x.stride(0), None, None, 0.0, gate_up.data_ptr(), K,
           float(gate_mult), None, 0, None, 0, 0.0, out.data_ptr(), out.stride(0), None, 1, _stream())
 
@@ -925,13 +982,15 @@ def skinny_swiglu_norm(h: Tensor, norm_weight: Tensor, eps: float, gate_up: Tens
     """out[M, F] = silu(gate * gate_mult) * up with [gate | up] = (rmsnorm(h) * norm_weight) @ gate_up^T."""
     _cuda(h, norm_weight, gate_up, out)
     M, K = h.shape
-    _need(h.dtype == torch.float32 and h.is_contiguous(), "skinny_swiglu_norm: h must be contiguous float32")
+    if not (h.dtype == torch.float32 and h.is_contiguous()):
+        raise KernelError("skinny_swiglu_norm: h must be contiguous float32")
     _skinny_check(M, gate_up, K, "skinny_swiglu_norm")
-    _need(skinny_fits(M, K), f"skinny_swiglu_norm: {M} tokens x {K} columns do not fit in shared memory")
+    if not (skinny_fits(M, K)):
+        raise KernelError(f"skinny_swiglu_norm: {M} tokens x {K} columns do not fit in shared memory")
     _f32vec(norm_weight, K, "skinny_swiglu_norm: norm weight")
     F = gate_up.shape[0] // 2
-    _need(gate_up.shape[0] == 2 * F and out.dtype == torch.bfloat16 and out.shape == (M, F) and out.is_contiguous(),
-          "skinny_swiglu_norm: out [M, F] bfloat16 for gate_up [2F, K]")
+    if not (gate_up.shape[0] == 2 * F and out.dtype == torch.bfloat16 and out.shape == (M, F) and out.is_contiguous()):
+        raise KernelError("skinny_swiglu_norm: out [M, F] bfloat16 for gate_up [2F, K]")
     _call("pmm_skinny_gemm", 1, M, F, None, 0, h.data_ptr(), norm_weight.data_ptr(), float(eps), gate_up.data_ptr(), K,
           float(gate_mult), None, 0, None, 0, 0.0, out.data_ptr(), out.stride(0), None, 1, _stream())
 
@@ -939,19 +998,23 @@ def skinny_swiglu_norm(h: Tensor, norm_weight: Tensor, eps: float, gate_up: Tens
 def skinny_residual(h: Tensor, products: Sequence[Tuple[Tensor, Tensor, float]]) -> None:
     """h[M, N] += sum_i scale_i * (x_i @ w_i^T) for one or two (x, w, scale); float32 atomics, the K
     ranges are split over blocks."""
-    _need(1 <= len(products) <= 2, "skinny_residual: one or two products")
+    if not (1 <= len(products) <= 2):
+        raise KernelError("skinny_residual: one or two products")
     M, N = h.shape
     _cuda(h)
-    _need(h.dtype == torch.float32 and h.is_contiguous(), "skinny_residual: h must be contiguous float32")
+    if not (h.dtype == torch.float32 and h.is_contiguous()):
+        raise KernelError("skinny_residual: h must be contiguous float32")
     args = []
     k_max = 0
     for x, w, sc in products:
         _cuda(x, w)
         K = x.shape[1]
-        _need(x.dtype == torch.bfloat16 and x.shape[0] == M and x.stride(1) == 1 and x.stride(0) % 8 == 0
-              and x.data_ptr() % 16 == 0, "skinny_residual: x must be bfloat16 [M, K] with 16-byte aligned rows")
+        if not (x.dtype == torch.bfloat16 and x.shape[0] == M and x.stride(1) == 1 and x.stride(0) % 8 == 0
+                and x.data_ptr() % 16 == 0):
+            raise KernelError("skinny_residual: x must be bfloat16 [M, K] with 16-byte aligned rows")
         _skinny_check(M, w, K, "skinny_residual")
-        _need(w.shape[0] == N, "skinny_residual: weight rows must equal the stream width")
+        if not (w.shape[0] == N):
+            raise KernelError("skinny_residual: weight rows must equal the stream width")
         args.append((x.data_ptr(), x.stride(0), w.data_ptr(), K, float(sc)))
         k_max = max(k_max, K)
     chunks = (k_max + 255) // 256
@@ -1002,22 +1065,27 @@ def skinny_chain(h: Tensor, phases: Sequence[Tuple]) -> None:
     """
     _cuda(h)
     M, D = h.shape
-    _need(h.dtype == torch.float32 and h.is_contiguous() and M <= 16, "skinny_chain: h must be contiguous float32 [<=16, D]")
-    _need(1 <= len(phases) <= SKINNY_CHAIN_MAX, f"skinny_chain: 1 to {SKINNY_CHAIN_MAX} phases")
+    if not (h.dtype == torch.float32 and h.is_contiguous() and M <= 16):
+        raise KernelError("skinny_chain: h must be contiguous float32 [<=16, D]")
+    if not (1 <= len(phases) <= SKINNY_CHAIN_MAX):
+        raise KernelError(f"skinny_chain: 1 to {SKINNY_CHAIN_MAX} phases")
     arr = (_SkinnyPhase * len(phases))()
     for ph, slot in zip(phases, arr):
         kind = ph[0]
         if kind == "residual":
             products = ph[1]
-            _need(1 <= len(products) <= 2, "skinny_chain: one or two products per residual phase")
+            if not (1 <= len(products) <= 2):
+                raise KernelError("skinny_chain: one or two products per residual phase")
             slot.mode, slot.N, slot.h_out = 2, D, h.data_ptr()
             for i, (x, w, sc) in enumerate(products):
                 _cuda(x, w)
                 K = x.shape[1]
-                _need(x.dtype == torch.bfloat16 and x.shape[0] == M and x.stride(1) == 1 and x.stride(0) % 8 == 0
-                      and x.data_ptr() % 16 == 0, "skinny_chain: x must be bfloat16 [M, K] with 16-byte aligned rows")
+                if not (x.dtype == torch.bfloat16 and x.shape[0] == M and x.stride(1) == 1 and x.stride(0) % 8 == 0
+                        and x.data_ptr() % 16 == 0):
+                    raise KernelError("skinny_chain: x must be bfloat16 [M, K] with 16-byte aligned rows")
                 _skinny_check(M, w, K, "skinny_chain")
-                _need(w.shape[0] == D, "skinny_chain: weight rows must equal the stream width")
+                if not (w.shape[0] == D):
+                    raise KernelError("skinny_chain: weight rows must equal the stream width")
                 if i == 0:
                     slot.x0, slot.ldx0, slot.w0, slot.K0, slot.scale0 = x.data_ptr(), x.stride(0), w.data_ptr(), K, float(sc)
                 else:
@@ -1027,11 +1095,13 @@ def skinny_chain(h: Tensor, phases: Sequence[Tuple]) -> None:
             out = ph[-1]
             _cuda(norm_w, w, out)
             _skinny_check(M, w, D, "skinny_chain")
-            _need(skinny_fits(M, D), f"skinny_chain: {M} tokens x {D} columns do not fit in shared memory")
+            if not (skinny_fits(M, D)):
+                raise KernelError(f"skinny_chain: {M} tokens x {D} columns do not fit in shared memory")
             _f32vec(norm_w, D, "skinny_chain: norm weight")
             n_out = w.shape[0] // 2 if kind == "swiglu" else w.shape[0]
-            _need(out.dtype == torch.bfloat16 and out.shape == (M, n_out) and out.stride(1) == 1
-                  and (kind == "store" or w.shape[0] == 2 * n_out), "skinny_chain: out must be bfloat16 [M, N]")
+            if not (out.dtype == torch.bfloat16 and out.shape == (M, n_out) and out.stride(1) == 1
+                    and (kind == "store" or w.shape[0] == 2 * n_out)):
+                raise KernelError("skinny_chain: out must be bfloat16 [M, N]")
             slot.mode, slot.N = (1 if kind == "swiglu" else 0), n_out
             slot.h_in, slot.norm_w, slot.eps = h.data_ptr(), norm_w.data_ptr(), float(eps)
             slot.w0, slot.K0, slot.scale0 = w.data_ptr(), D, (float(ph[4]) if kind == "swiglu" else 1.0)
@@ -1078,8 +1148,9 @@ def skinny_tc_supported(kind: str, x: Tensor, weight: Tensor, out: Optional[Tens
 def skinny_tc_linear(x: Tensor, weight: Tensor, out: Tensor) -> None:
     """out[T, N] (bfloat16) = x @ weight^T for up to 64 tokens on the tcgen05 tensor cores."""
     _cuda(x, weight, out)
-    _need(skinny_tc_supported("store", x, weight, out) and out.shape == (x.shape[0], weight.shape[0]),
-          "skinny_tc_linear: operands not supported (bfloat16, <= 64 tokens, K <= 1024 and a multiple of 8, aligned rows)")
+    if not (skinny_tc_supported("store", x, weight, out) and out.shape == (x.shape[0], weight.shape[0])):
+        raise KernelError("skinny_tc_linear: operands not supported (bfloat16, <= 64 tokens, K <= 1024 and a "
+                          "multiple of 8, aligned rows)")
     T, K = x.shape
     _call("pmm_skinny_tc", 0, T, weight.shape[0], x.data_ptr(), x.stride(0), weight.data_ptr(), K, 1.0, None, 0, None, 0,
           0.0, out.data_ptr(), out.stride(0), None, _tc_status(x.device).data_ptr(), _stream())
@@ -1089,8 +1160,9 @@ def skinny_tc_swiglu(x: Tensor, gate_up: Tensor, gate_mult: float, out: Tensor) 
     """out[T, F] = silu(gate * gate_mult) * up with [gate | up] = x @ gate_up^T (tcgen05, up to 64 tokens)."""
     _cuda(x, gate_up, out)
     F = gate_up.shape[0] // 2
-    _need(gate_up.shape[0] == 2 * F and skinny_tc_supported("swiglu", x, gate_up, out) and out.shape == (x.shape[0], F),
-          "skinny_tc_swiglu: operands not supported (bfloat16, <= 64 tokens, K <= 1024 and a multiple of 8, aligned rows)")
+    if not (gate_up.shape[0] == 2 * F and skinny_tc_supported("swiglu", x, gate_up, out) and out.shape == (x.shape[0], F)):
+        raise KernelError("skinny_tc_swiglu: operands not supported (bfloat16, <= 64 tokens, K <= 1024 and a "
+                          "multiple of 8, aligned rows)")
     T, K = x.shape
     _call("pmm_skinny_tc", 1, T, F, x.data_ptr(), x.stride(0), gate_up.data_ptr(), K, float(gate_mult), None, 0, None, 0,
           0.0, out.data_ptr(), out.stride(0), None, _tc_status(x.device).data_ptr(), _stream())
@@ -1099,15 +1171,18 @@ def skinny_tc_swiglu(x: Tensor, gate_up: Tensor, gate_mult: float, out: Tensor) 
 def skinny_tc_residual(h: Tensor, products: Sequence[Tuple[Tensor, Tensor, float]]) -> None:
     """h[T, N] += sum_i scale_i * (x_i @ w_i^T) for one or two products (tcgen05, up to 64 tokens;
     float32 atomics, K in slices of at most 1,024 columns)."""
-    _need(1 <= len(products) <= 2, "skinny_tc_residual: one or two products")
+    if not (1 <= len(products) <= 2):
+        raise KernelError("skinny_tc_residual: one or two products")
     _cuda(h)
     T, N = h.shape
-    _need(h.dtype == torch.float32 and h.is_contiguous(), "skinny_tc_residual: h must be contiguous float32")
+    if not (h.dtype == torch.float32 and h.is_contiguous()):
+        raise KernelError("skinny_tc_residual: h must be contiguous float32")
     flat = []
     for x, w, sc in products:
         _cuda(x, w)
-        _need(skinny_tc_supported("residual", x, w) and x.shape[0] == T and w.shape[0] == N,
-              "skinny_tc_residual: operands not supported (bfloat16, <= 64 tokens, K a multiple of 8, aligned rows)")
+        if not (skinny_tc_supported("residual", x, w) and x.shape[0] == T and w.shape[0] == N):
+            raise KernelError("skinny_tc_residual: operands not supported (bfloat16, <= 64 tokens, K a multiple of "
+                              "8, aligned rows)")
         flat.append((x.data_ptr(), x.stride(0), w.data_ptr(), x.shape[1], float(sc)))
     a0 = flat[0]
     a1 = flat[1] if len(flat) > 1 else (None, 0, None, 0, 0.0)
@@ -1131,9 +1206,10 @@ def tc_gemm_swiglu(x: Tensor, gate_up: Tensor, gate_mult: float, out: Tensor) ->
     _cuda(x, gate_up, out)
     T, K = x.shape
     F = gate_up.shape[0] // 2
-    _need(gate_up.shape == (2 * F, K) and out.shape == (T, F) and out.is_contiguous() and out.dtype == torch.bfloat16,
-          "tc_gemm_swiglu: out must be contiguous bfloat16 [T, F] for gate_up [2F, K]")
-    _need(tc_gemm_supported(x, gate_up, F, True), "tc_gemm_swiglu: sizes or alignment outside what the kernel takes")
+    if not (gate_up.shape == (2 * F, K) and out.shape == (T, F) and out.is_contiguous() and out.dtype == torch.bfloat16):
+        raise KernelError("tc_gemm_swiglu: out must be contiguous bfloat16 [T, F] for gate_up [2F, K]")
+    if not (tc_gemm_supported(x, gate_up, F, True)):
+        raise KernelError("tc_gemm_swiglu: sizes or alignment outside what the kernel takes")
     _call("pmm_tc_gemm", 1, x.data_ptr(), x.stride(0), gate_up.data_ptr(), out.data_ptr(), out.stride(0), T, K, F,
           float(gate_mult), _tc_status(x.device).data_ptr(), _stream())
 
@@ -1143,9 +1219,11 @@ def tc_gemm(x: Tensor, weight: Tensor, out: Tensor) -> None:
     _cuda(x, weight, out)
     T, K = x.shape
     N = weight.shape[0]
-    _need(weight.shape == (N, K) and out.shape == (T, N) and out.stride(1) == 1 and out.dtype == torch.bfloat16
-          and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0, "tc_gemm: out must be bfloat16 [T, N], rows 16-byte aligned")
-    _need(tc_gemm_supported(x, weight, N, False), "tc_gemm: sizes or alignment outside what the kernel takes")
+    if not (weight.shape == (N, K) and out.shape == (T, N) and out.stride(1) == 1 and out.dtype == torch.bfloat16
+            and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0):
+        raise KernelError("tc_gemm: out must be bfloat16 [T, N], rows 16-byte aligned")
+    if not (tc_gemm_supported(x, weight, N, False)):
+        raise KernelError("tc_gemm: sizes or alignment outside what the kernel takes")
     _call("pmm_tc_gemm", 0, x.data_ptr(), x.stride(0), weight.data_ptr(), out.data_ptr(), out.stride(0), T, K, N,
           1.0, _tc_status(x.device).data_ptr(), _stream())
 
@@ -1166,13 +1244,14 @@ def attention_tc(q: Tensor, pool: Tensor, block_table: Tensor, positions: Tensor
     the step's keys already; 128 rows of (token, query head of a group) per block."""
     _cuda(q, pool, block_table, positions, cu_seqlens, out, scratch, split_counter)
     T = q.shape[0]
-    _need(q.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
-          and q.is_contiguous() and out.is_contiguous() and q.shape == (T, n_q_heads * head_dim) and out.shape == q.shape,
-          "attention_tc: q and out must be contiguous bfloat16 [T, Hq*Dh]")
-    _need(pool.dim() == 4 and pool.shape[1] == 2 and pool.shape[3] == n_kv_heads * head_dim and pool.is_contiguous(),
-          "attention_tc: pool must be contiguous [pages, 2, page_size, Hkv*Dh]")
-    _need(attention_tc_supported(n_q_heads, n_kv_heads, head_dim, pool.shape[2]),
-          "attention_tc: head size 64 or 128, at most 64 query heads per key/value head and pages of a multiple of 64 tokens")
+    if not (q.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+            and q.is_contiguous() and out.is_contiguous() and q.shape == (T, n_q_heads * head_dim) and out.shape == q.shape):
+        raise KernelError("attention_tc: q and out must be contiguous bfloat16 [T, Hq*Dh]")
+    if not (pool.dim() == 4 and pool.shape[1] == 2 and pool.shape[3] == n_kv_heads * head_dim and pool.is_contiguous()):
+        raise KernelError("attention_tc: pool must be contiguous [pages, 2, page_size, Hkv*Dh]")
+    if not (attention_tc_supported(n_q_heads, n_kv_heads, head_dim, pool.shape[2])):
+        raise KernelError("attention_tc: head size 64 or 128, at most 64 query heads per key/value head and pages "
+                          "of a multiple of 64 tokens")
     _i32(block_table, "attention_tc: block_table")
     _i32(positions, "attention_tc: positions")
     _i32(cu_seqlens, "attention_tc: cu_seqlens")
@@ -1181,12 +1260,13 @@ def attention_tc(q: Tensor, pool: Tensor, block_table: Tensor, positions: Tensor
     part_o = part_ml = counter = None
     if n_splits > 1:
         need = attention_scratch_floats(T, n_q_heads, head_dim, n_splits)
-        _need(scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous()
-              and scratch.numel() >= need and scratch.data_ptr() % 16 == 0,
-              f"attention_tc: split keys need {need} floats of scratch")
-        _need(split_len > 0 and split_len % 64 == 0 and n_splits <= 64, "attention_tc: split_len must be a multiple of 64")
-        _need(split_counter is not None and split_counter.numel() >= n_tiles * n_kv_heads,
-              "attention_tc: split keys need a counter per (row tile, key/value head)")
+        if not (scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous()
+                and scratch.numel() >= need and scratch.data_ptr() % 16 == 0):
+            raise KernelError(f"attention_tc: split keys need {need} floats of scratch")
+        if not (split_len > 0 and split_len % 64 == 0 and n_splits <= 64):
+            raise KernelError("attention_tc: split_len must be a multiple of 64")
+        if not (split_counter is not None and split_counter.numel() >= n_tiles * n_kv_heads):
+            raise KernelError("attention_tc: split keys need a counter per (row tile, key/value head)")
         _i32(split_counter, "attention_tc: split_counter")
         part_o = scratch.data_ptr()
         part_ml = part_o + 4 * T * n_q_heads * n_splits * head_dim
@@ -1202,8 +1282,8 @@ def silu_mul(gate_up: Tensor, gate_mult: float, out: Tensor) -> None:
     _cuda(gate_up, out)
     ld = _rows_view(gate_up, "silu_mul: gate_up")
     T, F2 = gate_up.shape
-    _need(F2 % 2 == 0 and out.shape == (T, F2 // 2) and out.is_contiguous() and out.dtype == gate_up.dtype,
-          "silu_mul: out must be contiguous [T, F] for gate_up [T, 2F]")
+    if not (F2 % 2 == 0 and out.shape == (T, F2 // 2) and out.is_contiguous() and out.dtype == gate_up.dtype):
+        raise KernelError("silu_mul: out must be contiguous [T, F] for gate_up [T, 2F]")
     _call("pmm_silu_mul", gate_up.data_ptr(), ld, float(gate_mult), out.data_ptr(), T, F2 // 2,
           _dt(gate_up), _stream())
 
@@ -1211,7 +1291,8 @@ def silu_mul(gate_up: Tensor, gate_mult: float, out: Tensor) -> None:
 def add_row_bias_(x: Tensor, bias: Tensor) -> None:
     """x[t, :] += bias (float32 vector) for a contiguous [T, D] activation."""
     _cuda(x, bias)
-    _need(x.dim() == 2 and x.is_contiguous(), "add_row_bias_: x must be contiguous [T, D]")
+    if not (x.dim() == 2 and x.is_contiguous()):
+        raise KernelError("add_row_bias_: x must be contiguous [T, D]")
     _f32vec(bias, x.shape[1], "add_row_bias_: bias")
     _call("pmm_add_row_bias", x.data_ptr(), bias.data_ptr(), x.shape[0], x.shape[1], _dt(x), _stream())
 
@@ -1227,8 +1308,9 @@ def ensure_sample_scratch(device, rows: int = 4096) -> Tuple[Tensor, Tensor]:
     device = torch.device(device)
     have = _SAMPLE_SCRATCH.get(device)
     if have is None or have[0].numel() < rows:
-        _need(not torch.cuda.is_current_stream_capturing(),
-              "sample_rows: its scratch must exist before a CUDA graph is recorded (ensure_sample_scratch)")
+        if not (not torch.cuda.is_current_stream_capturing()):
+            raise KernelError("sample_rows: its scratch must exist before a CUDA graph is recorded "
+                              "(ensure_sample_scratch)")
         n = max(4096, rows)
         have = (torch.zeros(n, dtype=torch.int64, device=device), torch.zeros(n, dtype=torch.int32, device=device))
         _SAMPLE_SCRATCH[device] = have
@@ -1242,14 +1324,17 @@ def sample_rows(logits: Tensor, temperature: Optional[Tensor], seeds: Optional[T
     _cuda(logits, temperature, seeds, steps, out)
     ld = _rows_view(logits, "sample: logits")
     n, V = logits.shape
-    _need(logits.dtype == torch.float32, "sample: logits must be float32")
+    if not (logits.dtype == torch.float32):
+        raise KernelError("sample: logits must be float32")
     _i32(out, "sample: out")
-    _need(out.numel() == n, "sample: one output per row")
+    if not (out.numel() == n):
+        raise KernelError("sample: one output per row")
     if temperature is not None:
         _f32vec(temperature, n, "sample: temperature")
-        _need(seeds is not None and seeds.dtype == torch.int64 and seeds.numel() == n and seeds.is_contiguous(),
-              "sample: seeds must be int64 [rows]")
-        _need(steps is not None and steps.numel() == n, "sample: steps must be int32 [rows]")
+        if not (seeds is not None and seeds.dtype == torch.int64 and seeds.numel() == n and seeds.is_contiguous()):
+            raise KernelError("sample: seeds must be int64 [rows]")
+        if not (steps is not None and steps.numel() == n):
+            raise KernelError("sample: steps must be int32 [rows]")
         _i32(steps, "sample: steps")
     slots, tickets = ensure_sample_scratch(logits.device, n)
     _call("pmm_sample_rows", logits.data_ptr(), ld, _ptr(temperature), _ptr(seeds), _ptr(steps),
@@ -1264,7 +1349,8 @@ def l2_prefetch(tensors: Sequence[Tensor]) -> None:
         part = ts[i:i + 8]
         _cuda(*part)
         for t in part:
-            _need(t.is_contiguous() and t.data_ptr() % 16 == 0, "l2_prefetch: tensors must be contiguous and 16-byte aligned")
+            if not (t.is_contiguous() and t.data_ptr() % 16 == 0):
+                raise KernelError("l2_prefetch: tensors must be contiguous and 16-byte aligned")
         ptrs = (ctypes.c_void_p * len(part))(*[t.data_ptr() for t in part])
         sizes = (ctypes.c_longlong * len(part))(*[t.numel() * t.element_size() for t in part])
         _call("pmm_l2_prefetch", ctypes.cast(ptrs, ctypes.c_void_p), ctypes.cast(sizes, ctypes.c_void_p), len(part),

@@ -18,7 +18,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..kernels import ops as K
-from . import streaming
+from . import branches, streaming
 from .base import (FeedForward, LayerCache, LayerSpec, Mixer, Norm, ParamSpec, Part, PartSpec, StateSpec,
                    build_part, register_arrangement)
 from .norm import fold_branches
@@ -136,24 +136,13 @@ class ParallelPreNormBlock(Part):
             return False
         return len(self.mixers) <= 2
 
-    _SIDE_STREAMS: Dict[torch.device, "torch.cuda.Stream"] = {}
-    _FETCH_STREAMS: Dict[torch.device, "torch.cuda.Stream"] = {}
+    @staticmethod
+    def _side_stream(device: torch.device) -> "torch.cuda.Stream":
+        return branches.branch_stream(device, "mixer")
 
-    @classmethod
-    def _side_stream(cls, device: torch.device) -> "torch.cuda.Stream":
-        st = cls._SIDE_STREAMS.get(device)
-        if st is None:
-            st = torch.cuda.Stream(device=device)
-            cls._SIDE_STREAMS[device] = st
-        return st
-
-    @classmethod
-    def _fetch_stream(cls, device: torch.device) -> "torch.cuda.Stream":
-        st = cls._FETCH_STREAMS.get(device)
-        if st is None:
-            st = torch.cuda.Stream(device=device)
-            cls._FETCH_STREAMS[device] = st
-        return st
+    @staticmethod
+    def _fetch_stream(device: torch.device) -> "torch.cuda.Stream":
+        return branches.branch_stream(device, "fetch")
 
     def streamed_weights(self) -> List[Tensor]:
         """The matrices a step of few tokens reads once: what the layer before this one may
@@ -177,8 +166,7 @@ class ParallelPreNormBlock(Part):
         # (in a captured step the two become parallel branches of the graph).
         products = [None] * len(self.mixers)
         if side is not None:
-            side.wait_stream(main)
-            with torch.cuda.stream(side):
+            with branches.fork(main, side):
                 m, (c0, c1) = self.mixers[0], self._fused_cols[0]
                 products[0] = (m.pre_output(proj[:, c0:c1], ctx, cache), m.output_weight(), m.out_scale)
         for i, (m, (c0, c1)) in enumerate(zip(self.mixers, self._fused_cols)):
@@ -195,8 +183,7 @@ class ParallelPreNormBlock(Part):
             # 8 tokens 1.03 / 1.04 / 1.07, 16 tokens 1.32 / 1.48 / 1.45); a step of one token has no
             # phase to protect and is faster when nothing waits (1.06 / 0.88 / 0.92).
             fetch = side if side is not None and T > 1 else self._fetch_stream(h.device)
-            fetch.wait_stream(main)
-            with torch.cuda.stream(fetch):
+            with branches.fork(main, fetch):
                 K.l2_prefetch(ahead)
             ctx.unjoined_stream = fetch  # joined by the model when the step's last layer has run
         # h = (h + s0 * y0 W0^T) + s1 * y1 W1^T in one launch, then the feed-forward
@@ -231,8 +218,7 @@ class ParallelPreNormBlock(Part):
             main = torch.cuda.current_stream(proj.device)
             for i, (m, (c0, c1)) in enumerate(zip(self.mixers, self._fused_cols)):
                 if i == 0 and side is not None:
-                    side.wait_stream(main)
-                    with torch.cuda.stream(side):
+                    with branches.fork(main, side):
                         m.forward_projected(proj[:, c0:c1], ctx, cache, outs[i])
                 else:
                     m.forward_projected(proj[:, c0:c1], ctx, cache, outs[i])

@@ -22,6 +22,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from ..kernels import ops as K
+from . import branches
 from .base import Mixer, ParamSpec, StateSpec, register_mixer
 
 Tensor = torch.Tensor
@@ -32,19 +33,6 @@ _CHUNKED_FROM = 8
 # seven size pairs it is compiled for).
 _TC_SCAN = os.environ.get("PMM_TCGEN05_SCAN", "1") == "1"
 _NOTED = set()
-_BRANCH_STREAMS: Dict[tuple, "torch.cuda.Stream"] = {}
-
-
-def _branch_stream(device: torch.device, what: str) -> "torch.cuda.Stream":
-    """A stream for work that runs beside the scan's chain of launches: "lone" (a mixed step's lone
-    tokens beside the prompt portions), "window" (the convolution windows' update)."""
-    st = _BRANCH_STREAMS.get((device, what))
-    if st is None:
-        st = torch.cuda.Stream(device=device)
-        _BRANCH_STREAMS[(device, what)] = st
-    return st
-
-
 def _note_serial(d_head: int, d_state: int) -> None:
     """Says once that prompts of this shape are scanned token by token."""
     if (d_head, d_state) not in _NOTED:
@@ -193,9 +181,8 @@ class Mamba2Mixer(Mixer):
             # The window is next read by the next step: its update leaves the scan's chain (a branch
             # of its own in a captured step, joined before this mixer returns).
             here = torch.cuda.current_stream(xbc.device)
-            update = _branch_stream(xbc.device, "window")
-            update.wait_stream(here)
-            with torch.cuda.stream(update):
+            update = branches.branch_stream(xbc.device, "window")
+            with branches.fork(here, update):
                 K.conv1d_window_update(xbc_raw, self.conv_pre_scale, self.conv_pre_bias, window, ctx.cu_seqlens,
                                        ctx.slots, ctx.n_seq, self.d_conv)
             window_updating = (here, update)
@@ -216,10 +203,8 @@ class Mamba2Mixer(Mixer):
                 # tokens' scan is a read and write of their states at the memory's rate, the chunked one
                 # a chain of three tensor-core launches: they run side by side (parallel branches of a
                 # captured step).
-                here = torch.cuda.current_stream(xbc.device)
-                side = _branch_stream(xbc.device, "lone")
-                side.wait_stream(here)
-                with torch.cuda.stream(side):
+                side = branches.branch_stream(xbc.device, "lone")
+                with branches.fork(here, side):
                     K.ssm_scan_seq(xbc, dt, self.dt_scale, self.dt_shift, self.a_log, self.d_skip, state,
                                    ctx.cu_seqlens, ctx.slots, ctx.n_seq, y, self.n_groups, gate=gate, only_single=True)
             K.ssm_scan_tc(xbc, dt, self.dt_scale, self.dt_shift, self.a_log, self.d_skip, state, ctx.cu_seqlens,

@@ -137,6 +137,12 @@ class Model:
         normed = stream.normed(self.final_norm, rows=ctx.logit_rows)
         return self._head(normed, ctx)
 
+    def accepts_length_bounds(self, page_size: int) -> bool:
+        """Whether every layer stays right when a step's lengths are given as bounds (see
+        Mixer.accepts_length_bounds); an arrangement that does not say so does not."""
+        return self.dtype is not None and all(
+            getattr(layer, "accepts_length_bounds", lambda d, p: False)(self.dtype, page_size) for layer in self.layers)
+
     @staticmethod
     def _join(ctx: StepContext, device) -> None:
         """Wait for what a layer left running on a side stream (so that a recorded step ends joined)."""

@@ -13,6 +13,7 @@ buffer, one host-to-device copy.  Everything else is kernels on the current stre
 from __future__ import annotations
 
 import collections
+import os
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
@@ -22,9 +23,9 @@ import torch
 from ..cache.manager import CacheManager
 from ..cache.pages import OutOfPages
 from ..kernels import ops as K
-from .context import StepContext
+from .context import LengthBounds, StepContext
 from .model import Model
-from .workspace import Workspace, quiet_capture
+from .workspace import Workspace, lean_capture
 
 Tensor = torch.Tensor
 
@@ -40,14 +41,21 @@ class StepEntry:
 
 # Prompt steps whose shape (token counts per request, wanted rows, key-length bucket) comes a second
 # time are recorded into a CUDA graph and replayed from then on.  Two caches, so that a stream of
-# short steps of ever new shapes cannot push out the few large shapes of chunked prefill: steps of at
-# least _STEP_GRAPH_MIN_TOKENS tokens (their workspaces are large: few of them are kept), and shorter
-# ones down to _STEP_GRAPH_SMALL_FROM tokens (a short prompt costs the host 9 ms of launches when it is
-# not replayed, 36 layers of the 0.5B sizes).
+# short steps of ever new shapes cannot push out the shapes of chunked prefill: steps of at least
+# _STEP_GRAPH_MIN_TOKENS tokens (their workspaces are large: at most _STEP_GRAPH_CAPACITY of them and
+# _STEP_GRAPH_BYTES of workspace are kept), and shorter ones down to _STEP_GRAPH_SMALL_FROM tokens (a
+# short prompt costs the host 9 ms of launches when it is not replayed, 36 layers of the 0.5B sizes).
 _STEP_GRAPH_MIN_TOKENS = 256
-_STEP_GRAPH_CAPACITY = 6
+_STEP_GRAPH_CAPACITY = 32
+_STEP_GRAPH_BYTES = 8 << 30
 _STEP_GRAPH_SMALL_FROM = 2
 _STEP_GRAPH_SMALL_CAPACITY = 24
+# Large steps are recorded under a rounded shape (see ModelRunner._rounded_shape) where the model's
+# parts allow it, so that a server's ever-changing cuts share recordings: a 36-layer prompt step costs
+# the host 10 ms when issued launch by launch and the device 5.  PMM_ROUNDED_STEP_GRAPHS=0: exact
+# shapes only.
+_ROUNDED_STEP_GRAPHS = os.environ.get("PMM_ROUNDED_STEP_GRAPHS", "1") == "1"
+_ROUND_TOKENS = 64
 
 
 class _Staging:
@@ -104,7 +112,10 @@ class ModelRunner:
         self._sampler = None
         self._step_graphs: "collections.OrderedDict" = collections.OrderedDict()
         self._small_step_graphs: "collections.OrderedDict" = collections.OrderedDict()
+        self._shape_seen: Dict[Tuple, int] = {}  # how often a shape without a recording was issued
         self._step_kernels_replayed = 0  # kernels inside the step graphs replayed so far
+        self._accepts_bounds: Optional[bool] = None  # asked of the model when the first large step comes
+        self._largest_rounded = 0
 
     def enable_graphs(self, max_seq_len: int, buckets=None) -> None:
         """Serve decode-only steps from CUDA graphs (captured per batch-size bucket on first use).
@@ -144,19 +155,27 @@ class ModelRunner:
         self._last_sampled = self._sampler.sample_device(logits, temperatures, seeds, steps)
         return self._last_sampled
 
-    def _capture_step(self, entry: dict, total: int, fill, context) -> None:
+    def _capture_step(self, total: int, fill, context) -> dict:
         """Record the forward pass of one step shape into a CUDA graph over buffers of its own."""
         meta = torch.zeros(total, dtype=torch.int32, device=self.device)
         self._staging.upload(total, fill, dev=meta)
         workspace = Workspace(self.device, initial_bytes=self.workspace.high_water + (8 << 20))
         workspace.freeze()
         ctx, tables = context(meta, workspace)
-        torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         before = K.launch_count
-        with quiet_capture(graph):
+        with lean_capture(graph, self.device):
             logits = self.model.forward(ctx, self.cache.layer_caches(tables))
-        entry.update(graph=graph, meta=meta, workspace=workspace, logits=logits, kernels=K.launch_count - before)
+        return dict(graph=graph, meta=meta, workspace=workspace, logits=logits, kernels=K.launch_count - before)
+
+    @staticmethod
+    def _evict_step_graphs(shapes: "collections.OrderedDict", large: bool) -> None:
+        """Least recently replayed recordings go when there are too many of them, or (large steps)
+        when their workspaces together hold more than _STEP_GRAPH_BYTES; the newest two stay."""
+        cap = _STEP_GRAPH_CAPACITY if large else _STEP_GRAPH_SMALL_CAPACITY
+        while len(shapes) > 2 and (len(shapes) > cap or (
+                large and sum(e["workspace"].capacity() for e in shapes.values()) > _STEP_GRAPH_BYTES)):
+            shapes.popitem(last=False)
 
     def kernels_launched_since(self, launch_count_before: int) -> int:
         """Own kernels launched since ``launch_count_before`` (a value of kernels.ops.launch_count),
@@ -193,6 +212,98 @@ class ModelRunner:
         return (new_reqs <= self.cache.free_slots
                 and all(reserved[k] <= g.pool.n_free for k, g in self.cache.groups.items()))
 
+    # ------------------------------------------------------------------ step shapes
+    def _rounded_shape(self, new_lens: List[int], n_rows: int, kv_len: int):
+        """For a step of at least _STEP_GRAPH_MIN_TOKENS tokens through a model whose parts accept
+        lengths as bounds: (graph key, token counts of the padding sequences, rows, key-length bound)
+        of the rounded shape it is replayed with, else None.
+
+        The step is padded with sequences that belong to no request (tokens 0 from position 0, the
+        spare state slot, block tables full of the spare page) up to a power of two of sequences
+        (at least one padding sequence) and a multiple of _ROUND_TOKENS tokens, its wanted rows with
+        copies of the first up to a power of two.  The model sees the padded batch with
+        `LengthBounds` in place of the tokens per sequence, so every launch has the shape the key
+        gives it and the recording serves every cut of the real tokens; the real rows' results are
+        what they are without the padding (rows and sequences do not mix)."""
+        T, n_seq = sum(new_lens), len(new_lens)
+        if T < _STEP_GRAPH_MIN_TOKENS or max(new_lens) == 1 or not _ROUNDED_STEP_GRAPHS:
+            return None
+        if self._accepts_bounds is None:
+            self._accepts_bounds = bool(self.model.accepts_length_bounds(self.cache.page_size))
+        if not self._accepts_bounds:
+            return None
+        n_seq_b = 1 << n_seq.bit_length()          # the next power of two above n_seq
+        n_pad = n_seq_b - n_seq
+        T_b = -(-(T + n_pad) // _ROUND_TOKENS) * _ROUND_TOKENS
+        # Steps at the scheduler's token budget all round to one size.  The steps that end a burst of
+        # prompts have any size: they are rounded four times as coarsely (up to 255 tokens of padding
+        # against being issued launch by launch), so that few recordings serve them.
+        self._largest_rounded = max(self._largest_rounded, T_b)
+        if T_b < self._largest_rounded:
+            T_b = min(self._largest_rounded, -(-T_b // (4 * _ROUND_TOKENS)) * (4 * _ROUND_TOKENS))
+        pad_lens = [T_b - T - (n_pad - 1)] + [1] * (n_pad - 1)
+        kv_b = max(kv_len, 1 << (pad_lens[0] - 1).bit_length())
+        if kv_b > self.graphs.max_seq_len:
+            return None
+        rows_b = 1 << (n_rows - 1).bit_length() if n_rows > 0 else 0
+        return ("rounded", T_b, n_seq_b, rows_b, kv_b), pad_lens, rows_b, kv_b
+
+    def _layout(self, seqs, rows: List[int], groups, widths: List[int], kv_len: int, lens_for_parts):
+        """One packed int32 upload for a batch of sequences (token ids, tokens already held, state
+        slot, request or None for padding): tokens | positions | seq_of | cu | slots | rows | block
+        tables.  Returns (number of ints, fill(host array), context(device array, workspace))."""
+        cache = self.cache
+        n_seq = len(seqs)
+        lens = [len(q[0]) for q in seqs]
+        T = sum(lens)
+        n_rows = len(rows)
+        o_tok, o_pos, o_seq = 0, T, 2 * T
+        o_cu = 3 * T
+        o_slot = o_cu + n_seq + 1
+        o_rows = o_slot + n_seq
+        o_tab = o_rows + n_rows
+        tab_offsets = []
+        total = o_tab
+        for w in widths:
+            tab_offsets.append(total)
+            total += n_seq * w
+
+        def fill(buf: np.ndarray) -> None:
+            t0 = 0
+            buf[o_cu] = 0
+            for s, (toks, held, slot, _) in enumerate(seqs):
+                n = lens[s]
+                buf[o_tok + t0:o_tok + t0 + n] = toks
+                buf[o_pos + t0:o_pos + t0 + n] = np.arange(held, held + n, dtype=np.int32)
+                buf[o_seq + t0:o_seq + t0 + n] = s
+                buf[o_cu + s + 1] = t0 + n
+                buf[o_slot + s] = slot
+                t0 += n
+            buf[o_rows:o_rows + n_rows] = rows
+            for g, w, off in zip(groups, widths, tab_offsets):
+                tab = buf[off:off + n_seq * w].reshape(n_seq, w)
+                tab[:] = g.num_pages  # the spare page: never owned, safe to touch
+                for s, q in enumerate(seqs):
+                    if q[3] is None:
+                        continue
+                    row = g.tables[q[3]]
+                    arr = np.asarray(row, dtype=np.int32)
+                    arr[arr < 0] = g.num_pages
+                    tab[s, :len(row)] = arr
+
+        def context(dev: Tensor, workspace: Workspace):
+            tables = {g.key: dev[off:off + n_seq * w].view(n_seq, w) for g, w, off in zip(groups, widths, tab_offsets)}
+            return StepContext(
+                n_tokens=T, n_seq=n_seq,
+                tokens=dev[o_tok:o_tok + T], positions=dev[o_pos:o_pos + T], seq_of=dev[o_seq:o_seq + T],
+                cu_seqlens=dev[o_cu:o_cu + n_seq + 1], slots=dev[o_slot:o_slot + n_seq],
+                logit_rows=dev[o_rows:o_rows + n_rows], n_rows=n_rows,
+                decode_only=all(n == 1 for n in lens), kv_len_bound=kv_len,
+                dtype=self.dtype, workspace=workspace, new_lens=lens_for_parts,
+                past_lens=[q[1] for q in seqs]), tables
+
+        return total, fill, context
+
     # ------------------------------------------------------------------ the step
     def step(self, entries: Sequence[StepEntry]) -> Tensor:
         """Run one batch; returns logits [n_rows, vocab] float32 in the order of the entries
@@ -226,91 +337,63 @@ class ModelRunner:
                 self.start(e.req)
             cache.grow(e.req, cache.lengths[e.req] + len(e.tokens))
 
-        n_seq = len(entries)
         new_lens = [len(e.tokens) for e in entries]
         past = [cache.lengths[e.req] for e in entries]
         T = sum(new_lens)
-        n_rows = sum(len(e.want) for e in entries)
+        rows = [t0 + int(w) for e, t0 in zip(entries, np.cumsum([0] + new_lens[:-1]).tolist()) for w in e.want]
+        n_rows = len(rows)
         groups = list(cache.groups.values())
         kv_len = max(p + n for p, n in zip(past, new_lens))
+        seqs = [(token_arrays[s], past[s], cache.slot(e.req), e.req) for s, e in enumerate(entries)]
         # Steps of a shape that has been seen before are replayed from a CUDA graph (the host
         # issues hundreds of launches per step otherwise).  Such steps use block tables of a
         # fixed width and a key-length bound rounded up to a power of two, so that the launch
         # shapes depend on the key only.
         graph_key = None
+        rounded = None
         if self.graphs is not None and kv_len <= self.graphs.max_seq_len and T >= _STEP_GRAPH_SMALL_FROM:
             kv_len = min(self.graphs.max_seq_len, 1 << (kv_len - 1).bit_length())
-            graph_key = (tuple(new_lens), n_rows, kv_len)
             widths = [g.blocks_for(self.graphs.max_seq_len) for g in groups]
+            rounded = self._rounded_shape(new_lens, n_rows, kv_len)
+            graph_key = rounded[0] if rounded is not None else (tuple(new_lens), n_rows, kv_len)
         else:
             widths = [max(len(g.tables[e.req]) for e in entries) for g in groups]
-
-        # one packed int32 upload: tokens | positions | seq_of | cu | slots | rows | tables...
-        o_tok, o_pos, o_seq = 0, T, 2 * T
-        o_cu = 3 * T
-        o_slot = o_cu + n_seq + 1
-        o_rows = o_slot + n_seq
-        o_tab = o_rows + n_rows
-        tab_offsets = []
-        total = o_tab
-        for w in widths:
-            tab_offsets.append(total)
-            total += n_seq * w
-
-        def fill(buf: np.ndarray) -> None:
-            t0 = 0
-            r = 0
-            buf[o_cu] = 0
-            for s, e in enumerate(entries):
-                n = new_lens[s]
-                buf[o_tok + t0:o_tok + t0 + n] = token_arrays[s]
-                buf[o_pos + t0:o_pos + t0 + n] = np.arange(past[s], past[s] + n, dtype=np.int32)
-                buf[o_seq + t0:o_seq + t0 + n] = s
-                buf[o_cu + s + 1] = t0 + n
-                buf[o_slot + s] = cache.slot(e.req)
-                for w in e.want:
-                    buf[o_rows + r] = t0 + int(w)
-                    r += 1
-                t0 += n
-            for g, w, off in zip(groups, widths, tab_offsets):
-                tab = buf[off:off + n_seq * w].reshape(n_seq, w)
-                tab[:] = g.num_pages  # the spare page: never owned, safe to touch
-                for s, e in enumerate(entries):
-                    row = g.tables[e.req]
-                    arr = np.asarray(row, dtype=np.int32)
-                    arr[arr < 0] = g.num_pages
-                    tab[s, :len(row)] = arr
-
-        def context(dev: Tensor, workspace: Workspace):
-            tables = {g.key: dev[off:off + n_seq * w].view(n_seq, w) for g, w, off in zip(groups, widths, tab_offsets)}
-            return StepContext(
-                n_tokens=T, n_seq=n_seq,
-                tokens=dev[o_tok:o_tok + T], positions=dev[o_pos:o_pos + T], seq_of=dev[o_seq:o_seq + T],
-                cu_seqlens=dev[o_cu:o_cu + n_seq + 1], slots=dev[o_slot:o_slot + n_seq],
-                logit_rows=dev[o_rows:o_rows + n_rows], n_rows=n_rows,
-                decode_only=all(n == 1 for n in new_lens), kv_len_bound=kv_len,
-                dtype=self.dtype, workspace=workspace, new_lens=new_lens, past_lens=past), tables
 
         large = T >= _STEP_GRAPH_MIN_TOKENS
         shapes = self._step_graphs if large else self._small_step_graphs
         entry = shapes.get(graph_key) if graph_key is not None else None
-        if entry is not None and entry.get("graph") is None and entry["seen"] >= 1:
-            self._capture_step(entry, total, fill, context)  # second time this shape comes: capture it
-        if entry is not None and entry.get("graph") is not None:
+        seen = self._shape_seen.get(graph_key, 0) if graph_key is not None else 0
+        if rounded is not None and (entry is not None or seen >= 1):
+            _, pad_lens, rows_b, kv_b = rounded
+            spare = cache.spare_slot
+            seqs_g = seqs + [(np.zeros(n, dtype=np.int32), 0, spare, None) for n in pad_lens]
+            rows_g = rows + rows[:1] * (rows_b - n_rows)
+            lens_g = LengthBounds(T + sum(pad_lens), len(seqs_g))
+            total, fill, context = self._layout(seqs_g, rows_g, groups, widths, kv_b, lens_g)
+        else:
+            total, fill, context = self._layout(seqs, rows, groups, widths, kv_len, new_lens)
+        # A shape is issued launch by launch the first time it comes and recorded the second time; a
+        # rounded shape is first issued once more in its padded form (the recording must find every
+        # library product and scratch size already seen) and recorded the third time.
+        if entry is None and graph_key is not None and seen >= (2 if rounded is not None else 1):
+            entry = self._capture_step(total, fill, context)
+            shapes[graph_key] = entry
+            self._evict_step_graphs(shapes, large)
+        if entry is not None:
             shapes.move_to_end(graph_key)
             self._staging.upload(total, fill, dev=entry["meta"])
             entry["graph"].replay()
             self._step_kernels_replayed += entry["kernels"]
-            logits = entry["logits"]
+            logits = entry["logits"][:n_rows]
         else:
             if graph_key is not None:
-                shapes[graph_key] = {"seen": 1}
-                while len(shapes) > (_STEP_GRAPH_CAPACITY if large else _STEP_GRAPH_SMALL_CAPACITY):
-                    shapes.popitem(last=False)
+                if len(self._shape_seen) >= 4096:
+                    self._shape_seen.clear()
+                self._shape_seen[graph_key] = seen + 1
             dev = self._staging.upload(total, fill)
             self.workspace.reset()
             ctx, block_tables = context(dev, self.workspace)
-            logits = self.model.forward(ctx, cache.layer_caches(block_tables))
+            logits = self.model.forward(ctx, cache.layer_caches(block_tables))[:n_rows]
         self.h2d_bytes += 4 * total
         K.status_snapshot(self.device)  # read by check_kernels once the host has waited for this step
 

@@ -628,10 +628,13 @@ def ssm_scan_tc(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Tensor, 
     chunk_dt = chunk_decay + 4 * ((n_chunks * H + 3) // 4 * 4)
     start_state = chunk_dt + 4 * n_chunks * H * 2 * SSD_TC_CHUNK
     zp, ld_z, zs, zb = _gate_args(gate, out, "ssm_scan_tc")
+    n_multi = getattr(new_lens, "multi", None)  # lengths given as bounds carry the bound with them
+    if n_multi is None:
+        n_multi = sum(1 for n in new_lens if n > 1)
     _call("pmm_ssd_tc", xbc.data_ptr(), ld_x, dt_raw.data_ptr(), ld_dt, float(dt_scale), dt_shift.data_ptr(),
           a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), cu.data_ptr(), slots.data_ptr(), out.data_ptr(),
           chunk_state, chunk_decay, chunk_dt, start_state, len(new_lens), n_chunks, H, P, N, n_groups, zp, ld_z, zs, zb,
-          int(bool(skip_single)), sum(1 for n in new_lens if n > 1) if skip_single else 0,
+          int(bool(skip_single)), n_multi if skip_single else 0,
           _tc_status(xbc.device).data_ptr(), _stream())
 
 

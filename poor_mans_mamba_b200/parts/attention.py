@@ -183,6 +183,13 @@ class PagedAttention(Mixer):
                           split_counter=counter)
         return attn
 
+    def accepts_length_bounds(self, dtype: torch.dtype, page_size: int) -> bool:
+        # the tcgen05 kernel finds its tile's sequence from the lengths on the device, and a block
+        # beyond the last tile leaves; rotation and the page write go token by token
+        return (_TC_ATTENTION and dtype == torch.bfloat16 and hasattr(self.position_encoding, "inv_freq")
+                and getattr(self, "_split_counter", None) is not None
+                and K.attention_tc_supported(self.num_heads, self.num_kv_heads, self.head_dim, page_size))
+
     def plan_splits_tc(self, new_lens, kv_len_bound: int):
         """Key ranges for the tcgen05 kernel (128 rows a block, two blocks an SM): one range when
         the row tiles alone give a block per SM, else enough ranges of at least 256 keys to get there."""

@@ -172,6 +172,15 @@ class Mixer(Part):
     def output_bias(self) -> Optional[Tensor]:
         return None
 
+    def accepts_length_bounds(self, dtype: torch.dtype, page_size: int) -> bool:
+        """Whether this mixer's launches stay right when ``ctx.new_lens`` is not the true list of
+        tokens per sequence but a list of the same length and sum chosen so that every count
+        derived from it (chunks or tiles of any size, sequences of one token or of several) is an
+        upper bound of the true one, the true lengths being in ``ctx.cu_seqlens`` on the device:
+        kernels sized by such counts must let their surplus blocks leave.  Steps of recurring
+        rounded shapes are then recorded once and replayed whatever the cut (see ModelRunner)."""
+        return False
+
 
 class FeedForward(Part):
     """forward(x, ctx, out): x [T, D] normalised activations, out [T, D]."""

@@ -195,6 +195,10 @@ class ParallelPreNormBlock(Part):
             stream.add(out, self.ffn.out_scale)
         ws.release(mark)
 
+    def accepts_length_bounds(self, dtype: torch.dtype, page_size: int) -> bool:
+        """See Mixer.accepts_length_bounds: norms and feed-forwards go row by row, the mixers decide."""
+        return all(m.accepts_length_bounds(dtype, page_size) for m in self.mixers)
+
     def joins_side_stream(self, ctx) -> bool:
         """Whether this layer may start while ``ctx.unjoined_stream`` still works (a weight fetch that
         an earlier layer of the same kind left running: nothing this layer does depends on it)."""

@@ -160,6 +160,11 @@ class Mamba2Mixer(Mixer):
     def output_bias(self) -> Optional[Tensor]:
         return self.out_b
 
+    def accepts_length_bounds(self, dtype: torch.dtype, page_size: int) -> bool:
+        # the tcgen05 scan's blocks find their chunk's sequence from the lengths on the device and
+        # leave when there is none; the convolution and the lone tokens' scan go by token or sequence
+        return _TC_SCAN and dtype == torch.bfloat16 and K.ssd_tc_supported(self.d_head, self.d_state)
+
     def pre_output(self, proj: Tensor, ctx, cache) -> Tensor:
         T = proj.shape[0]
         ws = ctx.workspace

@@ -108,3 +108,61 @@ def test_bfloat16_agrees_with_the_float32_engine(model_05b):
     scale = float(outs["float32"].abs().max())
     diff = (outs["bfloat16"] - outs["float32"]).abs()
     assert float(diff.max()) <= 0.015 * scale and float(diff.mean()) <= 0.0025 * scale
+
+
+def test_rounded_step_graphs_serve_different_cuts(model_05b):
+    """Large steps are recorded under a rounded shape (sequences padded to a power of two, tokens to
+    a multiple of 64, lengths given to the parts as bounds) and replayed for every cut that rounds
+    to it.  Four rounds cut the same three prompts differently; their first steps all round to
+    (512 tokens, 4 sequences), their second steps (two continued prompts beside a decoding request,
+    447 tokens) to (512, 4) with other rows and key bound: each shape is issued twice launch by launch (exact, then padded),
+    recorded in the third round and replayed in the fourth.  Every wanted row of every round
+    against float64, and the padding leaves no trace in the cache's accounting."""
+    d, cfg, weights = model_05b
+    from poor_mans_mamba_b200.engine.runner import StepEntry
+    from gpu_harness import check_rows, make_runner
+    rng = random.Random(11)
+    V = cfg["vocab_size"]
+    seqs = {k: [rng.randrange(V) for _ in range(n)] for k, n in (("A", 700), ("B", 520), ("C", 300), ("D", 140))}
+    ref = {k: forward_logits(s, weights, cfg, torch.float64) for k, s in seqs.items()}
+    runner = make_runner(d, "bfloat16", page_size=64, num_pages=40, num_slots=5)
+    runner.enable_graphs(1024)
+    assert runner.model.accepts_length_bounds(64)
+    compared = 0
+
+    def step(portions, what):
+        """portions: [(name, request id, start, count, wanted places)]"""
+        nonlocal compared
+        entries = [StepEntry(rid, seqs[k][a:a + n], want) for k, rid, a, n, want in portions]
+        logits = runner.step(entries).float().cpu()
+        r = 0
+        for k, rid, a, n, want in portions:
+            for w in want:
+                check_rows(logits[r:r + 1], ref[k][a + w:a + w + 1], "bfloat16", f"{what}: {k} at {a + w}")
+                r += 1
+                compared += 1
+        assert r == logits.shape[0]
+
+    runner.step([StepEntry("d", seqs["D"][:130], [])])
+    cuts = [(200, 150, 120), (180, 200, 100), (250, 130, 110), (170, 170, 160)]
+    for rnd, (a, b, c) in enumerate(cuts):
+        ids = {k: (k, rnd) for k in "ABC"}
+        want_c = [0, c // 2, c - 1] + ([7] if rnd % 2 else [])       # 9 or 10 rows: both round to 16
+        step([("A", ids["A"], 0, a, [0, a // 2, a - 1]), ("B", ids["B"], 0, b, [1, b - 2, b - 1]),
+              ("C", ids["C"], 0, c, want_c)], f"round {rnd} first step")
+        a2, b2 = 256 + rnd, 190 - rnd
+        step([("A", ids["A"], a, a2, [0, 63, a2 - 1]), ("B", ids["B"], b, b2, [b2 - 1]),
+              ("D", "d", 130 + rnd, 1, [0])], f"round {rnd} second step")
+        step([("A", ids["A"], a + a2, 700 - a - a2, [700 - a - a2 - 1]), ("B", ids["B"], b + b2, 520 - b - b2, [0]),
+              ("C", ids["C"], c, 300 - c, [300 - c - 1])], f"round {rnd} last step")
+        for rid in ids.values():
+            runner.finish(rid)
+        runner.cache.check()
+    runner.finish("d")
+    runner.check_kernels(wait=True)
+    recorded = {k: v.get("graph") is not None for k, v in runner._step_graphs.items() if k[0] == "rounded"}
+    # (the second steps' 448 tokens are rounded on to 512: below the largest step seen, sizes go in steps of 256)
+    assert recorded.get(("rounded", 512, 4, 16, 256)) and recorded.get(("rounded", 512, 4, 8, 512)), recorded
+    assert runner._step_kernels_replayed > 0
+    assert compared == 70
+    assert runner.cache.min_free_pages() == 40 and runner.cache.free_slots == 5

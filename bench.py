@@ -280,6 +280,62 @@ def reference_arm(args) -> int:
     return 0
 
 
+def serve_workload(args, cfg, full_layers, model_dir, checked) -> int:
+    """`--workload serve`: bursts of 32 requests through the Python entry point (`Engine.generate`:
+    scheduler, chunked prefill under a budget of 2,048 tokens a step, decoding of all live
+    requests, sampling).  Every burst has new prompts of 200 to 1,500 tokens (uniform, seed 5) and
+    generates 128 tokens per request, so no two prefill steps are cut alike.  `value` is tokens
+    (prompt and generated) per second of wall time, host token ids in and out, over --steps
+    bursts after --warmup bursts (at least 12: recordings of step shapes are made while warming
+    up, as a server makes them in its first seconds)."""
+    import torch
+
+    from poor_mans_mamba_b200.entry import Engine
+
+    n_req, new_tokens, bursts, warm = 32, 128, max(1, args.steps // 8), max(12, args.warmup)
+    rng = random.Random(5)
+    vocab = cfg["vocab_size"]
+
+    def burst():
+        return [[rng.randrange(vocab) for _ in range(rng.randrange(200, 1500))] for _ in range(n_req)]
+
+    with torch.cuda.device(0):
+        eng = Engine(model_dir, dtype=args.dtype, max_tokens=(n_req + 8) * 2048, max_seqs=64, page_size=64,
+                     max_batched_tokens=2048, max_seq_len=2048)
+        for _ in range(warm):
+            eng.generate(burst(), max_new_tokens=new_tokens, eos_token_id=-1)
+        torch.cuda.synchronize()
+        launches0 = eng.runner.mark_launches()
+        tokens, wall = 0, 0.0
+        with ClockSampler() as clocks:
+            for _ in range(bursts):
+                prompts = burst()
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                out = eng.generate(prompts, max_new_tokens=new_tokens, eos_token_id=-1)
+                wall += time.perf_counter() - t0
+                tokens += sum(map(len, prompts)) + sum(map(len, out))
+        launches = eng.runner.kernels_launched_since(launches0)
+        eng.runner.check_kernels(wait=True)
+        recorded = sorted(k[1:] for k in eng.runner._step_graphs if k[0] == "rounded")
+    record = config_record(cfg, args, full_layers)
+    record.update({"global_batch": n_req, "seq_len": 2048, "prompt_tokens": "200..1500", "new_tokens": new_tokens,
+                   "token_budget": 2048})
+    result = {
+        "metric": f"served tokens/s (bursts of 32 requests through Engine.generate, Falcon-H1-{args.sizes.upper()} layer sizes)",
+        "value": round(tokens / wall, 1), "unit": "tokens/s", "n_gpus": 1, "steps": bursts, "warmup": warm,
+        "ms_per_step": round(wall / bursts * 1e3, 2), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
+        "data": "synthetic: uniform random token ids and prompt lengths (seed 5), random-init weights (seed 2)",
+        "config": record, "clocks": clocks.summary(), "gpu_launches": int(launches),
+        "rounded_step_shapes_recorded": len(recorded), "impl": "ours", "checked": checked is not None,
+    }
+    if checked is not None:
+        result["check"] = checked
+    print(json.dumps(result))
+    return 0
+
+
 def mixed_workload(args, cfg, full_layers, nums, peaks, model_dir, checked) -> int:
     """`--workload mixed`: one step that mixes 32 decoding requests (contexts spread over
     1,024..4,096 tokens) with four prompt portions of 512 tokens (at depths 0, 512, 1,024 and 1,536
@@ -415,10 +471,12 @@ def main() -> int:
                     "(same layer sizes) where memory or time needs it")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
-    ap.add_argument("--workload", default="decode", choices=["decode", "mixed"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "serve"],
                     help="decode: the benchmark (decode steps of a batch, with prefill and other points beside it); "
                          "mixed: one step of 32 decoding requests at contexts of 1,024..4,096 tokens beside four "
-                         "prompt portions of 512 tokens, by default at Falcon-H1-1.5B-Deep layer sizes")
+                         "prompt portions of 512 tokens, by default at Falcon-H1-1.5B-Deep layer sizes; "
+                         "serve: bursts of 32 requests with prompts of 200..1,500 tokens and 128 generated tokens "
+                         "each through Engine.generate (--steps / 8 timed bursts), tokens/s of wall time")
     ap.add_argument("--no-check", dest="check", action="store_false",
                     help="skip the comparison with the plain implementation that runs before the timing: the first "
                          "two layers of the run's model, in the run's dtype, on the benchmark's schedule (a "
@@ -577,6 +635,8 @@ def main() -> int:
 
     if args.workload == "mixed":
         return mixed_workload(args, cfg, full_layers, nums, peaks, tmp, checked)
+    if args.workload == "serve":
+        return serve_workload(args, cfg, full_layers, tmp, checked)
 
     result = {}
     with torch.cuda.device(0):

@@ -349,21 +349,33 @@ class ModelRunner:
         # issues hundreds of launches per step otherwise).  Such steps use block tables of a
         # fixed width and a key-length bound rounded up to a power of two, so that the launch
         # shapes depend on the key only.
-        graph_key = None
+        exact_key = None
         rounded = None
         if self.graphs is not None and kv_len <= self.graphs.max_seq_len and T >= _STEP_GRAPH_SMALL_FROM:
             kv_len = min(self.graphs.max_seq_len, 1 << (kv_len - 1).bit_length())
             widths = [g.blocks_for(self.graphs.max_seq_len) for g in groups]
+            exact_key = (tuple(new_lens), n_rows, kv_len)
             rounded = self._rounded_shape(new_lens, n_rows, kv_len)
-            graph_key = rounded[0] if rounded is not None else (tuple(new_lens), n_rows, kv_len)
         else:
             widths = [max(len(g.tables[e.req]) for e in entries) for g in groups]
 
+        # Which form the step takes: "exact" (the batch as it is) or "padded" (its rounded shape), and
+        # under which key it is replayed, recorded or counted.  A shape is issued launch by launch
+        # the first time and recorded the second time; a rounded shape is first issued once more in
+        # its padded form (the recording must find every library product and scratch size already
+        # seen) and recorded the third time.  An exact shape that keeps coming (a benchmark's, a
+        # fixed chunk size) gets a recording of its own the third time: it saves the padding.
         large = T >= _STEP_GRAPH_MIN_TOKENS
         shapes = self._step_graphs if large else self._small_step_graphs
-        entry = shapes.get(graph_key) if graph_key is not None else None
-        seen = self._shape_seen.get(graph_key, 0) if graph_key is not None else 0
-        if rounded is not None and (entry is not None or seen >= 1):
+        seen = self._shape_seen
+        key, padded = exact_key, False
+        if rounded is not None and exact_key not in shapes:
+            came = seen.get(("came",) + exact_key, 0) + 1
+            seen[("came",) + exact_key] = came
+            if came < 3:
+                key = rounded[0]
+                padded = key in shapes or seen.get(key, 0) >= 1
+        if padded:
             _, pad_lens, rows_b, kv_b = rounded
             spare = cache.spare_slot
             seqs_g = seqs + [(np.zeros(n, dtype=np.int32), 0, spare, None) for n in pad_lens]
@@ -372,24 +384,24 @@ class ModelRunner:
             total, fill, context = self._layout(seqs_g, rows_g, groups, widths, kv_b, lens_g)
         else:
             total, fill, context = self._layout(seqs, rows, groups, widths, kv_len, new_lens)
-        # A shape is issued launch by launch the first time it comes and recorded the second time; a
-        # rounded shape is first issued once more in its padded form (the recording must find every
-        # library product and scratch size already seen) and recorded the third time.
-        if entry is None and graph_key is not None and seen >= (2 if rounded is not None else 1):
+        entry = shapes.get(key) if key is not None else None
+        if entry is None and key is not None and seen.get(key, 0) >= (2 if key is not exact_key else 1):
             entry = self._capture_step(total, fill, context)
-            shapes[graph_key] = entry
+            shapes[key] = entry
             self._evict_step_graphs(shapes, large)
         if entry is not None:
-            shapes.move_to_end(graph_key)
+            shapes.move_to_end(key)
             self._staging.upload(total, fill, dev=entry["meta"])
             entry["graph"].replay()
             self._step_kernels_replayed += entry["kernels"]
             logits = entry["logits"][:n_rows]
         else:
-            if graph_key is not None:
-                if len(self._shape_seen) >= 4096:
-                    self._shape_seen.clear()
-                self._shape_seen[graph_key] = seen + 1
+            if key is not None:
+                if len(seen) >= 8192:
+                    seen.clear()
+                seen[key] = seen.get(key, 0) + 1
+                if not padded and key is not exact_key:
+                    seen[exact_key] = seen.get(exact_key, 0) + 1  # the exact form has been issued, too
             dev = self._staging.upload(total, fill)
             self.workspace.reset()
             ctx, block_tables = context(dev, self.workspace)

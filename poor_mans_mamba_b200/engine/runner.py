@@ -248,6 +248,36 @@ class ModelRunner:
         rows_b = 1 << (n_rows - 1).bit_length() if n_rows > 0 else 0
         return ("rounded", T_b, n_seq_b, rows_b, kv_b), pad_lens, rows_b, kv_b
 
+    def _choose_form(self, shapes, exact_key, rounded_key):
+        """(key, padded, record) for a step: the key it is replayed, recorded or counted under,
+        whether it runs in the padded form of its rounded shape, and whether it is recorded now.
+        ``shapes`` holds the recordings; `_note_issued` counts the steps issued launch by launch."""
+        seen = self._shape_seen
+        key, padded = exact_key, False
+        if rounded_key is not None and exact_key not in shapes:
+            came = seen.get(("came",) + exact_key, 0) + 1
+            seen[("came",) + exact_key] = came
+            if came < 3:
+                key = rounded_key
+                padded = key in shapes or seen.get(key, 0) >= 1
+        if key is None or key in shapes:
+            record = False
+        elif key is exact_key:
+            record = seen.get(key, 0) >= 1      # issued as it is at least once
+        else:
+            record = seen.get(key, 0) >= 2      # issued as it is and once more in its padded form
+        return key, padded, record
+
+    def _note_issued(self, key, exact_key, padded: bool) -> None:
+        if key is None:
+            return
+        seen = self._shape_seen
+        if len(seen) >= 8192:
+            seen.clear()
+        seen[key] = seen.get(key, 0) + 1
+        if not padded and key is not exact_key:
+            seen[exact_key] = seen.get(exact_key, 0) + 1  # the exact form has been issued, too
+
     def _layout(self, seqs, rows: List[int], groups, widths: List[int], kv_len: int, lens_for_parts):
         """One packed int32 upload for a batch of sequences (token ids, tokens already held, state
         slot, request or None for padding): tokens | positions | seq_of | cu | slots | rows | block
@@ -367,14 +397,7 @@ class ModelRunner:
         # fixed chunk size) gets a recording of its own the third time: it saves the padding.
         large = T >= _STEP_GRAPH_MIN_TOKENS
         shapes = self._step_graphs if large else self._small_step_graphs
-        seen = self._shape_seen
-        key, padded = exact_key, False
-        if rounded is not None and exact_key not in shapes:
-            came = seen.get(("came",) + exact_key, 0) + 1
-            seen[("came",) + exact_key] = came
-            if came < 3:
-                key = rounded[0]
-                padded = key in shapes or seen.get(key, 0) >= 1
+        key, padded, record = self._choose_form(shapes, exact_key, rounded[0] if rounded is not None else None)
         if padded:
             _, pad_lens, rows_b, kv_b = rounded
             spare = cache.spare_slot
@@ -385,7 +408,7 @@ class ModelRunner:
         else:
             total, fill, context = self._layout(seqs, rows, groups, widths, kv_len, new_lens)
         entry = shapes.get(key) if key is not None else None
-        if entry is None and key is not None and seen.get(key, 0) >= (2 if key is not exact_key else 1):
+        if record:
             entry = self._capture_step(total, fill, context)
             shapes[key] = entry
             self._evict_step_graphs(shapes, large)
@@ -396,12 +419,7 @@ class ModelRunner:
             self._step_kernels_replayed += entry["kernels"]
             logits = entry["logits"][:n_rows]
         else:
-            if key is not None:
-                if len(seen) >= 8192:
-                    seen.clear()
-                seen[key] = seen.get(key, 0) + 1
-                if not padded and key is not exact_key:
-                    seen[exact_key] = seen.get(exact_key, 0) + 1  # the exact form has been issued, too
+            self._note_issued(key, exact_key, padded)
             dev = self._staging.upload(total, fill)
             self.workspace.reset()
             ctx, block_tables = context(dev, self.workspace)

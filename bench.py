@@ -286,13 +286,13 @@ def serve_workload(args, cfg, full_layers, model_dir, checked) -> int:
     requests, sampling).  Every burst has new prompts of 200 to 1,500 tokens (uniform, seed 5) and
     generates 128 tokens per request, so no two prefill steps are cut alike.  `value` is tokens
     (prompt and generated) per second of wall time, host token ids in and out, over --steps
-    bursts after --warmup bursts (at least 12: recordings of step shapes are made while warming
-    up, as a server makes them in its first seconds)."""
+    bursts after --warmup bursts (at least 28, about ten seconds: recordings of step shapes are made
+    while warming up, as a server makes them in its first seconds)."""
     import torch
 
     from poor_mans_mamba_b200.entry import Engine
 
-    n_req, new_tokens, bursts, warm = 32, 128, max(1, args.steps // 8), max(12, args.warmup)
+    n_req, new_tokens, bursts, warm = 32, 128, max(1, args.steps // 8), max(28, args.warmup)
     rng = random.Random(5)
     vocab = cfg["vocab_size"]
 

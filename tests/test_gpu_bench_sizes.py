@@ -116,16 +116,17 @@ def test_rounded_step_graphs_serve_different_cuts(model_05b):
     to it.  Four rounds cut the same three prompts differently; their first steps all round to
     (512 tokens, 4 sequences), their second steps (two continued prompts beside a decoding request,
     447 tokens) to (512, 4) with other rows and key bound: each shape is issued twice launch by launch (exact, then padded),
-    recorded in the third round and replayed in the fourth.  Every wanted row of every round
+    recorded in the third round and replayed in the fourth.  Two short prompts in two portions each
+    (71 and 80 tokens a step) round up to 256 tokens the same way.  Every wanted row of every round
     against float64, and the padding leaves no trace in the cache's accounting."""
     d, cfg, weights = model_05b
     from poor_mans_mamba_b200.engine.runner import StepEntry
     from gpu_harness import check_rows, make_runner
     rng = random.Random(11)
     V = cfg["vocab_size"]
-    seqs = {k: [rng.randrange(V) for _ in range(n)] for k, n in (("A", 700), ("B", 520), ("C", 300), ("D", 140))}
+    seqs = {k: [rng.randrange(V) for _ in range(n)] for k, n in (("A", 700), ("B", 520), ("C", 300), ("D", 140), ("S", 90), ("U", 61))}
     ref = {k: forward_logits(s, weights, cfg, torch.float64) for k, s in seqs.items()}
-    runner = make_runner(d, "bfloat16", page_size=64, num_pages=40, num_slots=5)
+    runner = make_runner(d, "bfloat16", page_size=64, num_pages=40, num_slots=7)
     runner.enable_graphs(1024)
     assert runner.model.accepts_length_bounds(64)
     compared = 0
@@ -152,10 +153,16 @@ def test_rounded_step_graphs_serve_different_cuts(model_05b):
               ("C", ids["C"], 0, c, want_c)], f"round {rnd} first step")
         a2, b2 = 256 + rnd, 190 - rnd
         step([("A", ids["A"], a, a2, [0, 63, a2 - 1]), ("B", ids["B"], b, b2, [b2 - 1]),
-              ("D", "d", 130 + rnd, 1, [0])], f"round {rnd} second step")
+              ("D", "d", 130 + 2 * rnd, 1, [0])], f"round {rnd} second step")
         step([("A", ids["A"], a + a2, 700 - a - a2, [700 - a - a2 - 1]), ("B", ids["B"], b + b2, 520 - b - b2, [0]),
               ("C", ids["C"], c, 300 - c, [300 - c - 1])], f"round {rnd} last step")
-        for rid in ids.values():
+        # short steps round up to 256 tokens: two short prompts in two portions each, the first beside the decoding request
+        s1, u1 = 40 + rnd, 30 - rnd
+        step([("S", ("S", rnd), 0, s1, [0, s1 - 1]), ("U", ("U", rnd), 0, u1, [u1 - 1]), ("D", "d", 131 + 2 * rnd, 1, [0])],
+             f"round {rnd} short step")
+        step([("S", ("S", rnd), s1, 90 - s1, [90 - s1 - 1]), ("U", ("U", rnd), u1, 61 - u1, [0, 61 - u1 - 1])],
+             f"round {rnd} second short step")
+        for rid in list(ids.values()) + [("S", rnd), ("U", rnd)]:
             runner.finish(rid)
         runner.cache.check()
     runner.finish("d")
@@ -163,6 +170,7 @@ def test_rounded_step_graphs_serve_different_cuts(model_05b):
     recorded = {k: v.get("graph") is not None for k, v in runner._step_graphs.items() if k[0] == "rounded"}
     # (the second steps' 448 tokens are rounded on to 512: below the largest step seen, sizes go in steps of 256)
     assert recorded.get(("rounded", 512, 4, 16, 256)) and recorded.get(("rounded", 512, 4, 8, 512)), recorded
+    assert recorded.get(("rounded", 256, 4, 4, 256)), recorded
     assert runner._step_kernels_replayed > 0
-    assert compared == 70
-    assert runner.cache.min_free_pages() == 40 and runner.cache.free_slots == 5
+    assert compared == 70 + 4 * 7
+    assert runner.cache.min_free_pages() == 40 and runner.cache.free_slots == 7

@@ -58,10 +58,13 @@ def make_runner(accepts=True, max_seq_len=4096, page_size=4):
 
 def test_rounding_rule():
     r = make_runner()
-    assert r._rounded_shape([100, 100], 2, 128) is None           # fewer than 256 tokens
+    key, pads, _, kv_b = r._rounded_shape([100, 100], 2, 128)      # short steps round up to 256 tokens
+    assert key == ("rounded", 256, 4, 4, 128) and pads == [55, 1] and kv_b == 128
+    assert r._rounded_shape([2], 1, 64)[0] == ("rounded", 256, 2, 2, 256) and r._rounded_shape([2], 1, 64)[1] == [254]
+    assert r._rounded_shape([200, 100], 9, 256)[0] == ("rounded", 320, 4, 16, 256)   # more rows than sequences
     assert r._rounded_shape([1] * 300, 300, 512) is None          # decoding only
     key, pads, rows_b, kv_b = r._rounded_shape([2048], 1, 2048)
-    assert key == ("rounded", 2112, 2, 1, 2048) and pads == [64] and rows_b == 1 and kv_b == 2048
+    assert key == ("rounded", 2112, 2, 2, 2048) and pads == [64] and rows_b == 2 and kv_b == 2048
     key, pads, rows_b, kv_b = r._rounded_shape([1000, 700, 300, 1, 1], 5, 1024)
     # five sequences: three padding sequences make eight; 2,002 tokens and three more round to 2,048
     assert key == ("rounded", 2048, 8, 8, 1024) and pads == [44, 1, 1]

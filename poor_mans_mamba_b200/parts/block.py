@@ -13,13 +13,13 @@ writes the stream once.
 from __future__ import annotations
 
 import os
-from typing import Dict, List, Optional, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 
 from ..kernels import ops as K
 from . import branches, streaming
-from .base import (FeedForward, LayerCache, LayerSpec, Mixer, Norm, ParamSpec, Part, PartSpec, StateSpec,
+from .base import (FeedForward, LayerCache, LayerSpec, Mixer, Norm, Part, PartSpec, StateSpec,
                    build_part, register_arrangement)
 from .norm import fold_branches
 

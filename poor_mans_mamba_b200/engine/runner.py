@@ -155,11 +155,15 @@ class ModelRunner:
         self._last_sampled = self._sampler.sample_device(logits, temperatures, seeds, steps)
         return self._last_sampled
 
-    def _capture_step(self, total: int, fill, context) -> dict:
-        """Record the forward pass of one step shape into a CUDA graph over buffers of its own."""
-        meta = torch.zeros(total, dtype=torch.int32, device=self.device)
+    def _capture_step(self, total: int, fill, context) -> Optional[dict]:
+        """Record the forward pass of one step shape into a CUDA graph over buffers of its own; None
+        when the device has no memory left for them."""
+        try:
+            meta = torch.zeros(total, dtype=torch.int32, device=self.device)
+            workspace = Workspace(self.device, initial_bytes=self.workspace.high_water + (8 << 20))
+        except torch.cuda.OutOfMemoryError:
+            return None  # no room for another recording: the caller issues the step launch by launch
         self._staging.upload(total, fill, dev=meta)
-        workspace = Workspace(self.device, initial_bytes=self.workspace.high_water + (8 << 20))
         workspace.freeze()
         ctx, tables = context(meta, workspace)
         graph = torch.cuda.CUDAGraph()
@@ -415,8 +419,12 @@ class ModelRunner:
         entry = shapes.get(key) if key is not None else None
         if record:
             entry = self._capture_step(total, fill, context)
-            shapes[key] = entry
-            self._evict_step_graphs(shapes, large)
+            if entry is not None:
+                shapes[key] = entry
+                self._evict_step_graphs(shapes, large)
+            else:
+                for _ in range(len(shapes) // 2):  # make room; this shape may be recorded when it comes again
+                    shapes.popitem(last=False)
         if entry is not None:
             shapes.move_to_end(key)
             self._staging.upload(total, fill, dev=entry["meta"])

@@ -44,13 +44,13 @@ class StepEntry:
 # short steps of ever new shapes cannot push out the shapes of chunked prefill: steps of at least
 # _STEP_GRAPH_MIN_TOKENS tokens (their workspaces are large: at most _STEP_GRAPH_CAPACITY of them and
 # _STEP_GRAPH_BYTES of workspace are kept), and shorter ones down to _STEP_GRAPH_SMALL_FROM tokens (a
-# short prompt costs the host 9 ms of launches when it is not replayed, 36 layers of the 0.5B sizes).
+# short prompt costs the host 10 ms of launches when it is not replayed, 36 layers of the 0.5B sizes).
 _STEP_GRAPH_MIN_TOKENS = 256
 _STEP_GRAPH_CAPACITY = 32
 _STEP_GRAPH_BYTES = 8 << 30
 _STEP_GRAPH_SMALL_FROM = 2
 _STEP_GRAPH_SMALL_CAPACITY = 24
-# Large steps are recorded under a rounded shape (see ModelRunner._rounded_shape) where the model's
+# Steps are recorded under a rounded shape (see ModelRunner._rounded_shape) where the model's
 # parts allow it, so that a server's ever-changing cuts share recordings: a 36-layer prompt step costs
 # the host 10 ms when issued launch by launch and the device 5.  PMM_ROUNDED_STEP_GRAPHS=0: exact
 # shapes only.

@@ -116,6 +116,7 @@ class ModelRunner:
         self._step_kernels_replayed = 0  # kernels inside the step graphs replayed so far
         self._accepts_bounds: Optional[bool] = None  # asked of the model when the first large step comes
         self._largest_rounded = 0
+        self.token_budget: Optional[int] = None  # the scheduler's tokens per step, where there is one (see _rounded_shape)
 
     def enable_graphs(self, max_seq_len: int, buckets=None) -> None:
         """Serve decode-only steps from CUDA graphs (captured per batch-size bucket on first use).
@@ -244,10 +245,16 @@ class ModelRunner:
         T_b = max(_STEP_GRAPH_MIN_TOKENS, -(-(T + n_pad) // _ROUND_TOKENS) * _ROUND_TOKENS)
         # Steps at the scheduler's token budget all round to one size.  The steps that end a burst of
         # prompts have any size: they are rounded four times as coarsely (up to 255 tokens of padding
-        # against being issued launch by launch), so that few recordings serve them.
-        self._largest_rounded = max(self._largest_rounded, T_b)
-        if T_b < self._largest_rounded:
-            T_b = min(self._largest_rounded, -(-T_b // (4 * _ROUND_TOKENS)) * (4 * _ROUND_TOKENS))
+        # against being issued launch by launch), so that few recordings serve them.  "At the budget":
+        # within _ROUND_TOKENS of `token_budget` where the engine has set it, else no smaller than the
+        # largest rounded step this runner has seen.
+        if self.token_budget is not None:
+            full = T + _ROUND_TOKENS >= self.token_budget
+        else:
+            self._largest_rounded = max(self._largest_rounded, T_b)
+            full = T_b >= self._largest_rounded
+        if not full:
+            T_b = -(-T_b // (4 * _ROUND_TOKENS)) * (4 * _ROUND_TOKENS)
         pad_lens = [T_b - T - (n_pad - 1)] + [1] * (n_pad - 1)
         kv_b = max(kv_len, 1 << (pad_lens[0] - 1).bit_length())
         if kv_b > self.graphs.max_seq_len:

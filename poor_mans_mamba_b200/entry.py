@@ -66,6 +66,7 @@ class Engine:
                     self.runner.graphs.capture_all()
         self.scheduler = Scheduler(self.cache, max_batched_tokens=max_batched_tokens, max_seqs=max_seqs,
                                    max_seq_len=max_seq_len, release=self.runner.finish)
+        self.runner.token_budget = max_batched_tokens  # steps of about this size are rounded finely when recorded
         self.sampler = Sampler(self.device)
         self._next_id = 0
         self.run_ahead = run_ahead and cuda_graphs

@@ -53,6 +53,7 @@ def make_runner(accepts=True, max_seq_len=4096, page_size=4):
     r.graphs = types.SimpleNamespace(max_seq_len=max_seq_len)
     r._accepts_bounds = None
     r._largest_rounded = 0
+    r.token_budget = None
     return r
 
 
@@ -163,3 +164,17 @@ def test_which_form_a_step_takes_as_shapes_recur():
     assert got == [("issue", "exact"), ("issue", "padded"), ("record", "exact"), ("replay", "exact")]
     # no graphs at all (key None): always issued
     assert comings(r2, shapes2, None, None) == ("issue", "exact", None)
+
+
+def test_rounding_at_the_schedulers_budget():
+    """With the scheduler's token budget known, steps within 64 tokens of it round to multiples of
+    64 and all others to multiples of 256, whatever came before."""
+    r = make_runner()
+    r.token_budget = 2048
+    assert r._rounded_shape([8000, 192], 1, 4096)[0][1] == 8256        # a step far above the budget changes nothing below
+    assert r._rounded_shape([1500, 540, 1, 1, 1, 1, 1, 1], 8, 2048)[0][:3] == ("rounded", 2112, 16)
+    assert r._rounded_shape([1990], 1, 2048)[0][1] == 2048
+    assert r._rounded_shape([1900, 1], 1, 2048)[0][1] == 2048          # 1,903 -> 1,920 -> 2,048
+    assert r._rounded_shape([1000, 1], 1, 1024)[0][1] == 1024
+    assert r._rounded_shape([1000, 30], 1, 1024)[0][1] == 1280
+    assert r._rounded_shape([40, 1], 1, 64)[0][1] == 256

@@ -93,6 +93,36 @@ def test_decode_graph_at_larger_shapes(shaped):
     assert runner.graphs.replays == 12
 
 
+def test_rounded_step_graphs_at_larger_shapes(shaped):
+    """Steps recorded under a rounded shape at these widths (head size 128, state size 256): four
+    rounds cut the two prompts differently into two steps each; all eight steps round to (256 tokens,
+    4 sequences), so the shape is issued twice launch by launch, recorded at its third coming and
+    replayed five times.  Three rows of every portion against the plain implementation."""
+    name, d, cfg, seqs, refs = shaped
+    from poor_mans_mamba_b200.engine import StepEntry
+    runner = H.make_runner(d, "bfloat16", page_size=64, num_pages=8, num_slots=2)
+    runner.enable_graphs(max_seq_len=256)
+    assert runner.model.accepts_length_bounds(64)
+    for rnd in range(4):
+        a, b = 60 + rnd, 20 - rnd
+        for what, cuts in (("first", ((0, a), (0, b))), ("second", ((a, len(seqs[0]) - a), (b, len(seqs[1]) - b)))):
+            wants = [[0, n // 2, n - 1] for _, n in cuts]
+            logits = runner.step([StepEntry(("r", i, rnd), seqs[i][p:p + n], w)
+                                  for i, ((p, n), w) in enumerate(zip(cuts, wants))]).float().cpu()
+            r = 0
+            for i, ((p, n), w) in enumerate(zip(cuts, wants)):
+                for k in w:
+                    H.check_rows(logits[r:r + 1], refs[i][p + k:p + k + 1], "bfloat16",
+                                 f"{name} round {rnd} {what} step, request {i} at {p + k}")
+                    r += 1
+        for i in range(2):
+            runner.finish(("r", i, rnd))
+        runner.cache.check()
+    runner.check_kernels(wait=True)
+    assert ("rounded", 256, 4, 8, 256) in runner._step_graphs, list(runner._step_graphs)
+    assert runner._step_kernels_replayed > 0
+
+
 # ---------------------------------------------------------------------------------------------
 # A small model whose attention takes the tcgen05 kernel (head size 64, pages of 64 tokens, steps
 # of 256 tokens and more).

@@ -229,10 +229,11 @@ class ModelRunner:
         The step is padded with sequences that belong to no request (tokens 0 from position 0, the
         spare state slot, block tables full of the spare page) up to a power of two of sequences
         (at least one padding sequence) and a multiple of _ROUND_TOKENS tokens, its wanted rows with
-        copies of the first up to the number of sequences (or a power of two above it).  The model sees the padded batch with
-        `LengthBounds` in place of the tokens per sequence, so every launch has the shape the key
-        gives it and the recording serves every cut of the real tokens; the real rows' results are
-        what they are without the padding (rows and sequences do not mix)."""
+        copies of the first up to the number of sequences (or a power of two above it).  The model
+        sees the padded batch with `LengthBounds` in place of the tokens per sequence, so every
+        launch has the shape the key gives it and the recording serves every cut of the real
+        tokens; the real rows' results are what they are without the padding (rows and sequences do
+        not mix)."""
         T, n_seq = sum(new_lens), len(new_lens)
         if T < _STEP_GRAPH_SMALL_FROM or max(new_lens) == 1 or not _ROUNDED_STEP_GRAPHS:
             return None

@@ -17,8 +17,10 @@ class LengthBounds(list):
     sequence and count - 1 sequences of one token.  Of all ways to cut ``total`` tokens into
     ``count`` sequences this one needs the most chunks (or tiles) of any size c: sum ceil(n_i / c)
     <= floor((total - count) / c) + count, reached here.  ``multi`` bounds the number of sequences
-    of more than one token.  The true lengths are in ``cu_seqlens`` on the device; only parts
-    that say `accepts_length_bounds` are ever given this."""
+    of more than one token.  The true lengths are in ``cu_seqlens`` on the device and some of them
+    may be zero (a cut with empty sequences needs no more blocks than one without: the bound
+    floor((total - k) / c) + k does not fall as k grows); only parts that say
+    `accepts_length_bounds` are ever given this."""
 
     def __init__(self, total: int, count: int):
         if count < 2 or total < count:

@@ -228,7 +228,8 @@ class ModelRunner:
 
         The step is padded with sequences that belong to no request (tokens 0 from position 0, the
         spare state slot, block tables full of the spare page) up to a power of two of sequences
-        (at least one padding sequence) and a multiple of _ROUND_TOKENS tokens, its wanted rows with
+        (at least one padding sequence, which takes the padding tokens; further ones are empty) and
+        a multiple of _ROUND_TOKENS tokens, its wanted rows with
         copies of the first up to the number of sequences (or a power of two above it).  The model
         sees the padded batch with `LengthBounds` in place of the tokens per sequence, so every
         launch has the shape the key gives it and the recording serves every cut of the real
@@ -243,7 +244,7 @@ class ModelRunner:
             return None
         n_seq_b = 1 << n_seq.bit_length()          # the next power of two above n_seq
         n_pad = n_seq_b - n_seq
-        T_b = max(_STEP_GRAPH_MIN_TOKENS, -(-(T + n_pad) // _ROUND_TOKENS) * _ROUND_TOKENS)
+        T_b = max(_STEP_GRAPH_MIN_TOKENS, -(-T // _ROUND_TOKENS) * _ROUND_TOKENS)
         # Steps at the scheduler's token budget all round to one size.  The steps that end a burst of
         # prompts have any size: they are rounded four times as coarsely (up to 255 tokens of padding
         # against being issued launch by launch), so that few recordings serve them.  "At the budget":
@@ -256,9 +257,13 @@ class ModelRunner:
             full = T_b >= self._largest_rounded
         if not full:
             T_b = -(-T_b // (4 * _ROUND_TOKENS)) * (4 * _ROUND_TOKENS)
-        pad_lens = [T_b - T - (n_pad - 1)] + [1] * (n_pad - 1)
-        kv_b = max(kv_len, 1 << (pad_lens[0] - 1).bit_length())
-        if kv_b > self.graphs.max_seq_len:
+        # The padding tokens all go to the first padding sequence; the others are empty and cost
+        # nothing.  (Padding sequences of one token each were measured first: every one is a read and
+        # write of the spare slot's state, 2.6 MB a layer at the 1.5B-Deep sizes, and 60 of them made
+        # a burst of the serve workload 10 % slower than no recording at all.)
+        pad_lens = [T_b - T] + [0] * (n_pad - 1)
+        kv_b = max(kv_len, 1 << (pad_lens[0] - 1).bit_length()) if pad_lens[0] > 0 else kv_len
+        if kv_b > self.graphs.max_seq_len or T_b < n_seq_b:
             return None
         # wanted rows: none, or as many as sequences (a server wants at most one per sequence), or the
         # next power of two above that

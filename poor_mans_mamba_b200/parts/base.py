@@ -176,8 +176,9 @@ class Mixer(Part):
         """Whether this mixer's launches stay right when ``ctx.new_lens`` is not the true list of
         tokens per sequence but a list of the same length and sum chosen so that every count
         derived from it (chunks or tiles of any size, sequences of one token or of several) is an
-        upper bound of the true one, the true lengths being in ``ctx.cu_seqlens`` on the device:
-        kernels sized by such counts must let their surplus blocks leave.  Steps of recurring
+        upper bound of the true one, the true lengths being in ``ctx.cu_seqlens`` on the device
+        (some of them may be zero: sequences that bring no token must be left alone): kernels sized
+        by such counts must let their surplus blocks leave.  Steps of recurring
         rounded shapes are then recorded once and replayed whatever the cut (see ModelRunner)."""
         return False
 

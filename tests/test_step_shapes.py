@@ -32,6 +32,8 @@ def test_length_bounds_need_the_most_blocks_of_any_cut(total, count):
             assert need <= most, (cut, c)
             reached = reached or need == most
         assert reached  # the bound is the largest need, not merely above it
+        for fewer in range(1, count):  # cuts in which count - fewer sequences are empty
+            assert all(sum(-(-n // c) for n in cut) <= most for cut in compositions(total, fewer))
     for cut in compositions(total, count):
         assert sum(1 for n in cut if n > 1) <= bounds.multi
     assert any(n == 1 for n in bounds) and max(bounds) >= 2
@@ -60,27 +62,28 @@ def make_runner(accepts=True, max_seq_len=4096, page_size=4):
 def test_rounding_rule():
     r = make_runner()
     key, pads, _, kv_b = r._rounded_shape([100, 100], 2, 128)      # short steps round up to 256 tokens
-    assert key == ("rounded", 256, 4, 4, 128) and pads == [55, 1] and kv_b == 128
+    assert key == ("rounded", 256, 4, 4, 128) and pads == [56, 0] and kv_b == 128
     assert r._rounded_shape([2], 1, 64)[0] == ("rounded", 256, 2, 2, 256) and r._rounded_shape([2], 1, 64)[1] == [254]
     assert r._rounded_shape([200, 100], 9, 256)[0] == ("rounded", 320, 4, 16, 256)   # more rows than sequences
     assert r._rounded_shape([1] * 300, 300, 512) is None          # decoding only
     key, pads, rows_b, kv_b = r._rounded_shape([2048], 1, 2048)
-    assert key == ("rounded", 2112, 2, 2, 2048) and pads == [64] and rows_b == 2 and kv_b == 2048
+    assert key == ("rounded", 2048, 2, 2, 2048) and pads == [0] and rows_b == 2 and kv_b == 2048
     key, pads, rows_b, kv_b = r._rounded_shape([1000, 700, 300, 1, 1], 5, 1024)
-    # five sequences: three padding sequences make eight; 2,002 tokens and three more round to 2,048
-    assert key == ("rounded", 2048, 8, 8, 1024) and pads == [44, 1, 1]
-    # below the largest size seen (2,112) sizes go in steps of 256
+    # five sequences: three padding sequences make eight, the first holds the 46 tokens up to 2,048
+    assert key == ("rounded", 2048, 8, 8, 1024) and pads == [46, 0, 0]
+    # below the largest size seen (2,048) sizes go in steps of 256
     key, pads, _, _ = r._rounded_shape([300, 27], 0, 512)
-    assert key == ("rounded", 512, 4, 0, 512) and pads == [184, 1]
+    assert key == ("rounded", 512, 4, 0, 512) and pads == [185, 0]
     key, pads, _, kv_b = r._rounded_shape([257], 1, 512)
     assert key[1] == 512 and pads == [255] and kv_b == 512
     for lens in ([256], [255, 1], [64] * 4, [1000, 3, 3, 3, 3, 3, 3, 3], [2047, 1]):
         key, pads, _, _ = r._rounded_shape(list(lens), 1, 4096)
         n_seq_b = key[2]
         assert n_seq_b & (n_seq_b - 1) == 0 and n_seq_b > len(lens) and len(pads) == n_seq_b - len(lens)
-        assert min(pads) >= 1 and key[1] == sum(lens) + sum(pads) and key[1] % 64 == 0
+        assert pads[0] >= 0 and not any(pads[1:]) and key[1] == sum(lens) + sum(pads) and key[1] % 64 == 0
     # a padding sequence longer than the context the graphs are made for: not rounded
-    assert make_runner(max_seq_len=32)._rounded_shape([30] * 9, 1, 32) is None      # 44 padding tokens in a row
+    assert make_runner(max_seq_len=32)._rounded_shape([30] * 9, 1, 32) is None      # 50 padding tokens in a row
+    assert make_runner()._rounded_shape([2] + [1] * 300, 1, 64) is None             # more sequences than tokens after rounding
     assert make_runner(max_seq_len=64)._rounded_shape([30] * 9, 1, 32) is not None
     assert make_runner(accepts=False)._rounded_shape([2048], 1, 2048) is None
 
@@ -100,16 +103,16 @@ def test_packed_indices_of_a_padded_batch():
     group = next(iter(c.groups.values()))
     spare_page, spare_slot = group.num_pages, c.spare_slot
     seqs = [(np.array([5, 6, 7, 8]), 2, c.slot("a"), "a"), (np.array([9, 10, 11]), 0, c.slot("b"), "b"),
-            (np.zeros(4, dtype=np.int32), 0, spare_slot, None), (np.zeros(1, dtype=np.int32), 0, spare_slot, None)]
+            (np.zeros(5, dtype=np.int32), 0, spare_slot, None), (np.zeros(0, dtype=np.int32), 0, spare_slot, None)]
     rows = [3, 6, 3, 3]
     total, fill, context = r._layout(seqs, rows, [group], [5], 16, LengthBounds(12, 4))
     buf = np.full(total, -7, dtype=np.int32)
     fill(buf)
     T = 12
     assert buf[:T].tolist() == [5, 6, 7, 8, 9, 10, 11, 0, 0, 0, 0, 0]
-    assert buf[T:2 * T].tolist() == [2, 3, 4, 5, 0, 1, 2, 0, 1, 2, 3, 0]           # positions
-    assert buf[2 * T:3 * T].tolist() == [0] * 4 + [1] * 3 + [2] * 4 + [3]            # sequence of each token
-    assert buf[3 * T:3 * T + 5].tolist() == [0, 4, 7, 11, 12]                         # token offsets
+    assert buf[T:2 * T].tolist() == [2, 3, 4, 5, 0, 1, 2, 0, 1, 2, 3, 4]           # positions
+    assert buf[2 * T:3 * T].tolist() == [0] * 4 + [1] * 3 + [2] * 5                  # sequence of each token
+    assert buf[3 * T:3 * T + 5].tolist() == [0, 4, 7, 12, 12]                         # token offsets: the last is empty
     assert buf[3 * T + 5:3 * T + 9].tolist() == [c.slot("a"), c.slot("b"), spare_slot, spare_slot]
     assert buf[3 * T + 9:3 * T + 13].tolist() == rows
     tab = buf[3 * T + 13:].reshape(4, 5)
@@ -171,10 +174,10 @@ def test_rounding_at_the_schedulers_budget():
     64 and all others to multiples of 256, whatever came before."""
     r = make_runner()
     r.token_budget = 2048
-    assert r._rounded_shape([8000, 192], 1, 4096)[0][1] == 8256        # a step far above the budget changes nothing below
-    assert r._rounded_shape([1500, 540, 1, 1, 1, 1, 1, 1], 8, 2048)[0][:3] == ("rounded", 2112, 16)
+    assert r._rounded_shape([8000, 192], 1, 4096)[0][1] == 8192        # a step far above the budget changes nothing below
+    assert r._rounded_shape([1500, 540, 1, 1, 1, 1, 1, 1], 8, 2048)[0][:3] == ("rounded", 2048, 16)
     assert r._rounded_shape([1990], 1, 2048)[0][1] == 2048
-    assert r._rounded_shape([1900, 1], 1, 2048)[0][1] == 2048          # 1,903 -> 1,920 -> 2,048
+    assert r._rounded_shape([1900, 1], 1, 2048)[0][1] == 2048          # 1,901 -> 1,920 -> 2,048
     assert r._rounded_shape([1000, 1], 1, 1024)[0][1] == 1024
     assert r._rounded_shape([1000, 30], 1, 1024)[0][1] == 1280
     assert r._rounded_shape([40, 1], 1, 64)[0][1] == 256
